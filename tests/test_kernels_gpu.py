@@ -1,0 +1,290 @@
+"""Numerics of the CUDA kernels against plain PyTorch fp32 references (one B200)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from titanic_flash_41_b200.formats import codecs
+from titanic_flash_41_b200.models import engine as E
+from titanic_flash_41_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16, 27, 32])
+def test_smallm_fp8_dense(M):
+    torch.manual_seed(M)
+    N, K = 384, 1024
+    w = torch.randn(N, K, device=DEV) * 0.05
+    fw = E.quant_fp8_device(w)
+    x = torch.randn(M, K, device=DEV).half()
+    out = torch.zeros(M, N, device=DEV)
+    native.call("tf_smallm_gemm", 0, fw.q, None, fw.s, None, 0, 0, K, K // 128, x, K, out, N, 0, N, K, M,
+                None, None, None, None, None, 1, 0, M, 0.0)
+    ref = x.float() @ E.dequant_fp8(fw).t()
+    assert _rel(out, ref) < 2e-3
+
+
+def test_smallm_fp8_dual_swiglu_and_kslice():
+    torch.manual_seed(0)
+    N, K, M = 256, 512, 7
+    w1, w3 = (E.quant_fp8_device(torch.randn(N, K, device=DEV) * 0.1) for _ in range(2))
+    x = torch.randn(M, K, device=DEV).half()
+    out = torch.zeros(M, N, device=DEV, dtype=torch.float16)
+    native.call("tf_smallm_gemm", 0, w1.q, w3.q, w1.s, w3.s, 0, 0, K, K // 128, x, K, out, N, 1, N, K, M,
+                None, None, None, None, None, 1, 0, M, 10.0)
+    g = torch.clamp(x.float() @ E.dequant_fp8(w1).t(), max=10.0)
+    u = torch.clamp(x.float() @ E.dequant_fp8(w3).t(), -10.0, 10.0)
+    assert _rel(out, g * torch.sigmoid(g) * u) < 3e-3
+
+
+def test_smallm_bf16_head():
+    torch.manual_seed(1)
+    N, K, M = 2048, 512, 9
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    out = torch.zeros(M, N, device=DEV)
+    native.call("tf_smallm_gemm", 2, w, None, None, None, 0, 0, K * 2, 0, x, K, out, N, 0, N, K, M,
+                None, None, None, None, None, 1, 0, M, 0.0)
+    assert _rel(out, x.float() @ w.float().t()) < 1e-3
+
+
+def _group_tables(ids, e_lo, e_hi):
+    T, k = ids.shape
+    i32 = dict(dtype=torch.int32, device=DEV)
+    El = e_hi - e_lo
+    t = dict(ge=torch.zeros(El, **i32), gs=torch.zeros(El, **i32), gc=torch.zeros(El, **i32),
+             ng=torch.zeros(1, **i32), sp=torch.zeros(T * k, **i32), nl=torch.zeros(1, **i32))
+    native.call("tf_route_group", ids, T * k, e_lo, e_hi, t["ge"], t["gs"], t["gc"], t["ng"], t["sp"], t["nl"])
+    return t
+
+
+def test_grouped_mxfp4_experts():
+    torch.manual_seed(2)
+    El, I, d, T, k = 6, 256, 512, 11, 2
+    w1, w3 = torch.randn(El, I, d, device=DEV) * 0.05, torch.randn(El, I, d, device=DEV) * 0.05
+    w2 = torch.randn(El, d, I, device=DEV) * 0.05
+    (p1, s1), (p3, s3), (p2, s2) = (E.quant_mxfp4_device(w) for w in (w1, w3, w2))
+    ids = torch.stack([torch.randperm(8, device=DEV)[:k] for _ in range(T)]).int()   # experts 0..7, local 1..6
+    e_lo, e_hi = 1, 7
+    t = _group_tables(ids, e_lo, e_hi)
+    h = torch.randn(T, d, device=DEV).half()
+    act = torch.zeros(T * k, I, device=DEV, dtype=torch.float16)
+    y = torch.zeros(T * k, d, device=DEV)
+    native.call("tf_smallm_gemm", 1, p1, p3, s1, s3, I * d // 2, I * d // 32, d // 2, d // 32, h, d, act, I,
+                1, I, d, 0, t["ge"], t["gs"], t["gc"], t["ng"], t["sp"], k, El, 16, 10.0)
+    native.call("tf_smallm_gemm", 1, p2, None, s2, None, d * I // 2, d * I // 32, I // 2, I // 32, act, I, y, d,
+                0, d, I, 0, t["ge"], t["gs"], t["gc"], t["ng"], t["sp"], 1, El, 16, 0.0)
+    d1, d3, d2 = E.dequant_mxfp4(p1, s1), E.dequant_mxfp4(p3, s3), E.dequant_mxfp4(p2, s2)
+    for r in range(T):
+        for j in range(k):
+            e = int(ids[r, j]) - e_lo
+            if not 0 <= e < El:
+                continue
+            g = torch.clamp(h[r].float() @ d1[e].t(), max=10.0)
+            u = torch.clamp(h[r].float() @ d3[e].t(), -10.0, 10.0)
+            a = (g * torch.sigmoid(g) * u)
+            assert _rel(act[r * k + j], a) < 5e-3
+            assert _rel(y[r * k + j], act[r * k + j].float() @ d2[e].t()) < 5e-3
+
+
+def test_add_norm_and_fp8_quant():
+    torch.manual_seed(3)
+    T, d = 5, 512
+    x = torch.randn(T, d, device=DEV).bfloat16()
+    delta = torch.randn(T, d, device=DEV)
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    x0 = x.clone()
+    h16 = torch.zeros(T, d, device=DEV, dtype=torch.float16)
+    q8 = torch.zeros(T, d, device=DEV, dtype=torch.uint8)
+    qs = torch.zeros(T, d // 128, device=DEV)
+    native.call("tf_add_norm", x, delta, 0, d, w, h16, None, q8, qs, T, d, 1e-6)
+    xr = (x0.float() + delta).bfloat16().float()
+    assert torch.equal(x.float(), xr)
+    ref = (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float())
+    assert _rel(h16, ref) < 5e-3
+    deq = q8.view(torch.float8_e4m3fn).float().view(T, d // 128, 128) * qs[:, :, None]
+    assert _rel(deq.view(T, d), ref) < 4e-2
+
+
+def test_router_matches_oracle():
+    from titanic_flash_41_b200.config import tiny_config
+    from titanic_flash_41_b200.models.oracle import route
+    torch.manual_seed(4)
+    T, Ex, d, k = 13, 64, 512, 6
+    cfg = tiny_config(n_experts=Ex, topk=k, scoring="sqrtsoftplus", router_bias=True, route_scale=1.5)
+    h = torch.randn(T, d, device=DEV).half()
+    gate = (torch.randn(Ex, d, device=DEV) / math.sqrt(d)).bfloat16()
+    bias = torch.randn(Ex, device=DEV) * 0.1
+    logits = torch.zeros(T, Ex, device=DEV)
+    ids = torch.zeros(T, k, device=DEV, dtype=torch.int32)
+    wts = torch.zeros(T, k, device=DEV)
+    native.call("tf_router", h, gate, bias, logits, ids, wts, T, Ex, d, k, 1, 1, 1.5)
+    ref_logits = h.float() @ gate.float().t()
+    assert _rel(logits, ref_logits) < 1e-4
+    rid, rw = route(logits.cpu(), cfg, bias.cpu())
+    assert torch.equal(ids.cpu().long(), rid)
+    assert torch.allclose(wts.cpu(), rw, atol=1e-5)
+
+
+def test_index_scores_and_topk():
+    torch.manual_seed(5)
+    T, Hi, Di, C, k = 8, 4, 128, 700, 64
+    keys_f = torch.randn(2, C, Di)
+    krow = Di // 2 + Di // 32
+    enc = codecs.index_key_encode(keys_f)                          # [2, C, 68]
+    kd = codecs.index_key_decode(enc, Di)
+    keys = enc.to(DEV).contiguous()
+    q = torch.randn(T, Hi, Di, device=DEV).bfloat16()
+    w = torch.rand(T, Hi, device=DEV)
+    region = torch.tensor([0] * 4 + [1] * 4, dtype=torch.int32, device=DEV)
+    nvalid = torch.tensor([700, 650, 3, 0, 129, 128, 127, 64], dtype=torch.int32, device=DEV)
+    scores = torch.full((T, 1024), 7.0, device=DEV)
+    native.call("tf_index_scores", q, w, region, nvalid, keys, C * krow, krow, T, Hi, Di, 4, scores, 1024, 0, 700)
+    ref = torch.einsum("thd,tcd->thc", q.float().cpu(), kd[region.cpu().long()]).relu()
+    ref = (ref * w.cpu()[:, :, None]).sum(1)
+    for r in range(T):
+        n = int(nvalid[r])
+        assert torch.allclose(scores[r, :n].cpu(), ref[r, :n], atol=2e-2, rtol=2e-3)
+    sel = torch.zeros(T, k, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(T, dtype=torch.int32, device=DEV)
+    # duplicate values to exercise ties
+    scores[0, 10:20] = scores[0, 5].item()
+    native.call("tf_topk_select", scores, 1024, nvalid, k, sel, cnt, None, 0, T)
+    for r in range(T):
+        n = int(nvalid[r])
+        s = scores[r, :n].cpu()
+        got = sel[r].cpu().tolist()
+        if n <= k:
+            assert got == list(range(n)) + [-1] * (k - n) and int(cnt[r]) == n
+            continue
+        order = torch.sort(s, descending=True, stable=True).indices[:k]
+        assert got == sorted(order.tolist())
+
+
+def test_sparse_attention_matches_reference():
+    torch.manual_seed(6)
+    T, Hl, Dh, window, ring, C, k = 6, 4, 128, 16, 64, 50, 12
+    win_row, comp_row = 144, 80
+    kv = torch.randn(2, ring, Dh) * 1.5
+    win = torch.zeros(2, ring, win_row, dtype=torch.uint8)
+    win[:, :, :Dh + Dh // 32] = codecs.kv_v41_encode(kv)
+    kvd = codecs.kv_v41_decode(win, Dh)
+    ck = torch.randn(2, C, Dh)
+    comp = torch.zeros(2, C, comp_row, dtype=torch.uint8)
+    comp[:, :, :Dh // 2 + Dh // 16] = codecs.kv_v41fp4_encode(ck)
+    ckd = codecs.kv_v41fp4_decode(comp, Dh)
+    pos = torch.tensor([3, 20, 70, 100, 5, 64], dtype=torch.int32)
+    region = torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    sel = torch.full((T, k), -1, dtype=torch.int32)
+    for r in range(T):
+        n = [0, 3, 12, 12, 1, 7][r]
+        sel[r, :n] = torch.sort(torch.randperm(C)[:n]).values.int()
+    q = (torch.randn(T, Hl, Dh) * 0.5).bfloat16()
+    sink = torch.randn(Hl) * 0.5
+    freqs = torch.tensor([10000.0 ** (-2.0 * j / 64) for j in range(32)])
+    nsplit = 3
+    dev = lambda t: t.to(DEV).contiguous()
+    part_o = torch.zeros(T, nsplit, Hl, Dh, device=DEV)
+    part_lse = torch.zeros(T, nsplit, Hl, device=DEV)
+    out = torch.zeros(T, Hl * Dh, device=DEV, dtype=torch.float16)
+    st = native.StatusWord(DEV)
+    native.call("tf_sparse_attention", dev(q), T, Hl, Dh, dev(pos), dev(region), dev(win), ring * win_row,
+                win_row, ring, window, dev(comp), C * comp_row, comp_row, dev(sel), k, None, C,
+                1 / math.sqrt(Dh), nsplit, part_o, part_lse, dev(sink), dev(freqs), 64, out, None, Hl * Dh, st.t)
+    st.check()
+    from titanic_flash_41_b200.models.oracle import apply_rope
+    for r in range(T):
+        p, rg = int(pos[r]), int(region[r])
+        nw = min(p + 1, window)
+        ks = [kvd[rg, (p - nw + 1 + i) % ring] for i in range(nw)]
+        ks += [ckd[rg, int(c)] for c in sel[r] if c >= 0]
+        Kmat = torch.stack(ks)
+        lg = q[r].float() @ Kmat.t() / math.sqrt(Dh)
+        lg = torch.cat([lg, sink[:, None]], 1)
+        P = torch.softmax(lg, -1)[:, :-1]
+        o = apply_rope((P @ Kmat)[None], torch.tensor([p]), freqs, inverse=True)[0]
+        assert _rel(out[r].cpu().view(Hl, Dh), o) < 1e-2, r
+
+
+def test_sampling_kernels():
+    torch.manual_seed(7)
+    V, rows = 5000, 4
+    lg = torch.randn(rows, V, device=DEV) * 3
+    am = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    native.call("tf_argmax", lg, V, V, rows, am, None)
+    assert am.cpu().tolist() == lg.argmax(-1).cpu().tolist()
+    sb = native.lib().tf_rowstat_bytes()
+    stat = torch.zeros(rows, sb, dtype=torch.uint8, device=DEV)
+    st = native.StatusWord(DEV)
+    T, top_p = 0.6, 0.95
+    native.call("tf_rowstats", lg, V, V, rows, T, top_p, stat, st.t)
+    st.check()
+    raw = stat.cpu().numpy().view(np.dtype([("m", "<f4"), ("thr", "<u4"), ("z", "<f8")]))
+    pr = torch.softmax(lg.double().cpu() / T, -1)
+    for r in range(rows):
+        srt, _ = torch.sort(pr[r], descending=True)
+        cs = torch.cumsum(srt, 0)
+        n_in = int((cs < top_p).sum()) + 1
+        mass = float(srt[:n_in].sum())
+        z_total = float(torch.exp((lg[r].double().cpu() - lg[r].max().item()) / T).sum())
+        assert abs(raw["z"][r][0] / z_total - mass) < 1e-6
+    # plain sampling (g = 0): empirical law of the drawn tokens follows the nucleus distribution
+    S = 4096
+    lg1 = lg[:1].expand(S, V).contiguous()
+    stat1 = stat[:1].expand(S, sb).contiguous()
+    u = torch.rand(S, 2, dtype=torch.float64, device=DEV)
+    R = torch.zeros(S, 1, dtype=torch.float64, device=DEV)
+    w = torch.zeros(S, 1, dtype=torch.float64, device=DEV)
+    nacc = torch.zeros(S, dtype=torch.int32, device=DEV)
+    tok = torch.zeros(S, dtype=torch.int32, device=DEV)
+    native.call("tf_spec_verify", lg1, None, stat1, None, None, u, S, 0, V, V, T, T, 0, R, w, nacc, tok, st.t)
+    st.check()
+    srt, idx = torch.sort(pr[0], descending=True)
+    n_in = int((torch.cumsum(srt, 0) < top_p).sum()) + 1
+    allowed = set(idx[:n_in].tolist())
+    toks = tok.cpu().tolist()
+    assert set(toks) <= allowed
+    top = int(idx[0])
+    want = float(srt[0] / srt[:n_in].sum())
+    got = toks.count(top) / S
+    assert abs(got - want) < 4 * math.sqrt(want * (1 - want) / S) + 1e-3
+
+
+def test_block_verification_preserves_target_law():
+    """Proposals from a draft law, verified against a target law: accepted/corrected first tokens
+    must follow the target law (chi-square-style tolerance)."""
+    torch.manual_seed(8)
+    V, S, g = 64, 20000, 2
+    tl = torch.randn(g + 1, V, device=DEV) * 1.5
+    dl = tl[:g] + torch.randn(g, V, device=DEV) * 0.8
+    T = 1.0
+    sb = native.lib().tf_rowstat_bytes()
+    st = native.StatusWord(DEV)
+    tstat = torch.zeros(g + 1, sb, dtype=torch.uint8, device=DEV)
+    dstat = torch.zeros(g, sb, dtype=torch.uint8, device=DEV)
+    native.call("tf_rowstats", tl, V, V, g + 1, T, 1.0, tstat, st.t)
+    native.call("tf_rowstats", dl, V, V, g, T, 1.0, dstat, st.t)
+    q = torch.softmax(dl.double(), -1)
+    props = torch.stack([torch.multinomial(q[i], S, replacement=True) for i in range(g)], 1).int().contiguous()
+    tlS = tl[None].expand(S, g + 1, V).contiguous()
+    dlS = dl[None].expand(S, g, V).contiguous()
+    u = torch.rand(S, g + 2, dtype=torch.float64, device=DEV)
+    R = torch.zeros(S, g + 1, dtype=torch.float64, device=DEV)
+    w = torch.zeros(S, g + 1, dtype=torch.float64, device=DEV)
+    nacc = torch.zeros(S, dtype=torch.int32, device=DEV)
+    tok = torch.zeros(S, dtype=torch.int32, device=DEV)
+    native.call("tf_spec_verify", tlS, dlS, tstat[None].expand(S, g + 1, sb).contiguous(),
+                dstat[None].expand(S, g, sb).contiguous(), props, u, S, g, V, V, T, T, 0, R, w, nacc, tok, st.t)
+    st.check()
+    first = torch.where(nacc > 0, props[:, 0], tok).long().cpu()
+    emp = torch.bincount(first, minlength=V).double() / S
+    p0 = torch.softmax(tl[0].double().cpu(), -1)
+    assert float((emp - p0).abs().max()) < 0.012
+    assert 0.2 < float((nacc > 0).double().mean()) < 1.0

@@ -204,13 +204,15 @@ class ModelConfig(_JsonMixin):
     @property
     def window_kv_bytes(self) -> int:
         """V4.1 window-cache bytes/token: e4m3 values + one ue8m0 per 32
-        (528 for a 512-wide latent; reference src/attention.rs:18-38)."""
-        return self.head_dim + self.head_dim // 32
+        (528 for a 512-wide latent; reference src/attention.rs:18-38); the row stride is rounded
+        up to 16 bytes so that rows of narrower latents stay vector-load aligned."""
+        return -(-(self.head_dim + self.head_dim // 32) // 16) * 16
 
     @property
     def compressed_kv_bytes(self) -> int:
-        """V4.1-FP4 bytes/entry: packed e2m1 + one e4m3 scale per 16 (288 at 512)."""
-        return self.head_dim // 2 + self.head_dim // 16
+        """V4.1-FP4 bytes/entry: packed e2m1 + one e4m3 scale per 16 (288 at 512), stride
+        rounded up to 16 bytes."""
+        return -(-(self.head_dim // 2 + self.head_dim // 16) // 16) * 16
 
     @property
     def index_key_bytes(self) -> int:

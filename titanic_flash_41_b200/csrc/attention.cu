@@ -1,0 +1,326 @@
+// Sparse MQA attention over the V4.1 caches: every query row attends to its sliding window
+// (FP8 rows, e4m3 + UE8M0/32), to the compressed entries its indexer selected (FP4 rows, e2m1 +
+// e4m3/16) and to a per-head sink.  One latent per key is both K and V.
+//
+// Layout of the work: a CTA owns one query row and walks 64-key chunks of that row's key list
+// (split s takes chunks s, s+nsplit, ...).  Keys are dequantised once per chunk into shared
+// memory (row-major for QK^T and transposed for PV), each warp owns 16 heads and runs both
+// contractions on m16n8k16 tensor-core tiles with an online base-2 softmax.  Partials
+// (normalised output + log2-sum-exp) are merged with the sink as an extra zero-valued logit,
+// then the inverse RoPE rotation is applied to the output tail (the value shares the key's
+// rotated latent; reference src/layer_attention.rs:1416-1423).  Partial/merge arithmetic follows
+// the reference's split decode (runtime/kernels/attention-dsv41-decode-v1/decode.cu:249-314):
+// fp32 normalised partials, base-2 LSE, empty splits at -1e30.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kChunk = 64;
+constexpr float kNegBig = -1e30f;
+
+struct AttnParams {
+  const __nv_bfloat16* q;     // [T, Hl, Dh] (RoPE applied)
+  int T, Hl, Dh;
+  const int* pos;             // [T]
+  const int* region;          // [T]
+  const uint8_t* win;         // [regions][ring][Dh + Dh/32]
+  long win_region_stride;
+  int ring, window;
+  int win_row, comp_row;      // row strides in bytes (multiples of 16)
+  const uint8_t* comp;        // [regions][maxC][Dh/2 + Dh/16] or null
+  long comp_region_stride;
+  const int* sel;             // [T, sel_stride] ascending ids, -1 = none
+  int sel_stride;
+  const int* sel_count;       // [T] or null (then scan for -1)
+  int maxC;
+  float scale_log2;           // softmax scale * log2(e)
+  int nsplit;
+  float* part_o;              // [T, nsplit, Hl, Dh]
+  float* part_lse;            // [T, nsplit, Hl]  (log2 domain; kNegBig when empty)
+  TfStatusWord* st;
+};
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int DH>
+__global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
+  constexpr int KS = DH + 8;          // row stride of Ks (halfs)
+  constexpr int VS = kChunk + 8;      // row stride of Vt (halfs)
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half* Ks = reinterpret_cast<__half*>(smem_raw);          // [64][KS]
+  __half* Vt = Ks + kChunk * KS;                             // [DH][VS]
+  __shared__ int key_src[kChunk];                            // >=0: window slot; <0: ~compressed id
+
+  const int r = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int pos = p.pos[r], reg = p.region[r];
+  const int nwin = min(pos + 1, p.window);
+  int nsel = 0;
+  if (p.comp) {
+    if (p.sel_count) nsel = p.sel_count[r];
+    else {
+      // ids are ascending with -1 padding at the end: binary search for the first -1
+      int lo = 0, hi = p.sel_stride;
+      const int* s = p.sel + (long)r * p.sel_stride;
+      while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (s[mid] >= 0) lo = mid + 1; else hi = mid;
+      }
+      nsel = lo;
+    }
+  }
+  const int nkeys = nwin + nsel;
+  const int nchunks = (nkeys + kChunk - 1) / kChunk;
+  const int h0 = warp * 16;
+  const bool warp_active = h0 < p.Hl;
+
+  // ---- Q fragments (pre-scaled)
+  uint32_t qf[DH / 16][4];
+  if (warp_active) {
+    const __nv_bfloat16* q0 = p.q + ((long)r * p.Hl + min(h0 + g, p.Hl - 1)) * DH;
+    const __nv_bfloat16* q8 = p.q + ((long)r * p.Hl + min(h0 + g + 8, p.Hl - 1)) * DH;
+    const bool v0 = h0 + g < p.Hl, v8 = h0 + g + 8 < p.Hl;
+#pragma unroll
+    for (int ks = 0; ks < DH / 16; ++ks) {
+      const int k = ks * 16 + 2 * t;
+      float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k));
+      float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k));
+      float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k + 8));
+      float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k + 8));
+      const float s0 = v0 ? p.scale_log2 : 0.f, s8 = v8 ? p.scale_log2 : 0.f;
+      qf[ks][0] = pack_h2(a.x * s0, a.y * s0);
+      qf[ks][1] = pack_h2(b.x * s8, b.y * s8);
+      qf[ks][2] = pack_h2(c.x * s0, c.y * s0);
+      qf[ks][3] = pack_h2(d.x * s8, d.y * s8);
+    }
+  }
+  float o[DH / 8][4];
+#pragma unroll
+  for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = kNegBig, m8 = kNegBig, l0 = 0.f, l8 = 0.f;
+
+  const int wrow = p.win_row, crow = p.comp_row;
+  const uint8_t* win = p.win + (long)reg * p.win_region_stride;
+  const uint8_t* comp = p.comp ? p.comp + (long)reg * p.comp_region_stride : nullptr;
+
+  for (int c = split; c < nchunks; c += p.nsplit) {
+    const int kbase = c * kChunk;
+    __syncthreads();
+    for (int kk = threadIdx.x; kk < kChunk; kk += blockDim.x) {
+      const int i = kbase + kk;
+      int src = 0x7fffffff;
+      if (i < nwin) {
+        src = (pos - nwin + 1 + i) % p.ring;
+      } else if (i < nkeys) {
+        int id = p.sel[(long)r * p.sel_stride + (i - nwin)];
+        if (id < 0 || id >= p.maxC) {
+          tf_report(p.st, TF_BAD_INDEX, 10, r, id);
+          id = 0;
+        }
+        src = ~id;
+      }
+      key_src[kk] = src;
+    }
+    __syncthreads();
+    // dequantise: 8 threads per key, 16 elements each
+    for (int it = threadIdx.x; it < kChunk * (DH / 16); it += blockDim.x) {
+      const int key = it % kChunk, seg = it / kChunk;
+      const int src = key_src[key];
+      float v[16];
+      if (src == 0x7fffffff) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+      } else if (src >= 0) {
+        const uint8_t* row = win + (long)src * wrow;
+        uint4 raw = *reinterpret_cast<const uint4*>(row + seg * 16);
+        const float sc = ue8m0_to_float(row[DH + (seg >> 1)]);
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t h2 = e4m3x2_to_h2(h[j]);
+          float2 f = __half22float2(*reinterpret_cast<__half2*>(&h2));
+          v[2 * j] = f.x * sc;
+          v[2 * j + 1] = f.y * sc;
+        }
+      } else {
+        const uint8_t* row = comp + (long)(~src) * crow;
+        uint2 raw = *reinterpret_cast<const uint2*>(row + seg * 8);
+        const float sc = e4m3_to_float(row[DH / 2 + seg]);
+        const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = e2m1_to_float((w[j >> 3] >> (4 * (j & 7))) & 0xfu) * sc;
+      }
+      __half* kd = Ks + key * KS + seg * 16;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) *reinterpret_cast<__half2*>(kd + j) = __floats2half2_rn(v[j], v[j + 1]);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) Vt[(seg * 16 + j) * VS + key] = __float2half(v[j]);
+    }
+    __syncthreads();
+    if (!warp_active) continue;
+
+    // ---- S = Q K^T for 8 key tiles
+    float s[kChunk / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < kChunk / 8; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      const __half* kr = Ks + (nt * 8 + g) * KS + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < DH / 16; ++ks) {
+        uint32_t b[2];
+        b[0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
+        b[1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
+        mma_f16_16816(s[nt], qf[ks], b);
+      }
+    }
+    // mask keys beyond the list
+    const int valid = nkeys - kbase;
+    float cm0 = kNegBig, cm8 = kNegBig;
+#pragma unroll
+    for (int nt = 0; nt < kChunk / 8; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int key = nt * 8 + 2 * t + (i & 1);
+        if (key >= valid) s[nt][i] = kNegBig;
+      }
+      cm0 = fmaxf(cm0, fmaxf(s[nt][0], s[nt][1]));
+      cm8 = fmaxf(cm8, fmaxf(s[nt][2], s[nt][3]));
+    }
+    cm0 = fmaxf(cm0, __shfl_xor_sync(0xffffffffu, cm0, 1));
+    cm0 = fmaxf(cm0, __shfl_xor_sync(0xffffffffu, cm0, 2));
+    cm8 = fmaxf(cm8, __shfl_xor_sync(0xffffffffu, cm8, 1));
+    cm8 = fmaxf(cm8, __shfl_xor_sync(0xffffffffu, cm8, 2));
+    const float nm0 = fmaxf(m0, cm0), nm8 = fmaxf(m8, cm8);
+    const float f0 = exp2f(m0 - nm0), f8 = exp2f(m8 - nm8);
+    m0 = nm0;
+    m8 = nm8;
+    l0 *= f0;
+    l8 *= f8;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      o[i][0] *= f0;
+      o[i][1] *= f0;
+      o[i][2] *= f8;
+      o[i][3] *= f8;
+    }
+    uint32_t pf[kChunk / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < kChunk / 8; ++nt) {
+      float p0 = exp2f(s[nt][0] - m0), p1 = exp2f(s[nt][1] - m0);
+      float p2 = exp2f(s[nt][2] - m8), p3 = exp2f(s[nt][3] - m8);
+      if (s[nt][0] <= kNegBig) p0 = 0.f;
+      if (s[nt][1] <= kNegBig) p1 = 0.f;
+      if (s[nt][2] <= kNegBig) p2 = 0.f;
+      if (s[nt][3] <= kNegBig) p3 = 0.f;
+      l0 += p0 + p1;
+      l8 += p2 + p3;
+      // C tiles (2j, 2j+1) of S become the A fragment of k16 step j
+      pf[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(p0, p1);
+      pf[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(p2, p3);
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int dt = 0; dt < DH / 8; ++dt) {
+      const __half* vr = Vt + (dt * 8 + g) * VS + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < kChunk / 16; ++ks) {
+        uint32_t b[2];
+        b[0] = *reinterpret_cast<const uint32_t*>(vr + ks * 16);
+        b[1] = *reinterpret_cast<const uint32_t*>(vr + ks * 16 + 8);
+        mma_f16_16816(o[dt], pf[ks], b);
+      }
+    }
+  }
+  if (!warp_active) return;
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l8 += __shfl_xor_sync(0xffffffffu, l8, 1);
+  l8 += __shfl_xor_sync(0xffffffffu, l8, 2);
+  const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i8 = l8 > 0.f ? 1.f / l8 : 0.f;
+  const long base = ((long)r * p.nsplit + split) * p.Hl;
+  if (h0 + g < p.Hl) {
+    float* po = p.part_o + (base + h0 + g) * DH;
+#pragma unroll
+    for (int dt = 0; dt < DH / 8; ++dt)
+      *reinterpret_cast<float2*>(po + dt * 8 + 2 * t) = make_float2(o[dt][0] * i0, o[dt][1] * i0);
+    if (t == 0) p.part_lse[base + h0 + g] = l0 > 0.f ? m0 + log2f(l0) : kNegBig;
+  }
+  if (h0 + g + 8 < p.Hl) {
+    float* po = p.part_o + (base + h0 + g + 8) * DH;
+#pragma unroll
+    for (int dt = 0; dt < DH / 8; ++dt)
+      *reinterpret_cast<float2*>(po + dt * 8 + 2 * t) = make_float2(o[dt][2] * i8, o[dt][3] * i8);
+    if (t == 0) p.part_lse[base + h0 + g + 8] = l8 > 0.f ? m8 + log2f(l8) : kNegBig;
+  }
+}
+
+// merge splits + sink, inverse RoPE on the tail, write f16 and/or bf16.  grid (T, Hl), block Dh.
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                  const float* __restrict__ sink, const int* __restrict__ pos,
+                                  const float* __restrict__ freqs, int nsplit, int Hl, int Dh, int rope_dim,
+                                  __half* __restrict__ out16, __nv_bfloat16* __restrict__ outb, int ldo) {
+  extern __shared__ float vals[];   // Dh
+  const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const float* lse = part_lse + ((long)r * nsplit) * Hl + h;
+  float mx = sink ? sink[h] * 1.4426950408889634f : kNegBig;
+  for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, lse[(long)s * Hl]);
+  float den = sink ? exp2f(sink[h] * 1.4426950408889634f - mx) : 0.f;
+  float acc = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float l = lse[(long)s * Hl];
+    if (l <= kNegBig) continue;
+    const float w = exp2f(l - mx);
+    den += w;
+    acc += w * part_o[(((long)r * nsplit + s) * Hl + h) * Dh + d];
+  }
+  vals[d] = den > 0.f ? acc / den : 0.f;
+  __syncthreads();
+  float v = vals[d];
+  const int tail0 = Dh - rope_dim;
+  if (d >= tail0) {
+    const int j = (d - tail0) >> 1;
+    float sn, cs;
+    sincosf((float)pos[r] * freqs[j], &sn, &cs);
+    const float other = vals[d ^ 1];
+    // inverse rotation: angle -> -angle
+    v = ((d - tail0) & 1) ? (-other * sn + v * cs) : (v * cs + other * sn);
+  }
+  const long off = (long)r * ldo + (long)h * Dh + d;
+  if (out16) out16[off] = __float2half(v);
+  if (outb) outb[off] = __float2bfloat16(v);
+}
+
+}  // namespace
+
+TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* pos, const int* region,
+                               const void* win, long win_region_stride, int win_row, int ring, int window,
+                               const void* comp, long comp_region_stride, int comp_row, const int* sel, int sel_stride,
+                               const int* sel_count, int maxC, float scale, int nsplit, float* part_o,
+                               float* part_lse, const float* sink, const float* freqs, int rope_dim,
+                               void* out16, void* outb, int ldo, void* status, cudaStream_t st) {
+  if (Dh != 128 && Dh != 64) return -1;
+  if (Hl > 64 || nsplit < 1 || (win_row % 16) || (comp && (comp_row % 16))) return -1;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.T = T; p.Hl = Hl; p.Dh = Dh; p.pos = pos; p.region = region;
+  p.win = (const uint8_t*)win; p.win_region_stride = win_region_stride; p.ring = ring; p.window = window; p.win_row = win_row; p.comp_row = comp_row;
+  p.comp = (const uint8_t*)comp; p.comp_region_stride = comp_region_stride; p.sel = sel;
+  p.sel_stride = sel_stride; p.sel_count = sel_count; p.maxC = maxC;
+  p.scale_log2 = scale * 1.4426950408889634f; p.nsplit = nsplit; p.part_o = part_o; p.part_lse = part_lse;
+  p.st = (TfStatusWord*)status;
+  const int warps = (Hl + 15) / 16;
+  dim3 grid(T, nsplit);
+  if (Dh == 128) {
+    const int smem = (kChunk * (128 + 8) + 128 * (kChunk + 8)) * 2;
+    sparse_attn_kernel<128><<<grid, warps * 32, smem, st>>>(p);
+  } else {
+    const int smem = (kChunk * (64 + 8) + 64 * (kChunk + 8)) * 2;
+    sparse_attn_kernel<64><<<grid, warps * 32, smem, st>>>(p);
+  }
+  dim3 mg(T, Hl);
+  attn_merge_kernel<<<mg, Dh, Dh * sizeof(float), st>>>(part_o, part_lse, sink, pos, freqs, nsplit, Hl, Dh,
+                                                        rope_dim, (__half*)out16, (__nv_bfloat16*)outb, ldo);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,552 @@
+// Row-wise kernels around the GEMMs: embedding gather, residual + RMSNorm (+FP8 quant),
+// attention pre-processing (RoPE, KV norm/quant/store, compressor pooling, index keys),
+// router + expert grouping, expert combine.  One CTA per row unless noted.
+//
+// Reference arithmetic restated here: RMSNorm kernels/core.cu:851-857; RoPE table
+// kernels/core.cu:980-999; K store runtime/kernels/kv-v41-v1/kv_store.cu:33-150 (fp32 norm ->
+// bf16 -> RoPE tail in fp32 -> bf16 -> e4m3 + UE8M0 per 32); gated pooling
+// kernels/core.cu:944-950 generalised from pairs to groups of `ratio`; router
+// kernels/moe_frontend.cuh:27-130; ordered route sum kernels/ffn_sum_shared.cuh:7-33.
+#include "common.cuh"
+
+namespace {
+
+// --------------------------------------------------------------------------- embedding
+__global__ void embed_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                             __nv_bfloat16* __restrict__ out, int d, int vocab, TfStatusWord* st) {
+  const int r = blockIdx.x;
+  int tok = tokens[r];
+  if (tok < 0 || tok >= vocab) {
+    if (threadIdx.x == 0) tf_report(st, TF_BAD_INDEX, 1, r, tok);
+    tok = 0;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + (long)tok * d);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long)r * d);
+  for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// --------------------------------------------------------------------------- residual + norm
+// x (bf16 residual stream) += delta (optional, f32 or bf16); then h = rmsnorm(x) * w written as
+// f16 (decode GEMMs), bf16, and/or FP8 e4m3 with one fp32 scale per 128 along K (tensor-core
+// GEMMs).  `sumsq_out` optionally receives the row's mean square.
+__global__ void add_norm_kernel(__nv_bfloat16* __restrict__ x, const void* __restrict__ delta,
+                                int delta_kind, int ldd, const __nv_bfloat16* __restrict__ w,
+                                __half* __restrict__ h16, __nv_bfloat16* __restrict__ hb,
+                                uint8_t* __restrict__ q8, float* __restrict__ qs, int d, float eps) {
+  extern __shared__ float row[];            // d floats
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  __nv_bfloat16* xr = x + (long)r * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = __bfloat162float(xr[i]);
+    if (delta) {
+      float dv = delta_kind == 0 ? reinterpret_cast<const float*>(delta)[(long)r * ldd + i]
+                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(delta)[(long)r * ldd + i]);
+      v = bf16_round(v + dv);
+      xr[i] = __float2bfloat16(v);
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = bf16_round(row[i] * inv * __bfloat162float(w[i]));
+    row[i] = v;
+    if (h16) h16[(long)r * d + i] = __float2half(v);
+    if (hb) hb[(long)r * d + i] = __float2bfloat16(v);
+  }
+  if (q8) {
+    __syncthreads();
+    // one warp per 128-wide block
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int b = warp; b < d / 128; b += nw) {
+      float v[4], am = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[j] = row[b * 128 + lane * 4 + j];
+        am = fmaxf(am, fabsf(v[j]));
+      }
+      am = warp_max(am);
+      const float s = fmaxf(am, 1e-12f) / 448.f;
+      uint32_t packed = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) packed |= (uint32_t)float_to_e4m3(v[j] / s) << (8 * j);
+      reinterpret_cast<uint32_t*>(q8 + (long)r * d + b * 128)[lane] = packed;
+      if (lane == 0) qs[(long)r * (d / 128) + b] = s;
+    }
+  }
+}
+
+// --------------------------------------------------------------------------- attention prep
+struct PrepParams {
+  const void* P;        // fused projection output [T, ldp]; kind 0 = f32, 1 = bf16
+  int p_kind, ldp;
+  int T;
+  const int* pos;       // [T] absolute position
+  const int* region;    // [T] conversation slot
+  const int* first_row; // [T] first row of this row's conversation in the launch
+  const int* last_pos;  // [T] last position of this row's conversation in the launch
+  int Hl, Dh, rope_dim;
+  const float* freqs;   // [rope_dim/2]
+  const float* cfreqs;  // compressed-entry frequencies
+  const __nv_bfloat16* kv_norm_w;
+  float eps;
+  // outputs
+  __nv_bfloat16* q_out; // [T, Hl, Dh]
+  uint8_t* win;         // window ring base for this layer: [regions][ring][Dh + Dh/32]
+  long win_region_stride;
+  int ring;
+  int win_row, comp_row, key_row;   // row strides in bytes
+  // column offsets inside P
+  int off_q, off_kv, off_cv, off_cg, off_iq, off_iw;   // -1 = absent
+  // compressor (source layers)
+  int ratio, Di, Hi;
+  const __nv_bfloat16* comp_norm_w;
+  float* carry;         // [regions][ratio][2*(Dh+Di)]
+  uint8_t* comp;        // [regions][maxC][Dh/2 + Dh/16]
+  uint8_t* keys;        // [regions][maxC][Di/2 + Di/32]
+  int maxC;
+  __nv_bfloat16* iq_out; // [T, Hi, Di]
+  float* iw_out;         // [T, Hi]
+  TfStatusWord* st;
+};
+
+__device__ __forceinline__ float ldp(const PrepParams& p, long row, int col) {
+  return p.p_kind == 0 ? reinterpret_cast<const float*>(p.P)[row * p.ldp + col]
+                       : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.P)[row * p.ldp + col]);
+}
+
+// encode Dh values (shared memory, already bf16-rounded) as a V41 window row
+__device__ void store_v41(const float* v, uint8_t* dst, int D) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int b = warp; b < D / 32; b += nw) {
+    float x = v[b * 32 + lane];
+    float am = warp_max(fabsf(x));
+    uint8_t code = ue8m0_ceil(am / 448.f);
+    float s = ue8m0_to_float(code);
+    dst[b * 32 + lane] = float_to_e4m3(x / s);
+    if (lane == 0) dst[D + b] = code;
+  }
+}
+// encode D values as a V41-FP4 compressed row: packed e2m1 + one e4m3 scale per 16
+__device__ void store_v41fp4(const float* v, uint8_t* dst, int D) {
+  for (int b = threadIdx.x; b < D / 16; b += blockDim.x) {
+    float am = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) am = fmaxf(am, fabsf(v[b * 16 + j]));
+    uint8_t sc = float_to_e4m3(fmaxf(am / 6.f, 0.015625f));
+    float s = e4m3_to_float(sc);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t lo = float_to_e2m1(v[b * 16 + 2 * j] / s), hi = float_to_e2m1(v[b * 16 + 2 * j + 1] / s);
+      dst[b * 8 + j] = (uint8_t)(lo | (hi << 4));
+    }
+    dst[D / 2 + b] = sc;
+  }
+}
+// encode Di values as an index key: packed e2m1 + one UE8M0 per 32
+__device__ void store_index_key(const float* v, uint8_t* dst, int D) {
+  for (int b = threadIdx.x; b < D / 32; b += blockDim.x) {
+    float am = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) am = fmaxf(am, fabsf(v[b * 32 + j]));
+    uint8_t code = (uint8_t)min((int)ue8m0_ceil(am / 6.f), 247);
+    float s = ue8m0_to_float(code);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t lo = float_to_e2m1(v[b * 32 + 2 * j] / s), hi = float_to_e2m1(v[b * 32 + 2 * j + 1] / s);
+      dst[b * 16 + j] = (uint8_t)(lo | (hi << 4));
+    }
+    dst[D / 2 + b] = code;
+  }
+}
+
+__global__ void attn_prep_kernel(PrepParams p) {
+  extern __shared__ float sm[];     // max(Dh, Dh+Di) floats + scratch
+  __shared__ float scratch[32];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int pos = p.pos[r], reg = p.region[r];
+  const int half_rd = p.rope_dim / 2, tail0 = p.Dh - p.rope_dim;
+
+  // ---- q: RoPE on the tail of every head
+  if (p.off_q >= 0) {
+    for (int i = tid; i < p.Hl * p.Dh; i += blockDim.x) {
+      const int dd = i % p.Dh;
+      float v = ldp(p, r, p.off_q + i);
+      if (dd >= tail0) {
+        const int j = (dd - tail0) >> 1;
+        float sn, cs;
+        sincosf((float)pos * p.freqs[j], &sn, &cs);
+        float other = ldp(p, r, p.off_q + (i ^ 1));
+        v = ((dd - tail0) & 1) ? (other * sn + v * cs) : (v * cs - other * sn);
+      }
+      p.q_out[(long)r * p.Hl * p.Dh + i] = __float2bfloat16(v);
+    }
+  }
+  // ---- kv latent: norm -> bf16 -> RoPE -> bf16 -> V41 row
+  if (p.off_kv >= 0) {
+    float ss = 0.f;
+    for (int i = tid; i < p.Dh; i += blockDim.x) {
+      float v = ldp(p, r, p.off_kv + i);
+      sm[i] = v;
+      ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)p.Dh + p.eps);
+    for (int i = tid; i < p.Dh; i += blockDim.x)
+      sm[i] = bf16_round(sm[i] * inv * __bfloat162float(p.kv_norm_w[i]));
+    __syncthreads();
+    float rot = 0.f;
+    int ri = -1;
+    if (tid < p.rope_dim) {
+      const int dd = tail0 + tid, j = tid >> 1;
+      float sn, cs;
+      sincosf((float)pos * p.freqs[j], &sn, &cs);
+      float a = sm[dd], o = sm[dd ^ 1];
+      rot = (tid & 1) ? (o * sn + a * cs) : (a * cs - o * sn);
+      ri = dd;
+    }
+    __syncthreads();
+    if (ri >= 0) sm[ri] = bf16_round(rot);
+    __syncthreads();
+    uint8_t* dst = p.win + (long)reg * p.win_region_stride + (long)(pos % p.ring) * p.win_row;
+    store_v41(sm, dst, p.Dh);
+    __syncthreads();
+  }
+  // ---- indexer query / weights
+  if (p.off_iq >= 0) {
+    for (int i = tid; i < p.Hi * p.Di; i += blockDim.x)
+      p.iq_out[(long)r * p.Hi * p.Di + i] = __float2bfloat16(ldp(p, r, p.off_iq + i));
+    for (int i = tid; i < p.Hi; i += blockDim.x) p.iw_out[(long)r * p.Hi + i] = ldp(p, r, p.off_iw + i);
+  }
+  // ---- compressor: pool the group this row completes
+  if (p.off_cv >= 0 && ((pos + 1) % p.ratio) == 0) {
+    const int C = p.Dh + p.Di, g = pos / p.ratio;
+    if (g >= p.maxC) {
+      if (tid == 0) tf_report(p.st, TF_BAD_INDEX, 2, r, g);
+      return;
+    }
+    const int first = p.first_row[r];
+    const float* car = p.carry + (long)reg * p.ratio * 2 * C;
+    for (int c = tid; c < C; c += blockDim.x) {
+      float mx = -INFINITY;
+      for (int j = 0; j < p.ratio; ++j) {
+        const int mr = r - (p.ratio - 1 - j);
+        float gt = (mr >= first) ? ldp(p, mr, p.off_cg + c)
+                                 : car[((pos - (p.ratio - 1 - j)) % p.ratio) * 2 * C + C + c];
+        mx = fmaxf(mx, gt);
+      }
+      float den = 0.f, num = 0.f;
+      for (int j = 0; j < p.ratio; ++j) {
+        const int mr = r - (p.ratio - 1 - j);
+        float gt, vv;
+        if (mr >= first) {
+          gt = ldp(p, mr, p.off_cg + c);
+          vv = ldp(p, mr, p.off_cv + c);
+        } else {
+          const float* cs = car + ((pos - (p.ratio - 1 - j)) % p.ratio) * 2 * C;
+          gt = cs[C + c];
+          vv = cs[c];
+        }
+        float e = __expf(gt - mx);
+        den += e;
+        num += e * vv;
+      }
+      sm[c] = num / den;
+    }
+    __syncthreads();
+    // index key from the pooled tail
+    store_index_key(sm + p.Dh, p.keys + ((long)reg * p.maxC + g) * p.key_row, p.Di);
+    // compressed latent: norm -> bf16 -> RoPE at the entry's own index -> bf16 -> FP4 row
+    float ss = 0.f;
+    for (int i = tid; i < p.Dh; i += blockDim.x) ss += sm[i] * sm[i];
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)p.Dh + p.eps);
+    for (int i = tid; i < p.Dh; i += blockDim.x)
+      sm[i] = bf16_round(sm[i] * inv * __bfloat162float(p.comp_norm_w[i]));
+    __syncthreads();
+    float rot = 0.f;
+    int ri = -1;
+    if (tid < p.rope_dim) {
+      const int dd = tail0 + tid, j = tid >> 1;
+      float sn, cs;
+      sincosf((float)g * p.cfreqs[j], &sn, &cs);
+      float a = sm[dd], o = sm[dd ^ 1];
+      rot = (tid & 1) ? (o * sn + a * cs) : (a * cs - o * sn);
+      ri = dd;
+    }
+    __syncthreads();
+    if (ri >= 0) sm[ri] = bf16_round(rot);
+    __syncthreads();
+    store_v41fp4(sm, p.comp + ((long)reg * p.maxC + g) * p.comp_row, p.Dh);
+  }
+}
+
+// Save the compressor inputs of rows whose group is still open at the end of the launch (they
+// are read by a later launch).  Runs after attn_prep_kernel on the same stream, so no row of
+// this launch still reads the slots being written.
+__global__ void carry_save_kernel(PrepParams p) {
+  const int r = blockIdx.x;
+  const int pos = p.pos[r], reg = p.region[r];
+  const int group_end = (pos / p.ratio + 1) * p.ratio - 1;
+  if (group_end <= p.last_pos[r]) return;
+  const int C = p.Dh + p.Di;
+  float* cs = p.carry + ((long)reg * p.ratio + (pos % p.ratio)) * 2 * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    cs[c] = ldp(p, r, p.off_cv + c);
+    cs[C + c] = ldp(p, r, p.off_cg + c);
+  }
+}
+
+// --------------------------------------------------------------------------- router
+// logits[r, e] = h[r,:] . gate[e,:]  (f16 activations, bf16 gate), one warp per (expert, row-block)
+__global__ void router_logits_kernel(const __half* __restrict__ h, const __nv_bfloat16* __restrict__ gate,
+                                     float* __restrict__ logits, int M, int E, int d) {
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= E) return;
+  const __nv_bfloat16* g = gate + (long)e * d;
+  for (int r0 = 0; r0 < M; r0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = lane * 8; k < d; k += 256) {
+      uint4 gv = *reinterpret_cast<const uint4*>(g + k);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+      float gf[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 f = __bfloat1622float2(g2[q]);
+        gf[2 * q] = f.x;
+        gf[2 * q + 1] = f.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (r0 + j < M) {
+          uint4 hv = *reinterpret_cast<const uint4*>(h + (long)(r0 + j) * d + k);
+          const __half2* h2 = reinterpret_cast<const __half2*>(&hv);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float2 f = __half22float2(h2[q]);
+            acc[j] = fmaf(f.x, gf[2 * q], acc[j]);
+            acc[j] = fmaf(f.y, gf[2 * q + 1], acc[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = warp_sum(acc[j]);
+      if (lane == 0 && r0 + j < M) logits[(long)(r0 + j) * E + e] = v;
+    }
+  }
+}
+
+// top-k per row (one warp per row) + weights.  scoring 0 = softmax, 1 = sqrtsoftplus.
+// Ties go to the lowest expert id; NaN keys count as +inf.
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                   int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
+                                   int scoring, int renorm, float scale) {
+  extern __shared__ float sc[];                       // [warps][2][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int r = blockIdx.x * nw + warp;
+  if (r >= M) return;
+  float* score = sc + (long)warp * 2 * E;
+  float* key = score + E;
+  const float* lg = logits + (long)r * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+  mx = warp_max(mx);
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    float x = lg[e], s;
+    if (scoring == 1) {
+      float sp = x > 20.f ? x : log1pf(expf(x));
+      s = sqrtf(sp);
+    } else {
+      s = expf(x - mx);
+      den += s;
+    }
+    score[e] = s;
+  }
+  den = warp_sum(den);
+  for (int e = lane; e < E; e += 32) {
+    if (scoring == 0) score[e] /= den;
+    float k = score[e] + (bias ? bias[e] : 0.f);
+    key[e] = isnan(k) ? INFINITY : k;
+  }
+  __syncwarp();
+  float wsum = 0.f;
+  for (int j = 0; j < topk; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      float k = key[e];
+      if (k > best || (k == best && e < bi)) {
+        best = k;
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+    if (bi == 0x7fffffff) bi = 0;
+    if (lane == 0) {
+      ids[(long)r * topk + j] = bi;
+      wts[(long)r * topk + j] = score[bi];
+      key[bi] = -INFINITY;
+    }
+    wsum += score[bi];
+    __syncwarp();
+  }
+  if (lane == 0) {
+    for (int j = 0; j < topk; ++j) {
+      float w = wts[(long)r * topk + j];
+      if (renorm) w = w / (wsum + 1e-20f);
+      wts[(long)r * topk + j] = w * scale;
+    }
+  }
+}
+
+// Group (token, slot) pairs by expert for the experts this rank owns: counting sort in one CTA.
+// Outputs: group_expert/start/count for the compacted active experts, n_groups, sorted_pairs.
+__global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
+                                   int* group_expert, int* group_start, int* group_count, int* n_groups,
+                                   int* sorted_pairs, int* n_local_pairs) {
+  extern __shared__ int cnt[];   // [E_local] counts, then offsets
+  const int El = e_hi - e_lo;
+  for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    int e = ids[i] - e_lo;
+    if (e >= 0 && e < El) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, ng = 0;
+    for (int e = 0; e < El; ++e) {
+      int c = cnt[e];
+      if (c > 0) {
+        group_expert[ng] = e;
+        group_start[ng] = off;
+        group_count[ng] = c;
+        ++ng;
+      }
+      cnt[e] = off;
+      off += c;
+    }
+    *n_groups = ng;
+    *n_local_pairs = off;
+  }
+  __syncthreads();
+  // stable placement in pair order (single thread per expert keeps the order deterministic)
+  for (int e = threadIdx.x; e < El; e += blockDim.x) {
+    int off = cnt[e];
+    for (int i = 0; i < n_pairs; ++i)
+      if (ids[i] - e_lo == e) sorted_pairs[off++] = i;
+  }
+}
+
+// out[r,:] = sum_j wts[r,j] * y_pair[r*topk+j,:] (experts of this rank only, fixed order) + shared[r,:]
+__global__ void moe_combine_kernel(const float* __restrict__ y_pair, const int* __restrict__ ids,
+                                   const float* __restrict__ wts, const float* __restrict__ shared_y,
+                                   float* __restrict__ out, int d, int topk, int e_lo, int e_hi) {
+  const int r = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      const int e = ids[r * topk + j];
+      if (e >= e_lo && e < e_hi) acc = fmaf(wts[r * topk + j], y_pair[(long)(r * topk + j) * d + i], acc);
+    }
+    if (shared_y) acc += shared_y[(long)r * d + i];
+    out[(long)r * d + i] = acc;
+  }
+}
+
+__global__ void cast_f32_to_f16_kernel(const float* in, __half* out, long n) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2half(in[i]);
+}
+
+}  // namespace
+
+TF_API int tf_embed(const int* tokens, const void* table, void* out, int T, int d, int vocab,
+                    void* status, cudaStream_t st) {
+  if (d % 8) return -1;
+  embed_kernel<<<T, 128, 0, st>>>(tokens, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, d, vocab,
+                                  (TfStatusWord*)status);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_add_norm(void* x, const void* delta, int delta_kind, int ldd, const void* w, void* h16,
+                       void* hb, void* q8, void* qs, int T, int d, float eps, cudaStream_t st) {
+  if (d % 128) return -1;
+  add_norm_kernel<<<T, 256, d * sizeof(float), st>>>((__nv_bfloat16*)x, delta, delta_kind, ldd,
+                                                     (const __nv_bfloat16*)w, (__half*)h16,
+                                                     (__nv_bfloat16*)hb, (uint8_t*)q8, (float*)qs, d, eps);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_attn_prep(const void* P, int p_kind, int ldp, int T, const int* pos, const int* region,
+                        const int* first_row, const int* last_pos, int Hl, int Dh, int rope_dim,
+                        const float* freqs, const float* cfreqs, const void* kv_norm_w, float eps,
+                        void* q_out, void* win, long win_region_stride, int win_row, int comp_row,
+                        int key_row, int ring, int off_q, int off_kv,
+                        int off_cv, int off_cg, int off_iq, int off_iw, int ratio, int Di, int Hi,
+                        const void* comp_norm_w, float* carry, void* comp, void* keys, int maxC,
+                        void* iq_out, float* iw_out, void* status, cudaStream_t st) {
+  if (Dh % 32 || rope_dim > 256 || (off_cv >= 0 && Di % 32)) return -1;
+  PrepParams p;
+  p.P = P; p.p_kind = p_kind; p.ldp = ldp; p.T = T; p.pos = pos; p.region = region;
+  p.first_row = first_row; p.last_pos = last_pos; p.Hl = Hl; p.Dh = Dh; p.rope_dim = rope_dim;
+  p.freqs = freqs; p.cfreqs = cfreqs; p.kv_norm_w = (const __nv_bfloat16*)kv_norm_w; p.eps = eps;
+  p.q_out = (__nv_bfloat16*)q_out; p.win = (uint8_t*)win; p.win_region_stride = win_region_stride;
+  p.ring = ring; p.win_row = win_row; p.comp_row = comp_row; p.key_row = key_row; p.off_q = off_q; p.off_kv = off_kv; p.off_cv = off_cv; p.off_cg = off_cg;
+  p.off_iq = off_iq; p.off_iw = off_iw; p.ratio = ratio; p.Di = Di; p.Hi = Hi;
+  p.comp_norm_w = (const __nv_bfloat16*)comp_norm_w; p.carry = carry; p.comp = (uint8_t*)comp;
+  p.keys = (uint8_t*)keys; p.maxC = maxC; p.iq_out = (__nv_bfloat16*)iq_out; p.iw_out = iw_out;
+  p.st = (TfStatusWord*)status;
+  const int smf = (off_cv >= 0 ? Dh + Di : Dh);
+  attn_prep_kernel<<<T, 256, smf * sizeof(float), st>>>(p);
+  if (off_cv >= 0) carry_save_kernel<<<T, 128, 0, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_router(const void* h16, const void* gate, const float* bias, float* logits, int* ids,
+                     float* wts, int M, int E, int d, int topk, int scoring, int renorm, float scale,
+                     cudaStream_t st) {
+  if (d % 256) return -1;
+  router_logits_kernel<<<(E + 7) / 8, 256, 0, st>>>((const __half*)h16, (const __nv_bfloat16*)gate,
+                                                    logits, M, E, d);
+  const int nw = 4;
+  router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
+      logits, bias, ids, wts, M, E, topk, scoring, renorm, scale);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_route_group(const int* ids, int n_pairs, int e_lo, int e_hi, int* group_expert,
+                          int* group_start, int* group_count, int* n_groups, int* sorted_pairs,
+                          int* n_local_pairs, cudaStream_t st) {
+  route_group_kernel<<<1, 256, (e_hi - e_lo) * sizeof(int), st>>>(
+      ids, n_pairs, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
+      n_local_pairs);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_moe_combine(const float* y_pair, const int* ids, const float* wts, const float* shared_y,
+                          float* out, int M, int d, int topk, int e_lo, int e_hi, cudaStream_t st) {
+  moe_combine_kernel<<<M, 256, 0, st>>>(y_pair, ids, wts, shared_y, out, d, topk, e_lo, e_hi);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_cast_f32_f16(const float* in, void* out, long n, cudaStream_t st) {
+  cast_f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, (__half*)out, n);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,296 @@
+// Indexer: scores of query rows against the FP4 index keys of their conversation, and exact
+// top-k selection.
+//
+//   score(row, key) = sum_h relu(q[row,h,:] . k[key,:]) * w[row,h]
+//
+// Keys are packed e2m1 + one UE8M0 per 32 (68 bytes at 128 dims; reference
+// kernels/index_bf16.cu:8-10); queries are bf16, accumulation is fp32 on m16n8k16 tiles with the
+// (padded) heads of one row as the MMA's M.  Row `r` scores keys [0, nvalid[r]); the rest of its
+// score row is -inf.  Selection is exact: ties at the cut go to the lower position and the
+// output ids are ascending (reference contract: kernels/index_bf16.cu:1-21, src/topk.rs).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kKeysPerCta = 128;
+
+struct ScoreParams {
+  const __nv_bfloat16* q;   // [T, Hi, Di]
+  const float* w;           // [T, Hi]
+  const int* region;        // [T]
+  const int* nvalid;        // [T]
+  const uint8_t* keys;      // [regions][maxC][key_row]
+  long key_region_stride;
+  int key_row;
+  int T, Hi, Di;
+  int rows_per_group;       // consecutive rows sharing a region handled by one CTA
+  float* scores;            // [T, lds]
+  int lds;
+  int key_lo, key_hi;       // this rank's key shard [lo, hi) (key-sharded scoring)
+};
+
+template <int DI>
+__global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
+  constexpr int KS = DI + 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half* Ks = reinterpret_cast<__half*>(smem_raw);   // [128][KS]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.y * p.rows_per_group;
+  const int nrows = min(p.rows_per_group, p.T - row0);
+  const int key0 = p.key_lo + blockIdx.x * kKeysPerCta;
+  int maxvalid = 0;
+  for (int i = 0; i < nrows; ++i) maxvalid = max(maxvalid, p.nvalid[row0 + i]);
+  maxvalid = min(maxvalid, p.key_hi);
+  if (key0 >= maxvalid) {
+    // still have to blank the tail of the score rows this CTA covers
+    for (int i = 0; i < nrows; ++i)
+      for (int k = threadIdx.x; k < kKeysPerCta; k += blockDim.x)
+        if (key0 + k < p.lds && key0 + k < p.key_hi) p.scores[(long)(row0 + i) * p.lds + key0 + k] = -INFINITY;
+    return;
+  }
+  const uint8_t* kb = p.keys + (long)p.region[row0] * p.key_region_stride;
+  // dequantise 128 keys: one thread per (key, 32-block)
+  for (int it = threadIdx.x; it < kKeysPerCta * (DI / 32); it += blockDim.x) {
+    const int key = it % kKeysPerCta, blk = it / kKeysPerCta;
+    __half* dst = Ks + key * KS + blk * 32;
+    if (key0 + key < maxvalid) {
+      const uint8_t* row = kb + (long)(key0 + key) * p.key_row;
+      const float sc = ue8m0_to_float(row[DI / 2 + blk]);
+      const uint32_t* wv = reinterpret_cast<const uint32_t*>(row + blk * 16);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t w = wv[q];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2)
+          *reinterpret_cast<__half2*>(dst + q * 8 + j) = __floats2half2_rn(
+              e2m1_to_float((w >> (4 * j)) & 0xfu) * sc, e2m1_to_float((w >> (4 * j + 4)) & 0xfu) * sc);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) *reinterpret_cast<__half2*>(dst + j) = __floats2half2_rn(0.f, 0.f);
+    }
+  }
+  __syncthreads();
+  const int head_tiles = (p.Hi + 15) / 16;
+  for (int ri = warp; ri < nrows; ri += 4) {
+    const int r = row0 + ri;
+    const int nv = min(p.nvalid[r], p.key_hi);
+    float tot[kKeysPerCta / 8][2];
+#pragma unroll
+    for (int nt = 0; nt < kKeysPerCta / 8; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
+    for (int ht = 0; ht < head_tiles; ++ht) {
+      const int h0 = ht * 16 + g, h8 = h0 + 8;
+      const bool v0 = h0 < p.Hi, v8 = h8 < p.Hi;
+      const __nv_bfloat16* q0 = p.q + ((long)r * p.Hi + min(h0, p.Hi - 1)) * DI;
+      const __nv_bfloat16* q8 = p.q + ((long)r * p.Hi + min(h8, p.Hi - 1)) * DI;
+      const float w0 = v0 ? p.w[(long)r * p.Hi + h0] : 0.f, w8 = v8 ? p.w[(long)r * p.Hi + h8] : 0.f;
+      uint32_t qf[DI / 16][4];
+#pragma unroll
+      for (int ks = 0; ks < DI / 16; ++ks) {
+        const int k = ks * 16 + 2 * t;
+        float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k));
+        float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k));
+        float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k + 8));
+        float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k + 8));
+        __half2 ha = __floats2half2_rn(a.x, a.y), hb = __floats2half2_rn(b.x, b.y);
+        __half2 hc = __floats2half2_rn(c.x, c.y), hd = __floats2half2_rn(d.x, d.y);
+        qf[ks][0] = *reinterpret_cast<uint32_t*>(&ha);
+        qf[ks][1] = *reinterpret_cast<uint32_t*>(&hb);
+        qf[ks][2] = *reinterpret_cast<uint32_t*>(&hc);
+        qf[ks][3] = *reinterpret_cast<uint32_t*>(&hd);
+      }
+#pragma unroll
+      for (int nt = 0; nt < kKeysPerCta / 8; ++nt) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const __half* kr = Ks + (nt * 8 + g) * KS + 2 * t;
+#pragma unroll
+        for (int ks = 0; ks < DI / 16; ++ks) {
+          uint32_t b[2];
+          b[0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
+          b[1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
+          mma_f16_16816(s, qf[ks], b);
+        }
+        tot[nt][0] += fmaxf(s[0], 0.f) * w0 + fmaxf(s[2], 0.f) * w8;
+        tot[nt][1] += fmaxf(s[1], 0.f) * w0 + fmaxf(s[3], 0.f) * w8;
+      }
+    }
+    // sum over the 8 head rows held by lanes with equal t
+#pragma unroll
+    for (int nt = 0; nt < kKeysPerCta / 8; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float v = tot[nt][i];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        tot[nt][i] = v;
+      }
+      if (g == 0) {
+        const int k = key0 + nt * 8 + 2 * t;
+        float* out = p.scores + (long)r * p.lds;
+        if (k < p.lds && k < p.key_hi) out[k] = k < nv ? tot[nt][0] : -INFINITY;
+        if (k + 1 < p.lds && k + 1 < p.key_hi) out[k + 1] = k + 1 < nv ? tot[nt][1] : -INFINITY;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// exact top-k per row by radix select on the order-preserving integer image of the float
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t float_key(float f) {
+  uint32_t b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// scores [T, lds]; n[r] valid entries; out ids [T, k] ascending, -1 padded; count[r] = min(n, k).
+// `base` is added to every id (key-sharded scoring passes the shard offset).
+__global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restrict__ scores, int lds,
+                                                           const int* __restrict__ nvalid, int k,
+                                                           int* __restrict__ out, int* __restrict__ count,
+                                                           float* __restrict__ out_scores, int base) {
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need, s_run, s_tie_run;
+  __shared__ int warp_tot[32][2];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int n = min(nvalid[r], lds);
+  const float* s = scores + (long)r * lds;
+  int* o = out + (long)r * k;
+  if (n <= k) {
+    for (int i = tid; i < k; i += blockDim.x) {
+      o[i] = i < n ? base + i : -1;
+      if (out_scores) out_scores[(long)r * k + i] = i < n ? s[i] : -INFINITY;
+    }
+    if (tid == 0 && count) count[r] = n;
+    return;
+  }
+  // find the k-th largest key: MSB-first radix over 4 bytes
+  if (tid == 0) {
+    s_prefix = 0;
+    s_need = k;
+  }
+  uint32_t mask = 0;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    for (int i = tid; i < n; i += blockDim.x) {
+      uint32_t key = float_key(s[i]);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int need = s_need, b = 255;
+      for (; b > 0; --b) {
+        if (hist[b] >= need) break;
+        need -= hist[b];
+      }
+      s_need = need;                     // how many to take from bin b (at deeper levels)
+      s_prefix = prefix | ((uint32_t)b << shift);
+    }
+    __syncthreads();
+    mask |= 0xffu << shift;
+  }
+  const uint32_t thr = s_prefix;         // key of the k-th largest
+  const int need_ties = s_need;          // elements equal to thr to keep (lowest positions first)
+  if (tid == 0) {
+    s_run = 0;
+    s_tie_run = 0;
+  }
+  __syncthreads();
+  // ordered compaction in position order
+  const int lane = tid & 31, warp = tid >> 5;
+  for (int base_i = 0; base_i < n; base_i += blockDim.x) {
+    const int i = base_i + tid;
+    uint32_t key = i < n ? float_key(s[i]) : 0;
+    const int gt = (i < n && key > thr) ? 1 : 0;
+    const int eq = (i < n && key == thr) ? 1 : 0;
+    // inclusive scans of gt and eq within the block
+    int sg = gt, se = eq;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int a = __shfl_up_sync(0xffffffffu, sg, d), b = __shfl_up_sync(0xffffffffu, se, d);
+      if (lane >= d) {
+        sg += a;
+        se += b;
+      }
+    }
+    if (lane == 31) {
+      warp_tot[warp][0] = sg;
+      warp_tot[warp][1] = se;
+    }
+    __syncthreads();
+    int og = 0, oe = 0;
+    for (int w2 = 0; w2 < warp; ++w2) {
+      og += warp_tot[w2][0];
+      oe += warp_tot[w2][1];
+    }
+    const int run = s_run, tie_run = s_tie_run;
+    const int eq_rank = tie_run + oe + se - eq;           // ties before this element
+    const int take_eq = eq && (eq_rank < need_ties);
+    // position among kept elements = kept gt before + kept eq before
+    const int gt_before = run + og + sg - gt;
+    const int eq_before = min(eq_rank, need_ties);
+    if (gt || take_eq) {
+      const int dst = gt_before + eq_before - 0;
+      // run counts only gt; ties tracked separately: final index = gt_before + eq_before
+      if (dst < k) {
+        o[dst] = base + i;
+        if (out_scores) out_scores[(long)r * k + dst] = s[i];
+      }
+    }
+    __syncthreads();
+    if (tid == blockDim.x - 1) {
+      s_run = run + og + sg;
+      s_tie_run = tie_run + oe + se;
+    }
+    __syncthreads();
+  }
+  if (tid == 0 && count) count[r] = k;
+}
+
+// Merge per-rank candidate lists (key-sharded scoring): cand_scores/cand_ids [T, ranks*k] -> top-k
+// ids ascending.  Reuses the selection kernel on the gathered scores, then maps positions to ids.
+__global__ void map_ids_kernel(const int* __restrict__ picked, const int* __restrict__ cand_ids, int ldc,
+                               int k, int* __restrict__ out) {
+  const int r = blockIdx.x;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const int p = picked[(long)r * k + i];
+    out[(long)r * k + i] = p >= 0 ? cand_ids[(long)r * ldc + p] : -1;
+  }
+}
+
+}  // namespace
+
+TF_API int tf_index_scores(const void* q, const float* w, const int* region, const int* nvalid,
+                           const void* keys, long key_region_stride, int key_row, int T, int Hi, int Di,
+                           int rows_per_group, float* scores, int lds, int key_lo, int key_hi,
+                           cudaStream_t st) {
+  if ((Di != 128 && Di != 64 && Di != 32) || key_row % 4 || rows_per_group < 1) return -1;
+  if (key_hi <= key_lo) return 0;
+  ScoreParams p;
+  p.q = (const __nv_bfloat16*)q; p.w = w; p.region = region; p.nvalid = nvalid;
+  p.keys = (const uint8_t*)keys; p.key_region_stride = key_region_stride; p.key_row = key_row;
+  p.T = T; p.Hi = Hi; p.Di = Di; p.rows_per_group = rows_per_group; p.scores = scores; p.lds = lds;
+  p.key_lo = key_lo; p.key_hi = key_hi;
+  dim3 grid((key_hi - key_lo + kKeysPerCta - 1) / kKeysPerCta, (T + rows_per_group - 1) / rows_per_group);
+  const int smem = kKeysPerCta * (Di + 8) * 2;
+  if (Di == 128) index_score_kernel<128><<<grid, 128, smem, st>>>(p);
+  else if (Di == 64) index_score_kernel<64><<<grid, 128, smem, st>>>(p);
+  else index_score_kernel<32><<<grid, 128, smem, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_topk_select(const float* scores, int lds, const int* nvalid, int k, int* out, int* count,
+                          float* out_scores, int base, int T, cudaStream_t st) {
+  topk_select_kernel<<<T, 1024, 0, st>>>(scores, lds, nvalid, k, out, count, out_scores, base);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_map_ids(const int* picked, const int* cand_ids, int ldc, int k, int* out, int T,
+                      cudaStream_t st) {
+  map_ids_kernel<<<T, 256, 0, st>>>(picked, cand_ids, ldc, k, out);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,649 @@
+"""CUDA engine: the model graph executed with the sm_100a kernels of ``csrc/``.
+
+One ``Engine`` per rank owns the rank's quantised weight shard, the KV state of every serving
+region (window rings in the V4.1 FP8 row format, compressed streams in the V4.1-FP4 format,
+index keys, compressor carries) and the scratch of each row-count profile.  ``forward`` runs a
+batch of rows -- a prefill chunk of one conversation or the verification blocks of up to
+``regions`` conversations -- and returns fp32 logits for the requested rows.
+
+Row state is addressed by absolute position (ring slot = pos % ring, compressed entry =
+pos // ratio), so rejecting speculative rows needs no rollback copies: the next launch simply
+overwrites them (the reference keeps carry snapshots for this: src/carry_state.rs).
+
+Reference counterparts: src/target.rs (Target::execute_rows :5632, Plan :475), src/decoder.rs
+(SwaLayer), src/layer_attention.rs, src/ffn.rs, src/model_io.rs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..formats import codecs
+from ..ops import native
+from ..parallel.comm import Comm, LocalComm
+from . import oracle
+
+F8 = torch.float8_e4m3fn
+
+
+def _pad128(n: int) -> int:
+    return -(-n // 128) * 128
+
+
+# ---------------------------------------------------------------------------------------------
+# weight preparation
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class Fp8Weight:
+    """[N, K] e4m3 + fp32 scale per 128x128 block; N padded to 128."""
+    q: torch.Tensor
+    s: torch.Tensor
+    n: int
+    k: int
+
+
+@dataclass
+class LayerWeights:
+    proj: Fp8Weight = None
+    offs: Dict[str, int] = field(default_factory=dict)
+    wo: Fp8Weight = None
+    attn_norm: torch.Tensor = None
+    ffn_norm: torch.Tensor = None
+    kv_norm: torch.Tensor = None
+    comp_norm: Optional[torch.Tensor] = None
+    sink: Optional[torch.Tensor] = None
+    gate: torch.Tensor = None
+    gate_bias: Optional[torch.Tensor] = None
+    ew1: torch.Tensor = None
+    ew3: torch.Tensor = None
+    ew2: torch.Tensor = None
+    es1: torch.Tensor = None
+    es3: torch.Tensor = None
+    es2: torch.Tensor = None
+    sw1: Optional[Fp8Weight] = None
+    sw3: Optional[Fp8Weight] = None
+    sw2: Optional[Fp8Weight] = None
+    is_kv_source: bool = False
+    is_index_source: bool = False
+    kv_source: int = -1
+    index_source: int = -1
+
+
+def quant_fp8_device(w: torch.Tensor) -> Fp8Weight:
+    """Block-128 FP8 quantisation on the tensor's device; rows padded to a multiple of 128."""
+    n, k = w.shape
+    assert k % 128 == 0
+    npad = _pad128(n)
+    wf = torch.zeros(npad, k, dtype=torch.float32, device=w.device)
+    wf[:n] = w.float()
+    t = wf.view(npad // 128, 128, k // 128, 128)
+    s = t.abs().amax(dim=(1, 3)).clamp_min(1e-12) / codecs.E4M3_MAX
+    q = (t / s[:, None, :, None]).clamp(-448, 448).to(F8).view(npad, k)
+    return Fp8Weight(q.contiguous(), s.contiguous(), n, k)
+
+
+def dequant_fp8(w: Fp8Weight) -> torch.Tensor:
+    n, k = w.q.shape
+    t = w.q.float().view(n // 128, 128, k // 128, 128) * w.s[:, None, :, None]
+    return t.view(n, k)[: w.n]
+
+
+def quant_mxfp4_device(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[..., K] -> (packed e2m1 uint8 [..., K/2], ue8m0 uint8 [..., K/32]) on the tensor's device."""
+    *lead, K = w.shape
+    g = w.float().reshape(*lead, K // 32, 32)
+    amax = g.abs().amax(-1).clamp_min(2.0 ** -120)
+    e = torch.ceil(torch.log2(amax / 6.0))
+    e = torch.where(torch.exp2(e) < amax / 6.0, e + 1, e)
+    code = (e + 127).clamp(0, 247).to(torch.uint8)
+    s = torch.exp2(code.float() - 127)
+    x = g / s.unsqueeze(-1)
+    a = x.abs()
+    idx = torch.zeros_like(a, dtype=torch.uint8)
+    for i, (mid, even_up) in enumerate(((0.25, False), (0.75, True), (1.25, False), (1.75, True),
+                                        (2.5, False), (3.5, True), (5.0, False))):
+        up = (a > mid) | ((a == mid) & even_up)
+        idx = torch.where(up, torch.full_like(idx, i + 1), idx)
+    codes = (idx | ((x < 0).to(torch.uint8) << 3)).reshape(*lead, K)
+    packed = codes[..., 0::2] | (codes[..., 1::2] << 4)
+    return packed.contiguous(), code.contiguous()
+
+
+def dequant_mxfp4(p: torch.Tensor, code: torch.Tensor) -> torch.Tensor:
+    vals = torch.tensor(codecs.E2M1_VALUES, dtype=torch.float32, device=p.device)
+    lo, hi = (p & 0xF).long(), (p >> 4).long()
+    c = torch.stack([lo, hi], -1).reshape(*p.shape[:-1], p.shape[-1] * 2)
+    v = torch.where((c & 8) != 0, -vals[c & 7], vals[c & 7])
+    *lead, K = v.shape
+    s = torch.exp2(code.float() - 127).unsqueeze(-1)
+    return (v.reshape(*lead, K // 32, 32) * s).reshape(*lead, K)
+
+
+def _layer_prefix(cfg: ModelConfig, li: int) -> str:
+    return f"mtp.{li - cfg.n_layers}" if li >= cfg.n_layers else f"layers.{li}"
+
+
+def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: int, world: int,
+                  device, roundtrip: Optional[Dict[str, torch.Tensor]] = None) -> LayerWeights:
+    """Quantise one layer's shard from an fp32/bf16 weight dict (full, unsharded tensors) and, when
+    ``roundtrip`` is given, record the dequantised full tensors there for the oracle."""
+    assert cfg.q_lora_rank == 0 and cfg.o_groups == 0 and cfg.hc_mult == 1, \
+        "CUDA engine covers the direct-projection geometry; LoRA/mHC variants run on the oracle path"
+    p = _layer_prefix(cfg, li)
+    draft = li >= cfg.n_layers
+    H, Dh, d = cfg.n_heads, cfg.head_dim, cfg.hidden
+    Hl = H // world
+    L = LayerWeights()
+    L.is_kv_source = (not draft) and li in cfg.kv_source_layers
+    L.is_index_source = (not draft) and li in cfg.index_source_layers
+    L.kv_source = -1 if draft else cfg.kv_source_of(li)
+    L.index_source = -1 if draft else cfg.index_source_of(li)
+
+    def dev(t, dt=None):
+        t = t.to(device)
+        return t.to(dt) if dt is not None else t
+
+    def rt(name, full_q: Fp8Weight):
+        if roundtrip is not None:
+            roundtrip[name] = dequant_fp8(full_q).cpu()
+
+    segs: List[Tuple[str, torch.Tensor]] = []
+    wq = dev(W[f"{p}.attn.wq.weight"])
+    rt(f"{p}.attn.wq.weight", quant_fp8_device(wq))
+    segs.append(("q", wq[rank * Hl * Dh:(rank + 1) * Hl * Dh]))
+    segs.append(("kv", dev(W[f"{p}.attn.wkv.weight"])))
+    rt(f"{p}.attn.wkv.weight", quant_fp8_device(segs[-1][1]))
+    if L.is_kv_source:
+        for nm, key in (("cv", "wkv"), ("cg", "wgate")):
+            segs.append((nm, dev(W[f"{p}.attn.compressor.{key}.weight"])))
+            rt(f"{p}.attn.compressor.{key}.weight", quant_fp8_device(segs[-1][1]))
+    if L.is_index_source:
+        segs.append(("iq", dev(W[f"{p}.attn.indexer.wq.weight"])))
+        rt(f"{p}.attn.indexer.wq.weight", quant_fp8_device(segs[-1][1]))
+        segs.append(("iw", dev(W[f"{p}.attn.indexer.weights_proj.weight"])))
+        rt(f"{p}.attn.indexer.weights_proj.weight", quant_fp8_device(segs[-1][1]))
+    qs, ss, off = [], [], 0
+    for nm, t in segs:
+        fw = quant_fp8_device(t)
+        L.offs[nm] = off
+        off += fw.q.shape[0]
+        qs.append(fw.q)
+        ss.append(fw.s)
+    L.proj = Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d)
+    wo = dev(W[f"{p}.attn.wo.weight"])
+    rt(f"{p}.attn.wo.weight", quant_fp8_device(wo))
+    L.wo = quant_fp8_device(wo[:, rank * Hl * Dh:(rank + 1) * Hl * Dh].contiguous())
+    L.attn_norm = dev(W[f"{p}.attn_norm.weight"], torch.bfloat16)
+    L.ffn_norm = dev(W[f"{p}.ffn_norm.weight"], torch.bfloat16)
+    L.kv_norm = dev(W[f"{p}.attn.kv_norm.weight"], torch.bfloat16)
+    if L.is_kv_source:
+        L.comp_norm = dev(W[f"{p}.attn.compressor.norm.weight"], torch.bfloat16)
+    if cfg.attn_sink:
+        L.sink = dev(W[f"{p}.attn.attn_sink"], torch.float32)[rank * Hl:(rank + 1) * Hl].contiguous()
+    L.gate = dev(W[f"{p}.ffn.gate.weight"], torch.bfloat16).contiguous()
+    if roundtrip is not None:
+        roundtrip[f"{p}.ffn.gate.weight"] = L.gate.float().cpu()
+    if cfg.router_bias:
+        L.gate_bias = dev(W[f"{p}.ffn.gate.bias"], torch.float32)
+    El = cfg.n_experts // world
+    for nm in ("w1", "w3", "w2"):
+        full = dev(W[f"{p}.ffn.experts.{nm}.weight"])
+        if roundtrip is not None:
+            pk, sc = quant_mxfp4_device(full)
+            roundtrip[f"{p}.ffn.experts.{nm}.weight"] = dequant_mxfp4(pk, sc).cpu()
+        pk, sc = quant_mxfp4_device(full[rank * El:(rank + 1) * El])
+        setattr(L, "e" + nm, pk)
+        setattr(L, "es" + nm[1], sc)
+    if cfg.n_shared:
+        Is = cfg.shared_inter * cfg.n_shared
+        Il = Is // world
+        for nm in ("w1", "w3", "w2"):
+            full = dev(W[f"{p}.ffn.shared_experts.{nm}.weight"])
+            rt(f"{p}.ffn.shared_experts.{nm}.weight", quant_fp8_device(full))
+            sl = full[:, rank * Il:(rank + 1) * Il] if nm == "w2" else full[rank * Il:(rank + 1) * Il]
+            setattr(L, "s" + nm, quant_fp8_device(sl.contiguous()))
+    return L
+
+
+def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed: int) -> LayerWeights:
+    """Random-init one layer's shard directly on the device in its quantised storage formats
+    (the full-size model never exists in fp32): dense weights are N(0, init_std) quantised to
+    block-128 FP8; expert nibbles are uniform random e2m1 codes with a fixed 2^-7 group scale."""
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + li * 16 + rank)
+    H, Dh, d = cfg.n_heads, cfg.head_dim, cfg.hidden
+    Hl, El = H // world, cfg.n_experts // world
+    draft = li >= cfg.n_layers
+    L = LayerWeights()
+    L.is_kv_source = (not draft) and li in cfg.kv_source_layers
+    L.is_index_source = (not draft) and li in cfg.index_source_layers
+    L.kv_source = -1 if draft else cfg.kv_source_of(li)
+    L.index_source = -1 if draft else cfg.index_source_of(li)
+
+    def rnd(n, k, std=None):
+        return torch.randn(n, k, generator=g, device=device, dtype=torch.bfloat16) * (std or cfg.init_std)
+
+    segs = [("q", rnd(Hl * Dh, d)), ("kv", rnd(Dh, d))]
+    if L.is_kv_source:
+        segs += [("cv", rnd(Dh + cfg.index_dim, d)), ("cg", rnd(Dh + cfg.index_dim, d))]
+    if L.is_index_source:
+        segs += [("iq", rnd(cfg.index_heads * cfg.index_dim, d)), ("iw", rnd(cfg.index_heads, d, 1 / math.sqrt(d)))]
+    qs, ss, off = [], [], 0
+    for nm, t in segs:
+        fw = quant_fp8_device(t)
+        L.offs[nm] = off
+        off += fw.q.shape[0]
+        qs.append(fw.q)
+        ss.append(fw.s)
+    L.proj = Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d)
+    L.wo = quant_fp8_device(rnd(d, Hl * Dh))
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    L.attn_norm, L.ffn_norm, L.kv_norm = ones(d), ones(d), ones(Dh)
+    if L.is_kv_source:
+        L.comp_norm = ones(Dh)
+    if cfg.attn_sink:
+        L.sink = torch.randn(Hl, generator=g, device=device) * 0.5
+    L.gate = rnd(cfg.n_experts, d, 1 / math.sqrt(d)).contiguous()
+    if cfg.router_bias:
+        L.gate_bias = torch.zeros(cfg.n_experts, device=device)
+    I = cfg.moe_inter
+    for nm, n, k in (("w1", I, d), ("w3", I, d), ("w2", d, I)):
+        pk = torch.randint(0, 256, (El, n, k // 2), generator=g, device=device, dtype=torch.uint8)
+        sc = torch.full((El, n, k // 32), 120, dtype=torch.uint8, device=device)
+        setattr(L, "e" + nm, pk)
+        setattr(L, "es" + nm[1], sc)
+    if cfg.n_shared:
+        Il = cfg.shared_inter * cfg.n_shared // world
+        L.sw1, L.sw3 = quant_fp8_device(rnd(Il, d)), quant_fp8_device(rnd(Il, d))
+        L.sw2 = quant_fp8_device(rnd(d, Il))
+    return L
+
+
+# ---------------------------------------------------------------------------------------------
+# step plan (host metadata of one launch; reference: Plan, src/target.rs:475-683)
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class StepPlan:
+    """Rows of one launch.  Rows of a conversation are consecutive and at consecutive positions."""
+    tokens: np.ndarray          # [T] int32
+    pos: np.ndarray             # [T]
+    region: np.ndarray          # [T]
+    first_row: np.ndarray       # [T] first row index of the row's conversation in this launch
+    last_pos: np.ndarray        # [T] last position of the row's conversation in this launch
+    logit_rows: np.ndarray      # rows whose logits are wanted
+    group_rows: int             # rows per conversation block (uniform), used to group index scoring
+
+    @staticmethod
+    def build(blocks: Sequence[Tuple[int, int, Sequence[int]]], logits: str = "all") -> "StepPlan":
+        """blocks: (region, start position, tokens).  logits: "all" | "last" (last row per block)."""
+        toks, pos, reg, first, last, lrows = [], [], [], [], [], []
+        r0 = 0
+        sizes = set()
+        for region, start, t in blocks:
+            n = len(t)
+            sizes.add(n)
+            toks += list(t)
+            pos += list(range(start, start + n))
+            reg += [region] * n
+            first += [r0] * n
+            last += [start + n - 1] * n
+            lrows += list(range(r0, r0 + n)) if logits == "all" else [r0 + n - 1]
+            r0 += n
+        i32 = lambda a: np.asarray(a, dtype=np.int32)
+        gr = sizes.pop() if len(sizes) == 1 else 1
+        return StepPlan(i32(toks), i32(pos), i32(reg), i32(first), i32(last), i32(lrows), gr)
+
+    @property
+    def T(self) -> int:
+        return int(self.tokens.shape[0])
+
+
+class Engine:
+    SMALL_M = 32
+
+    def __init__(self, cfg: ModelConfig, ecfg: EngineConfig, layers: List[LayerWeights],
+                 embed: torch.Tensor, head: torch.Tensor, final_norm: torch.Tensor,
+                 comm: Optional[Comm] = None, device="cuda", max_chunk: int = 0,
+                 draft_layers: Optional[List[LayerWeights]] = None, draft_extra: Optional[dict] = None):
+        self.cfg, self.ecfg = cfg, ecfg
+        self.comm = comm or LocalComm()
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.dev = torch.device(device)
+        self.layers = layers
+        self.draft_layers = draft_layers or []
+        self.draft_extra = draft_extra or {}
+        self.embed_w, self.head_w, self.final_norm = embed, head, final_norm
+        native.lib()
+        self.status = native.StatusWord(self.dev)
+        r = cfg.rope
+        self.freqs = oracle.rope_frequencies(r.dim, r.theta, r.factor, r.beta_fast, r.beta_slow,
+                                             r.original_max_position).to(self.dev)
+        self.cfreqs = oracle.rope_frequencies(r.dim, r.compress_theta, r.factor, r.beta_fast,
+                                              r.beta_slow, r.original_max_position).to(self.dev)
+        self.Hl = cfg.n_heads // self.world
+        self.El = cfg.n_experts // self.world
+        self.regions = ecfg.regions
+        self.max_chunk = max_chunk or max(ecfg.prefill_widths)
+        self.ring = self.max_chunk + 2 * cfg.window
+        self.maxC = ecfg.max_context // cfg.compress_ratio + 8
+        self.win_row, self.comp_row = cfg.window_kv_bytes, cfg.compressed_kv_bytes
+        self.key_row = cfg.index_key_bytes
+        nl = len(layers) + len(self.draft_layers)
+        u8 = dict(dtype=torch.uint8, device=self.dev)
+        self.win = torch.zeros(nl, self.regions, self.ring, self.win_row, **u8)
+        self.src_slot = {l: i for i, l in enumerate(cfg.kv_source_layers)}
+        ns = max(1, len(cfg.kv_source_layers))
+        C = cfg.head_dim + cfg.index_dim
+        self.comp = torch.zeros(ns, self.regions, self.maxC, self.comp_row, **u8)
+        self.keys = torch.zeros(ns, self.regions, self.maxC, self.key_row, **u8)
+        self.carry = torch.zeros(ns, self.regions, cfg.compress_ratio, 2 * C, dtype=torch.float32,
+                                 device=self.dev)
+        self._scratch: Dict[int, dict] = {}
+        self._dq_cache: Dict[int, torch.Tensor] = {}
+        self.big_gemm = None        # set by ops.gemm when the tcgen05 path is loaded
+        self.last_hidden: Optional[torch.Tensor] = None
+
+    # -- construction helpers --------------------------------------------------------------
+    @classmethod
+    def from_weights(cls, cfg: ModelConfig, ecfg: EngineConfig, W: Dict[str, torch.Tensor],
+                     comm: Optional[Comm] = None, device="cuda", roundtrip: Optional[dict] = None,
+                     max_chunk: int = 0) -> "Engine":
+        comm = comm or LocalComm()
+        layers = [prepare_layer(cfg, W, li, comm.rank, comm.world, device, roundtrip)
+                  for li in range(cfg.n_layers)]
+        drafts, extra = [], {}
+        if cfg.draft is not None and "mtp.0.main_proj.weight" in W:
+            drafts = [prepare_layer(cfg, W, cfg.n_layers + j, comm.rank, comm.world, device, roundtrip)
+                      for j in range(cfg.draft.layers)]
+            mp = quant_fp8_device(W["mtp.0.main_proj.weight"].to(device))
+            if roundtrip is not None:
+                roundtrip["mtp.0.main_proj.weight"] = dequant_fp8(mp).cpu()
+            extra = dict(main_proj=mp, enorm=W["mtp.0.enorm.weight"].to(device, torch.bfloat16),
+                         hnorm=W["mtp.0.hnorm.weight"].to(device, torch.bfloat16))
+        V = cfg.vocab
+        Vl = V // comm.world
+        embed = W["embed.weight"].to(device, torch.bfloat16).contiguous()
+        head = W["head.weight"][comm.rank * Vl:(comm.rank + 1) * Vl].to(device, torch.bfloat16).contiguous()
+        if roundtrip is not None:
+            roundtrip["embed.weight"] = embed.float().cpu()
+            roundtrip["head.weight"] = W["head.weight"].to(torch.bfloat16).float()
+            for k, v in W.items():
+                if k not in roundtrip:
+                    roundtrip[k] = v.to(torch.bfloat16).float() if v.dim() == 1 else v
+        return cls(cfg, ecfg, layers, embed, head, W["norm.weight"].to(device, torch.bfloat16), comm,
+                   device, max_chunk, drafts, extra)
+
+    @classmethod
+    def random_init(cls, cfg: ModelConfig, ecfg: EngineConfig, comm: Optional[Comm] = None,
+                    device="cuda", seed: int = 0, max_chunk: int = 0) -> "Engine":
+        comm = comm or LocalComm()
+        layers = [random_layer(cfg, li, comm.rank, comm.world, device, seed) for li in range(cfg.n_layers)]
+        drafts, extra = [], {}
+        g = torch.Generator(device=device).manual_seed(seed + 7)
+        d = cfg.hidden
+        if cfg.draft is not None:
+            drafts = [random_layer(cfg, cfg.n_layers + j, comm.rank, comm.world, device, seed)
+                      for j in range(cfg.draft.layers)]
+            mp = torch.randn(d, d * (1 + cfg.draft.condition_layers), generator=g, device=device,
+                             dtype=torch.bfloat16) * cfg.init_std
+            extra = dict(main_proj=quant_fp8_device(mp),
+                         enorm=torch.ones(d, dtype=torch.bfloat16, device=device),
+                         hnorm=torch.ones(d * cfg.draft.condition_layers, dtype=torch.bfloat16, device=device))
+        Vl = cfg.vocab // comm.world
+        embed = torch.randn(cfg.vocab, d, generator=g, device=device, dtype=torch.bfloat16) * cfg.init_std
+        head = torch.randn(Vl, d, generator=g, device=device, dtype=torch.bfloat16) * cfg.init_std
+        return cls(cfg, ecfg, layers, embed, head, torch.ones(d, dtype=torch.bfloat16, device=device),
+                   comm, device, max_chunk, drafts, extra)
+
+    # -- scratch -----------------------------------------------------------------------------
+    def _bufs(self, T: int) -> dict:
+        b = self._scratch.get(T)
+        if b is not None:
+            return b
+        cfg, dev = self.cfg, self.dev
+        d, Dh, Hl = cfg.hidden, cfg.head_dim, self.Hl
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        maxN = max(l.proj.q.shape[0] for l in self.layers + self.draft_layers)
+        npairs = T * cfg.topk
+        nsplit = self._nsplit(T)
+        Il = cfg.shared_inter * cfg.n_shared // self.world
+        b = dict(
+            meta=torch.zeros(6, T, **i32),
+            x=torch.zeros(T, d, dtype=torch.bfloat16, device=dev),
+            h16=torch.zeros(T, d, dtype=torch.float16, device=dev),
+            hb=torch.zeros(T, d, dtype=torch.bfloat16, device=dev),
+            P=torch.zeros(T, maxN, **f32),
+            q=torch.zeros(T, Hl, Dh, dtype=torch.bfloat16, device=dev),
+            iq=torch.zeros(T, cfg.index_heads, cfg.index_dim, dtype=torch.bfloat16, device=dev),
+            iw=torch.zeros(T, cfg.index_heads, **f32),
+            sel={s: torch.full((T, cfg.index_topk), -1, **i32) for s in cfg.index_source_layers},
+            selcnt={s: torch.zeros(T, **i32) for s in cfg.index_source_layers},
+            part_o=torch.zeros(T, nsplit, Hl, Dh, **f32),
+            part_lse=torch.zeros(T, nsplit, Hl, **f32),
+            a16=torch.zeros(T, Hl * Dh, dtype=torch.float16, device=dev),
+            delta=torch.zeros(T, d, **f32),
+            logits_r=torch.zeros(T, cfg.n_experts, **f32),
+            ids=torch.zeros(T, cfg.topk, **i32),
+            wts=torch.zeros(T, cfg.topk, **f32),
+            g_expert=torch.zeros(self.El, **i32), g_start=torch.zeros(self.El, **i32),
+            g_count=torch.zeros(self.El, **i32), n_groups=torch.zeros(1, **i32),
+            sorted_pairs=torch.zeros(npairs, **i32), n_local=torch.zeros(1, **i32),
+            act=torch.zeros(npairs, cfg.moe_inter, dtype=torch.float16, device=dev),
+            y_pair=torch.zeros(npairs, d, **f32),
+            s_act=torch.zeros(T, max(Il, 1), dtype=torch.float16, device=dev),
+            s_y=torch.zeros(T, d, **f32),
+        )
+        self._scratch[T] = b
+        return b
+
+    def _nsplit(self, T: int) -> int:
+        if T > 64:
+            return 1
+        keys = self.cfg.window + self.cfg.index_topk
+        return max(1, min(32, -(-keys // 128)))
+
+    def scores_buffer(self, T: int, n: int) -> torch.Tensor:
+        key = ("scores", T)
+        b = self._scratch.get(key)
+        if b is None or b.shape[1] < n:
+            width = max(n, 1024)
+            width = -(-width // 1024) * 1024
+            b = torch.empty(T, width, dtype=torch.float32, device=self.dev)
+            self._scratch[key] = b
+        return b
+
+    # -- linear dispatch ---------------------------------------------------------------------
+    def _linear(self, x16: torch.Tensor, w: Fp8Weight, out: torch.Tensor, M: int,
+                w3: Optional[Fp8Weight] = None) -> None:
+        """out[:M] = x16[:M] @ W^T (f32/f16 out by dtype of ``out``); ``w3`` selects the dual
+        SwiGLU form.  Rows beyond SMALL_M go through the tensor-core (tcgen05) GEMM."""
+        N, K = w.q.shape
+        okind = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[out.dtype]
+        if M <= self.SMALL_M:
+            native.call("tf_smallm_gemm", 0, w.q, w3.q if w3 else None, w.s, w3.s if w3 else None,
+                        0, 0, K, K // 128, x16, x16.stride(0), out, out.stride(0), okind, N, K, M,
+                        None, None, None, None, None, 1, 0, M, self.cfg.swiglu_limit)
+            return
+        if self.big_gemm is not None:
+            self.big_gemm(self, x16, w, out, M, w3)
+            return
+        # staging path for large row counts when the tensor-core GEMM is not loaded: dequantised
+        # weights through torch.matmul (numerically the same contract, used for validation only)
+        wd = self._dequant_cached(w)
+        y = x16[:M].float() @ wd.t()
+        if w3 is not None:
+            y = oracle.swiglu(y, x16[:M].float() @ self._dequant_cached(w3).t(), self.cfg.swiglu_limit)
+        out[:M, : y.shape[1]] = y.to(out.dtype)
+
+    def _dequant_cached(self, w: Fp8Weight) -> torch.Tensor:
+        k = id(w)
+        if k not in self._dq_cache:
+            n, kk = w.q.shape
+            self._dq_cache[k] = (w.q.float().view(n // 128, 128, kk // 128, 128)
+                                 * w.s[:, None, :, None]).view(n, kk)
+        return self._dq_cache[k]
+
+    def _allreduce(self, t: torch.Tensor) -> None:
+        if self.world > 1:
+            self.comm.all_reduce(t)
+
+    # -- one layer ---------------------------------------------------------------------------
+    def _layer(self, li: int, L: LayerWeights, T: int, b: dict, plan: StepPlan, first: bool) -> None:
+        cfg = self.cfg
+        d, Dh, Hl = cfg.hidden, cfg.head_dim, self.Hl
+        pos, region, first_row, last_pos, nvalid = (b["meta"][i] for i in (1, 2, 3, 4, 5))
+        # boundary: x += delta (previous sublayer); h = rmsnorm(x)
+        native.call("tf_add_norm", b["x"], None if first else b["delta"], 0, d, L.attn_norm, b["h16"],
+                    None, None, None, T, d, cfg.rms_eps)
+        N = L.proj.q.shape[0]
+        P = b["P"]
+        self._linear(b["h16"], L.proj, P, T)
+        o = L.offs
+        slot = self.src_slot.get(li, 0)
+        native.call("tf_attn_prep", P, 0, P.stride(0), T, pos, region, first_row, last_pos, Hl, Dh,
+                    cfg.rope.dim, self.freqs, self.cfreqs, L.kv_norm, cfg.rms_eps, b["q"], self.win[li],
+                    self.win[li].stride(0), self.win_row, self.comp_row, self.key_row, self.ring,
+                    o["q"], o["kv"], o.get("cv", -1), o.get("cg", -1), o.get("iq", -1), o.get("iw", -1),
+                    cfg.compress_ratio, cfg.index_dim, cfg.index_heads, L.comp_norm,
+                    self.carry[slot] if L.is_kv_source else None,
+                    self.comp[slot] if L.is_kv_source else None,
+                    self.keys[slot] if L.is_kv_source else None, self.maxC, b["iq"], b["iw"],
+                    self.status.t)
+        comp = None
+        sel = selcnt = None
+        if L.kv_source >= 0:
+            sslot = self.src_slot[L.kv_source]
+            comp = self.comp[sslot]
+            if L.is_index_source:
+                self._index(L, T, b, plan, sslot, li)
+            sel, selcnt = b["sel"][L.index_source], b["selcnt"][L.index_source]
+        nsplit = b["part_o"].shape[1]
+        native.call("tf_sparse_attention", b["q"], T, Hl, Dh, pos, region, self.win[li],
+                    self.win[li].stride(0), self.win_row, self.ring, cfg.window, comp,
+                    comp.stride(0) if comp is not None else 0, self.comp_row, sel,
+                    cfg.index_topk, selcnt, self.maxC, 1.0 / math.sqrt(Dh), nsplit, b["part_o"],
+                    b["part_lse"], L.sink, self.freqs, cfg.rope.dim, b["a16"], None, Hl * Dh,
+                    self.status.t)
+        self._linear(b["a16"], L.wo, b["delta"], T)
+        self._allreduce(b["delta"][:T])
+        # FFN boundary
+        native.call("tf_add_norm", b["x"], b["delta"], 0, d, L.ffn_norm, b["h16"], None, None, None,
+                    T, d, cfg.rms_eps)
+        self._moe(L, T, b)
+        self._allreduce(b["delta"][:T])
+
+    def _index(self, L: LayerWeights, T: int, b: dict, plan: StepPlan, sslot: int, li: int) -> None:
+        cfg = self.cfg
+        region, nvalid = b["meta"][2], b["meta"][5]
+        nmax = int((plan.pos.max() + 1) // cfg.compress_ratio)
+        sel, selcnt = b["sel"][li], b["selcnt"][li]
+        if nmax == 0:
+            sel.fill_(-1)
+            selcnt.zero_()
+            return
+        scores = self.scores_buffer(T, nmax)
+        # a scoring CTA serves consecutive rows of ONE conversation
+        if plan.group_rows == T:
+            rows_per_group = min(T, 32)
+        else:
+            rows_per_group = plan.group_rows if plan.group_rows <= 32 else 1
+        native.call("tf_index_scores", b["iq"], b["iw"], region, nvalid, self.keys[sslot],
+                    self.keys[sslot].stride(0), self.key_row, T, cfg.index_heads, cfg.index_dim,
+                    rows_per_group, scores, scores.stride(0), 0, nmax)
+        native.call("tf_topk_select", scores, scores.stride(0), nvalid, cfg.index_topk, sel, selcnt,
+                    None, 0, T)
+
+    def _moe(self, L: LayerWeights, T: int, b: dict) -> None:
+        cfg = self.cfg
+        d, I = cfg.hidden, cfg.moe_inter
+        native.call("tf_router", b["h16"], L.gate, L.gate_bias, b["logits_r"], b["ids"], b["wts"], T,
+                    cfg.n_experts, d, cfg.topk, 1 if cfg.scoring == "sqrtsoftplus" else 0,
+                    1 if cfg.renorm else 0, cfg.route_scale)
+        e_lo = self.rank * self.El
+        npairs = T * cfg.topk
+        if T <= self.SMALL_M:
+            native.call("tf_route_group", b["ids"], npairs, e_lo, e_lo + self.El, b["g_expert"],
+                        b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
+            slots = min(self.El, npairs)
+            native.call("tf_smallm_gemm", 1, L.ew1, L.ew3, L.es1, L.es3, I * (d // 2), I * (d // 32),
+                        d // 2, d // 32, b["h16"], d, b["act"], I, 1, I, d, 0, b["g_expert"],
+                        b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], cfg.topk, slots,
+                        min(T, 16), cfg.swiglu_limit)
+            native.call("tf_smallm_gemm", 1, L.ew2, None, L.es2, None, d * (I // 2), d * (I // 32),
+                        I // 2, I // 32, b["act"], I, b["y_pair"], d, 0, d, I, 0, b["g_expert"],
+                        b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], 1, slots,
+                        min(T, 16), 0.0)
+        else:
+            self._moe_large(L, T, b)
+        shared = None
+        if cfg.n_shared:
+            self._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
+            self._linear(b["s_act"], L.sw2, b["s_y"], T)
+            shared = b["s_y"]
+        native.call("tf_moe_combine", b["y_pair"], b["ids"], b["wts"], shared, b["delta"], T, d,
+                    cfg.topk, e_lo, e_lo + self.El)
+
+    def _moe_large(self, L: LayerWeights, T: int, b: dict) -> None:
+        """Routed experts for a prefill chunk.  With the grouped tensor-core GEMM loaded this is a
+        permute + two grouped launches; the staging path below loops over the active experts."""
+        if getattr(self, "big_moe", None) is not None:
+            self.big_moe(self, L, T, b)
+            return
+        cfg = self.cfg
+        ids = b["ids"][:T].long()
+        e_lo = self.rank * self.El
+        h = b["h16"][:T].float()
+        for e in range(self.El):
+            m = ids == (e + e_lo)
+            if not m.any():
+                continue
+            rows, js = m.nonzero(as_tuple=True)
+            w1 = dequant_mxfp4(L.ew1[e], L.es1[e])
+            w3 = dequant_mxfp4(L.ew3[e], L.es3[e])
+            w2 = dequant_mxfp4(L.ew2[e], L.es2[e])
+            a = oracle.swiglu(h[rows] @ w1.t(), h[rows] @ w3.t(), cfg.swiglu_limit).half().float()
+            b["y_pair"][rows * cfg.topk + js] = a @ w2.t()
+
+    # -- public ------------------------------------------------------------------------------
+    def upload_plan(self, plan: StepPlan, b: dict) -> None:
+        T = plan.T
+        host = np.stack([plan.tokens, plan.pos, plan.region, plan.first_row, plan.last_pos,
+                         (plan.pos + 1) // self.cfg.compress_ratio]).astype(np.int32)
+        b["meta"][:, :T].copy_(torch.from_numpy(host), non_blocking=True)
+
+    def forward(self, plan: StepPlan, need_logits: bool = True) -> Optional[torch.Tensor]:
+        cfg = self.cfg
+        T = plan.T
+        assert T <= self.max_chunk
+        b = self._bufs(T)
+        self.upload_plan(plan, b)
+        native.call("tf_embed", b["meta"][0], self.embed_w, b["x"], T, cfg.hidden, cfg.vocab, self.status.t)
+        for li, L in enumerate(self.layers):
+            self._layer(li, L, T, b, plan, first=(li == 0))
+        return self._head(T, b, plan, need_logits)
+
+    def _head(self, T: int, b: dict, plan: StepPlan, need_logits: bool) -> Optional[torch.Tensor]:
+        cfg = self.cfg
+        d = cfg.hidden
+        native.call("tf_add_norm", b["x"], b["delta"], 0, d, self.final_norm, None, b["hb"], None, None,
+                    T, d, cfg.rms_eps)
+        self.last_hidden = b["x"]
+        if not need_logits:
+            return None
+        rows = torch.from_numpy(plan.logit_rows).to(self.dev).long()
+        hsel = b["hb"][rows].contiguous()
+        Vl = self.head_w.shape[0]
+        n = hsel.shape[0]
+        logits = torch.empty(n, Vl, dtype=torch.float32, device=self.dev)
+        for r0 in range(0, n, self.SMALL_M):
+            m = min(self.SMALL_M, n - r0)
+            native.call("tf_smallm_gemm", 2, self.head_w, None, None, None, 0, 0, d * 2, 0,
+                        hsel[r0:], d, logits[r0:], Vl, 0, Vl, d, m, None, None, None, None, None, 1, 0, m, 0.0)
+        if self.world > 1:
+            logits = self.comm.all_gather(logits, dim=1)
+        return logits

@@ -26,6 +26,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..config import ModelConfig
+from ..formats import codecs
 from ..parallel.comm import Comm, LocalComm
 
 
@@ -340,6 +341,8 @@ class OracleModel:
         kv = apply_rope(kv, pos, self.freqs)
         win = s.buf(s.window, p, s.max_tokens, Dh)
         p0, p1 = int(pos[0]), int(pos[-1]) + 1
+        if cfg.kv_quant == "v41":       # what the window cache actually stores
+            kv = codecs.kv_v41_decode(codecs.kv_v41_encode(kv.cpu()), Dh).to(kv.device)
         win[p0:p1] = kv.to(win.dtype)
 
         # compressor at source layers --------------------------------------------------
@@ -363,8 +366,12 @@ class OracleModel:
                 pooled = (v * wgt).sum(1)                                                # [G, C]
                 ck = rmsnorm(pooled[:, :Dh], W[f"{p}.attn.compressor.norm.weight"], cfg.rms_eps)
                 ck = apply_rope(ck, gi, self.cfreqs)
+                ik = pooled[:, Dh:]
+                if cfg.kv_quant == "v41":
+                    ck = codecs.kv_v41fp4_decode(codecs.kv_v41fp4_encode(ck.cpu()), Dh).to(ck.device)
+                    ik = codecs.index_key_decode(codecs.index_key_encode(ik.cpu()), cfg.index_dim).to(ik.device)
                 comp[gi] = ck.to(comp.dtype)
-                keys[gi] = pooled[:, Dh:].to(keys.dtype)
+                keys[gi] = ik.to(keys.dtype)
 
         # indexer ----------------------------------------------------------------------
         sel = None
@@ -375,6 +382,8 @@ class OracleModel:
                 keys = s.keys[src_prefix]
                 Hi, Di = cfg.index_heads, cfg.index_dim
                 qi = (h @ W[f"{p}.attn.indexer.wq.weight"].t()).reshape(T, Hi, Di)
+                if cfg.kv_quant == "v41":
+                    qi = codecs.bf16_round(qi)
                 wi = h @ W[f"{p}.attn.indexer.weights_proj.weight"].t()                  # [T, Hi]
                 nmax = int(nvalid.max())
                 if nmax > 0:
