@@ -1,0 +1,44 @@
+"""tcgen05 GEMM throughput (bf16, FP8, FP8 block-scaled) against torch.matmul (cuBLAS) bf16.
+
+    python benchmarks/bench_gemm.py [--sizes 8192,4096 ...]
+"""
+import argparse
+
+import torch
+
+from common import peaks, time_cuda
+from titanic_flash_41_b200.models import engine as E
+from titanic_flash_41_b200.ops import native
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="8192x8192x8192,16384x8192x4096,16384x4096x8192,4096x4096x4096,512x4096x4096")
+    args = ap.parse_args()
+    pk = peaks()
+    st = native.StatusWord("cuda")
+    print(f"# peaks ({pk['source']}): bf16 {pk['bf16_tflops']} TFLOP/s")
+    for shp in args.shapes.split(","):
+        M, N, K = map(int, shp.split("x"))
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        med, best = time_cuda(lambda: torch.matmul(a, b.t(), out=c))
+        print(f"{shp} cublas-bf16   {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f})")
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 0, a, K, b, K, c, N, M, N, K, None, 0, None, 0, 2, st.t))
+        print(f"{shp} tcgen05-bf16  {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f}) "
+              f"= {fl / med / 1e9 / pk['bf16_tflops']:.2f} of {pk['source']} bf16 peak")
+        aq = a.to(torch.float8_e4m3fn)
+        fw = E.quant_fp8_device(b.float())
+        sa = torch.ones(M, K // 128, device="cuda")
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 1, aq, K, fw.q, K, c, N, M, N, K, None, 0, None, 0, 2, st.t))
+        print(f"{shp} tcgen05-fp8   {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f})")
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 2, aq, K, fw.q, K, c, N, M, N, K, sa, K // 128, fw.s, K // 128, 2, st.t))
+        print(f"{shp} tcgen05-fp8bs {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f}) "
+              f"= {fl / med / 1e9 / pk['bf16_tflops']:.2f} x {pk['source']} bf16 peak")
+        st.check()
+
+
+if __name__ == "__main__":
+    main()
