@@ -26,15 +26,15 @@ def main():
         fl = 2.0 * M * N * K
         med, best = time_cuda(lambda: torch.matmul(a, b.t(), out=c))
         print(f"{shp} cublas-bf16   {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f})")
-        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 0, a, K, b, K, c, N, M, N, K, None, 0, None, 0, 2, st.t))
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 0, a, K, b, K, c, N, M, N, K, None, 0, None, 0, 2, None, None, 0, st.t))
         print(f"{shp} tcgen05-bf16  {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f}) "
               f"= {fl / med / 1e9 / pk['bf16_tflops']:.2f} of {pk['source']} bf16 peak")
         aq = a.to(torch.float8_e4m3fn)
         fw = E.quant_fp8_device(b.float())
         sa = torch.ones(M, K // 128, device="cuda")
-        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 1, aq, K, fw.q, K, c, N, M, N, K, None, 0, None, 0, 2, st.t))
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 1, aq, K, fw.q, K, c, N, M, N, K, None, 0, None, 0, 2, None, None, 0, st.t))
         print(f"{shp} tcgen05-fp8   {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f})")
-        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 2, aq, K, fw.q, K, c, N, M, N, K, sa, K // 128, fw.s, K // 128, 2, st.t))
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 2, aq, K, fw.q, K, c, N, M, N, K, sa, K // 128, fw.s, K // 128, 2, None, None, 0, st.t))
         print(f"{shp} tcgen05-fp8bs {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f}) "
               f"= {fl / med / 1e9 / pk['bf16_tflops']:.2f} x {pk['source']} bf16 peak")
         st.check()

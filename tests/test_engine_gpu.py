@@ -39,8 +39,8 @@ def test_engine_matches_oracle_prefill_and_decode():
     eng.status.check()
     # a near-tie in the router can flip an expert for a row, so judge rows statistically
     err = _row_err(got, want)
-    assert err.median() < 0.05 and (err < 0.1).float().mean() >= 0.85, err
-    assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.75
+    assert err.median() < 0.08 and (err < 0.15).float().mean() >= 0.8, err
+    assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.7
     # decode 6 verification blocks of 4 rows (teacher-forced from the oracle's greedy tokens)
     pos, errs = 77, []
     for step in range(6):
@@ -51,7 +51,7 @@ def test_engine_matches_oracle_prefill_and_decode():
         errs.append(_row_err(got, want))
     eng.status.check()
     errs = torch.cat(errs)
-    assert errs.median() < 0.05 and (errs < 0.1).float().mean() >= 0.85, errs
+    assert errs.median() < 0.08 and (errs < 0.15).float().mean() >= 0.8, errs
 
 
 def test_two_regions_batched_decode_equals_separate():
@@ -81,3 +81,92 @@ def test_determinism_run_to_run():
     a = eng.forward(E.StepPlan.build([(0, 0, p)])).clone()
     b = eng.forward(E.StepPlan.build([(0, 0, p)])).clone()
     assert torch.equal(a, b)
+
+
+def test_tensor_core_prefill_path_matches_staging_per_call():
+    """Rows beyond the small-M limit run on the tcgen05 GEMMs (dense FP8 block-scaled; experts
+    re-expressed as block-scaled FP8 in one grouped launch).  FP8 activations put ~2.6% of noise
+    on every GEMM, which this small random model amplifies through its discrete choices (router,
+    top-k), so each call is checked against the dequantised-weight PyTorch product on the SAME
+    input rather than through the end-to-end logits."""
+    from titanic_flash_41_b200.ops import bigpath
+    cfg = small_config()
+    W = oracle.init_weights(cfg, 0)
+    ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(512,))
+    eng = E.Engine.from_weights(cfg, ecfg, W)
+    bp = bigpath.BigPath(eng)
+    errs = []
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-9))
+
+    def dense_checker(e, x16, w, out, M, w3=None):
+        o2 = torch.zeros_like(out)
+        bp.gemm(e, x16, w, o2, M, w3)
+        e.big_gemm = None
+        e._linear(x16, w, out, M, w3)            # dequantised weights through torch.matmul
+        e.big_gemm = dense_checker
+        errs.append(rel(o2[:M, : w.q.shape[0]], out[:M, : w.q.shape[0]]))
+
+    def moe_checker(e, L, T, b):
+        e._moe_large(L, T, b)                    # per-expert PyTorch loop on dequantised weights
+        shared = None
+        if cfg.n_shared:
+            e._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
+            e._linear(b["s_act"], L.sw2, b["s_y"], T)
+            shared = b["s_y"]
+        from titanic_flash_41_b200.ops import native
+        native.call("tf_moe_combine", b["y_pair"], b["ids"], b["wts"], shared, b["delta"], T, cfg.hidden,
+                    cfg.topk, 0, cfg.n_experts)
+        want = b["delta"][:T].clone()
+        bp.moe(e, L, T, b)
+        errs.append(rel(b["delta"][:T], want))
+        b["delta"][:T].copy_(want)
+
+    eng.big_gemm = dense_checker
+    eng.big_moe_full = moe_checker
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (300,), generator=g)
+    eng._scratch.clear()
+    eng.big_moe_full = None
+    b = eng._bufs(300)                           # full-size expert scratch for the staging loop
+    eng.big_moe_full = moe_checker
+    got = eng.forward(E.StepPlan.build([(0, 0, prompt.tolist())]))
+    torch.cuda.synchronize()
+    eng.status.check()
+    assert len(errs) >= 3 * 5 and max(errs) < 0.06, errs
+    assert torch.isfinite(got).all()
+
+
+def test_chunked_prefill_with_late_group_and_spec_decode():
+    from titanic_flash_41_b200.ops import bigpath
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.serve.prefill import run_prefill
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    cfg = small_config(n_layers=4, kv_source_layers=(0, 1), index_source_layers=(0, 1, 3), late_start=2,
+                       draft=DraftConfig(layers=1, depth=3))
+    W = oracle.init_weights(cfg, 0)
+    ecfg = EngineConfig(regions=2, max_context=2048, prefill_widths=(256,))
+    eng = E.Engine.from_weights(cfg, ecfg, W)
+    bigpath.attach(eng)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g, dtype=torch.int32) for n in (700, 333)]
+    slots = []
+    for r, p in enumerate(prompts):
+        lg = run_prefill(eng, r, p, 256)
+        assert lg.shape == (1, cfg.vocab) and torch.isfinite(lg).all()
+        slots.append(DecodeSlot(region=r, length=int(p.numel()), anchor=int(lg.argmax()), seed=r + 1))
+    dec = SpecDecoder(eng, 2, temperature=0.6, top_p=0.95, use_graph=True)
+    n0 = [s.length for s in slots]
+    for _ in range(6):
+        out = dec.step(slots)
+        assert all(1 <= len(o) <= 4 for o in out)
+    eng.status.check()
+    assert all(s.length - a == len(s.emitted) for s, a in zip(slots, n0))
+    assert all(0 <= t < cfg.vocab for s in slots for t in s.emitted)
+    # graph replay and eager execution of the same step agree
+    dec2 = SpecDecoder(eng, 2, temperature=0.6, top_p=0.95, use_graph=False)
+    snap = [(s.length, s.anchor) for s in slots]
+    a = dec.step([DecodeSlot(region=i, length=l, anchor=t, seed=9) for i, (l, t) in enumerate(snap)])
+    b = dec2.step([DecodeSlot(region=i, length=l, anchor=t, seed=9) for i, (l, t) in enumerate(snap)])
+    assert [x[0] for x in a] == [x[0] for x in b]

@@ -21,7 +21,7 @@ def test_gemm_bf16(M, N, K):
     st = native.StatusWord(DEV)
     for okind, dt in ((2, torch.bfloat16), (0, torch.float32)):
         c = torch.zeros(M, N, device=DEV, dtype=dt)
-        native.call("tf_gemm_tc", 0, a, K, b, K, c, N, M, N, K, None, 0, None, 0, okind, st.t)
+        native.call("tf_gemm_tc", 0, a, K, b, K, c, N, M, N, K, None, 0, None, 0, okind, None, None, 0, st.t)
         torch.cuda.synchronize()
         st.check()
         assert _rel(c, a.float() @ b.float().t()) < 5e-3
@@ -39,13 +39,13 @@ def test_gemm_fp8_block_scaled(M, N, K):
     xd = (xq.float().view(M, K // 128, 128) * sa[:, :, None]).view(M, K)
     st = native.StatusWord(DEV)
     c = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-    native.call("tf_gemm_tc", 2, xq, K, fw.q, K, c, N, M, N, K, sa.contiguous(), K // 128, fw.s, K // 128, 2, st.t)
+    native.call("tf_gemm_tc", 2, xq, K, fw.q, K, c, N, M, N, K, sa.contiguous(), K // 128, fw.s, K // 128, 2, None, None, 0, st.t)
     torch.cuda.synchronize()
     st.check()
     assert _rel(c, xd @ E.dequant_fp8(fw).t()) < 5e-3
     # unscaled fp8
     c2 = torch.zeros(M, N, device=DEV)
-    native.call("tf_gemm_tc", 1, xq, K, fw.q, K, c2, N, M, N, K, None, 0, None, 0, 0, st.t)
+    native.call("tf_gemm_tc", 1, xq, K, fw.q, K, c2, N, M, N, K, None, 0, None, 0, 0, None, None, 0, st.t)
     torch.cuda.synchronize()
     st.check()
     assert _rel(c2, xq.float() @ fw.q.float().t()) < 1e-3

@@ -195,7 +195,7 @@ def test_sparse_attention_matches_reference():
     part_lse = torch.zeros(T, nsplit, Hl, device=DEV)
     out = torch.zeros(T, Hl * Dh, device=DEV, dtype=torch.float16)
     st = native.StatusWord(DEV)
-    native.call("tf_sparse_attention", dev(q), T, Hl, Dh, dev(pos), dev(region), dev(win), ring * win_row,
+    native.call("tf_sparse_attention", dev(q), T, Hl, Dh, dev(pos), dev(region), None, dev(win), ring * win_row,
                 win_row, ring, window, dev(comp), C * comp_row, comp_row, dev(sel), k, None, C,
                 1 / math.sqrt(Dh), nsplit, part_o, part_lse, dev(sink), dev(freqs), 64, out, None, Hl * Dh, st.t)
     st.check()

@@ -23,6 +23,7 @@ struct AttnParams {
   int T, Hl, Dh;
   const int* pos;             // [T]
   const int* region;          // [T]
+  const int* min_pos;         // [T] or null: oldest position a row may attend in the window
   const uint8_t* win;         // [regions][ring][Dh + Dh/32]
   long win_region_stride;
   int ring, window;
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
   const int r = blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int pos = p.pos[r], reg = p.region[r];
-  const int nwin = min(pos + 1, p.window);
+  const int nwin = min(pos + 1 - (p.min_pos ? p.min_pos[r] : 0), p.window);
   int nsel = 0;
   if (p.comp) {
     if (p.sel_count) nsel = p.sel_count[r];
@@ -296,6 +297,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 }  // namespace
 
 TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* pos, const int* region,
+                               const int* min_pos,
                                const void* win, long win_region_stride, int win_row, int ring, int window,
                                const void* comp, long comp_region_stride, int comp_row, const int* sel, int sel_stride,
                                const int* sel_count, int maxC, float scale, int nsplit, float* part_o,
@@ -304,7 +306,7 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
   if (Dh != 128 && Dh != 64) return -1;
   if (Hl > 64 || nsplit < 1 || (win_row % 16) || (comp && (comp_row % 16))) return -1;
   AttnParams p;
-  p.q = (const __nv_bfloat16*)q; p.T = T; p.Hl = Hl; p.Dh = Dh; p.pos = pos; p.region = region;
+  p.q = (const __nv_bfloat16*)q; p.T = T; p.Hl = Hl; p.Dh = Dh; p.pos = pos; p.region = region; p.min_pos = min_pos;
   p.win = (const uint8_t*)win; p.win_region_stride = win_region_stride; p.ring = ring; p.window = window; p.win_row = win_row; p.comp_row = comp_row;
   p.comp = (const uint8_t*)comp; p.comp_region_stride = comp_region_stride; p.sel = sel;
   p.sel_stride = sel_stride; p.sel_count = sel_count; p.maxC = maxC;

@@ -80,6 +80,11 @@ __global__ void add_norm_kernel(__nv_bfloat16* __restrict__ x, const void* __res
 }
 
 // --------------------------------------------------------------------------- attention prep
+// The compressor inputs of an open group wait in a ring addressed by absolute position with
+// `ratio + kCarrySpan` slots per conversation: a speculative row up to kCarrySpan positions past
+// the committed length can then never overwrite a slot that a later, shorter re-run still needs.
+constexpr int kCarrySpan = 32;
+
 struct PrepParams {
   const void* P;        // fused projection output [T, ldp]; kind 0 = f32, 1 = bf16
   int p_kind, ldp;
@@ -229,13 +234,14 @@ __global__ void attn_prep_kernel(PrepParams p) {
       return;
     }
     const int first = p.first_row[r];
-    const float* car = p.carry + (long)reg * p.ratio * 2 * C;
+    const int CS = p.ratio + kCarrySpan;
+    const float* car = p.carry + (long)reg * CS * 2 * C;
     for (int c = tid; c < C; c += blockDim.x) {
       float mx = -INFINITY;
       for (int j = 0; j < p.ratio; ++j) {
         const int mr = r - (p.ratio - 1 - j);
         float gt = (mr >= first) ? ldp(p, mr, p.off_cg + c)
-                                 : car[((pos - (p.ratio - 1 - j)) % p.ratio) * 2 * C + C + c];
+                                 : car[((pos - (p.ratio - 1 - j)) % CS) * 2 * C + C + c];
         mx = fmaxf(mx, gt);
       }
       float den = 0.f, num = 0.f;
@@ -246,7 +252,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
           gt = ldp(p, mr, p.off_cg + c);
           vv = ldp(p, mr, p.off_cv + c);
         } else {
-          const float* cs = car + ((pos - (p.ratio - 1 - j)) % p.ratio) * 2 * C;
+          const float* cs = car + ((pos - (p.ratio - 1 - j)) % CS) * 2 * C;
           gt = cs[C + c];
           vv = cs[c];
         }
@@ -293,7 +299,8 @@ __global__ void carry_save_kernel(PrepParams p) {
   const int group_end = (pos / p.ratio + 1) * p.ratio - 1;
   if (group_end <= p.last_pos[r]) return;
   const int C = p.Dh + p.Di;
-  float* cs = p.carry + ((long)reg * p.ratio + (pos % p.ratio)) * 2 * C;
+  const int CS = p.ratio + kCarrySpan;
+  float* cs = p.carry + ((long)reg * CS + (pos % CS)) * 2 * C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     cs[c] = ldp(p, r, p.off_cv + c);
     cs[C + c] = ldp(p, r, p.off_cg + c);

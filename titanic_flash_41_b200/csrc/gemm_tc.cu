@@ -40,6 +40,10 @@ struct GemmParams {
   int ldc;
   int out_kind;             // 0 f32, 2 bf16
   TfStatusWord* status;
+  // grouped form (routed experts): A rows are expert-sorted in 128-row padded segments; M tile i
+  // belongs to expert tile_expert[i] whose weights are rows [e*N, (e+1)*N) of B
+  const int* tile_expert;
+  const int* num_m_tiles;
 };
 
 template <int KIND>
@@ -61,7 +65,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int BK = (KIND == 0) ? 64 : 128;               // elements per 128-byte row
   const int kblocks = (p.K + BK - 1) / BK;
-  const int mt = (p.M + BM - 1) / BM, nt = p.N / BN;
+  const int mt = p.tile_expert ? *p.num_m_tiles : (p.M + BM - 1) / BM, nt = p.N / BN;
   const int tiles = mt * nt;
 
   if (threadIdx.x == 0) {
@@ -91,6 +95,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+        const int nb0 = n0 + (p.tile_expert ? p.tile_expert[tile % mt] * p.N : 0);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -98,7 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           tc::mbar_expect_tx(full(s), kStageBytes);
           const uint32_t sa = base + s * kStageBytes;
           tc::tma_load_2d(sa, &mapA, kb * BK, m0, full(s));
-          tc::tma_load_2d(sa + BM * 128, &mapB, kb * BK, n0, full(s));
+          tc::tma_load_2d(sa + BM * 128, &mapB, kb * BK, nb0, full(s));
         }
       }
       if (!ok) {
@@ -160,7 +165,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       }
       const int groups = (KIND == 2) ? kblocks : 1;
       const float* sa_row = (KIND == 2 && row < p.M) ? p.sa + (long)row * p.ldsa : nullptr;
-      const float* sb_row = (KIND == 2) ? p.sb + (long)(n0 >> 7) * p.ldsb : nullptr;
+      const int nb0 = n0 + (p.tile_expert ? p.tile_expert[tile % mt] * p.N : 0);
+      const float* sb_row = (KIND == 2) ? p.sb + (long)(nb0 >> 7) * p.ldsb : nullptr;
       float s_next = (KIND == 2) ? (sa_row ? sa_row[0] : 0.f) * sb_row[0] : 1.f;
       for (int g = 0; g < groups && ok; ++g, ++grp) {
         const int buf = grp % kAccBufs;
@@ -225,9 +231,12 @@ int g_sms = 0;
 
 // kind 0: A,B bf16; kind 1/2: A,B e4m3 (2 = block scales sa [M,K/128], sb [N/128,K/128]).
 // lda/ldb in elements, ldc in elements.  N must be a multiple of 128, K of 128 (64 for bf16).
+// Grouped form: `experts` > 0, B holds experts*N rows, M is the capacity of the padded A matrix,
+// tile_expert/num_m_tiles come from tf_moe_plan.
 TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb, void* C, int ldc, int M,
                       int N, int K, const float* sa, int ldsa, const float* sb, int ldsb, int out_kind,
-                      void* status, cudaStream_t stream) {
+                      const int* tile_expert, const int* num_m_tiles, int experts, void* status,
+                      cudaStream_t stream) {
   if (M <= 0) return 0;
   if (N % BN != 0 || (kind == 0 ? K % 64 : K % 128) != 0) return -1;
   if (out_kind != 0 && out_kind != 2) return -1;
@@ -237,7 +246,7 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
   const int es = kind == 0 ? 2 : 1;
   const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   if (!tc::make_map_2d(&ma, A, dt, es, M, K, (uint64_t)lda * es, BM)) return -2;
-  if (!tc::make_map_2d(&mb, B, dt, es, N, K, (uint64_t)ldb * es, BN)) return -2;
+  if (!tc::make_map_2d(&mb, B, dt, es, (uint64_t)N * (experts > 0 ? experts : 1), K, (uint64_t)ldb * es, BN)) return -2;
   if (!g_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -246,6 +255,7 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.kind = kind; p.sa = sa; p.ldsa = ldsa; p.sb = sb; p.ldsb = ldsb;
   p.C = C; p.ldc = ldc; p.out_kind = out_kind; p.status = (TfStatusWord*)status;
+  p.tile_expert = experts > 0 ? tile_expert : nullptr; p.num_m_tiles = num_m_tiles;
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < g_sms ? tiles : g_sms;
   static bool attr_set = false;

@@ -1,0 +1,243 @@
+// Kernels around the tensor-core GEMMs for large row counts (prefill chunks):
+//   * row-wise FP8 quantisation with one fp32 scale per 128 (activations entering an FP8 GEMM)
+//   * clamped SwiGLU (+ optional FP8 quantisation) over a [rows, 2I] GEMM output
+//   * routed-expert bookkeeping without a host round trip: histogram of (token, slot) pairs per
+//     local expert, 128-row-padded segment offsets, per-M-tile expert table, destination row of
+//     every pair
+//   * gather + quantise token rows into the expert-sorted, padded activation matrix
+//   * MXFP4 (e2m1 + UE8M0/32) expert weights re-expressed as FP8 with one power-of-two scale per
+//     128x128 block, the operand format of the block-scaled tcgen05 GEMM
+//   * weighted combine of the expert outputs in fixed top-k order (+ shared expert)
+// Reference counterparts: kernels/moe_frontend.cuh (route grouping tables), kernels/
+// shared_swiglu_quant.cuh, kernels/ffn_sum_shared.cuh, src/expert_packing.rs (weight repack).
+#include "common.cuh"
+
+namespace {
+
+// one warp per (row, 128-block): x f16/bf16/f32 -> e4m3 + scale
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<__half>(const __half* p) { return __half2float(*p); }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+
+template <typename T>
+__global__ void quant_rows_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ row_src,
+                                  int src_div, const int* __restrict__ row_dst, uint8_t* __restrict__ q,
+                                  float* __restrict__ s, int rows, int K) {
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_per_row = K / 128;
+  const long item = (long)blockIdx.x * warps + warp;
+  if (item >= (long)rows * kb_per_row) return;
+  const int r = (int)(item / kb_per_row), kb = (int)(item % kb_per_row);
+  const long src = row_src ? row_src[r] / src_div : (src_div > 1 ? r / src_div : r);
+  const long dst = row_dst ? row_dst[r] : r;
+  if (dst < 0) return;
+  const T* xp = x + src * ldx + kb * 128 + lane * 4;
+  float v[4], am = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = ldf<T>(xp + j);
+    am = fmaxf(am, fabsf(v[j]));
+  }
+  am = warp_max(am);
+  const float sc = fmaxf(am, 1e-12f) / 448.f;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) packed |= (uint32_t)float_to_e4m3(v[j] / sc) << (8 * j);
+  reinterpret_cast<uint32_t*>(q + dst * K + kb * 128)[lane] = packed;
+  if (lane == 0) s[dst * kb_per_row + kb] = sc;
+}
+
+// y [rows, 2I] (gate | up halves) -> act: f16 [rows, I] and/or fp8 + scales
+template <typename T>
+__global__ void swiglu_rows_kernel(const T* __restrict__ y, long ldy, __half* __restrict__ out16, long ldo,
+                                   uint8_t* __restrict__ q, float* __restrict__ s, int rows, int I, float limit,
+                                   const int* __restrict__ n_rows_dev) {
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_per_row = I / 128;
+  const long item = (long)blockIdx.x * warps + warp;
+  if (n_rows_dev) rows = min(rows, *n_rows_dev);
+  if (item >= (long)rows * kb_per_row) return;
+  const int r = (int)(item / kb_per_row), kb = (int)(item % kb_per_row);
+  const T* g = y + (long)r * ldy + kb * 128 + lane * 4;
+  const T* u = g + I;
+  float v[4], am = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float gate = ldf<T>(g + j), up = ldf<T>(u + j);
+    if (limit > 0.f) {
+      gate = fminf(gate, limit);
+      up = fminf(fmaxf(up, -limit), limit);
+    }
+    v[j] = __half2float(__float2half(gate / (1.f + __expf(-gate)) * up));
+    am = fmaxf(am, fabsf(v[j]));
+  }
+  if (out16) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out16[(long)r * ldo + kb * 128 + lane * 4 + j] = __float2half(v[j]);
+  }
+  if (q) {
+    am = warp_max(am);
+    const float sc = fmaxf(am, 1e-12f) / 448.f;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= (uint32_t)float_to_e4m3(v[j] / sc) << (8 * j);
+    reinterpret_cast<uint32_t*>(q + (long)r * I + kb * 128)[lane] = packed;
+    if (lane == 0) s[(long)r * kb_per_row + kb] = sc;
+  }
+}
+
+// ---- routed-expert bookkeeping ------------------------------------------------------------
+__global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int El, int* counts) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  const int e = ids[i] - e_lo;
+  if (e >= 0 && e < El) atomicAdd(&counts[e], 1);
+}
+// single CTA: padded offsets, tile table, cursors reset.  tile_expert has room for max_tiles ints.
+__global__ void moe_offsets_kernel(int* counts, int El, int* offsets, int* cursor, int* tile_expert,
+                                   int max_tiles, int* num_tiles, int* padded_rows) {
+  if (threadIdx.x == 0) {
+    int off = 0, t = 0;
+    for (int e = 0; e < El; ++e) {
+      offsets[e] = off;
+      cursor[e] = 0;
+      const int tiles = (counts[e] + 127) / 128;
+      for (int j = 0; j < tiles && t < max_tiles; ++j) tile_expert[t++] = e;
+      off += tiles * 128;
+      counts[e] = 0;            // ready for the next launch
+    }
+    offsets[El] = off;
+    *num_tiles = t;
+    *padded_rows = off;
+  }
+}
+__global__ void moe_place_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int El,
+                                 const int* __restrict__ offsets, int* cursor, int* pair_dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  const int e = ids[i] - e_lo;
+  pair_dst[i] = (e >= 0 && e < El) ? offsets[e] + atomicAdd(&cursor[e], 1) : -1;
+}
+
+// ---- MXFP4 -> FP8 with one power-of-two scale per 128x128 block -----------------------------
+// grid (K/128, N/128, experts), 128 threads: thread = row of the block
+__global__ void mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sc,
+                                          uint8_t* __restrict__ out, float* __restrict__ out_s, int N, int K,
+                                          long out_expert_stride, int out_row0, int out_N) {
+  __shared__ int smax;
+  const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
+  const long row = (long)e * N + nb * 128 + r;
+  const uint8_t* srow = sc + row * (K / 32) + kb * 4;
+  if (r == 0) smax = 0;
+  __syncthreads();
+  int c[4], mx = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    c[j] = srow[j];
+    mx = max(mx, c[j]);
+  }
+  atomicMax(&smax, mx);
+  __syncthreads();
+  const int top = smax;
+  const uint8_t* wrow = w + row * (K / 2) + kb * 64;
+  uint8_t* orow = out + (long)e * out_expert_stride + ((long)out_row0 + nb * 128 + r) * K + kb * 128;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float f = exp2f((float)(c[j] - top));
+    const uint4 pk = *reinterpret_cast<const uint4*>(wrow + j * 16);
+    const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo |= (uint32_t)float_to_e4m3(e2m1_to_float((words[q] >> (4 * i)) & 0xfu) * f) << (8 * i);
+        hi |= (uint32_t)float_to_e4m3(e2m1_to_float((words[q] >> (4 * i + 16)) & 0xfu) * f) << (8 * i);
+      }
+      o[2 * q] = lo;
+      o[2 * q + 1] = hi;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(orow + j * 32);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  if (r == 0) {
+    const long srow_o = ((long)e * out_N + out_row0) / 128 + nb;
+    out_s[srow_o * (K / 128) + kb] = ue8m0_to_float((uint8_t)top);
+  }
+}
+
+// out[t,:] = sum_j wts[t,j] * y[pair_dst[t*k+j],:] (fixed j order) + shared[t,:]
+template <typename T>
+__global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const int* __restrict__ pair_dst,
+                                        const float* __restrict__ wts, const float* __restrict__ shared_y,
+                                        float* __restrict__ out, int d, int topk) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      const int dst = pair_dst[t * topk + j];
+      if (dst >= 0) acc = fmaf(wts[t * topk + j], ldf<T>(y + (long)dst * ldy + i), acc);
+    }
+    if (shared_y) acc += shared_y[(long)t * d + i];
+    out[(long)t * d + i] = acc;
+  }
+}
+
+}  // namespace
+
+// x_kind: 0 f32, 1 f16, 2 bf16.  row_src/row_dst optional (gather / scatter); src row = row_src[r] / src_div.
+TF_API int tf_quant_rows(const void* x, int x_kind, long ldx, const int* row_src, int src_div,
+                         const int* row_dst, void* q, float* s, int rows, int K, cudaStream_t st) {
+  if (K % 128 || rows <= 0) return rows <= 0 ? 0 : -1;
+  const long items = (long)rows * (K / 128);
+  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (src_div < 1) src_div = 1;
+  if (x_kind == 0) quant_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
+  else if (x_kind == 1) quant_rows_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
+  else quant_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_swiglu_rows(const void* y, int y_kind, long ldy, void* out16, long ldo, void* q, float* s,
+                          int rows, int I, float limit, const int* n_rows_dev, cudaStream_t st) {
+  if (I % 128 || rows <= 0) return rows <= 0 ? 0 : -1;
+  const long items = (long)rows * (I / 128);
+  const unsigned grid = (unsigned)((items + 7) / 8);
+  if (y_kind == 0) swiglu_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
+  else if (y_kind == 2) swiglu_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
+  else return -1;
+  return (int)cudaGetLastError();
+}
+
+// counts must be zero on entry (it is left zeroed).  tile_expert capacity = max_tiles.
+TF_API int tf_moe_plan(const int* ids, int n_pairs, int e_lo, int El, int* counts, int* offsets, int* cursor,
+                       int* tile_expert, int max_tiles, int* num_tiles, int* padded_rows, int* pair_dst,
+                       cudaStream_t st) {
+  const unsigned grid = (unsigned)((n_pairs + 255) / 256);
+  moe_count_kernel<<<grid, 256, 0, st>>>(ids, n_pairs, e_lo, El, counts);
+  moe_offsets_kernel<<<1, 32, 0, st>>>(counts, El, offsets, cursor, tile_expert, max_tiles, num_tiles, padded_rows);
+  moe_place_kernel<<<grid, 256, 0, st>>>(ids, n_pairs, e_lo, El, offsets, cursor, pair_dst);
+  return (int)cudaGetLastError();
+}
+
+// w [E, N, K/2], sc [E, N, K/32] -> out rows [out_row0, out_row0+N) of every expert's [out_N, K] fp8 matrix
+TF_API int tf_mxfp4_to_fp8_block(const void* w, const void* sc, void* out, float* out_s, int E, int N, int K,
+                                 int out_row0, int out_N, cudaStream_t st) {
+  if (N % 128 || K % 128 || out_row0 % 128 || out_N % 128) return -1;
+  dim3 grid(K / 128, N / 128, E);
+  mxfp4_to_fp8_block_kernel<<<grid, 128, 0, st>>>((const uint8_t*)w, (const uint8_t*)sc, (uint8_t*)out, out_s,
+                                                  N, K, (long)out_N * K, out_row0, out_N);
+  return (int)cudaGetLastError();
+}
+
+TF_API int tf_moe_combine_perm(const void* y, int y_kind, long ldy, const int* pair_dst, const float* wts,
+                               const float* shared_y, float* out, int T, int d, int topk, cudaStream_t st) {
+  if (y_kind == 0) moe_combine_perm_kernel<float><<<T, 256, 0, st>>>((const float*)y, ldy, pair_dst, wts, shared_y, out, d, topk);
+  else if (y_kind == 2) moe_combine_perm_kernel<__nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, out, d, topk);
+  else return -1;
+  return (int)cudaGetLastError();
+}

@@ -276,6 +276,16 @@ class StepPlan:
     last_pos: np.ndarray        # [T] last position of the row's conversation in this launch
     logit_rows: np.ndarray      # rows whose logits are wanted
     group_rows: int             # rows per conversation block (uniform), used to group index scoring
+    min_pos: Optional[np.ndarray] = None   # [T] oldest window position a row may attend (default 0)
+
+    META_ROWS = 7
+
+    def meta_host(self, ratio: int) -> np.ndarray:
+        """[META_ROWS, T] int32 block uploaded per launch: tokens, pos, region, first_row, last_pos,
+        valid compressed entries, window floor."""
+        mp = self.min_pos if self.min_pos is not None else np.zeros_like(self.pos)
+        return np.stack([self.tokens, self.pos, self.region, self.first_row, self.last_pos,
+                         (self.pos + 1) // ratio, mp]).astype(np.int32)
 
     @staticmethod
     def build(blocks: Sequence[Tuple[int, int, Sequence[int]]], logits: str = "all") -> "StepPlan":
@@ -340,7 +350,8 @@ class Engine:
         C = cfg.head_dim + cfg.index_dim
         self.comp = torch.zeros(ns, self.regions, self.maxC, self.comp_row, **u8)
         self.keys = torch.zeros(ns, self.regions, self.maxC, self.key_row, **u8)
-        self.carry = torch.zeros(ns, self.regions, cfg.compress_ratio, 2 * C, dtype=torch.float32,
+        # position-addressed ring of open-group compressor inputs (ratio + 32 slots: csrc kCarrySpan)
+        self.carry = torch.zeros(ns, self.regions, cfg.compress_ratio + 32, 2 * C, dtype=torch.float32,
                                  device=self.dev)
         self._scratch: Dict[int, dict] = {}
         self._dq_cache: Dict[int, torch.Tensor] = {}
@@ -396,6 +407,8 @@ class Engine:
         Vl = cfg.vocab // comm.world
         embed = torch.randn(cfg.vocab, d, generator=g, device=device, dtype=torch.bfloat16) * cfg.init_std
         head = torch.randn(Vl, d, generator=g, device=device, dtype=torch.bfloat16) * cfg.init_std
+        if cfg.draft is not None and Vl % 128 == 0:
+            extra["head"] = quant_fp8_device(head)     # the draft reads an FP8 copy of the head
         return cls(cfg, ecfg, layers, embed, head, torch.ones(d, dtype=torch.bfloat16, device=device),
                    comm, device, max_chunk, drafts, extra)
 
@@ -411,13 +424,14 @@ class Engine:
         maxN = max(l.proj.q.shape[0] for l in self.layers + self.draft_layers)
         npairs = T * cfg.topk
         nsplit = self._nsplit(T)
+        big = T > self.SMALL_M and getattr(self, "big_moe_full", None) is not None
         Il = cfg.shared_inter * cfg.n_shared // self.world
         b = dict(
-            meta=torch.zeros(6, T, **i32),
+            meta=torch.zeros(StepPlan.META_ROWS, T, **i32),
             x=torch.zeros(T, d, dtype=torch.bfloat16, device=dev),
             h16=torch.zeros(T, d, dtype=torch.float16, device=dev),
             hb=torch.zeros(T, d, dtype=torch.bfloat16, device=dev),
-            P=torch.zeros(T, maxN, **f32),
+            P=(torch.zeros(T, maxN, **f32) if not big else torch.zeros(T, maxN, dtype=torch.bfloat16, device=dev)),
             q=torch.zeros(T, Hl, Dh, dtype=torch.bfloat16, device=dev),
             iq=torch.zeros(T, cfg.index_heads, cfg.index_dim, dtype=torch.bfloat16, device=dev),
             iw=torch.zeros(T, cfg.index_heads, **f32),
@@ -433,8 +447,8 @@ class Engine:
             g_expert=torch.zeros(self.El, **i32), g_start=torch.zeros(self.El, **i32),
             g_count=torch.zeros(self.El, **i32), n_groups=torch.zeros(1, **i32),
             sorted_pairs=torch.zeros(npairs, **i32), n_local=torch.zeros(1, **i32),
-            act=torch.zeros(npairs, cfg.moe_inter, dtype=torch.float16, device=dev),
-            y_pair=torch.zeros(npairs, d, **f32),
+            act=torch.zeros(1 if big else npairs, cfg.moe_inter, dtype=torch.float16, device=dev),
+            y_pair=torch.zeros(1 if big else npairs, d, **f32),
             s_act=torch.zeros(T, max(Il, 1), dtype=torch.float16, device=dev),
             s_y=torch.zeros(T, d, **f32),
         )
@@ -493,7 +507,7 @@ class Engine:
             self.comm.all_reduce(t)
 
     # -- one layer ---------------------------------------------------------------------------
-    def _layer(self, li: int, L: LayerWeights, T: int, b: dict, plan: StepPlan, first: bool) -> None:
+    def _layer(self, li: int, L: LayerWeights, T: int, b: dict, nmax: int, rpg: int, first: bool) -> None:
         cfg = self.cfg
         d, Dh, Hl = cfg.hidden, cfg.head_dim, self.Hl
         pos, region, first_row, last_pos, nvalid = (b["meta"][i] for i in (1, 2, 3, 4, 5))
@@ -505,7 +519,7 @@ class Engine:
         self._linear(b["h16"], L.proj, P, T)
         o = L.offs
         slot = self.src_slot.get(li, 0)
-        native.call("tf_attn_prep", P, 0, P.stride(0), T, pos, region, first_row, last_pos, Hl, Dh,
+        native.call("tf_attn_prep", P, 0 if P.dtype == torch.float32 else 1, P.stride(0), T, pos, region, first_row, last_pos, Hl, Dh,
                     cfg.rope.dim, self.freqs, self.cfreqs, L.kv_norm, cfg.rms_eps, b["q"], self.win[li],
                     self.win[li].stride(0), self.win_row, self.comp_row, self.key_row, self.ring,
                     o["q"], o["kv"], o.get("cv", -1), o.get("cg", -1), o.get("iq", -1), o.get("iw", -1),
@@ -520,10 +534,10 @@ class Engine:
             sslot = self.src_slot[L.kv_source]
             comp = self.comp[sslot]
             if L.is_index_source:
-                self._index(L, T, b, plan, sslot, li)
+                self._index(L, T, b, nmax, rpg, sslot, li)
             sel, selcnt = b["sel"][L.index_source], b["selcnt"][L.index_source]
         nsplit = b["part_o"].shape[1]
-        native.call("tf_sparse_attention", b["q"], T, Hl, Dh, pos, region, self.win[li],
+        native.call("tf_sparse_attention", b["q"], T, Hl, Dh, pos, region, b["meta"][6], self.win[li],
                     self.win[li].stride(0), self.win_row, self.ring, cfg.window, comp,
                     comp.stride(0) if comp is not None else 0, self.comp_row, sel,
                     cfg.index_topk, selcnt, self.maxC, 1.0 / math.sqrt(Dh), nsplit, b["part_o"],
@@ -537,21 +551,16 @@ class Engine:
         self._moe(L, T, b)
         self._allreduce(b["delta"][:T])
 
-    def _index(self, L: LayerWeights, T: int, b: dict, plan: StepPlan, sslot: int, li: int) -> None:
+    def _index(self, L: LayerWeights, T: int, b: dict, nmax: int, rows_per_group: int, sslot: int,
+               li: int) -> None:
         cfg = self.cfg
         region, nvalid = b["meta"][2], b["meta"][5]
-        nmax = int((plan.pos.max() + 1) // cfg.compress_ratio)
         sel, selcnt = b["sel"][li], b["selcnt"][li]
         if nmax == 0:
             sel.fill_(-1)
             selcnt.zero_()
             return
         scores = self.scores_buffer(T, nmax)
-        # a scoring CTA serves consecutive rows of ONE conversation
-        if plan.group_rows == T:
-            rows_per_group = min(T, 32)
-        else:
-            rows_per_group = plan.group_rows if plan.group_rows <= 32 else 1
         native.call("tf_index_scores", b["iq"], b["iw"], region, nvalid, self.keys[sslot],
                     self.keys[sslot].stride(0), self.key_row, T, cfg.index_heads, cfg.index_dim,
                     rows_per_group, scores, scores.stride(0), 0, nmax)
@@ -578,6 +587,9 @@ class Engine:
                         I // 2, I // 32, b["act"], I, b["y_pair"], d, 0, d, I, 0, b["g_expert"],
                         b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], 1, slots,
                         min(T, 16), 0.0)
+        elif getattr(self, "big_moe_full", None) is not None:
+            self.big_moe_full(self, L, T, b)       # permute, grouped GEMMs, shared expert, combine
+            return
         else:
             self._moe_large(L, T, b)
         shared = None
@@ -612,30 +624,69 @@ class Engine:
     # -- public ------------------------------------------------------------------------------
     def upload_plan(self, plan: StepPlan, b: dict) -> None:
         T = plan.T
-        host = np.stack([plan.tokens, plan.pos, plan.region, plan.first_row, plan.last_pos,
-                         (plan.pos + 1) // self.cfg.compress_ratio]).astype(np.int32)
+        host = plan.meta_host(self.cfg.compress_ratio)
         b["meta"][:, :T].copy_(torch.from_numpy(host), non_blocking=True)
 
+    @staticmethod
+    def plan_shape(plan: StepPlan, ratio: int) -> Tuple[int, int]:
+        """(largest count of compressed entries any row may score, rows per scoring group): a
+        scoring CTA serves consecutive rows of ONE conversation."""
+        nmax = int((plan.pos.max() + 1) // ratio)
+        T = plan.T
+        if plan.group_rows == T:
+            rpg = min(T, 32)
+        else:
+            rpg = plan.group_rows if plan.group_rows <= 32 else 1
+        return nmax, rpg
+
     def forward(self, plan: StepPlan, need_logits: bool = True) -> Optional[torch.Tensor]:
-        cfg = self.cfg
         T = plan.T
         assert T <= self.max_chunk
         b = self._bufs(T)
         self.upload_plan(plan, b)
-        native.call("tf_embed", b["meta"][0], self.embed_w, b["x"], T, cfg.hidden, cfg.vocab, self.status.t)
-        for li, L in enumerate(self.layers):
-            self._layer(li, L, T, b, plan, first=(li == 0))
-        return self._head(T, b, plan, need_logits)
+        nmax, rpg = self.plan_shape(plan, self.cfg.compress_ratio)
+        rows = torch.from_numpy(plan.logit_rows).to(self.dev).long() if need_logits else None
+        return self.run(T, b, nmax, rpg, rows)
 
-    def _head(self, T: int, b: dict, plan: StepPlan, need_logits: bool) -> Optional[torch.Tensor]:
+    def run(self, T: int, b: dict, nmax: int, rpg: int, logit_rows: Optional[torch.Tensor],
+            layer_lo: int = 0, layer_hi: Optional[int] = None, x_in: Optional[torch.Tensor] = None
+            ) -> Optional[torch.Tensor]:
+        """Launch layers [layer_lo, layer_hi) on rows whose metadata already sits in ``b['meta']``
+        (no host work: this is what a CUDA graph captures).  ``x_in`` replaces the embedding as
+        the input residual (late-group replay); the head runs only when the last layer does."""
+        cfg = self.cfg
+        layer_hi = len(self.layers) if layer_hi is None else layer_hi
+        if x_in is None:
+            native.call("tf_embed", b["meta"][0], self.embed_w, b["x"], T, cfg.hidden, cfg.vocab, self.status.t)
+        else:
+            b["x"][:T].copy_(x_in)
+        for li in range(layer_lo, layer_hi):
+            self._layer(li, self.layers[li], T, b, nmax, rpg, first=(li == layer_lo))
+        if layer_hi < len(self.layers):
+            return None
+        return self._head(T, b, logit_rows)
+
+    def residual_rows(self, b: dict, rows: torch.Tensor) -> torch.Tensor:
+        """Complete residual stream (x + pending sublayer output) of the given rows, bf16."""
+        return (b["x"][rows].float() + b["delta"][rows]).to(torch.bfloat16)
+
+    def _head(self, T: int, b: dict, rows: Optional[torch.Tensor], draft: bool = False
+              ) -> Optional[torch.Tensor]:
         cfg = self.cfg
         d = cfg.hidden
-        native.call("tf_add_norm", b["x"], b["delta"], 0, d, self.final_norm, None, b["hb"], None, None,
-                    T, d, cfg.rms_eps)
-        self.last_hidden = b["x"]
-        if not need_logits:
+        native.call("tf_add_norm", b["x"], b["delta"], 0, d, self.final_norm, b["h16"] if draft else None,
+                    b["hb"], None, None, T, d, cfg.rms_eps)
+        if not draft:
+            self.last_hidden = b["x"]
+        if rows is None:
             return None
-        rows = torch.from_numpy(plan.logit_rows).to(self.dev).long()
+        if draft and self.draft_extra.get("head") is not None:
+            hw = self.draft_extra["head"]
+            Vl = hw.n
+            h16 = b["h16"][rows].contiguous()
+            logits = torch.empty(h16.shape[0], Vl, dtype=torch.float32, device=self.dev)
+            self._linear(h16, hw, logits, h16.shape[0])
+            return self.comm.all_gather(logits, dim=1) if self.world > 1 else logits
         hsel = b["hb"][rows].contiguous()
         Vl = self.head_w.shape[0]
         n = hsel.shape[0]
@@ -647,3 +698,28 @@ class Engine:
         if self.world > 1:
             logits = self.comm.all_gather(logits, dim=1)
         return logits
+
+    # -- draft head ---------------------------------------------------------------------------
+    def draft_run(self, T: int, b: dict, hidden_prev: torch.Tensor, logit_rows: Optional[torch.Tensor]
+                  ) -> Optional[torch.Tensor]:
+        """Draft head on rows whose metadata sits in ``b['meta']``: the embedding of each row's token
+        and the hidden state of the position before it are normalised, concatenated and projected
+        to the model width, then run through the draft layer(s) and the FP8 copy of the vocabulary
+        head (reference conditioning: src/dspark_conditioning.rs, main_proj [d, 3d])."""
+        cfg = self.cfg
+        d = cfg.hidden
+        ex = self.draft_extra
+        if "cat16" not in b:
+            b["cat16"] = torch.zeros(T, 2 * d, dtype=torch.float16, device=self.dev)
+            b["e16"] = torch.zeros(T, d, dtype=torch.float16, device=self.dev)
+        native.call("tf_embed", b["meta"][0], self.embed_w, b["x"], T, d, cfg.vocab, self.status.t)
+        native.call("tf_add_norm", b["x"], None, 0, d, ex["enorm"], b["e16"], None, None, None, T, d, cfg.rms_eps)
+        native.call("tf_add_norm", hidden_prev, None, 0, d, ex["hnorm"], b["h16"], None, None, None, T, d,
+                    cfg.rms_eps)
+        b["cat16"][:, :d].copy_(b["e16"])
+        b["cat16"][:, d:].copy_(b["h16"])
+        self._linear(b["cat16"], ex["main_proj"], b["delta"], T)
+        b["x"].zero_()
+        for j, L in enumerate(self.draft_layers):
+            self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False)
+        return self._head(T, b, logit_rows, draft=True)

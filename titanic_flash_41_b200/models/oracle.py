@@ -295,6 +295,15 @@ class OracleModel:
         self.world, self.rank = self.comm.world, self.comm.rank
         self.last_hidden: Optional[torch.Tensor] = None
         self.last_selection: Dict[int, torch.Tensor] = {}
+        self.act_fp8 = False      # emulate FP8 (1x128 scaled) activations entering the linear layers
+
+    def _aq(self, x: torch.Tensor) -> torch.Tensor:
+        """What an FP8 GEMM actually multiplies: the activation after e4m3 quantisation with one
+        scale per (row, 128) — identity unless ``act_fp8`` is set."""
+        if not self.act_fp8 or x.shape[-1] % 128:
+            return x
+        q, s = codecs.fp8_act_quant_1x128(x.cpu())
+        return (q.float().reshape(*x.shape[:-1], -1, 128) * s.unsqueeze(-1)).reshape(x.shape).to(x.device, x.dtype)
 
     # -- pieces ----------------------------------------------------------
     def new_session(self, max_tokens: int) -> OracleSession:
@@ -330,6 +339,7 @@ class OracleModel:
         cfg, W = self.cfg, self.W
         T = h.shape[0]
         Dh = cfg.head_dim
+        h = self._aq(h)
         if cfg.q_lora_rank:
             qa = rmsnorm(h @ W[f"{p}.attn.wq_a.weight"].t(), W[f"{p}.attn.q_norm.weight"], cfg.rms_eps)
             q = qa @ W[f"{p}.attn.wq_b.weight"].t()
@@ -441,7 +451,7 @@ class OracleModel:
             mid = torch.einsum("tgp,grp->tgr", o.reshape(T, G, per), wa).reshape(T, G * cfg.o_lora_rank)
             out = mid @ W[f"{p}.attn.wo_b.weight"].t()
         else:
-            out = o.reshape(T, Hl * Dh) @ W[f"{p}.attn.wo.weight"].t()
+            out = self._aq(o.reshape(T, Hl * Dh)) @ W[f"{p}.attn.wo.weight"].t()
         return self.comm.all_reduce(out)
 
     def _ffn(self, p: str, h: torch.Tensor) -> torch.Tensor:
@@ -452,17 +462,18 @@ class OracleModel:
         y = torch.zeros(T, cfg.hidden, dtype=torch.float32, device=h.device)
         El = w1.shape[0]
         e0 = self.rank * El if (self.moe_parallel == "ep" and self.world > 1) else 0
+        h = self._aq(h)
         # fixed top-k order accumulation (kernels/ffn_sum_shared.cuh:7-33)
         for j in range(cfg.topk):
             for e in range(El):
                 m = ids[:, j] == (e + e0)
                 if m.any():
                     hh = h[m]
-                    a = swiglu(hh @ w1[e].t(), hh @ w3[e].t(), cfg.swiglu_limit)
+                    a = self._aq(swiglu(hh @ w1[e].t(), hh @ w3[e].t(), cfg.swiglu_limit))
                     y[m] += (a @ w2[e].t()).to(torch.float32) * wts[m, j:j + 1]
         if cfg.n_shared:
-            a = swiglu(h @ W[f"{p}.ffn.shared_experts.w1.weight"].t(),
-                       h @ W[f"{p}.ffn.shared_experts.w3.weight"].t(), cfg.swiglu_limit)
+            a = self._aq(swiglu(h @ W[f"{p}.ffn.shared_experts.w1.weight"].t(),
+                                h @ W[f"{p}.ffn.shared_experts.w3.weight"].t(), cfg.swiglu_limit))
             y = y + (a @ W[f"{p}.ffn.shared_experts.w2.weight"].t()).to(torch.float32)
         return self.comm.all_reduce(y.to(self.dtype))
 

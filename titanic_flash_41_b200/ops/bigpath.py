@@ -1,0 +1,113 @@
+"""Large-row-count (prefill) execution of the linear layers and routed experts on the tcgen05
+GEMM: activations are quantised to FP8 with one scale per (row, 128), dense weights are
+block-128 FP8, and MXFP4 expert weights are re-expressed per chunk as block-scaled FP8 so that
+one grouped launch covers every active expert of the rank.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+
+
+class BigPath:
+    def __init__(self, engine):
+        self.e = engine
+        self.buf = {}
+
+    def _get(self, name, shape, dtype):
+        t = self.buf.get(name)
+        n = 1
+        for s in shape:
+            n *= s
+        if t is None or t.numel() < n or t.dtype != dtype:
+            t = torch.empty(n, dtype=dtype, device=self.e.dev)
+            self.buf[name] = t
+        return t[:n].view(*shape)
+
+    # ---- dense ----------------------------------------------------------------------------
+    def gemm(self, eng, x16: torch.Tensor, w, out: torch.Tensor, M: int, w3=None) -> None:
+        N, K = w.q.shape
+        xq = self._get("xq", (M, K), torch.uint8)
+        xs = self._get("xs", (M, K // 128), torch.float32)
+        xk = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x16.dtype]
+        native.call("tf_quant_rows", x16, xk, x16.stride(0), None, 1, None, xq, xs, M, K)
+        st = eng.status.t
+        if w3 is None:
+            if out.dtype in (torch.float32, torch.bfloat16):
+                okind = 0 if out.dtype == torch.float32 else 2
+                native.call("tf_gemm_tc", 2, xq, K, w.q, K, out, out.stride(0), M, N, K, xs, K // 128, w.s,
+                            K // 128, okind, None, None, 0, st)
+            else:
+                tmp = self._get("gemm_tmp", (M, N), torch.bfloat16)
+                native.call("tf_gemm_tc", 2, xq, K, w.q, K, tmp, N, M, N, K, xs, K // 128, w.s, K // 128, 2,
+                            None, None, 0, st)
+                out[:M, :N].copy_(tmp)
+            return
+        # dual: gate and up projections side by side, then the clamped SwiGLU
+        y = self._get("dual_y", (M, 2 * N), torch.bfloat16)
+        native.call("tf_gemm_tc", 2, xq, K, w.q, K, y, 2 * N, M, N, K, xs, K // 128, w.s, K // 128, 2, None, None, 0, st)
+        native.call("tf_gemm_tc", 2, xq, K, w3.q, K, y[:, N:], 2 * N, M, N, K, xs, K // 128, w3.s, K // 128, 2,
+                    None, None, 0, st)
+        assert out.dtype == torch.float16
+        native.call("tf_swiglu_rows", y, 2, 2 * N, out, out.stride(0), None, None, M, N, eng.cfg.swiglu_limit, None)
+
+    # ---- routed experts ---------------------------------------------------------------------
+    def moe(self, eng, L, T: int, b: dict) -> None:
+        cfg = eng.cfg
+        d, I, El, k = cfg.hidden, cfg.moe_inter, eng.El, cfg.topk
+        npairs = T * k
+        cap = npairs + El * 127
+        cap = -(-cap // 128) * 128
+        max_tiles = cap // 128
+        i32 = torch.int32
+        z = self.buf.get("counts")
+        if z is None:
+            z = torch.zeros(El, dtype=i32, device=eng.dev)
+            self.buf["counts"] = z
+        offsets = self._get("offsets", (El + 1,), i32)
+        cursor = self._get("cursor", (El,), i32)
+        tile_e = self._get("tile_e", (max_tiles,), i32)
+        ntile = self._get("ntile", (2,), i32)
+        pair_dst = self._get("pair_dst", (npairs,), i32)
+        e_lo = eng.rank * El
+        native.call("tf_moe_plan", b["ids"], npairs, e_lo, El, z, offsets, cursor, tile_e, max_tiles, ntile[0:1],
+                    ntile[1:2], pair_dst)
+        # expert weights of this layer as block-scaled FP8: [El, 2I, d] (w1 | w3) and [El, d, I]
+        w13 = self._get("w13", (El, 2 * I, d), torch.uint8)
+        s13 = self._get("s13", (El * 2 * I // 128, d // 128), torch.float32)
+        w2 = self._get("w2", (El, d, I), torch.uint8)
+        s2 = self._get("s2", (El * d // 128, I // 128), torch.float32)
+        native.call("tf_mxfp4_to_fp8_block", L.ew1, L.es1, w13, s13, El, I, d, 0, 2 * I)
+        native.call("tf_mxfp4_to_fp8_block", L.ew3, L.es3, w13, s13, El, I, d, I, 2 * I)
+        native.call("tf_mxfp4_to_fp8_block", L.ew2, L.es2, w2, s2, El, d, I, 0, d)
+        # gather + quantise token rows into the expert-sorted padded matrix
+        xp = self._get("xp", (cap, d), torch.uint8)
+        xps = self._get("xps", (cap, d // 128), torch.float32)
+        native.call("tf_quant_rows", b["h16"], 1, d, None, k, pair_dst, xp, xps, npairs, d)
+        st = eng.status.t
+        y1 = self._get("y1", (cap, 2 * I), torch.bfloat16)
+        native.call("tf_gemm_tc", 2, xp, d, w13, d, y1, 2 * I, cap, 2 * I, d, xps, d // 128, s13, d // 128, 2,
+                    tile_e, ntile[0:1], El, st)
+        aq = self._get("aq", (cap, I), torch.uint8)
+        aqs = self._get("aqs", (cap, I // 128), torch.float32)
+        native.call("tf_swiglu_rows", y1, 2, 2 * I, None, 0, aq, aqs, cap, I, cfg.swiglu_limit, ntile[1:2])
+        y2 = self._get("y2", (cap, d), torch.bfloat16)
+        native.call("tf_gemm_tc", 2, aq, I, w2, I, y2, d, cap, d, I, aqs, I // 128, s2, I // 128, 2,
+                    tile_e, ntile[0:1], El, st)
+        shared = None
+        if cfg.n_shared:
+            eng._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
+            eng._linear(b["s_act"], L.sw2, b["s_y"], T)
+            shared = b["s_y"]
+        native.call("tf_moe_combine_perm", y2, 2, d, pair_dst, b["wts"], shared, b["delta"], T, d, k)
+
+
+def attach(engine) -> BigPath:
+    """Route rows beyond the small-M limit through the tensor-core path."""
+    bp = BigPath(engine)
+    engine.big_gemm = bp.gemm
+    engine.big_moe_full = bp.moe
+    return bp

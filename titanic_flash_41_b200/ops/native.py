@@ -101,6 +101,11 @@ def _conv(a, kind: str):
     return float(a)
 
 
+# kernels launched per exported call (for launch accounting); default 1
+_KERNELS_PER_CALL = {"tf_sparse_attention": 2, "tf_router": 2, "tf_spec_verify": 2}
+LAUNCHES = [0]
+
+
 def call(name: str, *args, stream: Optional[int] = None) -> None:
     """Invoke an exported kernel launcher; a trailing stream argument is filled in here."""
     l = lib()
@@ -113,6 +118,7 @@ def call(name: str, *args, stream: Optional[int] = None) -> None:
     if takes_stream:
         cargs.append(torch.cuda.current_stream().cuda_stream if stream is None else stream)
     rc = getattr(l, name)(*cargs)
+    LAUNCHES[0] += _KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
         raise NativeError(f"{name} failed with code {rc}" + (" (bad argument)" if rc == -1 else " (CUDA error)"))
 

@@ -1,0 +1,210 @@
+"""Speculative decoding of up to ``regions`` conversations in one batched step.
+
+One step (reference: GreedySession::batched_step, src/dspark_generation.rs:2333; finish_phase
+:2039): the draft head proposes ``depth`` tokens per conversation (sequential single-row passes,
+sampled at the request's temperature / top-p), the target verifies the anchor plus the
+proposals in one launch of ``S * (depth + 1)`` rows, block verification accepts a prefix and
+emits one more token, and the committed length advances by ``accepted + 1``.  Rejected rows need
+no rollback: all state is position-addressed.
+
+The whole device side of a step is captured in ONE CUDA graph per (conversations, depth)
+profile; per step the host uploads a small metadata block (positions, regions, uniforms),
+replays the graph and reads back (accepted, next token) per conversation.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..models.engine import Engine, StepPlan
+from ..ops import native
+from . import rng
+
+
+@dataclass
+class DecodeSlot:
+    region: int
+    length: int                 # committed tokens (all in the KV state)
+    anchor: int                 # sampled but not yet in the KV state
+    seed: int = 0
+    temperature: float = 0.6
+    top_p: float = 0.95
+    emitted: List[int] = field(default_factory=list)
+
+
+class SpecDecoder:
+    def __init__(self, engine: Engine, n_slots: int, depth: Optional[int] = None,
+                 temperature: float = 0.6, top_p: float = 0.95, use_graph: bool = True):
+        self.e = engine
+        cfg = engine.cfg
+        self.S = n_slots
+        self.g = cfg.draft.depth if depth is None else depth
+        if not engine.draft_layers:
+            self.g = 0
+        self.temperature, self.top_p = temperature, top_p
+        self.use_graph = use_graph and engine.ecfg.use_cuda_graphs
+        dev = engine.dev
+        S, g, V = self.S, self.g, cfg.vocab
+        self.R = g + 1
+        self.bv = engine._bufs(S * self.R)
+        self.bd = engine._bufs(S) if g > 0 else None
+        sb = native.lib().tf_rowstat_bytes()
+        f64 = dict(dtype=torch.float64, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        # pinned host staging + device mirrors: [meta_verify(6*S*R) | meta_draft(g*6*S)] ints, uniforms
+        self.n_meta_v = StepPlan.META_ROWS * S * self.R
+        self.n_meta_d = StepPlan.META_ROWS * S
+        self.h_int = torch.zeros(self.n_meta_v + g * self.n_meta_d, dtype=torch.int32).pin_memory()
+        self.d_int = torch.zeros_like(self.h_int, device=dev)
+        self.h_u = torch.zeros(S, g + 2, dtype=torch.float64).pin_memory()     # accept[g], final, spare
+        self.d_u = torch.zeros_like(self.h_u, device=dev)
+        self.h_ud = torch.zeros(S, max(g, 1), dtype=torch.float64).pin_memory()  # draft draws
+        self.d_ud = torch.zeros_like(self.h_ud, device=dev)
+        self.h_out = torch.zeros(2 + g, S, dtype=torch.int32).pin_memory()    # accepted, next, proposals
+        self.d_out = torch.zeros(2 + g, S, **i32)
+        self.hidden = torch.zeros(S, cfg.hidden, dtype=torch.bfloat16, device=dev)   # target hidden at length-1
+        self.dhid = torch.zeros(S, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.dlogits = torch.zeros(S, max(g, 1), V, dtype=torch.float32, device=dev)
+        self.dstat = torch.zeros(S, max(g, 1), sb, dtype=torch.uint8, device=dev)
+        self.tstat = torch.zeros(S, self.R, sb, dtype=torch.uint8, device=dev)
+        self.props = torch.zeros(S, max(g, 1), **i32)
+        self.ptok = torch.zeros(S, **i32)
+        self.pacc = torch.zeros(S, **i32)
+        self.u1 = torch.zeros(S, 2, **f64)
+        self.Rm = torch.zeros(S, self.R, **f64)
+        self.wm = torch.zeros(S, self.R, **f64)
+        self.R1 = torch.zeros(S, 1, **f64)
+        self.w1 = torch.zeros(S, 1, **f64)
+        self.rows_all = torch.arange(S * self.R, device=dev)
+        self.rows_d = torch.arange(S, device=dev)
+        self.row_of_anchor = torch.arange(S, device=dev) * self.R
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.nmax_bucket = 0
+        self.steps = 0
+
+    # ---------------------------------------------------------------------------------
+    def _fill_host(self, slots: Sequence[DecodeSlot]) -> int:
+        S, g, R = self.S, self.g, self.R
+        cfg = self.e.cfg
+        blocks = [(s.region, s.length, [s.anchor] + [0] * g) for s in slots]
+        plan = StepPlan.build(blocks)
+        ratio = cfg.compress_ratio
+        mv = plan.meta_host(ratio)
+        hi = self.h_int.numpy()
+        hi[: self.n_meta_v] = mv.reshape(-1)
+        for j in range(g):
+            pd = StepPlan.build([(s.region, s.length + j, [s.anchor if j == 0 else 0]) for s in slots])
+            md = pd.meta_host(ratio)
+            o = self.n_meta_v + j * self.n_meta_d
+            hi[o: o + self.n_meta_d] = md.reshape(-1)
+        hu = self.h_u.numpy()
+        for i, s in enumerate(slots):
+            dr, ac, fin = rng.round_uniforms(s.seed, s.length, g)
+            hu[i, :g] = ac
+            hu[i, g] = fin
+            if g:
+                self.h_ud.numpy()[i, :g] = dr
+        return int((max(s.length for s in slots) + g + 1) // ratio)
+
+    def _device_step(self, nmax: int) -> None:
+        """Everything between the metadata upload and the result download (graph-capturable)."""
+        e, S, g, R = self.e, self.S, self.g, self.R
+        cfg = e.cfg
+        V = cfg.vocab
+        st = e.status.t
+        mv = self.d_int[: self.n_meta_v].view(StepPlan.META_ROWS, S * R)
+        hid = self.hidden
+        for j in range(g):
+            o = self.n_meta_v + j * self.n_meta_d
+            md = self.d_int[o: o + self.n_meta_d].view(StepPlan.META_ROWS, S)
+            self.bd["meta"].copy_(md)
+            if j > 0:
+                self.bd["meta"][0].copy_(self.props[:, j - 1])
+            lg = e.draft_run(S, self.bd, hid, self.rows_d)
+            self.dlogits[:, j].copy_(lg)
+            hid = self.dhid
+            hid.copy_(self.bd["x"])
+            # sample proposal j from the modified draft law
+            stat = self.dstat[:, j].contiguous()
+            native.call("tf_rowstats", lg, V, V, S, self.temperature, self.top_p, stat, st)
+            self.dstat[:, j].copy_(stat)
+            self.u1[:, 0].copy_(self.d_ud[:, j])
+            self.u1[:, 1].copy_(self.d_ud[:, j])
+            native.call("tf_spec_verify", lg, None, stat, None, None, self.u1, S, 0, V, V, self.temperature,
+                        self.temperature, 0, self.R1, self.w1, self.pacc, self.ptok, st)
+            self.props[:, j].copy_(self.ptok)
+        # target verification of anchor + proposals
+        self.bv["meta"].copy_(mv)
+        if g > 0:
+            tok = self.bv["meta"][0].view(S, R)
+            tok[:, 1:].copy_(self.props[:, :g])
+        logits = e.run(S * R, self.bv, nmax, R if R <= 32 else 1, self.rows_all)
+        native.call("tf_rowstats", logits, V, V, S * R, self.temperature, self.top_p, self.tstat, st)
+        native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
+                    self.dstat if g > 0 else None, self.props if g > 0 else None, self.d_u, S, g, V, V,
+                    self.temperature, self.temperature, 0, self.Rm, self.wm, self.d_out[0], self.d_out[1], st)
+        # hidden state of the last committed row feeds the next round's draft
+        rows = self.row_of_anchor + self.d_out[0].long()
+        self.hidden.copy_(e.last_hidden[rows])
+        if g > 0:
+            self.d_out[2:].copy_(self.props[:, :g].t())
+
+    def step(self, slots: Sequence[DecodeSlot]) -> List[List[int]]:
+        """Advance every conversation by one verification round; returns the committed tokens."""
+        assert len(slots) == self.S
+        nmax = self._fill_host(slots)
+        bucket = -(-max(nmax, 1) // 4096) * 4096
+        self.d_int.copy_(self.h_int, non_blocking=True)
+        self.d_u.copy_(self.h_u, non_blocking=True)
+        self.d_ud.copy_(self.h_ud, non_blocking=True)
+        if self.use_graph:
+            if self.graph is None or bucket != self.nmax_bucket:
+                self.nmax_bucket = bucket
+                torch.cuda.synchronize()
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    self._device_step(bucket)          # warm-up outside capture
+                torch.cuda.current_stream().wait_stream(s)
+                torch.cuda.synchronize()
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph):
+                    self._device_step(bucket)
+            self.graph.replay()
+        else:
+            self._device_step(bucket)
+        self.h_out.copy_(self.d_out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.steps += 1
+        out = []
+        acc, nxt = self.h_out[0].tolist(), self.h_out[1].tolist()
+        props = self.h_out[2:].t().tolist() if self.g > 0 else None
+        for i, s in enumerate(slots):
+            toks = [s.anchor] + (props[i][: acc[i]] if props else [])
+            s.length += len(toks)
+            s.emitted += toks
+            s.anchor = nxt[i]
+            out.append(toks)
+        return out
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return self.h_int.numel() * 4 + self.h_u.numel() * 8 + self.h_ud.numel() * 8
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return self.h_out.numel() * 4
+
+    def count_launches(self, slots: Sequence[DecodeSlot]) -> int:
+        """Kernels of this package launched by one step, counted on an eager run of the step."""
+        self._fill_host(slots)
+        self.d_int.copy_(self.h_int)
+        self.d_u.copy_(self.h_u)
+        self.d_ud.copy_(self.h_ud)
+        n0 = native.LAUNCHES[0]
+        self._device_step(max(self.nmax_bucket, 4096))
+        torch.cuda.synchronize()
+        return native.LAUNCHES[0] - n0
