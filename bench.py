@@ -148,6 +148,8 @@ def main():
                         use_cuda_graphs=not args.no_graph)
     t0 = time.time()
     eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=0, max_chunk=chunk)
+    from titanic_flash_41_b200.ops import bigpath
+    bigpath.attach(eng)
     gen = torch.Generator(device=dev).manual_seed(1234)
     synth_state(eng, gen)
     torch.cuda.synchronize()
@@ -223,6 +225,7 @@ def main():
         value = tokens / (dev_ms / 1e3)
         e2e = tokens / (e2e_ms / 1e3)
         par = f"tp{world}+ep{world}" if world > 1 else "single"
+        mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
         out = {
             "metric": "decode tok/s at 131K ctx; cold 129.5K-token prefill s (max over ranks)",
             "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
@@ -243,7 +246,7 @@ def main():
                     "h2d_bytes_per_step": dec.h2d_bytes_per_step, "d2h_bytes_per_step": dec.d2h_bytes_per_step},
             "gpu_launches": launches * args.steps,
             "gpu_launches_per_step": launches,
-            "clocks": clocks, "init_s": round(init_s, 1), "impl": "own",
+            "clocks": clocks, "init_s": round(init_s, 1), "peak_mem_gb": round(mem_gb, 1), "impl": "own",
         }
         print(json.dumps(out))
     if world > 1:

@@ -133,9 +133,10 @@ def test_router_matches_oracle():
     assert torch.allclose(wts.cpu(), rw, atol=1e-5)
 
 
-def test_index_scores_and_topk():
+@pytest.mark.parametrize("Hi", [4, 8, 16, 32])
+def test_index_scores_and_topk(Hi):
     torch.manual_seed(5)
-    T, Hi, Di, C, k = 8, 4, 128, 700, 64
+    T, Di, C, k = 8, 128, 700, 64
     keys_f = torch.randn(2, C, Di)
     krow = Di // 2 + Di // 32
     enc = codecs.index_key_encode(keys_f)                          # [2, C, 68]

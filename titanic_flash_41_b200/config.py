@@ -252,7 +252,7 @@ def flash_b200_config(**over) -> ModelConfig:
     a few source layers, followers reuse them; the late group starts after the last source)."""
     kw = dict(name="flash-b200", n_layers=43, hidden=4096, vocab=129280, n_heads=64, head_dim=128,
               window=128, compress_ratio=4, kv_source_layers=(2, 8, 14, 20),
-              index_source_layers=(2, 8, 14, 20, 26, 32, 38), index_heads=16, index_dim=128,
+              index_source_layers=(2, 8, 14, 20, 26, 32, 38), index_heads=8, index_dim=128,
               index_topk=2048, candidate_blocks=2048, candidate_block=8, late_start=21,
               n_experts=256, topk=6, moe_inter=2048, n_shared=1, shared_inter=2048,
               scoring="sqrtsoftplus", router_bias=True, renorm=True, route_scale=1.5,

@@ -125,13 +125,15 @@ __device__ __forceinline__ uint32_t float_to_e2m1(float x) {
 // 8 packed e2m1 nibbles (element i in bits [4i,4i+4)) -> four f16x2 holding value * 2^-14
 // (the nibble's exponent/mantissa bits dropped into the f16 exponent field; subnormal exact).
 __device__ __forceinline__ void e2m1x8_to_h2x4_scaled(uint32_t w, uint32_t out[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t b = (w >> (8 * i)) & 0xffu;   // two nibbles: low = element 2i, high = element 2i+1
-    uint32_t lo = ((b & 0x7u) << 9) | ((b & 0x8u) << 12);
-    uint32_t hi = ((b & 0x70u) << 5) | ((b & 0x80u) << 8);
-    out[i] = lo | (hi << 16);
-  }
+  // one nibble per byte: t = elements 0,2,4,6 ; u = elements 1,3,5,7
+  const uint32_t t = w & 0x0f0f0f0fu, u = (w >> 4) & 0x0f0f0f0fu;
+  // high byte of the f16 image of a nibble n: sign -> bit 7, (n & 7) -> bits 1..3
+  const uint32_t ht = ((t << 4) & 0x80808080u) | ((t << 1) & 0x0e0e0e0eu);
+  const uint32_t hu = ((u << 4) & 0x80808080u) | ((u << 1) & 0x0e0e0e0eu);
+  out[0] = __byte_perm(ht, hu, 0x4000) & 0xff00ff00u;
+  out[1] = __byte_perm(ht, hu, 0x5111) & 0xff00ff00u;
+  out[2] = __byte_perm(ht, hu, 0x6222) & 0xff00ff00u;
+  out[3] = __byte_perm(ht, hu, 0x7333) & 0xff00ff00u;
 }
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }

@@ -71,19 +71,34 @@ __global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
     }
   }
   __syncthreads();
-  const int head_tiles = (p.Hi + 15) / 16;
-  for (int ri = warp; ri < nrows; ri += 4) {
-    const int r = row0 + ri;
-    const int nv = min(p.nvalid[r], p.key_hi);
-    float tot[kKeysPerCta / 8][2];
+  // One m16 MMA tile holds 16 (query row, head) pairs: with 16+ heads a row spans whole tiles,
+  // with fewer heads 16/Hi consecutive rows share one tile.
+  const int rpt = p.Hi >= 16 ? 1 : 16 / p.Hi;
+  const int head_tiles = p.Hi >= 16 ? (p.Hi + 15) / 16 : 1;
+  const int units = (nrows + rpt - 1) / rpt;
+  for (int u = warp; u < units; u += 4) {
+    float tot0[kKeysPerCta / 8][2], tot8[kKeysPerCta / 8][2];
 #pragma unroll
-    for (int nt = 0; nt < kKeysPerCta / 8; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
+    for (int nt = 0; nt < kKeysPerCta / 8; ++nt) tot0[nt][0] = tot0[nt][1] = tot8[nt][0] = tot8[nt][1] = 0.f;
+    int ra = 0, rb = 0;
     for (int ht = 0; ht < head_tiles; ++ht) {
-      const int h0 = ht * 16 + g, h8 = h0 + 8;
-      const bool v0 = h0 < p.Hi, v8 = h8 < p.Hi;
-      const __nv_bfloat16* q0 = p.q + ((long)r * p.Hi + min(h0, p.Hi - 1)) * DI;
-      const __nv_bfloat16* q8 = p.q + ((long)r * p.Hi + min(h8, p.Hi - 1)) * DI;
-      const float w0 = v0 ? p.w[(long)r * p.Hi + h0] : 0.f, w8 = v8 ? p.w[(long)r * p.Hi + h8] : 0.f;
+      int ha, hb;
+      if (p.Hi >= 16) {
+        ra = rb = u;
+        ha = ht * 16 + g;
+        hb = ha + 8;
+      } else {
+        ra = u * rpt + g / p.Hi;
+        ha = g % p.Hi;
+        rb = u * rpt + (g + 8) / p.Hi;
+        hb = (g + 8) % p.Hi;
+      }
+      const bool v0 = ra < nrows && ha < p.Hi, v8 = rb < nrows && hb < p.Hi;
+      const long pa = (long)(row0 + min(ra, nrows - 1)) * p.Hi + min(ha, p.Hi - 1);
+      const long pb = (long)(row0 + min(rb, nrows - 1)) * p.Hi + min(hb, p.Hi - 1);
+      const __nv_bfloat16* q0 = p.q + pa * DI;
+      const __nv_bfloat16* q8 = p.q + pb * DI;
+      const float w0 = v0 ? p.w[pa] : 0.f, w8 = v8 ? p.w[pb] : 0.f;
       uint32_t qf[DI / 16][4];
 #pragma unroll
       for (int ks = 0; ks < DI / 16; ++ks) {
@@ -92,44 +107,63 @@ __global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
         float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k));
         float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k + 8));
         float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k + 8));
-        __half2 ha = __floats2half2_rn(a.x, a.y), hb = __floats2half2_rn(b.x, b.y);
-        __half2 hc = __floats2half2_rn(c.x, c.y), hd = __floats2half2_rn(d.x, d.y);
-        qf[ks][0] = *reinterpret_cast<uint32_t*>(&ha);
-        qf[ks][1] = *reinterpret_cast<uint32_t*>(&hb);
-        qf[ks][2] = *reinterpret_cast<uint32_t*>(&hc);
-        qf[ks][3] = *reinterpret_cast<uint32_t*>(&hd);
+        __half2 ha2 = __floats2half2_rn(a.x, a.y), hb2 = __floats2half2_rn(b.x, b.y);
+        __half2 hc2 = __floats2half2_rn(c.x, c.y), hd2 = __floats2half2_rn(d.x, d.y);
+        qf[ks][0] = *reinterpret_cast<uint32_t*>(&ha2);
+        qf[ks][1] = *reinterpret_cast<uint32_t*>(&hb2);
+        qf[ks][2] = *reinterpret_cast<uint32_t*>(&hc2);
+        qf[ks][3] = *reinterpret_cast<uint32_t*>(&hd2);
       }
 #pragma unroll
       for (int nt = 0; nt < kKeysPerCta / 8; ++nt) {
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
         const __half* kr = Ks + (nt * 8 + g) * KS + 2 * t;
 #pragma unroll
         for (int ks = 0; ks < DI / 16; ++ks) {
           uint32_t b[2];
           b[0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
           b[1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
-          mma_f16_16816(s, qf[ks], b);
+          mma_f16_16816(sacc, qf[ks], b);
         }
-        tot[nt][0] += fmaxf(s[0], 0.f) * w0 + fmaxf(s[2], 0.f) * w8;
-        tot[nt][1] += fmaxf(s[1], 0.f) * w0 + fmaxf(s[3], 0.f) * w8;
+        tot0[nt][0] += fmaxf(sacc[0], 0.f) * w0;
+        tot0[nt][1] += fmaxf(sacc[1], 0.f) * w0;
+        tot8[nt][0] += fmaxf(sacc[2], 0.f) * w8;
+        tot8[nt][1] += fmaxf(sacc[3], 0.f) * w8;
       }
     }
-    // sum over the 8 head rows held by lanes with equal t
+    // sum over the heads of one query row: lanes that differ in the low log2(min(Hi,8)) bits of g
+    const int span = p.Hi >= 16 ? 8 : p.Hi;            // fragment rows of one query row within g
+    const bool writer = (g % span) == 0;
 #pragma unroll
     for (int nt = 0; nt < kKeysPerCta / 8; ++nt) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        float v = tot[nt][i];
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        tot[nt][i] = v;
+        float a = tot0[nt][i], b = tot8[nt][i];
+        if (p.Hi >= 16) {
+          a += b;
+          b = 0.f;
+        }
+        for (int m = 4; m < 4 * span; m <<= 1) {
+          a += __shfl_xor_sync(0xffffffffu, a, m);
+          b += __shfl_xor_sync(0xffffffffu, b, m);
+        }
+        tot0[nt][i] = a;
+        tot8[nt][i] = b;
       }
-      if (g == 0) {
+      if (writer) {
         const int k = key0 + nt * 8 + 2 * t;
-        float* out = p.scores + (long)r * p.lds;
-        if (k < p.lds && k < p.key_hi) out[k] = k < nv ? tot[nt][0] : -INFINITY;
-        if (k + 1 < p.lds && k + 1 < p.key_hi) out[k + 1] = k + 1 < nv ? tot[nt][1] : -INFINITY;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (half == 1 && p.Hi >= 16) break;
+          const int ri = half == 0 ? ra : rb;
+          if (ri >= nrows) continue;
+          const int r = row0 + ri;
+          const int nv = min(p.nvalid[r], p.key_hi);
+          const float* tv = half == 0 ? tot0[nt] : tot8[nt];
+          float* out = p.scores + (long)r * p.lds;
+          if (k < p.lds && k < p.key_hi) out[k] = k < nv ? tv[0] : -INFINITY;
+          if (k + 1 < p.lds && k + 1 < p.key_hi) out[k + 1] = k + 1 < nv ? tv[1] : -INFINITY;
+        }
       }
     }
   }

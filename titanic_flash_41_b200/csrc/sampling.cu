@@ -92,7 +92,6 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int ldl, int V, 
 __global__ void __launch_bounds__(1024) rowstat_kernel(const float* __restrict__ logits, int ldl, int V,
                                                        float temp, float top_p, RowStat* __restrict__ out,
                                                        TfStatusWord* st) {
-  __shared__ double scratch[32];
   __shared__ float fscr[32];
   const int r = blockIdx.x;
   const float* x = logits + (long)r * ldl;
@@ -113,30 +112,76 @@ __global__ void __launch_bounds__(1024) rowstat_kernel(const float* __restrict__
     }
     return;
   }
+  // Masses are accumulated as 2^-40 fixed point so that the (unordered) shared-memory atomics give
+  // the same sums on every run and on every rank that samples the same row.
+  __shared__ unsigned long long hist[4096];
+  __shared__ unsigned long long chunk[32];
+  __shared__ unsigned long long s_above, s_total, s_inbin;
+  __shared__ uint32_t s_prefix;
   const float inv_t = 1.f / temp;
-  double z = 0.0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) z += (double)expf((x[i] - m) * inv_t);
-  z = block_sum_d(z, scratch);
-  uint32_t thr = 0;
-  if (top_p < 1.f) {
-    const double target = (double)top_p * z;
-    // largest key t with mass(key >= t) >= target, bit by bit
-    for (int bit = 31; bit >= 0; --bit) {
-      const uint32_t cand = thr | (1u << bit);
-      double mass = 0.0;
-      for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        float v = x[i];
-        if (fkey(v) >= cand) mass += (double)expf((v - m) * inv_t);
-      }
-      mass = block_sum_d(mass, scratch);
-      if (mass >= target) thr = cand;
-    }
-    double zn = 0.0;
+  const double kFix = 1099511627776.0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t prefix = 0, mask = 0;
+  unsigned long long target = 0;
+  if (threadIdx.x == 0) s_above = 0;
+  // radix levels over the order-preserving key: 12 + 12 + 8 bits
+  for (int level = 0; level < 3; ++level) {
+    const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
+    const int nb = level == 2 ? 256 : 4096;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      float v = x[i];
-      if (fkey(v) >= thr) zn += (double)expf((v - m) * inv_t);
+      const float v = x[i];
+      const uint32_t key = fkey(v);
+      if ((key & mask) == prefix)
+        atomicAdd(&hist[(key >> shift) & (nb - 1)], (unsigned long long)((double)expf((v - m) * inv_t) * kFix));
     }
-    z = block_sum_d(zn, scratch);
+    __syncthreads();
+    // per-warp sums of nb/32 consecutive bins
+    {
+      const int per = nb / 32;
+      unsigned long long sacc = 0;
+      for (int j = lane; j < per; j += 32) sacc += hist[warp * per + j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+      if (lane == 0) chunk[warp] = sacc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (level == 0) {
+        unsigned long long tot = 0;
+        for (int w = 0; w < 32; ++w) tot += chunk[w];
+        s_total = tot;
+        target = top_p < 1.f ? (unsigned long long)((double)top_p * (double)tot) : 0ull;
+        if (target == 0) target = 1;
+      }
+      // first bin from the top whose inclusive cumulative mass reaches the target
+      const int per = nb / 32;
+      unsigned long long cum = s_above;
+      int w = 31;
+      for (; w > 0; --w) {
+        if (cum + chunk[w] >= target) break;
+        cum += chunk[w];
+      }
+      int b = w * per + per - 1;
+      for (; b > w * per; --b) {
+        if (cum + hist[b] >= target) break;
+        cum += hist[b];
+      }
+      s_above = cum;
+      s_inbin = hist[b];
+      s_prefix = prefix | ((uint32_t)b << shift);
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    mask |= (uint32_t)(nb - 1) << shift;
+    if (top_p >= 1.f) break;
+  }
+  uint32_t thr = 0;
+  double z = (double)s_total / kFix;
+  if (top_p < 1.f) {
+    thr = prefix;
+    z = (double)(s_above + s_inbin) / kFix;
   }
   if (threadIdx.x == 0) {
     out[r].m = m;

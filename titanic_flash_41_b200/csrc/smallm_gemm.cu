@@ -1,16 +1,19 @@
 // Weight-streaming GEMM for small row counts (decode / verification: M <= 32 rows per group).
 //
-//   Y[r, n] = sum_k X[r, k] * W[n, k]          W: FP8 e4m3 with 128x128 fp32 block scales, or
-//                                                 MXFP4 (packed e2m1 + one UE8M0 per 32 along K)
+//   Y[r, n] = sum_k X[r, k] * W[n, k]     W: FP8 e4m3 with 128x128 fp32 block scales (kind 0),
+//                                            MXFP4 = packed e2m1 + one UE8M0 per 32 along K (kind 1),
+//                                            or bf16 (kind 2, bf16 activations)
 //
 // At these row counts the op is bound by reading W once from HBM, so the kernel is organised
 // around the weight stream: every lane issues 16-byte loads of consecutive K of one weight row,
 // converts in registers (cvt e4m3x2->f16x2; e2m1 through an exponent-field trick) and feeds
-// m16n8k16 tensor-core tiles in which the 16 weight rows are the MMA's M and the (few)
-// activation rows its N.  The K index of an MMA slot is a permutation chosen so that the
-// 16-byte weight load IS the A fragment; the activation fragment follows the same permutation.
-// K is split over the warps of a CTA and reduced through shared memory in a fixed order, so
-// results are run-to-run deterministic.
+// m16n8k16 tensor-core tiles in which 16 weight rows are the MMA's M and the (few) activation
+// rows its N.  The K index of an MMA slot is a permutation chosen so that the 16-byte weight load
+// IS the A fragment; the activation fragment follows the same permutation.  Per K step a warp
+// first issues the loads of ALL its weight tiles (two 16-row tiles, times two matrices in the
+// dual form: 8 x 16 B per lane in flight), then the activation fragments once, then the MMAs,
+// which keeps enough bytes in flight to follow HBM.  K is split over the warps of a CTA and
+// reduced through shared memory in a fixed order: results are run-to-run deterministic.
 //
 // Grouped form (routed experts): blockIdx.y walks a compacted list of active experts; rows of a
 // group are gathered through `sorted_pairs`.  `dual` computes W1 and W3 tiles together and
@@ -22,7 +25,7 @@
 
 namespace {
 
-constexpr int kWarps = 8;
+constexpr int kWarps = 4;   // K is split four ways inside a CTA; four CTAs fit on an SM
 constexpr int kTileN = 32;   // output columns per CTA (two m16 tiles per warp)
 
 struct SmallMParams {
@@ -34,7 +37,7 @@ struct SmallMParams {
   long s_group_stride;       // elements of S
   int ldw;                   // bytes per weight row
   int lds;                   // scale row stride (elements)
-  const __half* X;           // activations f16
+  const __half* X;           // activations f16 (bf16 for kind 2)
   int ldx;                   // elements
   void* Y;                   // output
   int ldy;                   // elements
@@ -60,115 +63,162 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <int KIND>  // 0 = fp8 block128, 1 = mxfp4, 2 = bf16 weights with bf16 activations
-struct Loader;
-
-// ---- FP8: one step = 64 k -----------------------------------------------------------------
-template <>
-struct Loader<0> {
-  static constexpr int kStep = 64;
-  static __device__ __forceinline__ void load(const uint8_t* row0, const uint8_t* row8, int k, int t,
-                                              uint4& w0, uint4& w8) {
-    w0 = __ldg(reinterpret_cast<const uint4*>(row0 + k + t * 16));
-    w8 = __ldg(reinterpret_cast<const uint4*>(row8 + k + t * 16));
-  }
-};
-template <>
-struct Loader<1> {
-  static constexpr int kStep = 128;
-  static __device__ __forceinline__ void load(const uint8_t* row0, const uint8_t* row8, int k, int t,
-                                              uint4& w0, uint4& w8) {
-    w0 = __ldg(reinterpret_cast<const uint4*>(row0 + (k >> 1) + t * 16));
-    w8 = __ldg(reinterpret_cast<const uint4*>(row8 + (k >> 1) + t * 16));
-  }
-};
-
 __device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// Accumulate one 16-row weight tile over k in [k0, k1) against MT activation tiles.
-template <int KIND, int MT>
-__device__ __forceinline__ void stream_tile(const SmallMParams& p, const uint8_t* Wg, const void* Sg,
-                                            int n0, int k0, int k1, const __half* const xrow[MT],
-                                            float acc[MT][4]) {
-  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const uint8_t* row0 = Wg + (long)(n0 + g) * p.ldw;
-  const uint8_t* row8 = Wg + (long)(n0 + g + 8) * p.ldw;
+// streaming (evict-first) 16-byte load: weights are read exactly once per launch
+__device__ __forceinline__ uint4 ld_stream(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// One group (dense matrix or one expert): NT = 2 (or 4 in the dual form) weight tiles of 16 rows.
+template <int KIND, int MT, bool DUAL>
+__device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* Wg, const uint8_t* W3g,
+                                         const void* Sg, const void* S3g, int rows, const int* pairs,
+                                         int row_base, float (*red)[32][4]) {
+  constexpr int NM = DUAL ? 2 : 1;
+  constexpr int NT = 2 * NM;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * kTileN;
+  const int k0 = warp * p.k_per_warp, k1 = min(p.K, k0 + p.k_per_warp);
+
+  const __half* xrow[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    const int r = min(row_base + m * 8 + g, rows - 1);
+    const int xr = pairs ? pairs[r] / p.x_div : r;
+    xrow[m] = p.X + (long)xr * p.ldx;
+  }
+  // tile ti -> matrix (ti >> 1), 16-row half (ti & 1)
+  const uint8_t* wrow0[NT];
+  const uint8_t* wrow8[NT];
+#pragma unroll
+  for (int ti = 0; ti < NT; ++ti) {
+    const uint8_t* base = (ti >> 1) ? W3g : Wg;
+    wrow0[ti] = base + (long)(n0 + 16 * (ti & 1) + g) * p.ldw;
+    wrow8[ti] = wrow0[ti] + 8L * p.ldw;
+  }
+  float acc[NT][MT][4];
+#pragma unroll
+  for (int ti = 0; ti < NT; ++ti)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[ti][m][0] = acc[ti][m][1] = acc[ti][m][2] = acc[ti][m][3] = 0.f;
+
   if (KIND == 0) {
+    // ---------------- FP8, fp32 scale per 128x128 block: accumulate a block, then promote
     const float* S = reinterpret_cast<const float*>(Sg) + (long)(n0 >> 7) * p.lds;
+    const float* S3 = DUAL ? reinterpret_cast<const float*>(S3g) + (long)(n0 >> 7) * p.lds : nullptr;
     for (int kb = k0; kb < k1; kb += 128) {
-      float blk[MT][4];
+      float blk[NT][MT][4];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) blk[m][0] = blk[m][1] = blk[m][2] = blk[m][3] = 0.f;
-      uint4 w0[2], w8[2];
+      for (int ti = 0; ti < NT; ++ti)
 #pragma unroll
-      for (int s = 0; s < 2; ++s) Loader<0>::load(row0, row8, kb + s * 64, t, w0[s], w8[s]);
+        for (int m = 0; m < MT; ++m) blk[ti][m][0] = blk[ti][m][1] = blk[ti][m][2] = blk[ti][m][3] = 0.f;
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
-        const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[s]);
-        const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[s]);
+        const int k = kb + s * 64 + t * 16;
+        uint4 w0[NT], w8[NT];
+#pragma unroll
+        for (int ti = 0; ti < NT; ++ti) {
+          w0[ti] = ld_stream(wrow0[ti] + k);
+          w8[ti] = ld_stream(wrow8[ti] + k);
+        }
         uint4 xv[MT][2];
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-          const uint4* xp = reinterpret_cast<const uint4*>(xrow[m] + kb + s * 64 + t * 16);
+          const uint4* xp = reinterpret_cast<const uint4*>(xrow[m] + k);
           xv[m][0] = xp[0];
           xv[m][1] = xp[1];
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t a[4];
-          a[0] = e4m3x2_to_h2((uint16_t)(a0w[j] & 0xffffu));
-          a[1] = e4m3x2_to_h2((uint16_t)(a8w[j] & 0xffffu));
-          a[2] = e4m3x2_to_h2((uint16_t)(a0w[j] >> 16));
-          a[3] = e4m3x2_to_h2((uint16_t)(a8w[j] >> 16));
+        for (int ti = 0; ti < NT; ++ti) {
+          const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[ti]);
+          const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[ti]);
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[m][0]);
-            uint32_t b[2] = {xw[2 * j], xw[2 * j + 1]};
-            mma_f16_16816(blk[m], a, b);
+          for (int j = 0; j < 4; ++j) {
+            uint32_t a[4];
+            a[0] = e4m3x2_to_h2((uint16_t)(a0w[j] & 0xffffu));
+            a[1] = e4m3x2_to_h2((uint16_t)(a8w[j] & 0xffffu));
+            a[2] = e4m3x2_to_h2((uint16_t)(a0w[j] >> 16));
+            a[3] = e4m3x2_to_h2((uint16_t)(a8w[j] >> 16));
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[m][0]);
+              uint32_t b[2] = {xw[2 * j], xw[2 * j + 1]};
+              mma_f16_16816(blk[ti][m], a, b);
+            }
           }
         }
       }
       const float sc = __ldg(S + (kb >> 7));
+      const float sc3 = DUAL ? __ldg(S3 + (kb >> 7)) : 0.f;
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
+      for (int ti = 0; ti < NT; ++ti)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[m][i] = fmaf(sc, blk[m][i], acc[m][i]);
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[ti][m][i] = fmaf((ti >> 1) ? sc3 : sc, blk[ti][m][i], acc[ti][m][i]);
     }
   } else if (KIND == 2) {
-    // bf16: a 16-byte load holds 8 consecutive k of one row; one step = 32 k = two MMAs
-    for (int kb = k0; kb < k1; kb += 32) {
-      const uint4 w0 = __ldg(reinterpret_cast<const uint4*>(row0 + 2 * (kb + t * 8)));
-      const uint4 w8 = __ldg(reinterpret_cast<const uint4*>(row8 + 2 * (kb + t * 8)));
-      const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0);
-      const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8);
+    // ---------------- bf16 weights: a 16-byte load holds 8 consecutive k; 64 k per step
+    for (int kb = k0; kb < k1; kb += 64) {
+      uint4 w0[NT][2], w8[NT][2];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(xrow[m] + kb + t * 8);
-        const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv);
+      for (int ti = 0; ti < NT; ++ti)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          uint32_t a[4] = {a0w[2 * j], a8w[2 * j], a0w[2 * j + 1], a8w[2 * j + 1]};
-          uint32_t b[2] = {xw[2 * j], xw[2 * j + 1]};
-          mma_bf16_16816(acc[m], a, b);
+        for (int s = 0; s < 2; ++s) {
+          w0[ti][s] = ld_stream(wrow0[ti] + 2 * (kb + s * 32 + t * 8));
+          w8[ti][s] = ld_stream(wrow8[ti] + 2 * (kb + s * 32 + t * 8));
+        }
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        uint4 xv[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) xv[m] = *reinterpret_cast<const uint4*>(xrow[m] + kb + s * 32 + t * 8);
+#pragma unroll
+        for (int ti = 0; ti < NT; ++ti) {
+          const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[ti][s]);
+          const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[ti][s]);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            uint32_t a[4] = {a0w[2 * j], a8w[2 * j], a0w[2 * j + 1], a8w[2 * j + 1]};
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[m]);
+              uint32_t b[2] = {xw[2 * j], xw[2 * j + 1]};
+              mma_bf16_16816(acc[ti][m], a, b);
+            }
+          }
         }
       }
     }
   } else {
-    const uint8_t* S0 = reinterpret_cast<const uint8_t*>(Sg) + (long)(n0 + g) * p.lds;
-    const uint8_t* S8 = reinterpret_cast<const uint8_t*>(Sg) + (long)(n0 + g + 8) * p.lds;
+    // ---------------- MXFP4: 32 nibbles per 16-byte load = one scale group of one row; 128 k per step
+    const uint8_t* srow0[NT];
+    const uint8_t* srow8[NT];
+#pragma unroll
+    for (int ti = 0; ti < NT; ++ti) {
+      const uint8_t* sb = reinterpret_cast<const uint8_t*>((ti >> 1) ? S3g : Sg);
+      srow0[ti] = sb + (long)(n0 + 16 * (ti & 1) + g) * p.lds;
+      srow8[ti] = srow0[ti] + 8L * p.lds;
+    }
     for (int kb = k0; kb < k1; kb += 128) {
-      uint4 w0, w8;
-      Loader<1>::load(row0, row8, kb, t, w0, w8);
-      // factor = 2^14 * 2^(s-127) as f16x2 (exact for s in [99,142]; the loader checks the range)
-      const int sb = (kb >> 5) + t;
-      float f0 = ue8m0_to_float(__ldg(S0 + sb)) * 16384.f, f8 = ue8m0_to_float(__ldg(S8 + sb)) * 16384.f;
-      __half2 h0 = __float2half2_rn(f0), h8 = __float2half2_rn(f8);
-      const uint32_t s0 = *reinterpret_cast<uint32_t*>(&h0), s8 = *reinterpret_cast<uint32_t*>(&h8);
-      const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0);
-      const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8);
+      uint4 w0[NT], w8[NT];
+      uint8_t c0[NT], c8[NT];
+      const int sbi = (kb >> 5) + t;
+#pragma unroll
+      for (int ti = 0; ti < NT; ++ti) {
+        w0[ti] = ld_stream(wrow0[ti] + (kb >> 1) + t * 16);
+        w8[ti] = ld_stream(wrow8[ti] + (kb >> 1) + t * 16);
+        c0[ti] = __ldg(srow0[ti] + sbi);
+        c8[ti] = __ldg(srow8[ti] + sbi);
+      }
       uint4 xv[MT][4];
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
@@ -177,37 +227,86 @@ __device__ __forceinline__ void stream_tile(const SmallMParams& p, const uint8_t
         for (int q = 0; q < 4; ++q) xv[m][q] = xp[q];
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t h0x[4], h8x[4];
-        e2m1x8_to_h2x4_scaled(a0w[i], h0x);
-        e2m1x8_to_h2x4_scaled(a8w[i], h8x);
+      for (int ti = 0; ti < NT; ++ti) {
+        // factor = 2^14 * 2^(s-127) as f16x2 (exact for s in [99,142]; the loader checks the range)
+        __half2 h0 = __float2half2_rn(ue8m0_to_float(c0[ti]) * 16384.f);
+        __half2 h8 = __float2half2_rn(ue8m0_to_float(c8[ti]) * 16384.f);
+        const uint32_t s0 = *reinterpret_cast<uint32_t*>(&h0), s8 = *reinterpret_cast<uint32_t*>(&h8);
+        const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[ti]);
+        const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[ti]);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          h0x[q] = h2_mul(h0x[q], s0);
-          h8x[q] = h2_mul(h8x[q], s8);
-        }
+        for (int i = 0; i < 4; ++i) {
+          uint32_t h0x[4], h8x[4];
+          e2m1x8_to_h2x4_scaled(a0w[i], h0x);
+          e2m1x8_to_h2x4_scaled(a8w[i], h8x);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int j = 2 * i + half;
-          uint32_t a[4] = {h0x[2 * half], h8x[2 * half], h0x[2 * half + 1], h8x[2 * half + 1]};
+          for (int q = 0; q < 4; ++q) {
+            h0x[q] = h2_mul(h0x[q], s0);
+            h8x[q] = h2_mul(h8x[q], s8);
+          }
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[m][0]);
-            uint32_t b[2] = {xw[2 * j], xw[2 * j + 1]};
-            mma_f16_16816(acc[m], a, b);
+          for (int half = 0; half < 2; ++half) {
+            const int j = 2 * i + half;
+            uint32_t a[4] = {h0x[2 * half], h8x[2 * half], h0x[2 * half + 1], h8x[2 * half + 1]};
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv[m][0]);
+              uint32_t b[2] = {xw[2 * j], xw[2 * j + 1]};
+              mma_f16_16816(acc[ti][m], a, b);
+            }
           }
         }
       }
     }
   }
+
+  // ---- fixed-order reduction over the K-splitting warps, then the epilogue
+  // red is [kWarps * NT * MT][32][4]
+  __syncthreads();
+#pragma unroll
+  for (int ti = 0; ti < NT; ++ti)
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[(warp * NT + ti) * MT + m][lane][i] = acc[ti][m][i];
+  __syncthreads();
+  constexpr int kSlots = 2 * MT * 32 * 4;
+  for (int s = threadIdx.x; s < kSlots; s += kWarps * 32) {
+    const int i = s & 3, ln = (s >> 2) & 31, m = (s >> 7) % MT, h = (s >> 7) / MT;
+    float v = 0.f, v3 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      v += red[(w * NT + h) * MT + m][ln][i];
+      if (DUAL) v3 += red[(w * NT + 2 + h) * MT + m][ln][i];
+    }
+    // C fragment: weight row = g (+8 for i >= 2); activation row = 2t + (i & 1)
+    const int gg = ln >> 2, tt = ln & 3;
+    const int n = n0 + 16 * h + gg + ((i & 2) ? 8 : 0);
+    const int r = row_base + m * 8 + 2 * tt + (i & 1);
+    if (r < rows && n < p.N) {
+      float o = v;
+      if (DUAL) {
+        float gate = v, up = v3;
+        if (p.swiglu_limit > 0.f) {
+          gate = fminf(gate, p.swiglu_limit);
+          up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit);
+        }
+        o = gate / (1.f + __expf(-gate)) * up;
+      }
+      const long orow = pairs ? pairs[r] : r;
+      const long off = orow * p.ldy + n;
+      if (p.out_kind == 0) reinterpret_cast<float*>(p.Y)[off] = o;
+      else if (p.out_kind == 1) reinterpret_cast<__half*>(p.Y)[off] = __float2half(o);
+      else reinterpret_cast<__nv_bfloat16*>(p.Y)[off] = __float2bfloat16(o);
+    }
+  }
+  __syncthreads();
 }
 
-template <int KIND, int MT, bool DUAL>
+template <int KIND, bool DUAL>
 __global__ void __launch_bounds__(kWarps * 32) smallm_gemm_kernel(SmallMParams p) {
-  constexpr int NM = DUAL ? 2 : 1;
-  __shared__ float red[kWarps][NM][2][MT][32][4];   // [warp][matrix][m16 tile][n8 tile][lane][4]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  int rows, row_base = 0;
+  __shared__ float red[kWarps * (DUAL ? 4 : 2) * 2][32][4];
+  int rows;
   const uint8_t *Wg = p.W, *W3g = p.W3;
   const void *Sg = p.S, *S3g = p.S3;
   const int* pairs = nullptr;
@@ -227,97 +326,39 @@ __global__ void __launch_bounds__(kWarps * 32) smallm_gemm_kernel(SmallMParams p
   } else {
     rows = p.M;
   }
-  const int n0 = blockIdx.x * kTileN;
-  const int k0 = warp * p.k_per_warp, k1 = min(p.K, k0 + p.k_per_warp);
-
-  for (; row_base < rows; row_base += 8 * MT) {
-    const __half* xrow[MT];
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      int r = min(row_base + m * 8 + g, rows - 1);
-      int xr = pairs ? pairs[r] / p.x_div : r;
-      xrow[m] = p.X + (long)xr * p.ldx;
+  // 8 activation rows per MMA tile: one tile when the group has at most 8 rows, else 16 at a time
+  int row_base = 0;
+  while (row_base < rows) {
+    if (rows - row_base <= 8) {
+      run_rows<KIND, 1, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red);
+      row_base += 8;
+    } else {
+      run_rows<KIND, 2, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red);
+      row_base += 16;
     }
-    float acc[NM][2][MT][4];
-#pragma unroll
-    for (int a = 0; a < NM; ++a)
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[a][h][m][0] = acc[a][h][m][1] = acc[a][h][m][2] = acc[a][h][m][3] = 0.f;
-    if (k0 < k1) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        stream_tile<KIND, MT>(p, Wg, Sg, n0 + 16 * h, k0, k1, xrow, acc[0][h]);
-        if (DUAL) stream_tile<KIND, MT>(p, W3g, S3g, n0 + 16 * h, k0, k1, xrow, acc[NM - 1][h]);
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int a = 0; a < NM; ++a)
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int m = 0; m < MT; ++m)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) red[warp][a][h][m][lane][i] = acc[a][h][m][i];
-    __syncthreads();
-    // fixed-order reduction over warps; thread -> (h, m, lane, i) slots
-    constexpr int kSlots = 2 * MT * 32 * 4;
-    for (int s = threadIdx.x; s < kSlots; s += kWarps * 32) {
-      const int i = s & 3, ln = (s >> 2) & 31, m = (s >> 7) % MT, h = (s >> 7) / MT;
-      float v = 0.f, v3 = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        v += red[w][0][h][m][ln][i];
-        if (DUAL) v3 += red[w][NM - 1][h][m][ln][i];
-      }
-      // C fragment: rows (weight row) = g or g+8 for i>=2 ; cols (activation row) = 2t + (i&1)
-      const int gg = ln >> 2, tt = ln & 3;
-      const int n = n0 + 16 * h + gg + ((i & 2) ? 8 : 0);
-      const int r = row_base + m * 8 + 2 * tt + (i & 1);
-      if (r < rows && n < p.N) {
-        float o = v;
-        if (DUAL) {
-          float gate = v, up = v3;
-          if (p.swiglu_limit > 0.f) {
-            gate = fminf(gate, p.swiglu_limit);
-            up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit);
-          }
-          o = gate / (1.f + __expf(-gate)) * up;
-        }
-        const long orow = pairs ? pairs[r] : r;
-        const long off = orow * p.ldy + n;
-        if (p.out_kind == 0) reinterpret_cast<float*>(p.Y)[off] = o;
-        else if (p.out_kind == 1) reinterpret_cast<__half*>(p.Y)[off] = __float2half(o);
-        else reinterpret_cast<__nv_bfloat16*>(p.Y)[off] = __float2bfloat16(o);
-      }
-    }
-    __syncthreads();
   }
 }
 
 template <int KIND, bool DUAL>
-cudaError_t launch(const SmallMParams& p, int max_rows, int slots, cudaStream_t st) {
+cudaError_t launch(const SmallMParams& p, int slots, cudaStream_t st) {
   dim3 grid((p.N + kTileN - 1) / kTileN, slots > 0 ? slots : 1);
-  dim3 block(kWarps * 32);
-  if (max_rows <= 8) smallm_gemm_kernel<KIND, 1, DUAL><<<grid, block, 0, st>>>(p);
-  else smallm_gemm_kernel<KIND, 2, DUAL><<<grid, block, 0, st>>>(p);
+  smallm_gemm_kernel<KIND, DUAL><<<grid, kWarps * 32, 0, st>>>(p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
-// kind: 0 = FP8 block-128, 1 = MXFP4, 2 = bf16 weights (X is then bf16, not f16).  Returns a cudaError_t (0 = ok) or -1 for a bad argument.
+// kind: 0 = FP8 block-128, 1 = MXFP4, 2 = bf16 weights (X is then bf16, not f16).
+// Returns a cudaError_t (0 = ok) or -1 for a bad argument.  `max_rows` is accepted for ABI
+// stability; the kernel sizes its row tiles from the actual group sizes.
 TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S, const void* S3,
                           long w_group_stride, long s_group_stride, int ldw, int lds, const void* X,
                           int ldx, void* Y, int ldy, int out_kind, int N, int K, int M,
                           const int* group_expert, const int* group_start, const int* group_count,
                           const int* n_groups, const int* sorted_pairs, int x_div, int slots,
                           int max_rows, float swiglu_limit, cudaStream_t stream) {
-  if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0) return -1;
-  if (kind == 0 && (ldw % 16) != 0) return -1;
-  if (kind == 1 && (ldw % 16) != 0) return -1;
+  (void)max_rows;
+  if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0 || (ldw % 16) != 0) return -1;
   SmallMParams p;
   p.W = (const uint8_t*)W; p.W3 = (const uint8_t*)W3; p.S = S; p.S3 = S3;
   p.w_group_stride = w_group_stride; p.s_group_stride = s_group_stride;
@@ -326,13 +367,12 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   p.group_expert = group_expert; p.group_start = group_start; p.group_count = group_count;
   p.n_groups = n_groups; p.sorted_pairs = sorted_pairs; p.x_div = x_div > 0 ? x_div : 1;
   p.swiglu_limit = swiglu_limit;
-  int kpw = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
-  p.k_per_warp = kpw;
+  p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
   const bool dual = W3 != nullptr;
   cudaError_t e;
-  if (kind == 0) e = dual ? launch<0, true>(p, max_rows, slots, stream) : launch<0, false>(p, max_rows, slots, stream);
-  else if (kind == 1) e = dual ? launch<1, true>(p, max_rows, slots, stream) : launch<1, false>(p, max_rows, slots, stream);
-  else if (kind == 2) e = launch<2, false>(p, max_rows, slots, stream);
+  if (kind == 0) e = dual ? launch<0, true>(p, slots, stream) : launch<0, false>(p, slots, stream);
+  else if (kind == 1) e = dual ? launch<1, true>(p, slots, stream) : launch<1, false>(p, slots, stream);
+  else if (kind == 2) e = launch<2, false>(p, slots, stream);
   else return -1;
   return (int)e;
 }
