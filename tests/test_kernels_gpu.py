@@ -225,7 +225,9 @@ def test_sampling_kernels():
     stat = torch.zeros(rows, sb, dtype=torch.uint8, device=DEV)
     st = native.StatusWord(DEV)
     T, top_p = 0.6, 0.95
-    native.call("tf_rowstats", lg, V, V, rows, T, top_p, stat, st.t)
+    scr = torch.zeros(native.lib().tf_rowstats_scratch_bytes(rows), dtype=torch.uint8, device=DEV)
+    native.call("tf_rowstats", lg, V, V, rows, T, top_p, stat, scr, st.t)
+    assert int(scr.sum()) == 0          # every call leaves its scratch zeroed
     st.check()
     raw = stat.cpu().numpy().view(np.dtype([("m", "<f4"), ("thr", "<u4"), ("z", "<f8")]))
     pr = torch.softmax(lg.double().cpu() / T, -1)
@@ -241,7 +243,7 @@ def test_sampling_kernels():
     lg1 = lg[:1].expand(S, V).contiguous()
     stat1 = stat[:1].expand(S, sb).contiguous()
     u = torch.rand(S, 2, dtype=torch.float64, device=DEV)
-    R = torch.zeros(S, 1, dtype=torch.float64, device=DEV)
+    R = torch.zeros(native.lib().tf_spec_verify_scratch_doubles(S, 0, V), dtype=torch.float64, device=DEV)
     w = torch.zeros(S, 1, dtype=torch.float64, device=DEV)
     nacc = torch.zeros(S, dtype=torch.int32, device=DEV)
     tok = torch.zeros(S, dtype=torch.int32, device=DEV)
@@ -270,14 +272,15 @@ def test_block_verification_preserves_target_law():
     st = native.StatusWord(DEV)
     tstat = torch.zeros(g + 1, sb, dtype=torch.uint8, device=DEV)
     dstat = torch.zeros(g, sb, dtype=torch.uint8, device=DEV)
-    native.call("tf_rowstats", tl, V, V, g + 1, T, 1.0, tstat, st.t)
-    native.call("tf_rowstats", dl, V, V, g, T, 1.0, dstat, st.t)
+    scr = torch.zeros(native.lib().tf_rowstats_scratch_bytes(g + 1), dtype=torch.uint8, device=DEV)
+    native.call("tf_rowstats", tl, V, V, g + 1, T, 1.0, tstat, scr, st.t)
+    native.call("tf_rowstats", dl, V, V, g, T, 1.0, dstat, scr, st.t)
     q = torch.softmax(dl.double(), -1)
     props = torch.stack([torch.multinomial(q[i], S, replacement=True) for i in range(g)], 1).int().contiguous()
     tlS = tl[None].expand(S, g + 1, V).contiguous()
     dlS = dl[None].expand(S, g, V).contiguous()
     u = torch.rand(S, g + 2, dtype=torch.float64, device=DEV)
-    R = torch.zeros(S, g + 1, dtype=torch.float64, device=DEV)
+    R = torch.zeros(native.lib().tf_spec_verify_scratch_doubles(S, g, V), dtype=torch.float64, device=DEV)
     w = torch.zeros(S, g + 1, dtype=torch.float64, device=DEV)
     nacc = torch.zeros(S, dtype=torch.int32, device=DEV)
     tok = torch.zeros(S, dtype=torch.int32, device=DEV)

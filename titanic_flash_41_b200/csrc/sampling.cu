@@ -89,112 +89,196 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int ldl, int V, 
   }
 }
 
-__global__ void __launch_bounds__(1024) rowstat_kernel(const float* __restrict__ logits, int ldl, int V,
-                                                       float temp, float top_p, RowStat* __restrict__ out,
-                                                       TfStatusWord* st) {
-  __shared__ float fscr[32];
+// ---------------------------------------------------------------------------------------------
+// Row statistics for temperature + nucleus sampling, spread over the whole GPU.
+//
+// A row of 129,280 logits is too long for one CTA to walk several times at decode latency, so
+// every pass is a (rows x slices) grid and the passes talk through a small scratch area:
+//   max pass      -> scratch.maxkey[row]          (atomicMax on the order-preserving key)
+//   3 radix levels over the key (12 + 12 + 8 bits): a histogram pass adds each slice's
+//     shared-memory histogram of MASS into scratch.hist[row][4096]; a pick pass (one CTA per
+//     row) finds the first bin from the top whose inclusive cumulative mass reaches top_p * Z,
+//     records the prefix, and clears the histogram for the next level / next call.
+// Masses are 2^-40 fixed point: integer atomics make the sums independent of arrival order, so
+// every rank that samples the same row derives bit-identical statistics.
+// Scratch layout per row: RowScratch header (64 B) followed by 4096 uint64 bins; it must be
+// zero before the first call and is left zero by every call.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSlices = 16;
+constexpr double kFix = 1099511627776.0;     // 2^40
+
+struct RowScratch {
+  unsigned int maxkey;       // fkey of the row maximum (0 = not yet computed)
+  unsigned int prefix;       // key bits fixed so far
+  unsigned int mask;         // which bits of the key are fixed
+  int bad;                   // non-finite logit seen
+  unsigned long long above;  // mass strictly above the current prefix bin
+  unsigned long long total;  // Z in fixed point
+  unsigned long long target; // top_p * Z in fixed point
+  unsigned long long inbin;  // mass of the chosen bin at the last level
+  unsigned long long pad[2];
+};
+static_assert(sizeof(RowScratch) == 64, "RowScratch is 64 bytes");
+constexpr size_t kRowScratchBytes = sizeof(RowScratch) + 4096 * sizeof(unsigned long long);
+
+__device__ __forceinline__ RowScratch* row_scratch(void* base, int r) {
+  return reinterpret_cast<RowScratch*>(reinterpret_cast<uint8_t*>(base) + (size_t)r * kRowScratchBytes);
+}
+__device__ __forceinline__ unsigned long long* row_hist(void* base, int r) {
+  return reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(base) + (size_t)r * kRowScratchBytes +
+                                               sizeof(RowScratch));
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// slice bounds in units of float4
+__device__ __forceinline__ void slice_range(int V4, int& lo, int& hi) {
+  const int per = (V4 + gridDim.y - 1) / gridDim.y;
+  lo = blockIdx.y * per;
+  hi = min(V4, lo + per);
+}
+
+__global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ logits, int ldl, int V,
+                                                     void* scratch) {
   const int r = blockIdx.x;
-  const float* x = logits + (long)r * ldl;
+  const float4* x4 = reinterpret_cast<const float4*>(logits + (long)r * ldl);
+  int lo, hi;
+  slice_range(V / 4, lo, hi);
   float m = -INFINITY;
   int bad = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = x[i];
-    if (isnan(v) || v == INFINITY) bad = 1;
-    m = fmaxf(m, v);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float4 v = x4[i];
+    const float a = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+    if (!(a < INFINITY) || isnan(v.x + v.y + v.z + v.w)) bad = 1;
+    m = fmaxf(m, a);
   }
-  m = block_max(m, fscr);
-  if (__syncthreads_or(bad)) {
-    if (threadIdx.x == 0) {
-      tf_report(st, TF_NONFINITE, 20, r, 0);
-      out[r].m = 0.f;
-      out[r].thr = 0xffffffffu;
-      out[r].z = 1.0;
-    }
-    return;
-  }
-  // Masses are accumulated as 2^-40 fixed point so that the (unordered) shared-memory atomics give
-  // the same sums on every run and on every rank that samples the same row.
-  __shared__ unsigned long long hist[4096];
-  __shared__ unsigned long long chunk[32];
-  __shared__ unsigned long long s_above, s_total, s_inbin;
-  __shared__ uint32_t s_prefix;
-  const float inv_t = 1.f / temp;
-  const double kFix = 1099511627776.0;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t prefix = 0, mask = 0;
-  unsigned long long target = 0;
-  if (threadIdx.x == 0) s_above = 0;
-  // radix levels over the order-preserving key: 12 + 12 + 8 bits
-  for (int level = 0; level < 3; ++level) {
-    const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
-    const int nb = level == 2 ? 256 : 4096;
-    for (int i = threadIdx.x; i < nb; i += blockDim.x) hist[i] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float v = x[i];
-      const uint32_t key = fkey(v);
-      if ((key & mask) == prefix)
-        atomicAdd(&hist[(key >> shift) & (nb - 1)], (unsigned long long)((double)expf((v - m) * inv_t) * kFix));
-    }
-    __syncthreads();
-    // per-warp sums of nb/32 consecutive bins
-    {
-      const int per = nb / 32;
-      unsigned long long sacc = 0;
-      for (int j = lane; j < per; j += 32) sacc += hist[warp * per + j];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
-      if (lane == 0) chunk[warp] = sacc;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      if (level == 0) {
-        unsigned long long tot = 0;
-        for (int w = 0; w < 32; ++w) tot += chunk[w];
-        s_total = tot;
-        target = top_p < 1.f ? (unsigned long long)((double)top_p * (double)tot) : 0ull;
-        if (target == 0) target = 1;
-      }
-      // first bin from the top whose inclusive cumulative mass reaches the target
-      const int per = nb / 32;
-      unsigned long long cum = s_above;
-      int w = 31;
-      for (; w > 0; --w) {
-        if (cum + chunk[w] >= target) break;
-        cum += chunk[w];
-      }
-      int b = w * per + per - 1;
-      for (; b > w * per; --b) {
-        if (cum + hist[b] >= target) break;
-        cum += hist[b];
-      }
-      s_above = cum;
-      s_inbin = hist[b];
-      s_prefix = prefix | ((uint32_t)b << shift);
-    }
-    __syncthreads();
-    prefix = s_prefix;
-    mask |= (uint32_t)(nb - 1) << shift;
-    if (top_p >= 1.f) break;
-  }
-  uint32_t thr = 0;
-  double z = (double)s_total / kFix;
-  if (top_p < 1.f) {
-    thr = prefix;
-    z = (double)(s_above + s_inbin) / kFix;
-  }
-  if (threadIdx.x == 0) {
-    out[r].m = m;
-    out[r].thr = thr;
-    out[r].z = z;
+  if (blockIdx.y == gridDim.y - 1)
+    for (int i = (V / 4) * 4 + threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, logits[(long)r * ldl + i]);
+  m = warp_max(m);
+  bad = __any_sync(0xffffffffu, bad);
+  if ((threadIdx.x & 31) == 0) {
+    RowScratch* rs = row_scratch(scratch, r);
+    if (m > -INFINITY) atomicMax(&rs->maxkey, fkey(m));
+    if (bad) atomicExch(&rs->bad, 1);
   }
 }
 
+// level 0/1/2: shift 20/8/0, bins 4096/4096/256
+__global__ void __launch_bounds__(256) rowhist_kernel(const float* __restrict__ logits, int ldl, int V,
+                                                      float inv_t, int level, void* scratch) {
+  __shared__ unsigned long long sh[4096];
+  const int r = blockIdx.x;
+  RowScratch* rs = row_scratch(scratch, r);
+  const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
+  const int nb = level == 2 ? 256 : 4096;
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const float m = key_to_float(rs->maxkey);
+  const uint32_t prefix = rs->prefix, mask = rs->mask;
+  const float* x = logits + (long)r * ldl;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  int lo, hi;
+  slice_range(V / 4, lo, hi);
+  auto add = [&](float v) {
+    const uint32_t key = fkey(v);
+    if ((key & mask) == prefix)
+      atomicAdd(&sh[(key >> shift) & (nb - 1)], (unsigned long long)((double)expf((v - m) * inv_t) * kFix));
+  };
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float4 v = x4[i];
+    add(v.x);
+    add(v.y);
+    add(v.z);
+    add(v.w);
+  }
+  if (blockIdx.y == gridDim.y - 1)
+    for (int i = (V / 4) * 4 + threadIdx.x; i < V; i += blockDim.x) add(x[i]);
+  __syncthreads();
+  unsigned long long* gh = row_hist(scratch, r);
+  for (int i = threadIdx.x; i < nb; i += blockDim.x)
+    if (sh[i]) atomicAdd(&gh[i], sh[i]);
+}
+
+// one CTA (1024 threads) per row: choose the bin, clear the histogram
+__global__ void __launch_bounds__(1024) rowpick_kernel(int level, float top_p, int last, RowStat* __restrict__ out,
+                                                       void* scratch, TfStatusWord* st) {
+  __shared__ unsigned long long chunk[32];
+  const int r = blockIdx.x;
+  RowScratch* rs = row_scratch(scratch, r);
+  unsigned long long* gh = row_hist(scratch, r);
+  const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
+  const int nb = level == 2 ? 256 : 4096;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = nb / 32;
+  unsigned long long sacc = 0;
+  for (int j = lane; j < per; j += 32) sacc += gh[warp * per + j];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+  if (lane == 0) chunk[warp] = sacc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (level == 0) {
+      unsigned long long tot = 0;
+      for (int w = 0; w < 32; ++w) tot += chunk[w];
+      rs->total = tot;
+      unsigned long long tg = top_p < 1.f ? (unsigned long long)((double)top_p * (double)tot) : 0ull;
+      rs->target = tg ? tg : 1ull;
+      rs->above = 0;
+    }
+    const unsigned long long target = rs->target;
+    unsigned long long cum = rs->above;
+    int w = 31;
+    for (; w > 0; --w) {
+      if (cum + chunk[w] >= target) break;
+      cum += chunk[w];
+    }
+    int b = w * per + per - 1;
+    for (; b > w * per; --b) {
+      if (cum + gh[b] >= target) break;
+      cum += gh[b];
+    }
+    rs->above = cum;
+    rs->inbin = gh[b];
+    rs->prefix |= (uint32_t)b << shift;
+    rs->mask |= (uint32_t)(nb - 1) << shift;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) gh[i] = 0;
+  if (last && threadIdx.x == 0) {
+    RowStat o;
+    o.m = key_to_float(rs->maxkey);
+    if (rs->bad) {
+      tf_report(st, TF_NONFINITE, 20, r, 0);
+      o.m = 0.f;
+      o.thr = 0xffffffffu;
+      o.z = 1.0;
+    } else if (top_p < 1.f) {
+      o.thr = rs->prefix;
+      o.z = (double)(rs->above + rs->inbin) / kFix;
+    } else {
+      o.thr = 0;
+      o.z = (double)rs->total / kFix;
+    }
+    out[r] = o;
+    rs->maxkey = 0;
+    rs->prefix = 0;
+    rs->mask = 0;
+    rs->bad = 0;
+    rs->above = rs->total = rs->target = rs->inbin = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// block verification
+// ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ double prob_of(const float* x, const RowStat& s, float inv_t, int v) {
   const float l = x[v];
   if (fkey(l) < s.thr) return 0.0;
   return (double)expf((l - s.m) * inv_t) / s.z;
 }
+
+constexpr int kTile = 1024;
 
 struct VerifyParams {
   const float* tlogits;     // [S, g+1, V] target rows
@@ -206,123 +290,160 @@ struct VerifyParams {
   int S, g, V, ldl;
   float t_temp, d_temp;
   int point_mass;           // 1: q_i is a point mass at the proposal (text-lookup proposals)
-  double* R;                // [S, g+1] scratch: residual masses
+  double* tile_mass;        // [S, g+1, ntiles] scratch: residual mass of every 1024-token tile
   double* w;                // [S, g+1] scratch
   int* n_accept;            // [S]
   int* next_token;          // [S]
   TfStatusWord* st;
 };
 
-// residual value at token v of row i: max(w_i p_i(v) - q_i(v), 0); bonus row (i == g) has q = 0
-__device__ __forceinline__ double residual_at(const VerifyParams& p, int s, int i, double wi, int v) {
-  const float* tx = p.tlogits + ((long)s * (p.g + 1) + i) * p.ldl;
-  double val = wi * prob_of(tx, p.tstat[s * (p.g + 1) + i], 1.f / p.t_temp, v);
-  if (i < p.g) {
-    if (p.point_mass) {
-      if (v == p.proposals[s * p.g + i]) val -= 1.0;
-    } else {
-      const float* dx = p.dlogits + ((long)s * p.g + i) * p.ldl;
-      val -= prob_of(dx, p.dstat[s * p.g + i], 1.f / p.d_temp, v);
+// acceptance weight after i accepted proposals: w_0 = 1, w_i = min(1, w_{i-1} p_{i-1}(x_i) / q_{i-1}(x_i))
+__device__ double weight_chain(const VerifyParams& p, int s, int i) {
+  double w = 1.0;
+  for (int j = 1; j <= i; ++j) {
+    const int x = p.proposals[s * p.g + j - 1];
+    const float* tx = p.tlogits + ((long)s * (p.g + 1) + j - 1) * p.ldl;
+    const double pt = prob_of(tx, p.tstat[s * (p.g + 1) + j - 1], 1.f / p.t_temp, x);
+    double q = 1.0;
+    if (!p.point_mass) {
+      const float* dx = p.dlogits + ((long)s * p.g + j - 1) * p.ldl;
+      q = prob_of(dx, p.dstat[s * p.g + j - 1], 1.f / p.d_temp, x);
     }
+    const double ratio = q > 0.0 ? w * pt / q : (pt > 0.0 ? 1.0 : 0.0);
+    w = ratio < 1.0 ? ratio : 1.0;
+  }
+  return w;
+}
+
+// residual value at token v of row i: max(w_i p_i(v) - q_i(v), 0); the bonus row (i == g) has q = 0.
+// wz = w_i / Z_target, qz = 1 / Z_draft are hoisted by the callers.
+struct RowCtx {
+  const float* tx;
+  const float* dx;
+  float tm, dm, t_inv, d_inv;
+  uint32_t tthr, dthr;
+  double wz, qz;
+  int point_tok;            // >= 0: point-mass proposal at this token
+};
+__device__ __forceinline__ RowCtx row_ctx(const VerifyParams& p, int s, int i, double wi) {
+  RowCtx c;
+  const RowStat ts = p.tstat[s * (p.g + 1) + i];
+  c.tx = p.tlogits + ((long)s * (p.g + 1) + i) * p.ldl;
+  c.tm = ts.m;
+  c.tthr = ts.thr;
+  c.t_inv = 1.f / p.t_temp;
+  c.wz = wi / ts.z;
+  c.dx = nullptr;
+  c.point_tok = -1;
+  c.dm = 0.f;
+  c.dthr = 0;
+  c.d_inv = 1.f / p.d_temp;
+  c.qz = 0.0;
+  if (i < p.g) {
+    if (p.point_mass) c.point_tok = p.proposals[s * p.g + i];
+    else {
+      const RowStat ds = p.dstat[s * p.g + i];
+      c.dx = p.dlogits + ((long)s * p.g + i) * p.ldl;
+      c.dm = ds.m;
+      c.dthr = ds.thr;
+      c.qz = 1.0 / ds.z;
+    }
+  }
+  return c;
+}
+__device__ __forceinline__ double residual(const RowCtx& c, int v) {
+  const float l = c.tx[v];
+  double val = fkey(l) >= c.tthr ? c.wz * (double)expf((l - c.tm) * c.t_inv) : 0.0;
+  if (c.dx) {
+    const float d = c.dx[v];
+    if (fkey(d) >= c.dthr) val -= c.qz * (double)expf((d - c.dm) * c.d_inv);
+  } else if (v == c.point_tok) {
+    val -= 1.0;
   }
   return val > 0.0 ? val : 0.0;
 }
 
-// grid (S, g+1): w_i and R_i
-__global__ void __launch_bounds__(1024) verify_mass_kernel(VerifyParams p) {
-  __shared__ double scratch[32];
+// grid (S * (g+1), ntiles), 256 threads: residual mass of one 1024-token tile of one row
+__global__ void __launch_bounds__(256) verify_tiles_kernel(VerifyParams p) {
   __shared__ double s_w;
-  const int s = blockIdx.x, i = blockIdx.y;
-  if (threadIdx.x == 0) {
-    double w = 1.0;
-    for (int j = 1; j <= i; ++j) {
-      const int x = p.proposals[s * p.g + j - 1];
-      const float* tx = p.tlogits + ((long)s * (p.g + 1) + j - 1) * p.ldl;
-      double pt = prob_of(tx, p.tstat[s * (p.g + 1) + j - 1], 1.f / p.t_temp, x);
-      double q = 1.0;
-      if (!p.point_mass) {
-        const float* dx = p.dlogits + ((long)s * p.g + j - 1) * p.ldl;
-        q = prob_of(dx, p.dstat[s * p.g + j - 1], 1.f / p.d_temp, x);
-      }
-      double ratio = q > 0.0 ? w * pt / q : (pt > 0.0 ? 1.0 : 0.0);
-      w = ratio < 1.0 ? ratio : 1.0;
-    }
-    s_w = w;
-    p.w[s * (p.g + 1) + i] = w;
-  }
+  __shared__ double wsum[8];
+  const int row = blockIdx.x, s = row / (p.g + 1), i = row % (p.g + 1), tile = blockIdx.y;
+  if (threadIdx.x == 0) s_w = weight_chain(p, s, i);
   __syncthreads();
-  const double wi = s_w;
+  const RowCtx c = row_ctx(p, s, i, s_w);
   double acc = 0.0;
-  for (int v = threadIdx.x; v < p.V; v += blockDim.x) acc += residual_at(p, s, i, wi, v);
-  acc = block_sum_d(acc, scratch);
+  const int v0 = tile * kTile + threadIdx.x * 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (v0 + j < p.V) acc += residual(c, v0 + j);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = acc;
+  __syncthreads();
   if (threadIdx.x == 0) {
-    p.R[s * (p.g + 1) + i] = acc;
-    if (!(acc >= 0.0) || isinf(acc)) tf_report(p.st, TF_NONFINITE, 21, s, i);
+    double t = 0.0;
+    for (int k = 0; k < 8; ++k) t += wsum[k];
+    p.tile_mass[(long)row * gridDim.y + tile] = t;
   }
 }
 
-// grid S: decide tau and draw the token
-__global__ void __launch_bounds__(1024) verify_decide_kernel(VerifyParams p) {
-  constexpr int kTile = 1024;
-  __shared__ double tile_mass[512];
+// grid S, 1024 threads: acceptance length and the emitted token
+__global__ void __launch_bounds__(1024) verify_decide_kernel(VerifyParams p, int ntiles) {
   __shared__ double scan[1024];
+  __shared__ double Rrow[64], wrow[64];
   __shared__ int s_tau, s_tile, s_tok;
   __shared__ double s_target;
   const int s = blockIdx.x, g = p.g;
-  const double* R = p.R + s * (g + 1);
-  const double* w = p.w + s * (g + 1);
-  const double* u = p.uniforms + (long)s * (g + 2);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // R_i: fixed-order sums of the tile masses (one warp per row)
+  for (int i = warp; i <= g; i += 32) {
+    const double* tm = p.tile_mass + ((long)s * (g + 1) + i) * ntiles;
+    double acc = 0.0;
+    for (int t = lane; t < ntiles; t += 32) acc += tm[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) Rrow[i] = acc;
+  }
+  if (threadIdx.x == 0)
+    for (int i = 0; i <= g; ++i) {
+      wrow[i] = weight_chain(p, s, i);
+      p.w[s * (g + 1) + i] = wrow[i];
+    }
+  __syncthreads();
   if (threadIdx.x == 0) {
+    const double* u = p.uniforms + (long)s * (g + 2);
     int tau = 0;
     for (int i = 1; i <= g; ++i) {
-      double h = (i < g) ? (R[i] + 1.0 - w[i] > 0.0 ? R[i] / (R[i] + 1.0 - w[i]) : 0.0) : w[g];
+      const double R = Rrow[i], w = wrow[i];
+      if (!(R >= 0.0) || isinf(R)) tf_report(p.st, TF_NONFINITE, 21, s, i);
+      const double h = (i < g) ? (R + 1.0 - w > 0.0 ? R / (R + 1.0 - w) : 0.0) : w;
       if (u[i - 1] <= h) tau = i;
     }
     s_tau = tau;
     s_tok = -1;
-  }
-  __syncthreads();
-  const int tau = s_tau;
-  const double wi = w[tau];
-  const int ntiles = (p.V + kTile - 1) / kTile;
-  if (ntiles > 512) {
-    if (threadIdx.x == 0) tf_report(p.st, TF_BAD_ARG, 22, ntiles, 0);
-    return;
-  }
-  // tile masses: one warp per tile
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int tl = warp; tl < ntiles; tl += nw) {
-    double acc = 0.0;
-    for (int v = tl * kTile + lane; v < min(p.V, (tl + 1) * kTile); v += 32) acc += residual_at(p, s, tau, wi, v);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) tile_mass[tl] = acc;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    double total = 0.0;
-    for (int tl = 0; tl < ntiles; ++tl) total += tile_mass[tl];
+    const double* tm = p.tile_mass + ((long)s * (g + 1) + tau) * ntiles;
+    const double total = Rrow[tau];
     double target = u[g] * total;
-    // keep the target strictly inside the mass so that a token is always found
     if (target >= total) target = nextafter(total, 0.0);
     int tl = 0;
     double before = 0.0;
     for (; tl < ntiles - 1; ++tl) {
-      if (before + tile_mass[tl] > target) break;
-      before += tile_mass[tl];
+      if (before + tm[tl] > target) break;
+      before += tm[tl];
     }
     s_tile = tl;
     s_target = target - before;
     if (!(total > 0.0)) tf_report(p.st, TF_NONFINITE, 23, s, tau);
   }
   __syncthreads();
+  const int tau = s_tau;
+  const RowCtx c = row_ctx(p, s, tau, wrow[tau]);
   const int v = s_tile * kTile + threadIdx.x;
-  double val = (threadIdx.x < kTile && v < p.V) ? residual_at(p, s, tau, wi, v) : 0.0;
+  const double val = v < p.V ? residual(c, v) : 0.0;
   scan[threadIdx.x] = val;
   __syncthreads();
-  // inclusive scan (Hillis-Steele over 1024 entries)
   for (int d = 1; d < 1024; d <<= 1) {
-    double add = threadIdx.x >= d ? scan[threadIdx.x - d] : 0.0;
+    const double add = threadIdx.x >= d ? scan[threadIdx.x - d] : 0.0;
     __syncthreads();
     scan[threadIdx.x] += add;
     __syncthreads();
@@ -335,7 +456,7 @@ __global__ void __launch_bounds__(1024) verify_decide_kernel(VerifyParams p) {
     if (tok < 0) {
       // rounding pushed the target past the last positive entry: take the last positive one
       for (int j = min(kTile, p.V - s_tile * kTile) - 1; j >= 0; --j) {
-        double pv = j ? scan[j] - scan[j - 1] : scan[0];
+        const double pv = j ? scan[j] - scan[j - 1] : scan[0];
         if (pv > 0.0) {
           tok = s_tile * kTile + j;
           break;
@@ -361,25 +482,44 @@ TF_API int tf_argmax(const float* logits, int ldl, int V, int rows, int* out, fl
 
 TF_API int tf_rowstat_bytes() { return (int)sizeof(RowStat); }
 
+// bytes of zero-initialised scratch tf_rowstats needs for `rows` rows
+TF_API long tf_rowstats_scratch_bytes(int rows) { return (long)rows * (long)kRowScratchBytes; }
+
+// scratch: tf_rowstats_scratch_bytes(rows) bytes, zero before the first call (left zero by each call)
 TF_API int tf_rowstats(const float* logits, int ldl, int V, int rows, float temp, float top_p, void* out,
-                       void* status, cudaStream_t st) {
-  if (!(temp > 0.f)) return -1;
-  rowstat_kernel<<<rows, 1024, 0, st>>>(logits, ldl, V, temp, top_p, (RowStat*)out, (TfStatusWord*)status);
+                       void* scratch, void* status, cudaStream_t st) {
+  if (!(temp > 0.f) || (ldl % 4) != 0 || (((uintptr_t)logits) & 15) != 0 || scratch == nullptr) return -1;
+  const float inv_t = 1.f / temp;
+  dim3 grid(rows, kSlices);
+  rowmax_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, scratch);
+  const int levels = top_p < 1.f ? 3 : 1;
+  for (int level = 0; level < levels; ++level) {
+    rowhist_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, inv_t, level, scratch);
+    rowpick_kernel<<<rows, 1024, 0, st>>>(level, top_p, level == levels - 1, (RowStat*)out, scratch,
+                                          (TfStatusWord*)status);
+  }
   return (int)cudaGetLastError();
+}
+
+// doubles of scratch tf_spec_verify needs in `tile_mass`
+TF_API long tf_spec_verify_scratch_doubles(int S, int g, int V) {
+  return (long)S * (g + 1) * ((V + kTile - 1) / kTile);
 }
 
 // Block verification of g proposals per conversation (g may be 0: plain sampling of one row).
 TF_API int tf_spec_verify(const float* tlogits, const float* dlogits, const void* tstat, const void* dstat,
                           const int* proposals, const double* uniforms, int S, int g, int V, int ldl,
-                          float t_temp, float d_temp, int point_mass, double* R, double* w, int* n_accept,
-                          int* next_token, void* status, cudaStream_t st) {
+                          float t_temp, float d_temp, int point_mass, double* tile_mass, double* w,
+                          int* n_accept, int* next_token, void* status, cudaStream_t st) {
+  if (g > 62) return -1;
   VerifyParams p;
   p.tlogits = tlogits; p.dlogits = dlogits; p.tstat = (const RowStat*)tstat; p.dstat = (const RowStat*)dstat;
   p.proposals = proposals; p.uniforms = uniforms; p.S = S; p.g = g; p.V = V; p.ldl = ldl;
-  p.t_temp = t_temp; p.d_temp = d_temp; p.point_mass = point_mass; p.R = R; p.w = w;
+  p.t_temp = t_temp; p.d_temp = d_temp; p.point_mass = point_mass; p.tile_mass = tile_mass; p.w = w;
   p.n_accept = n_accept; p.next_token = next_token; p.st = (TfStatusWord*)status;
-  dim3 grid(S, g + 1);
-  verify_mass_kernel<<<grid, 1024, 0, st>>>(p);
-  verify_decide_kernel<<<S, 1024, 0, st>>>(p);
+  const int ntiles = (V + kTile - 1) / kTile;
+  dim3 grid(S * (g + 1), ntiles);
+  verify_tiles_kernel<<<grid, 256, 0, st>>>(p);
+  verify_decide_kernel<<<S, 1024, 0, st>>>(p, ntiles);
   return (int)cudaGetLastError();
 }

@@ -74,10 +74,13 @@ class SpecDecoder:
         self.ptok = torch.zeros(S, **i32)
         self.pacc = torch.zeros(S, **i32)
         self.u1 = torch.zeros(S, 2, **f64)
-        self.Rm = torch.zeros(S, self.R, **f64)
+        lib = native.lib()
+        self.Rm = torch.zeros(lib.tf_spec_verify_scratch_doubles(S, g, V), **f64)   # tile masses
         self.wm = torch.zeros(S, self.R, **f64)
-        self.R1 = torch.zeros(S, 1, **f64)
+        self.R1 = torch.zeros(lib.tf_spec_verify_scratch_doubles(S, 0, V), **f64)
         self.w1 = torch.zeros(S, 1, **f64)
+        # zero-initialised scratch of the row-statistics passes (left zero by every call)
+        self.rs_scratch = torch.zeros(lib.tf_rowstats_scratch_bytes(S * self.R), dtype=torch.uint8, device=dev)
         self.rows_all = torch.arange(S * self.R, device=dev)
         self.rows_d = torch.arange(S, device=dev)
         self.row_of_anchor = torch.arange(S, device=dev) * self.R
@@ -129,7 +132,7 @@ class SpecDecoder:
             hid.copy_(self.bd["x"])
             # sample proposal j from the modified draft law
             stat = self.dstat[:, j].contiguous()
-            native.call("tf_rowstats", lg, V, V, S, self.temperature, self.top_p, stat, st)
+            native.call("tf_rowstats", lg, V, V, S, self.temperature, self.top_p, stat, self.rs_scratch, st)
             self.dstat[:, j].copy_(stat)
             self.u1[:, 0].copy_(self.d_ud[:, j])
             self.u1[:, 1].copy_(self.d_ud[:, j])
@@ -142,7 +145,7 @@ class SpecDecoder:
             tok = self.bv["meta"][0].view(S, R)
             tok[:, 1:].copy_(self.props[:, :g])
         logits = e.run(S * R, self.bv, nmax, R if R <= 32 else 1, self.rows_all)
-        native.call("tf_rowstats", logits, V, V, S * R, self.temperature, self.top_p, self.tstat, st)
+        native.call("tf_rowstats", logits, V, V, S * R, self.temperature, self.top_p, self.tstat, self.rs_scratch, st)
         native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
                     self.dstat if g > 0 else None, self.props if g > 0 else None, self.d_u, S, g, V, V,
                     self.temperature, self.temperature, 0, self.Rm, self.wm, self.d_out[0], self.d_out[1], st)
