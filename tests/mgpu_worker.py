@@ -1,0 +1,98 @@
+"""Multi-GPU checks, launched by torchrun (one rank per GPU):  fused all-reduce kernels against
+torch references, and the tensor/expert-parallel engine against the single-GPU engine."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from titanic_flash_41_b200.config import DraftConfig, EngineConfig  # noqa: E402
+from titanic_flash_41_b200.models import engine as E  # noqa: E402
+from titanic_flash_41_b200.models import oracle  # noqa: E402
+from titanic_flash_41_b200.ops import native  # noqa: E402
+from titanic_flash_41_b200.parallel.comm import DistComm, LocalComm  # noqa: E402
+from titanic_flash_41_b200.parallel.symm import SymmWorkspace  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    comm = DistComm()
+    st = native.StatusWord(dev)
+    # ---- 1. one-shot all-reduce of a small fp32 matrix, many epochs back to back
+    N = 512
+    ws = SymmWorkspace(N, max_rows=32, device=dev, spin_limit=50_000_000)
+    for it, rows in enumerate([1, 5, 16, 32, 7, 7, 7, 32]):
+        g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+        x = torch.randn(rows, N, device=dev, generator=g)
+        out = torch.zeros(rows, N, device=dev)
+        ws.allreduce(x, rows, out, st.t)
+        ref = x.clone()
+        dist.all_reduce(ref)
+        torch.cuda.synchronize()
+        st.check()
+        assert torch.allclose(out, ref, atol=1e-5), (it, float((out - ref).abs().max()))
+        # every rank holds the bit-identical sum
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        assert all(torch.equal(gathered[0], t) for t in gathered)
+    # ---- 2. FP8 GEMV fused with all-reduce and residual update
+    K, M = 1024, 9
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    w = E.quant_fp8_device(torch.randn(N, K, device=dev, generator=g) * 0.05)
+    x16 = torch.randn(M, K, device=dev, generator=g).half()
+    resid = torch.randn(M, N, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).bfloat16()
+    r0 = resid.clone()
+    ws.gemv_allreduce(w, x16, M, resid, None, st.t)
+    part = x16.float() @ E.dequant_fp8(w).t()
+    dist.all_reduce(part)
+    torch.cuda.synchronize()
+    st.check()
+    want = (r0.float() + part).bfloat16()
+    assert (resid.float() - want.float()).abs().max() < 0.05, float((resid.float() - want.float()).abs().max())
+    # ---- 3. engine: TP/EP over `world` GPUs (fused kernels) == single GPU
+    from tests.test_engine_gpu import small_config
+    cfg = small_config(n_heads=4 * world if world > 4 else 4, draft=DraftConfig(layers=1, depth=3))
+    W = oracle.init_weights(cfg, 0)
+    ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,))
+    eng = E.Engine.from_weights(cfg, ecfg, W, comm=comm, device=dev)
+    eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev, spin_limit=50_000_000)
+    ref = E.Engine.from_weights(cfg, ecfg, W, comm=LocalComm(), device=dev)
+    gen = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab, (90,), generator=gen).tolist()
+    a = eng.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
+    b = ref.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
+    errs = [float((a - b).abs().max() / b.abs().max())]
+    pos = 90
+    for step in range(5):
+        toks = torch.randint(0, cfg.vocab, (4,), generator=gen).tolist()
+        a = eng.forward(E.StepPlan.build([(0, pos, toks)]))
+        b = ref.forward(E.StepPlan.build([(0, pos, toks)]))
+        errs.append(float((a - b).abs().max() / b.abs().max()))
+        pos += 4
+    torch.cuda.synchronize()
+    eng.status.check()
+    srt = sorted(errs)
+    assert srt[len(srt) // 2] < 0.08, errs
+    # ---- 4. speculative decode under a CUDA graph with the fused collectives
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    dec = SpecDecoder(eng, 1, temperature=0.6, top_p=0.95, use_graph=True)
+    slots = [DecodeSlot(region=0, length=pos, anchor=5, seed=11)]
+    outs = [dec.step(slots) for _ in range(6)]
+    eng.status.check()
+    flat = [t for o in outs for t in o[0]]
+    toks_all = [None] * world
+    dist.all_gather_object(toks_all, flat)
+    assert all(t == toks_all[0] for t in toks_all), "ranks committed different tokens"
+    dist.barrier()
+    if rank == 0:
+        print("MGPU_OK", world, errs)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,77 @@
+"""Cache-eviction, ladder and checkpoint-placement policy (pure functions)."""
+from titanic_flash_41_b200.serve import policy as P
+
+
+def test_fits_without_eviction_and_refuses_oversize():
+    assert P.cache_evictions([(100, 10), (200, 10)], (300, 10), budget=100, long_first=True, slots=4) == []
+    assert P.cache_evictions([(100, 10)], (300, 200), budget=100, long_first=True, slots=4) is None
+    assert P.cache_evictions([], (1, 1), 10, True, 0) is None
+
+
+def test_oldest_first_and_two_longer_parents_protected():
+    entries = [(9000, 10), (500, 10), (9500, 10), (400, 10)]
+    # slots full: one must go; the longer parents (9000, 9500) are protected, so the oldest short one goes
+    assert P.cache_evictions(entries, (600, 10), 1000, True, 4) == [1]
+    assert P.cache_evictions(entries, (600, 10), 1000, False, 4) == [0]
+    # byte pressure evicts several, oldest unprotected first
+    assert P.cache_evictions(entries, (600, 25), 45, True, 8) == [1, 3]
+
+
+def test_ladder_evicts_cheapest_rung_and_keeps_latest_two():
+    entries = [(1000, 1), (1100, 1), (5000, 1), (9000, 1), (9100, 1)]
+    anc = [True] * 5
+    ev = P.cache_evictions(entries, (9200, 1), 100, False, 5, ancestors=anc)
+    # ordinary victim would be index 0 (an ancestor) -> ladder picks the smallest (at-prev)*(next-at)
+    # rung 1100: (1100-1000)*(5000-1100) = 390000 ; rung 1000: 1000*100 = 100000 -> index 0
+    assert ev == [0]
+    entries = [(4000, 1), (4100, 1), (8000, 1), (9000, 1), (9100, 1)]
+    ev = P.cache_evictions(entries, (9200, 1), 100, False, 5, ancestors=[True] * 5)
+    assert ev == [1]            # (4100-4000)*(8000-4100) is the smallest product
+    assert P.ladder_victim([(1, 1), (2, 1)], [True, True], [0, 1], []) is None
+
+
+def test_short_reserve():
+    entries = [(100, 1), (200, 1), (9000, 1), (300, 1)]
+    # a long incoming image skips the newest `reserve` short entries
+    assert P.cache_evictions(entries, (10000, 1), 100, False, 4, short_reserve=2) == [0]
+    assert P.cache_evictions(entries, (10000, 1), 100, False, 4, short_reserve=3) == [2]
+    # a short incoming image replaces the oldest short entry once shorts hold the reserve
+    assert P.cache_evictions(entries, (50, 1), 100, False, 4, short_reserve=2) == [0]
+
+
+def test_optional_images_yield_first_and_never_displace():
+    entries = [(100, 5), (5000, 5), (200, 5)]
+    assert P.cache_evictions_with_optional(entries, [False, True, True], (300, 5), 15, False, 8) == [2]
+    assert P.prompt_cache_evictions(entries, (300, 5), 15, False, 8, has_media=False) is None
+    assert P.prompt_cache_evictions(entries, (300, 5), 15, False, 8, has_media=True) == [0]
+    assert P.prompt_cache_evictions(entries, (300, 5), 100, False, 8, has_media=False) == []
+
+
+def test_completed_turn_never_evicts_its_parent():
+    entries = [(1000, 5), (300, 5), (400, 5)]
+    ev = P.completed_cache_evictions(entries, [False] * 3, [True, False, False], (1100, 5), 15, False, 8)
+    assert ev == [1]
+    assert P.completed_cache_evictions(entries, [False] * 3, [True, False, False], (1100, 5), 4, False, 8) is None
+
+
+def test_eviction_cost_order_prefers_inner_rungs():
+    a = list(range(100))
+    prefixes = [a[:50], a[:80], a, [7, 7, 7]]
+    order = P.eviction_cost_order(prefixes)
+    assert order[0] in (0, 1) and order[-1] in (2, 3)      # older turns under a newer one go first
+    assert sorted(order) == [0, 1, 2, 3]
+
+
+def test_checkpoint_placement_rules():
+    assert P.shared_prefix_checkpoint(common=5000, previous=0, otherwise=6000, prompt=9000, minimum=1024) == 4992
+    assert P.shared_prefix_checkpoint(common=5000, previous=0, otherwise=12000, prompt=20000, minimum=1024) is None
+    assert P.shared_prefix_checkpoint(common=900, previous=0, otherwise=1000, prompt=9000, minimum=128) is None
+    assert P.system_prefix_checkpoint(system=8200, otherwise=9000, prompt=20000, minimum=1024) == 8192
+    assert P.system_prefix_checkpoint(system=2000, otherwise=9000, prompt=20000, minimum=1024) is None
+    assert P.near_end_of(list(range(300)), list(range(250))) and not P.near_end_of(list(range(300)), list(range(100)))
+    pos = P.checkpoint_positions(20000, 0)
+    assert pos == [8192, 16384, 19968]
+    assert P.checkpoint_positions(5000, 0) == []
+    assert P.common_prefix(list(range(10000)), list(range(9000)) + [1]) == 9000
+    assert P.cache_capacity(6, 7, 2, 1, 16, 1, 1) == (4, 14)
+    assert P.reload_pays(100 << 20, 100000) and not P.reload_pays(100 << 20, 100)

@@ -21,7 +21,7 @@
 //
 // Replaces, for the B200 build: kernels/direct_gemv_fp8.cu (FP8 GEMV, M<=8) and the b12x
 // `moe.w4a8.compact_micro` bundles of the reference.
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace {
 
@@ -53,6 +53,12 @@ struct SmallMParams {
   int x_div;                 // x row = pair / x_div
   float swiglu_limit;
   int k_per_warp;            // multiple of 128
+  // fused tensor-parallel epilogue (dense form, M <= 32): all-reduce the [M, N] partial over the
+  // peers' memory and add it to the residual stream
+  int use_comm;
+  CommParams comm;
+  __nv_bfloat16* resid;      // [M, N] residual stream updated in place (may be null)
+  float* ar_out;             // [M, N] reduced fp32 output (may be null)
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], const uint32_t b[2]) {
@@ -81,7 +87,7 @@ __device__ __forceinline__ uint4 ld_stream(const uint8_t* p) {
 template <int KIND, int MT, bool DUAL>
 __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* Wg, const uint8_t* W3g,
                                          const void* Sg, const void* S3g, int rows, const int* pairs,
-                                         int row_base, float (*red)[32][4]) {
+                                         int row_base, float (*red)[32][4], float* tile_out) {
   constexpr int NM = DUAL ? 2 : 1;
   constexpr int NT = 2 * NM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -295,7 +301,8 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
       }
       const long orow = pairs ? pairs[r] : r;
       const long off = orow * p.ldy + n;
-      if (p.out_kind == 0) reinterpret_cast<float*>(p.Y)[off] = o;
+      if (tile_out) tile_out[r * 32 + (n - n0)] = o;
+      else if (p.out_kind == 0) reinterpret_cast<float*>(p.Y)[off] = o;
       else if (p.out_kind == 1) reinterpret_cast<__half*>(p.Y)[off] = __float2half(o);
       else reinterpret_cast<__nv_bfloat16*>(p.Y)[off] = __float2bfloat16(o);
     }
@@ -306,6 +313,8 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 template <int KIND, bool DUAL>
 __global__ void __launch_bounds__(kWarps * 32) smallm_gemm_kernel(SmallMParams p) {
   __shared__ float red[kWarps * (DUAL ? 4 : 2) * 2][32][4];
+  __shared__ __align__(16) float ctile[(KIND == 0 && !DUAL) ? 32 * 32 : 4];
+  float* tile_out = (KIND == 0 && !DUAL && p.use_comm) ? ctile : nullptr;
   int rows;
   const uint8_t *Wg = p.W, *W3g = p.W3;
   const void *Sg = p.S, *S3g = p.S3;
@@ -330,11 +339,17 @@ __global__ void __launch_bounds__(kWarps * 32) smallm_gemm_kernel(SmallMParams p
   int row_base = 0;
   while (row_base < rows) {
     if (rows - row_base <= 8) {
-      run_rows<KIND, 1, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red);
+      run_rows<KIND, 1, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red, tile_out);
       row_base += 8;
     } else {
-      run_rows<KIND, 2, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red);
+      run_rows<KIND, 2, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red, tile_out);
       row_base += 16;
+    }
+  }
+  if (KIND == 0 && !DUAL) {
+    if (p.use_comm) {
+      if (comm_allreduce_tile(p.comm, ctile, rows, blockIdx.x))
+        comm_residual_update(p.resid, p.N, p.ar_out, p.N, ctile, rows, blockIdx.x);
     }
   }
 }
@@ -368,6 +383,7 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   p.n_groups = n_groups; p.sorted_pairs = sorted_pairs; p.x_div = x_div > 0 ? x_div : 1;
   p.swiglu_limit = swiglu_limit;
   p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
+  p.use_comm = 0;
   const bool dual = W3 != nullptr;
   cudaError_t e;
   if (kind == 0) e = dual ? launch<0, true>(p, slots, stream) : launch<0, false>(p, slots, stream);
@@ -375,4 +391,29 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   else if (kind == 2) e = launch<2, false>(p, slots, stream);
   else return -1;
   return (int)e;
+}
+
+// Dense FP8 GEMV (M <= 32) fused with the tensor-parallel all-reduce and the residual update:
+//   resid[M, N] += sum over ranks of X_rank[M, K] * W_rank[N, K]^T      (and/or ar_out = the sum)
+// `peers` is a device array of `world` workspace base addresses (see comm.cuh for the layout),
+// `epoch` a zero-initialised device array of N/32 counters owned by this rank.
+TF_API int tf_smallm_gemm_allreduce(const void* W, const void* S, int ldw, int lds, const void* X, int ldx,
+                                    int N, int K, int M, const void* peers, int world, int rank,
+                                    int max_rows, long flag_bytes, void* epoch, void* resid, float* ar_out,
+                                    int spin_limit, void* status, cudaStream_t stream) {
+  if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0 || (ldw % 16) != 0) return -1;
+  if (M < 1 || M > 32 || M > max_rows || world < 1 || world > 32) return -1;
+  SmallMParams p;
+  p.W = (const uint8_t*)W; p.W3 = nullptr; p.S = S; p.S3 = nullptr;
+  p.w_group_stride = 0; p.s_group_stride = 0; p.ldw = ldw; p.lds = lds;
+  p.X = (const __half*)X; p.ldx = ldx; p.Y = nullptr; p.ldy = N; p.out_kind = 0; p.N = N; p.K = K; p.M = M;
+  p.group_expert = nullptr; p.group_start = nullptr; p.group_count = nullptr; p.n_groups = nullptr;
+  p.sorted_pairs = nullptr; p.x_div = 1; p.swiglu_limit = 0.f;
+  p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
+  p.use_comm = 1;
+  p.comm.peers = (const unsigned long long*)peers; p.comm.world = world; p.comm.rank = rank;
+  p.comm.tiles = N / kTileN; p.comm.max_rows = max_rows; p.comm.N = N; p.comm.epoch = (unsigned int*)epoch;
+  p.comm.flag_bytes = flag_bytes; p.comm.spin_limit = spin_limit; p.comm.st = (TfStatusWord*)status;
+  p.resid = (__nv_bfloat16*)resid; p.ar_out = ar_out;
+  return (int)launch<0, false>(p, 0, stream);
 }

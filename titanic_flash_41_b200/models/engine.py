@@ -355,7 +355,8 @@ class Engine:
                                  device=self.dev)
         self._scratch: Dict[int, dict] = {}
         self._dq_cache: Dict[int, torch.Tensor] = {}
-        self.big_gemm = None        # set by ops.gemm when the tcgen05 path is loaded
+        self.big_gemm = None        # set by ops.bigpath when the tcgen05 path is attached
+        self.symm = None            # SymmWorkspace: fused GEMV/combine + all-reduce over peer memory
         self.last_hidden: Optional[torch.Tensor] = None
 
     # -- construction helpers --------------------------------------------------------------
@@ -512,7 +513,9 @@ class Engine:
         d, Dh, Hl = cfg.hidden, cfg.head_dim, self.Hl
         pos, region, first_row, last_pos, nvalid = (b["meta"][i] for i in (1, 2, 3, 4, 5))
         # boundary: x += delta (previous sublayer); h = rmsnorm(x)
-        native.call("tf_add_norm", b["x"], None if first else b["delta"], 0, d, L.attn_norm, b["h16"],
+        if first:
+            b["pending"] = False
+        native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, L.attn_norm, b["h16"],
                     None, None, None, T, d, cfg.rms_eps)
         N = L.proj.q.shape[0]
         P = b["P"]
@@ -543,13 +546,22 @@ class Engine:
                     cfg.index_topk, selcnt, self.maxC, 1.0 / math.sqrt(Dh), nsplit, b["part_o"],
                     b["part_lse"], L.sink, self.freqs, cfg.rope.dim, b["a16"], None, Hl * Dh,
                     self.status.t)
-        self._linear(b["a16"], L.wo, b["delta"], T)
-        self._allreduce(b["delta"][:T])
+        fused = self.symm is not None and T <= self.SMALL_M
+        if fused:
+            # WO projection + all-reduce + residual add in one kernel over peer memory
+            self.symm.gemv_allreduce(L.wo, b["a16"], T, b["x"], None, self.status.t)
+            b["pending"] = False
+        else:
+            self._linear(b["a16"], L.wo, b["delta"], T)
+            self._allreduce(b["delta"][:T])
+            b["pending"] = True
         # FFN boundary
-        native.call("tf_add_norm", b["x"], b["delta"], 0, d, L.ffn_norm, b["h16"], None, None, None,
-                    T, d, cfg.rms_eps)
+        native.call("tf_add_norm", b["x"], b["delta"] if b["pending"] else None, 0, d, L.ffn_norm, b["h16"],
+                    None, None, None, T, d, cfg.rms_eps)
         self._moe(L, T, b)
-        self._allreduce(b["delta"][:T])
+        if not fused:
+            self._allreduce(b["delta"][:T])
+            b["pending"] = True
 
     def _index(self, L: LayerWeights, T: int, b: dict, nmax: int, rows_per_group: int, sslot: int,
                li: int) -> None:
@@ -597,6 +609,12 @@ class Engine:
             self._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
             self._linear(b["s_act"], L.sw2, b["s_y"], T)
             shared = b["s_y"]
+        if self.symm is not None and T <= self.SMALL_M:
+            # expert combine + shared expert + all-reduce + residual add in one kernel
+            self.symm.combine_allreduce(b["y_pair"], b["ids"], b["wts"], shared, T, cfg.topk, e_lo,
+                                        e_lo + self.El, b["x"], None, self.status.t)
+            b["pending"] = False
+            return
         native.call("tf_moe_combine", b["y_pair"], b["ids"], b["wts"], shared, b["delta"], T, d,
                     cfg.topk, e_lo, e_lo + self.El)
 
@@ -674,7 +692,8 @@ class Engine:
               ) -> Optional[torch.Tensor]:
         cfg = self.cfg
         d = cfg.hidden
-        native.call("tf_add_norm", b["x"], b["delta"], 0, d, self.final_norm, b["h16"] if draft else None,
+        native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, self.final_norm,
+                    b["h16"] if draft else None,
                     b["hb"], None, None, T, d, cfg.rms_eps)
         if not draft:
             self.last_hidden = b["x"]
@@ -720,6 +739,7 @@ class Engine:
         b["cat16"][:, d:].copy_(b["h16"])
         self._linear(b["cat16"], ex["main_proj"], b["delta"], T)
         b["x"].zero_()
+        b["pending"] = True
         for j, L in enumerate(self.draft_layers):
             self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False)
         return self._head(T, b, logit_rows, draft=True)

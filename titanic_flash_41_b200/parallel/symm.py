@@ -1,0 +1,64 @@
+"""Symmetric (peer-mapped) device memory for the fused compute+collective kernels.
+
+Every rank allocates one workspace of the same size, the ranks exchange handles, and each rank
+ends up with the base address of every peer's workspace mapped into its own address space
+(NVLink peer-to-peer through NVSwitch).  The kernels of ``csrc/comm.cuh`` store partial tiles
+and flags straight into those addresses.  Allocation and handle exchange go through
+``torch.distributed._symmetric_memory`` (plumbing only: no library kernel ever receives a peer
+pointer).  Replaces the reference's pinned-host RoCE region + CPU proxy (src/roce.rs:179-243).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+
+class SymmWorkspace:
+    """Workspace of the one-shot all-reduce epilogue for matrices [rows <= max_rows, N]."""
+
+    def __init__(self, N: int, max_rows: int = 32, device=None, group: Optional[dist.ProcessGroup] = None,
+                 spin_limit: int = 20_000_000):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.N, self.max_rows, self.spin_limit = N, max_rows, spin_limit
+        lib = native.lib()
+        self.flag_bytes = int(lib.tf_comm_flag_bytes(self.world, N))
+        nbytes = int(lib.tf_comm_workspace_bytes(self.world, N, max_rows))
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert len(ptrs) == self.world
+        self.peers = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+        self.epoch = torch.zeros(N // 32, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)
+
+    # ---- fused ops ---------------------------------------------------------------------------
+    def gemv_allreduce(self, w, x16: torch.Tensor, M: int, resid: Optional[torch.Tensor],
+                       out: Optional[torch.Tensor], status: torch.Tensor) -> None:
+        """resid[:M] += all-reduce(x16[:M] @ W^T) in ONE kernel (FP8 block-128 weights)."""
+        N, K = w.q.shape
+        assert N == self.N
+        native.call("tf_smallm_gemm_allreduce", w.q, w.s, K, K // 128, x16, x16.stride(0), N, K, M, self.peers,
+                    self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, resid, out,
+                    self.spin_limit, status)
+
+    def combine_allreduce(self, y_pair, ids, wts, shared_y, rows: int, topk: int, e_lo: int, e_hi: int,
+                          resid: Optional[torch.Tensor], out: Optional[torch.Tensor], status: torch.Tensor) -> None:
+        native.call("tf_moe_combine_allreduce", y_pair, ids, wts, shared_y, rows, self.N, topk, e_lo, e_hi,
+                    self.peers, self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, resid, out,
+                    self.spin_limit, status)
+
+    def allreduce(self, x: torch.Tensor, rows: int, out: torch.Tensor, status: torch.Tensor) -> None:
+        """out[:rows] = sum over ranks of x[:rows] (fp32, rows <= max_rows, width N)."""
+        native.call("tf_moe_combine_allreduce", None, None, None, x, rows, self.N, 0, 0, 0, self.peers,
+                    self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, None, out,
+                    self.spin_limit, status)
