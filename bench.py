@@ -150,6 +150,9 @@ def main():
     eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=0, max_chunk=chunk)
     from titanic_flash_41_b200.ops import bigpath
     bigpath.attach(eng)
+    if world > 1:
+        from titanic_flash_41_b200.parallel.symm import SymmWorkspace
+        eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev)
     gen = torch.Generator(device=dev).manual_seed(1234)
     synth_state(eng, gen)
     torch.cuda.synchronize()
@@ -248,10 +251,11 @@ def main():
             "gpu_launches_per_step": launches,
             "clocks": clocks, "init_s": round(init_s, 1), "peak_mem_gb": round(mem_gb, 1), "impl": "own",
         }
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        os._exit(0)        # skip the collective teardown (it can block on live peer mappings)
 
 
 if __name__ == "__main__":

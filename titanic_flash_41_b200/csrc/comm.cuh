@@ -73,9 +73,11 @@ __device__ __forceinline__ bool comm_allreduce_tile(const CommParams& c, float* 
   if (threadIdx.x < c.world) {
     const unsigned int* mine = reinterpret_cast<const unsigned int*>(c.peers[c.rank]) + threadIdx.x * c.tiles + j;
     int spins = 0;
-    // epochs only grow; (int) difference handles wrap-around
+    const long long t0 = clock64();
+    // epochs only grow; (int) difference handles wrap-around.  The wait gives up after spin_limit
+    // polls or about one second of SM clocks, whichever comes first.
     while ((int)(ld_acquire_sys(mine) - e) < 0) {
-      if (++spins > c.spin_limit) {
+      if (++spins > c.spin_limit || clock64() - t0 > 2000000000LL) {
         tf_report(c.st, TF_TIMEOUT, 200, threadIdx.x, j);
         s_fail = 1;
         break;

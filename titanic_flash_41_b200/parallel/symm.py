@@ -21,7 +21,7 @@ class SymmWorkspace:
     """Workspace of the one-shot all-reduce epilogue for matrices [rows <= max_rows, N]."""
 
     def __init__(self, N: int, max_rows: int = 32, device=None, group: Optional[dist.ProcessGroup] = None,
-                 spin_limit: int = 20_000_000):
+                 spin_limit: int = 2_000_000):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group or dist.group.WORLD
         self.world = dist.get_world_size(self.group)
