@@ -538,6 +538,15 @@ TF_API int tf_router(const void* h16, const void* gate, const float* bias, float
   return (int)cudaGetLastError();
 }
 
+// top-k + weights only, for logits produced elsewhere (large row counts: tensor-core GEMM)
+TF_API int tf_router_topk(const float* logits, const float* bias, int* ids, float* wts, int M, int E, int topk,
+                          int scoring, int renorm, float scale, cudaStream_t st) {
+  const int nw = 4;
+  router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
+      logits, bias, ids, wts, M, E, topk, scoring, renorm, scale);
+  return (int)cudaGetLastError();
+}
+
 TF_API int tf_route_group(const int* ids, int n_pairs, int e_lo, int e_hi, int* group_expert,
                           int* group_start, int* group_count, int* n_groups, int* sorted_pairs,
                           int* n_local_pairs, cudaStream_t st) {

@@ -557,7 +557,7 @@ class Engine:
             b["pending"] = True
         # FFN boundary
         native.call("tf_add_norm", b["x"], b["delta"] if b["pending"] else None, 0, d, L.ffn_norm, b["h16"],
-                    None, None, None, T, d, cfg.rms_eps)
+                    b["hb"], None, None, T, d, cfg.rms_eps)
         self._moe(L, T, b)
         if not fused:
             self._allreduce(b["delta"][:T])
@@ -582,9 +582,22 @@ class Engine:
     def _moe(self, L: LayerWeights, T: int, b: dict) -> None:
         cfg = self.cfg
         d, I = cfg.hidden, cfg.moe_inter
-        native.call("tf_router", b["h16"], L.gate, L.gate_bias, b["logits_r"], b["ids"], b["wts"], T,
-                    cfg.n_experts, d, cfg.topk, 1 if cfg.scoring == "sqrtsoftplus" else 0,
-                    1 if cfg.renorm else 0, cfg.route_scale)
+        scoring = 1 if cfg.scoring == "sqrtsoftplus" else 0
+        if T > self.SMALL_M and self.big_gemm is not None and cfg.n_experts % 128 == 0:
+            # router logits of a prefill chunk on the tensor cores (bf16 x bf16), then top-k
+            native.call("tf_gemm_tc", 0, b["hb"], d, L.gate, d, b["logits_r"], cfg.n_experts, T, cfg.n_experts,
+                        d, None, 0, None, 0, 0, None, None, 0, self.status.t)
+            native.call("tf_router_topk", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
+                        cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
+        elif T <= self.SMALL_M and cfg.n_experts % 32 == 0:
+            # weight-streaming GEMV over the bf16 gate matrix, then top-k
+            native.call("tf_smallm_gemm", 2, L.gate, None, None, None, 0, 0, d * 2, 0, b["hb"], d, b["logits_r"],
+                        cfg.n_experts, 0, cfg.n_experts, d, T, None, None, None, None, None, 1, 0, T, 0.0)
+            native.call("tf_router_topk", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
+                        cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
+        else:
+            native.call("tf_router", b["h16"], L.gate, L.gate_bias, b["logits_r"], b["ids"], b["wts"], T,
+                        cfg.n_experts, d, cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
         e_lo = self.rank * self.El
         npairs = T * cfg.topk
         if T <= self.SMALL_M:
