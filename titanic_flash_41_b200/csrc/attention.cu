@@ -284,7 +284,11 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   if (d >= tail0) {
     const int j = (d - tail0) >> 1;
     float sn, cs;
-    sincosf((float)pos[r] * freqs[j], &sn, &cs);
+    {
+      const float ang = (float)pos[r] * freqs[j];
+      const double two_pi = 6.283185307179586476925286766559;
+      sincosf((float)((double)ang - two_pi * floor((double)ang / two_pi)), &sn, &cs);
+    }
     const float other = vals[d ^ 1];
     // inverse rotation: angle -> -angle
     v = ((d - tail0) & 1) ? (-other * sn + v * cs) : (v * cs + other * sn);
@@ -312,7 +316,8 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
   p.sel_stride = sel_stride; p.sel_count = sel_count; p.maxC = maxC;
   p.scale_log2 = scale * 1.4426950408889634f; p.nsplit = nsplit; p.part_o = part_o; p.part_lse = part_lse;
   p.st = (TfStatusWord*)status;
-  const int warps = (Hl + 15) / 16;
+  // four warps always: all of them dequantise the key chunk, those that own heads run the MMAs
+  const int warps = 4;
   dim3 grid(T, nsplit);
   if (Dh == 128) {
     const int smem = (kChunk * (128 + 8) + 128 * (kChunk + 8)) * 2;

@@ -118,6 +118,16 @@ struct PrepParams {
   TfStatusWord* st;
 };
 
+// sin/cos of pos * freq.  The product (fp32, as the reference's frequency table defines the angle)
+// is reduced to [0, 2*pi) in double before the fp32 sincos, which keeps the fast path even at
+// positions near a million without changing the angle.
+__device__ __forceinline__ void rope_sincos(int pos, float freq, float* sn, float* cs) {
+  const float ang = (float)pos * freq;
+  const double two_pi = 6.283185307179586476925286766559;
+  const double red = (double)ang - two_pi * floor((double)ang / two_pi);
+  sincosf((float)red, sn, cs);
+}
+
 __device__ __forceinline__ float ldp(const PrepParams& p, long row, int col) {
   return p.p_kind == 0 ? reinterpret_cast<const float*>(p.P)[row * p.ldp + col]
                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.P)[row * p.ldp + col]);
@@ -174,6 +184,10 @@ __global__ void attn_prep_kernel(PrepParams p) {
   const int r = blockIdx.x, tid = threadIdx.x;
   const int pos = p.pos[r], reg = p.region[r];
   const int half_rd = p.rope_dim / 2, tail0 = p.Dh - p.rope_dim;
+  // the row's rotation table, computed once (accurate sincos of large arguments is slow)
+  __shared__ float s_sin[128], s_cos[128];
+  if (tid < half_rd) rope_sincos(pos, p.freqs[tid], &s_sin[tid], &s_cos[tid]);
+  __syncthreads();
 
   // ---- q: RoPE on the tail of every head
   if (p.off_q >= 0) {
@@ -182,8 +196,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
       float v = ldp(p, r, p.off_q + i);
       if (dd >= tail0) {
         const int j = (dd - tail0) >> 1;
-        float sn, cs;
-        sincosf((float)pos * p.freqs[j], &sn, &cs);
+        const float sn = s_sin[j], cs = s_cos[j];
         float other = ldp(p, r, p.off_q + (i ^ 1));
         v = ((dd - tail0) & 1) ? (other * sn + v * cs) : (v * cs - other * sn);
       }
@@ -207,8 +220,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
     int ri = -1;
     if (tid < p.rope_dim) {
       const int dd = tail0 + tid, j = tid >> 1;
-      float sn, cs;
-      sincosf((float)pos * p.freqs[j], &sn, &cs);
+      const float sn = s_sin[j], cs = s_cos[j];
       float a = sm[dd], o = sm[dd ^ 1];
       rot = (tid & 1) ? (o * sn + a * cs) : (a * cs - o * sn);
       ri = dd;
@@ -278,7 +290,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
     if (tid < p.rope_dim) {
       const int dd = tail0 + tid, j = tid >> 1;
       float sn, cs;
-      sincosf((float)g * p.cfreqs[j], &sn, &cs);
+      rope_sincos(g, p.cfreqs[j], &sn, &cs);
       float a = sm[dd], o = sm[dd ^ 1];
       rot = (tid & 1) ? (o * sn + a * cs) : (a * cs - o * sn);
       ri = dd;
@@ -466,7 +478,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y_pair, const int* 
                                    const float* __restrict__ wts, const float* __restrict__ shared_y,
                                    float* __restrict__ out, int d, int topk, int e_lo, int e_hi) {
   const int r = blockIdx.x;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < topk; ++j) {
       const int e = ids[r * topk + j];
@@ -558,7 +570,7 @@ TF_API int tf_route_group(const int* ids, int n_pairs, int e_lo, int e_hi, int* 
 
 TF_API int tf_moe_combine(const float* y_pair, const int* ids, const float* wts, const float* shared_y,
                           float* out, int M, int d, int topk, int e_lo, int e_hi, cudaStream_t st) {
-  moe_combine_kernel<<<M, 256, 0, st>>>(y_pair, ids, wts, shared_y, out, d, topk, e_lo, e_hi);
+  moe_combine_kernel<<<dim3(M, M <= 64 ? (d + 255) / 256 : 1), 256, 0, st>>>(y_pair, ids, wts, shared_y, out, d, topk, e_lo, e_hi);
   return (int)cudaGetLastError();
 }
 

@@ -459,8 +459,9 @@ class Engine:
     def _nsplit(self, T: int) -> int:
         if T > 64:
             return 1
+        # decode: one 64-key chunk per CTA keeps every SM busy with few rows
         keys = self.cfg.window + self.cfg.index_topk
-        return max(1, min(32, -(-keys // 128)))
+        return max(1, min(64, -(-keys // 64)))
 
     def scores_buffer(self, T: int, n: int) -> torch.Tensor:
         key = ("scores", T)

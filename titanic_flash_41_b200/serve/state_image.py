@@ -1,0 +1,183 @@
+"""Lossless snapshots of a conversation's device state, and the tiers they live in.
+
+An image is an ordered list of named byte regions (window rings, compressed streams, index
+keys, compressor carries, draft state, logits) cut at the conversation's frontier, plus the
+token prefix it stands for.  Tiers: device (as captured), pinned host memory, and a directory
+of chunked files with a SHA-256 per 4 MiB chunk that is verified on reload.  Reference:
+src/state_image.rs:218-525 (Image, try_allocate, save, drop_device, reload, digest),
+src/disk_tier.rs:20-221 (CHUNK 4 MiB, batches of 32 chunks, digest check on read).
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import struct
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+CHUNK = 4 << 20
+BATCH_CHUNKS = 32
+
+
+class ImageError(RuntimeError):
+    pass
+
+
+@dataclass
+class Image:
+    tokens: Tuple[int, ...]                    # the prefix this image restores
+    regions: List[Tuple[str, torch.Tensor]]    # (name, flat uint8 tensor)
+    kind: str = "complete"                     # complete | checkpoint | encoder | request | optional
+    media: str = ""                            # identity of images inside the prefix
+    meta: Dict[str, int] = field(default_factory=dict)
+    tier: str = "device"                       # device | host | disk
+    path: Optional[str] = None
+    _bytes: int = 0
+
+    @property
+    def length(self) -> int:
+        return len(self.tokens)
+
+    @property
+    def nbytes(self) -> int:
+        if self.regions:
+            self._bytes = sum(int(t.numel()) for _, t in self.regions)
+        return self._bytes
+
+    def digest(self) -> str:
+        h = hashlib.sha256()
+        for name, t in self.regions:
+            h.update(name.encode())
+            h.update(struct.pack("<Q", t.numel()))
+            h.update(t.detach().cpu().contiguous().numpy().tobytes())
+        return h.hexdigest()
+
+    # ---- tier moves ---------------------------------------------------------------------------
+    def to_host(self, pin: bool = True) -> None:
+        if self.tier != "device":
+            return
+        moved = []
+        for name, t in self.regions:
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=pin and torch.cuda.is_available())
+            h.copy_(t)
+            moved.append((name, h))
+        self.regions, self.tier = moved, "host"
+
+    def to_device(self, device) -> None:
+        if self.tier == "disk":
+            raise ImageError("reload from the disk tier first")
+        self.regions = [(n, t.to(device, non_blocking=True)) for n, t in self.regions]
+        self.tier = "device"
+
+
+def capture(tokens: Sequence[int], named: Sequence[Tuple[str, torch.Tensor]], kind: str = "complete",
+            media: str = "", meta: Optional[Dict[str, int]] = None) -> Image:
+    """Copy the given tensor views (any dtype/shape) into a new image on their own device."""
+    regs = [(n, t.contiguous().view(torch.uint8).reshape(-1).clone()) for n, t in named]
+    return Image(tuple(int(x) for x in tokens), regs, kind, media, dict(meta or {}))
+
+
+def restore_into(img: Image, targets: Dict[str, torch.Tensor]) -> None:
+    """Copy every region back into the view of the same name (sizes must match exactly)."""
+    if img.tier == "disk":
+        raise ImageError("image is parked on disk")
+    for name, src in img.regions:
+        dst = targets.get(name)
+        if dst is None:
+            raise ImageError(f"no target for region {name}")
+        flat = dst.view(torch.uint8).reshape(-1) if dst.is_contiguous() else None
+        if flat is None or flat.numel() != src.numel():
+            # non-contiguous view: go through a contiguous staging copy
+            tmp = src.to(dst.device).view(dst.dtype).reshape(dst.shape)
+            dst.copy_(tmp)
+        else:
+            flat.copy_(src, non_blocking=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# disk tier
+# ---------------------------------------------------------------------------------------------
+class DiskTier:
+    """Write-behind snapshot files.  Layout of ``<id>.img``: JSON header line, then the regions'
+    bytes back to back; ``<id>.idx`` holds one SHA-256 per 4 MiB chunk of the payload.  A hook can
+    inject faults at named points (reference feature ``storage-fault-injection``; never enabled in
+    serving)."""
+
+    def __init__(self, directory: str, fault_hook: Optional[Callable[[str], None]] = None):
+        self.dir = directory
+        self.fault = fault_hook or (lambda point: None)
+        os.makedirs(directory, exist_ok=True)
+
+    def reset_dir(self) -> None:
+        for f in os.listdir(self.dir):
+            if f.endswith((".img", ".idx")):
+                os.remove(os.path.join(self.dir, f))
+
+    def write(self, image_id: str, img: Image) -> int:
+        if img.tier == "disk":
+            return img.nbytes
+        path = os.path.join(self.dir, image_id + ".img")
+        header = {"tokens": list(img.tokens), "kind": img.kind, "media": img.media, "meta": img.meta,
+                  "regions": [[n, int(t.numel())] for n, t in img.regions]}
+        digests: List[str] = []
+        total = 0
+        self.fault("write_open")
+        with open(path + ".tmp", "wb") as f:
+            hb = json.dumps(header).encode() + b"\n"
+            f.write(struct.pack("<Q", len(hb)))
+            f.write(hb)
+            pending = bytearray()
+            for _, t in img.regions:
+                data = t.detach().cpu().contiguous().numpy().tobytes()
+                pending += data
+                while len(pending) >= CHUNK:
+                    chunk, pending = bytes(pending[:CHUNK]), pending[CHUNK:]
+                    digests.append(hashlib.sha256(chunk).hexdigest())
+                    self.fault("write_chunk")
+                    f.write(chunk)
+                    total += len(chunk)
+            if pending:
+                digests.append(hashlib.sha256(bytes(pending)).hexdigest())
+                f.write(bytes(pending))
+                total += len(pending)
+            f.flush()
+            os.fsync(f.fileno())
+        with open(os.path.join(self.dir, image_id + ".idx"), "w") as f:
+            json.dump({"chunk": CHUNK, "digests": digests, "bytes": total}, f)
+        os.replace(path + ".tmp", path)
+        img._bytes = total
+        img.regions, img.tier, img.path = [], "disk", path
+        return total
+
+    def read(self, image_id: str, img: Optional[Image] = None, pin: bool = False) -> Image:
+        path = os.path.join(self.dir, image_id + ".img")
+        with open(os.path.join(self.dir, image_id + ".idx")) as f:
+            idx = json.load(f)
+        self.fault("read_open")
+        with open(path, "rb") as f:
+            (hl,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(hl))
+            payload = f.read()
+        if len(payload) != idx["bytes"]:
+            raise ImageError(f"{image_id}: truncated image ({len(payload)} of {idx['bytes']} bytes)")
+        for i, want in enumerate(idx["digests"]):
+            got = hashlib.sha256(payload[i * idx["chunk"]:(i + 1) * idx["chunk"]]).hexdigest()
+            if got != want:
+                raise ImageError(f"{image_id}: chunk {i} fails its digest")
+        regs, off = [], 0
+        for name, n in header["regions"]:
+            t = torch.frombuffer(bytearray(payload[off:off + n]), dtype=torch.uint8)
+            regs.append((name, t.pin_memory() if (pin and torch.cuda.is_available()) else t))
+            off += n
+        out = img or Image(tuple(header["tokens"]), [], header["kind"], header["media"], header["meta"])
+        out.regions, out.tier, out.path = regs, "host", path
+        return out
+
+    def remove(self, image_id: str) -> None:
+        for ext in (".img", ".idx"):
+            p = os.path.join(self.dir, image_id + ext)
+            if os.path.exists(p):
+                os.remove(p)
