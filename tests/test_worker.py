@@ -1,0 +1,95 @@
+"""Serving worker on the CPU oracle backend: admission, prefix reuse, batched decode, token-exact
+resume from a cached image, cancellation."""
+import threading
+
+import torch
+
+from titanic_flash_41_b200.config import tiny_config
+from titanic_flash_41_b200.models import oracle
+from titanic_flash_41_b200.serve.backend import OracleBackend
+from titanic_flash_41_b200.serve.scheduler import Job, QueueFull, Scheduler
+from titanic_flash_41_b200.serve.session_cache import SessionCache
+from titanic_flash_41_b200.serve.worker import Worker
+
+
+def _mk(regions=2, queue_limit=4, **kw):
+    cfg = tiny_config()
+    W = oracle.init_weights(cfg, 0)
+    b = OracleBackend(cfg, W, regions=regions, max_context=512, chunk=32)
+    s = Scheduler(regions, queue_limit, 2)
+    return cfg, Worker(b, s, SessionCache(slots=8, budget_bytes=1 << 30), eos_id=1, checkpoint_min=32,
+                       checkpoint_align=32, **kw), s
+
+
+def _job(jid, toks, n, events, **kw):
+    return Job(jid, list(toks), n, emit=lambda k, p: events.append((jid, k, p)), **kw)
+
+
+def _drain(w, max_cmds=400):
+    for _ in range(max_cmds):
+        if w.run_once(0.0) == "idle" and not w.active and w.sched.waiting() == 0:
+            return
+    raise AssertionError("worker did not drain")
+
+
+def test_generation_matches_plain_greedy_and_reuses_prefix():
+    cfg, w, s = _mk()
+    ev = []
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(3, cfg.vocab, (70,), generator=g).tolist()
+    s.submit(_job("a", prompt, 12, ev, temperature=0.0))
+    _drain(w)
+    toks = [t for j, k, p in ev if k == "tokens" for t in p]
+    ref = oracle.OracleModel(cfg, oracle.init_weights(cfg, 0))
+    want, _ = oracle.greedy_generate(ref, [torch.tensor(prompt)], 12)
+    # speculative decoding with a draft head must commit exactly the greedy tokens
+    assert toks == want[0][: len(toks)] and len(toks) == 12
+    ready = [p for j, k, p in ev if k == "ready"][0]
+    assert ready["prompt_n"] == 70 and ready["cache_n"] == 0
+    # the follow-up turn restores the completed image: only the new tokens are prefilled
+    ev2 = []
+    follow = prompt + toks + [5, 6, 7]
+    s.submit(_job("b", follow, 6, ev2, temperature=0.0))
+    _drain(w)
+    ready2 = [p for j, k, p in ev2 if k == "ready"][0]
+    assert ready2["cache_n"] >= 70 and ready2["prompt_n"] <= len(follow) - 70
+    toks2 = [t for j, k, p in ev2 if k == "tokens" for t in p]
+    want2, _ = oracle.greedy_generate(ref, [torch.tensor(follow)], 6)
+    assert toks2 == want2[0]          # token-exact resume from the snapshot
+    assert w.cache.stats["hits"] >= 1 and w.cache.stats["reused_tokens"] >= 70
+
+
+def test_four_requests_two_regions_queue_and_429():
+    cfg, w, s = _mk(regions=2, queue_limit=4)
+    ev = []
+    for i in range(4):
+        s.submit(_job(f"j{i}", [10 + i] * 20, 5, ev, temperature=0.6, top_p=0.95, seed=i))
+    try:
+        s.submit(_job("j4", [3] * 5, 5, ev))
+        assert False, "queue should be full"
+    except QueueFull as e:
+        assert e.code == "queue_full"
+    _drain(w)
+    done = sorted(j for j, k, p in ev if k == "done")
+    assert done == ["j0", "j1", "j2", "j3"]
+    for i in range(4):
+        n = sum(len(p) for j, k, p in ev if k == "tokens" and j == f"j{i}")
+        assert 1 <= n <= 5
+
+
+def test_cancel_and_background_hold():
+    cfg, w, s = _mk(regions=1)
+    ev = []
+    j = _job("c", [9] * 30, 200, ev, temperature=0.0)
+    s.submit(j)
+    for _ in range(3):
+        w.run_once(0.0)
+    j.cancelled.set()
+    _drain(w)
+    assert [p["finish_reason"] for jj, k, p in ev if k == "done"] == ["cancelled"]
+    s.priority_lease(30.0)
+    s.submit(_job("bg", [4] * 8, 2, ev, background=True))
+    assert s.admit() == []            # background held by the lease
+    s.priority_lease(0.0)
+    _drain(w)
+    assert any(jj == "bg" and k == "done" for jj, k, p in ev)

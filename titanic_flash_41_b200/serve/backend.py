@@ -1,0 +1,228 @@
+"""Model backends behind the serving worker: the PyTorch oracle (CPU, tiny geometries; used by
+the CPU test tier and the gloo plumbing runs) and the CUDA engine.
+
+Both expose the same operations on *regions* (one admitted conversation each): prefill a token
+range, run one batched speculative decode step, capture / restore a state image, reset.
+Reference counterpart: the Target / GreedySession surface used by the resident worker
+(src/target.rs:861, src/dspark_generation.rs:1816).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..models import oracle
+from ..spec import rng, verify
+from ..spec.decoder import DecodeSlot
+from . import state_image as SI
+
+
+class OracleBackend:
+    name = "oracle"
+
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], regions: int = 4,
+                 max_context: int = 4096, comm=None, moe_parallel: str = "ep", chunk: int = 256):
+        self.cfg, self.regions, self.max_context, self.chunk = cfg, regions, max_context, chunk
+        self.model = oracle.OracleModel(cfg, weights, comm, moe_parallel)
+        self.sessions = [self.model.new_session(max_context) for _ in range(regions)]
+        self.hidden: List[Optional[torch.Tensor]] = [None] * regions
+        self.depth = cfg.draft.depth if (cfg.draft and "mtp.0.main_proj.weight" in weights) else 0
+        self.device = "cpu"
+
+    def reset(self, region: int) -> None:
+        self.sessions[region] = self.model.new_session(self.max_context)
+        self.hidden[region] = None
+
+    def prefill(self, region: int, tokens: Sequence[int], start: int,
+                on_chunk: Optional[Callable[[int], bool]] = None) -> Optional[torch.Tensor]:
+        s = self.sessions[region]
+        s.length = start
+        toks = torch.tensor(list(tokens), dtype=torch.long)
+        done, logits = 0, None
+        while done < len(toks):
+            n = min(self.chunk, len(toks) - done)
+            logits = self.model.forward(toks[done:done + n], s)
+            self.hidden[region] = self.model.last_hidden[-1:].clone()
+            done += n
+            if on_chunk is not None and not on_chunk(done):
+                return None
+        return logits[-1] if logits is not None else None
+
+    def sample(self, logits: torch.Tensor, temperature: float, top_p: float, seed: int, position: int) -> int:
+        p = verify.modified_law(logits[None], temperature, top_p)[0]
+        if temperature <= 0:
+            return int(p.argmax())
+        return verify.sample_from(p, rng.uniform(rng.block_round_seed(seed, position), rng.TARGET_DOMAIN, position))
+
+    def decode_step(self, slots: Sequence[DecodeSlot]) -> List[List[int]]:
+        out = []
+        for sl in slots:
+            s = self.sessions[sl.region]
+            s.length = sl.length
+            g = self.depth if sl.length + self.depth + 2 < self.max_context else 0
+            draft_u, accept_u, final_u = rng.round_uniforms(sl.seed, sl.length, g)
+            props, Q = [], []
+            hid, tok = self.hidden[sl.region], sl.anchor
+            for j in range(g):
+                lg, hid = self.model.draft_forward(torch.tensor([tok]), hid, s, sl.length + j)
+                q = verify.modified_law(lg, sl.temperature, sl.top_p)[0]
+                tok = verify.sample_from(q, draft_u[j]) if sl.temperature > 0 else int(q.argmax())
+                props.append(tok)
+                Q.append(q)
+            rows = torch.tensor([sl.anchor] + props)
+            lg = self.model.forward(rows, s, start=sl.length, commit=False)
+            P = verify.modified_law(lg, sl.temperature, sl.top_p)
+            if g == 0:
+                tau = 0
+                nxt = int(P[0].argmax()) if sl.temperature <= 0 else verify.sample_from(P[0], final_u)
+            elif sl.temperature <= 0:
+                tau = 0
+                while tau < g and props[tau] == int(P[tau].argmax()):
+                    tau += 1
+                nxt = int(P[tau].argmax())
+            else:
+                tau, nxt = verify.block_verify(P, torch.stack(Q), props, accept_u, final_u)
+            toks = [sl.anchor] + props[:tau]
+            sl.length += len(toks)
+            s.length = sl.length
+            sl.emitted += toks
+            sl.anchor = nxt
+            self.hidden[sl.region] = self.model.last_hidden[tau:tau + 1].clone()
+            out.append(toks)
+        return out
+
+    # ---- state images ------------------------------------------------------------------------
+    def _views(self, region: int, length: int) -> List[Tuple[str, torch.Tensor]]:
+        s = self.sessions[region]
+        r = self.cfg.compress_ratio
+        out = []
+        for k, t in s.window.items():
+            out.append((f"swa.{k}", t[max(0, length - self.cfg.window - 8):length]))
+        for k, t in s.comp.items():
+            out.append((f"compressed.{k}.kv", t[: length // r]))
+        for k, t in s.keys.items():
+            out.append((f"compressed.{k}.keys", t[: length // r]))
+        for k, t in s.carry.items():
+            out.append((f"compressed.{k}.carry", t[length // r * r:length]))
+        if self.hidden[region] is not None:
+            out.append(("hidden", self.hidden[region]))
+        return out
+
+    def snapshot(self, region: int, tokens: Sequence[int], kind: str = "complete", media: str = "") -> SI.Image:
+        return SI.capture(tokens, self._views(region, len(tokens)), kind, media, {"length": len(tokens)})
+
+    def restore(self, region: int, img: SI.Image) -> None:
+        self.reset(region)
+        s = self.sessions[region]
+        n = img.length
+        r = self.cfg.compress_ratio
+        for name, flat in img.regions:
+            t = flat.view(torch.float32)
+            if name == "hidden":
+                self.hidden[region] = t.reshape(1, *([self.cfg.hc_mult] if self.cfg.hc_mult > 1 else []), self.cfg.hidden).clone()
+                continue
+            kind, key = name.split(".", 1)
+            if kind == "swa":
+                lo = max(0, n - self.cfg.window - 8)
+                buf = s.buf(s.window, key, s.max_tokens, self.cfg.head_dim)
+                buf[lo:n] = t.reshape(n - lo, -1)
+            else:
+                key, what = key.rsplit(".", 1)
+                if what == "kv":
+                    s.buf(s.comp, key, s.max_tokens // r + 1, self.cfg.head_dim)[: n // r] = t.reshape(n // r, -1)
+                elif what == "keys":
+                    s.buf(s.keys, key, s.max_tokens // r + 1, self.cfg.index_dim)[: n // r] = t.reshape(n // r, -1)
+                else:
+                    C = self.cfg.head_dim + self.cfg.index_dim
+                    s.buf(s.carry, key, s.max_tokens, 2, C)[n // r * r:n] = t.reshape(n - n // r * r, 2, C)
+        s.length = n
+
+
+class EngineBackend:
+    """The CUDA engine: tcgen05 prefill path, batched speculative decode under CUDA graphs."""
+    name = "engine"
+
+    def __init__(self, engine, chunk: int = 16384):
+        from ..ops import bigpath, native
+        from ..spec.decoder import SpecDecoder
+        self.e, self.cfg, self.regions = engine, engine.cfg, engine.regions
+        self.max_context, self.chunk = engine.ecfg.max_context, min(chunk, engine.max_chunk)
+        self.device = engine.dev
+        if engine.big_gemm is None:
+            bigpath.attach(engine)
+        self._dec: Dict[Tuple[int, float, float], object] = {}
+        self._SpecDecoder, self._native = SpecDecoder, native
+        self.last_hidden_rows: Dict[int, torch.Tensor] = {}
+
+    def reset(self, region: int) -> None:
+        pass     # state is position-addressed: a new conversation simply overwrites it
+
+    def prefill(self, region, tokens, start, on_chunk=None):
+        from .prefill import run_prefill
+        lg = run_prefill(self.e, region, torch.tensor(list(tokens), dtype=torch.int32), self.chunk, start,
+                         True, on_chunk)
+        if lg is None:
+            return None
+        self.last_hidden_rows[region] = self.e.last_hidden[-1:].clone() if self.e.last_hidden is not None else None
+        return lg[-1].float()
+
+    def sample(self, logits, temperature, top_p, seed, position) -> int:
+        if temperature <= 0:
+            return int(logits.argmax())
+        p = verify.modified_law(logits.detach().cpu()[None], temperature, top_p)[0]
+        return verify.sample_from(p, rng.uniform(rng.block_round_seed(seed, position), rng.TARGET_DOMAIN, position))
+
+    def decode_step(self, slots):
+        key = (len(slots), slots[0].temperature, slots[0].top_p)
+        dec = self._dec.get(key)
+        if dec is None:
+            dec = self._SpecDecoder(self.e, len(slots), temperature=max(slots[0].temperature, 1e-3),
+                                    top_p=slots[0].top_p)
+            self._dec[key] = dec
+        for i, s in enumerate(slots):
+            h = self.last_hidden_rows.get(s.region)
+            if h is not None:
+                dec.hidden[i].copy_(h.reshape(-1)[-self.cfg.hidden:])
+        out = dec.step(slots)
+        for i, s in enumerate(slots):
+            self.last_hidden_rows[s.region] = dec.hidden[i].clone()
+        return out
+
+    def _views(self, region: int, length: int):
+        e, cfg = self.e, self.cfg
+        out = []
+        keep = min(length, cfg.window + 64)
+        slots = torch.arange(length - keep, length, device=e.dev) % e.ring
+        out.append(("swa", e.win[:, region][:, slots]))
+        nC = length // cfg.compress_ratio
+        out.append(("compressed.kv", e.comp[:, region, :nC]))
+        out.append(("compressed.keys", e.keys[:, region, :nC]))
+        out.append(("compressed.carry", e.carry[:, region]))
+        h = self.last_hidden_rows.get(region)
+        if h is not None:
+            out.append(("hidden", h))
+        return out
+
+    def snapshot(self, region, tokens, kind="complete", media=""):
+        return SI.capture(tokens, self._views(region, len(tokens)), kind, media, {"length": len(tokens)})
+
+    def restore(self, region, img):
+        e, cfg = self.e, self.cfg
+        n = img.length
+        if img.tier != "device":
+            img.to_device(e.dev)
+        for name, flat in img.regions:
+            if name == "swa":
+                keep = min(n, cfg.window + 64)
+                slots = torch.arange(n - keep, n, device=e.dev) % e.ring
+                e.win[:, region][:, slots] = flat.view(e.win.shape[0], keep, e.win_row)
+            elif name == "compressed.kv":
+                e.comp[:, region, : n // cfg.compress_ratio] = flat.view(e.comp.shape[0], -1, e.comp_row)
+            elif name == "compressed.keys":
+                e.keys[:, region, : n // cfg.compress_ratio] = flat.view(e.keys.shape[0], -1, e.key_row)
+            elif name == "compressed.carry":
+                e.carry[:, region] = flat.view(torch.float32).view(e.carry[:, region].shape)
+            elif name == "hidden":
+                self.last_hidden_rows[region] = flat.view(torch.bfloat16).clone()

@@ -1,0 +1,253 @@
+"""The GPU-owner loop of one rank.
+
+Rank 0 turns queued jobs into commands (Begin / Step / Finish / Idle / Shutdown); every rank
+executes the same command stream deterministically and the ranks compare a digest of the
+committed tokens after every step (reference: src/resident_worker.rs:342 Command codec, :4049
+execute, :6115 run_http loop, :2559 agree_progress).
+
+Begin   restore the best cached image whose prefix the prompt starts with, prefill the rest in
+        chunks (saving prompt checkpoints on the way; other conversations take a batched decode
+        step when a prefill slice runs long), sample the first token
+Step    one batched speculative verification round for every decoding conversation
+Finish  save the completed turn into the session cache and free the region
+Idle    one unit of background cache work (tier moves)
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence
+
+from ..spec.decoder import DecodeSlot
+from ..utils.event_log import EventLog
+from . import policy
+from .scheduler import Job, Scheduler
+from .session_cache import SessionCache
+
+
+@dataclass
+class Active:
+    job: Job
+    slot: DecodeSlot
+    prompt: List[int]
+    limit: int
+    started: float
+    first_token_at: float = 0.0
+    steps: int = 0
+    finished: Optional[str] = None
+
+
+class Worker:
+    def __init__(self, backend, scheduler: Optional[Scheduler], cache: Optional[SessionCache] = None,
+                 eos_id: int = 1, log: Optional[EventLog] = None, control=None, rank: int = 0,
+                 prefill_slice_s: float = 0.5, checkpoint_min: int = policy.SHORT_TOKENS,
+                 checkpoint_align: int = 8192):
+        self.b, self.sched, self.cache = backend, scheduler, cache or SessionCache()
+        self.eos, self.log, self.control, self.rank = eos_id, log or EventLog(), control, rank
+        self.slice_s, self.ck_min, self.ck_align = prefill_slice_s, checkpoint_min, checkpoint_align
+        self.active: Dict[int, Active] = {}
+        self.jobs: Dict[str, Job] = {}
+        self.running = True
+        self.requests = 0
+
+    # ---------------------------------------------------------------- command codec
+    @staticmethod
+    def encode(cmd: Dict[str, Any]) -> bytes:
+        return json.dumps(cmd, separators=(",", ":")).encode()
+
+    @staticmethod
+    def decode(raw: bytes) -> Dict[str, Any]:
+        return json.loads(raw)
+
+    def _digest(self) -> bytes:
+        h = hashlib.sha256()
+        for r in sorted(self.active):
+            a = self.active[r]
+            h.update(f"{r}:{a.slot.length}:{a.slot.anchor}:{len(a.slot.emitted)}|".encode())
+        return h.digest()
+
+    # ---------------------------------------------------------------- rank-0 driver
+    def next_command(self) -> Dict[str, Any]:
+        """Decide the next command from the queue and the active set (rank 0 only)."""
+        for a in list(self.active.values()):
+            if a.finished or a.job.cancelled.is_set():
+                return {"op": "finish", "region": a.job.region, "reason": a.finished or "cancelled"}
+        new = self.sched.admit() if self.sched else []
+        if new:
+            j = new[0]
+            for extra in new[1:]:            # one Begin per command; the rest stay admitted for the next rounds
+                self._pending.append(extra)
+            return self._begin_cmd(j)
+        if getattr(self, "_pending", None):
+            return self._begin_cmd(self._pending.pop(0))
+        if self.active:
+            return {"op": "step"}
+        if self.sched is not None and self.sched.closed:
+            return {"op": "shutdown"}
+        return {"op": "idle"}
+
+    _pending: List[Job] = []
+
+    def _begin_cmd(self, j: Job) -> Dict[str, Any]:
+        self.jobs[j.id] = j
+        return {"op": "begin", "id": j.id, "region": j.region, "tokens": j.tokens, "limit": j.max_new_tokens,
+                "temperature": j.temperature, "top_p": j.top_p, "seed": j.seed, "media": j.media}
+
+    def run_once(self, idle_wait: float = 0.05) -> str:
+        """One command: chosen by rank 0, broadcast, executed everywhere, agreed."""
+        if self.rank == 0:
+            cmd = self.next_command()
+            if cmd["op"] == "idle" and self.sched is not None and not self.active:
+                self.sched.wait_for_work(idle_wait)
+            raw = self.encode(cmd)
+            if self.control is not None:
+                self.control.command(raw)
+        else:
+            cmd = self.decode(self.control.command(None))
+        self.execute(cmd)
+        if self.control is not None and cmd["op"] in ("begin", "step", "finish"):
+            self.control.agree(self._digest())
+        return cmd["op"]
+
+    def run_forever(self) -> None:
+        self._pending = []
+        while self.running:
+            self.run_once()
+
+    # ---------------------------------------------------------------- execution (every rank)
+    def execute(self, cmd: Dict[str, Any]) -> None:
+        op = cmd["op"]
+        if op == "begin":
+            self._begin(cmd)
+        elif op == "step":
+            self._step()
+        elif op == "finish":
+            self._finish(cmd["region"], cmd["reason"])
+        elif op == "idle":
+            did = self.cache.idle_step()
+            if did:
+                self.log.log("cache_tier", move=did)
+        elif op == "shutdown":
+            self.running = False
+
+    def _emit(self, job: Optional[Job], kind: str, payload: Any) -> None:
+        if job is not None and self.rank == 0:
+            job.emit(kind, payload)
+
+    def _begin(self, cmd: Dict[str, Any]) -> None:
+        t0 = time.monotonic()
+        region, prompt = cmd["region"], list(cmd["tokens"])
+        job = self.jobs.get(cmd["id"])
+        self.requests += 1
+        if len(prompt) + 1 >= self.b.max_context:
+            self._emit(job, "error", {"code": "context_length_exceeded", "message": "prompt does not fit"})
+            if self.sched and job:
+                self.sched.release(job)
+            return
+        # ---- prefix reuse
+        start, hit = 0, self.cache.best_match(prompt, cmd.get("media", ""))
+        if hit is not None and self.cache.ensure_loaded(hit, self.b.device):
+            self.b.restore(region, hit.image)
+            start = hit.image.length
+            self.cache.touch(hit, start)
+        else:
+            self.cache.stats["misses"] += 1
+            self.b.reset(region)
+        if start == len(prompt):
+            start -= 1                       # the last prompt token is re-run to produce its logits
+        # ---- checkpoint plan for the part that is prefilled now
+        cks = policy.checkpoint_positions(len(prompt), start, self.ck_min, self.ck_align)
+        shared = policy.shared_prefix_checkpoint(self.cache.longest_shared(prompt), start,
+                                                 cks[0] if cks else len(prompt), len(prompt), 128)
+        if shared is not None:
+            cks = sorted(set(cks + [shared]))
+        logits, pos = None, start
+        last_slice = time.monotonic()
+        for stop in cks + [len(prompt)]:
+            if stop <= pos:
+                continue
+
+            def on_chunk(done, _base=pos):
+                nonlocal last_slice
+                # a long prefill lets the decoding conversations take one batched step per slice
+                if self.active and time.monotonic() - last_slice > self.slice_s:
+                    self._step()
+                    last_slice = time.monotonic()
+                return not (job is not None and job.cancelled.is_set())
+            logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk)
+            if logits is None:
+                self._emit(job, "error", {"code": "cancelled", "message": "cancelled during prefill"})
+                if self.sched and job:
+                    self.sched.release(job)
+                return
+            pos = stop
+            if stop != len(prompt):
+                self.cache.insert(self.b.snapshot(region, prompt[:stop], "checkpoint", cmd.get("media", "")))
+        first = self.b.sample(logits, cmd["temperature"], cmd["top_p"], cmd["seed"], len(prompt))
+        slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=cmd["seed"],
+                          temperature=cmd["temperature"], top_p=cmd["top_p"])
+        a = Active(job or Job(cmd["id"], prompt, cmd["limit"]), slot, prompt, cmd["limit"], t0, time.monotonic())
+        a.job.region = region
+        self.active[region] = a
+        ms = (time.monotonic() - t0) * 1e3
+        new = len(prompt) - start
+        self._emit(job, "ready", {"prompt_n": new, "cache_n": start, "prompt_ms": round(ms, 3),
+                                  "prompt_per_second": round(new / max(ms / 1e3, 1e-9), 1), "scope": "request"})
+        self.log.log("begin", id=cmd["id"], region=region, prompt=len(prompt), reused=start, ms=round(ms, 2))
+        self._deliver(a, [first], pending=True)
+
+    def _deliver(self, a: Active, toks: Sequence[int], pending: bool = False) -> None:
+        """Emit committed tokens; the anchor counts as generated as soon as it is sampled."""
+        out = []
+        for t in toks:
+            if a.finished:
+                break
+            if t == self.eos:
+                a.finished = "stop"
+                break
+            a.job.generated.append(t)
+            out.append(t)
+            if len(a.job.generated) >= a.limit:
+                a.finished = "length"
+        if out:
+            self._emit(a.job, "tokens", out)
+
+    def _step(self) -> None:
+        acts = [a for a in self.active.values() if not a.finished]
+        if not acts:
+            return
+        acts.sort(key=lambda a: a.job.region)
+        for a in acts:
+            if a.slot.length + 8 >= self.b.max_context:
+                a.finished = "length"
+        acts = [a for a in acts if not a.finished]
+        if not acts:
+            return
+        before = [a.slot.anchor for a in acts]
+        committed = self.b.decode_step([a.slot for a in acts])
+        for a, toks, old_anchor in zip(acts, committed, before):
+            a.steps += 1
+            # toks = [old anchor] + accepted proposals are now in the KV state; the anchor was already
+            # delivered when it was sampled, so deliver the accepted proposals and the new anchor
+            self._deliver(a, list(toks[1:]) + [a.slot.anchor])
+
+    def _finish(self, region: int, reason: str) -> None:
+        a = self.active.pop(region, None)
+        if a is None:
+            return
+        committed = a.prompt + a.slot.emitted
+        try:
+            self.cache.insert(self.b.snapshot(region, committed[: a.slot.length], "complete", a.job.media),
+                              completed=True)
+        except Exception as e:  # noqa: BLE001  (a refused save never fails the request)
+            self.log.log("save_failed", incident=True, error=str(e))
+        dt = time.monotonic() - a.first_token_at
+        self._emit(a.job, "done", {"finish_reason": reason, "completion_tokens": len(a.job.generated),
+                                   "prompt_tokens": len(a.prompt), "steps": a.steps,
+                                   "decode_tok_s": round(max(len(a.job.generated) - 1, 0) / max(dt, 1e-9), 2)})
+        self.log.log("finish", id=a.job.id, reason=reason, tokens=len(a.job.generated), steps=a.steps)
+        if self.sched is not None:
+            self.sched.release(a.job)
+        self.jobs.pop(a.job.id, None)
