@@ -1,0 +1,120 @@
+"""Fused tensor-parallel collective GEMMs against NCCL + cuBLAS on the same GPUs.
+
+    torchrun --nproc-per-node N benchmarks/bench_tp_collective.py
+
+GEMM -> all-reduce (M <= 32: one kernel, FP8 weight stream, one-shot exchange over peer memory)
+and GEMM -> reduce-scatter (M >= 512: tcgen05 GEMM whose epilogue stores tiles into the owner's
+memory, then the owner-side sum) for A [M, K/tp] x W [N, K/tp], K = N = 4096.  Times are CUDA
+events, max over ranks, L2 flushed between iterations.  Roofline of each fused op: the slower
+of FLOPs / measured GEMM peak and bytes that must cross NVLink / 770 GB/s.
+"""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from common import flush_l2, peaks  # noqa: E402
+from titanic_flash_41_b200.models import engine as E  # noqa: E402
+from titanic_flash_41_b200.ops import native  # noqa: E402
+from titanic_flash_41_b200.parallel.symm import RsWorkspace, SymmWorkspace  # noqa: E402
+
+NVLINK_GBS = 770.0
+
+
+def timed(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ts.append(float(t))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+    st = native.StatusWord(dev)
+    K = N = 4096
+    Kl = K // world
+    g = torch.Generator(device=dev).manual_seed(rank)
+    w = torch.randn(N, Kl, device=dev, generator=g) * 0.02
+    w8 = E.quant_fp8_device(w)
+    wb = w.bfloat16()
+    rows = []
+    ws = SymmWorkspace(N, 32, device=dev)
+    for M in (1, 4, 16):
+        x = torch.randn(M, Kl, device=dev, generator=g)
+        x16, xb = x.half(), x.bfloat16()
+        out = torch.zeros(M, N, device=dev)
+        fused = timed(lambda: ws.gemv_allreduce(w8, x16, M, None, out, st.t))
+        ref = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+        def base():
+            torch.matmul(xb, wb.t(), out=ref)
+            dist.all_reduce(ref)
+        nccl = timed(base)
+        want = x16.float() @ E.dequant_fp8(w8).t()
+        dist.all_reduce(want)
+        err = float((out - want).abs().max() / want.abs().max())
+        rows.append(dict(op="gemv+allreduce", M=M, fused_us=round(fused * 1e3, 1), nccl_cublas_us=round(nccl * 1e3, 1),
+                         speedup=round(nccl / fused, 2), rel_err=round(err, 5)))
+    for M in (512, 4096, 16384):
+        if M % (world * 128):
+            continue
+        rsw = RsWorkspace(M, N, device=dev)
+        x = torch.randn(M, Kl, device=dev, generator=g)
+        xb = x.bfloat16()
+        out = torch.zeros(M // world, N, device=dev, dtype=torch.bfloat16)
+        flops = 2.0 * M * N * Kl
+        link_bytes = M * N * 2 * (world - 1) / world
+        roof_ms = max(flops / (pk["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        fused = timed(lambda: rsw.gemm_reduce_scatter(0, xb, wb, out, st.t))
+        full = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        rs_out = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+
+        def base():
+            torch.matmul(xb, wb.t(), out=full)
+            dist.reduce_scatter_tensor(rs_out, full)
+        nccl = timed(base)
+        base()
+        rsw.gemm_reduce_scatter(0, xb, wb, out, st.t)
+        torch.cuda.synchronize()
+        err = float((out.float() - rs_out.float()).abs().max() / rs_out.float().abs().max())
+        row = dict(op="gemm+reduce_scatter bf16", M=M, fused_ms=round(fused, 4), nccl_cublas_ms=round(nccl, 4),
+                   speedup=round(nccl / fused, 2), roofline_ms=round(roof_ms, 4), frac_of_roofline=round(roof_ms / fused, 3),
+                   rel_err=round(err, 5))
+        # FP8 block-scaled operands
+        xg = x.view(M, Kl // 128, 128)
+        sa = (xg.abs().amax(-1).clamp_min(1e-12) / 448.0).contiguous()
+        xq = (xg / sa[:, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(M, Kl)
+        f8 = timed(lambda: rsw.gemm_reduce_scatter(2, xq, w8.q, out, st.t, sa, w8.s))
+        row.update(fp8_fused_ms=round(f8, 4), fp8_speedup_vs_bf16_baseline=round(nccl / f8, 2))
+        rows.append(row)
+        del rsw
+    st.check()
+    if rank == 0:
+        print(json.dumps({"world": world, "K": K, "N": N, "peaks": pk, "rows": rows}, indent=1), flush=True)
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

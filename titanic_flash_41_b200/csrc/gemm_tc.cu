@@ -44,6 +44,13 @@ struct GemmParams {
   // belongs to expert tile_expert[i] whose weights are rows [e*N, (e+1)*N) of B
   const int* tile_expert;
   const int* num_m_tiles;
+  // reduce-scatter form (tensor-parallel partial products): the bf16 tile of rows owned by rank o
+  // is stored straight into rank o's receive slot for this rank over NVLink and the tile's
+  // arrival counter on rank o is bumped; tf_rs_reduce on rank o sums the `world` slots.
+  const unsigned long long* rs_peers;   // [world] workspace bases (null = plain store)
+  int rs_world, rs_rank, rs_rows;       // rs_rows = M / world (multiple of 128)
+  long rs_recv_off;                     // byte offset of this parity's receive area in a workspace
+  long rs_flag_off;                     // byte offset of the arrival counters
 };
 
 template <int KIND>
@@ -61,6 +68,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   auto tempty = [&](int b) { return bar0 + 8u * (2 * kStages + kAccBufs + b); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kStages * kStageBytes + 200);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + kStages * kStageBytes + 208);
+  unsigned int* rs_done = reinterpret_cast<unsigned int*>(aligned + kStages * kStageBytes + 216);   // [8]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int BK = (KIND == 0) ? 64 : 128;               // elements per 128-byte row
@@ -78,6 +86,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc::mbar_init(tempty(b), kEpiWarps / 2 * 0 + kEpiWarps);
     }
     *abort_flag = 0;
+    for (int i = 0; i < 8; ++i) rs_done[i] = 0;
     tc::fence_barrier_init();
   }
   if (warp == 1) tc::tmem_alloc(tc::smem_u32(const_cast<uint32_t*>(tmem_slot)), kAccBufs * BN);
@@ -153,9 +162,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const int ew = warp - 2;
     const int quad = warp & 3;                 // TMEM lanes this warp may touch: [32*quad, 32*quad+32)
     const int half = ew >> 2;                  // which 64 of the tile's 128 columns
-    int grp = 0;
+    int grp = 0, tile_iter = -1;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      ++tile_iter;
       const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
       const int row = m0 + quad * 32 + lane;
       float acc[64];
@@ -197,7 +207,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           }
         }
       }
-      if (ok && row < p.M) {
+      if (p.rs_peers) {
+        // ---- GEMM -> reduce-scatter: push the tile to the rank that owns these rows
+        const int owner = m0 / p.rs_rows;
+        if (ok && row < p.M) {
+          __nv_bfloat16* recv = reinterpret_cast<__nv_bfloat16*>(p.rs_peers[owner] + p.rs_recv_off);
+          uint4* dst = reinterpret_cast<uint4*>(
+              recv + ((long)p.rs_rank * p.rs_rows + (row - owner * p.rs_rows)) * p.N + n0 + half * 64);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
+            dst[i] = *reinterpret_cast<uint4*>(h);
+          }
+        }
+        __threadfence_system();
+        // the last of the eight epilogue warps to finish this tile publishes it (no blocking barrier:
+        // a warp that gave up on a time-out must not strand the others)
+        __syncwarp();
+        if (lane == 0) {
+          unsigned int* done = rs_done + (tile_iter & 7);
+          if (atomicAdd(done, 1u) == kEpiWarps - 1) {
+            *done = 0;
+            __threadfence_system();
+            if (ok) {
+              unsigned int* cnt = reinterpret_cast<unsigned int*>(p.rs_peers[owner] + p.rs_flag_off) +
+                                  ((m0 - owner * p.rs_rows) / BM) * (p.N / BN) + n0 / BN;
+              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+            }
+          }
+        }
+      } else if (ok && row < p.M) {
         const long off = (long)row * p.ldc + n0 + half * 64;
         if (p.out_kind == 0) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + off);
@@ -226,6 +267,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 }
 
 int g_sms = 0;
+
+struct RsConfig {
+  const unsigned long long* peers = nullptr;
+  int world = 0, rank = 0;
+  long recv_off = 0, flag_off = 0;
+} g_rs;   // set by tf_gemm_rs around the launch; plain calls leave it empty
+
+// sum the `world` received slots of every 128x128 tile in rank order once all of them arrived
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const unsigned long long* peers, int rank, int world,
+                                                        int rows, int N, long recv_off, long flag_off,
+                                                        unsigned int want, __nv_bfloat16* out, int ldo,
+                                                        int spin_limit, TfStatusWord* st) {
+  __shared__ int s_fail;
+  const int nt = N / BN, tile = blockIdx.x, mt_i = tile / nt, nt_i = tile % nt;
+  const unsigned int* cnt = reinterpret_cast<const unsigned int*>(peers[rank] + flag_off) + tile;
+  if (threadIdx.x == 0) {
+    s_fail = 0;
+    int spins = 0;
+    const long long t0 = clock64();
+    unsigned int v;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+      if ((int)(v - want) >= 0) break;
+      if (++spins > spin_limit || clock64() - t0 > 4000000000LL) {
+        tf_report(st, TF_TIMEOUT, 110, tile, (int)v);
+        s_fail = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_fail) return;
+  const __nv_bfloat16* recv = reinterpret_cast<const __nv_bfloat16*>(peers[rank] + recv_off);
+  // 128 x 128 tile: 256 threads x (8 columns x 8 rows-strided)
+  for (int i = threadIdx.x; i < BM * (BN / 8); i += blockDim.x) {
+    const int r = mt_i * BM + i / (BN / 8), c = nt_i * BN + (i % (BN / 8)) * 8;
+    if (r >= rows) continue;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int src = 0; src < world; ++src) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(recv + ((long)src * rows + r) * N + c));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + (long)r * ldo + c) = *reinterpret_cast<uint4*>(o);
+  }
+}
 
 }  // namespace
 
@@ -256,6 +351,9 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
   p.M = M; p.N = N; p.K = K; p.kind = kind; p.sa = sa; p.ldsa = ldsa; p.sb = sb; p.ldsb = ldsb;
   p.C = C; p.ldc = ldc; p.out_kind = out_kind; p.status = (TfStatusWord*)status;
   p.tile_expert = experts > 0 ? tile_expert : nullptr; p.num_m_tiles = num_m_tiles;
+  p.rs_peers = g_rs.peers; p.rs_world = g_rs.world; p.rs_rank = g_rs.rank; p.rs_rows = g_rs.world ? M / g_rs.world : 0;
+  p.rs_recv_off = g_rs.recv_off; p.rs_flag_off = g_rs.flag_off;
+  if (p.rs_peers && (M % (g_rs.world * BM) != 0)) return -1;
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < g_sms ? tiles : g_sms;
   static bool attr_set = false;
@@ -268,5 +366,39 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
   if (kind == 0) gemm_tc_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
   else if (kind == 1) gemm_tc_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
   else gemm_tc_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+// bytes of the symmetric workspace of the GEMM -> reduce-scatter form: two receive areas (epoch
+// parity) of [world][M/world][N] bf16 plus the arrival counters
+TF_API long tf_gemm_rs_flag_bytes(int M, int N, int world) {
+  return ((long)(M / world / BM) * (N / BN) * 4 + 255) / 256 * 256;
+}
+TF_API long tf_gemm_rs_workspace_bytes(int M, int N, int world) {
+  return tf_gemm_rs_flag_bytes(M, N, world) + 2L * M * N * 2;
+}
+
+// C_rank[M/world, N] = sum over ranks of (A_r[M, K] * B_r[N, K]^T)[rows of this rank].
+// One tcgen05 GEMM whose epilogue stores every tile into its owner's memory while the next tile is
+// being multiplied, followed by the owner-side rank-ordered sum.  `epoch` counts calls on this
+// workspace (1, 2, ...): arrival counters are monotonic and receive areas alternate by parity.
+TF_API int tf_gemm_rs(int kind, const void* A, long lda, const void* B, long ldb, int M, int N, int K,
+                      const float* sa, int ldsa, const float* sb, int ldsb, const void* peers, int world,
+                      int rank, int epoch, void* out, int ldo, int spin_limit, void* status, cudaStream_t stream) {
+  if (world < 1 || M % (world * BM) != 0 || N % BN != 0 || (ldo % 8) != 0) return -1;
+  const long flag_bytes = tf_gemm_rs_flag_bytes(M, N, world);
+  g_rs.peers = (const unsigned long long*)peers; g_rs.world = world; g_rs.rank = rank;
+  g_rs.flag_off = 0;
+  g_rs.recv_off = flag_bytes + (long)(epoch & 1) * M * N * 2;
+  const int rc = tf_gemm_tc(kind, A, lda, B, ldb, nullptr, N, M, N, K, sa, ldsa, sb, ldsb, 2, nullptr, nullptr, 0,
+                            status, stream);
+  const long recv_off = g_rs.recv_off;
+  g_rs = RsConfig();
+  if (rc != 0) return rc;
+  const int rows = M / world;
+  const int tiles = (rows / BM) * (N / BN);
+  rs_reduce_kernel<<<tiles, 256, 0, stream>>>((const unsigned long long*)peers, rank, world, rows, N, recv_off, 0,
+                                              (unsigned int)epoch * (unsigned int)world, (__nv_bfloat16*)out, ldo,
+                                              spin_limit, (TfStatusWord*)status);
   return (int)cudaGetLastError();
 }

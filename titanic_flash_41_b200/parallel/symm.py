@@ -62,3 +62,36 @@ class SymmWorkspace:
         native.call("tf_moe_combine_allreduce", None, None, None, x, rows, self.N, 0, 0, 0, self.peers,
                     self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, None, out,
                     self.spin_limit, status)
+
+
+class RsWorkspace:
+    """Workspace of the GEMM -> reduce-scatter kernel for partial products [M, N] (bf16 transport)."""
+
+    def __init__(self, M: int, N: int, device=None, group: Optional[dist.ProcessGroup] = None,
+                 spin_limit: int = 4_000_000):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.M, self.N, self.spin_limit = M, N, spin_limit
+        nbytes = int(native.lib().tf_gemm_rs_workspace_bytes(M, N, self.world))
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.peers = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64, device=dev)
+        self.epoch = 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)
+
+    def gemm_reduce_scatter(self, kind: int, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
+                            status: torch.Tensor, sa: Optional[torch.Tensor] = None,
+                            sb: Optional[torch.Tensor] = None) -> None:
+        """out[M/world, N] (bf16) = rows of this rank of sum_r a_r[M, K] @ b_r[N, K]^T."""
+        M, K = a.shape
+        N = b.shape[0]
+        assert (M, N) == (self.M, self.N)
+        self.epoch += 1
+        native.call("tf_gemm_rs", kind, a, a.stride(0), b, b.stride(0), M, N, K, sa, sa.stride(0) if sa is not None else 0,
+                    sb, sb.stride(0) if sb is not None else 0, self.peers, self.world, self.rank, self.epoch, out,
+                    out.stride(0), self.spin_limit, status)
