@@ -1,0 +1,91 @@
+"""Command line, launcher and an end-to-end HTTP request against the oracle backend (CPU)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import time
+
+import pytest
+import requests
+
+from titanic_flash_41_b200 import cli, launcher
+from titanic_flash_41_b200.config import tiny_config
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_probe_and_parser():
+    info = cli.probe()
+    assert "torch" in info and isinstance(info["devices"], list)
+    a = cli.build_parser().parse_args(["serve", "--preset", "tiny", "--backend", "oracle", "--port", "1234"])
+    assert a.cmd == "serve" and a.port == 1234 and cli.model_config(a).digest() == tiny_config().digest()
+
+
+def test_stage_weights_command(tmp_path, capsys):
+    from titanic_flash_41_b200.models import loader, oracle
+    cfg = tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4")
+    cfgp = os.path.join(str(tmp_path), "cfg.json")
+    open(cfgp, "w").write(cfg.to_json())
+    ck = os.path.join(str(tmp_path), "ck")
+    loader.export_checkpoint(oracle.init_weights(cfg, seed=1), cfg, ck)
+    rc = cli.main(["stage-weights", "--model-config", cfgp, "--checkpoint", ck, "--out", os.path.join(str(tmp_path), "st"),
+                   "--rank", "1", "--world", "2"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["rank"] == 1 and out["bytes"] > 0
+    assert os.path.exists(os.path.join(str(tmp_path), "st", "rank1", "atlas.bin"))
+
+
+def test_launcher_env_and_failure_propagation(tmp_path):
+    env = launcher.rank_env(3, 8, 29000, "t", base={})
+    assert env["RANK"] == "3" and env["WORLD_SIZE"] == "8" and env["MASTER_ADDR"] == "127.0.0.1"
+    assert len(launcher.cores_for(1, 4, n_cores=16)) == 4 and launcher.cores_for(1, 4, n_cores=16)[0] == 4
+    out = os.path.join(str(tmp_path), "r")
+    ok = ["-c", f"import os; open(r'{out}' + os.environ['RANK'], 'w').write(os.environ['TFLASH_CONTROL_TICKET'])"]
+    assert launcher.launch(ok, 2, master_port=_free_port(), pin=False, poll_s=0.02) == 0
+    assert open(out + "0").read() == open(out + "1").read() != ""
+    bad = ["-c", "import os, sys, time; time.sleep(0 if os.environ['RANK'] == '1' else 30); sys.exit(7)"]
+    t0 = time.time()
+    assert launcher.launch(bad, 2, master_port=_free_port(), pin=False, poll_s=0.02) == 7
+    assert time.time() - t0 < 20            # rank 0 was stopped, not waited for
+
+
+@pytest.mark.timeout(180)
+def test_serve_end_to_end_oracle_backend():
+    port = _free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    p = subprocess.Popen([sys.executable, "-m", "titanic_flash_41_b200", "serve", "--preset", "tiny", "--backend", "oracle",
+                          "--port", str(port), "--max-context", "512", "--regions", "2", "--api-key", "k"],
+                         env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        base = f"http://127.0.0.1:{port}"
+        for _ in range(600):
+            try:
+                if requests.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except requests.RequestException:
+                pass
+            assert p.poll() is None, p.stdout.read().decode()[-2000:]
+            time.sleep(0.1)
+        h = {"Authorization": "Bearer k"}
+        assert requests.post(base + "/v1/chat/completions", json={}, timeout=5).status_code == 401
+        body = {"model": "x", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0}
+        r = requests.post(base + "/v1/chat/completions", json=body, headers=h, timeout=120)
+        assert r.status_code == 200, r.text
+        j = r.json()
+        assert j["usage"]["completion_tokens"] >= 1 and j["choices"][0]["finish_reason"] in ("stop", "length")
+        r2 = requests.post(base + "/v1/chat/completions", json=body, headers=h, timeout=120).json()
+        assert r2["choices"][0]["message"] == j["choices"][0]["message"]          # greedy is deterministic
+        assert requests.post(base + "/_native/shutdown", headers=h, timeout=5).status_code == 200
+        assert p.wait(timeout=60) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()

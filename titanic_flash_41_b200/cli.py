@@ -1,0 +1,172 @@
+"""Command line: ``python -m titanic_flash_41_b200 {serve,bench,stage-weights,probe,launch}``.
+
+``serve`` runs the OpenAI-compatible server on rank 0 and a worker loop on every rank;
+``bench`` times prefill and speculative decode; ``stage-weights`` writes this rank's weight atlas;
+``probe`` prints the device / peer-access / build facts the engine depends on (reference:
+src/bin/titanic-flash-server.rs:49-93 Cli and subcommands, :95 entry).
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import os
+import sys
+import threading
+from typing import Optional
+
+from .config import EngineConfig, ModelConfig, ServerConfig, flash_b200_config, reference_1017_config, tiny_config
+
+PRESETS = {"tiny": tiny_config, "flash-b200": flash_b200_config, "v41-1017": reference_1017_config}
+
+
+def model_config(args) -> ModelConfig:
+    if args.model_config:
+        return ModelConfig.from_json(open(args.model_config).read())
+    return PRESETS[args.preset]()
+
+
+def _common(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--preset", choices=sorted(PRESETS), default="tiny")
+    p.add_argument("--model-config", help="JSON file written by ModelConfig.to_json")
+    p.add_argument("--checkpoint", help="directory of safetensors shards; random weights when absent")
+    p.add_argument("--backend", choices=["engine", "oracle"], default="engine")
+    p.add_argument("--regions", type=int, default=4)
+    p.add_argument("--max-context", type=int, default=131072)
+    p.add_argument("--seed", type=int, default=0)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="titanic_flash_41_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("serve", help="OpenAI-compatible HTTP server")
+    _common(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--api-key", default=os.environ.get("TFLASH_API_KEY", ""))
+    s.add_argument("--queue-limit", type=int, default=16)
+    s.add_argument("--tokenizer", help="tokenizer.json (byte-level BPE); byte tokenizer when absent")
+    s.add_argument("--disk-cache", help="directory for the disk tier of the session cache")
+    s.add_argument("--event-log", help="JSONL event log path")
+    b = sub.add_parser("bench", help="prefill + decode timing (bench.py of the source tree)")
+    b.add_argument("rest", nargs=argparse.REMAINDER)
+    w = sub.add_parser("stage-weights", help="write this rank's staged weight atlas")
+    _common(w)
+    w.add_argument("--out", required=True)
+    w.add_argument("--rank", type=int, default=int(os.environ.get("RANK", 0)))
+    w.add_argument("--world", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
+    w.add_argument("--moe-parallel", choices=["ep", "tp"], default="ep")
+    sub.add_parser("probe", help="device, peer access and build facts as JSON")
+    l = sub.add_parser("launch", help="start one process per GPU running a sub-command")
+    l.add_argument("--gpus", type=int, required=True)
+    l.add_argument("--master-port", type=int, default=29511)
+    l.add_argument("rest", nargs=argparse.REMAINDER)
+    return ap
+
+
+def probe() -> dict:
+    import torch
+    from .utils import build
+    out = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available(),
+           "library": str(build.OUT / "libtflash_cuda.so"), "devices": []}
+    out["library_built"] = os.path.exists(out["library"])
+    if torch.cuda.is_available():
+        n = torch.cuda.device_count()
+        for i in range(n):
+            p = torch.cuda.get_device_properties(i)
+            out["devices"].append({"index": i, "name": p.name, "sm": f"{p.major}.{p.minor}", "sms": p.multi_processor_count,
+                                   "memory_gib": round(p.total_memory / 2 ** 30, 1),
+                                   "peers": [j for j in range(n) if j != i and torch.cuda.can_device_access_peer(i, j)]})
+        out["sm_100"] = all(d["sm"] == "10.0" for d in out["devices"])
+    return out
+
+
+def stage_weights(args) -> dict:
+    from .formats import atlas, layout
+    from .formats.safetensors import Checkpoint
+    cfg = model_config(args)
+    if not args.checkpoint:
+        raise SystemExit("stage-weights needs --checkpoint")
+    ck = Checkpoint.scan(args.checkpoint)
+    layout.validate_checkpoint(ck, cfg)
+    plan = layout.RankPlan.build(ck, cfg, args.rank, args.world, args.moe_parallel)
+    meta = atlas.stage(ck, cfg, plan, os.path.join(args.out, f"rank{args.rank}"))
+    return {"rank": args.rank, "world": args.world, "bytes": meta["bytes"], "tensors": len(meta["tensors"]),
+            "sha256": meta["sha256"]}
+
+
+def make_backend(args, cfg: ModelConfig, comm):
+    import torch
+    from .serve.backend import EngineBackend, OracleBackend
+    if args.backend == "oracle":
+        from .models import loader, oracle
+        from .formats.safetensors import Checkpoint
+        W = (loader.checkpoint_weights(Checkpoint.scan(args.checkpoint), cfg) if args.checkpoint
+             else oracle.init_weights(cfg, seed=args.seed))
+        return OracleBackend(cfg, W, regions=args.regions, max_context=args.max_context, comm=comm)
+    from .models.engine import Engine
+    ecfg = EngineConfig(regions=args.regions, max_context=args.max_context)
+    if args.checkpoint:
+        from .models import loader
+        eng = loader.load_engine(args.checkpoint, cfg, ecfg, comm)
+    else:
+        eng = Engine.random_init(cfg, ecfg, comm, seed=args.seed)
+    return EngineBackend(eng)
+
+
+def serve_main(args) -> int:
+    from .api.server import Frontend, Server, serve
+    from .api.tokenizer import load_tokenizer
+    from .parallel.comm import LocalComm, init_distributed
+    from .parallel.control import ControlChannel
+    from .serve.scheduler import Scheduler
+    from .serve.session_cache import SessionCache
+    from .serve.worker import Worker
+    from .utils.event_log import EventLog
+    cfg = model_config(args)
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    comm = init_distributed() if world > 1 else LocalComm()
+    control = None
+    if world > 1:
+        control = ControlChannel.connect(rank, world, "127.0.0.1", int(os.environ.get("TFLASH_CONTROL_PORT", 29512)),
+                                         os.environ.get("TFLASH_CONTROL_TICKET", "").encode())
+    backend = make_backend(args, cfg, comm)
+    log = EventLog(args.event_log) if args.event_log else EventLog()
+    tok = load_tokenizer(args.tokenizer, cfg.vocab)
+    scfg = ServerConfig(host=args.host, port=args.port, api_key=args.api_key, queue_limit=args.queue_limit,
+                        max_admitted=args.regions)
+    sched = Scheduler(scfg.max_admitted, scfg.queue_limit, scfg.background_queue_limit) if rank == 0 else None
+    worker = Worker(backend, sched, SessionCache(), eos_id=getattr(tok, "eos_id", 1), log=log, control=control, rank=rank)
+    if rank != 0:
+        worker.run_forever()
+        return 0
+    server = Server(scfg, Frontend(tok, args.max_context), sched, log)
+    t = threading.Thread(target=worker.run_forever, daemon=True)
+    t.start()
+    server.ready(f"{cfg.digest()[:12]}/{backend.name}/tp{world}")
+    asyncio.run(serve(server))
+    sched.close()
+    t.join(timeout=30)
+    return 0
+
+
+def main(argv: Optional[list] = None) -> int:
+    args = build_parser().parse_args(argv)
+    if args.cmd == "probe":
+        print(json.dumps(probe()))
+        return 0
+    if args.cmd == "stage-weights":
+        print(json.dumps(stage_weights(args)))
+        return 0
+    if args.cmd == "bench":
+        import runpy
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        sys.argv = [os.path.join(root, "bench.py")] + [a for a in args.rest if a != "--"]
+        runpy.run_path(sys.argv[0], run_name="__main__")
+        return 0
+    if args.cmd == "launch":
+        from .launcher import launch
+        rest = [a for a in args.rest if a != "--"]
+        return launch(["-m", "titanic_flash_41_b200", *rest], args.gpus, args.master_port)
+    return serve_main(args)
