@@ -523,3 +523,52 @@ TF_API int tf_spec_verify(const float* tlogits, const float* dlogits, const void
   verify_decide_kernel<<<S, 1024, 0, st>>>(p, ntiles);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// tf_rowstats with library-owned scratch (contract in rowstats_static.h)
+// ---------------------------------------------------------------------------------------------
+#include <cstdio>
+#include <mutex>
+
+#include "rowstats_static.h"
+
+static __device__ __align__(256) unsigned char g_rowstats_static_scratch[TF_ROWSTATS_STATIC_MAX_ROWS * kRowScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+
+// address of this device's copy of the array; looked up once per device
+cudaError_t static_scratch(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_rowstats_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return cudaSuccess;
+}
+}  // namespace
+
+TF_API int tf_rowstats_static(const float* logits, int ldl, int V, int rows, float temp, float top_p, void* out,
+                              void* status, cudaStream_t st) {
+  if (rows > TF_ROWSTATS_STATIC_MAX_ROWS) {
+    fprintf(stderr, "tf_rowstats_static: %d rows exceed the built-in scratch of %d rows; use tf_rowstats\n", rows,
+            TF_ROWSTATS_STATIC_MAX_ROWS);
+    return TF_ROWSTATS_STATIC_TOO_MANY_ROWS;
+  }
+  if (rows <= 0 || V <= 0 || out == nullptr) return -1;
+  void* scratch = nullptr;
+  cudaError_t e = static_scratch(&scratch);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemsetAsync(scratch, 0, (size_t)rows * kRowScratchBytes, st);
+  if (e != cudaSuccess) return (int)e;
+  return tf_rowstats(logits, ldl, V, rows, temp, top_p, out, scratch, status, st);
+}
