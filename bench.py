@@ -117,6 +117,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="print a per-kernel time table of one extra prefill pass")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -183,6 +184,13 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         prefill_s = float(t)
+        if args.trace:
+            # a second, untimed pass under the kernel clock: where the prefill time goes
+            from titanic_flash_41_b200.utils.trace import KernelClock
+            with KernelClock() as kc:
+                run_prefill(eng, 0, prompt, chunk)
+            if rank == 0:
+                print(kc.report(), file=sys.stderr, flush=True)
         synth_state(eng, gen)
 
     # ------------------------------------------------------------------ decode

@@ -19,7 +19,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from common import flush_l2, peaks  # noqa: E402
 from titanic_flash_41_b200.models import engine as E  # noqa: E402
 from titanic_flash_41_b200.ops import native  # noqa: E402
-from titanic_flash_41_b200.parallel.symm import RsWorkspace, SymmWorkspace  # noqa: E402
+from titanic_flash_41_b200.parallel.symm import AgWorkspace, RsWorkspace, SymmWorkspace  # noqa: E402
 
 NVLINK_GBS = 770.0
 
@@ -108,6 +108,57 @@ def main():
         row.update(fp8_fused_ms=round(f8, 4), fp8_speedup_vs_bf16_baseline=round(nccl / f8, 2))
         rows.append(row)
         del rsw
+    # ---- all-gather -> GEMM: activations row-sharded [M/tp, K], weight column shard [N/tp, K]
+    Nl = N // world
+    wn = torch.randn(Nl, K, device=dev, generator=g) * 0.02
+    wnb, wn8 = wn.bfloat16(), E.quant_fp8_device(wn)
+    for M in (512, 4096, 16384):
+        if M % (world * 128):
+            continue
+        xs = torch.randn(M // world, K, device=dev, generator=g)
+        xsb = xs.bfloat16()
+        agw = AgWorkspace(0, M, K, device=dev)
+        out = torch.zeros(M, Nl, device=dev, dtype=torch.bfloat16)
+
+        def fused():
+            a, _ = agw.shard()
+            a.copy_(xsb)
+            agw.allgather_gemm(wnb, out, st.t)
+        full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+        ref = torch.empty(M, Nl, device=dev, dtype=torch.bfloat16)
+
+        def base():
+            dist.all_gather_into_tensor(full, xsb)
+            torch.matmul(full, wnb.t(), out=ref)
+        tf_, tn = timed(fused), timed(base)
+        base()
+        fused()
+        torch.cuda.synchronize()
+        err = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
+        flops = 2.0 * M * Nl * K
+        link_bytes = M * K * 2 * (world - 1) / world
+        roof_ms = max(flops / (pk["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        row = dict(op="allgather+gemm bf16", M=M, fused_ms=round(tf_, 4), nccl_cublas_ms=round(tn, 4),
+                   speedup=round(tn / tf_, 2), roofline_ms=round(roof_ms, 4), frac_of_roofline=round(roof_ms / tf_, 3),
+                   rel_err=round(err, 5))
+        del agw
+        ag8 = AgWorkspace(2, M, K, device=dev)
+        xg = xs.view(M // world, K // 128, 128)
+        sa = (xg.abs().amax(-1).clamp_min(1e-12) / 448.0).contiguous()
+        xq = (xg / sa[:, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(M // world, K)
+
+        def fused8():
+            a, s_ = ag8.shard()
+            a.copy_(xq)
+            s_.copy_(sa)
+            ag8.allgather_gemm(wn8.q, out, st.t, wn8.s)
+        t8 = timed(fused8)
+        fused8()
+        torch.cuda.synchronize()
+        err8 = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
+        row.update(fp8_fused_ms=round(t8, 4), fp8_speedup_vs_bf16_baseline=round(tn / t8, 2), fp8_rel_err=round(err8, 4))
+        rows.append(row)
+        del ag8
     st.check()
     if rank == 0:
         print(json.dumps({"world": world, "K": K, "N": N, "peaks": pk, "rows": rows}, indent=1), flush=True)

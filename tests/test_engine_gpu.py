@@ -170,3 +170,26 @@ def test_chunked_prefill_with_late_group_and_spec_decode():
     a = dec.step([DecodeSlot(region=i, length=l, anchor=t, seed=9) for i, (l, t) in enumerate(snap)])
     b = dec2.step([DecodeSlot(region=i, length=l, anchor=t, seed=9) for i, (l, t) in enumerate(snap)])
     assert [x[0] for x in a] == [x[0] for x in b]
+
+
+def test_layer_major_prefill_matches_chunk_major():
+    """Sweeping the encoder layer by layer over all chunks (experts converted once per layer) must
+    give the same logits and the same cached state as the chunk-by-chunk order."""
+    from titanic_flash_41_b200.ops import bigpath
+    from titanic_flash_41_b200.serve.prefill import run_prefill
+    cfg = small_config(n_layers=4, kv_source_layers=(0, 1), index_source_layers=(0, 1, 3), late_start=2)
+    W = oracle.init_weights(cfg, 0)
+    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=2048, prefill_widths=(256,)), W)
+    bigpath.attach(eng)
+    g = torch.Generator().manual_seed(5)
+    p = torch.randint(0, cfg.vocab, (900,), generator=g, dtype=torch.int32)
+    a = run_prefill(eng, 0, p, 256, layer_major=False)
+    b = run_prefill(eng, 1, p, 256, layer_major=True)
+    torch.cuda.synchronize()
+    eng.status.check()
+    assert int(a.argmax()) == int(b.argmax())
+    assert float((a - b).abs().max() / a.abs().max()) < 2e-2
+    for li in range(len(eng.layers)):
+        w = eng.win[li]
+        same = (w[0] == w[1]).float().mean()
+        assert same > 0.98, (li, float(same))

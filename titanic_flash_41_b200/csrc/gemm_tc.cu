@@ -27,7 +27,10 @@ constexpr int kStageBytes = (BM + BN) * 128;       // rows of 128 bytes
 constexpr int kAccBufs = 4;                        // TMEM accumulator buffers of BN columns
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = (2 + kEpiWarps) * 32;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kStagingBytes = kEpiWarps * 4096;     // per-warp 32 x 128 B transpose buffers (reduce-scatter stores)
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kStagingBytes;
+constexpr int kCopyPiece = 32768;                  // all-gather role: bytes per bulk copy
+constexpr int kCopyDepth = 3;                      // loads issued ahead of their stores
 
 struct GemmParams {
   int M, N, K;
@@ -51,7 +54,113 @@ struct GemmParams {
   int rs_world, rs_rank, rs_rows;       // rs_rows = M / world (multiple of 128)
   long rs_recv_off;                     // byte offset of this parity's receive area in a workspace
   long rs_flag_off;                     // byte offset of the arrival counters
+  // all-gather form (sequence-parallel activations): A is row-sharded over the ranks.  The last
+  // ag_copy_ctas CTAs pull every rank's shard (rows, then their block scales) from its workspace
+  // into this GPU's gathered buffer with bulk copies, 128 rows at a time, and publish one flag per
+  // 128-row block; the TMA producer of a GEMM CTA waits for the flag of the block it is about to
+  // read.  Blocks are visited own shard first, then rank+1, rank+2, ...
+  const unsigned long long* ag_peers;   // [world] workspace bases (null = A is local)
+  int ag_world, ag_rank, ag_rows;       // ag_rows = M / world (multiple of 128)
+  int ag_copy_ctas;
+  int ag_row_bytes, ag_srow_bytes;      // bytes per row of A and of its scales (0 = none)
+  long ag_shard_off;                    // this parity's shard area in every workspace
+  long ag_gath_off;                     // gathered A, then gathered scales, in the own workspace
+  long ag_flag_off;                     // [world] shard-ready words (peers write), then [M/128] block flags
+  unsigned int ag_epoch;
+  int spin_limit;
 };
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// wait until *p >= want (wrap-safe); false after spin_limit polls or ~1 s
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int want, int spin_limit) {
+  const long long t0 = clock64();
+  for (int spins = 0;; ++spins) {
+    const unsigned int v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if ((int)(v - want) >= 0) return true;
+    if (spins > spin_limit || clock64() - t0 > 2000000000LL) return false;
+  }
+}
+
+// The all-gather role of one CTA: a single thread drives a ring of kStages 32 KB buffers; loads run
+// kCopyDepth pieces ahead of the stores.
+__device__ void ag_copy_role(const GemmParams& p, uint32_t base, uint32_t bar0, int cta, int n_ctas) {
+  if (threadIdx.x != 0) return;
+  unsigned int* flags = reinterpret_cast<unsigned int*>(p.ag_peers[p.ag_rank] + p.ag_flag_off);
+  if (cta == 0) {
+    // our shard was written by earlier work on this stream: tell every rank it may be read
+    for (int r = 0; r < p.ag_world; ++r) {
+      unsigned int* f = reinterpret_cast<unsigned int*>(p.ag_peers[r] + p.ag_flag_off) + p.ag_rank;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ag_epoch) : "memory");
+    }
+  }
+  for (int s = 0; s < kStages; ++s) tc::mbar_init(bar0 + 8u * s, 1);
+  tc::fence_barrier_init();
+  volatile int abort_local = 0;
+  const int tpr = p.ag_rows / BM;
+  uint8_t* gath = reinterpret_cast<uint8_t*>(p.ag_peers[p.ag_rank] + p.ag_gath_off);
+  uint8_t* gath_s = gath + (long)p.M * p.ag_row_bytes;
+  long issued = 0, stored = 0;          // pieces over the whole kernel (ring position / parity)
+  bool ok = true;
+  for (int q = cta; q < p.ag_world * tpr && ok; q += n_ctas) {
+    const int src = (p.ag_rank + q / tpr) % p.ag_world, blk = q % tpr;
+    if (!wait_flag<true>(flags + src, p.ag_epoch, p.spin_limit)) {
+      tf_report(p.status, TF_TIMEOUT, 120, src, q);
+      break;
+    }
+    const uint8_t* shard = reinterpret_cast<const uint8_t*>(p.ag_peers[src] + p.ag_shard_off);
+    // two segments: 128 rows of A, then their scale rows
+    for (int seg = 0; seg < 2 && ok; ++seg) {
+      const long seg_bytes = (long)BM * (seg == 0 ? p.ag_row_bytes : p.ag_srow_bytes);
+      if (seg_bytes == 0) continue;
+      const uint8_t* from = seg == 0 ? shard + (long)blk * seg_bytes
+                                     : shard + (long)p.ag_rows * p.ag_row_bytes + (long)blk * seg_bytes;
+      uint8_t* to = seg == 0 ? gath + ((long)src * p.ag_rows + (long)blk * BM) * p.ag_row_bytes
+                             : gath_s + ((long)src * p.ag_rows + (long)blk * BM) * p.ag_srow_bytes;
+      const int n = (int)((seg_bytes + kCopyPiece - 1) / kCopyPiece);
+      for (int i = 0; i < n + kCopyDepth && ok; ++i) {
+        if (i < n) {
+          const int sl = (int)(issued % kStages);
+          // the store that last used this buffer is kStages pieces back: at most
+          // kStages - kCopyDepth - 1 younger store groups may still be reading shared memory
+          tc::bulk_wait_read<kStages - kCopyDepth - 1>();
+          const uint32_t bytes = (uint32_t)min((long)kCopyPiece, seg_bytes - (long)i * kCopyPiece);
+          tc::mbar_expect_tx(bar0 + 8u * sl, bytes);
+          tc::bulk_g2s(base + sl * kCopyPiece, from + (long)i * kCopyPiece, bytes, bar0 + 8u * sl);
+          ++issued;
+        }
+        const int j = i - kCopyDepth;
+        if (j >= 0) {
+          const int sl = (int)(stored % kStages);
+          if (!(ok = tc::mbar_wait(bar0 + 8u * sl, (uint32_t)((stored / kStages) & 1), &abort_local))) break;
+          const uint32_t bytes = (uint32_t)min((long)kCopyPiece, seg_bytes - (long)j * kCopyPiece);
+          tc::bulk_s2g(to + (long)j * kCopyPiece, base + sl * kCopyPiece, bytes);
+          tc::bulk_commit();
+          ++stored;
+        }
+      }
+    }
+    tc::bulk_wait_all<0>();
+    if (!ok) {
+      tf_report(p.status, TF_TIMEOUT, 121, src, q);
+      break;
+    }
+    tc::fence_proxy_async_global();
+    __threadfence();
+    unsigned int* bf = flags + p.ag_world + (src * tpr + blk);
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bf), "r"(p.ag_epoch) : "memory");
+  }
+  tc::bulk_wait_all<0>();
+}
 
 template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -70,11 +179,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + kStages * kStageBytes + 208);
   unsigned int* rs_done = reinterpret_cast<unsigned int*>(aligned + kStages * kStageBytes + 216);   // [8]
 
+  uint8_t* stage_out = aligned + kStages * kStageBytes + 256;                                        // [8][4096]
+
+  const int n_copy = p.ag_peers ? p.ag_copy_ctas : 0;
+  const int n_gemm = gridDim.x - n_copy;
+  if ((int)blockIdx.x >= n_gemm) {
+    ag_copy_role(p, base, bar0, blockIdx.x - n_gemm, n_copy);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int BK = (KIND == 0) ? 64 : 128;               // elements per 128-byte row
   const int kblocks = (p.K + BK - 1) / BK;
   const int mt = p.tile_expert ? *p.num_m_tiles : (p.M + BM - 1) / BM, nt = p.N / BN;
   const int tiles = mt * nt;
+  // tile -> (row block, column block).  Plain: row blocks fastest (one weight panel stays hot in L2).
+  // All-gather: column blocks fastest and row blocks in arrival order (own shard, rank+1, ...).
+  const int ag_tpr = p.ag_peers ? p.ag_rows / BM : 1;
+  auto tile_m = [&](int tile) {
+    if (!p.ag_peers) return tile % mt;
+    const int mi = tile / nt;
+    return ((p.ag_rank + mi / ag_tpr) % p.ag_world) * ag_tpr + mi % ag_tpr;
+  };
+  auto tile_n = [&](int tile) { return p.ag_peers ? tile % nt : tile / mt; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -102,9 +228,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc::prefetch_tmap(&mapB);
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+      const unsigned int* blk_flags =
+          p.ag_peers ? reinterpret_cast<const unsigned int*>(p.ag_peers[p.ag_rank] + p.ag_flag_off) + p.ag_world
+                     : nullptr;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += n_gemm) {
+        const int m0 = tile_m(tile) * BM, n0 = tile_n(tile) * BN;
         const int nb0 = n0 + (p.tile_expert ? p.tile_expert[tile % mt] * p.N : 0);
+        if (blk_flags) {
+          // rows of this block arrive through the copy CTAs (bulk stores): wait, then order the
+          // TMA reads after what the flag published
+          if (!wait_flag<false>(blk_flags + m0 / BM, p.ag_epoch, p.spin_limit)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc::fence_proxy_async_global();
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -127,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       constexpr uint32_t idesc = (KIND == 0) ? tc::instr_desc(1, 1, BM, BN) : tc::instr_desc(0, 0, BM, BN);
       int it = 0, grp = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += n_gemm) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const bool grp_start = (KIND == 2) || kb == 0;
           const bool grp_end = (KIND == 2) || kb == kblocks - 1;
@@ -164,10 +303,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const int half = ew >> 2;                  // which 64 of the tile's 128 columns
     int grp = 0, tile_iter = -1;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += n_gemm) {
       ++tile_iter;
-      const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+      const int m0 = tile_m(tile) * BM, n0 = tile_n(tile) * BN;
       const int row = m0 + quad * 32 + lane;
+      if (KIND == 2 && p.ag_peers) {
+        // the scale rows of this block come with the gathered rows: wait for the block as well
+        int good = 1;
+        if (lane == 0) {
+          const unsigned int* bf =
+              reinterpret_cast<const unsigned int*>(p.ag_peers[p.ag_rank] + p.ag_flag_off) + p.ag_world + m0 / BM;
+          good = wait_flag<false>(bf, p.ag_epoch, p.spin_limit) ? 1 : 0;
+          if (!good) *abort_flag = 1;
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+      }
       float acc[64];
       if (KIND == 2) {
 #pragma unroll
@@ -210,17 +364,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       if (p.rs_peers) {
         // ---- GEMM -> reduce-scatter: push the tile to the rank that owns these rows
         const int owner = m0 / p.rs_rows;
-        if (ok && row < p.M) {
-          __nv_bfloat16* recv = reinterpret_cast<__nv_bfloat16*>(p.rs_peers[owner] + p.rs_recv_off);
-          uint4* dst = reinterpret_cast<uint4*>(
-              recv + ((long)p.rs_rank * p.rs_rows + (row - owner * p.rs_rows)) * p.N + n0 + half * 64);
+        if (ok) {
+          // transpose the warp's 32 x 64 bf16 block through its private shared-memory buffer so
+          // that each store instruction covers four whole 128-byte row segments of the peer's
+          // memory (16-byte chunks XOR-swizzled by row: conflict-free both ways)
+          uint8_t* buf = stage_out + ew * 4096;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             __nv_bfloat162 h[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
-            dst[i] = *reinterpret_cast<uint4*>(h);
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((i ^ (lane & 7)) << 4)) = *reinterpret_cast<uint4*>(h);
           }
+          __syncwarp();
+          __nv_bfloat16* recv = reinterpret_cast<__nv_bfloat16*>(p.rs_peers[owner] + p.rs_recv_off);
+          const int rbase = m0 + quad * 32;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3), ch = lane & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((ch ^ (rr & 7)) << 4));
+            const int grow = rbase + rr;
+            if (grow < p.M)
+              *reinterpret_cast<uint4*>(recv + ((long)p.rs_rank * p.rs_rows + (grow - owner * p.rs_rows)) * p.N + n0 +
+                                        half * 64 + ch * 8) = v;
+          }
+          __syncwarp();
         }
         __threadfence_system();
         // the last of the eight epilogue warps to finish this tile publishes it (no blocking barrier:
@@ -273,6 +441,13 @@ struct RsConfig {
   int world = 0, rank = 0;
   long recv_off = 0, flag_off = 0;
 } g_rs;   // set by tf_gemm_rs around the launch; plain calls leave it empty
+
+struct AgConfig {
+  const unsigned long long* peers = nullptr;
+  int world = 0, rank = 0, copy_ctas = 0, spin_limit = 0;
+  long shard_off = 0, gath_off = 0;
+  unsigned int epoch = 0;
+} g_ag;   // set by tf_gemm_ag around the launch
 
 // sum the `world` received slots of every 128x128 tile in rank order once all of them arrived
 __global__ void __launch_bounds__(256) rs_reduce_kernel(const unsigned long long* peers, int rank, int world,
@@ -354,8 +529,17 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
   p.rs_peers = g_rs.peers; p.rs_world = g_rs.world; p.rs_rank = g_rs.rank; p.rs_rows = g_rs.world ? M / g_rs.world : 0;
   p.rs_recv_off = g_rs.recv_off; p.rs_flag_off = g_rs.flag_off;
   if (p.rs_peers && (M % (g_rs.world * BM) != 0)) return -1;
+  p.ag_peers = g_ag.peers; p.ag_world = g_ag.world; p.ag_rank = g_ag.rank; p.ag_rows = g_ag.world ? M / g_ag.world : 0;
+  p.ag_copy_ctas = g_ag.copy_ctas; p.ag_row_bytes = K * es; p.ag_srow_bytes = kind == 2 ? (K / 128) * 4 : 0;
+  p.ag_shard_off = g_ag.shard_off; p.ag_gath_off = g_ag.gath_off; p.ag_flag_off = 0; p.ag_epoch = g_ag.epoch;
+  p.spin_limit = g_ag.spin_limit;
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
-  const int grid = tiles < g_sms ? tiles : g_sms;
+  int grid = tiles < g_sms ? tiles : g_sms;
+  if (p.ag_peers) {
+    if (M % (g_ag.world * BM) != 0 || experts > 0 || g_ag.copy_ctas < 1 || g_ag.copy_ctas >= g_sms) return -1;
+    const int gemm_ctas = g_sms - g_ag.copy_ctas;
+    grid = (tiles < gemm_ctas ? tiles : gemm_ctas) + g_ag.copy_ctas;   // every CTA is resident: one per SM
+  }
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -401,4 +585,41 @@ TF_API int tf_gemm_rs(int kind, const void* A, long lda, const void* B, long ldb
                                               (unsigned int)epoch * (unsigned int)world, (__nv_bfloat16*)out, ldo,
                                               spin_limit, (TfStatusWord*)status);
   return (int)cudaGetLastError();
+}
+
+// ---- all-gather -> GEMM.  Workspace (symmetric, same layout on every rank):
+//   [0, 4096)            flags: [world] shard-ready words, then [M/128] block flags
+//   two shard areas      (epoch parity) of M/world rows of A followed by their scale rows
+//   gathered A [M rows], gathered scales [M rows]
+static long ag_shard_bytes(int kind, int M, int K, int world) {
+  const long es = kind == 0 ? 2 : 1;
+  return ((long)(M / world) * (K * es + (kind == 2 ? (K / 128) * 4 : 0)) + 255) / 256 * 256;
+}
+TF_API long tf_gemm_ag_shard_offset(int kind, int M, int K, int world, int epoch) {
+  return 4096 + (long)(epoch & 1) * ag_shard_bytes(kind, M, K, world);
+}
+TF_API long tf_gemm_ag_workspace_bytes(int kind, int M, int K, int world) {
+  const long es = kind == 0 ? 2 : 1;
+  return 4096 + 2 * ag_shard_bytes(kind, M, K, world) + (long)M * (K * es + (kind == 2 ? (K / 128) * 4 : 0)) + 256;
+}
+
+// C[M, N] = allgather_rows(A_shards)[M, K] * B[N, K]^T with B, C local.  The caller has written its
+// M/world rows of A (and, for kind 2, their [rows, K/128] fp32 scales right behind them) at
+// tf_gemm_ag_shard_offset(..., epoch) of its own workspace before this call on the same stream.
+// `epoch` counts calls on this workspace (1, 2, ...).  M/128 must not exceed 1024 - world.
+TF_API int tf_gemm_ag(int kind, const void* B, long ldb, void* C, int ldc, int M, int N, int K, const float* sb,
+                      int ldsb, int out_kind, const void* peers, const void* own_base, int world, int rank,
+                      int epoch, int copy_ctas, int spin_limit, void* status, cudaStream_t stream) {
+  if (world < 1 || M % (world * BM) != 0 || M / BM + world > 1024 || kind == 1) return -1;
+  const long es = kind == 0 ? 2 : 1;
+  g_ag.peers = (const unsigned long long*)peers; g_ag.world = world; g_ag.rank = rank; g_ag.copy_ctas = copy_ctas;
+  g_ag.spin_limit = spin_limit; g_ag.epoch = (unsigned int)epoch;
+  g_ag.shard_off = tf_gemm_ag_shard_offset(kind, M, K, world, epoch);
+  g_ag.gath_off = 4096 + 2 * ag_shard_bytes(kind, M, K, world);
+  const uint8_t* gath = reinterpret_cast<const uint8_t*>(own_base) + g_ag.gath_off;
+  const float* sa = kind == 2 ? reinterpret_cast<const float*>(gath + (long)M * K * es) : nullptr;
+  const int rc = tf_gemm_tc(kind, gath, K, B, ldb, C, ldc, M, N, K, sa, K / 128, sb, ldsb, out_kind, nullptr, nullptr,
+                            0, status, stream);
+  g_ag = AgConfig();
+  return rc;
 }

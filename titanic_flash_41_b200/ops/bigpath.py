@@ -16,6 +16,7 @@ class BigPath:
     def __init__(self, engine):
         self.e = engine
         self.buf = {}
+        self._converted = None      # layer whose experts currently sit in the FP8 staging copy
 
     def _get(self, name, shape, dtype):
         t = self.buf.get(name)
@@ -80,9 +81,12 @@ class BigPath:
         s13 = self._get("s13", (El * 2 * I // 128, d // 128), torch.float32)
         w2 = self._get("w2", (El, d, I), torch.uint8)
         s2 = self._get("s2", (El * d // 128, I // 128), torch.float32)
-        native.call("tf_mxfp4_to_fp8_block", L.ew1, L.es1, w13, s13, El, I, d, 0, 2 * I)
-        native.call("tf_mxfp4_to_fp8_block", L.ew3, L.es3, w13, s13, El, I, d, I, 2 * I)
-        native.call("tf_mxfp4_to_fp8_block", L.ew2, L.es2, w2, s2, El, d, I, 0, d)
+        if self._converted is not L:
+            # consecutive chunks of one layer (layer-major prefill) reuse the converted copy
+            native.call("tf_mxfp4_to_fp8_block", L.ew1, L.es1, w13, s13, El, I, d, 0, 2 * I)
+            native.call("tf_mxfp4_to_fp8_block", L.ew3, L.es3, w13, s13, El, I, d, I, 2 * I)
+            native.call("tf_mxfp4_to_fp8_block", L.ew2, L.es2, w2, s2, El, d, I, 0, d)
+            self._converted = L
         # gather + quantise token rows into the expert-sorted padded matrix
         xp = self._get("xp", (cap, d), torch.uint8)
         xps = self._get("xps", (cap, d // 128), torch.float32)

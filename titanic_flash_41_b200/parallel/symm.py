@@ -95,3 +95,51 @@ class RsWorkspace:
         native.call("tf_gemm_rs", kind, a, a.stride(0), b, b.stride(0), M, N, K, sa, sa.stride(0) if sa is not None else 0,
                     sb, sb.stride(0) if sb is not None else 0, self.peers, self.world, self.rank, self.epoch, out,
                     out.stride(0), self.spin_limit, status)
+
+
+class AgWorkspace:
+    """Workspace of the all-gather -> GEMM kernel for row-sharded activations [M/world, K] per rank.
+
+    ``shard(kind)`` returns views of this call's slot for the rank's rows (and, for FP8, their
+    1x128 scales); fill them, then call ``allgather_gemm``: the kernel's copy CTAs pull every
+    rank's slot over NVLink with bulk copies while its GEMM CTAs multiply the blocks that have
+    already arrived."""
+
+    def __init__(self, kind: int, M: int, K: int, device=None, group: Optional[dist.ProcessGroup] = None,
+                 spin_limit: int = 4_000_000, copy_ctas: int = 16):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.kind, self.M, self.K, self.spin_limit, self.copy_ctas = kind, M, K, spin_limit, copy_ctas
+        nbytes = int(native.lib().tf_gemm_ag_workspace_bytes(kind, M, K, self.world))
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.peers = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64, device=dev)
+        self.epoch = 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)
+
+    def shard(self):
+        """(rows view, scales view or None) of the slot the NEXT allgather_gemm call will publish."""
+        rows = self.M // self.world
+        off = int(native.lib().tf_gemm_ag_shard_offset(self.kind, self.M, self.K, self.world, self.epoch + 1))
+        es = 2 if self.kind == 0 else 1
+        a = self.buf[off:off + rows * self.K * es].view(torch.bfloat16 if self.kind == 0 else torch.float8_e4m3fn)
+        a = a.view(rows, self.K)
+        s = None
+        if self.kind == 2:
+            so = off + rows * self.K
+            s = self.buf[so:so + rows * (self.K // 128) * 4].view(torch.float32).view(rows, self.K // 128)
+        return a, s
+
+    def allgather_gemm(self, b: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+                       sb: Optional[torch.Tensor] = None) -> None:
+        """out[M, N] = allgather(shards)[M, K] @ b[N, K]^T (out bf16 or fp32)."""
+        self.epoch += 1
+        N = b.shape[0]
+        native.call("tf_gemm_ag", self.kind, b, b.stride(0), out, out.stride(0), self.M, N, self.K, sb,
+                    sb.stride(0) if sb is not None else 0, 2 if out.dtype == torch.bfloat16 else 0, self.peers,
+                    self.buf, self.world, self.rank, self.epoch, self.copy_ctas, self.spin_limit, status)

@@ -18,9 +18,57 @@ from ..models.engine import Engine, StepPlan
 from .planner import plan_chunks
 
 
+def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List[int], start: int, late: int,
+                         tail: torch.Tensor, tail_n: int) -> None:
+    """Encoder layers [0, late) layer by layer over ALL chunks of the prompt.
+
+    The residual stream of the whole prompt (n x hidden bf16: 1 GB at 129K tokens) and the current
+    index source's selections stay resident between layers, so each layer's weights are touched
+    once per prompt instead of once per chunk: the routed experts are re-expressed as FP8 for the
+    tensor-core path once per layer, and a layer's dense weights stay in L2 across its chunks.
+    Causality holds because layer l of chunk c only needs layer l's own KV of chunks < c (written
+    earlier in the same sweep) and layer l-1's output of chunk c."""
+    cfg = eng.cfg
+    n = int(toks.shape[0])
+    resid = torch.empty(n, cfg.hidden, dtype=torch.bfloat16, device=eng.dev)
+    offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    plans = [StepPlan.build([(region, start + int(offs[c]), toks[offs[c]:offs[c + 1]].tolist())], logits="last")
+             for c in range(len(sizes))]
+    shapes = [eng.plan_shape(p, cfg.compress_ratio) for p in plans]
+    sel_store: dict = {}
+    for li in range(late):
+        Lw = eng.layers[li]
+        src = Lw.index_source if Lw.kv_source >= 0 else -1
+        for c, T in enumerate(sizes):
+            b = eng._bufs(T)
+            eng.upload_plan(plans[c], b)
+            lo, hi = int(offs[c]), int(offs[c + 1])
+            if src >= 0 and not Lw.is_index_source:
+                b["sel"][src][:T].copy_(sel_store[src][0][lo:hi])
+                b["selcnt"][src][:T].copy_(sel_store[src][1][lo:hi])
+            eng.run(T, b, shapes[c][0], shapes[c][1], None, li, li + 1, x_in=None if li == 0 else resid[lo:hi])
+            # x + pending sublayer output, rounded once to bf16
+            resid[lo:hi].copy_(eng.residual_rows(b, slice(0, T)) if b.get("pending") else b["x"][:T])
+            if Lw.is_index_source:
+                if li not in sel_store:
+                    sel_store.clear()             # followers only ever read the latest source
+                    sel_store[li] = (torch.empty(n, b["sel"][li].shape[1], dtype=b["sel"][li].dtype, device=eng.dev),
+                                     torch.empty(n, dtype=b["selcnt"][li].dtype, device=eng.dev))
+                sel_store[li][0][lo:hi].copy_(b["sel"][li][:T])
+                sel_store[li][1][lo:hi].copy_(b["selcnt"][li][:T])
+    if tail_n > 0:
+        tail[:tail_n].copy_(resid[n - tail_n:])
+    # leave the last chunk's residual in its buffers for a head that follows directly
+    T = sizes[-1]
+    b = eng._bufs(T)
+    b["x"][:T].copy_(resid[n - T:])
+    b["pending"] = False
+
+
 def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, need_logits: bool = True,
                 on_chunk: Optional[Callable[[int], bool]] = None,
-                widths: Optional[Sequence[int]] = None) -> Optional[torch.Tensor]:
+                widths: Optional[Sequence[int]] = None, layer_major: Optional[bool] = None
+                ) -> Optional[torch.Tensor]:
     """Prefill ``tokens`` at positions start.. into ``region``.  Returns fp32 logits of the last
     row (or None when cancelled by ``on_chunk`` returning False)."""
     cfg = eng.cfg
@@ -31,8 +79,15 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
     tail_n = min(n, cfg.window) if late < L else 0
     tail = torch.zeros(max(tail_n, 1), cfg.hidden, dtype=torch.bfloat16, device=eng.dev)
     sizes = plan_chunks(n, tuple(widths) if widths else (chunk,))
+    if layer_major is None:
+        layer_major = len(sizes) > 1 and getattr(eng, "big_moe_full", None) is not None and on_chunk is None
     done = 0
     logits = None
+    if layer_major:
+        _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n)
+        if late == L and need_logits:
+            logits = eng._head(sizes[-1], eng._bufs(sizes[-1]), torch.tensor([sizes[-1] - 1], device=eng.dev))
+        sizes = []
     for T in sizes:
         plan = StepPlan.build([(region, start + done, toks[done:done + T].tolist())], logits="last")
         b = eng._bufs(T)

@@ -1,0 +1,113 @@
+"""Diagnostics that stay out of the serving path unless switched on.
+
+``KernelClock``   times every exported kernel call with CUDA events on the launching stream and
+                  folds them by (part, kernel) — the layer clock of the engine: ``part(name)``
+                  marks forward parts (attention, moe, head...), ``report()`` gives the table a
+                  request's ``timings`` carries (reference: src/layer_clock.rs:45 arm, :135 part,
+                  :148 mark, :99 parts_us; globaltimer marks become event pairs here).
+``Knockout``      skips named kernels so that their cost can be bounded by difference; results are
+                  wrong on purpose while it is active (reference: src/knockout.rs:37-63).
+``RouteCensus``   per-expert routing counts from the router's id tensor
+                  (reference: src/route_census.rs; kernels/core.cu:161 ca_route_census).
+
+Timing serialises nothing by itself, but reading the table synchronises the device once.
+Delay / fault injection on the device is deliberately absent: failures are injected on the host.
+"""
+from __future__ import annotations
+
+import contextlib
+from collections import defaultdict
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from ..ops import native
+
+
+class KernelClock:
+    def __init__(self):
+        self.events: List[Tuple[str, str, torch.cuda.Event, torch.cuda.Event]] = []
+        self._part = "-"
+        self._orig = None
+
+    def part(self, name: str) -> None:
+        self._part = name
+
+    def __enter__(self):
+        self._orig = native.call
+        clock = self
+
+        def timed(name, *args, **kw):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            try:
+                return clock._orig(name, *args, **kw)
+            finally:
+                b.record()
+                clock.events.append((clock._part, name, a, b))
+        native.call = timed
+        return self
+
+    def __exit__(self, *exc):
+        native.call = self._orig
+        self._orig = None
+        return False
+
+    def table(self, by_part: bool = False) -> List[Tuple[str, int, float]]:
+        """[(key, calls, total_ms)] sorted by time; one device synchronisation."""
+        torch.cuda.synchronize()
+        tot: Dict[str, List[float]] = defaultdict(lambda: [0, 0.0])
+        for part, name, a, b in self.events:
+            k = f"{part}/{name}" if by_part else name
+            tot[k][0] += 1
+            tot[k][1] += a.elapsed_time(b)
+        return sorted(((k, int(v[0]), v[1]) for k, v in tot.items()), key=lambda r: -r[2])
+
+    def report(self, by_part: bool = False, top: int = 20) -> str:
+        rows = self.table(by_part)
+        total = sum(r[2] for r in rows) or 1.0
+        out = [f"{'kernel':34s} {'calls':>7s} {'ms':>10s} {'share':>7s}"]
+        for k, n, ms in rows[:top]:
+            out.append(f"{k:34s} {n:7d} {ms:10.3f} {100 * ms / total:6.1f}%")
+        out.append(f"{'total':34s} {sum(r[1] for r in rows):7d} {total:10.3f}")
+        return "\n".join(out)
+
+
+class Knockout(contextlib.AbstractContextManager):
+    """``with Knockout({"tf_index_scores", "tf_topk_select"}): ...`` skips those launches."""
+
+    def __init__(self, names: Iterable[str]):
+        self.names, self._orig, self.skipped = set(names), None, 0
+
+    def __enter__(self):
+        self._orig = native.call
+        ko = self
+
+        def gated(name, *args, **kw):
+            if name in ko.names:
+                ko.skipped += 1
+                return None
+            return ko._orig(name, *args, **kw)
+        native.call = gated
+        return self
+
+    def __exit__(self, *exc):
+        native.call = self._orig
+        return False
+
+
+class RouteCensus:
+    """Accumulates how often each expert was chosen."""
+
+    def __init__(self, n_experts: int, device="cpu"):
+        self.counts = torch.zeros(n_experts, dtype=torch.int64, device=device)
+
+    def add(self, ids: torch.Tensor) -> None:
+        flat = ids.reshape(-1).to(self.counts.device, torch.int64)
+        self.counts += torch.bincount(flat[flat >= 0], minlength=self.counts.numel())[: self.counts.numel()]
+
+    def summary(self) -> dict:
+        c = self.counts.float()
+        mean = float(c.mean()) or 1.0
+        return {"total": int(c.sum()), "max_over_mean": float(c.max()) / mean, "unused": int((c == 0).sum()),
+                "top": [int(i) for i in torch.topk(c, min(8, c.numel())).indices]}
