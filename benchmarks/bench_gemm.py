@@ -37,6 +37,12 @@ def main():
         med, best = time_cuda(lambda: native.call("tf_gemm_tc", 2, aq, K, fw.q, K, c, N, M, N, K, sa, K // 128, fw.s, K // 128, 2, None, None, 0, st.t))
         print(f"{shp} tcgen05-fp8bs {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s (best {fl / best / 1e9:.1f}) "
               f"= {fl / med / 1e9 / pk['bf16_tflops']:.2f} x {pk['source']} bf16 peak")
+        native.lib().tf_gemm_tc_force_tile(128)
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 0, a, K, b, K, c, N, M, N, K, None, 0, None, 0, 2, None, None, 0, st.t))
+        print(f"{shp} tcgen05-bf16 128x128 tiles  {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s")
+        med, best = time_cuda(lambda: native.call("tf_gemm_tc", 2, aq, K, fw.q, K, c, N, M, N, K, sa, K // 128, fw.s, K // 128, 2, None, None, 0, st.t))
+        print(f"{shp} tcgen05-fp8bs 128x128 tiles {med:8.3f} ms  {fl / med / 1e9:8.1f} TFLOP/s")
+        native.lib().tf_gemm_tc_force_tile(0)
         st.check()
 
 

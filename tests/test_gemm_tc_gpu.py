@@ -13,7 +13,8 @@ def _rel(a, b):
     return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 512), (300, 256, 1024), (1000, 384, 4096)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 512), (300, 256, 1024), (1000, 384, 4096),
+                                   (4096, 2048, 512), (5000, 1024, 256)])   # the last two take 128x256 tiles
 def test_gemm_bf16(M, N, K):
     torch.manual_seed(0)
     a = torch.randn(M, K, device=DEV).bfloat16()
@@ -27,7 +28,7 @@ def test_gemm_bf16(M, N, K):
         assert _rel(c, a.float() @ b.float().t()) < 5e-3
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (200, 256, 1024), (1024, 512, 4096)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (200, 256, 1024), (1024, 512, 4096), (4736, 1024, 1024)])
 def test_gemm_fp8_block_scaled(M, N, K):
     torch.manual_seed(1)
     x = torch.randn(M, K, device=DEV)
@@ -56,7 +57,8 @@ def _one_rank_workspace(nbytes):
     return buf, torch.tensor([buf.data_ptr()], dtype=torch.int64, device=DEV)
 
 
-@pytest.mark.parametrize("kind,M,N,K", [(0, 512, 256, 1024), (2, 384, 128, 2048), (0, 2048, 384, 512)])
+@pytest.mark.parametrize("kind,M,N,K", [(0, 512, 256, 1024), (2, 384, 128, 2048), (0, 2048, 384, 512),
+                                        (2, 4864, 1024, 512)])
 def test_allgather_gemm_single_rank(kind, M, N, K):
     """The all-gather form with one rank: copy CTAs move the shard into the gathered buffer with
     bulk copies, GEMM CTAs wait for each 128-row block.  Two calls exercise both slot parities."""
@@ -92,7 +94,11 @@ def test_gemm_reduce_scatter_single_rank():
     """Reduce-scatter form with one rank: staged (transposed) tile stores into the receive slot and
     the owner-side sum must reproduce the plain GEMM."""
     torch.manual_seed(3)
-    M, N, K = 512, 256, 512
+    _rs_case(512, 256, 512)
+    _rs_case(4864, 1024, 256)          # 128x256 tiles: two owner-side counters per tile
+
+
+def _rs_case(M, N, K):
     L = native.lib()
     buf, peers = _one_rank_workspace(L.tf_gemm_rs_workspace_bytes(M, N, 1))
     a = torch.randn(M, K, device=DEV).bfloat16()

@@ -21,14 +21,12 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128;
-constexpr int kStages = 6;
-constexpr int kStageBytes = (BM + BN) * 128;       // rows of 128 bytes
-constexpr int kAccBufs = 4;                        // TMEM accumulator buffers of BN columns
+constexpr int BM = 128;
+constexpr int kRingBytes = 6 * 32768;              // operand ring: 6 x 32 KB (BN 128) or 4 x 48 KB (BN 256)
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = (2 + kEpiWarps) * 32;
 constexpr int kStagingBytes = kEpiWarps * 4096;     // per-warp 32 x 128 B transpose buffers (reduce-scatter stores)
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kStagingBytes;
+constexpr int kSmemBytes = kRingBytes + 1024 /*align*/ + 256 /*barriers*/ + kStagingBytes;
 constexpr int kCopyPiece = 32768;                  // all-gather role: bytes per bulk copy
 constexpr int kCopyDepth = 3;                      // loads issued ahead of their stores
 
@@ -91,7 +89,8 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int wa
   }
 }
 
-// The all-gather role of one CTA: a single thread drives a ring of kStages 32 KB buffers; loads run
+constexpr int kCopyStages = 6;
+// The all-gather role of one CTA: a single thread drives a ring of kCopyStages 32 KB buffers; loads run
 // kCopyDepth pieces ahead of the stores.
 __device__ void ag_copy_role(const GemmParams& p, uint32_t base, uint32_t bar0, int cta, int n_ctas) {
   if (threadIdx.x != 0) return;
@@ -103,7 +102,7 @@ __device__ void ag_copy_role(const GemmParams& p, uint32_t base, uint32_t bar0, 
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ag_epoch) : "memory");
     }
   }
-  for (int s = 0; s < kStages; ++s) tc::mbar_init(bar0 + 8u * s, 1);
+  for (int s = 0; s < kCopyStages; ++s) tc::mbar_init(bar0 + 8u * s, 1);
   tc::fence_barrier_init();
   volatile int abort_local = 0;
   const int tpr = p.ag_rows / BM;
@@ -129,10 +128,10 @@ __device__ void ag_copy_role(const GemmParams& p, uint32_t base, uint32_t bar0, 
       const int n = (int)((seg_bytes + kCopyPiece - 1) / kCopyPiece);
       for (int i = 0; i < n + kCopyDepth && ok; ++i) {
         if (i < n) {
-          const int sl = (int)(issued % kStages);
-          // the store that last used this buffer is kStages pieces back: at most
-          // kStages - kCopyDepth - 1 younger store groups may still be reading shared memory
-          tc::bulk_wait_read<kStages - kCopyDepth - 1>();
+          const int sl = (int)(issued % kCopyStages);
+          // the store that last used this buffer is kCopyStages pieces back: at most
+          // kCopyStages - kCopyDepth - 1 younger store groups may still be reading shared memory
+          tc::bulk_wait_read<kCopyStages - kCopyDepth - 1>();
           const uint32_t bytes = (uint32_t)min((long)kCopyPiece, seg_bytes - (long)i * kCopyPiece);
           tc::mbar_expect_tx(bar0 + 8u * sl, bytes);
           tc::bulk_g2s(base + sl * kCopyPiece, from + (long)i * kCopyPiece, bytes, bar0 + 8u * sl);
@@ -140,8 +139,8 @@ __device__ void ag_copy_role(const GemmParams& p, uint32_t base, uint32_t bar0, 
         }
         const int j = i - kCopyDepth;
         if (j >= 0) {
-          const int sl = (int)(stored % kStages);
-          if (!(ok = tc::mbar_wait(bar0 + 8u * sl, (uint32_t)((stored / kStages) & 1), &abort_local))) break;
+          const int sl = (int)(stored % kCopyStages);
+          if (!(ok = tc::mbar_wait(bar0 + 8u * sl, (uint32_t)((stored / kCopyStages) & 1), &abort_local))) break;
           const uint32_t bytes = (uint32_t)min((long)kCopyPiece, seg_bytes - (long)j * kCopyPiece);
           tc::bulk_s2g(to + (long)j * kCopyPiece, base + sl * kCopyPiece, bytes);
           tc::bulk_commit();
@@ -162,10 +161,16 @@ __device__ void ag_copy_role(const GemmParams& p, uint32_t base, uint32_t bar0, 
   tc::bulk_wait_all<0>();
 }
 
-template <int KIND>
+template <int KIND, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const GemmParams p) {
+  // BN = 128: six 32 KB stages, four TMEM buffers; BN = 256: four 48 KB stages, two TMEM buffers
+  // (a third less operand traffic from L2 per FLOP)
+  constexpr int kStages = (BN == 128) ? 6 : 4;
+  constexpr int kStageBytes = (BM + BN) * 128;
+  constexpr int kAccBufs = 512 / BN;
+  constexpr int CH = BN / 2;                               // output columns per epilogue warp
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = tc::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;            // swizzled tiles need 1024-byte alignment
@@ -322,15 +327,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           break;
         }
       }
-      float acc[64];
+      float acc[CH];
       if (KIND == 2) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        for (int i = 0; i < CH; ++i) acc[i] = 0.f;
       }
       const int groups = (KIND == 2) ? kblocks : 1;
       const float* sa_row = (KIND == 2 && row < p.M) ? p.sa + (long)row * p.ldsa : nullptr;
       const int nb0 = n0 + (p.tile_expert ? p.tile_expert[tile % mt] * p.N : 0);
-      const float* sb_row = (KIND == 2) ? p.sb + (long)(nb0 >> 7) * p.ldsb : nullptr;
+      const float* sb_row = (KIND == 2) ? p.sb + (long)((nb0 + half * CH) >> 7) * p.ldsb : nullptr;
       float s_next = (KIND == 2) ? (sa_row ? sa_row[0] : 0.f) * sb_row[0] : 1.f;
       for (int g = 0; g < groups && ok; ++g, ++grp) {
         const int buf = grp % kAccBufs;
@@ -339,25 +344,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (KIND == 2 && g + 1 < groups) s_next = (sa_row ? sa_row[g + 1] : 0.f) * sb_row[g + 1];
         if (!(ok = tc::mbar_wait(tfull(buf), gph, abort_flag))) break;
         tc::tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + half * 64;
-        uint32_t v0[32], v1[32];
-        tc::tmem_ld32(taddr, v0);
-        tc::tmem_ld32(taddr + 32, v1);
-        tc::tmem_ld_wait();
-        tc::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(tempty(buf));
-        if (KIND == 2) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + half * CH;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc[i] = fmaf(s, __uint_as_float(v0[i]), acc[i]);
-            acc[32 + i] = fmaf(s, __uint_as_float(v1[i]), acc[32 + i]);
+        for (int c = 0; c < CH; c += 64) {
+          uint32_t v0[32], v1[32];
+          tc::tmem_ld32(taddr + c, v0);
+          tc::tmem_ld32(taddr + c + 32, v1);
+          tc::tmem_ld_wait();
+          if (c + 64 >= CH) {
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tempty(buf));
           }
-        } else {
+          if (KIND == 2) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc[i] = __uint_as_float(v0[i]);
-            acc[32 + i] = __uint_as_float(v1[i]);
+            for (int i = 0; i < 32; ++i) {
+              acc[c + i] = fmaf(s, __uint_as_float(v0[i]), acc[c + i]);
+              acc[c + 32 + i] = fmaf(s, __uint_as_float(v1[i]), acc[c + 32 + i]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              acc[c + i] = __uint_as_float(v0[i]);
+              acc[c + 32 + i] = __uint_as_float(v1[i]);
+            }
           }
         }
       }
@@ -369,26 +379,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           // that each store instruction covers four whole 128-byte row segments of the peer's
           // memory (16-byte chunks XOR-swizzled by row: conflict-free both ways)
           uint8_t* buf = stage_out + ew * 4096;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            __nv_bfloat162 h[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((i ^ (lane & 7)) << 4)) = *reinterpret_cast<uint4*>(h);
-          }
-          __syncwarp();
           __nv_bfloat16* recv = reinterpret_cast<__nv_bfloat16*>(p.rs_peers[owner] + p.rs_recv_off);
           const int rbase = m0 + quad * 32;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + (lane >> 3), ch = lane & 7;
-            const uint4 v = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((ch ^ (rr & 7)) << 4));
-            const int grow = rbase + rr;
-            if (grow < p.M)
-              *reinterpret_cast<uint4*>(recv + ((long)p.rs_rank * p.rs_rows + (grow - owner * p.rs_rows)) * p.N + n0 +
-                                        half * 64 + ch * 8) = v;
+          for (int c = 0; c < CH; c += 64) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                h[j] = __floats2bfloat162_rn(acc[c + 8 * i + 2 * j], acc[c + 8 * i + 2 * j + 1]);
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((i ^ (lane & 7)) << 4)) = *reinterpret_cast<uint4*>(h);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), ch = lane & 7;
+              const uint4 v = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((ch ^ (rr & 7)) << 4));
+              const int grow = rbase + rr;
+              if (grow < p.M)
+                *reinterpret_cast<uint4*>(recv + ((long)p.rs_rank * p.rs_rows + (grow - owner * p.rs_rows)) * p.N + n0 +
+                                          half * CH + c + ch * 8) = v;
+            }
+            __syncwarp();
           }
-          __syncwarp();
         }
         __threadfence_system();
         // the last of the eight epilogue warps to finish this tile publishes it (no blocking barrier:
@@ -401,21 +415,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             __threadfence_system();
             if (ok) {
               unsigned int* cnt = reinterpret_cast<unsigned int*>(p.rs_peers[owner] + p.rs_flag_off) +
-                                  ((m0 - owner * p.rs_rows) / BM) * (p.N / BN) + n0 / BN;
-              asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+                                  ((m0 - owner * p.rs_rows) / BM) * (p.N / 128) + n0 / 128;
+              for (int j = 0; j < BN / 128; ++j)      // the owner sums 128-column tiles
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt + j) : "memory");
             }
           }
         }
       } else if (ok && row < p.M) {
-        const long off = (long)row * p.ldc + n0 + half * 64;
+        const long off = (long)row * p.ldc + n0 + half * CH;
         if (p.out_kind == 0) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + off);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+          for (int i = 0; i < CH / 4; ++i) dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
         } else {
           uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + off);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < CH / 8; ++i) {
             __nv_bfloat162 h[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
@@ -427,7 +442,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   }
   tc::tc_fence_before();
   __syncthreads();
-  if (*abort_flag && threadIdx.x == 0) tf_report(p.status, TF_TIMEOUT, 100 + KIND, blockIdx.x, 0);
+  if (*abort_flag && threadIdx.x == 0) tf_report(p.status, TF_TIMEOUT, 100 + KIND, blockIdx.x, BN);
   if (warp == 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, kAccBufs * BN);
@@ -435,6 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 }
 
 int g_sms = 0;
+int g_force_bn = 0;   // tests: 128 pins the small tile
 
 struct RsConfig {
   const unsigned long long* peers = nullptr;
@@ -455,7 +471,7 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const unsigned long long
                                                         unsigned int want, __nv_bfloat16* out, int ldo,
                                                         int spin_limit, TfStatusWord* st) {
   __shared__ int s_fail;
-  const int nt = N / BN, tile = blockIdx.x, mt_i = tile / nt, nt_i = tile % nt;
+  const int nt = N / 128, tile = blockIdx.x, mt_i = tile / nt, nt_i = tile % nt;
   const unsigned int* cnt = reinterpret_cast<const unsigned int*>(peers[rank] + flag_off) + tile;
   if (threadIdx.x == 0) {
     s_fail = 0;
@@ -476,8 +492,8 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const unsigned long long
   if (s_fail) return;
   const __nv_bfloat16* recv = reinterpret_cast<const __nv_bfloat16*>(peers[rank] + recv_off);
   // 128 x 128 tile: 256 threads x (8 columns x 8 rows-strided)
-  for (int i = threadIdx.x; i < BM * (BN / 8); i += blockDim.x) {
-    const int r = mt_i * BM + i / (BN / 8), c = nt_i * BN + (i % (BN / 8)) * 8;
+  for (int i = threadIdx.x; i < BM * (128 / 8); i += blockDim.x) {
+    const int r = mt_i * BM + i / (128 / 8), c = nt_i * 128 + (i % (128 / 8)) * 8;
     if (r >= rows) continue;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int src = 0; src < world; ++src) {
@@ -508,20 +524,22 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
                       const int* tile_expert, const int* num_m_tiles, int experts, void* status,
                       cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (N % BN != 0 || (kind == 0 ? K % 64 : K % 128) != 0) return -1;
+  if (N % 128 != 0 || (kind == 0 ? K % 64 : K % 128) != 0) return -1;
   if (out_kind != 0 && out_kind != 2) return -1;
   if ((out_kind == 0 ? ldc % 4 : ldc % 8) != 0) return -1;
   if (kind == 2 && (!sa || !sb)) return -1;
   CUtensorMap ma, mb;
   const int es = kind == 0 ? 2 : 1;
   const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  if (!tc::make_map_2d(&ma, A, dt, es, M, K, (uint64_t)lda * es, BM)) return -2;
-  if (!tc::make_map_2d(&mb, B, dt, es, (uint64_t)N * (experts > 0 ? experts : 1), K, (uint64_t)ldb * es, BN)) return -2;
   if (!g_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
   }
+  // 128x256 tiles once they still fill the machine; 128x128 otherwise
+  const int BN = (N % 256 == 0 && (long)((M + BM - 1) / BM) * (N / 256) >= g_sms && g_force_bn != 128) ? 256 : 128;
+  if (!tc::make_map_2d(&ma, A, dt, es, M, K, (uint64_t)lda * es, BM)) return -2;
+  if (!tc::make_map_2d(&mb, B, dt, es, (uint64_t)N * (experts > 0 ? experts : 1), K, (uint64_t)ldb * es, BN)) return -2;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.kind = kind; p.sa = sa; p.ldsa = ldsa; p.sb = sb; p.ldsb = ldsb;
   p.C = C; p.ldc = ldc; p.out_kind = out_kind; p.status = (TfStatusWord*)status;
@@ -542,21 +560,30 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
   }
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<0, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<1, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<2, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<0, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<1, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<2, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     attr_set = true;
   }
-  if (kind == 0) gemm_tc_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
-  else if (kind == 1) gemm_tc_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
-  else gemm_tc_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+  if (BN == 128) {
+    if (kind == 0) gemm_tc_kernel<0, 128><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    else if (kind == 1) gemm_tc_kernel<1, 128><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    else gemm_tc_kernel<2, 128><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+  } else {
+    if (kind == 0) gemm_tc_kernel<0, 256><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    else if (kind == 1) gemm_tc_kernel<1, 256><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    else gemm_tc_kernel<2, 256><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+  }
   return (int)cudaGetLastError();
 }
 
 // bytes of the symmetric workspace of the GEMM -> reduce-scatter form: two receive areas (epoch
 // parity) of [world][M/world][N] bf16 plus the arrival counters
 TF_API long tf_gemm_rs_flag_bytes(int M, int N, int world) {
-  return ((long)(M / world / BM) * (N / BN) * 4 + 255) / 256 * 256;
+  return ((long)(M / world / BM) * (N / 128) * 4 + 255) / 256 * 256;
 }
 TF_API long tf_gemm_rs_workspace_bytes(int M, int N, int world) {
   return tf_gemm_rs_flag_bytes(M, N, world) + 2L * M * N * 2;
@@ -569,7 +596,7 @@ TF_API long tf_gemm_rs_workspace_bytes(int M, int N, int world) {
 TF_API int tf_gemm_rs(int kind, const void* A, long lda, const void* B, long ldb, int M, int N, int K,
                       const float* sa, int ldsa, const float* sb, int ldsb, const void* peers, int world,
                       int rank, int epoch, void* out, int ldo, int spin_limit, void* status, cudaStream_t stream) {
-  if (world < 1 || M % (world * BM) != 0 || N % BN != 0 || (ldo % 8) != 0) return -1;
+  if (world < 1 || M % (world * BM) != 0 || N % 128 != 0 || (ldo % 8) != 0) return -1;
   const long flag_bytes = tf_gemm_rs_flag_bytes(M, N, world);
   g_rs.peers = (const unsigned long long*)peers; g_rs.world = world; g_rs.rank = rank;
   g_rs.flag_off = 0;
@@ -580,7 +607,7 @@ TF_API int tf_gemm_rs(int kind, const void* A, long lda, const void* B, long ldb
   g_rs = RsConfig();
   if (rc != 0) return rc;
   const int rows = M / world;
-  const int tiles = (rows / BM) * (N / BN);
+  const int tiles = (rows / BM) * (N / 128);
   rs_reduce_kernel<<<tiles, 256, 0, stream>>>((const unsigned long long*)peers, rank, world, rows, N, recv_off, 0,
                                               (unsigned int)epoch * (unsigned int)world, (__nv_bfloat16*)out, ldo,
                                               spin_limit, (TfStatusWord*)status);
@@ -622,4 +649,10 @@ TF_API int tf_gemm_ag(int kind, const void* B, long ldb, void* C, int ldc, int M
                             0, status, stream);
   g_ag = AgConfig();
   return rc;
+}
+
+// tests / benchmarks: 128 pins the 128x128 tile, 0 restores the automatic choice
+TF_API int tf_gemm_tc_force_tile(int bn) {
+  g_force_bn = bn;
+  return 0;
 }
