@@ -97,6 +97,53 @@ def main():
     toks_all = [None] * world
     dist.all_gather_object(toks_all, flat)
     assert all(t == toks_all[0] for t in toks_all), "ranks committed different tokens"
+    # ---- 5. tensor-core GEMMs fused with reduce-scatter / all-gather, and the expert-parallel layer
+    from titanic_flash_41_b200.parallel.ep import EpMoE
+    from titanic_flash_41_b200.parallel.symm import AgWorkspace, RsWorkspace
+    M, Nn, Kl = 256 * world, 256, 512
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    xa = torch.randn(M, Kl, device=dev, generator=g).bfloat16()
+    wb = (torch.randn(Nn, Kl, device=dev, generator=g) * 0.05).bfloat16()
+    rsw = RsWorkspace(M, Nn, device=dev)
+    for _ in range(3):
+        out = torch.zeros(M // world, Nn, device=dev, dtype=torch.bfloat16)
+        rsw.gemm_reduce_scatter(0, xa, wb, out, st.t)
+        full = (xa.float() @ wb.float().t()).bfloat16()
+        want = torch.empty(M // world, Nn, device=dev, dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(want, full)
+        torch.cuda.synchronize()
+        st.check()
+        assert (out.float() - want.float()).abs().max() <= 0.02 * want.float().abs().max()
+    agw = AgWorkspace(0, M, Kl, device=dev, copy_ctas=4)
+    for _ in range(3):
+        shard = torch.randn(M // world, Kl, device=dev, generator=g).bfloat16()
+        a_view, _ = agw.shard()
+        a_view.copy_(shard)
+        out = torch.zeros(M, Nn, device=dev, dtype=torch.bfloat16)
+        agw.allgather_gemm(wb, out, st.t)
+        full = torch.empty(M, Kl, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, shard)
+        torch.cuda.synchronize()
+        st.check()
+        want = full.float() @ wb.float().t()
+        assert (out.float() - want).abs().max() <= 0.02 * want.abs().max()
+    say("gemm + reduce-scatter / all-gather ok")
+    d, I, Eg, k, Tl = 512, 256, 8 * world, 2, 40 + rank
+    El = Eg // world
+    q = [E.quant_mxfp4_device(torch.randn(El, n, kk, device=dev, generator=g) * 0.06)
+         for n, kk in ((I, d), (I, d), (d, I))]
+    moe = EpMoE(d, I, Eg, k, 64, q[0][0], q[0][1], q[1][0], q[1][1], q[2][0], q[2][1], device=dev)
+    for _ in range(2):
+        x = torch.randn(Tl, d, device=dev, generator=g).bfloat16()
+        ids = torch.stack([torch.randperm(Eg, device=dev, generator=g)[:k] for _ in range(Tl)]).int().contiguous()
+        wts = torch.rand(Tl, k, device=dev, generator=g).contiguous()
+        out = torch.zeros(Tl, d, device=dev, dtype=torch.bfloat16)
+        moe.forward(x, ids, wts, out, st.t)
+        want = moe.forward_nccl(x, ids, wts, st.t)
+        torch.cuda.synchronize()
+        st.check()
+        assert float((out.float() - want.float()).norm() / want.float().norm()) < 1e-2
+    say("expert-parallel dispatch / combine ok")
     dist.barrier()
     if rank == 0:
         print("MGPU_OK", world, errs, flush=True)
