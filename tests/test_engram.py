@@ -1,0 +1,78 @@
+"""Engram hash history (CPU) and device ops (GPU)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from titanic_flash_41_b200.models import engram as EG
+
+
+def test_hash_history_is_causal_and_transactional():
+    md = EG.HashMetadata.synthetic(1000, seed=1, image_token=999)
+    h = EG.HashHistory(lineage=7)
+    toks = [5, 17, 300, 42, 8, 999, 11, 12, 13, 14]
+    whole = h.prepare(toks, md)
+    assert whole.rows.shape == (10, 2, 24)
+    # every id falls inside its head's slice of the table
+    for t in range(2):
+        for j in range(24):
+            lo = int(md.offsets[t][j])
+            assert ((whole.rows[:, t, j] >= lo) & (whole.rows[:, t, j] < lo + int(md.primes[t][j]))).all()
+    # committing a prefix and hashing the rest reproduces the same rows (speculative acceptance)
+    spec = h.prepare(toks[:4], md)
+    h.commit(spec, 3)
+    assert h.position == 3 and h.generation == 1
+    rest = h.prepare(toks[3:], md)
+    assert np.array_equal(rest.rows, whole.rows[3:])
+    with pytest.raises(ValueError, match="stale"):
+        h.commit(spec, 1)
+    # rows whose window touches an image token only depend on the tokens after it
+    other = list(toks)
+    other[4] = 77
+    h2 = EG.HashHistory(lineage=9)
+    b2 = h2.prepare(other, md)
+    assert np.array_equal(b2.rows[9], whole.rows[9]) and not np.array_equal(b2.rows[4], whole.rows[4])
+    assert np.array_equal(b2.rows[6][:, :8], whole.rows[6][:, :8])      # bigram of (11, image) is blocked -> pad
+    # padded launch: padding rows cannot be committed
+    pad = h.prepare_padded(toks[3:5] + [md.pad_token] * 3, 2, md)
+    assert len(pad.tokens) == 2 and pad.rows.shape[0] == 5
+    with pytest.raises(ValueError):
+        h.commit(pad, 3)
+
+
+def test_row_format_round_trip(tmp_path):
+    v = torch.randn(50, 256) * 3
+    packed = EG.pack_rows(v)
+    assert packed.shape == (50, 264)
+    assert (EG.unpack_rows(packed) - v).abs().max() < 0.07 * v.abs().max()
+    p = os.path.join(str(tmp_path), "t.bin")
+    EG.write_table(p, packed, row_start=100)
+    back, start = EG.read_table(p)
+    assert start == 100 and torch.equal(back, packed)
+    with open(p, "r+b") as f:
+        f.truncate(4096 + 10 * 264)
+    with pytest.raises(ValueError, match="truncated"):
+        EG.read_table(p)
+
+
+@pytest.mark.gpu
+def test_device_lookup_and_gate_match_references():
+    dev = "cuda"
+    v = torch.randn(300, 256) * 2
+    packed = EG.pack_rows(v)
+    tab = EG.EngramTable(packed[100:200], 100, dev)
+    ids = torch.tensor([100, 150, 199, 99, 200, 5], dtype=torch.int64)
+    got = tab.lookup(ids).float().cpu()
+    want = EG.unpack_rows(packed)[ids].bfloat16().float()
+    want[3:] = 0                                            # not owned by this rank
+    assert torch.equal(got, want)
+    g = torch.Generator().manual_seed(0)
+    r, m, d = 9, 4, 1024
+    x = torch.randn(r, m, d, generator=g).bfloat16()
+    kv = torch.randn(r, m + 1, d, generator=g).bfloat16()
+    qw = (1 + 0.1 * torch.randn(m, d, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(m, d, generator=g)).bfloat16()
+    out = EG.gate(x.to(dev), kv.to(dev), qw.to(dev), kw.to(dev), 1e-6).float().cpu()
+    ref = EG.gate_reference(x.float(), kv.float(), qw.float(), kw.float(), 1e-6)
+    assert (out - ref).abs().max() < 0.03
