@@ -62,3 +62,43 @@ def test_vision_tower_matches_oracle():
     assert got.shape == want.shape == (3 * (4 + 1) + 2, d_model)
     rel = float((got - want).norm() / want.norm())
     assert rel < 0.03, rel
+
+
+def test_media_expansion_and_identity():
+    import base64
+    from PIL import Image
+    from titanic_flash_41_b200.api import media as M
+    buf = io.BytesIO()
+    Image.fromarray(np.full((600, 600, 3), 200, dtype=np.uint8)).save(buf, format="PNG")
+    uri = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    cache = VI.ImageCache()
+    pm = M.expand([5, 900, 6, 900, 7], [uri, uri], marker_id=900, image_token_id=901, cache=cache)
+    n = pm.images[0].plan.tokens
+    assert len(pm.tokens) == 3 + 2 * n and pm.tokens[1] == 901 and pm.offsets == [(1, n), (2 + n, n)]
+    assert cache.hits == 1 and len(pm.identity) == 64
+    assert M.expand([5], [], 900, 901).identity == ""
+    for bad in ("http://example.com/x.png", "data:image/png;base64,@@@"):
+        with pytest.raises(M.MediaError):
+            M.expand([900], [bad], 900, 901)
+    with pytest.raises(M.MediaError, match="disagree"):
+        M.expand([5], [uri], 900, 901)
+
+
+@pytest.mark.gpu
+def test_prefill_with_image_span_embeddings():
+    """Replacing embeddings through ``embeds`` with the tokens' own embeddings is a no-op; other rows change the logits."""
+    from tests.test_engine_gpu import small_config
+    from titanic_flash_41_b200.config import EngineConfig
+    from titanic_flash_41_b200.models import engine as E, oracle
+    from titanic_flash_41_b200.serve.prefill import run_prefill
+    cfg = small_config()
+    W = oracle.init_weights(cfg, 0)
+    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(64,)), W)
+    p = torch.randint(0, cfg.vocab, (150,), generator=torch.Generator().manual_seed(1), dtype=torch.int32)
+    base = run_prefill(eng, 0, p, 64)
+    offs = torch.arange(70, 90)
+    own = eng.embed_w[p[70:90].long().to(eng.dev)]
+    same = run_prefill(eng, 1, p, 64, embeds=(offs, own))
+    assert torch.equal(base, same)
+    other = run_prefill(eng, 1, p, 64, embeds=(offs, own.flip(0)))
+    assert not torch.equal(base, other) and torch.isfinite(other).all()

@@ -681,8 +681,8 @@ class Engine:
         return self.run(T, b, nmax, rpg, rows)
 
     def run(self, T: int, b: dict, nmax: int, rpg: int, logit_rows: Optional[torch.Tensor],
-            layer_lo: int = 0, layer_hi: Optional[int] = None, x_in: Optional[torch.Tensor] = None
-            ) -> Optional[torch.Tensor]:
+            layer_lo: int = 0, layer_hi: Optional[int] = None, x_in: Optional[torch.Tensor] = None,
+            x_patch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
         """Launch layers [layer_lo, layer_hi) on rows whose metadata already sits in ``b['meta']``
         (no host work: this is what a CUDA graph captures).  ``x_in`` replaces the embedding as
         the input residual (late-group replay); the head runs only when the last layer does."""
@@ -690,6 +690,9 @@ class Engine:
         layer_hi = len(self.layers) if layer_hi is None else layer_hi
         if x_in is None:
             native.call("tf_embed", b["meta"][0], self.embed_w, b["x"], T, cfg.hidden, cfg.vocab, self.status.t)
+            if x_patch is not None:
+                # rows that stand for image tokens take the vision tower's features instead
+                b["x"].index_copy_(0, x_patch[0], x_patch[1].to(b["x"].dtype))
         else:
             b["x"][:T].copy_(x_in)
         for li in range(layer_lo, layer_hi):

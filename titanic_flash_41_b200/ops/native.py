@@ -24,17 +24,19 @@ _CSRC = Path(__file__).resolve().parent.parent / "csrc"
 _DECL = re.compile(r"TF_API\s+(\w+)\s+(\w+)\s*\(([^)]*)\)", re.S)
 
 
-def _parse_signatures():
-    """Read the exported declarations out of csrc/*.cu so the argument types used by ctypes
-    can never drift from the C side."""
+def _parse_signatures(pattern: str = "*.cu"):
+    """Read the exported declarations out of csrc/*.cu (device library) or csrc/*.cc (host
+    library) so the argument types used by ctypes can never drift from the C side."""
     sigs, rets = {}, {}
-    for src in sorted(_CSRC.glob("*.cu")) + sorted(_CSRC.glob("*.cc")):
+    for src in sorted(_CSRC.glob(pattern)):
         for ret, name, args in _DECL.findall(src.read_text()):
             sig = ""
             for a in [x.strip() for x in args.split(",") if x.strip()]:
                 if a == "void":
                     continue
-                if "*" in a:
+                if "char*" in a.replace(" *", "*") and "const" in a:
+                    sig += "c"
+                elif "*" in a:
                     sig += "p"
                 elif a.startswith("cudaStream_t"):
                     sig += "s"
@@ -50,9 +52,10 @@ def _parse_signatures():
     return sigs, rets
 
 
-_SIGS, _RETS = _parse_signatures()
+_SIGS, _RETS = _parse_signatures("*.cu")
+_HSIGS, _HRETS = _parse_signatures("*.cc")
 _CT = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_long, "f": ctypes.c_float,
-       "d": ctypes.c_double, "s": ctypes.c_void_p}
+       "d": ctypes.c_double, "s": ctypes.c_void_p, "c": ctypes.c_char_p}
 
 
 class NativeError(RuntimeError):
@@ -81,11 +84,18 @@ def lib() -> ctypes.CDLL:
 
 
 def host_lib() -> Optional[ctypes.CDLL]:
+    """The C++ host runtime (digests, direct I/O, frame codec); None when it has not been built."""
     global _host
     if _host is None:
         path = _LIB_DIR / "libtflash_host.so"
         if path.exists():
             _host = ctypes.CDLL(str(path))
+            for name, sig in _HSIGS.items():
+                fn = getattr(_host, name, None)
+                if fn is None:
+                    raise NativeError(f"{path} does not export {name}: rebuild the library")
+                fn.argtypes = [_CT[c] for c in sig]
+                fn.restype = ctypes.c_long if _HRETS[name] == "long" else ctypes.c_int
     return _host
 
 

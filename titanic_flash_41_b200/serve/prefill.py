@@ -9,7 +9,7 @@ A callback after every chunk lets the scheduler cancel or yield (reference :4520
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence
+from typing import Callable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -18,8 +18,20 @@ from ..models.engine import Engine, StepPlan
 from .planner import plan_chunks
 
 
+def _patch_for(embeds, lo: int, T: int, dev):
+    """The part of ``embeds`` that falls into prompt offsets [lo, lo+T), as (chunk rows, values)."""
+    if embeds is None:
+        return None
+    offs, vals = embeds
+    offs = offs.to(dev)
+    m = (offs >= lo) & (offs < lo + T)
+    if not bool(m.any()):
+        return None
+    return (offs[m] - lo).long(), vals.to(dev)[m]
+
+
 def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List[int], start: int, late: int,
-                         tail: torch.Tensor, tail_n: int) -> None:
+                         tail: torch.Tensor, tail_n: int, embeds=None) -> None:
     """Encoder layers [0, late) layer by layer over ALL chunks of the prompt.
 
     The residual stream of the whole prompt (n x hidden bf16: 1 GB at 129K tokens) and the current
@@ -46,7 +58,8 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
             if src >= 0 and not Lw.is_index_source:
                 b["sel"][src][:T].copy_(sel_store[src][0][lo:hi])
                 b["selcnt"][src][:T].copy_(sel_store[src][1][lo:hi])
-            eng.run(T, b, shapes[c][0], shapes[c][1], None, li, li + 1, x_in=None if li == 0 else resid[lo:hi])
+            eng.run(T, b, shapes[c][0], shapes[c][1], None, li, li + 1, x_in=None if li == 0 else resid[lo:hi],
+                    x_patch=_patch_for(embeds, lo, T, eng.dev) if li == 0 else None)
             # x + pending sublayer output, rounded once to bf16
             resid[lo:hi].copy_(eng.residual_rows(b, slice(0, T)) if b.get("pending") else b["x"][:T])
             if Lw.is_index_source:
@@ -67,10 +80,11 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
 
 def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, need_logits: bool = True,
                 on_chunk: Optional[Callable[[int], bool]] = None,
-                widths: Optional[Sequence[int]] = None, layer_major: Optional[bool] = None
-                ) -> Optional[torch.Tensor]:
+                widths: Optional[Sequence[int]] = None, layer_major: Optional[bool] = None,
+                embeds: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
     """Prefill ``tokens`` at positions start.. into ``region``.  Returns fp32 logits of the last
-    row (or None when cancelled by ``on_chunk`` returning False)."""
+    row (or None when cancelled by ``on_chunk`` returning False).  ``embeds`` = (prompt offsets
+    [m], rows [m, hidden]) replaces the token embedding at those offsets (image spans)."""
     cfg = eng.cfg
     toks = np.asarray(tokens.cpu() if isinstance(tokens, torch.Tensor) else tokens, dtype=np.int32)
     n = int(toks.shape[0])
@@ -84,7 +98,7 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
     done = 0
     logits = None
     if layer_major:
-        _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n)
+        _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n, embeds)
         if late == L and need_logits:
             logits = eng._head(sizes[-1], eng._bufs(sizes[-1]), torch.tensor([sizes[-1] - 1], device=eng.dev))
         sizes = []
@@ -95,7 +109,7 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
         nmax, rpg = eng.plan_shape(plan, cfg.compress_ratio)
         last_chunk = done + T == n
         rows = torch.tensor([T - 1], device=eng.dev) if (late == L and last_chunk and need_logits) else None
-        out = eng.run(T, b, nmax, rpg, rows, 0, late)
+        out = eng.run(T, b, nmax, rpg, rows, 0, late, x_patch=_patch_for(embeds, done, T, eng.dev))
         if late < L:
             # keep the encoder output of the prompt's last `window` rows for the late-group replay
             lo = max(done, n - tail_n)

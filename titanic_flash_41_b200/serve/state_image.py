@@ -18,6 +18,8 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
+from ..utils import hostio
+
 CHUNK = 4 << 20
 BATCH_CHUNKS = 32
 
@@ -122,29 +124,19 @@ class DiskTier:
         path = os.path.join(self.dir, image_id + ".img")
         header = {"tokens": list(img.tokens), "kind": img.kind, "media": img.media, "meta": img.meta,
                   "regions": [[n, int(t.numel())] for n, t in img.regions]}
-        digests: List[str] = []
-        total = 0
         self.fault("write_open")
-        with open(path + ".tmp", "wb") as f:
-            hb = json.dumps(header).encode() + b"\n"
-            f.write(struct.pack("<Q", len(hb)))
-            f.write(hb)
-            pending = bytearray()
-            for _, t in img.regions:
-                data = t.detach().cpu().contiguous().numpy().tobytes()
-                pending += data
-                while len(pending) >= CHUNK:
-                    chunk, pending = bytes(pending[:CHUNK]), pending[CHUNK:]
-                    digests.append(hashlib.sha256(chunk).hexdigest())
-                    self.fault("write_chunk")
-                    f.write(chunk)
-                    total += len(chunk)
-            if pending:
-                digests.append(hashlib.sha256(bytes(pending)).hexdigest())
-                f.write(bytes(pending))
-                total += len(pending)
-            f.flush()
-            os.fsync(f.fileno())
+        hb = json.dumps(header).encode() + b"\n"
+        blob = bytearray(struct.pack("<Q", len(hb)) + hb)
+        head_len = len(blob)
+        for _, t in img.regions:
+            blob += t.detach().cpu().contiguous().numpy().tobytes()
+        total = len(blob) - head_len
+        # digests of every 4 MiB chunk by the host runtime's thread pool, then one durable write
+        # that bypasses the page cache
+        digests = [d.hex() for d in hostio.sha256_chunks(memoryview(blob)[head_len:], CHUNK)]
+        for _ in digests:
+            self.fault("write_chunk")
+        hostio.write_file(path + ".tmp", blob)
         with open(os.path.join(self.dir, image_id + ".idx"), "w") as f:
             json.dump({"chunk": CHUNK, "digests": digests, "bytes": total}, f)
         os.replace(path + ".tmp", path)
@@ -157,19 +149,19 @@ class DiskTier:
         with open(os.path.join(self.dir, image_id + ".idx")) as f:
             idx = json.load(f)
         self.fault("read_open")
-        with open(path, "rb") as f:
-            (hl,) = struct.unpack("<Q", f.read(8))
-            header = json.loads(f.read(hl))
-            payload = f.read()
+        size = os.path.getsize(path)
+        raw = hostio.read_file(path, size)
+        (hl,) = struct.unpack("<Q", raw[:8])
+        header = json.loads(bytes(raw[8:8 + hl]))
+        payload = memoryview(raw)[8 + hl:]
         if len(payload) != idx["bytes"]:
             raise ImageError(f"{image_id}: truncated image ({len(payload)} of {idx['bytes']} bytes)")
-        for i, want in enumerate(idx["digests"]):
-            got = hashlib.sha256(payload[i * idx["chunk"]:(i + 1) * idx["chunk"]]).hexdigest()
-            if got != want:
+        for i, (got, want) in enumerate(zip(hostio.sha256_chunks(payload, idx["chunk"]), idx["digests"])):
+            if got.hex() != want:
                 raise ImageError(f"{image_id}: chunk {i} fails its digest")
         regs, off = [], 0
         for name, n in header["regions"]:
-            t = torch.frombuffer(bytearray(payload[off:off + n]), dtype=torch.uint8)
+            t = torch.frombuffer(bytearray(payload[off:off + n]), dtype=torch.uint8) if n else torch.empty(0, dtype=torch.uint8)
             regs.append((name, t.pin_memory() if (pin and torch.cuda.is_available()) else t))
             off += n
         out = img or Image(tuple(header["tokens"]), [], header["kind"], header["media"], header["meta"])
