@@ -292,3 +292,30 @@ def test_block_verification_preserves_target_law():
     p0 = torch.softmax(tl[0].double().cpu(), -1)
     assert float((emp - p0).abs().max()) < 0.012
     assert 0.2 < float((nacc > 0).double().mean()) < 1.0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_key_sharded_selection_equals_unsharded(world):
+    """Scoring split over `world` key shards (run one after the other here) + gather + merge gives
+    exactly the ids of the unsharded selection."""
+    from titanic_flash_41_b200.parallel import key_sharded as KS
+    torch.manual_seed(9)
+    T, Hi, Di, C, k = 6, 8, 128, 5000, 256
+    krow = Di // 2 + Di // 32
+    keys = codecs.index_key_encode(torch.randn(1, C, Di)).to(DEV).contiguous()
+    q = torch.randn(T, Hi, Di, device=DEV).bfloat16()
+    w = torch.rand(T, Hi, device=DEV)
+    region = torch.zeros(T, dtype=torch.int32, device=DEV)
+    nvalid = torch.tensor([5000, 4097, 300, 0, 129, 2600], dtype=torch.int32, device=DEV)
+    lds = 5120
+    scores = torch.zeros(T, lds, device=DEV)
+    native.call("tf_index_scores", q, w, region, nvalid, keys, C * krow, krow, T, Hi, Di, 2, scores, lds, 0, C)
+    want = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    wcnt = torch.zeros(T, dtype=torch.int32, device=DEV)
+    native.call("tf_topk_select", scores, lds, nvalid, k, want, wcnt, None, 0, T)
+    parts = [KS.local_candidates(q, w, region, nvalid, keys, C * krow, krow, T, Hi, Di, 2,
+                                 torch.zeros(T, lds, device=DEV), C, k, r, world) for r in range(world)]
+    ids, cnt = KS.merge(torch.cat([p[0] for p in parts], 1), torch.cat([p[1] for p in parts], 1), k)
+    torch.cuda.synchronize()
+    assert torch.equal(cnt, wcnt)
+    assert torch.equal(ids, want)

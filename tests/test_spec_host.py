@@ -1,0 +1,67 @@
+"""Host-side speculative-decoding helpers: exact-text copy proposals, request pause / resume."""
+import pytest
+import torch
+
+from titanic_flash_41_b200.config import tiny_config
+from titanic_flash_41_b200.models import oracle
+from titanic_flash_41_b200.serve import request_checkpoint as RC
+from titanic_flash_41_b200.spec.history_lookup import HistoryLookup, fingerprint
+
+
+def test_history_lookup_proposes_what_followed_last_time():
+    base = list(range(100, 140))
+    h = HistoryLookup(base + [7, 8, 9] + base[:20])
+    p = h.propose()
+    assert p is not None and p.tokens == base[20:25] and p.matched >= 16 and p.source_end == 20
+    # the pending anchor extends the match
+    p2 = h.propose(pending=[base[20]])
+    assert p2.tokens == base[21:26]
+    # no earlier occurrence -> nothing
+    assert HistoryLookup(list(range(50))).propose() is None
+    # shorter than the minimum match -> nothing
+    assert HistoryLookup([1, 2, 3, 4, 1, 2, 3]).propose() is None
+    # a forged table entry (collision) is rejected by the token comparison
+    h3 = HistoryLookup(list(range(30)))
+    h3.tables[0][fingerprint(list(range(22, 30))) % h3.slots] = 12
+    assert h3.propose() is None
+    # commits must be contiguous; truncation makes stale slots harmless
+    with pytest.raises(ValueError):
+        h.commit(3, [1])
+    h.truncate(45)
+    assert h.propose() is None or h.propose().source_end <= 45
+    # same text on two "ranks" gives the same proposal
+    a, b = HistoryLookup(base * 3), HistoryLookup(base * 3)
+    assert a.propose() == b.propose()
+
+
+def test_pause_and_resume_is_token_exact():
+    from titanic_flash_41_b200.serve.backend import OracleBackend
+    from titanic_flash_41_b200.serve.scheduler import Job, Scheduler
+    from titanic_flash_41_b200.serve.session_cache import SessionCache
+    from titanic_flash_41_b200.serve.worker import Worker
+    cfg = tiny_config()
+    W = oracle.init_weights(cfg, 0)
+    prompt = torch.randint(3, cfg.vocab, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def run(interrupt):
+        b = OracleBackend(cfg, W, regions=2, max_context=256, chunk=32)
+        s = Scheduler(2, 4, 2)
+        w = Worker(b, s, SessionCache(slots=4, budget_bytes=1 << 30), eos_id=1, checkpoint_min=1 << 20)
+        ev = []
+        job = Job("r", list(prompt), 14, emit=lambda k, p: ev.append((k, p)), temperature=0.6, top_p=0.95, seed=5)
+        s.submit(job)
+        w.run_once(0.0)                                   # begin
+        for _ in range(2):
+            w.run_once(0.0)                               # two decode steps
+        if interrupt:
+            region = next(iter(w.active))
+            ck = RC.pause(w, region)
+            assert ck.charge > 0 and not w.active and ck.needs_prefix(ck.committed + [1, 2])
+            b.reset(region)
+            RC.resume(w, ck, 1 - region, job)
+        for _ in range(100):
+            if w.run_once(0.0) == "idle" and not w.active:
+                break
+        return [t for k, p in ev if k == "tokens" for t in p]
+    plain, paused = run(False), run(True)
+    assert plain == paused and len(plain) >= 1

@@ -1,0 +1,84 @@
+"""Exact-text copy proposals: when the committed text ends with a phrase that occurred before,
+propose the tokens that followed it last time.  A proposal is a point mass (q = 1 on the proposed
+token), so verification accepts it with probability p_target(token) and the output law is
+unchanged.  Pure host bookkeeping on public token ids: every rank computes the same proposal.
+
+Suffixes of several lengths are fingerprinted into small direct-mapped tables (longest match
+wins); a hit is confirmed by comparing the actual tokens, so a hash collision can only lose an
+opportunity, never invent a match (reference: src/history_lookup.rs:1-60 design, LENGTHS
+[8,12,16,32,64], SLOTS 65,536; examples/history_lookup_*.rs screens).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+LENGTHS = (8, 12, 16, 32, 64)
+SLOTS = 1 << 16
+EMPTY = -1
+MASK = (1 << 64) - 1
+
+
+def fingerprint(ids: Sequence[int]) -> int:
+    v = 0xCBF29CE484222325
+    for t in ids:
+        v = ((v ^ (t & 0xFFFFFFFF)) * 0x100000001B3) & MASK
+    return v ^ (v >> 32)
+
+
+@dataclass
+class Proposal:
+    tokens: List[int]
+    matched: int            # length of the confirmed suffix match
+    source_end: int         # index in the history right after the earlier occurrence
+
+
+class HistoryLookup:
+    def __init__(self, prefix: Sequence[int] = (), slots: int = SLOTS, lengths: Sequence[int] = LENGTHS,
+                 minimum_match: Optional[int] = None, depth: int = 5):
+        self.tokens: List[int] = []
+        self.slots, self.lengths, self.depth = slots, tuple(lengths), depth
+        self.minimum = minimum_match or self.lengths[0]
+        self.tables = [[EMPTY] * slots for _ in self.lengths]
+        if prefix:
+            self.commit(0, prefix)
+
+    def commit(self, at: int, tokens: Sequence[int]) -> None:
+        """Append ``tokens`` at position ``at`` (must equal the current length: history is append-only)."""
+        if at != len(self.tokens):
+            raise ValueError("history commits must be contiguous")
+        for t in tokens:
+            self.tokens.append(int(t))
+            end = len(self.tokens)
+            # the suffix that ENDS BEFORE this token predicts it: index suffixes ending at end-1
+            for li, L in enumerate(self.lengths):
+                if end - 1 >= L:
+                    key = fingerprint(self.tokens[end - 1 - L:end - 1]) % self.slots
+                    self.tables[li][key] = end - 1           # position of the token that followed
+
+    def truncate(self, length: int) -> None:
+        """Drop text past ``length`` (a cancelled or rolled-back turn); stale slots are caught by confirmation."""
+        del self.tokens[length:]
+
+    def propose(self, pending: Sequence[int] = ()) -> Optional[Proposal]:
+        """``pending``: tokens already emitted but not yet committed (the anchor); the match runs over
+        committed text followed by them."""
+        text = self.tokens + [int(t) for t in pending]
+        n = len(text)
+        for li in range(len(self.lengths) - 1, -1, -1):
+            L = self.lengths[li]
+            if n < L or L < self.minimum:
+                continue
+            pos = self.tables[li][fingerprint(text[n - L:]) % self.slots]
+            if pos == EMPTY or pos >= len(self.tokens) or pos < L:
+                continue
+            if self.tokens[pos - L:pos] != text[n - L:]:
+                continue                                       # collision or stale slot
+            out = self.tokens[pos:pos + self.depth]
+            if not out:
+                continue
+            m = L                                              # extend the confirmed match backwards
+            while m < min(pos, n) and self.tokens[pos - m - 1] == text[n - m - 1]:
+                m += 1
+            return Proposal(out, m, pos)
+        return None
