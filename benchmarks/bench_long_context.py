@@ -1,0 +1,149 @@
+"""Long-context serving stress: several conversations grown in large appended chunks, short
+requests interleaved, then every conversation resumed with a small follow-up.
+
+    python benchmarks/bench_long_context.py [--sessions 4] [--target 131072] [--grow 65536]
+                                            [--short 17] [--follow 2048] [--backend engine|oracle]
+
+Runs the real serving stack (scheduler, worker, session cache with host and disk tiers, state
+images, engine) in one process.  Reports, as one JSON line: time to first token of the resumed
+turns, the share of prompt tokens served from cached state, and where the restored images came
+from (device / host / disk).  The oracle backend with ``--preset tiny`` runs the same script on
+the CPU in seconds (used by the tests).
+"""
+import argparse
+import json
+import os
+import sys
+import tempfile
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from titanic_flash_41_b200.config import EngineConfig, flash_b200_config, tiny_config  # noqa: E402
+from titanic_flash_41_b200.serve.scheduler import Job, Scheduler  # noqa: E402
+from titanic_flash_41_b200.serve.session_cache import SessionCache  # noqa: E402
+from titanic_flash_41_b200.serve.state_image import DiskTier  # noqa: E402
+from titanic_flash_41_b200.serve.worker import Worker  # noqa: E402
+
+
+def build_backend(a):
+    if a.backend == "oracle":
+        from titanic_flash_41_b200.models import oracle
+        from titanic_flash_41_b200.serve.backend import OracleBackend
+        cfg = tiny_config()
+        return cfg, OracleBackend(cfg, oracle.init_weights(cfg, 0), regions=a.regions, max_context=a.target + a.follow + 512,
+                                  chunk=a.chunk)
+    from titanic_flash_41_b200.models.engine import Engine
+    from titanic_flash_41_b200.serve.backend import EngineBackend
+    cfg = flash_b200_config() if a.preset == "flash-b200" else tiny_config()
+    ecfg = EngineConfig(regions=a.regions, max_context=a.target + a.follow + 4096, prefill_widths=(a.chunk,))
+    eng = Engine.random_init(cfg, ecfg, seed=0, max_chunk=a.chunk)
+    return cfg, EngineBackend(eng, chunk=a.chunk)
+
+
+def drain(w, limit=100000):
+    for _ in range(limit):
+        if w.run_once(0.0) == "idle" and not w.active and w.sched.waiting() == 0:
+            return
+    raise RuntimeError("worker did not drain")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--backend", default="engine", choices=["engine", "oracle"])
+    ap.add_argument("--preset", default="flash-b200")
+    ap.add_argument("--sessions", type=int, default=4)
+    ap.add_argument("--regions", type=int, default=4)
+    ap.add_argument("--target", type=int, default=131072, help="context each conversation is grown to")
+    ap.add_argument("--grow", type=int, default=65536, help="tokens appended per turn")
+    ap.add_argument("--short", type=int, default=17, help="short requests interleaved between the long turns")
+    ap.add_argument("--short-tokens", type=int, default=200)
+    ap.add_argument("--follow", type=int, default=2048)
+    ap.add_argument("--new-tokens", type=int, default=8)
+    ap.add_argument("--chunk", type=int, default=16384)
+    ap.add_argument("--cache-slots", type=int, default=64)
+    ap.add_argument("--checkpoint", type=int, default=65536, help="prompt checkpoint spacing (tokens)")
+    ap.add_argument("--device-cache-gb", type=float, default=2.0)
+    ap.add_argument("--host-cache-gb", type=float, default=16.0)
+    a = ap.parse_args(argv)
+    cfg, backend = build_backend(a)
+    tmp = tempfile.mkdtemp(prefix="tflash_tier_")
+    disk = DiskTier(tmp)
+    cache = SessionCache(slots=a.cache_slots, budget_bytes=int(a.device_cache_gb * 2 ** 30), disk=disk,
+                         host_budget_bytes=int(a.host_cache_gb * 2 ** 30), park_after=2)
+    sched = Scheduler(a.regions, 64, 8)
+    w = Worker(backend, sched, cache, eos_id=-1, checkpoint_min=a.checkpoint, checkpoint_align=a.checkpoint)
+    g = torch.Generator().manual_seed(0)
+    rand = lambda n: torch.randint(3, cfg.vocab, (n,), generator=g).tolist()
+    events = {}
+
+    def submit(jid, toks, n):
+        events[jid] = []
+        sched.submit(Job(jid, list(toks), n, emit=lambda k, p, _j=jid: events[_j].append((k, p, time.monotonic())),
+                         temperature=0.6, top_p=0.95, seed=len(events)))
+
+    def ready(jid):
+        return [p for k, p, _ in events[jid] if k == "ready"][0]
+
+    def tokens_of(jid):
+        return [t for k, p, _ in events[jid] if k == "tokens" for t in p]
+
+    convs = [[] for _ in range(a.sessions)]
+    turns = max(1, a.target // a.grow)
+    shorts_left = a.short
+    t_start = time.monotonic()
+    prompt_total = reused_total = 0
+    for turn in range(turns):
+        for s in range(a.sessions):
+            convs[s] = convs[s] + rand(a.grow)
+            jid = f"s{s}t{turn}"
+            submit(jid, convs[s], a.new_tokens)
+            # interleave short requests so that regions are recycled and images get displaced
+            if shorts_left > 0 and (turn * a.sessions + s) % max(1, (turns * a.sessions) // max(1, a.short)) == 0:
+                submit(f"short{shorts_left}", rand(a.short_tokens), a.new_tokens)
+                shorts_left -= 1
+        while shorts_left > 0 and turn == turns - 1:
+            submit(f"short{shorts_left}", rand(a.short_tokens), a.new_tokens)
+            shorts_left -= 1
+        drain(w)
+        for s in range(a.sessions):
+            jid = f"s{s}t{turn}"
+            r = ready(jid)
+            prompt_total += r["prompt_n"] + r["cache_n"]
+            reused_total += r["cache_n"]
+            convs[s] = convs[s] + tokens_of(jid)
+    grow_s = time.monotonic() - t_start
+    # let idle steps write images behind to the lower tiers
+    for _ in range(64):
+        w.execute({"op": "idle"})
+    tiers_before = {t: sum(1 for e in cache.entries if e.image.tier == t) for t in ("device", "host", "disk")}
+    # ---- resume every conversation with a short follow-up
+    ttft, resumed = [], []
+    for s in range(a.sessions):
+        jid = f"s{s}resume"
+        t0 = time.monotonic()
+        submit(jid, convs[s] + rand(a.follow), a.new_tokens)
+        drain(w)
+        first = [t for k, p, t in events[jid] if k == "tokens"][0]
+        ttft.append(first - t0)
+        r = ready(jid)
+        resumed.append(r)
+        prompt_total += r["prompt_n"] + r["cache_n"]
+        reused_total += r["cache_n"]
+    out = {"metric": "resume TTFT (s) and cached-prefix share, long-context serving stress", "backend": a.backend,
+           "sessions": a.sessions, "context": len(convs[0]), "grow": a.grow, "short_requests": a.short,
+           "grow_phase_s": round(grow_s, 3), "resume_ttft_s": [round(t, 4) for t in ttft],
+           "resume_ttft_mean_s": round(sum(ttft) / len(ttft), 4),
+           "resume_cached_tokens": [r["cache_n"] for r in resumed], "resume_prefilled_tokens": [r["prompt_n"] for r in resumed],
+           "reused_token_share": round(reused_total / max(1, prompt_total), 4), "cache_stats": dict(cache.stats),
+           "image_tiers_before_resume": tiers_before,
+           "data": "synthetic token ids, random-init weights"}
+    print(json.dumps(out), flush=True)
+    disk.reset_dir()
+    os.rmdir(tmp)
+    return out
+
+
+if __name__ == "__main__":
+    main()

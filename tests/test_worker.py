@@ -93,3 +93,23 @@ def test_cancel_and_background_hold():
     s.priority_lease(0.0)
     _drain(w)
     assert any(jj == "bg" and k == "done" for jj, k, p in ev)
+
+
+def test_long_context_stress_script_on_the_oracle():
+    """The long-context serving benchmark, scaled down: every resumed conversation is served from its
+    cached image (only the follow-up is prefilled)."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_long_context", os.path.join(root, "benchmarks", "bench_long_context.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = mod.main(["--backend", "oracle", "--sessions", "3", "--regions", "2", "--target", "192", "--grow", "96",
+                    "--short", "4", "--short-tokens", "20", "--follow", "24", "--new-tokens", "3", "--chunk", "32",
+                    "--checkpoint", "32", "--cache-slots", "16",
+                    "--device-cache-gb", "0.0006", "--host-cache-gb", "0.004"])
+    assert out["context"] >= 192 and len(out["resume_ttft_s"]) == 3
+    # tiny cache budgets force displacement: most conversations still resume from their last image,
+    # the others from an earlier checkpoint of the same conversation
+    assert sum(c >= 190 for c in out["resume_cached_tokens"]) >= 2 and all(c >= 96 for c in out["resume_cached_tokens"]), out
+    assert out["reused_token_share"] > 0.3 and out["cache_stats"]["parked"] > 0

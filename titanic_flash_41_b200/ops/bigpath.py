@@ -17,6 +17,8 @@ class BigPath:
         self.e = engine
         self.buf = {}
         self._converted = None      # layer whose experts currently sit in the FP8 staging copy
+        self.resident = engine.world >= 4          # per-layer FP8 expert copies stay on the device
+        self._resident = {}
 
     def _get(self, name, shape, dtype):
         t = self.buf.get(name)
@@ -77,16 +79,30 @@ class BigPath:
         native.call("tf_moe_plan", b["ids"], npairs, e_lo, El, z, offsets, cursor, tile_e, max_tiles, ntile[0:1],
                     ntile[1:2], pair_dst)
         # expert weights of this layer as block-scaled FP8: [El, 2I, d] (w1 | w3) and [El, d, I]
-        w13 = self._get("w13", (El, 2 * I, d), torch.uint8)
-        s13 = self._get("s13", (El * 2 * I // 128, d // 128), torch.float32)
-        w2 = self._get("w2", (El, d, I), torch.uint8)
-        s2 = self._get("s2", (El * d // 128, I // 128), torch.float32)
-        if self._converted is not L:
-            # consecutive chunks of one layer (layer-major prefill) reuse the converted copy
+        def convert(w13, s13, w2, s2):
             native.call("tf_mxfp4_to_fp8_block", L.ew1, L.es1, w13, s13, El, I, d, 0, 2 * I)
             native.call("tf_mxfp4_to_fp8_block", L.ew3, L.es3, w13, s13, El, I, d, I, 2 * I)
             native.call("tf_mxfp4_to_fp8_block", L.ew2, L.es2, w2, s2, El, d, I, 0, d)
-            self._converted = L
+        if self.resident:
+            # enough HBM per rank (experts split over >= 4 ranks): every layer keeps its FP8 copy
+            keep = self._resident.get(id(L))
+            if keep is None:
+                keep = (torch.empty(El, 2 * I, d, dtype=torch.uint8, device=eng.dev),
+                        torch.empty(El * 2 * I // 128, d // 128, dtype=torch.float32, device=eng.dev),
+                        torch.empty(El, d, I, dtype=torch.uint8, device=eng.dev),
+                        torch.empty(El * d // 128, I // 128, dtype=torch.float32, device=eng.dev))
+                convert(*keep)
+                self._resident[id(L)] = keep
+            w13, s13, w2, s2 = keep
+        else:
+            w13 = self._get("w13", (El, 2 * I, d), torch.uint8)
+            s13 = self._get("s13", (El * 2 * I // 128, d // 128), torch.float32)
+            w2 = self._get("w2", (El, d, I), torch.uint8)
+            s2 = self._get("s2", (El * d // 128, I // 128), torch.float32)
+            if self._converted is not L:
+                # consecutive chunks of one layer (layer-major prefill) reuse the converted copy
+                convert(w13, s13, w2, s2)
+                self._converted = L
         # gather + quantise token rows into the expert-sorted padded matrix
         xp = self._get("xp", (cap, d), torch.uint8)
         xps = self._get("xps", (cap, d // 128), torch.float32)

@@ -31,7 +31,7 @@ def _patch_for(embeds, lo: int, T: int, dev):
 
 
 def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List[int], start: int, late: int,
-                         tail: torch.Tensor, tail_n: int, embeds=None) -> None:
+                         tail: torch.Tensor, tail_n: int, embeds=None, on_chunk=None) -> bool:
     """Encoder layers [0, late) layer by layer over ALL chunks of the prompt.
 
     The residual stream of the whole prompt (n x hidden bf16: 1 GB at 129K tokens) and the current
@@ -69,6 +69,10 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
                                      torch.empty(n, dtype=b["selcnt"][li].dtype, device=eng.dev))
                 sel_store[li][0][lo:hi].copy_(b["sel"][li][:T])
                 sel_store[li][1][lo:hi].copy_(b["selcnt"][li][:T])
+            # the scheduler's hook (cancel / let decoding conversations take a step) runs between
+            # units of work; rows count as done only when the last layer has seen them
+            if on_chunk is not None and not on_chunk(hi if li == late - 1 else 0):
+                return False
     if tail_n > 0:
         tail[:tail_n].copy_(resid[n - tail_n:])
     # leave the last chunk's residual in its buffers for a head that follows directly
@@ -76,6 +80,7 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
     b = eng._bufs(T)
     b["x"][:T].copy_(resid[n - T:])
     b["pending"] = False
+    return True
 
 
 def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, need_logits: bool = True,
@@ -94,11 +99,12 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
     tail = torch.zeros(max(tail_n, 1), cfg.hidden, dtype=torch.bfloat16, device=eng.dev)
     sizes = plan_chunks(n, tuple(widths) if widths else (chunk,))
     if layer_major is None:
-        layer_major = len(sizes) > 1 and getattr(eng, "big_moe_full", None) is not None and on_chunk is None
+        layer_major = len(sizes) > 1 and getattr(eng, "big_moe_full", None) is not None
     done = 0
     logits = None
     if layer_major:
-        _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n, embeds)
+        if not _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n, embeds, on_chunk):
+            return None
         if late == L and need_logits:
             logits = eng._head(sizes[-1], eng._bufs(sizes[-1]), torch.tensor([sizes[-1] - 1], device=eng.dev))
         sizes = []
