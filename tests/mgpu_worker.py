@@ -64,7 +64,9 @@ def main():
     say("fused gemv ok")
     # ---- 3. engine: TP/EP over `world` GPUs (fused kernels) == single GPU
     from tests.test_engine_gpu import small_config
-    cfg = small_config(n_heads=4 * world if world > 4 else 4, draft=DraftConfig(layers=1, depth=3))
+    # keep every per-rank slice at least one 128-wide block: heads and shared-expert width grow with the world
+    cfg = small_config(n_heads=4 * world if world > 4 else 4, shared_inter=max(256, 128 * world),
+                       draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
     ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W, comm=comm, device=dev)

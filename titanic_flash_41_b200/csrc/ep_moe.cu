@@ -37,6 +37,7 @@ struct EpParams {
 
 // control block at offset 0 of every workspace (uint32 words)
 constexpr int kMaxWorld = 16;
+constexpr int kWalkCtas = 148 * 8;               // grid of the kernels that walk received entries
 constexpr int W_DISP_FLAG = 0;                 // [world] written by sources
 constexpr int W_DISP_CNT = kMaxWorld;          // [world] written by sources
 constexpr int W_RET_FLAG = 2 * kMaxWorld;      // [world] written by destinations
@@ -145,36 +146,48 @@ __global__ void __launch_bounds__(256) ep_recv_ids_kernel(EpParams p, int* __res
   ids_out[i] = e;
 }
 
-// rows that arrived -> their place in the expert-sorted padded matrix
+// rows that arrived -> their place in the expert-sorted padded matrix.  A fixed grid walks only
+// the entries that arrived (counts were published with the dispatch flags, which the receive
+// kernel of this call has already waited for).
 __global__ void __launch_bounds__(256) ep_gather_kernel(EpParams p, const int* __restrict__ pair_dst,
                                                         uint8_t* __restrict__ xp, float* __restrict__ xps) {
-  const long i = blockIdx.x;
-  const int dst = pair_dst[i];
-  if (dst < 0) return;
+  const unsigned int* mine = ctrl(p, p.rank);
   const uint8_t* base = reinterpret_cast<const uint8_t*>(p.peers[p.rank]);
-  const uint4* sx = reinterpret_cast<const uint4*>(base + p.off_x + i * p.d);
-  uint4* dx = reinterpret_cast<uint4*>(xp + (long)dst * p.d);
-  for (int j = threadIdx.x; j < p.d / 16; j += 256) dx[j] = sx[j];
-  const float* ss = reinterpret_cast<const float*>(base + p.off_s + i * (p.d / 128) * 4);
-  if (threadIdx.x < p.d / 128) xps[(long)dst * (p.d / 128) + threadIdx.x] = ss[threadIdx.x];
+  for (int src = 0; src < p.world; ++src) {
+    const int cnt = (int)mine[W_DISP_CNT + src];
+    for (int slot = blockIdx.x; slot < cnt; slot += gridDim.x) {
+      const long i = (long)src * p.cap + slot;
+      const int dst = pair_dst[i];
+      if (dst < 0) continue;
+      const uint4* sx = reinterpret_cast<const uint4*>(base + p.off_x + i * p.d);
+      uint4* dx = reinterpret_cast<uint4*>(xp + (long)dst * p.d);
+      for (int j = threadIdx.x; j < p.d / 16; j += 256) dx[j] = sx[j];
+      const float* ss = reinterpret_cast<const float*>(base + p.off_s + i * (p.d / 128) * 4);
+      if (threadIdx.x < p.d / 128) xps[(long)dst * (p.d / 128) + threadIdx.x] = ss[threadIdx.x];
+    }
+  }
 }
 
 // expert outputs back to the rank that owns the token
 __global__ void __launch_bounds__(256) ep_return_kernel(EpParams p, const int* __restrict__ pair_dst,
                                                         const __nv_bfloat16* __restrict__ y, long ldy) {
-  const long i = blockIdx.x;
-  const int dst = pair_dst[i];
-  if (dst >= 0) {
-    const int src = (int)(i / p.cap);
-    const int2 meta = reinterpret_cast<const int2*>(reinterpret_cast<const uint8_t*>(p.peers[p.rank]) + p.off_meta)[i];
-    const uint4* sy = reinterpret_cast<const uint4*>(y + (long)dst * ldy);
-    uint4* dy = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peers[src]) + p.off_ret + (long)meta.y * p.d * 2);
-    for (int j = threadIdx.x; j < p.d / 8; j += 256) dy[j] = sy[j];
+  unsigned int* mine = ctrl(p, p.rank);
+  for (int src = 0; src < p.world; ++src) {
+    const int cnt = (int)mine[W_DISP_CNT + src];
+    for (int slot = blockIdx.x; slot < cnt; slot += gridDim.x) {
+      const long i = (long)src * p.cap + slot;
+      const int dst = pair_dst[i];
+      if (dst < 0) continue;
+      const int2 meta = reinterpret_cast<const int2*>(reinterpret_cast<const uint8_t*>(p.peers[p.rank]) + p.off_meta)[i];
+      const uint4* sy = reinterpret_cast<const uint4*>(y + (long)dst * ldy);
+      uint4* dy =
+          reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peers[src]) + p.off_ret + (long)meta.y * p.d * 2);
+      for (int j = threadIdx.x; j < p.d / 8; j += 256) dy[j] = sy[j];
+    }
   }
   __threadfence_system();
   __syncthreads();
   __shared__ int s_last;
-  unsigned int* mine = ctrl(p, p.rank);
   if (threadIdx.x == 0) s_last = atomicAdd(mine + W_DONE + 1, 1u) == gridDim.x - 1;
   __syncthreads();
   if (s_last && threadIdx.x < p.world) {
@@ -265,14 +278,14 @@ TF_API int tf_ep_recv_ids(const void* peers, int world, int rank, int cap, int d
 TF_API int tf_ep_gather(const void* peers, int world, int rank, int cap, int d, int k, int El, int Tl_max,
                         const int* pair_dst, void* xp, float* xps, cudaStream_t st) {
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, 0, 0, nullptr);
-  ep_gather_kernel<<<(unsigned)((long)world * cap), 256, 0, st>>>(p, pair_dst, (uint8_t*)xp, xps);
+  ep_gather_kernel<<<kWalkCtas, 256, 0, st>>>(p, pair_dst, (uint8_t*)xp, xps);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_ep_return(const void* peers, int world, int rank, int cap, int d, int k, int El, int Tl_max, int epoch,
                         const int* pair_dst, const void* y, long ldy, void* status, cudaStream_t st) {
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, epoch, 0, status);
-  ep_return_kernel<<<(unsigned)((long)world * cap), 256, 0, st>>>(p, pair_dst, (const __nv_bfloat16*)y, ldy);
+  ep_return_kernel<<<kWalkCtas, 256, 0, st>>>(p, pair_dst, (const __nv_bfloat16*)y, ldy);
   return (int)cudaGetLastError();
 }
 
