@@ -89,3 +89,32 @@ def test_serve_end_to_end_oracle_backend():
     finally:
         if p.poll() is None:
             p.kill()
+
+
+def test_protocol_and_checkpoint_utilities(tmp_path, capsys):
+    req = os.path.join(str(tmp_path), "req.json")
+    open(req, "w").write(json.dumps({"model": "m", "messages": [{"role": "user", "content": "hello"}]}))
+    assert cli.main(["encode-chat", req, "--vocab", "1024"]) == 0
+    enc = json.loads(capsys.readouterr().out)
+    assert enc["n"] == len(enc["tokens"]) > 0 and "hello" in enc["prompt"]
+    toks = os.path.join(str(tmp_path), "t.json")
+    open(toks, "w").write(json.dumps(enc["tokens"]))
+    assert cli.main(["decode-tokens", toks, "--vocab", "1024"]) == 0
+    assert "hello" in json.loads(capsys.readouterr().out)["text"]
+    txt = os.path.join(str(tmp_path), "c.txt")
+    open(txt, "w").write("thinking...</think>\\n\\nThe answer.")
+    assert cli.main(["parse-completion", txt]) == 0
+    msg = json.loads(capsys.readouterr().out)
+    assert "The answer." in json.dumps(msg)
+    cfgp = os.path.join(str(tmp_path), "cfg.json")
+    open(cfgp, "w").write(tiny_config().to_json())
+    assert cli.main(["config-validate", cfgp]) == 0
+    assert json.loads(capsys.readouterr().out)["digest"] == tiny_config().digest()
+    from titanic_flash_41_b200.models import loader, oracle
+    cfg = tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4")
+    open(cfgp, "w").write(cfg.to_json())
+    ck = os.path.join(str(tmp_path), "ck")
+    loader.export_checkpoint(oracle.init_weights(cfg, seed=1), cfg, ck)
+    assert cli.main(["scan", ck, "--model-config", cfgp]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["matches_config"] and "F8_E4M3" in out["dtypes"]

@@ -57,6 +57,28 @@ def build_parser() -> argparse.ArgumentParser:
     w.add_argument("--world", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
     w.add_argument("--moe-parallel", choices=["ep", "tp"], default="ep")
     sub.add_parser("probe", help="device, peer access and build facts as JSON")
+    # ---- protocol / checkpoint utilities (no GPU)
+    e = sub.add_parser("encode-chat", help="chat request JSON (file or -) -> rendered prompt and token ids")
+    e.add_argument("request")
+    e.add_argument("--tokenizer")
+    e.add_argument("--vocab", type=int, default=129280)
+    dt = sub.add_parser("decode-tokens", help="token ids (JSON list, file or -) -> text")
+    dt.add_argument("tokens")
+    dt.add_argument("--tokenizer")
+    dt.add_argument("--vocab", type=int, default=129280)
+    pc = sub.add_parser("parse-completion", help="raw completion text (file or -) -> OpenAI message JSON")
+    pc.add_argument("text")
+    pc.add_argument("--no-thinking", action="store_true")
+    pc.add_argument("--tools", action="store_true")
+    cv = sub.add_parser("config-validate", help="validate a model configuration JSON and print its digest")
+    cv.add_argument("config")
+    sc = sub.add_parser("scan", help="scan a safetensors checkpoint and check it against a model configuration")
+    sc.add_argument("checkpoint")
+    sc.add_argument("--preset", choices=sorted(PRESETS))
+    sc.add_argument("--model-config")
+    sm = sub.add_parser("smoke", help="live endpoint check: health, models, one completion, one stream")
+    sm.add_argument("--url", default="http://127.0.0.1:8000")
+    sm.add_argument("--api-key", default=os.environ.get("TFLASH_API_KEY", ""))
     l = sub.add_parser("launch", help="start one process per GPU running a sub-command")
     l.add_argument("--gpus", type=int, required=True)
     l.add_argument("--master-port", type=int, default=29511)
@@ -151,8 +173,55 @@ def serve_main(args) -> int:
     return 0
 
 
+def _read(arg: str) -> str:
+    return sys.stdin.read() if arg == "-" else open(arg).read()
+
+
+def utility(args) -> Optional[int]:
+    """Protocol / checkpoint sub-commands; returns None when ``args.cmd`` is not one of them."""
+    from .api import protocol as P
+    from .api.tokenizer import load_tokenizer
+    if args.cmd == "encode-chat":
+        req = P.normalize_chat_request(json.loads(_read(args.request)))
+        text = P.render_chat(req)
+        tok = load_tokenizer(args.tokenizer, args.vocab)
+        ids = tok.encode(text)
+        print(json.dumps({"prompt": text, "tokens": ids, "n": len(ids), "images": len(P.image_parts(req.messages))}))
+        return 0
+    if args.cmd == "decode-tokens":
+        tok = load_tokenizer(args.tokenizer, args.vocab)
+        print(json.dumps({"text": tok.decode(json.loads(_read(args.tokens)))}))
+        return 0
+    if args.cmd == "parse-completion":
+        out = P.parse_completion(_read(args.text), not args.no_thinking, args.tools, "stop", 0, 0, "cli")
+        print(json.dumps(out))
+        return 0
+    if args.cmd == "config-validate":
+        cfg = ModelConfig.from_json(_read(args.config))
+        print(json.dumps({"ok": True, "name": cfg.name, "digest": cfg.digest(), "layers": cfg.n_layers,
+                          "experts": cfg.n_experts, "kv_bytes_per_token": cfg.window_kv_bytes}))
+        return 0
+    if args.cmd == "scan":
+        from .formats import layout
+        from .formats.safetensors import Checkpoint
+        ck = Checkpoint.scan(args.checkpoint)
+        out = {"tensors": len(ck.tensors), "bytes": sum(t.nbytes for t in ck.tensors.values()),
+               "dtypes": sorted({t.dtype for t in ck.tensors.values()})}
+        if args.preset or args.model_config:
+            layout.validate_checkpoint(ck, model_config(args))
+            out["matches_config"] = True
+        print(json.dumps(out))
+        return 0
+    if args.cmd == "smoke":
+        from .api.smoke import run as smoke_run
+        return smoke_run(args.url, args.api_key)
+    return None
+
+
 def main(argv: Optional[list] = None) -> int:
     args = build_parser().parse_args(argv)
+    if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke"):
+        return utility(args)
     if args.cmd == "probe":
         print(json.dumps(probe()))
         return 0
