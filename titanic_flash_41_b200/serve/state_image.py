@@ -67,6 +67,16 @@ class Image:
             h.copy_(t)
             moved.append((name, h))
         self.regions, self.tier = moved, "host"
+        self.release_pool()
+
+    def release_pool(self) -> None:
+        """Give a pooled image's chunks back (after its device copies are no longer needed)."""
+        rng = getattr(self, "_range", None)
+        if rng is not None:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            rng.free()
+            self._range = None
 
     def to_device(self, device) -> None:
         if self.tier == "disk":
@@ -76,10 +86,31 @@ class Image:
 
 
 def capture(tokens: Sequence[int], named: Sequence[Tuple[str, torch.Tensor]], kind: str = "complete",
-            media: str = "", meta: Optional[Dict[str, int]] = None) -> Image:
-    """Copy the given tensor views (any dtype/shape) into a new image on their own device."""
-    regs = [(n, t.contiguous().view(torch.uint8).reshape(-1).clone()) for n, t in named]
-    return Image(tuple(int(x) for x in tokens), regs, kind, media, dict(meta or {}))
+            media: str = "", meta: Optional[Dict[str, int]] = None, pool=None) -> Image:
+    """Copy the given tensor views (any dtype/shape) into a new image on their own device.
+
+    With ``pool`` (a ``utils.vmm.ChunkPool``) the image's regions are carved from ONE pooled range
+    (256-byte aligned slices), so saving and dropping images never touches the device heap; the
+    range goes back to the pool when the image leaves the device tier.  ``PoolExhausted``
+    propagates: the caller treats it like any other refused optional allocation."""
+    if pool is None:
+        regs = [(n, t.contiguous().view(torch.uint8).reshape(-1).clone()) for n, t in named]
+        return Image(tuple(int(x) for x in tokens), regs, kind, media, dict(meta or {}))
+    flats = [(n, t.contiguous().view(torch.uint8).reshape(-1)) for n, t in named]
+    offs, total = [], 0
+    for _, f in flats:
+        offs.append(total)
+        total += -(-int(f.numel()) // 256) * 256
+    rng = pool.alloc(max(total, 1))
+    whole = rng.tensor()
+    regs = []
+    for (n, f), o in zip(flats, offs):
+        dst = whole[o:o + f.numel()]
+        dst.copy_(f)
+        regs.append((n, dst))
+    img = Image(tuple(int(x) for x in tokens), regs, kind, media, dict(meta or {}))
+    img._range = rng
+    return img
 
 
 def restore_into(img: Image, targets: Dict[str, torch.Tensor]) -> None:
