@@ -58,12 +58,30 @@ def main():
         native.call("tf_smallm_gemm", 0, fw.q, None, fw.s, None, 0, 0, d, fw.s.shape[1], h16, d, yd, d * 2, 0, d * 2, d, T,
                     None, None, None, None, None, 1, 0, T, 0.0)
 
+    # FP8-activation variants on the quad-packed layout (random nibbles: packing them is a no-op for timing)
+    xq = torch.zeros(T, d, dtype=torch.uint8, device=dev)
+    xs = torch.zeros(T, device=dev)
+    aq = torch.zeros(npairs, I, dtype=torch.uint8, device=dev)
+    as_ = torch.zeros(npairs, device=dev)
+
+    def fc1_w4a8():
+        native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
+        native.call("tf_smallm_gemm_w4a8", w1, w3, s1, s3, I * (d // 2), I * (d // 32), d // 2, d // 32, xq, d, xs, act, I,
+                    1, I, d, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0)
+
+    def fc2_w4a8():
+        native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
+        native.call("tf_smallm_gemm_w4a8", w2, None, s2, None, d * (I // 2), d * (I // 32), I // 2, I // 32, aq, I, as_, y,
+                    d, 0, d, I, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0)
+
     print(f"# peaks ({pk['source']}): HBM {pk['hbm_gbs']} GB/s; {used} of {El} experts hit by {npairs} pairs")
     for name, fn, nbytes in (("moe_fc1_mxfp4_dual", fc1, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_mxfp4", fc2, used * d * (I // 2 + I // 32)),
+                             ("moe_fc1_w4a8_dual (+quant)", fc1_w4a8, used * 2 * I * (d // 2 + d // 32)),
+                             ("moe_fc2_w4a8 (+quant)", fc2_w4a8, used * d * (I // 2 + I // 32)),
                              ("dense_fp8_block128", dense, 2 * d * d + fw.s.numel() * 4)):
         med, best = time_cuda(fn, iters=a.iters)
-        print(f"{name:22s} {med * 1e3:8.1f} us  {nbytes / med / 1e6:8.1f} GB/s = "
+        print(f"{name:28s} {med * 1e3:8.1f} us  {nbytes / med / 1e6:8.1f} GB/s = "
               f"{nbytes / med / 1e6 / pk['hbm_gbs']:.2f} of {pk['source']} HBM copy bandwidth (best {best * 1e3:.1f} us)")
 
 

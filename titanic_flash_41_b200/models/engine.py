@@ -114,6 +114,20 @@ def quant_mxfp4_device(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return packed.contiguous(), code.contiguous()
 
 
+def quad_pack(p: torch.Tensor) -> torch.Tensor:
+    """Packed e2m1 [..., K/2] -> the decode kernels' layout: inside every 64-byte run (128 k = four
+    32-wide scale groups) the sixteen 4-byte words are transposed, so that the 16 bytes one lane
+    loads hold eight weights of EACH of the four groups and one FP8 tensor-core step covers exactly
+    one scale group (the B200 counterpart of the reference's expert repack, src/expert_packing.rs)."""
+    *lead, kb = p.shape
+    assert kb % 64 == 0
+    return p.reshape(*lead, kb // 64, 4, 4, 4).transpose(-3, -2).contiguous().reshape(*lead, kb)
+
+
+def quad_unpack(p: torch.Tensor) -> torch.Tensor:
+    return quad_pack(p)          # the word transpose is its own inverse
+
+
 def dequant_mxfp4(p: torch.Tensor, code: torch.Tensor) -> torch.Tensor:
     vals = torch.tensor(codecs.E2M1_VALUES, dtype=torch.float32, device=p.device)
     lo, hi = (p & 0xF).long(), (p >> 4).long()
