@@ -39,7 +39,7 @@ def main():
     native.call("tf_route_group", ids, npairs, 0, El, g_expert, g_start, g_count, n_groups, sorted_pairs, n_local)
     h16 = (torch.randn(T, d, device=dev, generator=g) * 0.5).half()
     act = torch.zeros(npairs, I, device=dev, dtype=torch.float16)
-    y = torch.zeros(npairs, d, device=dev, dtype=torch.float16)
+    y = torch.zeros(npairs, d, device=dev, dtype=torch.float32)      # the FC2 calls below ask for fp32 output
     slots = min(El, npairs)
     used = int(n_groups.item())
 
@@ -67,21 +67,48 @@ def main():
     def fc1_w4a8():
         native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
         native.call("tf_smallm_gemm_w4a8", w1, w3, s1, s3, I * (d // 2), I * (d // 32), d // 2, d // 32, xq, d, xs, act, I,
-                    1, I, d, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0)
+                    1, I, d, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0, 0)
 
     def fc2_w4a8():
         native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
         native.call("tf_smallm_gemm_w4a8", w2, None, s2, None, d * (I // 2), d * (I // 32), I // 2, I // 32, aq, I, as_, y,
-                    d, 0, d, I, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0)
+                    d, 0, d, I, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, 0)
+
+    def fc1_sm():
+        native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
+        native.call("tf_smallm_gemm_w4a8", w1, w3, s1, s3, I * (d // 2), I * (d // 32), 64, 4, xq, d, xs, act, I,
+                    1, I, d, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0, 1)
+
+    def fc2_sm():
+        native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
+        native.call("tf_smallm_gemm_w4a8", w2, None, s2, None, d * (I // 2), d * (I // 32), 64, 4, aq, I, as_, y,
+                    d, 0, d, I, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, 1)
+
+    stw = native.StatusWord(dev)
+
+    def fc1_tma():
+        native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
+        native.call("tf_moe_gemv_w4a8_tma", w1, w3, s1, s3, El, d // 2, d // 32, I * (d // 32), xq, d, xs, act, I, 1, I, d,
+                    g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0, stw.t)
+
+    def fc2_tma():
+        native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
+        native.call("tf_moe_gemv_w4a8_tma", w2, None, s2, None, El, I // 2, I // 32, d * (I // 32), aq, I, as_, y, d, 0, d, I,
+                    g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, stw.t)
 
     print(f"# peaks ({pk['source']}): HBM {pk['hbm_gbs']} GB/s; {used} of {El} experts hit by {npairs} pairs")
     for name, fn, nbytes in (("moe_fc1_mxfp4_dual", fc1, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_mxfp4", fc2, used * d * (I // 2 + I // 32)),
                              ("moe_fc1_w4a8_dual (+quant)", fc1_w4a8, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_w4a8 (+quant)", fc2_w4a8, used * d * (I // 2 + I // 32)),
+                             ("moe_fc1_w4a8 step-major (+quant)", fc1_sm, used * 2 * I * (d // 2 + d // 32)),
+                             ("moe_fc2_w4a8 step-major (+quant)", fc2_sm, used * d * (I // 2 + I // 32)),
+                             ("moe_fc1_w4a8_tma_dual (+quant)", fc1_tma, used * 2 * I * (d // 2 + d // 32)),
+                             ("moe_fc2_w4a8_tma (+quant)", fc2_tma, used * d * (I // 2 + I // 32)),
                              ("dense_fp8_block128", dense, 2 * d * d + fw.s.numel() * 4)):
         med, best = time_cuda(fn, iters=a.iters)
-        print(f"{name:28s} {med * 1e3:8.1f} us  {nbytes / med / 1e6:8.1f} GB/s = "
+        stw.check()
+        print(f"{name:32s} {med * 1e3:8.1f} us  {nbytes / med / 1e6:8.1f} GB/s = "
               f"{nbytes / med / 1e6 / pk['hbm_gbs']:.2f} of {pk['source']} HBM copy bandwidth (best {best * 1e3:.1f} us)")
 
 

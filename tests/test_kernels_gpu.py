@@ -321,8 +321,9 @@ def test_key_sharded_selection_equals_unsharded(world):
     assert torch.equal(ids, want)
 
 
-@pytest.mark.parametrize("dual,rows_per", [(True, 3), (False, 11), (True, 16)])
-def test_w4a8_expert_gemv_matches_reference(dual, rows_per):
+@pytest.mark.parametrize("tma", [False, True])
+@pytest.mark.parametrize("dual,rows_per", [(True, 3), (False, 11), (True, 16), (False, 40), (True, 40)])
+def test_w4a8_expert_gemv_matches_reference(dual, rows_per, tma):
     """Quad-packed MXFP4 weights x FP8 activations (m16n8k32 tensor-core steps, one scale group each)
     against fp32 math on the dequantised weights and the dequantised FP8 activations."""
     from titanic_flash_41_b200.models import engine as E
@@ -347,9 +348,17 @@ def test_w4a8_expert_gemv_matches_reference(dual, rows_per):
     xd = xq.view(torch.float8_e4m3fn).float().view(T, K // 8, 2, 4).transpose(2, 3).reshape(T, K) * xs[:, None]
     assert (xd - x.float()).abs().max() <= 0.07 * x.float().abs().max()
     y = torch.zeros(npairs, N, device=DEV)
-    native.call("tf_smallm_gemm_w4a8", E.quad_pack(p1), E.quad_pack(p3) if dual else None, s1, s3 if dual else None,
-                N * (K // 2), N * (K // 32), K // 2, K // 32, xq, K, xs, y, N, 0, N, K, 0, ge, gs, gc, ng, sp, k,
-                min(El, npairs), 10.0 if dual else 0.0)
+    if tma:
+        st = native.StatusWord(DEV)
+        native.call("tf_moe_gemv_w4a8_tma", E.quad_pack(p1), E.quad_pack(p3) if dual else None, s1, s3 if dual else None,
+                    El, K // 2, K // 32, N * (K // 32), xq, K, xs, y, N, 0, N, K, ge, gs, gc, ng, sp, k,
+                    min(El, npairs), 10.0 if dual else 0.0, st.t)
+        torch.cuda.synchronize()
+        st.check()
+    else:
+        native.call("tf_smallm_gemm_w4a8", E.quad_pack(p1), E.quad_pack(p3) if dual else None, s1, s3 if dual else None,
+                    N * (K // 2), N * (K // 32), K // 2, K // 32, xq, K, xs, y, N, 0, N, K, 0, ge, gs, gc, ng, sp, k,
+                    min(El, npairs), 10.0 if dual else 0.0, 0)
     torch.cuda.synchronize()
     for t in range(T):
         for j in range(k):

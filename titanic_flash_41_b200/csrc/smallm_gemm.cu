@@ -62,6 +62,10 @@ struct SmallMParams {
   // kind 3: X is e4m3 bytes (ldx in bytes), every 8 consecutive k stored as x0 x2 x4 x6 x1 x3 x5 x7,
   // with one fp32 scale per activation row
   const float* x_scale;
+  // kind 3: byte distance between consecutive 128-k steps of one weight row / of its scale word
+  // (64 and 4 = plain row-major; N*64 and N*4 = the k-step-major layout, where the 16 rows of a
+  // tile are adjacent and every step of a tile is one contiguous kilobyte)
+  long kstep, s_kstep;
 };
 
 // m16n8k32 e4m3 x e4m3 -> f32 with a zero C operand (each k32 step is one MXFP4 scale group,
@@ -248,10 +252,10 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
       uint32_t c0[NT], c8[NT];
 #pragma unroll
       for (int ti = 0; ti < NT; ++ti) {
-        w0[ti] = ld_stream(wrow0[ti] + (kb >> 1) + t * 16);
-        w8[ti] = ld_stream(wrow8[ti] + (kb >> 1) + t * 16);
-        c0[ti] = __ldg(reinterpret_cast<const uint32_t*>(srow0[ti] + (kb >> 5)));
-        c8[ti] = __ldg(reinterpret_cast<const uint32_t*>(srow8[ti] + (kb >> 5)));
+        w0[ti] = ld_stream(wrow0[ti] + (kb >> 7) * p.kstep + t * 16);
+        w8[ti] = ld_stream(wrow8[ti] + (kb >> 7) * p.kstep + t * 16);
+        c0[ti] = __ldg(reinterpret_cast<const uint32_t*>(srow0[ti] + (kb >> 7) * p.s_kstep));
+        c8[ti] = __ldg(reinterpret_cast<const uint32_t*>(srow8[ti] + (kb >> 7) * p.s_kstep));
       }
       uint2 xv[MT][4];
 #pragma unroll
@@ -396,7 +400,7 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 }
 
 template <int KIND, bool DUAL>
-__global__ void __launch_bounds__(kWarps * 32) smallm_gemm_kernel(SmallMParams p) {
+__global__ void __launch_bounds__(kWarps * 32, (KIND == 3 ? (DUAL ? 4 : 5) : 1)) smallm_gemm_kernel(SmallMParams p) {
   __shared__ float red[kWarps * (DUAL ? 4 : 2) * 2][32][4];
   __shared__ __align__(16) float ctile[(KIND == 0 && !DUAL) ? 32 * 32 : 4];
   float* tile_out = (KIND == 0 && !DUAL && p.use_comm) ? ctile : nullptr;
@@ -516,6 +520,7 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
   p.use_comm = 0;
   p.x_scale = nullptr;
+  p.kstep = 64; p.s_kstep = 4;
   const bool dual = W3 != nullptr;
   cudaError_t e;
   if (kind == 0) e = dual ? launch<0, true>(p, slots, stream) : launch<0, false>(p, slots, stream);
@@ -527,12 +532,13 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
 
 // Routed-expert GEMV with FP8 activations: W / W3 are MXFP4 in the quad-packed layout (see the
 // kind-3 loop), X is the output of tf_quant_rows_e4m3_perm ([rows, K] bytes, ldx in bytes) with
-// its per-row scales.  Other arguments as tf_smallm_gemm (grouped form).
+// its per-row scales.  Other arguments as tf_smallm_gemm (grouped form).  With `step_major` the caller
+// passes ldw = 64, lds = 4 and the k-step-major layout described at SmallMParams::kstep.
 TF_API int tf_smallm_gemm_w4a8(const void* W, const void* W3, const void* S, const void* S3, long w_group_stride,
                                long s_group_stride, int ldw, int lds, const void* X, int ldx, const float* x_scale,
                                void* Y, int ldy, int out_kind, int N, int K, int M, const int* group_expert,
                                const int* group_start, const int* group_count, const int* n_groups,
-                               const int* sorted_pairs, int x_div, int slots, float swiglu_limit,
+                               const int* sorted_pairs, int x_div, int slots, float swiglu_limit, int step_major,
                                cudaStream_t stream) {
   if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0 || (ldw % 16) != 0 || (lds % 4) != 0 || !x_scale) return -1;
   SmallMParams p;
@@ -546,6 +552,9 @@ TF_API int tf_smallm_gemm_w4a8(const void* W, const void* W3, const void* S, con
   p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
   p.use_comm = 0;
   p.x_scale = x_scale;
+  // step_major: W is [experts][K/128][N][64 B] and S [experts][K/128][N][4 B]; ldw / lds are then 64 / 4
+  p.kstep = step_major ? (long)N * 64 : 64;
+  p.s_kstep = step_major ? (long)N * 4 : 4;
   return (int)(W3 ? launch<3, true>(p, slots, stream) : launch<3, false>(p, slots, stream));
 }
 
@@ -577,6 +586,7 @@ TF_API int tf_smallm_gemm_allreduce(const void* W, const void* S, int ldw, int l
   p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
   p.use_comm = 1;
   p.x_scale = nullptr;
+  p.kstep = 64; p.s_kstep = 4;
   p.comm.peers = (const unsigned long long*)peers; p.comm.world = world; p.comm.rank = rank;
   p.comm.tiles = N / kTileN; p.comm.max_rows = max_rows; p.comm.N = N; p.comm.epoch = (unsigned int*)epoch;
   p.comm.flag_bytes = flag_bytes; p.comm.spin_limit = spin_limit; p.comm.st = (TfStatusWord*)status;
