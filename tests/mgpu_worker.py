@@ -69,7 +69,9 @@ def main():
                        draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
     ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,))
-    eng = E.Engine.from_weights(cfg, ecfg, W, comm=comm, device=dev)
+    # the TP engine also splits index scoring by key range from 8 keys on (decode rows)
+    ecfg_tp = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,), key_sharded_index_min=8)
+    eng = E.Engine.from_weights(cfg, ecfg_tp, W, comm=comm, device=dev)
     eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev, spin_limit=2_000_000)
     ref = E.Engine.from_weights(cfg, ecfg, W, comm=LocalComm(), device=dev)
     gen = torch.Generator().manual_seed(3)

@@ -314,6 +314,7 @@ class EngineConfig(_JsonMixin):
     prefill_slice_ms: int = 500
     spin_limit: int = 20_000_000       # bounded device waits (reference src/roce.rs:1196-1199)
     use_cuda_graphs: bool = True
+    key_sharded_index_min: int = 8192  # decode rows: split index scoring over the ranks from this many keys (0 = never)
     seed: int = 0
 
 

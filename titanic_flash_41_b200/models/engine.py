@@ -588,6 +588,17 @@ class Engine:
             selcnt.zero_()
             return
         scores = self.scores_buffer(T, nmax)
+        ks_min = self.ecfg.key_sharded_index_min
+        if self.world > 1 and ks_min > 0 and T <= self.SMALL_M and nmax >= ks_min:
+            # every rank holds all index keys: split the scoring work by key range, gather the local
+            # top-k (score, id) pairs and select the global top-k from them (identical result)
+            from ..parallel import key_sharded as KS
+            ids, cnt = KS.select(b["iq"], b["iw"], region, nvalid, self.keys[sslot], self.keys[sslot].stride(0),
+                                 self.key_row, T, cfg.index_heads, cfg.index_dim, rows_per_group, scores, nmax,
+                                 cfg.index_topk, self.rank, self.world, lambda t: self.comm.all_gather(t, dim=1))
+            sel[:T].copy_(ids)
+            selcnt[:T].copy_(cnt)
+            return
         native.call("tf_index_scores", b["iq"], b["iw"], region, nvalid, self.keys[sslot],
                     self.keys[sslot].stride(0), self.key_row, T, cfg.index_heads, cfg.index_dim,
                     rows_per_group, scores, scores.stride(0), 0, nmax)
