@@ -75,3 +75,26 @@ def test_checkpoint_placement_rules():
     assert P.common_prefix(list(range(10000)), list(range(9000)) + [1]) == 9000
     assert P.cache_capacity(6, 7, 2, 1, 16, 1, 1) == (4, 14)
     assert P.reload_pays(100 << 20, 100000) and not P.reload_pays(100 << 20, 100)
+
+
+def test_draw_trace_and_logit_export(tmp_path):
+    import numpy as np
+    import torch
+    from titanic_flash_41_b200.utils.trace import DrawTrace, LogitExport, RouteCensus
+    dt = DrawTrace(capacity=16)
+    for i in range(40):
+        dt.add(position=i, accepted=i % 4, token=i)
+    assert len(dt.records) <= 16 and sum(dt.acceptance_histogram().values()) == len(dt.records)
+    p = str(tmp_path / "t.jsonl")
+    dt.dump(p)
+    assert len(open(p).read().splitlines()) == len(dt.records)
+    le = LogitExport(str(tmp_path / "l.npz"), limit=2)
+    for pos in (5, 3, 9):
+        le.add(pos, torch.arange(4.0) + pos)
+    assert le.save() == 2
+    z = np.load(str(tmp_path / "l.npz"))
+    assert z["positions"].tolist() == [3, 5] and z["logits"].shape == (2, 4)
+    rc = RouteCensus(8)
+    rc.add(torch.tensor([[0, 1], [1, 7], [1, -1]]))
+    s = rc.summary()
+    assert s["total"] == 5 and s["top"][0] == 1 and s["unused"] == 5

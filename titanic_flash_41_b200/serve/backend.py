@@ -153,6 +153,7 @@ class EngineBackend:
         if engine.big_gemm is None:
             bigpath.attach(engine)
         self._dec: Dict[Tuple[int, float, float], object] = {}
+        self.max_graph_variants = 8      # (sessions, temperature, top-p) decoders kept with their CUDA graphs
         self._SpecDecoder, self._native = SpecDecoder, native
         self.last_hidden_rows: Dict[int, torch.Tensor] = {}
 
@@ -176,11 +177,14 @@ class EngineBackend:
 
     def decode_step(self, slots):
         key = (len(slots), slots[0].temperature, slots[0].top_p)
-        dec = self._dec.get(key)
+        dec = self._dec.pop(key, None)
         if dec is None:
             dec = self._SpecDecoder(self.e, len(slots), temperature=max(slots[0].temperature, 1e-3),
                                     top_p=slots[0].top_p)
-            self._dec[key] = dec
+            # bounded retention of captured graph variants (least recently used goes first)
+            while len(self._dec) >= self.max_graph_variants:
+                self._dec.pop(next(iter(self._dec)))
+        self._dec[key] = dec                     # most recently used last
         for i, s in enumerate(slots):
             h = self.last_hidden_rows.get(s.region)
             if h is not None:

@@ -111,3 +111,49 @@ class RouteCensus:
         mean = float(c.mean()) or 1.0
         return {"total": int(c.sum()), "max_over_mean": float(c.max()) / mean, "unused": int((c == 0).sum()),
                 "top": [int(i) for i in torch.topk(c, min(8, c.numel())).indices]}
+
+
+class LogitExport:
+    """Keeps the raw logits of chosen positions for offline divergence studies and writes them as
+    one ``.npz`` (reference: src/logit_export.rs).  Off unless constructed."""
+
+    def __init__(self, path: str, limit: int = 4096):
+        self.path, self.limit = path, limit
+        self.rows: Dict[int, "torch.Tensor"] = {}
+
+    def add(self, position: int, logits: torch.Tensor) -> None:
+        if len(self.rows) < self.limit:
+            self.rows[int(position)] = logits.detach().float().cpu().reshape(-1).clone()
+
+    def save(self) -> int:
+        import numpy as np
+        pos = sorted(self.rows)
+        np.savez_compressed(self.path, positions=np.asarray(pos, dtype=np.int64),
+                            logits=np.stack([self.rows[p].numpy() for p in pos]) if pos else np.zeros((0, 0), np.float32))
+        return len(pos)
+
+
+class DrawTrace:
+    """One record per speculative step and conversation: position, proposals, uniforms used, accepted
+    count and the committed token (reference: src/draw_trace.rs).  Bounded ring."""
+
+    def __init__(self, capacity: int = 65536):
+        self.capacity = capacity
+        self.records: List[dict] = []
+
+    def add(self, **rec) -> None:
+        if len(self.records) >= self.capacity:
+            del self.records[: self.capacity // 8]
+        self.records.append(rec)
+
+    def acceptance_histogram(self) -> Dict[int, int]:
+        h: Dict[int, int] = defaultdict(int)
+        for r in self.records:
+            h[int(r.get("accepted", 0))] += 1
+        return dict(h)
+
+    def dump(self, path: str) -> None:
+        import json
+        with open(path, "w") as f:
+            for r in self.records:
+                f.write(json.dumps(r) + "\n")
