@@ -369,3 +369,45 @@ def test_w4a8_expert_gemv_matches_reference(dual, rows_per, tma):
                 a = torch.nn.functional.silu(a.clamp(max=10)) * up
             got = y[t * k + j]
             assert (got - a).abs().max() <= 2e-3 * a.abs().max() + 1e-4, (t, j)
+
+
+def test_two_level_candidates_match_dense_selection():
+    """Sparse scores equal the dense ones at the candidate keys, and selecting among the published
+    blocks gives the dense top-k whenever all of it lies inside them."""
+    from titanic_flash_41_b200.ops import two_level as TL
+    torch.manual_seed(11)
+    T, Hi, Di, C, k = 5, 8, 128, 4000, 64
+    krow = Di // 2 + Di // 32
+    keys = codecs.index_key_encode(torch.randn(1, C, Di)).to(DEV).contiguous()
+    q = torch.randn(T, Hi, Di, device=DEV).bfloat16()
+    w = torch.rand(T, Hi, device=DEV)
+    region = torch.zeros(T, dtype=torch.int32, device=DEV)
+    nvalid = torch.tensor([4000, 3001, 517, 64, 9], dtype=torch.int32, device=DEV)
+    lds = 4096
+    scores = torch.zeros(T, lds, device=DEV)
+    native.call("tf_index_scores", q, w, region, nvalid, keys, C * krow, krow, T, Hi, Di, 1, scores, lds, 0, C)
+    want = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    wcnt = torch.zeros(T, dtype=torch.int32, device=DEV)
+    native.call("tf_topk_select", scores, lds, nvalid, k, want, wcnt, None, 0, T)
+    cand = TL.publish(scores[:, :C], nvalid, n_blocks=128, T=T)
+    assert cand.shape == (T, 1024)
+    for r in range(T):
+        c = cand[r][cand[r] >= 0]
+        assert bool((c[1:] > c[:-1]).all()) and int(c.max()) < int(nvalid[r])
+    sc = torch.empty(T, cand.shape[1], device=DEV)
+    native.call("tf_index_scores_sparse", q, w, region, cand, cand.stride(0), keys, C * krow, krow, T, Hi, Di,
+                cand.shape[1], sc, cand.shape[1])
+    torch.cuda.synchronize()
+    ok = cand >= 0
+    dense_at = torch.gather(scores, 1, cand.clamp_min(0).long())
+    assert (sc[ok] - dense_at[ok]).abs().max() <= 1e-3 * dense_at[ok].abs().max() + 1e-5
+    assert bool(torch.isinf(sc[~ok]).all())
+    ids, cnt = TL.consume(q, w, region, cand, keys, C * krow, krow, T, Hi, Di, k)
+    assert torch.equal(cnt, wcnt)
+    # the best 64 keys sit in the best 128 blocks of 8 (every top key's block maximum is at least its own
+    # score); the two scorings may only disagree about keys that tie with the cut within rounding
+    for r in range(T):
+        a, b = set(ids[r][ids[r] >= 0].tolist()), set(want[r][want[r] >= 0].tolist())
+        if a != b:
+            cut = min(float(scores[r, i]) for i in b)
+            assert all(abs(float(scores[r, i]) - cut) <= 1e-3 * abs(cut) + 1e-5 for i in a ^ b), r

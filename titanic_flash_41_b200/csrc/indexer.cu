@@ -296,6 +296,67 @@ __global__ void map_ids_kernel(const int* __restrict__ picked, const int* __rest
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// two-level selection: block maxima of a source layer's scores, and scoring of candidate keys only
+// ---------------------------------------------------------------------------------------------
+// bmax[r, j] = max of scores[r, 8j .. 8j+7] over valid keys (-inf when none)
+__global__ void __launch_bounds__(256) index_block_max_kernel(const float* __restrict__ scores, int lds,
+                                                              const int* __restrict__ nvalid,
+                                                              float* __restrict__ bmax, int ldb, int nblk) {
+  const int r = blockIdx.y, j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= nblk) return;
+  const int nv = nvalid[r];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = 8 * j + i;
+    if (k < nv) m = fmaxf(m, scores[(long)r * lds + k]);
+  }
+  bmax[(long)r * ldb + j] = m;
+}
+
+// one warp per (row, candidate): the key is decoded exactly as in the dense kernel (value * scale
+// rounded to f16, query rounded to f16), products accumulate in fp32
+template <int DI>
+__global__ void __launch_bounds__(256) index_scores_sparse_kernel(const __nv_bfloat16* __restrict__ q,
+                                                                  const float* __restrict__ w,
+                                                                  const int* __restrict__ region,
+                                                                  const int* __restrict__ cand, int ldc,
+                                                                  const uint8_t* __restrict__ keys,
+                                                                  long key_region_stride, int key_row, int Hi,
+                                                                  int C, float* __restrict__ out, int ldo) {
+  constexpr int PER = DI / 32;                       // dims per lane
+  const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 8 + warp;
+  if (c >= C) return;
+  const int id = cand[(long)r * ldc + c];
+  if (id < 0) {
+    if (lane == 0) out[(long)r * ldo + c] = -INFINITY;
+    return;
+  }
+  const uint8_t* row = keys + (long)region[r] * key_region_stride + (long)id * key_row;
+  float kv[PER];
+  const int d0 = lane * PER;
+  const float sc = ue8m0_to_float(row[DI / 2 + d0 / 32]);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int d = d0 + i;
+    const uint8_t b = row[d >> 1];
+    kv[i] = __half2float(__float2half_rn(e2m1_to_float((d & 1) ? (b >> 4) : (b & 0xf)) * sc));
+  }
+  float total = 0.f;
+  for (int h = 0; h < Hi; ++h) {
+    const __nv_bfloat16* qh = q + ((long)r * Hi + h) * DI + d0;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc = fmaf(__half2float(__float2half_rn(__bfloat162float(qh[i]))), kv[i], acc);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    total += fmaxf(acc, 0.f) * w[(long)r * Hi + h];
+  }
+  if (lane == 0) out[(long)r * ldo + c] = total;
+}
+
 }  // namespace
 
 TF_API int tf_index_scores(const void* q, const float* w, const int* region, const int* nvalid,
@@ -326,5 +387,29 @@ TF_API int tf_topk_select(const float* scores, int lds, const int* nvalid, int k
 TF_API int tf_map_ids(const int* picked, const int* cand_ids, int ldc, int k, int* out, int T,
                       cudaStream_t st) {
   map_ids_kernel<<<T, 256, 0, st>>>(picked, cand_ids, ldc, k, out);
+  return (int)cudaGetLastError();
+}
+
+// block maxima over blocks of 8 keys (two-level candidates: reference src/candidates.rs:1-20)
+TF_API int tf_index_block_max(const float* scores, int lds, const int* nvalid, float* bmax, int ldb, int nblk, int T,
+                              cudaStream_t st) {
+  if (T <= 0 || nblk <= 0) return 0;
+  index_block_max_kernel<<<dim3((nblk + 255) / 256, T), 256, 0, st>>>(scores, lds, nvalid, bmax, ldb, nblk);
+  return (int)cudaGetLastError();
+}
+
+// scores of candidate keys only: cand [T, C] key ids (-1 = none) -> out [T, C] (-inf for none)
+TF_API int tf_index_scores_sparse(const void* q, const float* w, const int* region, const int* cand, int ldc,
+                                  const void* keys, long key_region_stride, int key_row, int T, int Hi, int Di, int C,
+                                  float* out, int ldo, cudaStream_t st) {
+  if (T <= 0 || C <= 0) return 0;
+  dim3 grid((C + 7) / 8, T);
+  if (Di == 128)
+    index_scores_sparse_kernel<128><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, w, region, cand, ldc,
+                                                          (const uint8_t*)keys, key_region_stride, key_row, Hi, C, out, ldo);
+  else if (Di == 64)
+    index_scores_sparse_kernel<64><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, w, region, cand, ldc,
+                                                         (const uint8_t*)keys, key_region_stride, key_row, Hi, C, out, ldo);
+  else return -1;
   return (int)cudaGetLastError();
 }
