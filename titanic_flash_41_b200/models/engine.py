@@ -72,6 +72,11 @@ class LayerWeights:
     is_index_source: bool = False
     kv_source: int = -1
     index_source: int = -1
+    # geometry of the reference model proper (reference: src/layout.rs:57-144)
+    q_norm: Optional[torch.Tensor] = None          # low-rank query: proj holds wq_a, then norm, then wq_b
+    wq_b: Optional[Fp8Weight] = None
+    wo_a: Optional[List[Fp8Weight]] = None         # grouped output projection: one [rank, per] per local group
+    hc: Optional[Dict[str, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]] = None   # "attn"/"ffn" -> (fn, base, scale)
 
 
 def quant_fp8_device(w: torch.Tensor) -> Fp8Weight:
@@ -146,8 +151,6 @@ def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: i
                   device, roundtrip: Optional[Dict[str, torch.Tensor]] = None) -> LayerWeights:
     """Quantise one layer's shard from an fp32/bf16 weight dict (full, unsharded tensors) and, when
     ``roundtrip`` is given, record the dequantised full tensors there for the oracle."""
-    assert cfg.q_lora_rank == 0 and cfg.o_groups == 0 and cfg.hc_mult == 1, \
-        "CUDA engine covers the direct-projection geometry; LoRA/mHC variants run on the oracle path"
     p = _layer_prefix(cfg, li)
     draft = li >= cfg.n_layers
     H, Dh, d = cfg.n_heads, cfg.head_dim, cfg.hidden
@@ -167,9 +170,19 @@ def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: i
             roundtrip[name] = dequant_fp8(full_q).cpu()
 
     segs: List[Tuple[str, torch.Tensor]] = []
-    wq = dev(W[f"{p}.attn.wq.weight"])
-    rt(f"{p}.attn.wq.weight", quant_fp8_device(wq))
-    segs.append(("q", wq[rank * Hl * Dh:(rank + 1) * Hl * Dh]))
+    if cfg.q_lora_rank:
+        # low-rank query: wq_a (replicated) rides in the fused projection, wq_b keeps this rank's heads
+        wqa = dev(W[f"{p}.attn.wq_a.weight"])
+        rt(f"{p}.attn.wq_a.weight", quant_fp8_device(wqa))
+        segs.append(("qa", wqa))
+        wqb = dev(W[f"{p}.attn.wq_b.weight"])
+        rt(f"{p}.attn.wq_b.weight", quant_fp8_device(wqb))
+        L.wq_b = quant_fp8_device(wqb[rank * Hl * Dh:(rank + 1) * Hl * Dh].contiguous())
+        L.q_norm = dev(W[f"{p}.attn.q_norm.weight"], torch.bfloat16)
+    else:
+        wq = dev(W[f"{p}.attn.wq.weight"])
+        rt(f"{p}.attn.wq.weight", quant_fp8_device(wq))
+        segs.append(("q", wq[rank * Hl * Dh:(rank + 1) * Hl * Dh]))
     segs.append(("kv", dev(W[f"{p}.attn.wkv.weight"])))
     rt(f"{p}.attn.wkv.weight", quant_fp8_device(segs[-1][1]))
     if L.is_kv_source:
@@ -189,9 +202,24 @@ def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: i
         qs.append(fw.q)
         ss.append(fw.s)
     L.proj = Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d)
-    wo = dev(W[f"{p}.attn.wo.weight"])
-    rt(f"{p}.attn.wo.weight", quant_fp8_device(wo))
-    L.wo = quant_fp8_device(wo[:, rank * Hl * Dh:(rank + 1) * Hl * Dh].contiguous())
+    if cfg.o_groups:
+        # grouped low-rank output projection: this rank's groups of wo_a (block-diagonal), then the
+        # matching K-slice of wo_b
+        G, R = cfg.o_groups // world, cfg.o_lora_rank
+        woa = dev(W[f"{p}.attn.wo_a.weight"])                    # [o_groups * R, H*Dh / o_groups]
+        rt(f"{p}.attn.wo_a.weight", quant_fp8_device(woa))
+        L.wo_a = [quant_fp8_device(woa[(rank * G + g) * R:(rank * G + g + 1) * R].contiguous()) for g in range(G)]
+        wob = dev(W[f"{p}.attn.wo_b.weight"])                    # [d, o_groups * R]
+        rt(f"{p}.attn.wo_b.weight", quant_fp8_device(wob))
+        L.wo = quant_fp8_device(wob[:, rank * G * R:(rank + 1) * G * R].contiguous())
+    else:
+        wo = dev(W[f"{p}.attn.wo.weight"])
+        rt(f"{p}.attn.wo.weight", quant_fp8_device(wo))
+        L.wo = quant_fp8_device(wo[:, rank * Hl * Dh:(rank + 1) * Hl * Dh].contiguous())
+    if cfg.hc_mult > 1:
+        L.hc = {br: (dev(W[f"{p}.hc_{br}_fn"], torch.float32).contiguous(),
+                     dev(W[f"{p}.hc_{br}_base"], torch.float32).contiguous(),
+                     dev(W[f"{p}.hc_{br}_scale"], torch.float32).contiguous()) for br in ("attn", "ffn")}
     L.attn_norm = dev(W[f"{p}.attn_norm.weight"], torch.bfloat16)
     L.ffn_norm = dev(W[f"{p}.ffn_norm.weight"], torch.bfloat16)
     L.kv_norm = dev(W[f"{p}.attn.kv_norm.weight"], torch.bfloat16)
@@ -241,7 +269,12 @@ def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed:
     def rnd(n, k, std=None):
         return torch.randn(n, k, generator=g, device=device, dtype=torch.bfloat16) * (std or cfg.init_std)
 
-    segs = [("q", rnd(Hl * Dh, d)), ("kv", rnd(Dh, d))]
+    if cfg.q_lora_rank:
+        segs = [("qa", rnd(cfg.q_lora_rank, d)), ("kv", rnd(Dh, d))]
+        L.wq_b = quant_fp8_device(rnd(Hl * Dh, cfg.q_lora_rank))
+        L.q_norm = torch.ones(cfg.q_lora_rank, dtype=torch.bfloat16, device=device)
+    else:
+        segs = [("q", rnd(Hl * Dh, d)), ("kv", rnd(Dh, d))]
     if L.is_kv_source:
         segs += [("cv", rnd(Dh + cfg.index_dim, d)), ("cg", rnd(Dh + cfg.index_dim, d))]
     if L.is_index_source:
@@ -254,7 +287,16 @@ def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed:
         qs.append(fw.q)
         ss.append(fw.s)
     L.proj = Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d)
-    L.wo = quant_fp8_device(rnd(d, Hl * Dh))
+    if cfg.o_groups:
+        G, R = cfg.o_groups // world, cfg.o_lora_rank
+        L.wo_a = [quant_fp8_device(rnd(R, Hl * Dh // G)) for _ in range(G)]
+        L.wo = quant_fp8_device(rnd(d, G * R))
+    else:
+        L.wo = quant_fp8_device(rnd(d, Hl * Dh))
+    if cfg.hc_mult > 1:
+        m = cfg.hc_mult
+        L.hc = {br: ((torch.randn(m * (2 + m), m * d, generator=g, device=device) * cfg.init_std).contiguous(),
+                     torch.zeros(m * (2 + m), device=device), torch.ones(3, device=device)) for br in ("attn", "ffn")}
     ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
     L.attn_norm, L.ffn_norm, L.kv_norm = ones(d), ones(d), ones(Dh)
     if L.is_kv_source:
@@ -390,6 +432,9 @@ class Engine:
                 roundtrip["mtp.0.main_proj.weight"] = dequant_fp8(mp).cpu()
             extra = dict(main_proj=mp, enorm=W["mtp.0.enorm.weight"].to(device, torch.bfloat16),
                          hnorm=W["mtp.0.hnorm.weight"].to(device, torch.bfloat16))
+        if cfg.hc_mult > 1:
+            extra = dict(extra, hc_head=tuple(W[k].to(device, torch.float32).contiguous()
+                                              for k in ("hc_head_fn", "hc_head_base", "hc_head_scale")))
         V = cfg.vocab
         Vl = V // comm.world
         embed = W["embed.weight"].to(device, torch.bfloat16).contiguous()
@@ -424,6 +469,10 @@ class Engine:
         head = torch.randn(Vl, d, generator=g, device=device, dtype=torch.bfloat16) * cfg.init_std
         if cfg.draft is not None and Vl % 128 == 0:
             extra["head"] = quant_fp8_device(head)     # the draft reads an FP8 copy of the head
+        if cfg.hc_mult > 1:
+            m = cfg.hc_mult
+            extra["hc_head"] = ((torch.randn(m, m * d, generator=g, device=device) * cfg.init_std).contiguous(),
+                                torch.zeros(m, device=device), torch.ones(1, device=device))
         return cls(cfg, ecfg, layers, embed, head, torch.ones(d, dtype=torch.bfloat16, device=device),
                    comm, device, max_chunk, drafts, extra)
 
@@ -437,6 +486,9 @@ class Engine:
         f32 = dict(dtype=torch.float32, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
         maxN = max(l.proj.q.shape[0] for l in self.layers + self.draft_layers)
+        self.q_col = maxN                      # low-rank query: wq_b's output lands behind the fused projection
+        if cfg.q_lora_rank:
+            maxN += Hl * Dh
         npairs = T * cfg.topk
         nsplit = self._nsplit(T)
         big = T > self.SMALL_M and getattr(self, "big_moe_full", None) is not None
@@ -467,6 +519,19 @@ class Engine:
             s_act=torch.zeros(T, max(Il, 1), dtype=torch.float16, device=dev),
             s_y=torch.zeros(T, d, **f32),
         )
+        m = cfg.hc_mult
+        if m > 1:
+            # the residual stream is m copies per row; b["x"] is their flat [T, m*d] view
+            b["x"] = torch.zeros(T, m * d, dtype=torch.bfloat16, device=dev)
+            b["x2"] = torch.zeros(T, m * d, dtype=torch.bfloat16, device=dev)
+            b["e"] = torch.zeros(T, d, dtype=torch.bfloat16, device=dev)
+            b["v"] = torch.zeros(T, d, dtype=torch.bfloat16, device=dev)
+            b["coef"] = torch.zeros(T, native.lib().tf_hc_coef_bytes(), dtype=torch.uint8, device=dev)
+        if cfg.q_lora_rank:
+            b["qa16"] = torch.zeros(T, cfg.q_lora_rank, dtype=torch.float16, device=dev)
+            b["qfull"] = torch.zeros(T, Hl * Dh, dtype=b["P"].dtype, device=dev)
+        if cfg.o_groups:
+            b["mid16"] = torch.zeros(T, (cfg.o_groups // self.world) * cfg.o_lora_rank, dtype=torch.float16, device=dev)
         self._scratch[T] = b
         return b
 
@@ -528,19 +593,28 @@ class Engine:
         d, Dh, Hl = cfg.hidden, cfg.head_dim, self.Hl
         pos, region, first_row, last_pos, nvalid = (b["meta"][i] for i in (1, 2, 3, 4, 5))
         # boundary: x += delta (previous sublayer); h = rmsnorm(x)
+        hc = cfg.hc_mult > 1
         if first:
             b["pending"] = False
-        native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, L.attn_norm, b["h16"],
-                    None, None, None, T, d, cfg.rms_eps)
+        self._boundary(L, "attn", T, b, want_hb=False)
         N = L.proj.q.shape[0]
         P = b["P"]
         self._linear(b["h16"], L.proj, P, T)
         o = L.offs
+        q_off = o.get("q", -1)
+        if cfg.q_lora_rank:
+            # low-rank query: RMSNorm of the wq_a output, then this rank's heads through wq_b
+            R = cfg.q_lora_rank
+            qa = P[:T, o["qa"]:o["qa"] + R].float()
+            qa = qa * torch.rsqrt(qa.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * L.q_norm.float()
+            b["qa16"][:T].copy_(qa)
+            q_off = self.q_col
+            self._linear(b["qa16"], L.wq_b, P[:, q_off:q_off + Hl * Dh], T)
         slot = self.src_slot.get(li, 0)
         native.call("tf_attn_prep", P, 0 if P.dtype == torch.float32 else 1, P.stride(0), T, pos, region, first_row, last_pos, Hl, Dh,
                     cfg.rope.dim, self.freqs, self.cfreqs, L.kv_norm, cfg.rms_eps, b["q"], self.win[li],
                     self.win[li].stride(0), self.win_row, self.comp_row, self.key_row, self.ring,
-                    o["q"], o["kv"], o.get("cv", -1), o.get("cg", -1), o.get("iq", -1), o.get("iw", -1),
+                    q_off, o["kv"], o.get("cv", -1), o.get("cg", -1), o.get("iq", -1), o.get("iw", -1),
                     cfg.compress_ratio, cfg.index_dim, cfg.index_heads, L.comp_norm,
                     self.carry[slot] if L.is_kv_source else None,
                     self.comp[slot] if L.is_kv_source else None,
@@ -562,21 +636,61 @@ class Engine:
                     b["part_lse"], L.sink, self.freqs, cfg.rope.dim, b["a16"], None, Hl * Dh,
                     self.status.t)
         fused = self.symm is not None and T <= self.SMALL_M
-        if fused:
+        wo_in = b["a16"]
+        if cfg.o_groups:
+            # grouped low-rank output projection: block-diagonal wo_a per local head group, then wo_b
+            G, R = cfg.o_groups // self.world, cfg.o_lora_rank
+            per = Hl * Dh // G
+            for g in range(G):
+                self._linear(b["a16"][:, g * per:(g + 1) * per], L.wo_a[g], b["mid16"][:, g * R:(g + 1) * R], T)
+            wo_in = b["mid16"]
+        if hc:
+            # the reduced sublayer output goes through the hc post-mix instead of a plain add
+            if fused:
+                self.symm.gemv_allreduce(L.wo, wo_in, T, None, b["delta"], self.status.t)
+            else:
+                self._linear(wo_in, L.wo, b["delta"], T)
+                self._allreduce(b["delta"][:T])
+            self._hc_post(T, b)
+        elif fused:
             # WO projection + all-reduce + residual add in one kernel over peer memory
-            self.symm.gemv_allreduce(L.wo, b["a16"], T, b["x"], None, self.status.t)
+            self.symm.gemv_allreduce(L.wo, wo_in, T, b["x"], None, self.status.t)
             b["pending"] = False
         else:
-            self._linear(b["a16"], L.wo, b["delta"], T)
+            self._linear(wo_in, L.wo, b["delta"], T)
             self._allreduce(b["delta"][:T])
             b["pending"] = True
         # FFN boundary
-        native.call("tf_add_norm", b["x"], b["delta"] if b["pending"] else None, 0, d, L.ffn_norm, b["h16"],
-                    b["hb"], None, None, T, d, cfg.rms_eps)
+        self._boundary(L, "ffn", T, b, want_hb=True)
         self._moe(L, T, b)
-        if not fused:
+        if hc:
+            if not (fused and T <= self.SMALL_M):
+                self._allreduce(b["delta"][:T])
+            self._hc_post(T, b)
+        elif not fused:
             self._allreduce(b["delta"][:T])
             b["pending"] = True
+
+    def _boundary(self, L: LayerWeights, br: str, T: int, b: dict, want_hb: bool) -> None:
+        """Sublayer input: residual (+ pending sublayer output) -> RMSNorm, or with hc_mult > 1 the
+        pre-mix collapse of the residual copies -> RMSNorm.  Fills b["h16"] (and b["hb"])."""
+        cfg = self.cfg
+        d = cfg.hidden
+        norm_w = L.attn_norm if br == "attn" else L.ffn_norm
+        if cfg.hc_mult > 1:
+            fn, base, scale = L.hc[br]
+            native.call("tf_hc_prepare", b["x"], fn, base, scale, b["coef"], b["v"], norm_w, b["h16"],
+                        b["hb"] if want_hb else None, T, cfg.hc_mult, d, cfg.sinkhorn_iters, cfg.hc_eps, cfg.rms_eps)
+            return
+        native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, norm_w, b["h16"],
+                    b["hb"] if want_hb else None, None, None, T, d, cfg.rms_eps)
+
+    def _hc_post(self, T: int, b: dict) -> None:
+        """New residual copies from the reduced sublayer output in b["delta"] and the coefficients of
+        the boundary that fed the sublayer."""
+        native.call("tf_hc_post", b["x"], b["delta"], b["coef"], b["x2"], T, self.cfg.hc_mult, self.cfg.hidden)
+        b["x"], b["x2"] = b["x2"], b["x"]
+        b["pending"] = False
 
     def _index(self, L: LayerWeights, T: int, b: dict, nmax: int, rows_per_group: int, sslot: int,
                li: int) -> None:
@@ -650,8 +764,10 @@ class Engine:
             shared = b["s_y"]
         if self.symm is not None and T <= self.SMALL_M:
             # expert combine + shared expert + all-reduce + residual add in one kernel
+            hc = cfg.hc_mult > 1
             self.symm.combine_allreduce(b["y_pair"], b["ids"], b["wts"], shared, T, cfg.topk, e_lo,
-                                        e_lo + self.El, b["x"], None, self.status.t)
+                                        e_lo + self.El, None if hc else b["x"], b["delta"] if hc else None,
+                                        self.status.t)
             b["pending"] = False
             return
         native.call("tf_moe_combine", b["y_pair"], b["ids"], b["wts"], shared, b["delta"], T, d,
@@ -714,10 +830,14 @@ class Engine:
         cfg = self.cfg
         layer_hi = len(self.layers) if layer_hi is None else layer_hi
         if x_in is None:
-            native.call("tf_embed", b["meta"][0], self.embed_w, b["x"], T, cfg.hidden, cfg.vocab, self.status.t)
+            e = b["e"] if cfg.hc_mult > 1 else b["x"]
+            native.call("tf_embed", b["meta"][0], self.embed_w, e, T, cfg.hidden, cfg.vocab, self.status.t)
             if x_patch is not None:
                 # rows that stand for image tokens take the vision tower's features instead
-                b["x"].index_copy_(0, x_patch[0], x_patch[1].to(b["x"].dtype))
+                e.index_copy_(0, x_patch[0], x_patch[1].to(e.dtype))
+            if cfg.hc_mult > 1:
+                # every residual copy starts as the embedding (reference: kernels/core.cu:530-543)
+                b["x"].view(T, cfg.hc_mult, cfg.hidden).copy_(e[:T, None, :].expand(T, cfg.hc_mult, cfg.hidden))
         else:
             b["x"][:T].copy_(x_in)
         for li in range(layer_lo, layer_hi):
@@ -727,18 +847,35 @@ class Engine:
         return self._head(T, b, logit_rows)
 
     def residual_rows(self, b: dict, rows: torch.Tensor) -> torch.Tensor:
-        """Complete residual stream (x + pending sublayer output) of the given rows, bf16."""
+        """Complete residual stream (x + pending sublayer output) of the given rows, bf16
+        (with hc_mult > 1: the flat [rows, hc_mult * hidden] copies, which never carry a pending part)."""
+        if self.cfg.hc_mult > 1 or not b.get("pending"):
+            return b["x"][rows].clone()
         return (b["x"][rows].float() + b["delta"][rows]).to(torch.bfloat16)
 
     def _head(self, T: int, b: dict, rows: Optional[torch.Tensor], draft: bool = False
               ) -> Optional[torch.Tensor]:
         cfg = self.cfg
         d = cfg.hidden
-        native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, self.final_norm,
-                    b["h16"] if draft else None,
-                    b["hb"], None, None, T, d, cfg.rms_eps)
-        if not draft:
-            self.last_hidden = b["x"]
+        if cfg.hc_mult > 1:
+            # final collapse of the residual copies with the head's own pre-mix weights
+            # (reference: src/model_io.rs final hc combine)
+            fn, base, scale = self.draft_extra["hc_head"]
+            xh = b["x"][:T].view(T, cfg.hc_mult, d).float()
+            flat = xh.reshape(T, -1)
+            inv = torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + cfg.rms_eps)
+            pre = torch.sigmoid((flat @ fn.t()) * inv * scale[0] + base) + cfg.hc_eps
+            b["v"][:T].copy_((xh * pre[:, :, None]).sum(1))
+            native.call("tf_add_norm", b["v"], None, 0, d, self.final_norm, b["h16"] if draft else None, b["hb"], None,
+                        None, T, d, cfg.rms_eps)
+            if not draft:
+                self.last_hidden = xh.mean(1).to(torch.bfloat16)
+        else:
+            native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, self.final_norm,
+                        b["h16"] if draft else None,
+                        b["hb"], None, None, T, d, cfg.rms_eps)
+            if not draft:
+                self.last_hidden = b["x"]
         if rows is None:
             return None
         if draft and self.draft_extra.get("head") is not None:
@@ -780,8 +917,12 @@ class Engine:
         b["cat16"][:, :d].copy_(b["e16"])
         b["cat16"][:, d:].copy_(b["h16"])
         self._linear(b["cat16"], ex["main_proj"], b["delta"], T)
-        b["x"].zero_()
-        b["pending"] = True
+        if cfg.hc_mult > 1:
+            b["x"].view(T, cfg.hc_mult, d).copy_(b["delta"][:T, None, :].expand(T, cfg.hc_mult, d))
+            b["pending"] = False
+        else:
+            b["x"].zero_()
+            b["pending"] = True
         for j, L in enumerate(self.draft_layers):
             self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False)
         return self._head(T, b, logit_rows, draft=True)

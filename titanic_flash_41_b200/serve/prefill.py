@@ -42,7 +42,7 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
     earlier in the same sweep) and layer l-1's output of chunk c."""
     cfg = eng.cfg
     n = int(toks.shape[0])
-    resid = torch.empty(n, cfg.hidden, dtype=torch.bfloat16, device=eng.dev)
+    resid = torch.empty(n, cfg.hidden * cfg.hc_mult, dtype=torch.bfloat16, device=eng.dev)
     offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
     plans = [StepPlan.build([(region, start + int(offs[c]), toks[offs[c]:offs[c + 1]].tolist())], logits="last")
              for c in range(len(sizes))]
@@ -96,7 +96,7 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
     L = len(eng.layers)
     late = cfg.late_start if 0 < cfg.late_start < L else L
     tail_n = min(n, cfg.window) if late < L else 0
-    tail = torch.zeros(max(tail_n, 1), cfg.hidden, dtype=torch.bfloat16, device=eng.dev)
+    tail = torch.zeros(max(tail_n, 1), cfg.hidden * cfg.hc_mult, dtype=torch.bfloat16, device=eng.dev)
     sizes = plan_chunks(n, tuple(widths) if widths else (chunk,))
     if layer_major is None:
         layer_major = len(sizes) > 1 and getattr(eng, "big_moe_full", None) is not None
