@@ -225,7 +225,8 @@ def test_reference_geometry_matches_oracle(geom):
     eng.status.check()
     err = _row_err(got, want)
     # rows whose router decision flips on a near-tie differ a lot; judge the rows statistically
-    assert err.median() < 0.1 and (err < 0.2).float().mean() >= 0.7, err
+    med, lim, frac = (0.15, 0.25, 0.55) if cfg.hc_mult > 1 else (0.1, 0.2, 0.7)   # bf16 residual copies feed the mix
+    assert err.median() < med and (err < lim).float().mean() >= frac, err
     pos, errs = 61, []
     for step in range(8):
         toks = torch.randint(0, cfg.vocab, (4,), generator=g)
@@ -235,4 +236,38 @@ def test_reference_geometry_matches_oracle(geom):
         errs.append(_row_err(got, want))
     eng.status.check()
     errs = torch.cat(errs)
-    assert errs.median() < 0.1 and (errs < 0.2).float().mean() >= 0.7, errs
+    assert errs.median() < med and (errs < lim).float().mean() >= frac, errs
+
+
+@pytest.mark.parametrize("hc", [1, 4])
+def test_engram_layers_match_oracle(hc):
+    """Hashed n-gram memory in the engine's layer loop (table lookup, projection, gate) against the oracle."""
+    from titanic_flash_41_b200.config import EngramConfig
+    cfg = small_config(engram=EngramConfig(layers=(0, 2), rows_per_table=1500), hc_mult=hc)
+    W = oracle.init_weights(cfg, 0)
+    rt = {}
+    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,)), W, roundtrip=rt)
+    ref = oracle.OracleModel(cfg, rt)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(3, cfg.vocab, (50,), generator=g)
+    s = ref.new_session(256)
+    want = ref.forward(prompt, s)
+    got = eng.forward(E.StepPlan.build([(1, 0, prompt.tolist())]).attach_engram(cfg, [[]])).cpu()
+    eng.status.check()
+    err = _row_err(got, want)
+    med, lim, frac = (0.15, 0.25, 0.55) if cfg.hc_mult > 1 else (0.1, 0.2, 0.7)   # bf16 residual copies feed the mix
+    assert err.median() < med and (err < lim).float().mean() >= frac, err
+    hist, pos, errs = prompt.tolist(), 50, []
+    for step in range(6):
+        toks = torch.randint(3, cfg.vocab, (4,), generator=g)
+        want = ref.forward(toks, s)
+        got = eng.forward(E.StepPlan.build([(1, pos, toks.tolist())]).attach_engram(cfg, [hist[-3:]])).cpu()
+        hist += toks.tolist()
+        pos += 4
+        errs.append(_row_err(got, want))
+    eng.status.check()
+    errs = torch.cat(errs)
+    assert errs.median() < med and (errs < lim).float().mean() >= frac, errs
+    # a plan without hashes is refused for this model
+    with pytest.raises(ValueError, match="attach_engram"):
+        eng.forward(E.StepPlan.build([(1, pos, [5, 6])]))

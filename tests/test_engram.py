@@ -76,3 +76,31 @@ def test_device_lookup_and_gate_match_references():
     out = EG.gate(x.to(dev), kv.to(dev), qw.to(dev), kw.to(dev), 1e-6).float().cpu()
     ref = EG.gate_reference(x.float(), kv.float(), qw.float(), kw.float(), 1e-6)
     assert (out - ref).abs().max() < 0.03
+
+
+def test_engram_layer_in_the_oracle_model():
+    """Engram in the model path: chunked == whole, overwritten speculative rows leave no trace, and the
+    memory actually changes the logits."""
+    from titanic_flash_41_b200.config import EngramConfig, tiny_config
+    from titanic_flash_41_b200.models import oracle
+    cfg = tiny_config(engram=EngramConfig(layers=(0, 1), rows_per_table=1500))
+    W = oracle.init_weights(cfg, 1)
+    assert W["engram.0.table"].shape[1] == 256 and "layers.1.engram.wkv.weight" in W
+    m = oracle.OracleModel(cfg, W)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(3, cfg.vocab, (30,), generator=g)
+    s1 = m.new_session(64)
+    whole = m.forward(toks, s1)
+    s2 = m.new_session(64)
+    a = m.forward(toks[:13], s2)
+    b = m.forward(toks[13:], s2)
+    assert torch.allclose(torch.cat([a, b]), whole, atol=2e-4, rtol=1e-4)
+    # speculative rows at positions 30.. are replaced by other tokens: same result as never having run them
+    m.forward(torch.randint(3, cfg.vocab, (4,), generator=g), s2, commit=False)
+    nxt = torch.randint(3, cfg.vocab, (4,), generator=g)
+    x = m.forward(nxt, s2, start=30)
+    y = m.forward(nxt, s1)
+    assert torch.allclose(x, y, atol=2e-4, rtol=1e-4)
+    # without the memory the model is a different function
+    plain = oracle.OracleModel(tiny_config(), {k: v for k, v in W.items() if "engram" not in k})
+    assert not torch.allclose(plain.forward(toks, plain.new_session(64)), whole, atol=1e-3)

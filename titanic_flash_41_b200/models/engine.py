@@ -333,8 +333,18 @@ class StepPlan:
     logit_rows: np.ndarray      # rows whose logits are wanted
     group_rows: int             # rows per conversation block (uniform), used to group index scoring
     min_pos: Optional[np.ndarray] = None   # [T] oldest window position a row may attend (default 0)
+    engram_ids: Optional[np.ndarray] = None   # [T, tables, ids] int64 row ids of the hashed n-gram memory
+    blocks: Optional[list] = None          # (region, start, tokens) as given to build()
 
     META_ROWS = 7
+
+    def attach_engram(self, cfg: ModelConfig, prevs: Sequence[Sequence[int]]) -> "StepPlan":
+        """Hash every block's rows; ``prevs[i]`` are the (up to ngram-1) tokens right before block i."""
+        from . import engram as EG
+        md = EG.metadata_for(cfg)
+        self.engram_ids = np.concatenate([EG.hash_positions(md, prev, list(t), start)
+                                          for (region, start, t), prev in zip(self.blocks, prevs)]).astype(np.int64)
+        return self
 
     def meta_host(self, ratio: int) -> np.ndarray:
         """[META_ROWS, T] int32 block uploaded per launch: tokens, pos, region, first_row, last_pos,
@@ -361,7 +371,8 @@ class StepPlan:
             r0 += n
         i32 = lambda a: np.asarray(a, dtype=np.int32)
         gr = sizes.pop() if len(sizes) == 1 else 1
-        return StepPlan(i32(toks), i32(pos), i32(reg), i32(first), i32(last), i32(lrows), gr)
+        return StepPlan(i32(toks), i32(pos), i32(reg), i32(first), i32(last), i32(lrows), gr,
+                        blocks=[(r, s, list(t)) for r, s, t in blocks])
 
     @property
     def T(self) -> int:
@@ -411,6 +422,9 @@ class Engine:
                                  device=self.dev)
         self._scratch: Dict[int, dict] = {}
         self._dq_cache: Dict[int, torch.Tensor] = {}
+        self._side: Optional[torch.cuda.Stream] = None     # parallel branch for the shared expert (decode rows)
+        # hashed n-gram memory, one entry per Engram layer: (table, wkv, q_weight, k_weight)
+        self.engram: List[tuple] = self.draft_extra.get("engram", [])
         self.big_gemm = None        # set by ops.bigpath when the tcgen05 path is attached
         self.symm = None            # SymmWorkspace: fused GEMV/combine + all-reduce over peer memory
         self.last_hidden: Optional[torch.Tensor] = None
@@ -435,6 +449,22 @@ class Engine:
         if cfg.hc_mult > 1:
             extra = dict(extra, hc_head=tuple(W[k].to(device, torch.float32).contiguous()
                                               for k in ("hc_head_fn", "hc_head_base", "hc_head_scale")))
+        if cfg.engram is not None and cfg.engram.layers:
+            # row-sharded tables in HBM (rows of other ranks read as zero and are summed in), the
+            # projection replicated
+            from . import engram as EG
+            eg = []
+            for e, l in enumerate(cfg.engram.layers):
+                packed = EG.pack_rows(W[f"engram.{e}.table"].float())
+                n = packed.shape[0]
+                lo, hi = n * comm.rank // comm.world, n * (comm.rank + 1) // comm.world
+                wkv = quant_fp8_device(W[f"layers.{l}.engram.wkv.weight"].to(device))
+                if roundtrip is not None:
+                    roundtrip[f"layers.{l}.engram.wkv.weight"] = dequant_fp8(wkv).cpu()
+                eg.append((EG.EngramTable(packed[lo:hi], lo, device), wkv,
+                           W[f"layers.{l}.engram.q_weight"].to(device, torch.bfloat16).contiguous(),
+                           W[f"layers.{l}.engram.k_weight"].to(device, torch.bfloat16).contiguous()))
+            extra = dict(extra, engram=eg)
         V = cfg.vocab
         Vl = V // comm.world
         embed = W["embed.weight"].to(device, torch.bfloat16).contiguous()
@@ -532,6 +562,14 @@ class Engine:
             b["qfull"] = torch.zeros(T, Hl * Dh, dtype=b["P"].dtype, device=dev)
         if cfg.o_groups:
             b["mid16"] = torch.zeros(T, (cfg.o_groups // self.world) * cfg.o_lora_rank, dtype=torch.float16, device=dev)
+        if self.engram:
+            ec = cfg.engram
+            n_ids = (ec.ngram - 1) * ec.heads
+            b["eg_ids"] = torch.zeros(len(ec.layers), T, n_ids, dtype=torch.int64, device=dev)
+            b["eg_rows16"] = torch.zeros(T, n_ids * ec.width, dtype=torch.float16, device=dev)
+            b["eg_kv"] = torch.zeros(T, (m + 1) * d, dtype=torch.bfloat16, device=dev)
+            if "x2" not in b:
+                b["x2"] = torch.zeros(T, d, dtype=torch.bfloat16, device=dev)
         self._scratch[T] = b
         return b
 
@@ -596,6 +634,8 @@ class Engine:
         hc = cfg.hc_mult > 1
         if first:
             b["pending"] = False
+        if self.engram and li < cfg.n_layers and li in cfg.engram.layers:
+            self._engram(cfg.engram.layers.index(li), L, T, b)
         self._boundary(L, "attn", T, b, want_hb=False)
         N = L.proj.q.shape[0]
         P = b["P"]
@@ -671,6 +711,27 @@ class Engine:
             self._allreduce(b["delta"][:T])
             b["pending"] = True
 
+    def _engram(self, e: int, L: LayerWeights, T: int, b: dict) -> None:
+        """Hashed n-gram memory in front of an Engram layer: gather this rank's rows (others read as
+        zero), sum over the ranks, project to (copies + 1) x hidden and gate into the residual copies
+        (reference: src/engram_gpu.rs:40 Rows, :279 ownership reduction, :347 projection; gate
+        kernels/core.cu:952)."""
+        cfg = self.cfg
+        d, m = cfg.hidden, cfg.hc_mult
+        table, wkv, qw, kw = self.engram[e]
+        if m == 1 and b.get("pending"):
+            # fold the previous sublayer's output into the residual first
+            native.call("tf_add_norm", b["x"], b["delta"], 0, d, L.attn_norm, b["h16"], None, None, None, T, d,
+                        cfg.rms_eps)
+            b["pending"] = False
+        rows = table.lookup(b["eg_ids"][e, :T].reshape(-1))                  # [T * ids, 256] bf16
+        if self.world > 1:
+            self.comm.all_reduce(rows)                                       # disjoint ownership: exact
+        b["eg_rows16"][:T].copy_(rows.view(T, -1))
+        self._linear(b["eg_rows16"], wkv, b["eg_kv"], T)
+        native.call("tf_engram_gate", b["x"], b["eg_kv"], qw, kw, b["x2"], T, m, d, cfg.rms_eps)
+        b["x"], b["x2"] = b["x2"], b["x"]
+
     def _boundary(self, L: LayerWeights, br: str, T: int, b: dict, want_hb: bool) -> None:
         """Sublayer input: residual (+ pending sublayer output) -> RMSNorm, or with hc_mult > 1 the
         pre-mix collapse of the residual copies -> RMSNorm.  Fills b["h16"] (and b["hb"])."""
@@ -723,6 +784,18 @@ class Engine:
         cfg = self.cfg
         d, I = cfg.hidden, cfg.moe_inter
         scoring = 1 if cfg.scoring == "sqrtsoftplus" else 0
+        side = None
+        if cfg.n_shared and T <= self.SMALL_M:
+            # the shared expert depends only on the normalised input: run its two small GEMVs as a
+            # parallel branch (second stream; a parallel branch of the step's CUDA graph) next to the
+            # router and the routed experts, and join before the combine
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.dev)
+            side = self._side
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
+                self._linear(b["s_act"], L.sw2, b["s_y"], T)
         if T > self.SMALL_M and self.big_gemm is not None and cfg.n_experts % 128 == 0:
             # router logits of a prefill chunk on the tensor cores (bf16 x bf16), then top-k
             native.call("tf_gemm_tc", 0, b["hb"], d, L.gate, d, b["logits_r"], cfg.n_experts, T, cfg.n_experts,
@@ -758,7 +831,10 @@ class Engine:
         else:
             self._moe_large(L, T, b)
         shared = None
-        if cfg.n_shared:
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)       # join the shared-expert branch
+            shared = b["s_y"]
+        elif cfg.n_shared:
             self._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
             self._linear(b["s_act"], L.sw2, b["s_y"], T)
             shared = b["s_y"]
@@ -799,6 +875,12 @@ class Engine:
         T = plan.T
         host = plan.meta_host(self.cfg.compress_ratio)
         b["meta"][:, :T].copy_(torch.from_numpy(host), non_blocking=True)
+        if self.engram:
+            if plan.engram_ids is None:
+                raise ValueError("this model has Engram layers: the plan needs attach_engram()")
+            # [tables, T, ids] on the device
+            b["eg_ids"][:, :T].copy_(torch.from_numpy(np.ascontiguousarray(plan.engram_ids.transpose(1, 0, 2))),
+                                     non_blocking=True)
 
     @staticmethod
     def plan_shape(plan: StepPlan, ratio: int) -> Tuple[int, int]:

@@ -212,3 +212,41 @@ def gate(x: torch.Tensor, kv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, 
     out = torch.empty_like(x)
     native.call("tf_engram_gate", x.contiguous(), kv.contiguous(), qw.contiguous(), kw.contiguous(), out, r, m, d, eps)
     return out
+
+
+# ---------------------------------------------------------------------------------- model glue
+_MD_CACHE: dict = {}
+
+
+def metadata_for(cfg) -> HashMetadata:
+    """The hash metadata that belongs to a model configuration (deterministic; one table per
+    Engram layer, ``rows_per_table`` split over the (ngram-1) * heads id slots)."""
+    ec = cfg.engram
+    key = (cfg.vocab, ec.rows_per_table, len(ec.layers), ec.heads, ec.ngram)
+    if key not in _MD_CACHE:
+        per_head = max(16, ec.rows_per_table // ((ec.ngram - 1) * ec.heads) - 8)
+        _MD_CACHE[key] = HashMetadata.synthetic(cfg.vocab, rows_per_head=per_head, tables=len(ec.layers), heads=ec.heads,
+                                                ngram=ec.ngram, seed=20240917)
+    return _MD_CACHE[key]
+
+
+def table_rows(cfg) -> int:
+    return metadata_for(cfg).table_rows
+
+
+def hash_positions(md: HashMetadata, prev: Sequence[int], tokens: Sequence[int], start: int) -> np.ndarray:
+    """Row ids [T, tables, ids] of ``tokens`` placed at positions start.. after the ``prev`` tokens
+    (the up to ngram-1 tokens right before ``start``, oldest first)."""
+    h = HashHistory(lineage=1, pad_token=md.pad_token, ngram=md.ngram)
+    h.position = start
+    rec = list(reversed(list(prev)[-(md.ngram - 1):]))
+    h.recent = rec + [md.pad_token] * (md.ngram - 1 - len(rec))
+    return h.prepare(list(tokens), md).rows
+
+
+def apply_reference(x: torch.Tensor, rows: torch.Tensor, wkv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor,
+                    eps: float) -> torch.Tensor:
+    """x [T, m, d] residual copies, rows [T, ids*256] looked-up memory -> gated update (fp32)."""
+    T, m, d = x.shape
+    kv = (rows @ wkv.t()).reshape(T, m + 1, d)
+    return gate_reference(x, kv, qw, kw, eps)

@@ -210,6 +210,19 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32) -> Dict[s
             mat(f"{p}.main_proj.weight", d, d * (1 + cfg.draft.condition_layers))
             W[f"{p}.enorm.weight"] = torch.ones(d, dtype=dtype)
             W[f"{p}.hnorm.weight"] = torch.ones(d * cfg.draft.condition_layers, dtype=dtype)
+    if cfg.engram is not None and cfg.engram.layers:
+        # hashed n-gram memory: one table per Engram layer (values exactly representable in the packed
+        # MXFP8 row format), the projection of the looked-up rows to (copies + 1) x hidden, gate weights
+        from . import engram as EG
+        ec, m = cfg.engram, cfg.hc_mult
+        rows = EG.table_rows(cfg)
+        ids = (ec.ngram - 1) * ec.heads
+        for e, l in enumerate(ec.layers):
+            raw = torch.randn(rows, ec.width, generator=g) * 0.5
+            W[f"engram.{e}.table"] = EG.unpack_rows(EG.pack_rows(raw)).to(dtype)
+            mat(f"layers.{l}.engram.wkv.weight", (m + 1) * d, ids * ec.width, std=1.0 / math.sqrt(ids * ec.width))
+            W[f"layers.{l}.engram.q_weight"] = (1 + 0.1 * torch.randn(m, d, generator=g)).to(dtype)
+            W[f"layers.{l}.engram.k_weight"] = (1 + 0.1 * torch.randn(m, d, generator=g)).to(dtype)
     return W
 
 
@@ -270,6 +283,7 @@ class OracleSession:
     keys: Dict[str, torch.Tensor] = field(default_factory=dict)       # src prefix -> [maxC, Di]
     carry: Dict[str, torch.Tensor] = field(default_factory=dict)      # src prefix -> [max_tokens, 2, C]
     tokens: List[int] = field(default_factory=list)
+    token_at: Optional[torch.Tensor] = None                           # [max_tokens] token id by position (Engram)
 
     def buf(self, store: Dict[str, torch.Tensor], key: str, rows: int, *shape) -> torch.Tensor:
         if key not in store:
@@ -477,10 +491,31 @@ class OracleModel:
             y = y + (a @ W[f"{p}.ffn.shared_experts.w2.weight"].t()).to(torch.float32)
         return self.comm.all_reduce(y.to(self.dtype))
 
-    def _layer(self, p, layer, x, pos, s, draft=False):
+    def _engram(self, p: str, e: int, x: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Hashed n-gram memory in front of an Engram layer: gather the rows named by ``ids`` [T, n]
+        from table e (row-sharded tables: every rank contributes the rows it owns, summed), project
+        them to (copies + 1) x hidden and gate them into the residual copies
+        (reference: src/engram_gpu.rs; kernels/core.cu:952 ca_engram_gate)."""
+        from . import engram as EG
+        cfg, W = self.cfg, self.W
+        table = W[f"engram.{e}.table"]
+        T = ids.shape[0]
+        rows = table[ids.reshape(-1)].reshape(T, -1).to(torch.float32)
+        if cfg.kv_quant == "v41":
+            rows = codecs.bf16_round(rows)
+        xm = x if cfg.hc_mult > 1 else x[:, None, :]
+        out = EG.apply_reference(xm.to(torch.float32), rows, W[f"{p}.engram.wkv.weight"].to(torch.float32),
+                                 W[f"{p}.engram.q_weight"].to(torch.float32),
+                                 W[f"{p}.engram.k_weight"].to(torch.float32), cfg.rms_eps)
+        return out if cfg.hc_mult > 1 else out[:, 0]
+
+    def _layer(self, p, layer, x, pos, s, draft=False, engram_ids=None):
         cfg = self.cfg
         src = cfg.kv_source_of(layer) if not draft else -1
         src_prefix = f"layers.{src}" if src >= 0 else None
+        if engram_ids is not None and not draft and layer in cfg.engram.layers:
+            e = cfg.engram.layers.index(layer)
+            x = self._engram(p, e, x, engram_ids[:, e])
         h, hc = self._boundary(x, p, "attn")
         a = self._attention(p, layer, h.to(self.dtype), pos, s, src_prefix,
                             (not draft) and layer in cfg.index_source_layers, draft)
@@ -518,8 +553,20 @@ class OracleModel:
         x = self.embed(tokens)
         if cfg.hc_mult > 1:
             x = x[:, None, :].expand(T, cfg.hc_mult, cfg.hidden).contiguous()      # core.cu:536
+        eg_ids = None
+        if cfg.engram is not None and cfg.engram.layers:
+            # token ids are kept by position so that the n-gram hashes of speculative rows can be
+            # recomputed after a rejection without any history rollback
+            from . import engram as EG
+            if s.token_at is None:
+                s.token_at = torch.zeros(s.max_tokens, dtype=torch.long)
+            s.token_at[start:start + T] = tokens.to("cpu", torch.long)
+            md = EG.metadata_for(cfg)
+            prev = s.token_at[max(0, start - (md.ngram - 1)):start].tolist()
+            eg_ids = torch.from_numpy(EG.hash_positions(md, prev, tokens.tolist(), start).astype("int64")
+                                      ).to(tokens.device)
         for l in range(cfg.n_layers):
-            x = self._layer(f"layers.{l}", l, x, pos, s)
+            x = self._layer(f"layers.{l}", l, x, pos, s, engram_ids=eg_ids)
         self.last_hidden = x
         if commit:
             s.length = start + T
