@@ -271,3 +271,23 @@ def test_engram_layers_match_oracle(hc):
     # a plan without hashes is refused for this model
     with pytest.raises(ValueError, match="attach_engram"):
         eng.forward(E.StepPlan.build([(1, pos, [5, 6])]))
+
+
+def test_reference_model_widths_run_on_the_engine():
+    """The reference model's real widths (hidden 5120, 512-wide latent heads, low-rank query 1280, eight
+    output groups of rank 1024, four residual copies, 32 index heads, expert width 2304) with few layers and
+    experts: prefill and a decode block produce finite logits and no kernel reports a problem."""
+    from titanic_flash_41_b200.config import DraftConfig, reference_1017_config
+    cfg = reference_1017_config(n_layers=4, kv_source_layers=(2,), index_source_layers=(2,), late_start=3, n_experts=32,
+                                draft=DraftConfig(layers=1, depth=3), engram=None, dense_quant="fp8_block128", vocab=16384)
+    eng = E.Engine.random_init(cfg, EngineConfig(regions=2, max_context=4096, prefill_widths=(256,)), seed=0, max_chunk=256)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(3, cfg.vocab, (200,), generator=g).tolist()
+    lg = eng.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
+    torch.cuda.synchronize()
+    eng.status.check()
+    assert lg.shape == (1, cfg.vocab) and bool(torch.isfinite(lg).all())
+    lg = eng.forward(E.StepPlan.build([(0, 200, [5, 6, 7, 8])]))
+    torch.cuda.synchronize()
+    eng.status.check()
+    assert lg.shape == (4, cfg.vocab) and bool(torch.isfinite(lg).all()) and float(lg.std()) > 0

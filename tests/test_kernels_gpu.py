@@ -169,10 +169,12 @@ def test_index_scores_and_topk(Hi):
         assert got == sorted(order.tolist())
 
 
-def test_sparse_attention_matches_reference():
+@pytest.mark.parametrize("Dh,Hl", [(128, 4), (512, 4), (512, 20), (256, 16)])
+def test_sparse_attention_matches_reference(Dh, Hl):
+    """Dh 128 runs the register-resident kernel, 256 / 512 the wide-latent one (head dim split over warps)."""
     torch.manual_seed(6)
-    T, Hl, Dh, window, ring, C, k = 6, 4, 128, 16, 64, 50, 12
-    win_row, comp_row = 144, 80
+    T, window, ring, C, k = 6, 16, 64, 50, 12
+    win_row, comp_row = -(-(Dh + Dh // 32) // 16) * 16, -(-(Dh // 2 + Dh // 16) // 16) * 16
     kv = torch.randn(2, ring, Dh) * 1.5
     win = torch.zeros(2, ring, win_row, dtype=torch.uint8)
     win[:, :, :Dh + Dh // 32] = codecs.kv_v41_encode(kv)

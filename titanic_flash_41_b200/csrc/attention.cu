@@ -258,6 +258,236 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Wide latent (head_dim 256 / 512, the reference model's 512-wide MLA latent): the head dimension is
+// split over the four warps.  Each warp forms the partial scores of all 16 heads of a head tile over
+// its DH/4 dims, the partials are summed through shared memory, every warp then runs the same
+// online softmax and accumulates P.V for its own DH/4 output dims, so the per-warp register
+// footprint is that of a 128-wide head.  Head tiles of 16 are processed one after the other.
+// ---------------------------------------------------------------------------------------------
+template <int DH>
+__global__ void __launch_bounds__(128) sparse_attn_wide_kernel(AttnParams p) {
+  constexpr int SL = DH / 4;          // dims owned by one warp
+  constexpr int KS = DH + 8;
+  constexpr int VS = kChunk + 8;
+  constexpr int SP = kChunk + 4;      // row stride of the partial-score tiles (floats)
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half* Ks = reinterpret_cast<__half*>(smem_raw);                    // [64][KS]
+  __half* Vt = Ks + kChunk * KS;                                       // [DH][VS]
+  float* Sp = reinterpret_cast<float*>(Vt + DH * VS);                  // [4 warps][16][SP]
+  __shared__ int key_src[kChunk];
+
+  const int r = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int pos = p.pos[r], reg = p.region[r];
+  const int nwin = min(pos + 1 - (p.min_pos ? p.min_pos[r] : 0), p.window);
+  int nsel = 0;
+  if (p.comp) {
+    if (p.sel_count) nsel = p.sel_count[r];
+    else {
+      int lo = 0, hi = p.sel_stride;
+      const int* sidx = p.sel + (long)r * p.sel_stride;
+      while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (sidx[mid] >= 0) lo = mid + 1; else hi = mid;
+      }
+      nsel = lo;
+    }
+  }
+  const int nkeys = nwin + nsel;
+  const int nchunks = (nkeys + kChunk - 1) / kChunk;
+  const int wrow = p.win_row, crow = p.comp_row;
+  const uint8_t* win = p.win + (long)reg * p.win_region_stride;
+  const uint8_t* comp = p.comp ? p.comp + (long)reg * p.comp_region_stride : nullptr;
+  const int d0 = warp * SL;
+
+  for (int h0 = 0; h0 < p.Hl; h0 += 16) {
+    // ---- this warp's slice of the (pre-scaled) Q fragments of the head tile
+    uint32_t qf[SL / 16][4];
+    {
+      const __nv_bfloat16* q0 = p.q + ((long)r * p.Hl + min(h0 + g, p.Hl - 1)) * DH + d0;
+      const __nv_bfloat16* q8 = p.q + ((long)r * p.Hl + min(h0 + g + 8, p.Hl - 1)) * DH + d0;
+      const float s0 = h0 + g < p.Hl ? p.scale_log2 : 0.f, s8 = h0 + g + 8 < p.Hl ? p.scale_log2 : 0.f;
+#pragma unroll
+      for (int ks = 0; ks < SL / 16; ++ks) {
+        const int k = ks * 16 + 2 * t;
+        float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k));
+        float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k));
+        float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q0 + k + 8));
+        float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q8 + k + 8));
+        qf[ks][0] = pack_h2(a.x * s0, a.y * s0);
+        qf[ks][1] = pack_h2(b.x * s8, b.y * s8);
+        qf[ks][2] = pack_h2(c.x * s0, c.y * s0);
+        qf[ks][3] = pack_h2(d.x * s8, d.y * s8);
+      }
+    }
+    float o[SL / 8][4];
+#pragma unroll
+    for (int i = 0; i < SL / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = kNegBig, m8 = kNegBig, l0 = 0.f, l8 = 0.f;
+
+    for (int c = split; c < nchunks; c += p.nsplit) {
+      const int kbase = c * kChunk;
+      __syncthreads();
+      for (int kk = threadIdx.x; kk < kChunk; kk += blockDim.x) {
+        const int i = kbase + kk;
+        int src = 0x7fffffff;
+        if (i < nwin) {
+          src = (pos - nwin + 1 + i) % p.ring;
+        } else if (i < nkeys) {
+          int id = p.sel[(long)r * p.sel_stride + (i - nwin)];
+          if (id < 0 || id >= p.maxC) {
+            tf_report(p.st, TF_BAD_INDEX, 11, r, id);
+            id = 0;
+          }
+          src = ~id;
+        }
+        key_src[kk] = src;
+      }
+      __syncthreads();
+      for (int it = threadIdx.x; it < kChunk * (DH / 16); it += blockDim.x) {
+        const int key = it % kChunk, seg = it / kChunk;
+        const int src = key_src[key];
+        float v[16];
+        if (src == 0x7fffffff) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        } else if (src >= 0) {
+          const uint8_t* row = win + (long)src * wrow;
+          uint4 raw = *reinterpret_cast<const uint4*>(row + seg * 16);
+          const float sc = ue8m0_to_float(row[DH + (seg >> 1)]);
+          const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t h2 = e4m3x2_to_h2(h[j]);
+            float2 f = __half22float2(*reinterpret_cast<__half2*>(&h2));
+            v[2 * j] = f.x * sc;
+            v[2 * j + 1] = f.y * sc;
+          }
+        } else {
+          const uint8_t* row = comp + (long)(~src) * crow;
+          uint2 raw = *reinterpret_cast<const uint2*>(row + seg * 8);
+          const float sc = e4m3_to_float(row[DH / 2 + seg]);
+          const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = e2m1_to_float((w[j >> 3] >> (4 * (j & 7))) & 0xfu) * sc;
+        }
+        __half* kd = Ks + key * KS + seg * 16;
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) *reinterpret_cast<__half2*>(kd + j) = __floats2half2_rn(v[j], v[j + 1]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) Vt[(seg * 16 + j) * VS + key] = __float2half(v[j]);
+      }
+      __syncthreads();
+      // ---- partial S over this warp's dims, summed through shared memory
+      float s[kChunk / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < kChunk / 8; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        const __half* kr = Ks + (nt * 8 + g) * KS + d0 + 2 * t;
+#pragma unroll
+        for (int ks = 0; ks < SL / 16; ++ks) {
+          uint32_t b[2];
+          b[0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
+          b[1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
+          mma_f16_16816(s[nt], qf[ks], b);
+        }
+        float* sp = Sp + (warp * 16) * SP + nt * 8 + 2 * t;
+        *reinterpret_cast<float2*>(sp + g * SP) = make_float2(s[nt][0], s[nt][1]);
+        *reinterpret_cast<float2*>(sp + (g + 8) * SP) = make_float2(s[nt][2], s[nt][3]);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int nt = 0; nt < kChunk / 8; ++nt) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {                   // fixed order: every warp gets the same sums
+          const float* sp = Sp + (w * 16) * SP + nt * 8 + 2 * t;
+          const float2 x = *reinterpret_cast<const float2*>(sp + g * SP);
+          const float2 y = *reinterpret_cast<const float2*>(sp + (g + 8) * SP);
+          a0 += x.x; a1 += x.y; a2 += y.x; a3 += y.y;
+        }
+        s[nt][0] = a0; s[nt][1] = a1; s[nt][2] = a2; s[nt][3] = a3;
+      }
+      const int valid = nkeys - kbase;
+      float cm0 = kNegBig, cm8 = kNegBig;
+#pragma unroll
+      for (int nt = 0; nt < kChunk / 8; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = nt * 8 + 2 * t + (i & 1);
+          if (key >= valid) s[nt][i] = kNegBig;
+        }
+        cm0 = fmaxf(cm0, fmaxf(s[nt][0], s[nt][1]));
+        cm8 = fmaxf(cm8, fmaxf(s[nt][2], s[nt][3]));
+      }
+      cm0 = fmaxf(cm0, __shfl_xor_sync(0xffffffffu, cm0, 1));
+      cm0 = fmaxf(cm0, __shfl_xor_sync(0xffffffffu, cm0, 2));
+      cm8 = fmaxf(cm8, __shfl_xor_sync(0xffffffffu, cm8, 1));
+      cm8 = fmaxf(cm8, __shfl_xor_sync(0xffffffffu, cm8, 2));
+      const float nm0 = fmaxf(m0, cm0), nm8 = fmaxf(m8, cm8);
+      const float f0 = exp2f(m0 - nm0), f8 = exp2f(m8 - nm8);
+      m0 = nm0;
+      m8 = nm8;
+      l0 *= f0;
+      l8 *= f8;
+#pragma unroll
+      for (int i = 0; i < SL / 8; ++i) {
+        o[i][0] *= f0;
+        o[i][1] *= f0;
+        o[i][2] *= f8;
+        o[i][3] *= f8;
+      }
+      uint32_t pf[kChunk / 16][4];
+#pragma unroll
+      for (int nt = 0; nt < kChunk / 8; ++nt) {
+        float p0 = exp2f(s[nt][0] - m0), p1 = exp2f(s[nt][1] - m0);
+        float p2 = exp2f(s[nt][2] - m8), p3 = exp2f(s[nt][3] - m8);
+        if (s[nt][0] <= kNegBig) p0 = 0.f;
+        if (s[nt][1] <= kNegBig) p1 = 0.f;
+        if (s[nt][2] <= kNegBig) p2 = 0.f;
+        if (s[nt][3] <= kNegBig) p3 = 0.f;
+        l0 += p0 + p1;
+        l8 += p2 + p3;
+        pf[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(p0, p1);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(p2, p3);
+      }
+      // ---- O[:, this warp's dims] += P V
+#pragma unroll
+      for (int dt = 0; dt < SL / 8; ++dt) {
+        const __half* vr = Vt + (d0 + dt * 8 + g) * VS + 2 * t;
+#pragma unroll
+        for (int ks = 0; ks < kChunk / 16; ++ks) {
+          uint32_t b[2];
+          b[0] = *reinterpret_cast<const uint32_t*>(vr + ks * 16);
+          b[1] = *reinterpret_cast<const uint32_t*>(vr + ks * 16 + 8);
+          mma_f16_16816(o[dt], pf[ks], b);
+        }
+      }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l8 += __shfl_xor_sync(0xffffffffu, l8, 1);
+    l8 += __shfl_xor_sync(0xffffffffu, l8, 2);
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i8 = l8 > 0.f ? 1.f / l8 : 0.f;
+    const long base = ((long)r * p.nsplit + split) * p.Hl;
+    if (h0 + g < p.Hl) {
+      float* po = p.part_o + (base + h0 + g) * DH + d0;
+#pragma unroll
+      for (int dt = 0; dt < SL / 8; ++dt)
+        *reinterpret_cast<float2*>(po + dt * 8 + 2 * t) = make_float2(o[dt][0] * i0, o[dt][1] * i0);
+      if (t == 0 && warp == 0) p.part_lse[base + h0 + g] = l0 > 0.f ? m0 + log2f(l0) : kNegBig;
+    }
+    if (h0 + g + 8 < p.Hl) {
+      float* po = p.part_o + (base + h0 + g + 8) * DH + d0;
+#pragma unroll
+      for (int dt = 0; dt < SL / 8; ++dt)
+        *reinterpret_cast<float2*>(po + dt * 8 + 2 * t) = make_float2(o[dt][2] * i8, o[dt][3] * i8);
+      if (t == 0 && warp == 0) p.part_lse[base + h0 + g + 8] = l8 > 0.f ? m8 + log2f(l8) : kNegBig;
+    }
+  }
+}
+
 // merge splits + sink, inverse RoPE on the tail, write f16 and/or bf16.  grid (T, Hl), block Dh.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                   const float* __restrict__ sink, const int* __restrict__ pos,
@@ -307,7 +537,7 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
                                const int* sel_count, int maxC, float scale, int nsplit, float* part_o,
                                float* part_lse, const float* sink, const float* freqs, int rope_dim,
                                void* out16, void* outb, int ldo, void* status, cudaStream_t st) {
-  if (Dh != 128 && Dh != 64) return -1;
+  if (Dh != 128 && Dh != 64 && Dh != 256 && Dh != 512) return -1;
   if (Hl > 64 || nsplit < 1 || (win_row % 16) || (comp && (comp_row % 16))) return -1;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.T = T; p.Hl = Hl; p.Dh = Dh; p.pos = pos; p.region = region; p.min_pos = min_pos;
@@ -319,7 +549,19 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
   // four warps always: all of them dequantise the key chunk, those that own heads run the MMAs
   const int warps = 4;
   dim3 grid(T, nsplit);
-  if (Dh == 128) {
+  if (Dh == 512 || Dh == 256) {
+    const int smem = (kChunk * (Dh + 8) + Dh * (kChunk + 8)) * 2 + 4 * 16 * (kChunk + 4) * 4;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(sparse_attn_wide_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (kChunk * (512 + 8) + 512 * (kChunk + 8)) * 2 + 4 * 16 * (kChunk + 4) * 4);
+      cudaFuncSetAttribute(sparse_attn_wide_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (kChunk * (256 + 8) + 256 * (kChunk + 8)) * 2 + 4 * 16 * (kChunk + 4) * 4);
+      attr_set = true;
+    }
+    if (Dh == 512) sparse_attn_wide_kernel<512><<<grid, warps * 32, smem, st>>>(p);
+    else sparse_attn_wide_kernel<256><<<grid, warps * 32, smem, st>>>(p);
+  } else if (Dh == 128) {
     const int smem = (kChunk * (128 + 8) + 128 * (kChunk + 8)) * 2;
     sparse_attn_kernel<128><<<grid, warps * 32, smem, st>>>(p);
   } else {
