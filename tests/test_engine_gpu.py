@@ -291,3 +291,16 @@ def test_reference_model_widths_run_on_the_engine():
     torch.cuda.synchronize()
     eng.status.check()
     assert lg.shape == (4, cfg.vocab) and bool(torch.isfinite(lg).all()) and float(lg.std()) > 0
+
+
+def test_startup_self_check_and_bitwise_determinism_on_the_engine():
+    """Two runs of the fixture (prefill + speculative decode under CUDA graphs) in different regions give
+    identical tokens, logits and state digests."""
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.serve.backend import EngineBackend
+    from titanic_flash_41_b200.serve.warmup import self_check
+    cfg = small_config(draft=DraftConfig(layers=1, depth=3))
+    W = oracle.init_weights(cfg, 0)
+    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(64,)), W)
+    rep = self_check(EngineBackend(eng, chunk=64), steps=4)
+    assert rep["tokens"] >= 5

@@ -113,3 +113,25 @@ def test_long_context_stress_script_on_the_oracle():
     # the others from an earlier checkpoint of the same conversation
     assert sum(c >= 190 for c in out["resume_cached_tokens"]) >= 2 and all(c >= 96 for c in out["resume_cached_tokens"]), out
     assert out["reused_token_share"] > 0.3 and out["cache_stats"]["parked"] > 0
+
+
+def test_startup_self_check_on_the_oracle_backend():
+    from titanic_flash_41_b200.serve.warmup import SelfCheckError, self_check
+    cfg = tiny_config()
+    W = oracle.init_weights(cfg, 0)
+    b = OracleBackend(cfg, W, regions=2, max_context=256, chunk=32)
+    rep = self_check(b, steps=3)
+    assert rep["tokens"] >= 4 and rep["state_bytes"] > 0
+    # a backend whose second run differs is caught
+    orig = b.sample
+    calls = {"n": 0}
+
+    def flaky(*a, **k):
+        calls["n"] += 1
+        return (orig(*a, **k) + (1 if calls["n"] == 2 else 0)) % cfg.vocab
+    b.sample = flaky
+    try:
+        self_check(b, steps=1)
+        assert False, "difference not detected"
+    except SelfCheckError:
+        pass

@@ -48,6 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--tokenizer", help="tokenizer.json (byte-level BPE); byte tokenizer when absent")
     s.add_argument("--disk-cache", help="directory for the disk tier of the session cache")
     s.add_argument("--event-log", help="JSONL event log path")
+    s.add_argument("--no-self-check", action="store_true", help="skip the start-up reproducibility check")
     b = sub.add_parser("bench", help="prefill + decode timing (bench.py of the source tree)")
     b.add_argument("rest", nargs=argparse.REMAINDER)
     w = sub.add_parser("stage-weights", help="write this rank's staged weight atlas")
@@ -160,6 +161,10 @@ def serve_main(args) -> int:
                         max_admitted=args.regions)
     sched = Scheduler(scfg.max_admitted, scfg.queue_limit, scfg.background_queue_limit) if rank == 0 else None
     worker = Worker(backend, sched, SessionCache(), eos_id=getattr(tok, "eos_id", 1), log=log, control=control, rank=rank)
+    if not args.no_self_check and backend.regions >= 2:
+        # every rank runs the same fixture (its collectives line up); raises before the server reports ready
+        from .serve.warmup import self_check
+        log.log("self_check", **self_check(backend))
     if rank != 0:
         worker.run_forever()
         return 0

@@ -167,12 +167,16 @@ class SpecDecoder:
             if self.graph is None or bucket != self.nmax_bucket:
                 self.nmax_bucket = bucket
                 torch.cuda.synchronize()
+                # the step reads `hidden` first and overwrites it last, so the warm-up run must not
+                # leave its result there: the replay below is the run that counts
+                carried = self.hidden.clone()
                 s = torch.cuda.Stream()
                 s.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(s):
                     self._device_step(bucket)          # warm-up outside capture
                 torch.cuda.current_stream().wait_stream(s)
                 torch.cuda.synchronize()
+                self.hidden.copy_(carried)
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
                     self._device_step(bucket)
