@@ -21,6 +21,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--inter", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--graph", action="store_true", help="time the replay of a captured CUDA graph")
+    ap.add_argument("--only", default="", help="run only the variants whose name contains this")
     a = ap.parse_args()
     dev, pk = "cuda", peaks()
     El, T, k, d, I = a.experts, a.tokens, a.topk, a.hidden, a.inter
@@ -96,6 +98,21 @@ def main():
         native.call("tf_moe_gemv_w4a8_tma", w2, None, s2, None, El, I // 2, I // 32, d * (I // 32), aq, I, as_, y, d, 0, d, I,
                     g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, stw.t)
 
+    # block-scaled tensor-core form: MXFP8 activations, the MMA consumes nibbles and scales
+    x8 = torch.zeros(T, d, dtype=torch.uint8, device=dev)
+    x8s = torch.zeros(T, d // 32, dtype=torch.uint8, device=dev)
+    a8 = torch.zeros(npairs, I, dtype=torch.uint8, device=dev)
+    a8s = torch.zeros(npairs, I // 32, dtype=torch.uint8, device=dev)
+
+    def fc1_mx(blocked=0):
+        native.call("tf_quant_rows_mx8", h16, d, x8, x8s, T, d)
+        native.call("tf_moe_gemv_mx", w1, w3, s1, s3, El, x8, x8s, T, None, I, a8, a8s, I, d, k, g_expert, g_start,
+                    g_count, n_groups, sorted_pairs, slots, 10.0, 0, blocked, stw.t)
+
+    def fc2_mx(blocked=0):
+        native.call("tf_moe_gemv_mx", w2, None, s2, None, El, a8, a8s, npairs, y, d, None, None, d, I, 1, g_expert,
+                    g_start, g_count, n_groups, sorted_pairs, slots, 0.0, 0, blocked, stw.t)
+
     print(f"# peaks ({pk['source']}): HBM {pk['hbm_gbs']} GB/s; {used} of {El} experts hit by {npairs} pairs")
     for name, fn, nbytes in (("moe_fc1_mxfp4_dual", fc1, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_mxfp4", fc2, used * d * (I // 2 + I // 32)),
@@ -105,8 +122,15 @@ def main():
                              ("moe_fc2_w4a8 step-major (+quant)", fc2_sm, used * d * (I // 2 + I // 32)),
                              ("moe_fc1_w4a8_tma_dual (+quant)", fc1_tma, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_w4a8_tma (+quant)", fc2_tma, used * d * (I // 2 + I // 32)),
+                             ("moe_fc1_mx_tcgen05_dual (+quant)", fc1_mx, used * 2 * I * (d // 2 + d // 32)),
+                             ("moe_fc2_mx_tcgen05 (input quantised by FC1)", fc2_mx, used * d * (I // 2 + I // 32)),
+                             # same bytes read as [128 x 128] blocks of 8 KB (random nibbles: timing only)
+                             ("moe_fc1_mx_tcgen05 blocked", lambda: fc1_mx(1), used * 2 * I * (d // 2 + d // 32)),
+                             ("moe_fc2_mx_tcgen05 blocked", lambda: fc2_mx(1), used * d * (I // 2 + I // 32)),
                              ("dense_fp8_block128", dense, 2 * d * d + fw.s.numel() * 4)):
-        med, best = time_cuda(fn, iters=a.iters)
+        if a.only and a.only not in name:
+            continue
+        med, best = time_cuda(fn, iters=a.iters, graph=a.graph)
         stw.check()
         print(f"{name:32s} {med * 1e3:8.1f} us  {nbytes / med / 1e6:8.1f} GB/s = "
               f"{nbytes / med / 1e6 / pk['hbm_gbs']:.2f} of {pk['source']} HBM copy bandwidth (best {best * 1e3:.1f} us)")

@@ -19,11 +19,20 @@ def flush_l2():
     _flush.zero_()
 
 
-def time_cuda(fn, warmup=3, iters=10, flush=True):
-    """Returns (median_ms, best_ms) of fn() measured with CUDA events."""
+def time_cuda(fn, warmup=3, iters=10, flush=True, graph=False):
+    """Returns (median_ms, best_ms) of fn() measured with CUDA events.  ``graph``: capture fn() in a
+    CUDA graph first and time its replay (what a captured decode step sees: no host work between
+    the launches of fn)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
+        fn()
+        torch.cuda.synchronize()
     times = []
     for _ in range(iters):
         if flush:

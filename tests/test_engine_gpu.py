@@ -54,6 +54,52 @@ def test_engine_matches_oracle_prefill_and_decode():
     assert errs.median() < 0.08 and (errs < 0.15).float().mean() >= 0.8, errs
 
 
+def test_block_scaled_expert_path_matches_register_path_and_oracle():
+    """Decode rows with the routed experts on block-scaled tcgen05 MMAs.  MXFP8 activations are a
+    different arithmetic from f16 ones (the W4A8 form of the reference's expert kernels): the
+    oracle's logits move by some amount when its experts see MXFP8 activations, and the engine's
+    move by no more than that when it switches from the register-fed f16 form to this one."""
+    cfg = small_config(moe_inter=512)
+    W = oracle.init_weights(cfg, 0)
+    rt = {}
+    ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
+    eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
+    assert eng._moe_mx_ok(4) and "x8" in eng._bufs(4)
+    old = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,),
+                                                  moe_block_scaled=False), W)
+    assert "x8" not in old._bufs(4)
+    ref = oracle.OracleModel(cfg, rt)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (77,), generator=g)
+    s, s_mx = ref.new_session(256), ref.new_session(256)
+    ref.forward(prompt, s)
+    ref.forward(prompt, s_mx)
+    eng.forward(E.StepPlan.build([(1, 0, prompt.tolist())]))
+    old.forward(E.StepPlan.build([(1, 0, prompt.tolist())]))
+    pos, errs, errs_old, between, oracle_shift = 77, [], [], [], []
+    for step in range(6):
+        toks = torch.randint(0, cfg.vocab, (4,), generator=g)
+        ref.expert_act_mx8 = False
+        want = ref.forward(toks, s)
+        ref.expert_act_mx8 = True          # the oracle's experts see MXFP8 activations as the kernel's do
+        want_mx = ref.forward(toks, s_mx)
+        got = eng.forward(E.StepPlan.build([(1, pos, toks.tolist())])).cpu()
+        got_old = old.forward(E.StepPlan.build([(1, pos, toks.tolist())])).cpu()
+        pos += 4
+        errs.append(_row_err(got, want_mx))
+        errs_old.append(_row_err(got_old, want))
+        between.append(_row_err(got, got_old))
+        oracle_shift.append(_row_err(want_mx, want))
+    eng.status.check()
+    ref.expert_act_mx8 = False
+    errs, errs_old, between, oracle_shift = (torch.cat(v) for v in (errs, errs_old, between, oracle_shift))
+    assert errs_old.median() < 0.08, errs_old
+    assert between.median() < 1.5 * oracle_shift.median() + 0.01, (between, oracle_shift)
+    # rounding decisions of two noisy paths are independent: the distances add in quadrature
+    bound = (errs_old.median() ** 2 + 2 * oracle_shift.median() ** 2) ** 0.5 + 0.02
+    assert errs.median() < bound and (errs < 0.2).float().mean() >= 0.8, (errs, bound)
+
+
 def test_two_regions_batched_decode_equals_separate():
     cfg = small_config()
     W = oracle.init_weights(cfg, 3)

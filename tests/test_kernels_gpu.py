@@ -373,6 +373,80 @@ def test_w4a8_expert_gemv_matches_reference(dual, rows_per, tma):
             assert (got - a).abs().max() <= 2e-3 * a.abs().max() + 1e-4, (t, j)
 
 
+def test_mx8_row_quantiser_matches_codec():
+    """e4m3 values with one UE8M0 scale per 32 inputs: same bytes as the host codec."""
+    torch.manual_seed(5)
+    x = (torch.randn(7, 512, device=DEV) * torch.rand(7, 1, device=DEV) * 4).half()
+    x[3, 64:96] = 0
+    q = torch.zeros(7, 512, dtype=torch.uint8, device=DEV)
+    s = torch.zeros(7, 16, dtype=torch.uint8, device=DEV)
+    native.call("tf_quant_rows_mx8", x, 512, q, s, 7, 512)
+    torch.cuda.synchronize()
+    wq, ws = codecs.mxfp8_quant(x.float().cpu(), 32)
+    assert torch.equal(s.cpu()[ws != 0], ws[ws != 0])          # an all-zero group may carry any scale
+    back = q.view(torch.float8_e4m3fn).float().view(7, 16, 32) * torch.exp2(s.float() - 127)[..., None]
+    assert (back.view(7, 512) - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+    assert torch.equal(q.cpu().view(7, 16, 32)[ws != 0], wq.view(torch.uint8).view(7, 16, 32)[ws != 0])
+
+
+@pytest.mark.parametrize("dual,T", [(True, 16), (True, 5), (False, 16), (False, 3)])
+def test_block_scaled_expert_gemv_matches_reference(dual, T):
+    """MXFP4 weights x MXFP8 activations on tcgen05 block-scaled MMAs (scales applied by the tensor
+    core) against fp32 math on the dequantised operands."""
+    from titanic_flash_41_b200.models import engine as E
+    torch.manual_seed(7)
+    El, N, K, k = 6, 256, 1024, 2
+    w1 = torch.randn(El, N, K, device=DEV) * 0.1 * (1 + 3 * torch.rand(El, N, 1, device=DEV))
+    w3 = torch.randn(El, N, K, device=DEV) * 0.1
+    p1, s1 = E.quant_mxfp4_device(w1)
+    p3, s3 = E.quant_mxfp4_device(w3)
+    d1, d3 = E.dequant_mxfp4(p1, s1), E.dequant_mxfp4(p3, s3)
+    ids = torch.stack([torch.randperm(El, device=DEV)[:k] for _ in range(T)]).int().contiguous()
+    npairs = T * k
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=DEV)
+    ge, gs, gc, ng, sp, nl = i32(El), i32(El), i32(El), i32(1), i32(npairs), i32(1)
+    native.call("tf_route_group", ids, npairs, 0, El, ge, gs, gc, ng, sp, nl)
+    rows = T if dual else npairs                       # plain form: one activation row per sorted pair
+    x = (torch.randn(rows, K, device=DEV) * (0.2 + 2 * torch.rand(rows, 1, device=DEV))).half()
+    xq = torch.zeros(rows, K, dtype=torch.uint8, device=DEV)
+    xs = torch.zeros(rows, K // 32, dtype=torch.uint8, device=DEV)
+    native.call("tf_quant_rows_mx8", x, K, xq, xs, rows, K)
+    xd = (xq.view(torch.float8_e4m3fn).float().view(rows, K // 32, 32)
+          * torch.exp2(xs.float() - 127)[..., None]).view(rows, K)
+    st = native.StatusWord(DEV)
+    if dual:
+        y = torch.zeros(npairs, N, device=DEV, dtype=torch.float16)
+    else:
+        y = torch.zeros(npairs, N, device=DEV)
+    y8 = torch.zeros(npairs, N, dtype=torch.uint8, device=DEV)
+    y8s = torch.zeros(npairs, N // 32, dtype=torch.uint8, device=DEV)
+    native.call("tf_moe_gemv_mx", p1, p3 if dual else None, s1, s3 if dual else None, El, xq, xs, rows, y, N,
+                y8 if dual else None, y8s if dual else None, N, K, k, ge, gs, gc, ng, sp, min(El, npairs),
+                10.0 if dual else 0.0, 0, 0, st.t)
+    torch.cuda.synchronize()
+    st.check()
+    if dual:
+        # the MXFP8 copy of the fused output equals quantising the f16 rows (up to f16 rounding of the input)
+        back = (y8.view(torch.float8_e4m3fn).float().view(npairs, N // 32, 32)
+                * torch.exp2(y8s.float() - 127)[..., None]).view(npairs, N)
+        assert (back - y.float()).abs().max() <= 0.07 * y.float().abs().max() + 1e-3
+    order = sp.tolist()
+    for pos, pair in enumerate(order):
+        t, j = divmod(pair, k)
+        e = int(ids[t, j])
+        if dual:
+            a = d1[e] @ xd[t]
+            up = (d3[e] @ xd[t]).clamp(-10, 10)
+            want = torch.nn.functional.silu(a.clamp(max=10)) * up
+            got = y[pos].float()                       # fused form writes rows in sorted pair order
+            tol = 2e-3 * want.abs().max() + 2e-3
+        else:
+            want = d1[e] @ xd[pos]
+            got = y[pair]
+            tol = 1e-3 * want.abs().max() + 1e-4
+        assert (got - want).abs().max() <= tol, (pos, pair, float((got - want).abs().max()), float(want.abs().max()))
+
+
 def test_two_level_candidates_match_dense_selection():
     """Sparse scores equal the dense ones at the candidate keys, and selecting among the published
     blocks gives the dense top-k whenever all of it lies inside them."""

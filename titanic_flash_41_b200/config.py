@@ -315,6 +315,7 @@ class EngineConfig(_JsonMixin):
     spin_limit: int = 20_000_000       # bounded device waits (reference src/roce.rs:1196-1199)
     use_cuda_graphs: bool = True
     key_sharded_index_min: int = 8192  # decode rows: split index scoring over the ranks from this many keys (0 = never)
+    moe_block_scaled: bool = True      # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
     seed: int = 0
 
 

@@ -549,6 +549,11 @@ class Engine:
             s_act=torch.zeros(T, max(Il, 1), dtype=torch.float16, device=dev),
             s_y=torch.zeros(T, d, **f32),
         )
+        if self._moe_mx_ok(T):
+            # MXFP8 copies of the expert inputs for the block-scaled tensor-core GEMV
+            u8 = dict(dtype=torch.uint8, device=dev)
+            b.update(x8=torch.zeros(T, d, **u8), x8s=torch.zeros(T, d // 32, **u8),
+                     a8=torch.zeros(npairs, cfg.moe_inter, **u8), a8s=torch.zeros(npairs, cfg.moe_inter // 32, **u8))
         m = cfg.hc_mult
         if m > 1:
             # the residual stream is m copies per row; b["x"] is their flat [T, m*d] view
@@ -817,19 +822,51 @@ class Engine:
             native.call("tf_route_group", b["ids"], npairs, e_lo, e_lo + self.El, b["g_expert"],
                         b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
             slots = min(self.El, npairs)
-            native.call("tf_smallm_gemm", 1, L.ew1, L.ew3, L.es1, L.es3, I * (d // 2), I * (d // 32),
-                        d // 2, d // 32, b["h16"], d, b["act"], I, 1, I, d, 0, b["g_expert"],
-                        b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], cfg.topk, slots,
-                        min(T, 16), cfg.swiglu_limit)
-            native.call("tf_smallm_gemm", 1, L.ew2, None, L.es2, None, d * (I // 2), d * (I // 32),
-                        I // 2, I // 32, b["act"], I, b["y_pair"], d, 0, d, I, 0, b["g_expert"],
-                        b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], 1, slots,
-                        min(T, 16), 0.0)
+            if "x8" in b:
+                # MXFP4 weights x MXFP8 activations on block-scaled tcgen05 MMAs: the tensor core
+                # consumes nibbles and scales, the first launch hands the second its MXFP8 input
+                native.call("tf_quant_rows_mx8", b["h16"], d, b["x8"], b["x8s"], T, d)
+                native.call("tf_moe_gemv_mx", L.ew1, L.ew3, L.es1, L.es3, self.El, b["x8"], b["x8s"], T, None, I,
+                            b["a8"], b["a8s"], I, d, cfg.topk, b["g_expert"], b["g_start"], b["g_count"],
+                            b["n_groups"], b["sorted_pairs"], slots, cfg.swiglu_limit, 0, 0, self.status.t)
+                native.call("tf_moe_gemv_mx", L.ew2, None, L.es2, None, self.El, b["a8"], b["a8s"], npairs,
+                            b["y_pair"], d, None, None, d, I, 1, b["g_expert"], b["g_start"], b["g_count"],
+                            b["n_groups"], b["sorted_pairs"], slots, 0.0, 0, 0, self.status.t)
+            else:
+                self._moe_small_f16(L, T, b, slots)
         elif getattr(self, "big_moe_full", None) is not None:
             self.big_moe_full(self, L, T, b)       # permute, grouped GEMMs, shared expert, combine
             return
         else:
             self._moe_large(L, T, b)
+        self._moe_finish(L, T, b, side)
+
+    def _moe_mx_ok(self, T: int) -> bool:
+        """Block-scaled tensor-core GEMV for the routed experts: up to 16 rows, MXFP4 experts,
+        widths in whole 512-input scale loads and 128-feature tiles."""
+        cfg = self.cfg
+        return (self.ecfg.moe_block_scaled and T <= 16 and cfg.expert_quant == "mxfp4"
+                and cfg.hidden % 512 == 0 and cfg.moe_inter % 512 == 0)
+
+    def _moe_small_f16(self, L: LayerWeights, T: int, b: dict, slots: int) -> None:
+        """Register-fed form (f16 activations, nibbles unpacked on the CUDA cores): rows 17..32 and
+        widths the tensor-core form does not tile."""
+        cfg = self.cfg
+        d, I = cfg.hidden, cfg.moe_inter
+        native.call("tf_smallm_gemm", 1, L.ew1, L.ew3, L.es1, L.es3, I * (d // 2), I * (d // 32),
+                    d // 2, d // 32, b["h16"], d, b["act"], I, 1, I, d, 0, b["g_expert"],
+                    b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], cfg.topk, slots,
+                    min(T, 16), cfg.swiglu_limit)
+        native.call("tf_smallm_gemm", 1, L.ew2, None, L.es2, None, d * (I // 2), d * (I // 32),
+                    I // 2, I // 32, b["act"], I, b["y_pair"], d, 0, d, I, 0, b["g_expert"],
+                    b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], 1, slots,
+                    min(T, 16), 0.0)
+
+    def _moe_finish(self, L: LayerWeights, T: int, b: dict, side) -> None:
+        """Join the shared-expert branch and combine (with the all-reduce when the fused kernel is up)."""
+        cfg = self.cfg
+        d = cfg.hidden
+        e_lo = self.rank * self.El
         shared = None
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)       # join the shared-expert branch

@@ -310,6 +310,16 @@ class OracleModel:
         self.last_hidden: Optional[torch.Tensor] = None
         self.last_selection: Dict[int, torch.Tensor] = {}
         self.act_fp8 = False      # emulate FP8 (1x128 scaled) activations entering the linear layers
+        # emulate MXFP8 (e4m3, one UE8M0 scale per 32 inputs) activations entering the routed
+        # experts: the W4A8 form of the reference's expert GEMMs (moe.w4a8 kernels, MXFP8 K32
+        # quantisation in kernels/moe_frontend.cuh)
+        self.expert_act_mx8 = False
+
+    def _aq_mx(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.expert_act_mx8 or x.shape[-1] % 32:
+            return x
+        q, s = codecs.mxfp8_quant(x.float().cpu(), 32)
+        return codecs.mxfp8_dequant(q, s, 32).to(x.device, x.dtype)
 
     def _aq(self, x: torch.Tensor) -> torch.Tensor:
         """What an FP8 GEMM actually multiplies: the activation after e4m3 quantisation with one
@@ -482,8 +492,8 @@ class OracleModel:
             for e in range(El):
                 m = ids[:, j] == (e + e0)
                 if m.any():
-                    hh = h[m]
-                    a = self._aq(swiglu(hh @ w1[e].t(), hh @ w3[e].t(), cfg.swiglu_limit))
+                    hh = self._aq_mx(h[m])
+                    a = self._aq_mx(self._aq(swiglu(hh @ w1[e].t(), hh @ w3[e].t(), cfg.swiglu_limit)))
                     y[m] += (a @ w2[e].t()).to(torch.float32) * wts[m, j:j + 1]
         if cfg.n_shared:
             a = self._aq(swiglu(h @ W[f"{p}.ffn.shared_experts.w1.weight"].t(),
