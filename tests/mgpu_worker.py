@@ -65,8 +65,9 @@ def main():
     # ---- 3. engine: TP/EP over `world` GPUs (fused kernels) == single GPU
     from tests.test_engine_gpu import small_config
     # keep every per-rank slice at least one 128-wide block: heads and shared-expert width grow with the world
+    # (moe_inter 512: the routed experts of decode rows run on the block-scaled tensor-core GEMV)
     cfg = small_config(n_heads=4 * world if world > 4 else 4, shared_inter=max(256, 128 * world),
-                       draft=DraftConfig(layers=1, depth=3))
+                       moe_inter=512, draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
     ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,))
     # the TP engine also splits index scoring by key range from 8 keys on (decode rows)
