@@ -117,7 +117,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--trace", action="store_true", help="print a per-kernel time table of one extra prefill pass")
+    ap.add_argument("--trace", action="store_true", help="print per-kernel time tables of one extra prefill pass and one eager decode step")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -198,6 +198,13 @@ def main():
     slots = [DecodeSlot(region=r, length=start_len, anchor=100 + r, seed=r + 1) for r in range(SESSIONS)]
     dec = SpecDecoder(eng, SESSIONS, temperature=0.6, top_p=0.95, use_graph=not args.no_graph)
     launches = dec.count_launches(slots)
+    if args.trace:
+        # one eager decode step under the kernel clock: where the step time goes
+        from titanic_flash_41_b200.utils.trace import KernelClock
+        with KernelClock(shapes=True) as kc:
+            dec.count_launches(slots)
+        if rank == 0:
+            print("decode step (eager, per-kernel CUDA events)\n" + kc.report(top=30), file=sys.stderr, flush=True)
     for _ in range(args.warmup):
         dec.step(slots)
     barrier()

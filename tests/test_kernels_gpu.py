@@ -373,6 +373,43 @@ def test_w4a8_expert_gemv_matches_reference(dual, rows_per, tma):
             assert (got - a).abs().max() <= 2e-3 * a.abs().max() + 1e-4, (t, j)
 
 
+@pytest.mark.parametrize("T", [1, 5, 16, 19])
+def test_router_logits_small_matches_fp32(T):
+    torch.manual_seed(T)
+    E_, d = 72, 1024
+    x = torch.randn(T, d, device=DEV).bfloat16()
+    gate = (torch.randn(E_, d, device=DEV) / 32).bfloat16()
+    out = torch.zeros(T, E_, device=DEV)
+    native.call("tf_router_logits_small", x, d, gate, out, E_, T, E_, d)
+    again = torch.zeros(T, E_, device=DEV)
+    native.call("tf_router_logits_small", x, d, gate, again, E_, T, E_, d)
+    torch.cuda.synchronize()
+    want = x.float() @ gate.float().t()
+    assert (out - want).abs().max() <= 1e-4 * want.abs().max() + 1e-5
+    assert torch.equal(out, again)
+
+
+def test_route_group_many_experts_is_sorted_and_stable():
+    torch.manual_seed(9)
+    El, T, k, e_lo = 200, 16, 6, 56
+    ids = torch.stack([torch.randperm(256, device=DEV)[:k] for _ in range(T)]).int().contiguous()
+    n = T * k
+    i32 = lambda m: torch.zeros(m, dtype=torch.int32, device=DEV)
+    ge, gs, gc, ng, sp, nl = i32(El), i32(El), i32(El), i32(1), i32(n), i32(1)
+    native.call("tf_route_group", ids, n, e_lo, e_lo + El, ge, gs, gc, ng, sp, nl)
+    torch.cuda.synchronize()
+    flat = ids.flatten().cpu() - e_lo
+    local = [(int(e), i) for i, e in enumerate(flat.tolist()) if 0 <= e < El]
+    want_sorted = [i for _, i in sorted(local)]                      # by expert, then pair order
+    assert int(nl) == len(local) and sp[: len(local)].tolist() == want_sorted
+    experts = sorted({e for e, _ in local})
+    assert int(ng) == len(experts) and ge[: len(experts)].tolist() == experts
+    counts = [sum(1 for e, _ in local if e == x) for x in experts]
+    assert gc[: len(experts)].tolist() == counts
+    starts = [sum(counts[:j]) for j in range(len(experts))]
+    assert gs[: len(experts)].tolist() == starts
+
+
 def test_mx8_row_quantiser_matches_codec():
     """e4m3 values with one UE8M0 scale per 32 inputs: same bytes as the host codec."""
     torch.manual_seed(5)

@@ -439,37 +439,57 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
 __global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
                                    int* group_expert, int* group_start, int* group_count, int* n_groups,
                                    int* sorted_pairs, int* n_local_pairs) {
-  extern __shared__ int cnt[];   // [E_local] counts, then offsets
+  extern __shared__ int cnt[];   // [E_local] counts, then offsets; then the local expert of every pair
   const int El = e_hi - e_lo;
-  for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
-  __syncthreads();
+  int* loc = cnt + El;
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    int e = ids[i] - e_lo;
-    if (e >= 0 && e < El) atomicAdd(&cnt[e], 1);
+    const int e = ids[i] - e_lo;
+    loc[i] = (e >= 0 && e < El) ? e : -1;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  // one thread per expert counts its pairs out of shared memory (no atomics: fixed order)
+  for (int e = threadIdx.x; e < El; e += blockDim.x) {
+    int c = 0;
+    for (int i = 0; i < n_pairs; ++i) c += (loc[i] == e);
+    cnt[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // warp 0: exclusive scan of the counts and compaction of the active experts, 32 at a time
+    const int lane = threadIdx.x;
     int off = 0, ng = 0;
-    for (int e = 0; e < El; ++e) {
-      int c = cnt[e];
-      if (c > 0) {
-        group_expert[ng] = e;
-        group_start[ng] = off;
-        group_count[ng] = c;
-        ++ng;
+    for (int base = 0; base < El; base += 32) {
+      const int e = base + lane;
+      const int c = e < El ? cnt[e] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
       }
-      cnt[e] = off;
-      off += c;
+      const unsigned act = __ballot_sync(0xffffffffu, c > 0);
+      const int start = off + inc - c;
+      if (c > 0) {
+        const int gi = ng + __popc(act & ((1u << lane) - 1u));
+        group_expert[gi] = e;
+        group_start[gi] = start;
+        group_count[gi] = c;
+      }
+      if (e < El) cnt[e] = start;
+      off += __shfl_sync(0xffffffffu, inc, 31);
+      ng += __popc(act);
     }
-    *n_groups = ng;
-    *n_local_pairs = off;
+    if (lane == 0) {
+      *n_groups = ng;
+      *n_local_pairs = off;
+    }
   }
   __syncthreads();
   // stable placement in pair order (single thread per expert keeps the order deterministic)
   for (int e = threadIdx.x; e < El; e += blockDim.x) {
     int off = cnt[e];
     for (int i = 0; i < n_pairs; ++i)
-      if (ids[i] - e_lo == e) sorted_pairs[off++] = i;
+      if (loc[i] == e) sorted_pairs[off++] = i;
   }
 }
 
@@ -562,7 +582,8 @@ TF_API int tf_router_topk(const float* logits, const float* bias, int* ids, floa
 TF_API int tf_route_group(const int* ids, int n_pairs, int e_lo, int e_hi, int* group_expert,
                           int* group_start, int* group_count, int* n_groups, int* sorted_pairs,
                           int* n_local_pairs, cudaStream_t st) {
-  route_group_kernel<<<1, 256, (e_hi - e_lo) * sizeof(int), st>>>(
+  if (n_pairs <= 0 || e_hi <= e_lo || (size_t)(e_hi - e_lo + n_pairs) * sizeof(int) > 48 * 1024) return -1;
+  route_group_kernel<<<1, 256, (e_hi - e_lo + n_pairs) * sizeof(int), st>>>(
       ids, n_pairs, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
       n_local_pairs);
   return (int)cudaGetLastError();

@@ -145,21 +145,32 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
     // ---------------- FP8, fp32 scale per 128x128 block: accumulate a block, then promote
     const float* S = reinterpret_cast<const float*>(Sg) + (long)(n0 >> 7) * p.lds;
     const float* S3 = DUAL ? reinterpret_cast<const float*>(S3g) + (long)(n0 >> 7) * p.lds : nullptr;
+    // The weights of the NEXT 128-k block are requested before the MMAs of this one (plain form;
+    // the fused form already has twice the loads per step): with N / 32 CTAs on the grid only a
+    // few warps run per SM, so the bytes each keeps in flight decide how well the stream follows HBM.
+    constexpr bool kPrefetch = !DUAL;
+    uint4 w0[2][NT], w8[2][NT], w0n[2][NT], w8n[2][NT];
+    auto load_block = [&](int kb, uint4 (&a0)[2][NT], uint4 (&a8)[2][NT]) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s)
+#pragma unroll
+        for (int ti = 0; ti < NT; ++ti) {
+          a0[s][ti] = ld_stream(wrow0[ti] + kb + s * 64 + t * 16);
+          a8[s][ti] = ld_stream(wrow8[ti] + kb + s * 64 + t * 16);
+        }
+    };
+    if (kPrefetch && k0 < k1) load_block(k0, w0, w8);
     for (int kb = k0; kb < k1; kb += 128) {
       float blk[NT][MT][4];
 #pragma unroll
       for (int ti = 0; ti < NT; ++ti)
 #pragma unroll
         for (int m = 0; m < MT; ++m) blk[ti][m][0] = blk[ti][m][1] = blk[ti][m][2] = blk[ti][m][3] = 0.f;
+      if (!kPrefetch) load_block(kb, w0, w8);
+      else if (kb + 128 < k1) load_block(kb + 128, w0n, w8n);
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         const int k = kb + s * 64 + t * 16;
-        uint4 w0[NT], w8[NT];
-#pragma unroll
-        for (int ti = 0; ti < NT; ++ti) {
-          w0[ti] = ld_stream(wrow0[ti] + k);
-          w8[ti] = ld_stream(wrow8[ti] + k);
-        }
         uint4 xv[MT][2];
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
@@ -169,8 +180,8 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
         }
 #pragma unroll
         for (int ti = 0; ti < NT; ++ti) {
-          const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[ti]);
-          const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[ti]);
+          const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[s][ti]);
+          const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[s][ti]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint32_t a[4];
@@ -195,6 +206,15 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
         for (int m = 0; m < MT; ++m)
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[ti][m][i] = fmaf((ti >> 1) ? sc3 : sc, blk[ti][m][i], acc[ti][m][i]);
+      if (kPrefetch) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int ti = 0; ti < NT; ++ti) {
+            w0[s][ti] = w0n[s][ti];
+            w8[s][ti] = w8n[s][ti];
+          }
+      }
     }
   } else if (KIND == 2) {
     // ---------------- bf16 weights: a 16-byte load holds 8 consecutive k; 64 k per step

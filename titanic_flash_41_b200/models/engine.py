@@ -808,9 +808,9 @@ class Engine:
             native.call("tf_router_topk", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
                         cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
         elif T <= self.SMALL_M and cfg.n_experts % 32 == 0:
-            # weight-streaming GEMV over the bf16 gate matrix, then top-k
-            native.call("tf_smallm_gemm", 2, L.gate, None, None, None, 0, 0, d * 2, 0, b["hb"], d, b["logits_r"],
-                        cfg.n_experts, 0, cfg.n_experts, d, T, None, None, None, None, None, 1, 0, T, 0.0)
+            # one warp per expert row over the bf16 gate matrix, then top-k
+            native.call("tf_router_logits_small", b["hb"], d, L.gate, b["logits_r"], cfg.n_experts, T,
+                        cfg.n_experts, d)
             native.call("tf_router_topk", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
                         cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
         else:

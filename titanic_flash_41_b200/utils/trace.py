@@ -25,7 +25,8 @@ from ..ops import native
 
 
 class KernelClock:
-    def __init__(self):
+    def __init__(self, shapes: bool = False):
+        self.shapes = shapes      # split the weight-streaming GEMV rows of the table by matrix shape
         self.events: List[Tuple[str, str, torch.cuda.Event, torch.cuda.Event]] = []
         self._part = "-"
         self._orig = None
@@ -44,6 +45,9 @@ class KernelClock:
                 return clock._orig(name, *args, **kw)
             finally:
                 b.record()
+                if name == "tf_smallm_gemm" and clock.shapes:
+                    # kind, output features x inputs, fused second matrix
+                    name = "%s[k%d %dx%d%s]" % (name, args[0], args[14], args[15], " dual" if args[2] is not None else "")
                 clock.events.append((clock._part, name, a, b))
         native.call = timed
         return self
