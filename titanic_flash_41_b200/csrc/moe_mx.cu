@@ -10,11 +10,13 @@
 //   scale factors in tensor memory: for A four 32-bit columns per 128 inputs (column j holds
 //       rows 32j..32j+31, byte b the b-th group of 32 inputs), for B one column per 128 inputs;
 //   D = f32 in tensor memory, 128 lanes x 16 columns.
-// The CUDA cores touch only the scales (16 bytes per row and 512 inputs, written to tensor memory
-// with tcgen05.st by the four warps that later run the epilogue) and the 16 x 128 results.
+// The CUDA cores touch only the scales (16 bytes per row and 512 inputs: TMA stages them in shared
+// memory with the data, the four warps that later run the epilogue rearrange them and write them
+// to tensor memory with tcgen05.st) and the 16 x 128 results.
 //
 // Work item = (active expert, 128 output features); persistent CTAs, one per SM:
-//   warp 0  TMA producer   (ring of 128-input stages: weights of w1 [and w3] + activation rows)
+//   warp 0  TMA producer   (ring of 128-input stages: weights of w1 [and w3] + activation rows;
+//                           ring of scale blocks, one per 512 inputs)
 //   warp 1  MMA issuer     (owns the TMEM allocation)
 //   warps 2-5  scale loaders, then epilogue (clamped SwiGLU for the fused w1/w3 form)
 // Every wait is bounded: on a time-out the CTA raises its abort flag, reports TF_TIMEOUT, frees its
@@ -89,30 +91,35 @@ __device__ __forceinline__ uint32_t idesc_mx(uint32_t sf) {
 template <int DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__ CUtensorMap mapW3,
-              const __grid_constant__ CUtensorMap mapX, const MxParams p) {
+              const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapS1,
+              const __grid_constant__ CUtensorMap mapS3, const __grid_constant__ CUtensorMap mapSX, const MxParams p) {
   constexpr int kMats = DUAL ? 2 : 1;
-  constexpr int kStages = DUAL ? 6 : 10;
+  constexpr int kStages = DUAL ? 6 : 11;
+  // scale bytes of one 512-input block: [128 rows][16] per matrix, then [16 rows][16] of the activations
+  constexpr int kSfsBytes = (kMats * kTile * 16 + kRows * 16 + 127) / 128 * 128;
   constexpr int kStageBytes = kMats * kTile * 128 + kRows * 128;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = tc::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - raw);
-  const uint32_t bar0 = base + kStages * kStageBytes;
+  const uint32_t sfs0 = base + kStages * kStageBytes;                    // kSfBufs staging slots for scales
+  const uint32_t bar0 = sfs0 + kSfBufs * kSfsBytes;
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto sf_full = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
   auto sf_empty = [&](int b) { return bar0 + 8u * (2 * kStages + kSfBufs + b); };
   auto acc_full = [&](int b) { return bar0 + 8u * (2 * kStages + 2 * kSfBufs + b); };
   auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kStages + 2 * kSfBufs + 2 + b); };
-  volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(aligned + kStages * kStageBytes + 8 * (2 * kStages + 2 * kSfBufs + 4));
+  auto sfs_full = [&](int b) { return bar0 + 8u * (2 * kStages + 2 * kSfBufs + 4 + b); };
+  auto sfs_empty = [&](int b) { return bar0 + 8u * (2 * kStages + 3 * kSfBufs + 4 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      aligned + kStages * kStageBytes + kSfBufs * kSfsBytes + 8 * (2 * kStages + 4 * kSfBufs + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(const_cast<uint32_t*>(tmem_slot) + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = p.N / kTile;
   const int items = *p.n_groups * tiles_n;
   const int kchunks = p.K / kBK, nsuper = p.K / kSuper;
-  const int ks = p.K / 32;                      // scale bytes per row
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -122,6 +129,8 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
     for (int b = 0; b < kSfBufs; ++b) {
       tc::mbar_init(sf_full(b), 4);
       tc::mbar_init(sf_empty(b), 1);
+      tc::mbar_init(sfs_full(b), 1);
+      tc::mbar_init(sfs_empty(b), 4);
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(acc_full(b), 1);
@@ -143,14 +152,28 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
       tc::prefetch_tmap(&mapW1);
       if (DUAL) tc::prefetch_tmap(&mapW3);
       tc::prefetch_tmap(&mapX);
+      tc::prefetch_tmap(&mapS1);
+      tc::prefetch_tmap(&mapSX);
       const uint32_t tx = kMats * p.a_tx_bytes + kRows * 128;
-      int it = 0;
+      int it = 0, fsf = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const int g = item / tiles_n, n0 = (item % tiles_n) * kTile;
         const int wrow = p.g_expert[g] * p.N + n0;
         const int xrow = DUAL ? 0 : p.g_start[g];
         for (int kc = 0; kc < kchunks; ++kc, ++it) {
+          if (kc % (kSuper / kBK) == 0) {
+            // the scale bytes of the next 512 inputs travel with the data: the four loader warps
+            // find them in shared memory instead of waiting on first-touch global loads
+            const int sl = fsf % kSfBufs, sc = kc / (kSuper / kBK);
+            if (!(ok = tc::mbar_wait(sfs_empty(sl), ((fsf / kSfBufs) & 1) ^ 1, abort_flag))) break;
+            tc::mbar_expect_tx(sfs_full(sl), kMats * kTile * 16 + kRows * 16);
+            const uint32_t d = sfs0 + sl * kSfsBytes;
+            tc::tma_load_2d(d, &mapS1, sc * 16, wrow, sfs_full(sl));
+            if (DUAL) tc::tma_load_2d(d + kTile * 16, &mapS3, sc * 16, wrow, sfs_full(sl));
+            tc::tma_load_2d(d + kMats * kTile * 16, &mapSX, sc * 16, xrow, sfs_full(sl));
+            ++fsf;
+          }
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!(ok = tc::mbar_wait(empty(s), ph ^ 1, abort_flag))) break;
@@ -207,24 +230,13 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------------ scale loaders + epilogue
-    // One flat sequence of (item, 512-input block) runs through the loaders: the loads of the next
-    // block are in flight while this one is written to tensor memory, and the epilogue of an item
-    // runs only after the first block of the NEXT item has been delivered, so the MMA warp never
-    // waits for an epilogue.
+    // One flat sequence of (item, 512-input block) runs through the loaders: the scale bytes of a
+    // block arrive in shared memory by TMA (requested a ring ahead by the producer), each warp
+    // rearranges them into the tensor-memory layout for its own lane quadrant, and the epilogue of
+    // an item runs only after the first block of the NEXT item has been delivered, so the MMA warp
+    // never waits for an epilogue.
     const int quad = warp & 3;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    auto issue = [&](int item, int sc, uint4 (&w)[kMats][4], uint4& xv) {
-      const int g = item / tiles_n, n0 = (item % tiles_n) * kTile;
-      const int e = p.g_expert[g];
-      const int xrow = min((DUAL ? 0 : p.g_start[g]) + (lane & 15), p.x_rows - 1);
-#pragma unroll
-      for (int m = 0; m < kMats; ++m) {
-        const uint8_t* srow = (m == 0 ? p.sw1 : p.sw3) + ((long)e * p.N + n0 + lane) * ks + sc * 16;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w[m][j] = __ldg(reinterpret_cast<const uint4*>(srow + (long)(32 * j) * ks));
-      }
-      xv = *reinterpret_cast<const uint4*>(p.sx + (long)xrow * ks + sc * 16);
-    };
     auto epilogue = [&](int item, int n_item) -> bool {
       const int g = item / tiles_n, n0 = (item % tiles_n) * kTile;
       const int gs = p.g_start[g], gc = p.g_count[g];
@@ -285,27 +297,37 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
     };
     int f = 0, n_item = 0, item = blockIdx.x, sc = 0, pend_item = -1, pend_n = 0;
     bool ok = true;
-    uint4 wa[kMats][4], wb[kMats][4], xa, xb;
-    if (item < items) issue(item, sc, wa, xa);
     while (item < items && ok) {
       int nitem = item, nsc = sc + 1;
       if (nsc == nsuper) {
         nitem += gridDim.x;
         nsc = 0;
       }
-      if (nitem < items) issue(nitem, nsc, wb, xb);
       const int sb = f % kSfBufs;
-      if (!(ok = tc::mbar_wait(sf_empty(sb), ((f / kSfBufs) & 1) ^ 1, abort_flag))) break;
+      const uint32_t par = (f / kSfBufs) & 1;
+      if (!(ok = tc::mbar_wait(sfs_full(sb), par, abort_flag))) break;
+      // rows lane, lane+32, lane+64, lane+96 of each matrix: 16 scale bytes = four 128-input words
+      const uint8_t* sl = aligned + kStages * kStageBytes + sb * kSfsBytes;
+      uint4 w[kMats][4];
+#pragma unroll
+      for (int m = 0; m < kMats; ++m)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          w[m][j] = *reinterpret_cast<const uint4*>(sl + m * kTile * 16 + (lane + 32 * j) * 16);
+      const uint4 xa = *reinterpret_cast<const uint4*>(sl + kMats * kTile * 16 + (lane & 15) * 16);
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(sfs_empty(sb));
+      if (!(ok = tc::mbar_wait(sf_empty(sb), par ^ 1, abort_flag))) break;
       tc::tc_fence_after();
 #pragma unroll
       for (int m = 0; m < kMats; ++m) {
         uint32_t v[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          v[0 + j] = wa[m][j].x;       // inputs   0..127 of this block: column j = rows 32j..32j+31
-          v[4 + j] = wa[m][j].y;       // inputs 128..255
-          v[8 + j] = wa[m][j].z;
-          v[12 + j] = wa[m][j].w;
+          v[0 + j] = w[m][j].x;       // inputs   0..127 of this block: column j = rows 32j..32j+31
+          v[4 + j] = w[m][j].y;       // inputs 128..255
+          v[8 + j] = w[m][j].z;
+          v[12 + j] = w[m][j].w;
         }
         tmem_st16(tmem_base + lane_base + 64 + sb * 32 + m * 16, v);
       }
@@ -329,11 +351,6 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
         pend_item = item;
         pend_n = n_item++;
       }
-#pragma unroll
-      for (int m = 0; m < kMats; ++m)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) wa[m][j] = wb[m][j];
-      xa = xb;
       item = nitem;
       sc = nsc;
     }
@@ -443,7 +460,10 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
     cudaFuncSetAttribute(moe_mx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(moe_mx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   }
-  CUtensorMap m1, m3, mx;
+  CUtensorMap m1, m3, mx, ms1, ms3, msx;
+  if (!tc::make_map_2d_plain(&ms1, s1, (uint64_t)experts * N, K / 32, K / 32, 16, kTile)) return -4;
+  if (!tc::make_map_2d_plain(&ms3, dual ? s3 : s1, (uint64_t)experts * N, K / 32, K / 32, 16, kTile)) return -4;
+  if (!tc::make_map_2d_plain(&msx, sx, x_rows, K / 32, K / 32, 16, kRows)) return -4;
   // blocked: [experts * N/128 * K/128] blocks of [128 rows x 128 inputs], each 8 KB contiguous
   const uint64_t wrows = blocked ? (uint64_t)experts * N * (K / kBK) : (uint64_t)experts * N;
   const uint64_t wcols = blocked ? kBK : K;
@@ -464,9 +484,10 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
   p.blocked = blocked;
   p.status = reinterpret_cast<TfStatusWord*>(status);
   const int grid = min(g_mx_sms, max_groups * (N / kTile));
-  const int stages = dual ? 6 : 10;
-  const int smem = stages * ((dual ? 2 : 1) * kTile * 128 + kRows * 128) + 1024 + 512;
-  if (dual) moe_mx_kernel<1><<<grid, kThreads, smem, st>>>(m1, m3, mx, p);
-  else moe_mx_kernel<0><<<grid, kThreads, smem, st>>>(m1, m3, mx, p);
+  const int stages = dual ? 6 : 11, mats = dual ? 2 : 1;
+  const int sfs = (mats * kTile * 16 + kRows * 16 + 127) / 128 * 128;
+  const int smem = stages * (mats * kTile * 128 + kRows * 128) + kSfBufs * sfs + 1024 + 512;
+  if (dual) moe_mx_kernel<1><<<grid, kThreads, smem, st>>>(m1, m3, mx, ms1, ms3, msx, p);
+  else moe_mx_kernel<0><<<grid, kThreads, smem, st>>>(m1, m3, mx, ms1, ms3, msx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
