@@ -319,6 +319,44 @@ def test_engram_layers_match_oracle(hc):
         eng.forward(E.StepPlan.build([(1, pos, [5, 6])]))
 
 
+def test_engram_ids_hashed_on_the_device_equal_the_host_hashes():
+    """Two conversations in one launch, one at its start (blocked orders), one mid-stream: the ids
+    written by tf_engram_hash equal HashHistory's, and the logits equal those of host-hashed plans
+    bit for bit; a speculative decoder on an Engram model commits the same tokens on both paths."""
+    from titanic_flash_41_b200.config import DraftConfig, EngramConfig
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    cfg = small_config(engram=EngramConfig(layers=(0, 2), rows_per_table=1500), draft=DraftConfig(layers=1, depth=3))
+    W = oracle.init_weights(cfg, 0)
+    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,)), W)
+    g = torch.Generator().manual_seed(4)
+    a = torch.randint(3, cfg.vocab, (9,), generator=g).tolist()
+    hist = torch.randint(3, cfg.vocab, (40,), generator=g).tolist()
+    eng.forward(E.StepPlan.build([(1, 0, hist)]).attach_recent(cfg, [[]]))
+    bt = torch.randint(3, cfg.vocab, (9,), generator=g).tolist()
+    blocks = [(0, 0, a), (1, 40, bt)]
+    prevs = [[], hist[-3:]]
+    host = E.StepPlan.build(blocks).attach_engram(cfg, prevs)
+    want = eng.forward(host).clone()
+    dev_plan = E.StepPlan.build(blocks).attach_recent(cfg, prevs)
+    got = eng.forward(dev_plan).clone()
+    eng.status.check()
+    ids = eng._bufs(18)["eg_ids"][:, :18].cpu()                      # [tables, T, ids]
+    assert torch.equal(ids, torch.from_numpy(host.engram_ids.transpose(1, 0, 2).copy()))
+    assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="attach_recent"):
+        eng.forward(E.StepPlan.build([(1, 49, [5, 6])]))
+    # speculative decoding: proposals are sampled inside the graph, so only the device can hash them
+    toks = {}
+    for use_graph in (True, False):
+        eng.forward(E.StepPlan.build([(1, 0, hist)]).attach_recent(cfg, [[]]))
+        dec = SpecDecoder(eng, 1, temperature=0.6, top_p=0.95, use_graph=use_graph)
+        slots = [DecodeSlot(region=1, length=40, anchor=7, seed=3, recent=hist[-3:])]
+        toks[use_graph] = [t for _ in range(5) for t in dec.step(slots)[0]]
+        eng.status.check()
+        assert slots[0].recent == (hist + toks[use_graph])[-3:]
+    assert toks[True] == toks[False]
+
+
 def test_reference_model_widths_run_on_the_engine():
     """The reference model's real widths (hidden 5120, 512-wide latent heads, low-rank query 1280, eight
     output groups of rank 1024, four residual copies, 32 index heads, expert width 2304) with few layers and

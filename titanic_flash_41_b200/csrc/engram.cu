@@ -91,3 +91,68 @@ TF_API int tf_engram_gate(const void* x, const void* kv, const void* qw, const v
                                                     (__nv_bfloat16*)out, m, d, eps);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// n-gram hash ids on the device.  A verification step samples its proposal tokens inside the
+// captured graph, so the host cannot hash them; this kernel reads the tokens of the launch where
+// the embedding reads them.  One thread per (row, table); same arithmetic as the host
+// (models/engram.py HashHistory.prepare; reference: src/engram.rs hash history): compressed token
+// ids, rolling = c0*m0 ^ c1*m1 ^ ... in 64 bits, id = rolling mod prime + offset per (order, head).
+// `recent` holds, per row, the ngram-1 tokens before the row's conversation block, newest first.
+namespace {
+constexpr int kMaxNgram = 8;
+
+__global__ void engram_hash_kernel(const int* __restrict__ tokens, const int* __restrict__ pos,
+                                   const int* __restrict__ first_row, const int* __restrict__ recent,
+                                   const long long* __restrict__ token_map, int vocab,
+                                   const unsigned long long* __restrict__ mult,
+                                   const unsigned long long* __restrict__ primes,
+                                   const unsigned long long* __restrict__ offsets, long long* __restrict__ out,
+                                   int T, long out_table_stride, int tables, int ngram, int heads, int pad_token,
+                                   int image_token, TfStatusWord* st) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * tables) return;
+  const int i = idx / tables, t = idx % tables;
+  const int in_block = i - first_row[i];
+  const unsigned long long pad = (unsigned long long)token_map[pad_token];
+  unsigned long long comp[kMaxNgram];
+  bool blocked = false;
+  for (int back = 0; back < ngram; ++back) {
+    if (pos[i] < back) blocked = true;
+    const int tok = back <= in_block ? tokens[i - back] : recent[i * (ngram - 1) + (back - in_block - 1)];
+    if (tok == image_token) {
+      blocked = true;
+    } else if (tok < 0 || tok >= vocab) {
+      tf_report(st, TF_BAD_INDEX, 140, i, tok);
+      blocked = true;
+    }
+    comp[back] = blocked ? pad : (unsigned long long)token_map[tok];
+  }
+  const int ids = (ngram - 1) * heads;
+  long long* o = out + (long)t * out_table_stride + (long)i * ids;
+  unsigned long long rolling = comp[0] * mult[t * ngram];
+  for (int back = 1; back < ngram; ++back) {
+    rolling ^= comp[back] * mult[t * ngram + back];
+    for (int head = 0; head < heads; ++head) {
+      const int h = (back - 1) * heads + head;
+      o[h] = (long long)(rolling % primes[t * ids + h] + offsets[t * ids + h]);
+    }
+  }
+}
+}  // namespace
+
+// tokens / pos / first_row [T] int32; recent [T, ngram-1] int32; token_map [vocab] int64;
+// mult [tables, ngram], primes / offsets [tables, (ngram-1)*heads] uint64; out [tables][T rows at
+// out_table_stride elements per table][(ngram-1)*heads] int64
+TF_API int tf_engram_hash(const int* tokens, const int* pos, const int* first_row, const int* recent,
+                          const void* token_map, int vocab, const void* mult, const void* primes, const void* offsets,
+                          void* out, int T, long out_table_stride, int tables, int ngram, int heads, int pad_token,
+                          int image_token, void* status, cudaStream_t st) {
+  if (T <= 0 || ngram < 2 || ngram > kMaxNgram || pad_token < 0 || pad_token >= vocab) return -1;
+  const int n = T * tables;
+  engram_hash_kernel<<<(n + 127) / 128, 128, 0, st>>>(
+      tokens, pos, first_row, recent, (const long long*)token_map, vocab, (const unsigned long long*)mult,
+      (const unsigned long long*)primes, (const unsigned long long*)offsets, (long long*)out, T, out_table_stride,
+      tables, ngram, heads, pad_token, image_token, (TfStatusWord*)status);
+  return (int)cudaGetLastError();
+}

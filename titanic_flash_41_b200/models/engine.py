@@ -334,6 +334,7 @@ class StepPlan:
     group_rows: int             # rows per conversation block (uniform), used to group index scoring
     min_pos: Optional[np.ndarray] = None   # [T] oldest window position a row may attend (default 0)
     engram_ids: Optional[np.ndarray] = None   # [T, tables, ids] int64 row ids of the hashed n-gram memory
+    engram_recent: Optional[np.ndarray] = None  # [T, ngram-1] int32: tokens before the row's block, newest first
     blocks: Optional[list] = None          # (region, start, tokens) as given to build()
 
     META_ROWS = 7
@@ -345,6 +346,29 @@ class StepPlan:
         self.engram_ids = np.concatenate([EG.hash_positions(md, prev, list(t), start)
                                           for (region, start, t), prev in zip(self.blocks, prevs)]).astype(np.int64)
         return self
+
+    def attach_recent(self, cfg: ModelConfig, prevs: Sequence[Sequence[int]]) -> "StepPlan":
+        """Leave the hashing to the device (``tf_engram_hash`` at the start of the launch): record, for
+        every row, the ngram-1 tokens right before its block (``prevs[i]``, oldest first; shorter at
+        the start of a conversation), newest first and padded with the pad token."""
+        return self._set_recent(self.recent_rows(cfg, [(len(t), prev) for (_, _, t), prev in zip(self.blocks, prevs)]))
+
+    def _set_recent(self, rows: np.ndarray) -> "StepPlan":
+        self.engram_recent = rows
+        return self
+
+    @staticmethod
+    def recent_rows(cfg: ModelConfig, blocks: Sequence[Tuple[int, Sequence[int]]]) -> np.ndarray:
+        """[(rows, previous tokens oldest first)] -> [sum rows, ngram-1] int32, newest first."""
+        from . import engram as EG
+        md = EG.metadata_for(cfg)
+        n = md.ngram - 1
+        out = []
+        for rows, prev in blocks:
+            rec = list(reversed(list(prev)[-n:]))
+            rec += [md.pad_token] * (n - len(rec))
+            out.append(np.tile(np.asarray(rec, dtype=np.int32), (rows, 1)))
+        return np.concatenate(out)
 
     def meta_host(self, ratio: int) -> np.ndarray:
         """[META_ROWS, T] int32 block uploaded per launch: tokens, pos, region, first_row, last_pos,
@@ -571,6 +595,8 @@ class Engine:
             ec = cfg.engram
             n_ids = (ec.ngram - 1) * ec.heads
             b["eg_ids"] = torch.zeros(len(ec.layers), T, n_ids, dtype=torch.int64, device=dev)
+            b["eg_recent"] = torch.zeros(T, ec.ngram - 1, dtype=torch.int32, device=dev)
+            b["eg_hash"] = False         # True: the launch hashes its own tokens on the device
             b["eg_rows16"] = torch.zeros(T, n_ids * ec.width, dtype=torch.float16, device=dev)
             b["eg_kv"] = torch.zeros(T, (m + 1) * d, dtype=torch.bfloat16, device=dev)
             if "x2" not in b:
@@ -715,6 +741,28 @@ class Engine:
         elif not fused:
             self._allreduce(b["delta"][:T])
             b["pending"] = True
+
+    def _engram_hash(self, T: int, b: dict) -> None:
+        """Row ids of every Engram table from the tokens of this launch (the verification rows of a
+        decode step carry proposals sampled inside the graph, which the host never sees)."""
+        md = self._engram_md()
+        ec = self.cfg.engram
+        meta = b["meta"]
+        native.call("tf_engram_hash", meta[0], meta[1], meta[3], b["eg_recent"], md["token_map"], self.cfg.vocab,
+                    md["mult"], md["primes"], md["offsets"], b["eg_ids"], T, b["eg_ids"].stride(0), len(ec.layers),
+                    ec.ngram, ec.heads, md["pad"], md["image"], self.status.t)
+
+    def _engram_md(self) -> dict:
+        md = getattr(self, "_eg_md", None)
+        if md is None:
+            from . import engram as EG
+            h = EG.metadata_for(self.cfg)
+            dev = self.dev
+            as_i64 = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.uint64).view(np.int64)).to(dev)
+            md = dict(token_map=as_i64(h.token_map), mult=as_i64(h.multipliers), primes=as_i64(h.primes),
+                      offsets=as_i64(h.offsets), pad=h.pad_token, image=h.image_token)
+            self._eg_md = md
+        return md
 
     def _engram(self, e: int, L: LayerWeights, T: int, b: dict) -> None:
         """Hashed n-gram memory in front of an Engram layer: gather this rank's rows (others read as
@@ -913,11 +961,16 @@ class Engine:
         host = plan.meta_host(self.cfg.compress_ratio)
         b["meta"][:, :T].copy_(torch.from_numpy(host), non_blocking=True)
         if self.engram:
-            if plan.engram_ids is None:
-                raise ValueError("this model has Engram layers: the plan needs attach_engram()")
-            # [tables, T, ids] on the device
-            b["eg_ids"][:, :T].copy_(torch.from_numpy(np.ascontiguousarray(plan.engram_ids.transpose(1, 0, 2))),
-                                     non_blocking=True)
+            if plan.engram_recent is not None:
+                b["eg_recent"][:T].copy_(torch.from_numpy(plan.engram_recent), non_blocking=True)
+                b["eg_hash"] = True
+            elif plan.engram_ids is not None:
+                # host-hashed ids, [tables, T, ids] on the device
+                b["eg_ids"][:, :T].copy_(torch.from_numpy(np.ascontiguousarray(plan.engram_ids.transpose(1, 0, 2))),
+                                         non_blocking=True)
+                b["eg_hash"] = False
+            else:
+                raise ValueError("this model has Engram layers: the plan needs attach_recent() or attach_engram()")
 
     @staticmethod
     def plan_shape(plan: StepPlan, ratio: int) -> Tuple[int, int]:
@@ -948,6 +1001,8 @@ class Engine:
         the input residual (late-group replay); the head runs only when the last layer does."""
         cfg = self.cfg
         layer_hi = len(self.layers) if layer_hi is None else layer_hi
+        if self.engram and b.get("eg_hash"):
+            self._engram_hash(T, b)
         if x_in is None:
             e = b["e"] if cfg.hc_mult > 1 else b["x"]
             native.call("tf_embed", b["meta"][0], self.embed_w, e, T, cfg.hidden, cfg.vocab, self.status.t)

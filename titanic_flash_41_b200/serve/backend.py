@@ -160,10 +160,12 @@ class EngineBackend:
     def reset(self, region: int) -> None:
         pass     # state is position-addressed: a new conversation simply overwrites it
 
-    def prefill(self, region, tokens, start, on_chunk=None):
+    wants_prev = True      # prefill(..., prev=tokens right before `start`)
+
+    def prefill(self, region, tokens, start, on_chunk=None, prev=()):
         from .prefill import run_prefill
         lg = run_prefill(self.e, region, torch.tensor(list(tokens), dtype=torch.int32), self.chunk, start,
-                         True, on_chunk)
+                         True, on_chunk, prev=prev)
         if lg is None:
             return None
         self.last_hidden_rows[region] = self.e.last_hidden[-1:].clone() if self.e.last_hidden is not None else None

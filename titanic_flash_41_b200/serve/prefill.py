@@ -30,8 +30,18 @@ def _patch_for(embeds, lo: int, T: int, dev):
     return (offs[m] - lo).long(), vals.to(dev)[m]
 
 
+def _recent(plan: StepPlan, cfg, prev, toks: np.ndarray, offset: int) -> StepPlan:
+    """Models with Engram layers: give the plan the tokens right before its block (the prompt's own
+    rows before ``offset``, and ``prev``, the tokens before the prompt part being prefilled)."""
+    if cfg.engram is None or not cfg.engram.layers:
+        return plan
+    n = cfg.engram.ngram - 1
+    before = (list(prev)[-n:] + toks[max(0, offset - n):offset].tolist())[-n:]
+    return plan.attach_recent(cfg, [before])
+
+
 def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List[int], start: int, late: int,
-                         tail: torch.Tensor, tail_n: int, embeds=None, on_chunk=None) -> bool:
+                         tail: torch.Tensor, tail_n: int, embeds=None, on_chunk=None, prev=()) -> bool:
     """Encoder layers [0, late) layer by layer over ALL chunks of the prompt.
 
     The residual stream of the whole prompt (n x hidden bf16: 1 GB at 129K tokens) and the current
@@ -44,7 +54,8 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
     n = int(toks.shape[0])
     resid = torch.empty(n, cfg.hidden * cfg.hc_mult, dtype=torch.bfloat16, device=eng.dev)
     offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
-    plans = [StepPlan.build([(region, start + int(offs[c]), toks[offs[c]:offs[c + 1]].tolist())], logits="last")
+    plans = [_recent(StepPlan.build([(region, start + int(offs[c]), toks[offs[c]:offs[c + 1]].tolist())],
+                                    logits="last"), cfg, prev, toks, int(offs[c]))
              for c in range(len(sizes))]
     shapes = [eng.plan_shape(p, cfg.compress_ratio) for p in plans]
     sel_store: dict = {}
@@ -86,10 +97,12 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
 def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, need_logits: bool = True,
                 on_chunk: Optional[Callable[[int], bool]] = None,
                 widths: Optional[Sequence[int]] = None, layer_major: Optional[bool] = None,
-                embeds: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
+                embeds: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                prev: Sequence[int] = ()) -> Optional[torch.Tensor]:
     """Prefill ``tokens`` at positions start.. into ``region``.  Returns fp32 logits of the last
     row (or None when cancelled by ``on_chunk`` returning False).  ``embeds`` = (prompt offsets
-    [m], rows [m, hidden]) replaces the token embedding at those offsets (image spans)."""
+    [m], rows [m, hidden]) replaces the token embedding at those offsets (image spans).  ``prev``:
+    the tokens right before ``start`` (models with Engram layers hash n-grams across the seam)."""
     cfg = eng.cfg
     toks = np.asarray(tokens.cpu() if isinstance(tokens, torch.Tensor) else tokens, dtype=np.int32)
     n = int(toks.shape[0])
@@ -103,13 +116,14 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
     done = 0
     logits = None
     if layer_major:
-        if not _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n, embeds, on_chunk):
+        if not _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n, embeds, on_chunk, prev):
             return None
         if late == L and need_logits:
             logits = eng._head(sizes[-1], eng._bufs(sizes[-1]), torch.tensor([sizes[-1] - 1], device=eng.dev))
         sizes = []
     for T in sizes:
-        plan = StepPlan.build([(region, start + done, toks[done:done + T].tolist())], logits="last")
+        plan = _recent(StepPlan.build([(region, start + done, toks[done:done + T].tolist())], logits="last"),
+                       cfg, prev, toks, done)
         b = eng._bufs(T)
         eng.upload_plan(plan, b)
         nmax, rpg = eng.plan_shape(plan, cfg.compress_ratio)
@@ -129,7 +143,8 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
             return None
     if late < L and tail_n > 0:
         p0 = start + n - tail_n
-        plan = StepPlan.build([(region, p0, toks[n - tail_n:].tolist())], logits="last")
+        plan = _recent(StepPlan.build([(region, p0, toks[n - tail_n:].tolist())], logits="last"),
+                       cfg, prev, toks, n - tail_n)
         plan.min_pos = np.full(tail_n, p0, dtype=np.int32)     # older rows never ran in the late group
         b = eng._bufs(tail_n)
         eng.upload_plan(plan, b)

@@ -60,7 +60,7 @@ def resume(worker, ck: RequestCheckpoint, region: int, job) -> None:
     from .worker import Active
     worker.b.restore(region, ck.image)
     slot = DecodeSlot(region=region, length=len(ck.committed), anchor=ck.anchor, seed=ck.seed,
-                      temperature=ck.temperature, top_p=ck.top_p)
+                      temperature=ck.temperature, top_p=ck.top_p, recent=list(ck.committed[-8:]))
     job.generated = list(ck.emitted)
     job.region = region
     worker.active[region] = Active(job, slot, list(ck.prompt), ck.limit, time.monotonic(), time.monotonic())

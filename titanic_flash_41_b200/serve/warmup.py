@@ -26,7 +26,8 @@ def _run(backend, region: int, prompt: List[int], steps: int, seed: int):
     backend.reset(region)
     logits = backend.prefill(region, prompt, 0, None)
     first = backend.sample(logits, 0.0, 1.0, seed, len(prompt))
-    slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=seed, temperature=0.0, top_p=1.0)
+    slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=seed, temperature=0.0, top_p=1.0,
+                      recent=list(prompt[-8:]))
     out = [first]
     for _ in range(steps):
         out += backend.decode_step([slot])[0]

@@ -176,7 +176,11 @@ class Worker:
                     self._step()
                     last_slice = time.monotonic()
                 return not (job is not None and job.cancelled.is_set())
-            logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk)
+            if getattr(self.b, "wants_prev", False):
+                # n-gram memory layers hash across the seam between reused and new tokens
+                logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk, prev=prompt[max(0, pos - 8):pos])
+            else:
+                logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk)
             if logits is None:
                 self._emit(job, "error", {"code": "cancelled", "message": "cancelled during prefill"})
                 if self.sched and job:
@@ -187,7 +191,7 @@ class Worker:
                 self.cache.insert(self.b.snapshot(region, prompt[:stop], "checkpoint", cmd.get("media", "")))
         first = self.b.sample(logits, cmd["temperature"], cmd["top_p"], cmd["seed"], len(prompt))
         slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=cmd["seed"],
-                          temperature=cmd["temperature"], top_p=cmd["top_p"])
+                          temperature=cmd["temperature"], top_p=cmd["top_p"], recent=list(prompt[-8:]))
         a = Active(job or Job(cmd["id"], prompt, cmd["limit"]), slot, prompt, cmd["limit"], t0, time.monotonic())
         a.job.region = region
         self.active[region] = a

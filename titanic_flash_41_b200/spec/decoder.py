@@ -33,6 +33,9 @@ class DecodeSlot:
     temperature: float = 0.6
     top_p: float = 0.95
     emitted: List[int] = field(default_factory=list)
+    # models with Engram layers: the committed tokens right before ``anchor`` (oldest first; the
+    # last ngram-1 are used), from which the device hashes the n-gram ids of the step's rows
+    recent: List[int] = field(default_factory=list)
 
 
 class SpecDecoder:
@@ -57,7 +60,11 @@ class SpecDecoder:
         # pinned host staging + device mirrors: [meta_verify(6*S*R) | meta_draft(g*6*S)] ints, uniforms
         self.n_meta_v = StepPlan.META_ROWS * S * self.R
         self.n_meta_d = StepPlan.META_ROWS * S
-        self.h_int = torch.zeros(self.n_meta_v + g * self.n_meta_d, dtype=torch.int32).pin_memory()
+        self.n_rec = (cfg.engram.ngram - 1) if engine.engram else 0
+        self.n_eg = S * self.R * self.n_rec          # per verify row: the tokens before its block
+        if engine.engram:
+            self.bv["eg_hash"] = True
+        self.h_int = torch.zeros(self.n_meta_v + g * self.n_meta_d + self.n_eg, dtype=torch.int32).pin_memory()
         self.d_int = torch.zeros_like(self.h_int, device=dev)
         self.h_u = torch.zeros(S, g + 2, dtype=torch.float64).pin_memory()     # accept[g], final, spare
         self.d_u = torch.zeros_like(self.h_u, device=dev)
@@ -103,6 +110,9 @@ class SpecDecoder:
             md = pd.meta_host(ratio)
             o = self.n_meta_v + j * self.n_meta_d
             hi[o: o + self.n_meta_d] = md.reshape(-1)
+        if self.n_eg:
+            o = self.n_meta_v + g * self.n_meta_d
+            hi[o: o + self.n_eg] = StepPlan.recent_rows(cfg, [(R, s.recent) for s in slots]).reshape(-1)
         hu = self.h_u.numpy()
         for i, s in enumerate(slots):
             dr, ac, fin = rng.round_uniforms(s.seed, s.length, g)
@@ -141,6 +151,9 @@ class SpecDecoder:
             self.props[:, j].copy_(self.ptok)
         # target verification of anchor + proposals
         self.bv["meta"].copy_(mv)
+        if self.n_eg:
+            o = self.n_meta_v + g * self.n_meta_d
+            self.bv["eg_recent"].copy_(self.d_int[o: o + self.n_eg].view(S * R, self.n_rec))
         if g > 0:
             tok = self.bv["meta"][0].view(S, R)
             tok[:, 1:].copy_(self.props[:, :g])
@@ -193,6 +206,8 @@ class SpecDecoder:
             toks = [s.anchor] + (props[i][: acc[i]] if props else [])
             s.length += len(toks)
             s.emitted += toks
+            if self.n_rec:
+                s.recent = (list(s.recent) + toks)[-self.n_rec:]
             s.anchor = nxt[i]
             out.append(toks)
         return out
