@@ -357,6 +357,89 @@ def test_engram_ids_hashed_on_the_device_equal_the_host_hashes():
     assert toks[True] == toks[False]
 
 
+def test_two_level_candidates_in_the_layer_loop():
+    """Long decode rows: the candidate source layer publishes its best blocks of 8 keys and the
+    index layer after it selects only among them; short rows and prefill chunks score densely."""
+    from titanic_flash_41_b200.ops import two_level as TL
+    cfg = small_config(candidate_blocks=4, index_topk=8)
+    W = oracle.init_weights(cfg, 0)
+    mk = lambda tl: E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(256,),
+                                                            two_level_index_min=tl), W)
+    eng, dense = mk(16), mk(0)
+    assert eng.candidate_source == 0
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab, (230,), generator=g).tolist()
+    calls = []
+    orig = TL.consume
+    TL.consume = lambda *a, **k: (calls.append(a[3].clone()), orig(*a, **k))[1]
+    try:
+        a = eng.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
+        b = dense.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
+        assert not calls and torch.equal(a, b)                     # a prefill chunk never takes the sparse path
+        toks = [5, 6, 7, 8]
+        a = eng.forward(E.StepPlan.build([(0, 230, toks)])).clone()
+        b = dense.forward(E.StepPlan.build([(0, 230, toks)])).clone()
+        eng.status.check()
+    finally:
+        TL.consume = orig
+    assert len(calls) == 1                                          # layer 2 consumed what layer 0 published
+    cand = calls[0]
+    assert cand.shape == (4, 32)
+    sel = eng._bufs(4)["sel"][2][:4]
+    cnt = eng._bufs(4)["selcnt"][2][:4]
+    for r in range(4):
+        c = set(cand[r][cand[r] >= 0].tolist())
+        picked = sel[r][: int(cnt[r])].tolist()
+        assert int(cnt[r]) == min(cfg.index_topk, len(c)) and set(picked) <= c and picked == sorted(picked)
+    # the source layer itself selects densely on both engines
+    assert torch.equal(eng._bufs(4)["sel"][0][:4], dense._bufs(4)["sel"][0][:4])
+    err = _row_err(a.cpu(), b.cpu())
+    assert err.median() < 0.2, err
+
+
+def test_draft_head_with_markov_correction_matches_oracle():
+    """Draft logits = draft head + rank-r bigram term of the token each row was fed."""
+    from titanic_flash_41_b200.config import DraftConfig
+    cfg = small_config(draft=DraftConfig(layers=1, depth=3, markov_rank=256))
+    plain = small_config(draft=DraftConfig(layers=1, depth=3))
+    W = oracle.init_weights(cfg, 0)
+    assert W["mtp.markov_head.head.weight"].shape == (cfg.vocab, 256)
+    rt = {}
+    ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
+    eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
+    base = E.Engine.from_weights(plain, ecfg, {k: v for k, v in W.items() if "markov" not in k})
+    ref = oracle.OracleModel(cfg, rt)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab, (60,), generator=g)
+    s = ref.new_session(256)
+    ref.forward(prompt, s)
+    hid_ref = ref.last_hidden[-1:].clone()
+    for e in (eng, base):
+        e.forward(E.StepPlan.build([(0, 0, prompt.tolist())], logits="last"))
+    hid = eng.last_hidden[-1:].clone()
+    toks = torch.tensor([11, 900, 5, 1300])
+    want = []
+    for t in toks.tolist():                                    # four candidate anchors at position 60
+        lg, _ = ref.draft_forward(torch.tensor([t]), hid_ref, s, 60)
+        want.append(lg[0])
+    want = torch.stack(want)
+    got, got_plain = [], []
+    for t in toks.tolist():
+        for e, out in ((eng, got), (base, got_plain)):
+            b = e._bufs(1)
+            e.upload_plan(E.StepPlan.build([(0, 60, [t])]), b)
+            out.append(e.draft_run(1, b, hid, torch.arange(1, device="cuda"))[0].clone())
+    got, got_plain = torch.stack(got).cpu(), torch.stack(got_plain).cpu()
+    eng.status.check()
+    err = _row_err(got, want)
+    assert err.median() < 0.1, err
+    # the correction is exactly the bigram term
+    bias = (W["mtp.markov_head.embed.weight"][toks].bfloat16().float()
+            @ W["mtp.markov_head.head.weight"].bfloat16().float().t())
+    assert (got - got_plain - bias).abs().max() <= 2e-3 * bias.abs().max() + 1e-3
+    assert bias.abs().max() > 0.5
+
+
 def test_reference_model_widths_run_on_the_engine():
     """The reference model's real widths (hidden 5120, 512-wide latent heads, low-rank query 1280, eight
     output groups of rank 1024, four residual copies, 32 index heads, expert width 2304) with few layers and

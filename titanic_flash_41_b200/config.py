@@ -81,6 +81,7 @@ class DraftConfig(_JsonMixin):
     condition_layers: int = 1          # last N target layers whose output feeds the draft
     temperature: float = 0.7           # proposal temperature when sampling
     confidence_ladder: Tuple[float, ...] = (0.15, 0.25, 0.20, 0.15)
+    markov_rank: int = 0               # rank of the Markov (bigram) correction of the draft logits; 0 = none (reference: 256)
 
 
 @dataclass
@@ -315,7 +316,8 @@ class EngineConfig(_JsonMixin):
     spin_limit: int = 20_000_000       # bounded device waits (reference src/roce.rs:1196-1199)
     use_cuda_graphs: bool = True
     key_sharded_index_min: int = 8192  # decode rows: split index scoring over the ranks from this many keys (0 = never)
-    moe_block_scaled: bool = True      # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
+    two_level_index_min: int = 65536   # decode rows: from this many index keys on, layers after the candidate source score only its published blocks (0 = never)
+    moe_block_scaled: bool = True     # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
     seed: int = 0
 
 

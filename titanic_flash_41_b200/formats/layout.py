@@ -38,7 +38,7 @@ _EXPERT = re.compile(r"\.ffn\.experts\.(\d+)\.")
 
 def classify(name: str, shape: Tuple[int, ...], cfg: ModelConfig, rank: int, world: int,
              moe_parallel: str = "ep") -> Placement:
-    if name in ("embed.weight", "head.weight"):
+    if name in ("embed.weight", "head.weight", "mtp.markov_head.head.weight"):
         return _split(shape[0], rank, world, 0)
     m = re.match(r"(?:layers|mtp)\.(\d+)\.", name)
     layer = int(m.group(1)) if m else None
@@ -92,6 +92,10 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
             out.append((name + ".scale", sdt, (-(-n // blk), -(-k // blk))))
 
     n_draft = cfg.draft.layers if cfg.draft is not None else 0
+    if n_draft and cfg.draft.markov_rank:
+        # Markov correction of the draft logits: embedding replicated, head rows split like the vocabulary head
+        out.append(("mtp.markov_head.embed.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
+        out.append(("mtp.markov_head.head.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
     for l in range(cfg.n_layers + n_draft):
         draft = l >= cfg.n_layers
         p = f"mtp.{l - cfg.n_layers}" if draft else f"layers.{l}"

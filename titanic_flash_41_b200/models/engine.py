@@ -470,6 +470,12 @@ class Engine:
                 roundtrip["mtp.0.main_proj.weight"] = dequant_fp8(mp).cpu()
             extra = dict(main_proj=mp, enorm=W["mtp.0.enorm.weight"].to(device, torch.bfloat16),
                          hnorm=W["mtp.0.hnorm.weight"].to(device, torch.bfloat16))
+            if cfg.draft.markov_rank:
+                # low-rank bigram correction of the draft logits: embed replicated, head rows sharded
+                Vm = cfg.vocab // comm.world
+                extra["markov_embed"] = W["mtp.markov_head.embed.weight"].to(device, torch.bfloat16).contiguous()
+                extra["markov_head"] = W["mtp.markov_head.head.weight"][comm.rank * Vm:(comm.rank + 1) * Vm].to(
+                    device, torch.bfloat16).contiguous()
         if cfg.hc_mult > 1:
             extra = dict(extra, hc_head=tuple(W[k].to(device, torch.float32).contiguous()
                                               for k in ("hc_head_fn", "hc_head_base", "hc_head_scale")))
@@ -815,9 +821,22 @@ class Engine:
             sel.fill_(-1)
             selcnt.zero_()
             return
+        # two-level selection of long decode rows: the candidate source layer scores every key and
+        # publishes its best blocks of 8; the index layers after it score only inside those blocks
+        # (reference: src/candidates.rs:1-20, src/sparse_index.rs)
+        tl_min, pub = self.ecfg.two_level_index_min, self.candidate_source
+        two_level = (tl_min > 0 and pub >= 0 and T <= self.SMALL_M and nmax >= tl_min
+                     and 0 < cfg.candidate_blocks * 8 < nmax)
+        if two_level and li > pub and b.get("cand") is not None:
+            from ..ops import two_level as TL
+            ids, cnt = TL.consume(b["iq"], b["iw"], region, b["cand"], self.keys[sslot], self.keys[sslot].stride(0),
+                                  self.key_row, T, cfg.index_heads, cfg.index_dim, cfg.index_topk)
+            sel[:T].copy_(ids)
+            selcnt[:T].copy_(cnt)
+            return
         scores = self.scores_buffer(T, nmax)
         ks_min = self.ecfg.key_sharded_index_min
-        if self.world > 1 and ks_min > 0 and T <= self.SMALL_M and nmax >= ks_min:
+        if self.world > 1 and ks_min > 0 and T <= self.SMALL_M and nmax >= ks_min and not (two_level and li == pub):
             # every rank holds all index keys: split the scoring work by key range, gather the local
             # top-k (score, id) pairs and select the global top-k from them (identical result)
             from ..parallel import key_sharded as KS
@@ -832,6 +851,22 @@ class Engine:
                     rows_per_group, scores, scores.stride(0), 0, nmax)
         native.call("tf_topk_select", scores, scores.stride(0), nvalid, cfg.index_topk, sel, selcnt,
                     None, 0, T)
+        if two_level and li == pub:
+            from ..ops import two_level as TL
+            b["cand"] = TL.publish(scores[:T, :nmax], nvalid, cfg.candidate_blocks, T)
+
+    @property
+    def candidate_source(self) -> int:
+        """The index source layer that publishes candidate blocks: the last one before the late
+        group (the reference's layer 20), the first index source when there is no late group, -1
+        when the model keeps no candidates."""
+        cfg = self.cfg
+        if cfg.candidate_blocks <= 0 or not cfg.index_source_layers:
+            return -1
+        if cfg.late_start <= 0:
+            return cfg.index_source_layers[0]
+        early = [l for l in cfg.index_source_layers if l < cfg.late_start]
+        return early[-1] if early else -1
 
     def _moe(self, L: LayerWeights, T: int, b: dict) -> None:
         cfg = self.cfg
@@ -1003,6 +1038,7 @@ class Engine:
         layer_hi = len(self.layers) if layer_hi is None else layer_hi
         if self.engram and b.get("eg_hash"):
             self._engram_hash(T, b)
+        b["cand"] = None               # candidate blocks are published and consumed within one launch
         if x_in is None:
             e = b["e"] if cfg.hc_mult > 1 else b["x"]
             native.call("tf_embed", b["meta"][0], self.embed_w, e, T, cfg.hidden, cfg.vocab, self.status.t)
@@ -1099,4 +1135,26 @@ class Engine:
             b["pending"] = True
         for j, L in enumerate(self.draft_layers):
             self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False)
-        return self._head(T, b, logit_rows, draft=True)
+        logits = self._head(T, b, logit_rows, draft=True)
+        if logits is not None and "markov_head" in ex:
+            logits = logits + self._markov_bias(T, b)[logit_rows]
+        return logits
+
+    def _markov_bias(self, T: int, b: dict) -> torch.Tensor:
+        """Markov correction of the draft logits: bias[r, :] = head_m @ embed_m[token of row r], the
+        token being the one the row was fed (the anchor or the previous proposal), fp32 (reference:
+        src/dspark_markov.rs:886-971; kernels/core.cu:1110 ca_dspark_markov_embed, :1118
+        ca_dspark_markov_local; rank-256 bf16 operands)."""
+        cfg, ex = self.cfg, self.draft_extra
+        r = cfg.draft.markov_rank
+        hm = ex["markov_head"]
+        if "mk_lat" not in b:
+            b["mk_lat"] = torch.zeros(T, r, dtype=torch.bfloat16, device=self.dev)
+            b["mk_bias"] = torch.zeros(T, hm.shape[0], dtype=torch.float32, device=self.dev)
+        native.call("tf_embed", b["meta"][0], ex["markov_embed"], b["mk_lat"], T, r, cfg.vocab, self.status.t)
+        Vl = hm.shape[0]
+        for r0 in range(0, T, self.SMALL_M):
+            m = min(self.SMALL_M, T - r0)
+            native.call("tf_smallm_gemm", 2, hm, None, None, None, 0, 0, r * 2, 0, b["mk_lat"][r0:], r,
+                        b["mk_bias"][r0:], Vl, 0, Vl, r, m, None, None, None, None, None, 1, 0, m, 0.0)
+        return self.comm.all_gather(b["mk_bias"], dim=1) if self.world > 1 else b["mk_bias"]

@@ -210,6 +210,11 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32) -> Dict[s
             mat(f"{p}.main_proj.weight", d, d * (1 + cfg.draft.condition_layers))
             W[f"{p}.enorm.weight"] = torch.ones(d, dtype=dtype)
             W[f"{p}.hnorm.weight"] = torch.ones(d * cfg.draft.condition_layers, dtype=dtype)
+            if cfg.draft.markov_rank:
+                # Markov correction head (reference names: mtp.2.markov_head.{embed,head}.weight)
+                mat("mtp.markov_head.embed.weight", cfg.vocab, cfg.draft.markov_rank, std=1.0)
+                mat("mtp.markov_head.head.weight", cfg.vocab, cfg.draft.markov_rank,
+                    std=1.0 / math.sqrt(cfg.draft.markov_rank))
     if cfg.engram is not None and cfg.engram.layers:
         # hashed n-gram memory: one table per Engram layer (values exactly representable in the packed
         # MXFP8 row format), the projection of the looked-up rows to (copies + 1) x hidden, gate weights
@@ -243,7 +248,7 @@ def shard_weights(W: Dict[str, torch.Tensor], cfg: ModelConfig, rank: int, world
         return t.narrow(axis, rank * (n // world), n // world).contiguous()
 
     for name, t in W.items():
-        if name in ("embed.weight", "head.weight"):
+        if name in ("embed.weight", "head.weight", "mtp.markov_head.head.weight"):
             out[name] = sl(t, 0)
         elif name.endswith((".attn.wq.weight", ".attn.wq_b.weight", ".attn.attn_sink")):
             out[name] = sl(t, 0)
@@ -598,7 +603,14 @@ class OracleModel:
             x = x[:, None, :].expand(T, cfg.hc_mult, cfg.hidden).contiguous()
         for j in range(cfg.draft.layers):
             x = self._layer(f"mtp.{j}", cfg.n_layers + j, x, pos, s, draft=True)
-        return self.head(x), x
+        logits = self.head(x)
+        if cfg.draft.markov_rank:
+            # Markov correction: a rank-r bigram term from the token each row was fed
+            # (reference: src/dspark_markov.rs:886-971, kernels/core.cu:1110-1122)
+            lat = W["mtp.markov_head.embed.weight"][tokens.long()].to(self.dtype)
+            bias = (lat @ W["mtp.markov_head.head.weight"].t()).to(torch.float32)
+            logits = logits + self.comm.all_gather(bias, dim=1)
+        return logits, x
 
 
 def greedy_generate(model: OracleModel, prompts: Sequence[torch.Tensor], steps: int
