@@ -410,6 +410,51 @@ def test_route_group_many_experts_is_sorted_and_stable():
     assert gs[: len(experts)].tolist() == starts
 
 
+@pytest.mark.parametrize("d", [512, 4096])
+def test_fused_boundary_equals_combine_then_norm_then_quantiser(d):
+    """tf_add_norm_fused against tf_moe_combine + tf_add_norm + tf_quant_rows_mx8: the residual is
+    bit-identical; the mean square is summed in another order, so a normalised value may land on the
+    neighbouring bf16 value."""
+    torch.manual_seed(12)
+    T, k, El, e_lo = 9, 3, 6, 2
+    x0 = torch.randn(T, d, device=DEV).bfloat16()
+    y_pair = torch.randn(T * k, d, device=DEV)
+    ids = torch.randint(0, 10, (T, k), device=DEV, dtype=torch.int32)
+    wts = torch.rand(T, k, device=DEV)
+    shared = torch.randn(T, d, device=DEV)
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    # separate kernels
+    xa, delta = x0.clone(), torch.zeros(T, d, device=DEV)
+    h16a, hba = torch.zeros(T, d, device=DEV, dtype=torch.float16), torch.zeros(T, d, device=DEV, dtype=torch.bfloat16)
+    qa, sa = torch.zeros(T, d, dtype=torch.uint8, device=DEV), torch.zeros(T, d // 32, dtype=torch.uint8, device=DEV)
+    native.call("tf_moe_combine", y_pair, ids, wts, shared, delta, T, d, k, e_lo, e_lo + El)
+    native.call("tf_add_norm", xa, delta, 0, d, w, h16a, hba, None, None, T, d, 1e-6)
+    native.call("tf_quant_rows_mx8", h16a, d, qa, sa, T, d)
+    # one kernel
+    xb = x0.clone()
+    h16b, hbb, qb, sb = torch.zeros_like(h16a), torch.zeros_like(hba), torch.zeros_like(qa), torch.zeros_like(sa)
+    native.call("tf_add_norm_fused", xb, None, y_pair, ids, wts, shared, k, e_lo, e_lo + El, w, h16b, hbb, qb, sb, T, d, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(xa, xb)
+    for a, b_ in ((h16a, h16b), (hba, hbb)):
+        assert (a.float() - b_.float()).abs().max() <= 0.01 * a.float().abs().max()
+        assert (a == b_).float().mean() > 0.98
+    deq = lambda q, s_: (q.view(torch.float8_e4m3fn).float().view(T, d // 32, 32) * torch.exp2(s_.float() - 127)[..., None])
+    assert (deq(qa, sa) - deq(qb, sb)).abs().max() <= 0.07 * h16a.float().abs().max()
+    assert (sa == sb).float().mean() > 0.98
+    again = [torch.zeros_like(t) for t in (h16b, qb, sb)]
+    xb2 = x0.clone()
+    native.call("tf_add_norm_fused", xb2, None, y_pair, ids, wts, shared, k, e_lo, e_lo + El, w, again[0], None, again[1],
+                again[2], T, d, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(again[0], h16b) and torch.equal(again[1], qb) and torch.equal(again[2], sb)   # run to run
+    # plain delta source, no quantised copy
+    xc, h16c = x0.clone(), torch.zeros_like(h16a)
+    native.call("tf_add_norm_fused", xc, delta, None, None, None, None, 0, 0, 0, w, h16c, None, None, None, T, d, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(xc, xa) and (h16c == h16a).float().mean() > 0.98
+
+
 def test_mx8_row_quantiser_matches_codec():
     """e4m3 values with one UE8M0 scale per 32 inputs: same bytes as the host codec."""
     torch.manual_seed(5)

@@ -802,6 +802,19 @@ class Engine:
             native.call("tf_hc_prepare", b["x"], fn, base, scale, b["coef"], b["v"], norm_w, b["h16"],
                         b["hb"] if want_hb else None, T, cfg.hc_mult, d, cfg.sinkhorn_iters, cfg.hc_eps, cfg.rms_eps)
             return
+        pc = b.pop("pending_combine", None)
+        use_mx = br == "ffn" and "x8" in b
+        b["x8_ready"] = use_mx
+        if pc is not None or use_mx or T <= self.SMALL_M:
+            # one launch: (deferred expert combine +) residual add + RMSNorm (+ the MXFP8 rows the
+            # block-scaled expert GEMV reads); same arithmetic as the separate kernels
+            shared, e_lo = (pc if pc is not None else (None, 0))
+            native.call("tf_add_norm_fused", b["x"], b["delta"] if (pc is None and b.get("pending")) else None,
+                        b["y_pair"] if pc is not None else None, b["ids"] if pc is not None else None,
+                        b["wts"] if pc is not None else None, shared, cfg.topk, e_lo, e_lo + self.El, norm_w,
+                        b["h16"], b["hb"] if want_hb else None, b["x8"] if use_mx else None,
+                        b["x8s"] if use_mx else None, T, d, cfg.rms_eps)
+            return
         native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, norm_w, b["h16"],
                     b["hb"] if want_hb else None, None, None, T, d, cfg.rms_eps)
 
@@ -908,7 +921,8 @@ class Engine:
             if "x8" in b:
                 # MXFP4 weights x MXFP8 activations on block-scaled tcgen05 MMAs: the tensor core
                 # consumes nibbles and scales, the first launch hands the second its MXFP8 input
-                native.call("tf_quant_rows_mx8", b["h16"], d, b["x8"], b["x8s"], T, d)
+                if not b.get("x8_ready"):
+                    native.call("tf_quant_rows_mx8", b["h16"], d, b["x8"], b["x8s"], T, d)
                 native.call("tf_moe_gemv_mx", L.ew1, L.ew3, L.es1, L.es3, self.El, b["x8"], b["x8s"], T, None, I,
                             b["a8"], b["a8s"], I, d, cfg.topk, b["g_expert"], b["g_start"], b["g_count"],
                             b["n_groups"], b["sorted_pairs"], slots, cfg.swiglu_limit, 0, 0, self.status.t)
@@ -965,6 +979,10 @@ class Engine:
                                         e_lo + self.El, None if hc else b["x"], b["delta"] if hc else None,
                                         self.status.t)
             b["pending"] = False
+            return
+        if b.get("defer_combine"):
+            # the next layer's boundary sums the expert outputs itself (tf_add_norm_fused)
+            b["pending_combine"] = (shared, e_lo)
             return
         native.call("tf_moe_combine", b["y_pair"], b["ids"], b["wts"], shared, b["delta"], T, d,
                     cfg.topk, e_lo, e_lo + self.El)
@@ -1050,8 +1068,15 @@ class Engine:
                 b["x"].view(T, cfg.hc_mult, cfg.hidden).copy_(e[:T, None, :].expand(T, cfg.hc_mult, cfg.hidden))
         else:
             b["x"][:T].copy_(x_in)
+        b.pop("pending_combine", None)
+        eg_layers = cfg.engram.layers if self.engram else ()
         for li in range(layer_lo, layer_hi):
+            # decode rows on one GPU: leave the expert combine of this layer to the boundary kernel
+            # of the next one (not before an Engram layer, which reads the folded residual first)
+            b["defer_combine"] = (T <= self.SMALL_M and self.world == 1 and cfg.hc_mult == 1
+                                  and li + 1 < layer_hi and (li + 1) not in eg_layers)
             self._layer(li, self.layers[li], T, b, nmax, rpg, first=(li == layer_lo))
+        b["defer_combine"] = False
         if layer_hi < len(self.layers):
             return None
         return self._head(T, b, logit_rows)
@@ -1133,6 +1158,8 @@ class Engine:
         else:
             b["x"].zero_()
             b["pending"] = True
+        b["defer_combine"] = False
+        b.pop("pending_combine", None)
         for j, L in enumerate(self.draft_layers):
             self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False)
         logits = self._head(T, b, logit_rows, draft=True)
