@@ -455,6 +455,30 @@ def test_fused_boundary_equals_combine_then_norm_then_quantiser(d):
     assert torch.equal(xc, xa) and (h16c == h16a).float().mean() > 0.98
 
 
+@pytest.mark.parametrize("M", [3, 16, 27])
+def test_router_topk_group_equals_the_two_launches(M):
+    torch.manual_seed(M)
+    E_, k, e_lo, El = 64, 6, 16, 32
+    logits = torch.randn(M, E_, device=DEV)
+    bias = torch.randn(E_, device=DEV) * 0.1
+    i32 = lambda *s_: torch.zeros(*s_, dtype=torch.int32, device=DEV)
+    out = []
+    for fused in (False, True):
+        ids, wts = i32(M, k), torch.zeros(M, k, device=DEV)
+        ge, gs, gc, ng, sp, nl = i32(El), i32(El), i32(El), i32(1), i32(M * k), i32(1)
+        if fused:
+            native.call("tf_router_topk_group", logits, bias, ids, wts, M, E_, k, 1, 1, 1.5, e_lo, e_lo + El,
+                        ge, gs, gc, ng, sp, nl)
+        else:
+            native.call("tf_router_topk", logits, bias, ids, wts, M, E_, k, 1, 1, 1.5)
+            native.call("tf_route_group", ids, M * k, e_lo, e_lo + El, ge, gs, gc, ng, sp, nl)
+        torch.cuda.synchronize()
+        n, g = int(nl), int(ng)
+        out.append((ids, wts, ge[:g].clone(), gs[:g].clone(), gc[:g].clone(), sp[:n].clone(), n, g))
+    for a, b_ in zip(*out):
+        assert torch.equal(a, b_) if isinstance(a, torch.Tensor) else a == b_
+
+
 def test_mx8_row_quantiser_matches_codec():
     """e4m3 values with one UE8M0 scale per 32 inputs: same bytes as the host codec."""
     torch.manual_seed(5)

@@ -364,12 +364,12 @@ __global__ void router_logits_kernel(const __half* __restrict__ h, const __nv_bf
 
 // top-k per row (one warp per row) + weights.  scoring 0 = softmax, 1 = sqrtsoftplus.
 // Ties go to the lowest expert id; NaN keys count as +inf.
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                   int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
-                                   int scoring, int renorm, float scale) {
-  extern __shared__ float sc[];                       // [warps][2][E]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int r = blockIdx.x * nw + warp;
+__device__ __forceinline__ void router_topk_rows(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                 int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
+                                                 int scoring, int renorm, float scale, float* sc, int row0) {
+  // sc: [warps][2][E] floats of shared memory; warp w serves row row0 + w
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = row0 + warp;
   if (r >= M) return;
   float* score = sc + (long)warp * 2 * E;
   float* key = score + E;
@@ -434,12 +434,19 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
   }
 }
 
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                   int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
+                                   int scoring, int renorm, float scale) {
+  extern __shared__ float sc[];                       // [warps][2][E]
+  router_topk_rows(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, sc, blockIdx.x * (blockDim.x >> 5));
+}
+
 // Group (token, slot) pairs by expert for the experts this rank owns: counting sort in one CTA.
 // Outputs: group_expert/start/count for the compacted active experts, n_groups, sorted_pairs.
-__global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
-                                   int* group_expert, int* group_start, int* group_count, int* n_groups,
-                                   int* sorted_pairs, int* n_local_pairs) {
-  extern __shared__ int cnt[];   // [E_local] counts, then offsets; then the local expert of every pair
+__device__ __forceinline__ void route_group_body(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
+                                                 int* group_expert, int* group_start, int* group_count,
+                                                 int* n_groups, int* sorted_pairs, int* n_local_pairs, int* cnt) {
+  // cnt: [E_local] counts, then offsets; then the local expert of every pair (shared memory)
   const int El = e_hi - e_lo;
   int* loc = cnt + El;
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
@@ -491,6 +498,28 @@ __global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int
     for (int i = 0; i < n_pairs; ++i)
       if (loc[i] == e) sorted_pairs[off++] = i;
   }
+}
+
+__global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
+                                   int* group_expert, int* group_start, int* group_count, int* n_groups,
+                                   int* sorted_pairs, int* n_local_pairs) {
+  extern __shared__ int cnt_smem[];
+  route_group_body(ids, n_pairs, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
+                   n_local_pairs, cnt_smem);
+}
+
+// Decode rows: top-k of every row (one warp each, 16 rows per pass) and the grouping of the
+// resulting pairs in ONE single-CTA launch.
+__global__ void __launch_bounds__(512) router_topk_group_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ wts,
+    int M, int E, int topk, int scoring, int renorm, float scale, int e_lo, int e_hi, int* group_expert,
+    int* group_start, int* group_count, int* n_groups, int* sorted_pairs, int* n_local_pairs) {
+  extern __shared__ float fsm[];                       // [16][2][E] floats, reused as ints by the grouping
+  for (int row0 = 0; row0 < M; row0 += 16)
+    router_topk_rows(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, fsm, row0);
+  __syncthreads();                                     // ids of every row are written (same CTA)
+  route_group_body(ids, M * topk, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
+                   n_local_pairs, reinterpret_cast<int*>(fsm));
 }
 
 // out[r,:] = sum_j wts[r,j] * y_pair[r*topk+j,:] (experts of this rank only, fixed order) + shared[r,:]
@@ -576,6 +605,19 @@ TF_API int tf_router_topk(const float* logits, const float* bias, int* ids, floa
   const int nw = 4;
   router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
       logits, bias, ids, wts, M, E, topk, scoring, renorm, scale);
+  return (int)cudaGetLastError();
+}
+
+// tf_router_topk followed by tf_route_group for up to 32 rows, one launch
+TF_API int tf_router_topk_group(const float* logits, const float* bias, int* ids, float* wts, int M, int E, int topk,
+                                int scoring, int renorm, float scale, int e_lo, int e_hi, int* group_expert,
+                                int* group_start, int* group_count, int* n_groups, int* sorted_pairs,
+                                int* n_local_pairs, cudaStream_t st) {
+  const size_t smem = max((size_t)16 * 2 * E * sizeof(float), (size_t)(e_hi - e_lo + M * topk) * sizeof(int));
+  if (M <= 0 || M > 32 || e_hi <= e_lo || smem > 48 * 1024) return -1;
+  router_topk_group_kernel<<<1, 512, smem, st>>>(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, e_lo, e_hi,
+                                                 group_expert, group_start, group_count, n_groups, sorted_pairs,
+                                                 n_local_pairs);
   return (int)cudaGetLastError();
 }
 

@@ -886,6 +886,7 @@ class Engine:
         d, I = cfg.hidden, cfg.moe_inter
         scoring = 1 if cfg.scoring == "sqrtsoftplus" else 0
         side = None
+        grouped = False            # True once the router launch has also grouped the pairs by expert
         if cfg.n_shared and T <= self.SMALL_M:
             # the shared expert depends only on the normalised input: run its two small GEMVs as a
             # parallel branch (second stream; a parallel branch of the step's CUDA graph) next to the
@@ -907,16 +908,20 @@ class Engine:
             # one warp per expert row over the bf16 gate matrix, then top-k
             native.call("tf_router_logits_small", b["hb"], d, L.gate, b["logits_r"], cfg.n_experts, T,
                         cfg.n_experts, d)
-            native.call("tf_router_topk", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
-                        cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
+            e0 = self.rank * self.El
+            native.call("tf_router_topk_group", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
+                        cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale, e0, e0 + self.El,
+                        b["g_expert"], b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
+            grouped = True
         else:
             native.call("tf_router", b["h16"], L.gate, L.gate_bias, b["logits_r"], b["ids"], b["wts"], T,
                         cfg.n_experts, d, cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
         e_lo = self.rank * self.El
         npairs = T * cfg.topk
         if T <= self.SMALL_M:
-            native.call("tf_route_group", b["ids"], npairs, e_lo, e_lo + self.El, b["g_expert"],
-                        b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
+            if not grouped:
+                native.call("tf_route_group", b["ids"], npairs, e_lo, e_lo + self.El, b["g_expert"],
+                            b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
             slots = min(self.El, npairs)
             if "x8" in b:
                 # MXFP4 weights x MXFP8 activations on block-scaled tcgen05 MMAs: the tensor core
