@@ -115,6 +115,8 @@ def main():
     ap.add_argument("--model", default="flash-b200")
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (result is then not a headline number)")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--knockout", default="", help="diagnostic: comma-separated exported kernel names whose launches are "
+                    "left out of the captured decode graph (the printed number is then NOT a benchmark value)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--trace", action="store_true", help="print per-kernel time tables of one extra prefill pass and one eager decode step")
@@ -197,6 +199,12 @@ def main():
     start_len = CONTEXT - DECODE_TOKENS
     slots = [DecodeSlot(region=r, length=start_len, anchor=100 + r, seed=r + 1) for r in range(SESSIONS)]
     dec = SpecDecoder(eng, SESSIONS, temperature=0.6, top_p=0.95, use_graph=not args.no_graph)
+    if args.knockout:
+        # capture the graph without the named families: the difference to a plain run is what they
+        # cost inside the graph, dependent-launch gaps included
+        from titanic_flash_41_b200.utils.trace import Knockout
+        with Knockout(set(args.knockout.split(","))):
+            dec.step(slots)
     launches = dec.count_launches(slots)
     if args.trace:
         # one eager decode step under the kernel clock: where the step time goes
@@ -266,6 +274,8 @@ def main():
             "gpu_launches_per_step": launches,
             "clocks": clocks, "init_s": round(init_s, 1), "peak_mem_gb": round(mem_gb, 1), "impl": "own",
         }
+        if args.knockout:
+            out["diagnostic"] = "decode graph captured WITHOUT " + args.knockout + ": not a benchmark value"
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
