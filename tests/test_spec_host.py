@@ -65,3 +65,19 @@ def test_pause_and_resume_is_token_exact():
         return [t for k, p in ev if k == "tokens" for t in p]
     plain, paused = run(False), run(True)
     assert plain == paused and len(plain) >= 1
+
+
+def test_step_meta_equals_step_plans():
+    """The array-built metadata of a verification round equals the StepPlan-built one."""
+    import numpy as np
+    from titanic_flash_41_b200.models.engine import StepPlan
+    from titanic_flash_41_b200.spec.decoder import step_meta
+    regions, lengths, anchors = [2, 0, 3], [130001, 7, 4095], [11, 12, 13]
+    for g in (0, 3):
+        mv, mds = step_meta(regions, lengths, anchors, g, 4)
+        want = StepPlan.build([(r, n, [a] + [0] * g) for r, n, a in zip(regions, lengths, anchors)]).meta_host(4)
+        assert mv.dtype == np.int32 and np.array_equal(mv, want)
+        assert len(mds) == g
+        for j in range(g):
+            wd = StepPlan.build([(r, n + j, [a if j == 0 else 0]) for r, n, a in zip(regions, lengths, anchors)]).meta_host(4)
+            assert np.array_equal(mds[j], wd)

@@ -189,9 +189,12 @@ __global__ void attn_prep_kernel(PrepParams p) {
   if (tid < half_rd) rope_sincos(pos, p.freqs[tid], &s_sin[tid], &s_cos[tid]);
   __syncthreads();
 
-  // ---- q: RoPE on the tail of every head
-  if (p.off_q >= 0) {
-    for (int i = tid; i < p.Hl * p.Dh; i += blockDim.x) {
+  // ---- q: RoPE on the tail of every head.  With few rows the launch has gridDim.y > 1: the CTAs
+  // with blockIdx.y > 0 share the query elements of the row, the CTA with blockIdx.y == 0 does the rest.
+  const int qparts = gridDim.y > 1 ? gridDim.y - 1 : 1;
+  const int qpart = gridDim.y > 1 ? (int)blockIdx.y - 1 : 0;
+  if (p.off_q >= 0 && qpart >= 0) {
+    for (int i = qpart * blockDim.x + tid; i < p.Hl * p.Dh; i += qparts * blockDim.x) {
       const int dd = i % p.Dh;
       float v = ldp(p, r, p.off_q + i);
       if (dd >= tail0) {
@@ -203,6 +206,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
       p.q_out[(long)r * p.Hl * p.Dh + i] = __float2bfloat16(v);
     }
   }
+  if (gridDim.y > 1 && blockIdx.y > 0) return;      // query-only CTA
   // ---- kv latent: norm -> bf16 -> RoPE -> bf16 -> V41 row
   if (p.off_kv >= 0) {
     float ss = 0.f;
@@ -582,7 +586,8 @@ TF_API int tf_attn_prep(const void* P, int p_kind, int ldp, int T, const int* po
   p.keys = (uint8_t*)keys; p.maxC = maxC; p.iq_out = (__nv_bfloat16*)iq_out; p.iw_out = iw_out;
   p.st = (TfStatusWord*)status;
   const int smf = (off_cv >= 0 ? Dh + Di : Dh);
-  attn_prep_kernel<<<T, 256, smf * sizeof(float), st>>>(p);
+  // few rows (decode): eight more CTAs per row share the query heads
+  attn_prep_kernel<<<dim3(T, (T <= 64 && off_q >= 0) ? 9 : 1), 256, smf * sizeof(float), st>>>(p);
   if (off_cv >= 0) carry_save_kernel<<<T, 128, 0, st>>>(p);
   return (int)cudaGetLastError();
 }

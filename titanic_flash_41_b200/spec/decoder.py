@@ -38,6 +38,31 @@ class DecodeSlot:
     recent: List[int] = field(default_factory=list)
 
 
+def step_meta(regions: Sequence[int], lengths: Sequence[int], anchors: Sequence[int], g: int, ratio: int):
+    """Metadata blocks of one verification round, built with array arithmetic (this runs on the
+    host every step): the verify block ``StepPlan.build([(region, length, [anchor] + [0] * g)
+    ...]).meta_host(ratio)`` and, for proposal j, the block of one row per conversation at
+    position length + j (token: the anchor for j = 0, else filled in on the device)."""
+    S, R = len(regions), g + 1
+    reg = np.asarray(regions, dtype=np.int32)
+    ln = np.asarray(lengths, dtype=np.int32)
+    an = np.asarray(anchors, dtype=np.int32)
+    j = np.arange(R, dtype=np.int32)
+    pos = (ln[:, None] + j[None, :]).reshape(-1)
+    tok = np.zeros((S, R), dtype=np.int32)
+    tok[:, 0] = an
+    zeros = np.zeros(S * R, dtype=np.int32)
+    mv = np.stack([tok.reshape(-1), pos, np.repeat(reg, R), np.repeat(np.arange(S, dtype=np.int32) * R, R),
+                   np.repeat(ln + R - 1, R), (pos + 1) // ratio, zeros]).astype(np.int32)
+    mds = []
+    z = np.zeros(S, dtype=np.int32)
+    rows = np.arange(S, dtype=np.int32)
+    for jj in range(g):
+        p = ln + jj
+        mds.append(np.stack([an if jj == 0 else z, p, reg, rows, p, (p + 1) // ratio, z]).astype(np.int32))
+    return mv, mds
+
+
 class SpecDecoder:
     def __init__(self, engine: Engine, n_slots: int, depth: Optional[int] = None,
                  temperature: float = 0.6, top_p: float = 0.95, use_graph: bool = True):
@@ -99,17 +124,13 @@ class SpecDecoder:
     def _fill_host(self, slots: Sequence[DecodeSlot]) -> int:
         S, g, R = self.S, self.g, self.R
         cfg = self.e.cfg
-        blocks = [(s.region, s.length, [s.anchor] + [0] * g) for s in slots]
-        plan = StepPlan.build(blocks)
         ratio = cfg.compress_ratio
-        mv = plan.meta_host(ratio)
         hi = self.h_int.numpy()
+        mv, mds = step_meta([s.region for s in slots], [s.length for s in slots], [s.anchor for s in slots], g, ratio)
         hi[: self.n_meta_v] = mv.reshape(-1)
         for j in range(g):
-            pd = StepPlan.build([(s.region, s.length + j, [s.anchor if j == 0 else 0]) for s in slots])
-            md = pd.meta_host(ratio)
             o = self.n_meta_v + j * self.n_meta_d
-            hi[o: o + self.n_meta_d] = md.reshape(-1)
+            hi[o: o + self.n_meta_d] = mds[j].reshape(-1)
         if self.n_eg:
             o = self.n_meta_v + g * self.n_meta_d
             hi[o: o + self.n_eg] = StepPlan.recent_rows(cfg, [(R, s.recent) for s in slots]).reshape(-1)
