@@ -26,6 +26,7 @@
 namespace {
 
 constexpr int kWarps = 4;   // K is split four ways inside a CTA; four CTAs fit on an SM
+constexpr int kMaxWarps = 8;   // dense matrices with few 32-feature tiles split K eight ways instead (more warps per SM)
 constexpr int kTileN = 32;   // output columns per CTA (two m16 tiles per warp)
 
 struct SmallMParams {
@@ -380,11 +381,11 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
       for (int i = 0; i < 4; ++i) red[(warp * NT + ti) * MT + m][lane][i] = acc[ti][m][i];
   __syncthreads();
   constexpr int kSlots = 2 * MT * 32 * 4;
-  for (int s = threadIdx.x; s < kSlots; s += kWarps * 32) {
+  const int nwarps = blockDim.x >> 5;
+  for (int s = threadIdx.x; s < kSlots; s += blockDim.x) {
     const int i = s & 3, ln = (s >> 2) & 31, m = (s >> 7) % MT, h = (s >> 7) / MT;
     float v = 0.f, v3 = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
+    for (int w = 0; w < nwarps; ++w) {
       v += red[(w * NT + h) * MT + m][ln][i];
       if (DUAL) v3 += red[(w * NT + 2 + h) * MT + m][ln][i];
     }
@@ -420,8 +421,9 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 }
 
 template <int KIND, bool DUAL>
-__global__ void __launch_bounds__(kWarps * 32, (KIND == 3 ? (DUAL ? 4 : 5) : 1)) smallm_gemm_kernel(SmallMParams p) {
-  __shared__ float red[kWarps * (DUAL ? 4 : 2) * 2][32][4];
+__global__ void __launch_bounds__((KIND == 3 ? kWarps : kMaxWarps) * 32, (KIND == 3 ? (DUAL ? 4 : 5) : 1))
+smallm_gemm_kernel(SmallMParams p) {
+  __shared__ float red[(KIND == 3 ? kWarps : kMaxWarps) * (DUAL ? 4 : 2) * 2][32][4];
   __shared__ __align__(16) float ctile[(KIND == 0 && !DUAL) ? 32 * 32 : 4];
   float* tile_out = (KIND == 0 && !DUAL && p.use_comm) ? ctile : nullptr;
   int rows;
@@ -510,9 +512,9 @@ __global__ void __launch_bounds__(256) quant_rows_e4m3_perm_kernel(const __half*
 }
 
 template <int KIND, bool DUAL>
-cudaError_t launch(const SmallMParams& p, int slots, cudaStream_t st) {
+cudaError_t launch(const SmallMParams& p, int slots, cudaStream_t st, int warps = kWarps) {
   dim3 grid((p.N + kTileN - 1) / kTileN, slots > 0 ? slots : 1);
-  smallm_gemm_kernel<KIND, DUAL><<<grid, kWarps * 32, 0, st>>>(p);
+  smallm_gemm_kernel<KIND, DUAL><<<grid, warps * 32, 0, st>>>(p);
   return cudaGetLastError();
 }
 
@@ -543,7 +545,13 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   p.kstep = 64; p.s_kstep = 4;
   const bool dual = W3 != nullptr;
   cudaError_t e;
-  if (kind == 0) e = dual ? launch<0, true>(p, slots, stream) : launch<0, false>(p, slots, stream);
+  // dense FP8 with so few tiles that an SM gets two CTAs or fewer: eight K-splitting warps per CTA
+  int warps = kWarps;
+  if (kind == 0 && !dual && !group_expert && N / kTileN <= 320 && K >= 8 * 256) {
+    warps = kMaxWarps;
+    p.k_per_warp = ((K + warps - 1) / warps + 127) / 128 * 128;
+  }
+  if (kind == 0) e = dual ? launch<0, true>(p, slots, stream) : launch<0, false>(p, slots, stream, warps);
   else if (kind == 1) e = dual ? launch<1, true>(p, slots, stream) : launch<1, false>(p, slots, stream);
   else if (kind == 2) e = launch<2, false>(p, slots, stream);
   else return -1;
