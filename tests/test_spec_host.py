@@ -81,3 +81,33 @@ def test_step_meta_equals_step_plans():
         for j in range(g):
             wd = StepPlan.build([(r, n + j, [a if j == 0 else 0]) for r, n, a in zip(regions, lengths, anchors)]).meta_host(4)
             assert np.array_equal(mds[j], wd)
+
+
+def test_recent_rows_and_prefill_seams_for_engram_models():
+    """Tokens before each block, newest first and padded; a prefill chunk takes them from the
+    prompt's own earlier rows and, at the seam, from the tokens before the prefilled part."""
+    import numpy as np
+    from titanic_flash_41_b200.config import EngramConfig, tiny_config
+    from titanic_flash_41_b200.models import engram as EG
+    from titanic_flash_41_b200.models.engine import StepPlan
+    from titanic_flash_41_b200.serve.prefill import _recent
+    cfg = tiny_config(engram=EngramConfig(layers=(0,), rows_per_table=1500))
+    md = EG.metadata_for(cfg)
+    n = md.ngram - 1
+    rows = StepPlan.recent_rows(cfg, [(2, [7, 8, 9, 10, 11]), (1, [5])])
+    assert rows.shape == (3, n) and rows.dtype == np.int32
+    assert rows[0].tolist() == [11, 10, 9][:n] and rows[1].tolist() == rows[0].tolist()
+    assert rows[2].tolist() == ([5] + [md.pad_token] * n)[:n]
+    toks = np.arange(100, 120, dtype=np.int32)
+    plan = _recent(StepPlan.build([(0, 50, toks[:8].tolist())]), cfg, [1, 2, 3, 4], toks, 0)
+    assert plan.engram_recent[0].tolist() == [4, 3, 2][:n]                       # seam: tokens before the part
+    plan = _recent(StepPlan.build([(0, 58, toks[8:16].tolist())]), cfg, [1, 2, 3, 4], toks, 8)
+    assert plan.engram_recent[0].tolist() == [107, 106, 105][:n]                 # inside the part
+    plan = _recent(StepPlan.build([(0, 51, toks[1:9].tolist())]), cfg, [1, 2, 3, 4], toks, 1)
+    assert plan.engram_recent[0].tolist() == [100, 4, 3][:n]                     # straddling the seam
+    # the host hashes of a block agree with hashing the same rows through recent_rows' convention
+    ids = EG.hash_positions(md, [4, 3, 2][::-1], toks[:4].tolist(), 50)
+    assert ids.shape == (4, md.tables, md.ids_per_table)
+    # models without Engram layers: the plan is left alone
+    plain = tiny_config()
+    assert _recent(StepPlan.build([(0, 0, [1, 2])]), plain, [], toks, 0).engram_recent is None
