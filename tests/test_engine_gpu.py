@@ -440,6 +440,54 @@ def test_draft_head_with_markov_correction_matches_oracle():
     assert bias.abs().max() > 0.5
 
 
+def test_draft_subset_head_in_four_bits_matches_oracle_and_proposes_subset_tokens():
+    """The drafter's vocabulary-subset head: MXFP4 rows x MXFP8 activations on the block-scaled GEMV."""
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    cfg = small_config(draft=DraftConfig(layers=1, depth=3, subset_rows=1024))
+    W = oracle.init_weights(cfg, 0)
+    ids = W["mtp.head_subset.ids"]
+    assert ids.shape == (1024,) and bool((ids[1:] > ids[:-1]).all())
+    rt = {}
+    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,)), W, roundtrip=rt)
+    assert "head_mx" in eng.draft_extra and torch.equal(rt["mtp.head_subset.ids"], ids)
+    ref = oracle.OracleModel(cfg, rt)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab, (60,), generator=g)
+    s = ref.new_session(256)
+    ref.forward(prompt, s)
+    hid_ref = ref.last_hidden[-1:].clone()
+    eng.forward(E.StepPlan.build([(0, 0, prompt.tolist())], logits="last"))
+    hid = eng.last_hidden[-1:].clone()
+    inside = torch.zeros(cfg.vocab, dtype=torch.bool)
+    inside[ids] = True
+    errs = []
+    for t in (11, 900, 5, 1300):
+        want, _ = ref.draft_forward(torch.tensor([t]), hid_ref, s, 60)
+        b = eng._bufs(1)
+        eng.upload_plan(E.StepPlan.build([(0, 60, [t])]), b)
+        got = eng.draft_run(1, b, hid, torch.arange(1, device="cuda"))[0].cpu()
+        assert bool(torch.isinf(got[~inside]).all()) and bool(torch.isfinite(got[inside]).all())
+        assert bool(torch.isinf(want[0][~inside]).all())
+        errs.append(float((got[inside] - want[0][inside]).abs().max() / want[0][inside].abs().max()))
+    eng.status.check()
+    assert sorted(errs)[len(errs) // 2] < 0.1, errs
+    # speculative decoding with the subset head: every proposal is a subset token, the committed
+    # tokens do not depend on graph capture
+    runs = {}
+    for use_graph in (True, False):
+        eng.forward(E.StepPlan.build([(0, 0, prompt.tolist())], logits="last"))
+        dec = SpecDecoder(eng, 1, temperature=0.8, top_p=0.95, use_graph=use_graph)
+        slots = [DecodeSlot(region=0, length=60, anchor=7, seed=5)]
+        toks = []
+        for _ in range(5):
+            toks += dec.step(slots)[0]
+            assert bool(inside[dec.h_out[2:, 0].long()].all())
+        runs[use_graph] = toks
+        eng.status.check()
+    assert runs[True] == runs[False]
+
+
 def test_reference_model_widths_run_on_the_engine():
     """The reference model's real widths (hidden 5120, 512-wide latent heads, low-rank query 1280, eight
     output groups of rank 1024, four residual copies, 32 index heads, expert width 2304) with few layers and

@@ -82,6 +82,7 @@ class DraftConfig(_JsonMixin):
     temperature: float = 0.7           # proposal temperature when sampling
     confidence_ladder: Tuple[float, ...] = (0.15, 0.25, 0.20, 0.15)
     markov_rank: int = 0               # rank of the Markov (bigram) correction of the draft logits; 0 = none (reference: 256)
+    subset_rows: int = 0               # 4-bit vocabulary-subset head of the drafter: it proposes only these many tokens (multiple of 128; 0 = whole vocabulary; reference: 61 % of the vocabulary)
 
 
 @dataclass

@@ -92,6 +92,9 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
             out.append((name + ".scale", sdt, (-(-n // blk), -(-k // blk))))
 
     n_draft = cfg.draft.layers if cfg.draft is not None else 0
+    if n_draft and cfg.draft.subset_rows:
+        # token ids of the drafter's 4-bit vocabulary-subset head (the rows themselves are cut from head.weight)
+        out.append(("mtp.head_subset.ids", "I64", (cfg.draft.subset_rows,)))
     if n_draft and cfg.draft.markov_rank:
         # Markov correction of the draft logits: embedding replicated, head rows split like the vocabulary head
         out.append(("mtp.markov_head.embed.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))

@@ -470,6 +470,15 @@ class Engine:
                 roundtrip["mtp.0.main_proj.weight"] = dequant_fp8(mp).cpu()
             extra = dict(main_proj=mp, enorm=W["mtp.0.enorm.weight"].to(device, torch.bfloat16),
                          hnorm=W["mtp.0.hnorm.weight"].to(device, torch.bfloat16))
+            if cfg.draft.subset_rows and comm.world == 1 and cfg.hidden % 512 == 0 and cfg.draft.subset_rows % 128 == 0:
+                # 4-bit vocabulary-subset head of the drafter: MXFP4 copy of the subset's head rows,
+                # multiplied on the block-scaled tensor-core GEMV (one "expert" of subset_rows features)
+                ids = W["mtp.head_subset.ids"].to(device, torch.int64)
+                rows = W["head.weight"].to(device, torch.float32)[ids]
+                pk, sc = quant_mxfp4_device(rows.unsqueeze(0))
+                extra["head_mx"] = (pk.contiguous(), sc.contiguous(), ids)
+                if roundtrip is not None:
+                    roundtrip["mtp.head_subset.weight"] = dequant_mxfp4(pk[0], sc[0]).cpu()
             if cfg.draft.markov_rank:
                 # low-rank bigram correction of the draft logits: embed replicated, head rows sharded
                 Vm = cfg.vocab // comm.world
@@ -504,7 +513,7 @@ class Engine:
             roundtrip["head.weight"] = W["head.weight"].to(torch.bfloat16).float()
             for k, v in W.items():
                 if k not in roundtrip:
-                    roundtrip[k] = v.to(torch.bfloat16).float() if v.dim() == 1 else v
+                    roundtrip[k] = v.to(torch.bfloat16).float() if (v.dim() == 1 and v.is_floating_point()) else v
         return cls(cfg, ecfg, layers, embed, head, W["norm.weight"].to(device, torch.bfloat16), comm,
                    device, max_chunk, drafts, extra)
 
@@ -1121,6 +1130,8 @@ class Engine:
                 self.last_hidden = b["x"]
         if rows is None:
             return None
+        if draft and self.draft_extra.get("head_mx") is not None:
+            return self._head_subset(b["h16"][rows].contiguous())
         if draft and self.draft_extra.get("head") is not None:
             hw = self.draft_extra["head"]
             Vl = hw.n
@@ -1138,6 +1149,28 @@ class Engine:
                         hsel[r0:], d, logits[r0:], Vl, 0, Vl, d, m, None, None, None, None, None, 1, 0, m, 0.0)
         if self.world > 1:
             logits = self.comm.all_gather(logits, dim=1)
+        return logits
+
+    def _head_subset(self, h16: torch.Tensor) -> torch.Tensor:
+        """Draft logits from the 4-bit subset head: MXFP8 rows x MXFP4 head rows on the block-scaled
+        GEMV, scattered into a full-vocabulary row of -inf (the drafter proposes subset tokens only;
+        reference: src/nvfp4_head.rs, a 4-bit head over 61 % of the vocabulary)."""
+        pk, sc, ids = self.draft_extra["head_mx"]
+        n, d, Vs = h16.shape[0], self.cfg.hidden, pk.shape[1]
+        assert n <= 16
+        st = self._scratch.get(("head_mx", n))
+        if st is None:
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.dev)
+            st = dict(x8=torch.zeros(n, d, dtype=torch.uint8, device=self.dev),
+                      x8s=torch.zeros(n, d // 32, dtype=torch.uint8, device=self.dev),
+                      ge=i32([0]), gs=i32([0]), gc=i32([n]), ng=i32([1]), sp=torch.arange(n, dtype=torch.int32, device=self.dev))
+            self._scratch[("head_mx", n)] = st
+        native.call("tf_quant_rows_mx8", h16, d, st["x8"], st["x8s"], n, d)
+        y = torch.empty(n, Vs, dtype=torch.float32, device=self.dev)
+        native.call("tf_moe_gemv_mx", pk, None, sc, None, 1, st["x8"], st["x8s"], n, y, Vs, None, None, Vs, d, 1,
+                    st["ge"], st["gs"], st["gc"], st["ng"], st["sp"], 1, 0.0, 0, 0, self.status.t)
+        logits = torch.full((n, self.cfg.vocab), float("-inf"), dtype=torch.float32, device=self.dev)
+        logits.index_copy_(1, ids, y)
         return logits
 
     # -- draft head ---------------------------------------------------------------------------

@@ -210,6 +210,11 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32) -> Dict[s
             mat(f"{p}.main_proj.weight", d, d * (1 + cfg.draft.condition_layers))
             W[f"{p}.enorm.weight"] = torch.ones(d, dtype=dtype)
             W[f"{p}.hnorm.weight"] = torch.ones(d * cfg.draft.condition_layers, dtype=dtype)
+            if cfg.draft.subset_rows:
+                # vocabulary subset of the drafter's 4-bit head: sorted token ids
+                # (reference: src/nvfp4_head.rs over src/latin_subset_v1.bin)
+                W["mtp.head_subset.ids"] = torch.sort(
+                    torch.randperm(cfg.vocab, generator=g)[: cfg.draft.subset_rows]).values.to(torch.int64)
             if cfg.draft.markov_rank:
                 # Markov correction head (reference names: mtp.2.markov_head.{embed,head}.weight)
                 mat("mtp.markov_head.embed.weight", cfg.vocab, cfg.draft.markov_rank, std=1.0)
@@ -539,7 +544,7 @@ class OracleModel:
         f = self._ffn(p, h.to(self.dtype))
         return self._residual(x, f, hc)
 
-    def head(self, x: torch.Tensor) -> torch.Tensor:
+    def head(self, x: torch.Tensor, subset: bool = False) -> torch.Tensor:
         """final (hc combine) -> RMSNorm -> vocabulary head -> gathered fp32 logits
         (reference: src/model_io.rs:21,704)."""
         cfg, W = self.cfg, self.W
@@ -551,6 +556,18 @@ class OracleModel:
             pre = torch.sigmoid(m * W["hc_head_scale"][0] + W["hc_head_base"]) + cfg.hc_eps
             x = hc_collapse(x, pre)
         hn = rmsnorm(x, W["norm.weight"], cfg.rms_eps).to(self.dtype)
+        if subset:
+            # the drafter's subset head: logits only for the subset's tokens, -inf elsewhere
+            # (single rank; "mtp.head_subset.weight" holds what a 4-bit copy of those rows decodes to)
+            assert self.world == 1, "the subset head is built for one rank"
+            ids = W["mtp.head_subset.ids"].to(hn.device)
+            w = W["mtp.head_subset.weight"] if "mtp.head_subset.weight" in W else W["head.weight"][ids]
+            logits = torch.full((hn.shape[0], cfg.vocab), float("-inf"), dtype=torch.float32, device=hn.device)
+            # the 4-bit head multiplies MXFP8 activations (e4m3, one UE8M0 scale per 32 inputs)
+            q8, s8 = codecs.mxfp8_quant(hn.float().cpu(), 32)
+            hq = codecs.mxfp8_dequant(q8, s8, 32).to(hn.device, torch.float32)
+            logits[:, ids] = hq @ w.to(torch.float32).t()
+            return logits
         logits = (hn @ W["head.weight"].t()).to(torch.float32)
         return self.comm.all_gather(logits, dim=1)
 
@@ -603,7 +620,7 @@ class OracleModel:
             x = x[:, None, :].expand(T, cfg.hc_mult, cfg.hidden).contiguous()
         for j in range(cfg.draft.layers):
             x = self._layer(f"mtp.{j}", cfg.n_layers + j, x, pos, s, draft=True)
-        logits = self.head(x)
+        logits = self.head(x, subset=bool(cfg.draft.subset_rows))
         if cfg.draft.markov_rank:
             # Markov correction: a rank-r bigram term from the token each row was fed
             # (reference: src/dspark_markov.rs:886-971, kernels/core.cu:1110-1122)
