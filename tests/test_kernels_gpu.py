@@ -31,6 +31,24 @@ def test_smallm_fp8_dense(M):
     assert _rel(out, ref) < 2e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 256, 2048), (9, 384, 4096), (16, 128, 2176)])
+def test_smallm_fp8_dense_eight_way_k_split(M, N, K):
+    """Dense matrices with few 32-feature tiles and long rows split K over eight warps per CTA
+    (K not a multiple of 8 x 128 leaves the last warps short or idle); results are run-to-run identical."""
+    torch.manual_seed(K + M)
+    fw = E.quant_fp8_device(torch.randn(N, K, device=DEV) * 0.05)
+    x = torch.randn(M, K, device=DEV).half()
+    outs = []
+    for _ in range(2):
+        out = torch.zeros(M, N, device=DEV)
+        native.call("tf_smallm_gemm", 0, fw.q, None, fw.s, None, 0, 0, K, K // 128, x, K, out, N, 0, N, K, M,
+                    None, None, None, None, None, 1, 0, M, 0.0)
+        outs.append(out)
+    ref = x.float() @ E.dequant_fp8(fw).t()
+    assert _rel(outs[0], ref) < 2e-3
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_smallm_fp8_dual_swiglu_and_kslice():
     torch.manual_seed(0)
     N, K, M = 256, 512, 7
