@@ -135,3 +135,35 @@ def test_startup_self_check_on_the_oracle_backend():
         assert False, "difference not detected"
     except SelfCheckError:
         pass
+
+
+def test_worker_hands_the_tokens_before_each_prefilled_part_to_backends_that_want_them():
+    """Backends whose models hash n-grams (wants_prev) get the tokens right before every prefilled
+    part, across the seam between a restored prefix and the new tokens; decode slots carry the
+    tokens before their anchor."""
+    cfg, w, s = _mk()
+    seen = []
+
+    class Wants(type(w.b)):
+        wants_prev = True
+
+        def prefill(self, region, tokens, start, on_chunk=None, prev=()):
+            seen.append((start, list(tokens)[:2], list(prev)))
+            return super().prefill(region, tokens, start, on_chunk)
+
+    w.b.__class__ = Wants
+    ev = []
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(3, cfg.vocab, (70,), generator=g).tolist()
+    s.submit(_job("a", prompt, 6, ev, temperature=0.0))
+    _drain(w)
+    assert seen and seen[0][0] == 0 and seen[0][2] == []
+    for start, head, prev in seen:
+        assert prev == prompt[max(0, start - 8):start] and head == prompt[start:start + 2]
+    toks = [t for j, k, p in ev if k == "tokens" for t in p]
+    seen.clear()
+    follow = prompt + toks + [5, 6, 7]
+    s.submit(_job("b", follow, 4, [], temperature=0.0))
+    _drain(w)
+    assert seen and all(prev == follow[max(0, start - 8):start] for start, _, prev in seen)
+    assert min(start for start, _, _ in seen) >= 64            # the restored prefix was not prefilled again
