@@ -497,6 +497,34 @@ def test_router_topk_group_equals_the_two_launches(M):
         assert torch.equal(a, b_) if isinstance(a, torch.Tensor) else a == b_
 
 
+def test_mxfp4_to_fp8_block_conversion_is_exact_where_representable():
+    """e2m1 x 2^e re-expressed as e4m3 with one power-of-two scale per 128 x 128 block: exact while a
+    group's scale is within 2^-6 of the block's largest (e4m3 holds the shifted magnitudes), rounded
+    to nearest below that, signs kept."""
+    torch.manual_seed(21)
+    E_, N, K = 2, 256, 512
+    pk = torch.randint(0, 256, (E_, N, K // 2), device=DEV, dtype=torch.uint8)
+    sc = torch.randint(118, 126, (E_, N, K // 32), device=DEV, dtype=torch.uint8)
+    sc[0, :5, :3] = 100                                   # far below the block maximum: rounds towards zero
+    out = torch.zeros(E_, N, K, dtype=torch.uint8, device=DEV)
+    out_s = torch.zeros(E_ * N // 128, K // 128, device=DEV)
+    native.call("tf_mxfp4_to_fp8_block", pk, sc, out, out_s, E_, N, K, 0, N)
+    torch.cuda.synchronize()
+    want = E.dequant_mxfp4(pk, sc)                        # [E, N, K] fp32
+    got = out.view(torch.float8_e4m3fn).float().view(E_, N // 128, 128, K // 128, 128) \
+        * out_s.view(E_, N // 128, 1, K // 128, 1)
+    got = got.reshape(E_, N, K)
+    close = sc.view(E_, N // 128, 128, K // 128, 4).float()
+    top = close.amax(dim=(2, 4), keepdim=True)
+    exact = ((top - close) <= 6).expand_as(close).reshape(E_, N, K // 32).repeat_interleave(32, dim=2)
+    assert torch.equal(got[exact], want[exact])
+    blk_max = want.abs().view(E_, N // 128, 128, K // 128, 128).amax(dim=(2, 4), keepdim=True).expand(
+        E_, N // 128, 128, K // 128, 128).reshape(E_, N, K)
+    assert ((got - want).abs() <= blk_max * 2.0 ** -9).all()
+    nz = got != 0
+    assert torch.equal(torch.signbit(got[nz]), torch.signbit(want[nz]))
+
+
 def test_mx8_row_quantiser_matches_codec():
     """e4m3 values with one UE8M0 scale per 32 inputs: same bytes as the host codec."""
     torch.manual_seed(5)

@@ -122,43 +122,53 @@ __global__ void moe_place_kernel(const int* __restrict__ ids, int n_pairs, int e
 }
 
 // ---- MXFP4 -> FP8 with one power-of-two scale per 128x128 block -----------------------------
-// grid (K/128, N/128, experts), 128 threads: thread = row of the block
-__global__ void mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sc,
-                                          uint8_t* __restrict__ out, float* __restrict__ out_s, int N, int K,
-                                          long out_expert_stride, int out_row0, int out_N) {
+// grid (K/128, N/128, experts), 128 threads: thread = row of the block.  A 32-input group whose
+// UE8M0 scale is 2^-shift of the block's largest one turns into e4m3 through a table of the eight
+// e2m1 magnitudes times 2^-shift (built per CTA with the same rounding as a direct conversion):
+// one byte-permute per four weights, the sign bits moved from nibble to byte positions.
+__device__ __forceinline__ uint32_t e2m1x4_signs_to_bytes(uint32_t half16) {
+  const uint32_t s = half16 & 0x8888u;                               // sign bits at 3, 7, 11, 15
+  const uint32_t z = (s & 0x00ffu) | ((s & 0xff00u) << 8);           // ... at 3, 7, 19, 23
+  return ((z & 0x00080008u) << 4) | ((z & 0x00800080u) << 8);        // ... at 7, 15, 23, 31
+}
+__global__ void __launch_bounds__(128)
+mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sc,
+                          uint8_t* __restrict__ out, float* __restrict__ out_s, int N, int K,
+                          long out_expert_stride, int out_row0, int out_N) {
   __shared__ int smax;
+  __shared__ uint2 lut[16];                // [shift]: bytes 0..7 = e4m3 of magnitude code 0..7 times 2^-shift
   const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
   const long row = (long)e * N + nb * 128 + r;
   const uint8_t* srow = sc + row * (K / 32) + kb * 4;
   if (r == 0) smax = 0;
+  reinterpret_cast<uint8_t*>(lut)[r] = float_to_e4m3(e2m1_to_float(r & 7) * exp2f((float)-(r >> 3)));
   __syncthreads();
+  const uint32_t codes = *reinterpret_cast<const uint32_t*>(srow);
   int c[4], mx = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    c[j] = srow[j];
+    c[j] = (codes >> (8 * j)) & 0xff;
     mx = max(mx, c[j]);
   }
-  atomicMax(&smax, mx);
+  mx = __reduce_max_sync(0xffffffffu, mx);
+  if ((r & 31) == 0) atomicMax(&smax, mx);
   __syncthreads();
   const int top = smax;
   const uint8_t* wrow = w + row * (K / 2) + kb * 64;
   uint8_t* orow = out + (long)e * out_expert_stride + ((long)out_row0 + nb * 128 + r) * K + kb * 128;
+  uint4 pk[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) pk[j] = *reinterpret_cast<const uint4*>(wrow + j * 16);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float f = exp2f((float)(c[j] - top));
-    const uint4 pk = *reinterpret_cast<const uint4*>(wrow + j * 16);
-    const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+    const uint2 L = lut[min(top - c[j], 15)];       // from 2^-15 on every magnitude rounds to zero
+    const uint32_t words[4] = {pk[j].x, pk[j].y, pk[j].z, pk[j].w};
     uint32_t o[8];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      uint32_t lo = 0, hi = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        lo |= (uint32_t)float_to_e4m3(e2m1_to_float((words[q] >> (4 * i)) & 0xfu) * f) << (8 * i);
-        hi |= (uint32_t)float_to_e4m3(e2m1_to_float((words[q] >> (4 * i + 16)) & 0xfu) * f) << (8 * i);
-      }
-      o[2 * q] = lo;
-      o[2 * q + 1] = hi;
+      const uint32_t lo16 = words[q] & 0xffffu, hi16 = words[q] >> 16;
+      o[2 * q] = __byte_perm(L.x, L.y, lo16 & 0x7777u) | e2m1x4_signs_to_bytes(lo16);
+      o[2 * q + 1] = __byte_perm(L.x, L.y, hi16 & 0x7777u) | e2m1x4_signs_to_bytes(hi16);
     }
     uint4* dst = reinterpret_cast<uint4*>(orow + j * 32);
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
