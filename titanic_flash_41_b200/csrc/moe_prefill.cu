@@ -122,7 +122,7 @@ __global__ void moe_place_kernel(const int* __restrict__ ids, int n_pairs, int e
 }
 
 // ---- MXFP4 -> FP8 with one power-of-two scale per 128x128 block -----------------------------
-// grid (K/128, N/128, experts), 128 threads: thread = row of the block.  A 32-input group whose
+// grid (K/128, N/128, experts), 128 threads.  A 32-input group whose
 // UE8M0 scale is 2^-shift of the block's largest one turns into e4m3 through a table of the eight
 // e2m1 magnitudes times 2^-shift (built per CTA with the same rounding as a direct conversion):
 // one byte-permute per four weights, the sign bits moved from nibble to byte positions.
@@ -137,32 +137,31 @@ mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restri
                           long out_expert_stride, int out_row0, int out_N) {
   __shared__ int smax;
   __shared__ uint2 lut[16];                // [shift]: bytes 0..7 = e4m3 of magnitude code 0..7 times 2^-shift
-  const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z, r = threadIdx.x;
-  const long row = (long)e * N + nb * 128 + r;
-  const uint8_t* srow = sc + row * (K / 32) + kb * 4;
-  if (r == 0) smax = 0;
-  reinterpret_cast<uint8_t*>(lut)[r] = float_to_e4m3(e2m1_to_float(r & 7) * exp2f((float)-(r >> 3)));
+  const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z, t = threadIdx.x;
+  // four lanes share a row (one 32-input group = 16 packed bytes each): a warp reads 8 rows x 64
+  // contiguous bytes and writes 8 rows x 128 contiguous bytes per step; four steps cover 128 rows
+  const int g = t & 3, r0 = t >> 2;
+  const long row0 = (long)e * N + nb * 128;
+  if (t == 0) smax = 0;
+  reinterpret_cast<uint8_t*>(lut)[t] = float_to_e4m3(e2m1_to_float(t & 7) * exp2f((float)-(t >> 3)));
   __syncthreads();
-  const uint32_t codes = *reinterpret_cast<const uint32_t*>(srow);
   int c[4], mx = 0;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    c[j] = (codes >> (8 * j)) & 0xff;
-    mx = max(mx, c[j]);
-  }
-  mx = __reduce_max_sync(0xffffffffu, mx);
-  if ((r & 31) == 0) atomicMax(&smax, mx);
-  __syncthreads();
-  const int top = smax;
-  const uint8_t* wrow = w + row * (K / 2) + kb * 64;
-  uint8_t* orow = out + (long)e * out_expert_stride + ((long)out_row0 + nb * 128 + r) * K + kb * 128;
   uint4 pk[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) pk[j] = *reinterpret_cast<const uint4*>(wrow + j * 16);
+  for (int i = 0; i < 4; ++i) {
+    const long row = row0 + r0 + 32 * i;
+    c[i] = sc[row * (K / 32) + kb * 4 + g];
+    pk[i] = *reinterpret_cast<const uint4*>(w + row * (K / 2) + kb * 64 + g * 16);
+    mx = max(mx, c[i]);
+  }
+  mx = __reduce_max_sync(0xffffffffu, mx);
+  if ((t & 31) == 0) atomicMax(&smax, mx);
+  __syncthreads();
+  const int top = smax;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint2 L = lut[min(top - c[j], 15)];       // from 2^-15 on every magnitude rounds to zero
-    const uint32_t words[4] = {pk[j].x, pk[j].y, pk[j].z, pk[j].w};
+  for (int i = 0; i < 4; ++i) {
+    const uint2 L = lut[min(top - c[i], 15)];       // from 2^-15 on every magnitude rounds to zero
+    const uint32_t words[4] = {pk[i].x, pk[i].y, pk[i].z, pk[i].w};
     uint32_t o[8];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -170,11 +169,12 @@ mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restri
       o[2 * q] = __byte_perm(L.x, L.y, lo16 & 0x7777u) | e2m1x4_signs_to_bytes(lo16);
       o[2 * q + 1] = __byte_perm(L.x, L.y, hi16 & 0x7777u) | e2m1x4_signs_to_bytes(hi16);
     }
-    uint4* dst = reinterpret_cast<uint4*>(orow + j * 32);
+    uint8_t* orow = out + (long)e * out_expert_stride + ((long)out_row0 + nb * 128 + r0 + 32 * i) * K + kb * 128;
+    uint4* dst = reinterpret_cast<uint4*>(orow + g * 32);
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
   }
-  if (r == 0) {
+  if (t == 0) {
     const long srow_o = ((long)e * out_N + out_row0) / 128 + nb;
     out_s[srow_o * (K / 128) + kb] = ue8m0_to_float((uint8_t)top);
   }
