@@ -20,6 +20,25 @@ __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<__half>(const __half* p) { return __half2float(*p); }
 template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+// four consecutive elements in one load (the address is a multiple of four elements)
+template <typename T>
+__device__ __forceinline__ void ld4(const T* p, float v[4]);
+template <> __device__ __forceinline__ void ld4<__half>(const __half* p, float v[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <> __device__ __forceinline__ void ld4<__nv_bfloat16>(const __nv_bfloat16* p, float v[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <> __device__ __forceinline__ void ld4<float>(const float* p, float v[4]) {
+  const float4 raw = *reinterpret_cast<const float4*>(p);
+  v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+}
 
 template <typename T>
 __global__ void quant_rows_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ row_src,
@@ -35,11 +54,9 @@ __global__ void quant_rows_kernel(const T* __restrict__ x, long ldx, const int* 
   if (dst < 0) return;
   const T* xp = x + src * ldx + kb * 128 + lane * 4;
   float v[4], am = 0.f;
+  ld4<T>(xp, v);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    v[j] = ldf<T>(xp + j);
-    am = fmaxf(am, fabsf(v[j]));
-  }
+  for (int j = 0; j < 4; ++j) am = fmaxf(am, fabsf(v[j]));
   am = warp_max(am);
   const float sc = fmaxf(am, 1e-12f) / 448.f;
   uint32_t packed = 0;
@@ -62,10 +79,12 @@ __global__ void swiglu_rows_kernel(const T* __restrict__ y, long ldy, __half* __
   const int r = (int)(item / kb_per_row), kb = (int)(item % kb_per_row);
   const T* g = y + (long)r * ldy + kb * 128 + lane * 4;
   const T* u = g + I;
-  float v[4], am = 0.f;
+  float v[4], am = 0.f, gv[4], uv[4];
+  ld4<T>(g, gv);
+  ld4<T>(u, uv);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    float gate = ldf<T>(g + j), up = ldf<T>(u + j);
+    float gate = gv[j], up = uv[j];
     if (limit > 0.f) {
       gate = fminf(gate, limit);
       up = fminf(fmaxf(up, -limit), limit);
@@ -203,6 +222,7 @@ __global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const
 TF_API int tf_quant_rows(const void* x, int x_kind, long ldx, const int* row_src, int src_div,
                          const int* row_dst, void* q, float* s, int rows, int K, cudaStream_t st) {
   if (K % 128 || rows <= 0) return rows <= 0 ? 0 : -1;
+  if (ldx % 4 || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;      // rows are read four elements at a time
   const long items = (long)rows * (K / 128);
   const unsigned grid = (unsigned)((items + 7) / 8);
   if (src_div < 1) src_div = 1;
@@ -215,6 +235,7 @@ TF_API int tf_quant_rows(const void* x, int x_kind, long ldx, const int* row_src
 TF_API int tf_swiglu_rows(const void* y, int y_kind, long ldy, void* out16, long ldo, void* q, float* s,
                           int rows, int I, float limit, const int* n_rows_dev, cudaStream_t st) {
   if (I % 128 || rows <= 0) return rows <= 0 ? 0 : -1;
+  if (ldy % 4 || (reinterpret_cast<uintptr_t>(y) & 15)) return -1;      // rows are read four elements at a time
   const long items = (long)rows * (I / 128);
   const unsigned grid = (unsigned)((items + 7) / 8);
   if (y_kind == 0) swiglu_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
