@@ -54,14 +54,30 @@ def main():
     x16 = torch.randn(M, K, device=dev, generator=g).half()
     resid = torch.randn(M, N, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).bfloat16()
     r0 = resid.clone()
-    ws.gemv_allreduce(w, x16, M, resid, None, st.t)
+    nw = (1 + 0.1 * torch.randn(N, device=dev, generator=torch.Generator(device=dev).manual_seed(2))).bfloat16()
+    h16 = torch.zeros(M, N, device=dev, dtype=torch.float16)
+    hb = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    x8 = torch.zeros(M, N, device=dev, dtype=torch.uint8)
+    x8s = torch.zeros(M, N // 32, device=dev, dtype=torch.uint8)
+    ws.gemv_allreduce(w, x16, M, resid, None, st.t, norm=dict(w=nw, h16=h16, hb=hb, x8=x8, x8s=x8s, eps=1e-6))
     part = x16.float() @ E.dequant_fp8(w).t()
     dist.all_reduce(part)
     torch.cuda.synchronize()
     st.check()
     want = (r0.float() + part).bfloat16()
-    assert (resid.float() - want.float()).abs().max() < 0.05, float((resid.float() - want.float()).abs().max())
-    say("fused gemv ok")
+    assert (resid.float() - want.float()).abs().max() < 0.08, float((resid.float() - want.float()).abs().max())
+    # the boundary computed in the epilogue: RMSNorm of the NEW residual, and its MXFP8 form
+    xf = resid.float()
+    hn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).bfloat16().float()
+    assert (hb.float() - hn).abs().max() <= 0.02 * hn.abs().max()
+    assert (h16.float() - hn).abs().max() <= 0.02 * hn.abs().max()
+    deq = x8.view(torch.float8_e4m3fn).float().view(M, N // 32, 32) * torch.exp2(x8s.float() - 127)[..., None]
+    assert (deq.view(M, N) - hn).abs().max() <= 0.08 * hn.abs().max()
+    for t in (resid, h16, x8):                              # bit-identical on every rank
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        assert all(torch.equal(gathered[0].view(torch.uint8), g_.view(torch.uint8)) for g_ in gathered)
+    say("fused gemv + boundary ok")
     # ---- 3. engine: TP/EP over `world` GPUs (fused kernels) == single GPU
     from tests.test_engine_gpu import small_config
     # keep every per-rank slice at least one 128-wide block: heads and shared-expert width grow with the world

@@ -267,7 +267,7 @@ def test_sampling_kernels():
     w = torch.zeros(S, 1, dtype=torch.float64, device=DEV)
     nacc = torch.zeros(S, dtype=torch.int32, device=DEV)
     tok = torch.zeros(S, dtype=torch.int32, device=DEV)
-    native.call("tf_spec_verify", lg1, None, stat1, None, None, u, S, 0, V, V, T, T, 0, R, w, nacc, tok, st.t)
+    native.call("tf_spec_verify", lg1, None, stat1, None, None, u, S, 0, V, V, T, T, None, 0, R, w, nacc, tok, st.t)
     st.check()
     srt, idx = torch.sort(pr[0], descending=True)
     n_in = int((torch.cumsum(srt, 0) < top_p).sum()) + 1
@@ -305,7 +305,7 @@ def test_block_verification_preserves_target_law():
     nacc = torch.zeros(S, dtype=torch.int32, device=DEV)
     tok = torch.zeros(S, dtype=torch.int32, device=DEV)
     native.call("tf_spec_verify", tlS, dlS, tstat[None].expand(S, g + 1, sb).contiguous(),
-                dstat[None].expand(S, g, sb).contiguous(), props, u, S, g, V, V, T, T, 0, R, w, nacc, tok, st.t)
+                dstat[None].expand(S, g, sb).contiguous(), props, u, S, g, V, V, T, T, None, 0, R, w, nacc, tok, st.t)
     st.check()
     first = torch.where(nacc > 0, props[:, 0], tok).long().cpu()
     emp = torch.bincount(first, minlength=V).double() / S

@@ -48,3 +48,24 @@ def test_static_scratch_refuses_too_many_rows():
     assert _static(lg, 1024, 17, 1.0, 1.0, out, st.t) == -3
     torch.cuda.synchronize()
     assert int(out.sum()) == 0                                 # nothing ran
+
+
+def test_static_scratch_refuses_bad_arguments_on_the_host():
+    """A bad argument is answered with -1 before anything is enqueued: no launch ever sees a null or
+    short logits row, and a nucleus mass outside (0, 1] never reaches the kernels."""
+    dev = "cuda:0"
+    st = native.StatusWord(dev)
+    sb = native.lib().tf_rowstat_bytes()
+    rows, V = 4, 1024
+    lg = torch.randn(rows, V, device=dev)
+    out = torch.full((rows * sb,), 0xCD, dtype=torch.uint8, device=dev)
+    fn = native.lib().tf_rowstats_static
+    stream = torch.cuda.current_stream().cuda_stream
+    assert _static(None, V, rows, 1.0, 1.0, out, st.t) == -1                     # null logits
+    assert fn(lg.data_ptr(), V - 4, V, rows, 1.0, 1.0, out.data_ptr(), st.t.data_ptr(), stream) == -1   # ldl < V
+    assert _static(lg, V, rows, 1.0, 0.0, out, st.t) == -1                      # top_p = 0
+    assert _static(lg, V, rows, 1.0, float("nan"), out, st.t) == -1
+    assert _static(lg, V, rows, 0.0, 1.0, out, st.t) == -1                      # temperature = 0
+    torch.cuda.synchronize()
+    assert (out == 0xCD).all()                                 # untouched
+    st.check()

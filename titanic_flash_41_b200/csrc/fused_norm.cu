@@ -11,9 +11,7 @@
 // Reference behaviour: the FFN sum with the shared expert (kernels/ffn_sum_shared.cuh:7-33), the
 // residual RMSNorm (kernels/core.cu:851 ca_rms_bf16) and the MXFP8 K32 activation quantisation of
 // the MoE front-end (kernels/moe_frontend.cuh).
-#include <cuda_fp8.h>
-
-#include "common.cuh"
+#include "rownorm.cuh"
 
 namespace {
 
@@ -84,31 +82,7 @@ __global__ void __launch_bounds__(1024) fused_norm_kernel(const FusedNormParams 
     }
   }
   ss = block_sum(ss, scratch);
-  const float inv = rsqrtf(ss / (float)d + p.eps);
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    const float v = bf16_round(row[i] * inv * __bfloat162float(p.w[i]));
-    row[i] = v;
-    if (p.h16) p.h16[(long)r * d + i] = __float2half(v);
-    if (p.hb) p.hb[(long)r * d + i] = __float2bfloat16(v);
-  }
-  if (p.x8) {
-    __syncthreads();
-    // one warp per group of 32 inputs; values as the f16 copy holds them
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int b = warp; b < d / 32; b += nw) {
-      const float v = __half2float(__float2half(row[b * 32 + lane]));
-      const float amax = warp_max(fabsf(v));
-      int ex = -127;
-      if (amax > 0.f) {
-        int e2;
-        const float m = frexpf(amax * (1.f / 448.f), &e2);
-        ex = max(-127, min(127, (m == 0.5f) ? e2 - 1 : e2));
-      }
-      p.x8[(long)r * d + b * 32 + lane] =
-          (uint8_t)__nv_cvt_float_to_fp8(v * exp2f((float)-ex), __NV_SATFINITE, __NV_E4M3);
-      if (lane == 0) p.x8s[(long)r * (d / 32) + b] = (uint8_t)(ex + 127);
-    }
-  }
+  row_norm_store(row, d, ss, p.eps, p.w, p.h16, p.hb, p.x8, p.x8s, r);
 }
 
 }  // namespace

@@ -6,7 +6,7 @@
 //  * block verification (Sun et al., arXiv:2403.10444; reference kernels/block_rejection.cuh:1-63):
 //      w_0 = 1, w_i = min(1, w_{i-1} p_{i-1}(x_i) / q_{i-1}(x_i)),
 //      R_i = sum_v max(w_i p_i(v) - q_i(v), 0),  h_i = R_i / (R_i + 1 - w_i) (i < g), h_g = w_g,
-//      tau = max{ i : u_i <= h_i } (0 if none); token at tau from the normalised residual (or from
+//      tau = max{ i : u_i < h_i } (0 if none); token at tau from the normalised residual (or from
 //      p_g when tau = g).  p and q are the temperature- and nucleus-modified distributions, so the
 //      output law is exactly the modified target law.  Masses are fp64; non-finite logits or
 //      negative masses raise a status word instead of producing a token.
@@ -154,7 +154,11 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ l
     m = fmaxf(m, a);
   }
   if (blockIdx.y == gridDim.y - 1)
-    for (int i = (V / 4) * 4 + threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, logits[(long)r * ldl + i]);
+    for (int i = (V / 4) * 4 + threadIdx.x; i < V; i += blockDim.x) {
+      const float v = logits[(long)r * ldl + i];
+      if (!(v < INFINITY) || isnan(v)) bad = 1;
+      m = fmaxf(m, v);
+    }
   m = warp_max(m);
   bad = __any_sync(0xffffffffu, bad);
   if ((threadIdx.x & 31) == 0) {
@@ -166,9 +170,11 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ l
 
 // level 0/1/2: shift 20/8/0, bins 4096/4096/256
 __global__ void __launch_bounds__(256) rowhist_kernel(const float* __restrict__ logits, int ldl, int V,
-                                                      float inv_t, int level, void* scratch) {
+                                                      float inv_t, const float* __restrict__ sess_temp, int rps,
+                                                      int level, void* scratch) {
   __shared__ unsigned long long sh[4096];
   const int r = blockIdx.x;
+  if (sess_temp) inv_t = 1.f / sess_temp[r / rps];
   RowScratch* rs = row_scratch(scratch, r);
   const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
   const int nb = level == 2 ? 256 : 4096;
@@ -201,10 +207,12 @@ __global__ void __launch_bounds__(256) rowhist_kernel(const float* __restrict__ 
 }
 
 // one CTA (1024 threads) per row: choose the bin, clear the histogram
-__global__ void __launch_bounds__(1024) rowpick_kernel(int level, float top_p, int last, RowStat* __restrict__ out,
-                                                       void* scratch, TfStatusWord* st) {
+__global__ void __launch_bounds__(1024) rowpick_kernel(int level, float top_p, const float* __restrict__ sess_top_p,
+                                                       int rps, int last, RowStat* __restrict__ out, void* scratch,
+                                                       TfStatusWord* st) {
   __shared__ unsigned long long chunk[32];
   const int r = blockIdx.x;
+  if (sess_top_p) top_p = sess_top_p[r / rps];
   RowScratch* rs = row_scratch(scratch, r);
   unsigned long long* gh = row_hist(scratch, r);
   const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
@@ -289,6 +297,7 @@ struct VerifyParams {
   const double* uniforms;   // [S, g+2]: u_1..u_g (acceptance), u_draw at index g, spare
   int S, g, V, ldl;
   float t_temp, d_temp;
+  const float* sess_temp;   // [S] or null: temperature of conversation s for its target AND draft rows
   int point_mass;           // 1: q_i is a point mass at the proposal (text-lookup proposals)
   double* tile_mass;        // [S, g+1, ntiles] scratch: residual mass of every 1024-token tile
   double* w;                // [S, g+1] scratch
@@ -303,11 +312,11 @@ __device__ double weight_chain(const VerifyParams& p, int s, int i) {
   for (int j = 1; j <= i; ++j) {
     const int x = p.proposals[s * p.g + j - 1];
     const float* tx = p.tlogits + ((long)s * (p.g + 1) + j - 1) * p.ldl;
-    const double pt = prob_of(tx, p.tstat[s * (p.g + 1) + j - 1], 1.f / p.t_temp, x);
+    const double pt = prob_of(tx, p.tstat[s * (p.g + 1) + j - 1], 1.f / (p.sess_temp ? p.sess_temp[s] : p.t_temp), x);
     double q = 1.0;
     if (!p.point_mass) {
       const float* dx = p.dlogits + ((long)s * p.g + j - 1) * p.ldl;
-      q = prob_of(dx, p.dstat[s * p.g + j - 1], 1.f / p.d_temp, x);
+      q = prob_of(dx, p.dstat[s * p.g + j - 1], 1.f / (p.sess_temp ? p.sess_temp[s] : p.d_temp), x);
     }
     const double ratio = q > 0.0 ? w * pt / q : (pt > 0.0 ? 1.0 : 0.0);
     w = ratio < 1.0 ? ratio : 1.0;
@@ -331,13 +340,13 @@ __device__ __forceinline__ RowCtx row_ctx(const VerifyParams& p, int s, int i, d
   c.tx = p.tlogits + ((long)s * (p.g + 1) + i) * p.ldl;
   c.tm = ts.m;
   c.tthr = ts.thr;
-  c.t_inv = 1.f / p.t_temp;
+  c.t_inv = 1.f / (p.sess_temp ? p.sess_temp[s] : p.t_temp);
   c.wz = wi / ts.z;
   c.dx = nullptr;
   c.point_tok = -1;
   c.dm = 0.f;
   c.dthr = 0;
-  c.d_inv = 1.f / p.d_temp;
+  c.d_inv = 1.f / (p.sess_temp ? p.sess_temp[s] : p.d_temp);
   c.qz = 0.0;
   if (i < p.g) {
     if (p.point_mass) c.point_tok = p.proposals[s * p.g + i];
@@ -417,7 +426,7 @@ __global__ void __launch_bounds__(1024) verify_decide_kernel(VerifyParams p, int
       const double R = Rrow[i], w = wrow[i];
       if (!(R >= 0.0) || isinf(R)) tf_report(p.st, TF_NONFINITE, 21, s, i);
       const double h = (i < g) ? (R + 1.0 - w > 0.0 ? R / (R + 1.0 - w) : 0.0) : w;
-      if (u[i - 1] <= h) tau = i;
+      if (u[i - 1] < h) tau = i;
     }
     s_tau = tau;
     s_tok = -1;
@@ -485,20 +494,41 @@ TF_API int tf_rowstat_bytes() { return (int)sizeof(RowStat); }
 // bytes of zero-initialised scratch tf_rowstats needs for `rows` rows
 TF_API long tf_rowstats_scratch_bytes(int rows) { return (long)rows * (long)kRowScratchBytes; }
 
-// scratch: tf_rowstats_scratch_bytes(rows) bytes, zero before the first call (left zero by each call)
-TF_API int tf_rowstats(const float* logits, int ldl, int V, int rows, float temp, float top_p, void* out,
-                       void* scratch, void* status, cudaStream_t st) {
-  if (!(temp > 0.f) || (ldl % 4) != 0 || (((uintptr_t)logits) & 15) != 0 || scratch == nullptr) return -1;
+// scratch: tf_rowstats_scratch_bytes(rows) bytes, zero before the first call (left zero by each call).
+// sess_temp / sess_top_p (device arrays, may be null): per-conversation settings, row r belonging to
+// conversation r / rows_per_sess; they override the scalars, so requests with different sampling
+// settings share one launch (and one captured graph).  The host must have validated them
+// (temperature > 0, 0 < top_p <= 1).
+static int rowstats_launch(const float* logits, int ldl, int V, int rows, float temp, float top_p,
+                           const float* sess_temp, const float* sess_top_p, int rows_per_sess, void* out,
+                           void* scratch, void* status, cudaStream_t st) {
+  if (logits == nullptr || out == nullptr || scratch == nullptr || rows <= 0 || V <= 0 || ldl < V) return -1;
+  if (!(temp > 0.f) || !(top_p > 0.f && top_p <= 1.f) || (ldl % 4) != 0 || (((uintptr_t)logits) & 15) != 0) return -1;
+  if ((sess_temp || sess_top_p) && rows_per_sess <= 0) return -1;
   const float inv_t = 1.f / temp;
+  const int rps = rows_per_sess > 0 ? rows_per_sess : 1;
   dim3 grid(rows, kSlices);
   rowmax_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, scratch);
-  const int levels = top_p < 1.f ? 3 : 1;
+  const int levels = (sess_top_p || top_p < 1.f) ? 3 : 1;
   for (int level = 0; level < levels; ++level) {
-    rowhist_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, inv_t, level, scratch);
-    rowpick_kernel<<<rows, 1024, 0, st>>>(level, top_p, level == levels - 1, (RowStat*)out, scratch,
+    rowhist_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, inv_t, sess_temp, rps, level, scratch);
+    rowpick_kernel<<<rows, 1024, 0, st>>>(level, top_p, sess_top_p, rps, level == levels - 1, (RowStat*)out, scratch,
                                           (TfStatusWord*)status);
   }
   return (int)cudaGetLastError();
+}
+
+TF_API int tf_rowstats(const float* logits, int ldl, int V, int rows, float temp, float top_p, void* out,
+                       void* scratch, void* status, cudaStream_t st) {
+  return rowstats_launch(logits, ldl, V, rows, temp, top_p, nullptr, nullptr, 1, out, scratch, status, st);
+}
+
+// tf_rowstats with per-conversation temperature / top-p arrays (see rowstats_launch)
+TF_API int tf_rowstats_per_session(const float* logits, int ldl, int V, int rows, const float* sess_temp,
+                                   const float* sess_top_p, int rows_per_sess, void* out, void* scratch,
+                                   void* status, cudaStream_t st) {
+  if (!sess_temp || !sess_top_p) return -1;
+  return rowstats_launch(logits, ldl, V, rows, 1.f, 1.f, sess_temp, sess_top_p, rows_per_sess, out, scratch, status, st);
 }
 
 // doubles of scratch tf_spec_verify needs in `tile_mass`
@@ -509,13 +539,17 @@ TF_API long tf_spec_verify_scratch_doubles(int S, int g, int V) {
 // Block verification of g proposals per conversation (g may be 0: plain sampling of one row).
 TF_API int tf_spec_verify(const float* tlogits, const float* dlogits, const void* tstat, const void* dstat,
                           const int* proposals, const double* uniforms, int S, int g, int V, int ldl,
-                          float t_temp, float d_temp, int point_mass, double* tile_mass, double* w,
-                          int* n_accept, int* next_token, void* status, cudaStream_t st) {
-  if (g > 62) return -1;
+                          float t_temp, float d_temp, const float* sess_temp, int point_mass, double* tile_mass,
+                          double* w, int* n_accept, int* next_token, void* status, cudaStream_t st) {
+  if (g > 62 || g < 0 || S <= 0 || V <= 0 || !tlogits || !tstat || !uniforms || !tile_mass || !w || !n_accept ||
+      !next_token)
+    return -1;
+  if (g > 0 && (!proposals || (!point_mass && (!dlogits || !dstat)))) return -1;
+  if (!sess_temp && (!(t_temp > 0.f) || !(d_temp > 0.f))) return -1;
   VerifyParams p;
   p.tlogits = tlogits; p.dlogits = dlogits; p.tstat = (const RowStat*)tstat; p.dstat = (const RowStat*)dstat;
   p.proposals = proposals; p.uniforms = uniforms; p.S = S; p.g = g; p.V = V; p.ldl = ldl;
-  p.t_temp = t_temp; p.d_temp = d_temp; p.point_mass = point_mass; p.tile_mass = tile_mass; p.w = w;
+  p.t_temp = t_temp; p.d_temp = d_temp; p.sess_temp = sess_temp; p.point_mass = point_mass; p.tile_mass = tile_mass; p.w = w;
   p.n_accept = n_accept; p.next_token = next_token; p.st = (TfStatusWord*)status;
   const int ntiles = (V + kTile - 1) / kTile;
   dim3 grid(S * (g + 1), ntiles);
@@ -564,7 +598,8 @@ TF_API int tf_rowstats_static(const float* logits, int ldl, int V, int rows, flo
             TF_ROWSTATS_STATIC_MAX_ROWS);
     return TF_ROWSTATS_STATIC_TOO_MANY_ROWS;
   }
-  if (rows <= 0 || V <= 0 || out == nullptr) return -1;
+  if (rows <= 0 || V <= 0 || out == nullptr || logits == nullptr || ldl < V) return -1;
+  if (!(temp > 0.f) || !(top_p > 0.f && top_p <= 1.f) || (ldl % 4) != 0 || (((uintptr_t)logits) & 15) != 0) return -1;
   void* scratch = nullptr;
   cudaError_t e = static_scratch(&scratch);
   if (e != cudaSuccess) return (int)e;

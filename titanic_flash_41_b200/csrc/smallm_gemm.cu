@@ -55,11 +55,10 @@ struct SmallMParams {
   float swiglu_limit;
   int k_per_warp;            // multiple of 128
   // fused tensor-parallel epilogue (dense form, M <= 32): all-reduce the [M, N] partial over the
-  // peers' memory and add it to the residual stream
-  int use_comm;
+  // peers' memory, add it to the residual stream and run the boundary that follows (comm.cuh)
+  int use_comm;              // 0 = off, 1 = bf16 transport, 2 = fp32 transport
   CommParams comm;
-  __nv_bfloat16* resid;      // [M, N] residual stream updated in place (may be null)
-  float* ar_out;             // [M, N] reduced fp32 output (may be null)
+  RowEpilogue ep;
   // kind 3: X is e4m3 bytes (ldx in bytes), every 8 consecutive k stored as x0 x2 x4 x6 x1 x3 x5 x7,
   // with one fp32 scale per activation row
   const float* x_scale;
@@ -459,8 +458,9 @@ smallm_gemm_kernel(SmallMParams p) {
   }
   if (KIND == 0 && !DUAL) {
     if (p.use_comm) {
-      if (comm_allreduce_tile(p.comm, ctile, rows, blockIdx.x))
-        comm_residual_update(p.resid, p.N, p.ar_out, p.N, ctile, rows, blockIdx.x);
+      extern __shared__ float rowbuf[];      // N floats, comm form only
+      if (p.use_comm == 2) comm_allreduce_rows<true>(p.comm, ctile, rows, p.ep, rowbuf);
+      else comm_allreduce_rows<false>(p.comm, ctile, rows, p.ep, rowbuf);
     }
   }
 }
@@ -595,29 +595,44 @@ TF_API int tf_quant_rows_e4m3_perm(const void* x, long ldx, void* q, long ldq, f
   return (int)cudaGetLastError();
 }
 
-// Dense FP8 GEMV (M <= 32) fused with the tensor-parallel all-reduce and the residual update:
+// Dense FP8 GEMV (M <= 32) fused with the tensor-parallel all-reduce, the residual update and the
+// boundary that follows:
 //   resid[M, N] += sum over ranks of X_rank[M, K] * W_rank[N, K]^T      (and/or ar_out = the sum)
+//   norm_w given: h16 / hb / (x8, x8s) = RMSNorm(resid) * norm_w in f16 / bf16 / MXFP8
 // `peers` is a device array of `world` workspace base addresses (see comm.cuh for the layout),
-// `epoch` a zero-initialised device array of N/32 counters owned by this rank.
+// `epoch` a zero-initialised device array of N/32 counters owned by this rank.  With a residual the
+// partials travel as bf16, without one (ar_out only) as fp32.
 TF_API int tf_smallm_gemm_allreduce(const void* W, const void* S, int ldw, int lds, const void* X, int ldx,
                                     int N, int K, int M, const void* peers, int world, int rank,
-                                    int max_rows, long flag_bytes, void* epoch, void* resid, float* ar_out,
-                                    int spin_limit, void* status, cudaStream_t stream) {
-  if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0 || (ldw % 16) != 0) return -1;
-  if (M < 1 || M > 32 || M > max_rows || world < 1 || world > 32) return -1;
+                                    int max_rows, void* epoch, void* resid, float* ar_out, const void* norm_w,
+                                    void* h16, void* hb, void* x8, void* x8s, float eps, int spin_limit,
+                                    void* status, cudaStream_t stream) {
+  if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0 || (ldw % 16) != 0 || N % 128 != 0) return -1;
+  if (M < 1 || M > 32 || M > max_rows || world < 1 || world > kCommMaxWorld || N / kTileN < M) return -1;
+  if (!W || !S || !X || !peers || !epoch || (!resid && !ar_out) || (x8 && !x8s) || (norm_w && !resid)) return -1;
   SmallMParams p;
   p.W = (const uint8_t*)W; p.W3 = nullptr; p.S = S; p.S3 = nullptr;
   p.w_group_stride = 0; p.s_group_stride = 0; p.ldw = ldw; p.lds = lds;
   p.X = (const __half*)X; p.ldx = ldx; p.Y = nullptr; p.ldy = N; p.out_kind = 0; p.N = N; p.K = K; p.M = M;
   p.group_expert = nullptr; p.group_start = nullptr; p.group_count = nullptr; p.n_groups = nullptr;
   p.sorted_pairs = nullptr; p.x_div = 1; p.swiglu_limit = 0.f;
-  p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
-  p.use_comm = 1;
+  p.k_per_warp = ((K + kMaxWarps - 1) / kMaxWarps + 127) / 128 * 128;
+  p.use_comm = resid ? 1 : 2;
   p.x_scale = nullptr;
   p.kstep = 64; p.s_kstep = 4;
   p.comm.peers = (const unsigned long long*)peers; p.comm.world = world; p.comm.rank = rank;
   p.comm.tiles = N / kTileN; p.comm.max_rows = max_rows; p.comm.N = N; p.comm.epoch = (unsigned int*)epoch;
-  p.comm.flag_bytes = flag_bytes; p.comm.spin_limit = spin_limit; p.comm.st = (TfStatusWord*)status;
-  p.resid = (__nv_bfloat16*)resid; p.ar_out = ar_out;
-  return (int)launch<0, false>(p, 0, stream);
+  p.comm.spin_limit = spin_limit; p.comm.st = (TfStatusWord*)status;
+  p.ep.resid = (__nv_bfloat16*)resid; p.ep.ar_out = ar_out; p.ep.norm_w = (const __nv_bfloat16*)norm_w;
+  p.ep.h16 = (__half*)h16; p.ep.hb = (__nv_bfloat16*)hb; p.ep.x8 = (uint8_t*)x8; p.ep.x8s = (uint8_t*)x8s;
+  p.ep.eps = eps;
+  const size_t dyn = (size_t)N * sizeof(float);
+  if (dyn > 24 * 1024) {
+    cudaError_t a = cudaFuncSetAttribute(smallm_gemm_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)dyn);
+    if (a != cudaSuccess) return (int)a;
+  }
+  dim3 grid(N / kTileN, 1);
+  smallm_gemm_kernel<0, false><<<grid, kMaxWarps * 32, dyn, stream>>>(p);
+  return (int)cudaGetLastError();
 }

@@ -675,7 +675,11 @@ class Engine:
             self.comm.all_reduce(t)
 
     # -- one layer ---------------------------------------------------------------------------
-    def _layer(self, li: int, L: LayerWeights, T: int, b: dict, nmax: int, rpg: int, first: bool) -> None:
+    def _layer(self, li: int, L: LayerWeights, T: int, b: dict, nmax: int, rpg: int, first: bool,
+               next_norm: Optional[torch.Tensor] = None) -> None:
+        """One decoder layer.  ``next_norm``: RMSNorm weight of the boundary that follows this layer
+        (the next layer's attention norm, or the final norm); when the fused all-reduce is up it
+        computes that boundary in its epilogue."""
         cfg = self.cfg
         d, Dh, Hl = cfg.hidden, cfg.head_dim, self.Hl
         pos, region, first_row, last_pos, nvalid = (b["meta"][i] for i in (1, 2, 3, 4, 5))
@@ -743,15 +747,18 @@ class Engine:
             self._hc_post(T, b)
         elif fused:
             # WO projection + all-reduce + residual add in one kernel over peer memory
-            self.symm.gemv_allreduce(L.wo, wo_in, T, b["x"], None, self.status.t)
+            # (and the FFN boundary: RMSNorm + f16 / bf16 / MXFP8 rows, in the same epilogue)
+            self.symm.gemv_allreduce(L.wo, wo_in, T, b["x"], None, self.status.t,
+                                     norm=self._epilogue_norm(b, L.ffn_norm))
             b["pending"] = False
+            b["normed"] = True
         else:
             self._linear(wo_in, L.wo, b["delta"], T)
             self._allreduce(b["delta"][:T])
             b["pending"] = True
         # FFN boundary
         self._boundary(L, "ffn", T, b, want_hb=True)
-        self._moe(L, T, b)
+        self._moe(L, T, b, next_norm)
         if hc:
             if not (fused and T <= self.SMALL_M):
                 self._allreduce(b["delta"][:T])
@@ -809,6 +816,10 @@ class Engine:
         cfg = self.cfg
         d = cfg.hidden
         norm_w = L.attn_norm if br == "attn" else L.ffn_norm
+        if b.pop("normed", False):
+            # the all-reduce that produced this residual already wrote the normalised rows
+            b["x8_ready"] = "x8" in b
+            return
         if cfg.hc_mult > 1:
             fn, base, scale = L.hc[br]
             native.call("tf_hc_prepare", b["x"], fn, base, scale, b["coef"], b["v"], norm_w, b["h16"],
@@ -893,7 +904,13 @@ class Engine:
         early = [l for l in cfg.index_source_layers if l < cfg.late_start]
         return early[-1] if early else -1
 
-    def _moe(self, L: LayerWeights, T: int, b: dict) -> None:
+    def _epilogue_norm(self, b: dict, w: torch.Tensor) -> dict:
+        """Boundary outputs the fused all-reduce writes from its epilogue (csrc/comm.cuh)."""
+        mx = "x8" in b
+        return dict(w=w, h16=b["h16"], hb=b["hb"], x8=b["x8"] if mx else None, x8s=b["x8s"] if mx else None,
+                    eps=self.cfg.rms_eps)
+
+    def _moe(self, L: LayerWeights, T: int, b: dict, next_norm: Optional[torch.Tensor] = None) -> None:
         cfg = self.cfg
         d, I = cfg.hidden, cfg.moe_inter
         scoring = 1 if cfg.scoring == "sqrtsoftplus" else 0
@@ -953,7 +970,7 @@ class Engine:
             return
         else:
             self._moe_large(L, T, b)
-        self._moe_finish(L, T, b, side)
+        self._moe_finish(L, T, b, side, next_norm)
 
     def _moe_mx_ok(self, T: int) -> bool:
         """Block-scaled tensor-core GEMV for the routed experts: up to 16 rows, MXFP4 experts,
@@ -976,7 +993,7 @@ class Engine:
                     b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], 1, slots,
                     min(T, 16), 0.0)
 
-    def _moe_finish(self, L: LayerWeights, T: int, b: dict, side) -> None:
+    def _moe_finish(self, L: LayerWeights, T: int, b: dict, side, next_norm: Optional[torch.Tensor] = None) -> None:
         """Join the shared-expert branch and combine (with the all-reduce when the fused kernel is up)."""
         cfg = self.cfg
         d = cfg.hidden
@@ -992,10 +1009,12 @@ class Engine:
         if self.symm is not None and T <= self.SMALL_M:
             # expert combine + shared expert + all-reduce + residual add in one kernel
             hc = cfg.hc_mult > 1
+            norm = self._epilogue_norm(b, next_norm) if (next_norm is not None and not hc) else None
             self.symm.combine_allreduce(b["y_pair"], b["ids"], b["wts"], shared, T, cfg.topk, e_lo,
                                         e_lo + self.El, None if hc else b["x"], b["delta"] if hc else None,
-                                        self.status.t)
+                                        self.status.t, norm=norm)
             b["pending"] = False
+            b["normed"] = norm is not None
             return
         if b.get("defer_combine"):
             # the next layer's boundary sums the expert outputs itself (tf_add_norm_fused)
@@ -1086,13 +1105,21 @@ class Engine:
         else:
             b["x"][:T].copy_(x_in)
         b.pop("pending_combine", None)
+        b.pop("normed", None)
         eg_layers = cfg.engram.layers if self.engram else ()
+        fuse_norm = self.symm is not None and T <= self.SMALL_M and cfg.hc_mult == 1
         for li in range(layer_lo, layer_hi):
             # decode rows on one GPU: leave the expert combine of this layer to the boundary kernel
             # of the next one (not before an Engram layer, which reads the folded residual first)
             b["defer_combine"] = (T <= self.SMALL_M and self.world == 1 and cfg.hc_mult == 1
                                   and li + 1 < layer_hi and (li + 1) not in eg_layers)
-            self._layer(li, self.layers[li], T, b, nmax, rpg, first=(li == layer_lo))
+            nxt = None
+            if fuse_norm:
+                if li + 1 < layer_hi:
+                    nxt = None if (li + 1) in eg_layers else self.layers[li + 1].attn_norm
+                elif layer_hi == len(self.layers):
+                    nxt = self.final_norm
+            self._layer(li, self.layers[li], T, b, nmax, rpg, first=(li == layer_lo), next_norm=nxt)
         b["defer_combine"] = False
         if layer_hi < len(self.layers):
             return None
@@ -1123,9 +1150,10 @@ class Engine:
             if not draft:
                 self.last_hidden = xh.mean(1).to(torch.bfloat16)
         else:
-            native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, self.final_norm,
-                        b["h16"] if draft else None,
-                        b["hb"], None, None, T, d, cfg.rms_eps)
+            if not b.pop("normed", False):
+                native.call("tf_add_norm", b["x"], b["delta"] if b.get("pending") else None, 0, d, self.final_norm,
+                            b["h16"] if draft else None,
+                            b["hb"], None, None, T, d, cfg.rms_eps)
             if not draft:
                 self.last_hidden = b["x"]
         if rows is None:
@@ -1201,8 +1229,13 @@ class Engine:
             b["pending"] = True
         b["defer_combine"] = False
         b.pop("pending_combine", None)
+        b.pop("normed", None)
+        fuse_norm = self.symm is not None and T <= self.SMALL_M and cfg.hc_mult == 1
         for j, L in enumerate(self.draft_layers):
-            self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False)
+            nxt = None
+            if fuse_norm:
+                nxt = self.draft_layers[j + 1].attn_norm if j + 1 < len(self.draft_layers) else self.final_norm
+            self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False, next_norm=nxt)
         logits = self._head(T, b, logit_rows, draft=True)
         if logits is not None and "markov_head" in ex:
             logits = logits + self._markov_bias(T, b)[logit_rows]

@@ -18,7 +18,9 @@ from ..ops import native
 
 
 class SymmWorkspace:
-    """Workspace of the one-shot all-reduce epilogue for matrices [rows <= max_rows, N]."""
+    """Workspace of the one-shot all-reduce epilogue for matrices [rows <= max_rows, N] (layout:
+    ``csrc/comm.cuh``).  ``norm`` arguments name the boundary computed in the epilogue: a dict with
+    ``w`` (RMSNorm weight) and any of ``h16``, ``hb``, ``x8``, ``x8s`` output tensors, plus ``eps``."""
 
     def __init__(self, N: int, max_rows: int = 32, device=None, group: Optional[dist.ProcessGroup] = None,
                  spin_limit: int = 2_000_000):
@@ -28,7 +30,6 @@ class SymmWorkspace:
         self.rank = dist.get_rank(self.group)
         self.N, self.max_rows, self.spin_limit = N, max_rows, spin_limit
         lib = native.lib()
-        self.flag_bytes = int(lib.tf_comm_flag_bytes(self.world, N))
         nbytes = int(lib.tf_comm_workspace_bytes(self.world, N, max_rows))
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -41,27 +42,58 @@ class SymmWorkspace:
         torch.cuda.synchronize(dev)
         dist.barrier(self.group)
 
+    @staticmethod
+    def _norm_args(norm: Optional[dict]):
+        if not norm:
+            return (None, None, None, None, None, 0.0)
+        return (norm["w"], norm.get("h16"), norm.get("hb"), norm.get("x8"), norm.get("x8s"), float(norm["eps"]))
+
     # ---- fused ops ---------------------------------------------------------------------------
     def gemv_allreduce(self, w, x16: torch.Tensor, M: int, resid: Optional[torch.Tensor],
-                       out: Optional[torch.Tensor], status: torch.Tensor) -> None:
-        """resid[:M] += all-reduce(x16[:M] @ W^T) in ONE kernel (FP8 block-128 weights)."""
+                       out: Optional[torch.Tensor], status: torch.Tensor, norm: Optional[dict] = None) -> None:
+        """resid[:M] += all-reduce(x16[:M] @ W^T), then the boundary ``norm``, in ONE kernel (FP8
+        block-128 weights)."""
         N, K = w.q.shape
         assert N == self.N
         native.call("tf_smallm_gemm_allreduce", w.q, w.s, K, K // 128, x16, x16.stride(0), N, K, M, self.peers,
-                    self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, resid, out,
+                    self.world, self.rank, self.max_rows, self.epoch, resid, out, *self._norm_args(norm),
                     self.spin_limit, status)
 
     def combine_allreduce(self, y_pair, ids, wts, shared_y, rows: int, topk: int, e_lo: int, e_hi: int,
-                          resid: Optional[torch.Tensor], out: Optional[torch.Tensor], status: torch.Tensor) -> None:
+                          resid: Optional[torch.Tensor], out: Optional[torch.Tensor], status: torch.Tensor,
+                          norm: Optional[dict] = None) -> None:
         native.call("tf_moe_combine_allreduce", y_pair, ids, wts, shared_y, rows, self.N, topk, e_lo, e_hi,
-                    self.peers, self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, resid, out,
-                    self.spin_limit, status)
+                    self.peers, self.world, self.rank, self.max_rows, self.epoch, resid, out,
+                    *self._norm_args(norm), self.spin_limit, status)
 
     def allreduce(self, x: torch.Tensor, rows: int, out: torch.Tensor, status: torch.Tensor) -> None:
-        """out[:rows] = sum over ranks of x[:rows] (fp32, rows <= max_rows, width N)."""
+        """out[:rows] = sum over ranks of x[:rows] (fp32 on the wire, rows <= max_rows, width N)."""
         native.call("tf_moe_combine_allreduce", None, None, None, x, rows, self.N, 0, 0, 0, self.peers,
-                    self.world, self.rank, self.max_rows, self.flag_bytes, self.epoch, None, out,
+                    self.world, self.rank, self.max_rows, self.epoch, None, out, *self._norm_args(None),
                     self.spin_limit, status)
+
+
+class EmulatedRanks:
+    """``world`` ranks of the one-shot all-reduce emulated on ONE GPU by a single cooperative launch
+    (every emulated rank gets its own workspace area in the same device memory).  Exercises the
+    push / poll / rank-ordered sum / boundary epilogue without a second device."""
+
+    def __init__(self, world: int, N: int, max_rows: int = 32, device="cuda", spin_limit: int = 2_000_000):
+        lib = native.lib()
+        self.world, self.N, self.max_rows, self.spin_limit = world, N, max_rows, spin_limit
+        nbytes = int(lib.tf_comm_workspace_bytes(world, N, max_rows))
+        dev = torch.device(device)
+        self.bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+        self.peers = torch.tensor([b.data_ptr() for b in self.bufs], dtype=torch.int64, device=dev)
+        self.epoch = torch.zeros(world * (N // 32), dtype=torch.int32, device=dev)
+
+    def allreduce(self, partial: torch.Tensor, rows: int, status: torch.Tensor, resid=None, out=None,
+                  norm: Optional[dict] = None) -> None:
+        """partial [world, rows_alloc, N] fp32; resid / out / norm outputs [world, rows_alloc, N]
+        (x8s [world, rows_alloc, N / 32]): every emulated rank updates its own slice."""
+        assert partial.shape[0] == self.world and partial.shape[2] == self.N and partial.is_contiguous()
+        native.call("tf_comm_allreduce_emulated", partial, rows, partial.shape[1], self.N, self.peers, self.world,
+                    self.max_rows, self.epoch, resid, out, *SymmWorkspace._norm_args(norm), self.spin_limit, status)
 
 
 class RsWorkspace:

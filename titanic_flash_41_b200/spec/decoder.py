@@ -168,7 +168,7 @@ class SpecDecoder:
             self.u1[:, 0].copy_(self.d_ud[:, j])
             self.u1[:, 1].copy_(self.d_ud[:, j])
             native.call("tf_spec_verify", lg, None, stat, None, None, self.u1, S, 0, V, V, self.temperature,
-                        self.temperature, 0, self.R1, self.w1, self.pacc, self.ptok, st)
+                        self.temperature, None, 0, self.R1, self.w1, self.pacc, self.ptok, st)
             self.props[:, j].copy_(self.ptok)
         # target verification of anchor + proposals
         self.bv["meta"].copy_(mv)
@@ -182,7 +182,7 @@ class SpecDecoder:
         native.call("tf_rowstats", logits, V, V, S * R, self.temperature, self.top_p, self.tstat, self.rs_scratch, st)
         native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
                     self.dstat if g > 0 else None, self.props if g > 0 else None, self.d_u, S, g, V, V,
-                    self.temperature, self.temperature, 0, self.Rm, self.wm, self.d_out[0], self.d_out[1], st)
+                    self.temperature, self.temperature, None, 0, self.Rm, self.wm, self.d_out[0], self.d_out[1], st)
         # hidden state of the last committed row feeds the next round's draft
         rows = self.row_of_anchor + self.d_out[0].long()
         self.hidden.copy_(e.last_hidden[rows])
