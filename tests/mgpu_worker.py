@@ -29,7 +29,7 @@ def main():
             print("[mgpu]", msg, flush=True)
     say("process group up")
     # ---- 1. one-shot all-reduce of a small fp32 matrix, many epochs back to back
-    N = 512
+    N = 1024
     ws = SymmWorkspace(N, max_rows=32, device=dev, spin_limit=2_000_000)
     say("workspace ready")
     for it, rows in enumerate([1, 5, 16, 32, 7, 7, 7, 32]):

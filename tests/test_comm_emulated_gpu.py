@@ -20,7 +20,7 @@ def _emu(world, N, max_rows=32):
 def test_plain_sum_is_exact_and_identical_on_every_rank(world):
     """fp32 transport: the result is the rank-ordered fp32 sum, bit for bit, on every emulated rank,
     over many epochs back to back (both parities, rows changing between calls)."""
-    N = 512
+    N = 1024                                    # 32 column tiles: one row owner per row up to 32 rows
     emu = _emu(world, N)
     st = native.StatusWord(DEV)
     for it, rows in enumerate([1, 5, 16, 32, 7, 7, 7, 32, 3]):

@@ -670,6 +670,11 @@ class Engine:
                                  * w.s[:, None, :, None]).view(n, kk)
         return self._dq_cache[k]
 
+    def _fused_ok(self, T: int) -> bool:
+        """The fused all-reduce kernels take decode rows: every row needs its own owner CTA among the
+        hidden / 32 column tiles."""
+        return self.symm is not None and T <= self.SMALL_M and T <= self.cfg.hidden // 32
+
     def _allreduce(self, t: torch.Tensor) -> None:
         if self.world > 1:
             self.comm.all_reduce(t)
@@ -728,7 +733,7 @@ class Engine:
                     cfg.index_topk, selcnt, self.maxC, 1.0 / math.sqrt(Dh), nsplit, b["part_o"],
                     b["part_lse"], L.sink, self.freqs, cfg.rope.dim, b["a16"], None, Hl * Dh,
                     self.status.t)
-        fused = self.symm is not None and T <= self.SMALL_M
+        fused = self._fused_ok(T)
         wo_in = b["a16"]
         if cfg.o_groups:
             # grouped low-rank output projection: block-diagonal wo_a per local head group, then wo_b
@@ -1006,7 +1011,7 @@ class Engine:
             self._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
             self._linear(b["s_act"], L.sw2, b["s_y"], T)
             shared = b["s_y"]
-        if self.symm is not None and T <= self.SMALL_M:
+        if self._fused_ok(T):
             # expert combine + shared expert + all-reduce + residual add in one kernel
             hc = cfg.hc_mult > 1
             norm = self._epilogue_norm(b, next_norm) if (next_norm is not None and not hc) else None
@@ -1084,10 +1089,13 @@ class Engine:
 
     def run(self, T: int, b: dict, nmax: int, rpg: int, logit_rows: Optional[torch.Tensor],
             layer_lo: int = 0, layer_hi: Optional[int] = None, x_in: Optional[torch.Tensor] = None,
-            x_patch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
+            x_patch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, local_logits: bool = False
+            ) -> Optional[torch.Tensor]:
         """Launch layers [layer_lo, layer_hi) on rows whose metadata already sits in ``b['meta']``
         (no host work: this is what a CUDA graph captures).  ``x_in`` replaces the embedding as
-        the input residual (late-group replay); the head runs only when the last layer does."""
+        the input residual (late-group replay); the head runs only when the last layer does.
+        ``local_logits``: return this rank's vocabulary columns [rows, vocab / world] instead of
+        gathering the full rows (the chunked sampler works on the local columns)."""
         cfg = self.cfg
         layer_hi = len(self.layers) if layer_hi is None else layer_hi
         if self.engram and b.get("eg_hash"):
@@ -1107,7 +1115,7 @@ class Engine:
         b.pop("pending_combine", None)
         b.pop("normed", None)
         eg_layers = cfg.engram.layers if self.engram else ()
-        fuse_norm = self.symm is not None and T <= self.SMALL_M and cfg.hc_mult == 1
+        fuse_norm = self._fused_ok(T) and cfg.hc_mult == 1
         for li in range(layer_lo, layer_hi):
             # decode rows on one GPU: leave the expert combine of this layer to the boundary kernel
             # of the next one (not before an Engram layer, which reads the folded residual first)
@@ -1123,7 +1131,7 @@ class Engine:
         b["defer_combine"] = False
         if layer_hi < len(self.layers):
             return None
-        return self._head(T, b, logit_rows)
+        return self._head(T, b, logit_rows, local=local_logits)
 
     def residual_rows(self, b: dict, rows: torch.Tensor) -> torch.Tensor:
         """Complete residual stream (x + pending sublayer output) of the given rows, bf16
@@ -1132,8 +1140,8 @@ class Engine:
             return b["x"][rows].clone()
         return (b["x"][rows].float() + b["delta"][rows]).to(torch.bfloat16)
 
-    def _head(self, T: int, b: dict, rows: Optional[torch.Tensor], draft: bool = False
-              ) -> Optional[torch.Tensor]:
+    def _head(self, T: int, b: dict, rows: Optional[torch.Tensor], draft: bool = False,
+              local: bool = False) -> Optional[torch.Tensor]:
         cfg = self.cfg
         d = cfg.hidden
         if cfg.hc_mult > 1:
@@ -1166,7 +1174,7 @@ class Engine:
             h16 = b["h16"][rows].contiguous()
             logits = torch.empty(h16.shape[0], Vl, dtype=torch.float32, device=self.dev)
             self._linear(h16, hw, logits, h16.shape[0])
-            return self.comm.all_gather(logits, dim=1) if self.world > 1 else logits
+            return self.comm.all_gather(logits, dim=1) if (self.world > 1 and not local) else logits
         hsel = b["hb"][rows].contiguous()
         Vl = self.head_w.shape[0]
         n = hsel.shape[0]
@@ -1175,7 +1183,7 @@ class Engine:
             m = min(self.SMALL_M, n - r0)
             native.call("tf_smallm_gemm", 2, self.head_w, None, None, None, 0, 0, d * 2, 0,
                         hsel[r0:], d, logits[r0:], Vl, 0, Vl, d, m, None, None, None, None, None, 1, 0, m, 0.0)
-        if self.world > 1:
+        if self.world > 1 and not local:
             logits = self.comm.all_gather(logits, dim=1)
         return logits
 
@@ -1202,8 +1210,8 @@ class Engine:
         return logits
 
     # -- draft head ---------------------------------------------------------------------------
-    def draft_run(self, T: int, b: dict, hidden_prev: torch.Tensor, logit_rows: Optional[torch.Tensor]
-                  ) -> Optional[torch.Tensor]:
+    def draft_run(self, T: int, b: dict, hidden_prev: torch.Tensor, logit_rows: Optional[torch.Tensor],
+                  local_logits: bool = False) -> Optional[torch.Tensor]:
         """Draft head on rows whose metadata sits in ``b['meta']``: the embedding of each row's token
         and the hidden state of the position before it are normalised, concatenated and projected
         to the model width, then run through the draft layer(s) and the FP8 copy of the vocabulary
@@ -1230,18 +1238,20 @@ class Engine:
         b["defer_combine"] = False
         b.pop("pending_combine", None)
         b.pop("normed", None)
-        fuse_norm = self.symm is not None and T <= self.SMALL_M and cfg.hc_mult == 1
+        fuse_norm = self._fused_ok(T) and cfg.hc_mult == 1
         for j, L in enumerate(self.draft_layers):
             nxt = None
             if fuse_norm:
                 nxt = self.draft_layers[j + 1].attn_norm if j + 1 < len(self.draft_layers) else self.final_norm
             self._layer(len(self.layers) + j, L, T, b, 0, 1, first=False, next_norm=nxt)
-        logits = self._head(T, b, logit_rows, draft=True)
+        if local_logits and ex.get("head_mx") is not None:
+            raise ValueError("the vocabulary-subset draft head produces full rows: no local logits")
+        logits = self._head(T, b, logit_rows, draft=True, local=local_logits)
         if logits is not None and "markov_head" in ex:
-            logits = logits + self._markov_bias(T, b)[logit_rows]
+            logits = logits + self._markov_bias(T, b, local_logits)[logit_rows]
         return logits
 
-    def _markov_bias(self, T: int, b: dict) -> torch.Tensor:
+    def _markov_bias(self, T: int, b: dict, local: bool = False) -> torch.Tensor:
         """Markov correction of the draft logits: bias[r, :] = head_m @ embed_m[token of row r], the
         token being the one the row was fed (the anchor or the previous proposal), fp32 (reference:
         src/dspark_markov.rs:886-971; kernels/core.cu:1110 ca_dspark_markov_embed, :1118
@@ -1258,4 +1268,4 @@ class Engine:
             m = min(self.SMALL_M, T - r0)
             native.call("tf_smallm_gemm", 2, hm, None, None, None, 0, 0, r * 2, 0, b["mk_lat"][r0:], r,
                         b["mk_bias"][r0:], Vl, 0, Vl, r, m, None, None, None, None, None, 1, 0, m, 0.0)
-        return self.comm.all_gather(b["mk_bias"], dim=1) if self.world > 1 else b["mk_bias"]
+        return self.comm.all_gather(b["mk_bias"], dim=1) if (self.world > 1 and not local) else b["mk_bias"]

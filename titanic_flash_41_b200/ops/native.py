@@ -112,7 +112,7 @@ def _conv(a, kind: str):
 
 
 # kernels launched per exported call (for launch accounting); default 1
-_KERNELS_PER_CALL = {"tf_sparse_attention": 2, "tf_router": 2, "tf_spec_verify": 2, "tf_rowstats": 7,
+_KERNELS_PER_CALL = {"tf_sparse_attention": 2, "tf_router": 2, "tf_spec_verify": 2, "tf_rowstats": 7, "tf_rowstats_per_session": 7,
                      "tf_moe_plan": 3}
 LAUNCHES = [0]
 

@@ -96,6 +96,67 @@ class EmulatedRanks:
                     self.max_rows, self.epoch, resid, out, *SymmWorkspace._norm_args(norm), self.spin_limit, status)
 
 
+class SampleWorkspace:
+    """Exchange area and call counters of the chunked sampler (``csrc/sample_chunks.cu``): one
+    launch computes the row statistics and the block verification (or a plain draw) of up to
+    ``max_rows`` rows from this rank's columns of the logits.  With ``world > 1`` the area is
+    symmetric memory and construction is collective; ``emulate > 1`` places that many ranks on this
+    GPU (tests on one device)."""
+
+    def __init__(self, V: int, max_rows: int, device, world: int = 1, rank: int = 0,
+                 group: Optional[dist.ProcessGroup] = None, emulate: int = 1, spin_limit: int = 4_000_000):
+        lib = native.lib()
+        self.V, self.max_rows, self.spin_limit = V, max_rows, spin_limit
+        self.P = int(lib.tf_sample_chunks_count(V))
+        if self.P == 0:
+            raise ValueError(f"a vocabulary of {V} cannot be chunked for rank-local sampling")
+        self.emulate = emulate
+        self.world = emulate if emulate > 1 else world
+        self.rank = 0 if emulate > 1 else rank
+        if self.P % self.world:
+            raise ValueError(f"{self.P} chunks do not split over {self.world} ranks")
+        self.csplit = self.P // self.world
+        self.Vl = V // self.world
+        nbytes = int(lib.tf_sample_chunks_workspace_bytes(V, max_rows))
+        dev = torch.device(device)
+        if emulate > 1:
+            self.bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(emulate)]
+            ptrs = [b.data_ptr() for b in self.bufs]
+        elif world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.group = group or dist.group.WORLD
+            self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+            self.buf.zero_()
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+            ptrs = [self.buf.data_ptr()]
+        self.peers = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+        self.ctr = torch.zeros(max(emulate, 1) * max_rows * self.csplit, dtype=torch.int32, device=dev)
+        if world > 1 and emulate <= 1:
+            torch.cuda.synchronize(dev)
+            dist.barrier(self.group)
+
+    @staticmethod
+    def usable(V: int, rows: int, world: int, device) -> bool:
+        """Whether ``rows`` rows of a ``V``-token vocabulary can be sampled by the chunked kernel on
+        ``world`` ranks: V must chunk, and the (row, local chunk) CTAs of a GPU must all be resident."""
+        P = int(native.lib().tf_sample_chunks_count(V))
+        if P == 0 or P % world:
+            return False
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        return rows * (P // world) <= sms
+
+    def sample(self, tlogits, dlogits, dstat, proposals, uniforms, u_stride: int, sess_temp, sess_top_p, S: int,
+               g: int, ldl: int, tstat, stat_stride: int, n_accept, next_token, tok_stride: int, status,
+               point_mass: bool = False, emu_strides=(0, 0, 0, 0, 0)) -> None:
+        native.call("tf_sample_chunks", tlogits, dlogits, dstat, proposals, uniforms, u_stride, sess_temp, sess_top_p,
+                    S, g, self.V, ldl, 1 if point_mass else 0, tstat, stat_stride, n_accept, next_token, tok_stride,
+                    self.peers, self.world, self.rank, self.max_rows, self.ctr, self.spin_limit, status,
+                    self.emulate, *emu_strides)
+
+
 class RsWorkspace:
     """Workspace of the GEMM -> reduce-scatter kernel for partial products [M, N] (bf16 transport)."""
 

@@ -152,8 +152,8 @@ class EngineBackend:
         self.device = engine.dev
         if engine.big_gemm is None:
             bigpath.attach(engine)
-        self._dec: Dict[Tuple[int, float, float], object] = {}
-        self.max_graph_variants = 8      # (sessions, temperature, top-p) decoders kept with their CUDA graphs
+        self._dec: Dict[int, object] = {}
+        self.max_graph_variants = 8      # decoders (one per batch size) kept with their CUDA graphs
         self._SpecDecoder, self._native = SpecDecoder, native
         self.last_hidden_rows: Dict[int, torch.Tensor] = {}
 
@@ -178,11 +178,12 @@ class EngineBackend:
         return verify.sample_from(p, rng.uniform(rng.block_round_seed(seed, position), rng.TARGET_DOMAIN, position))
 
     def decode_step(self, slots):
-        key = (len(slots), slots[0].temperature, slots[0].top_p)
+        # one decoder (and one captured graph) per batch size: every conversation's temperature and
+        # top-p travel with the step metadata, so mixed settings share the launch
+        key = len(slots)
         dec = self._dec.pop(key, None)
         if dec is None:
-            dec = self._SpecDecoder(self.e, len(slots), temperature=max(slots[0].temperature, 1e-3),
-                                    top_p=slots[0].top_p)
+            dec = self._SpecDecoder(self.e, len(slots))
             # bounded retention of captured graph variants (least recently used goes first)
             while len(self._dec) >= self.max_graph_variants:
                 self._dec.pop(next(iter(self._dec)))

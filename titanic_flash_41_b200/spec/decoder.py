@@ -8,8 +8,15 @@ emits one more token, and the committed length advances by ``accepted + 1``.  Re
 no rollback: all state is position-addressed.
 
 The whole device side of a step is captured in ONE CUDA graph per (conversations, depth)
-profile; per step the host uploads a small metadata block (positions, regions, uniforms),
-replays the graph and reads back (accepted, next token) per conversation.
+profile; per step the host uploads a small metadata block (positions, regions, uniforms, each
+conversation's temperature and top-p), replays the graph and reads back (accepted, next token)
+per conversation.  Conversations with different sampling settings share the launch and the graph.
+
+Sampling and verification run on each rank's own vocabulary columns (``csrc/sample_chunks.cu``:
+one launch per draft proposal and one for the verification; the ranks exchange only maxima, mass
+histograms, chunk masses and the chosen token), so no logits are gathered and a step contains no
+NCCL call.  Vocabularies that do not chunk fall back to gathered rows and the full-row kernels of
+``csrc/sampling.cu``.
 """
 from __future__ import annotations
 
@@ -64,6 +71,9 @@ def step_meta(regions: Sequence[int], lengths: Sequence[int], anchors: Sequence[
 
 
 class SpecDecoder:
+    """``temperature`` / ``top_p`` are kept for callers that name them; the settings that count are
+    the ones each ``DecodeSlot`` carries (uploaded per step)."""
+
     def __init__(self, engine: Engine, n_slots: int, depth: Optional[int] = None,
                  temperature: float = 0.6, top_p: float = 0.95, use_graph: bool = True):
         self.e = engine
@@ -99,7 +109,15 @@ class SpecDecoder:
         self.d_out = torch.zeros(2 + g, S, **i32)
         self.hidden = torch.zeros(S, cfg.hidden, dtype=torch.bfloat16, device=dev)   # target hidden at length-1
         self.dhid = torch.zeros(S, cfg.hidden, dtype=torch.bfloat16, device=dev)
-        self.dlogits = torch.zeros(S, max(g, 1), V, dtype=torch.float32, device=dev)
+        from ..parallel.symm import SampleWorkspace
+        self.ws = None
+        if SampleWorkspace.usable(V, S * self.R, engine.world, dev) and not engine.draft_extra.get("head_mx"):
+            self.ws = SampleWorkspace(V, S * self.R, dev, world=engine.world, rank=engine.rank)
+        self.Vl = V // engine.world if self.ws is not None else V
+        # per-conversation sampling settings: [temperature | top-p], uploaded with the step metadata
+        self.h_f = torch.zeros(2, S, dtype=torch.float32).pin_memory()
+        self.d_f = torch.zeros_like(self.h_f, device=dev)
+        self.dlogits = torch.zeros(S, max(g, 1), self.Vl, dtype=torch.float32, device=dev)
         self.dstat = torch.zeros(S, max(g, 1), sb, dtype=torch.uint8, device=dev)
         self.tstat = torch.zeros(S, self.R, sb, dtype=torch.uint8, device=dev)
         self.props = torch.zeros(S, max(g, 1), **i32)
@@ -134,8 +152,11 @@ class SpecDecoder:
         if self.n_eg:
             o = self.n_meta_v + g * self.n_meta_d
             hi[o: o + self.n_eg] = StepPlan.recent_rows(cfg, [(R, s.recent) for s in slots]).reshape(-1)
+        hf = self.h_f.numpy()
         hu = self.h_u.numpy()
         for i, s in enumerate(slots):
+            hf[0, i] = max(float(s.temperature), 1e-3)      # temperature 0 (greedy) = a very sharp law
+            hf[1, i] = min(max(float(s.top_p), 1e-6), 1.0)
             dr, ac, fin = rng.round_uniforms(s.seed, s.length, g)
             hu[i, :g] = ac
             hu[i, g] = fin
@@ -151,24 +172,34 @@ class SpecDecoder:
         st = e.status.t
         mv = self.d_int[: self.n_meta_v].view(StepPlan.META_ROWS, S * R)
         hid = self.hidden
+        ws = self.ws
+        local = ws is not None
+        temp, topp = self.d_f[0], self.d_f[1]
+        gs = max(g, 1)
         for j in range(g):
             o = self.n_meta_v + j * self.n_meta_d
             md = self.d_int[o: o + self.n_meta_d].view(StepPlan.META_ROWS, S)
             self.bd["meta"].copy_(md)
             if j > 0:
                 self.bd["meta"][0].copy_(self.props[:, j - 1])
-            lg = e.draft_run(S, self.bd, hid, self.rows_d)
+            lg = e.draft_run(S, self.bd, hid, self.rows_d, local_logits=local)
             self.dlogits[:, j].copy_(lg)
             hid = self.dhid
             hid.copy_(self.bd["x"])
             # sample proposal j from the modified draft law
+            if local:
+                # one launch: statistics of the row (kept for the verification) + the draw, on this
+                # rank's columns; writes props[:, j] and dstat[:, j] in place
+                ws.sample(lg, None, None, None, self.d_ud[:, j:], gs, temp, topp, S, 0, lg.stride(0),
+                          self.dstat[:, j], gs, None, self.props[:, j:], gs, st)
+                continue
             stat = self.dstat[:, j].contiguous()
-            native.call("tf_rowstats", lg, V, V, S, self.temperature, self.top_p, stat, self.rs_scratch, st)
+            native.call("tf_rowstats_per_session", lg, V, V, S, temp, topp, 1, stat, self.rs_scratch, st)
             self.dstat[:, j].copy_(stat)
             self.u1[:, 0].copy_(self.d_ud[:, j])
             self.u1[:, 1].copy_(self.d_ud[:, j])
-            native.call("tf_spec_verify", lg, None, stat, None, None, self.u1, S, 0, V, V, self.temperature,
-                        self.temperature, None, 0, self.R1, self.w1, self.pacc, self.ptok, st)
+            native.call("tf_spec_verify", lg, None, stat, None, None, self.u1, S, 0, V, V, 1.0, 1.0, temp, 0,
+                        self.R1, self.w1, self.pacc, self.ptok, st)
             self.props[:, j].copy_(self.ptok)
         # target verification of anchor + proposals
         self.bv["meta"].copy_(mv)
@@ -178,11 +209,16 @@ class SpecDecoder:
         if g > 0:
             tok = self.bv["meta"][0].view(S, R)
             tok[:, 1:].copy_(self.props[:, :g])
-        logits = e.run(S * R, self.bv, nmax, R if R <= 32 else 1, self.rows_all)
-        native.call("tf_rowstats", logits, V, V, S * R, self.temperature, self.top_p, self.tstat, self.rs_scratch, st)
-        native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
-                    self.dstat if g > 0 else None, self.props if g > 0 else None, self.d_u, S, g, V, V,
-                    self.temperature, self.temperature, None, 0, self.Rm, self.wm, self.d_out[0], self.d_out[1], st)
+        logits = e.run(S * R, self.bv, nmax, R if R <= 32 else 1, self.rows_all, local_logits=local)
+        if local:
+            ws.sample(logits, self.dlogits if g > 0 else None, self.dstat if g > 0 else None,
+                      self.props if g > 0 else None, self.d_u, g + 2, temp, topp, S, g, logits.stride(0),
+                      self.tstat, 1, self.d_out[0], self.d_out[1], 1, st)
+        else:
+            native.call("tf_rowstats_per_session", logits, V, V, S * R, temp, topp, R, self.tstat, self.rs_scratch, st)
+            native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
+                        self.dstat if g > 0 else None, self.props if g > 0 else None, self.d_u, S, g, V, V,
+                        1.0, 1.0, temp, 0, self.Rm, self.wm, self.d_out[0], self.d_out[1], st)
         # hidden state of the last committed row feeds the next round's draft
         rows = self.row_of_anchor + self.d_out[0].long()
         self.hidden.copy_(e.last_hidden[rows])
@@ -197,6 +233,7 @@ class SpecDecoder:
         self.d_int.copy_(self.h_int, non_blocking=True)
         self.d_u.copy_(self.h_u, non_blocking=True)
         self.d_ud.copy_(self.h_ud, non_blocking=True)
+        self.d_f.copy_(self.h_f, non_blocking=True)
         if self.use_graph:
             if self.graph is None or bucket != self.nmax_bucket:
                 self.nmax_bucket = bucket
@@ -235,7 +272,7 @@ class SpecDecoder:
 
     @property
     def h2d_bytes_per_step(self) -> int:
-        return self.h_int.numel() * 4 + self.h_u.numel() * 8 + self.h_ud.numel() * 8
+        return self.h_int.numel() * 4 + self.h_u.numel() * 8 + self.h_ud.numel() * 8 + self.h_f.numel() * 4
 
     @property
     def d2h_bytes_per_step(self) -> int:
@@ -247,6 +284,7 @@ class SpecDecoder:
         self.d_int.copy_(self.h_int)
         self.d_u.copy_(self.h_u)
         self.d_ud.copy_(self.h_ud)
+        self.d_f.copy_(self.h_f)
         n0 = native.LAUNCHES[0]
         self._device_step(max(self.nmax_bucket, 4096))
         torch.cuda.synchronize()
