@@ -167,3 +167,91 @@ def test_worker_hands_the_tokens_before_each_prefilled_part_to_backends_that_wan
     _drain(w)
     assert seen and all(prev == follow[max(0, start - 8):start] for start, _, prev in seen)
     assert min(start for start, _, _ in seen) >= 64            # the restored prefix was not prefilled again
+
+
+def test_two_ranks_follow_rank0_prefill_directives_despite_clock_skew_and_local_cancel():
+    """Tensor-parallel serving: whether a prefill chunk is followed by an interleaved decode step, or
+    the prefill stops because the request was cancelled, is rank 0's decision, broadcast per chunk.
+    Rank 1 has a clock that never advances and no job table; it must still take exactly the same
+    steps (the agreement after every command would poison the channel otherwise)."""
+    import socket
+
+    from titanic_flash_41_b200.parallel.control import ControlChannel
+    from titanic_flash_41_b200.serve import worker as WK
+
+    cfg = tiny_config()
+    W = oracle.init_weights(cfg, 0)
+    srv = socket.create_server(("127.0.0.1", 0))
+    port = srv.getsockname()[1]
+    sched = Scheduler(2, 4, 2)
+    ev = []
+    workers, errors = [None, None], [None, None]
+    ticks = {"n": 0}
+    jobs = {}
+
+    def fast_clock():                      # rank 0: every look at the clock is a second later
+        ticks["n"] += 1
+        if "b" in jobs and ticks["n"] >= jobs["b_cancel_at"]:
+            jobs["b"].cancelled.set()       # the client of request b goes away mid-prefill (seen by rank 0 only)
+        return float(ticks["n"])
+
+    def run(rank):
+        try:
+            ch = ControlChannel.connect(rank, 2, "127.0.0.1", port, b"t", 20.0, srv if rank == 0 else None)
+            b = OracleBackend(cfg, W, regions=2, max_context=512, chunk=32)
+            w = Worker(b, sched if rank == 0 else None, SessionCache(slots=8, budget_bytes=1 << 30), eos_id=1,
+                       control=ch, rank=rank, prefill_slice_s=0.5, checkpoint_min=512, checkpoint_align=512)
+            w.clock = fast_clock if rank == 0 else (lambda: 0.0)
+            workers[rank] = w
+            w._pending = []
+            while w.running:
+                w.run_once(0.0)
+        except Exception as e:  # noqa: BLE001
+            errors[rank] = e
+
+    g = torch.Generator().manual_seed(4)
+    sched.submit(_job("a", torch.randint(3, cfg.vocab, (40,), generator=g).tolist(), 60, ev, temperature=0.0))
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for t in ts:
+        t.start()
+    # wait until a decodes, then submit a long prompt b that will be cancelled on rank 0 during prefill
+    import time as _t
+    t0 = _t.time()
+    while not any(j == "a" and k == "tokens" for j, k, p in ev) and _t.time() - t0 < 30:
+        _t.sleep(0.01)
+    jb = _job("b", torch.randint(3, cfg.vocab, (230,), generator=g).tolist(), 8, ev, temperature=0.0)
+    jobs["b_cancel_at"] = 10 ** 9
+    jobs["b"] = jb
+    sched.submit(jb)
+    t0 = _t.time()
+    while not workers[0].directives and _t.time() - t0 < 30:
+        _t.sleep(0.005)
+    jobs["b_cancel_at"] = ticks["n"] + 6          # a few chunks later
+    t0 = _t.time()
+    while not any(j == "a" and k == "done" for j, k, p in ev) and _t.time() - t0 < 60:
+        _t.sleep(0.01)
+    sched.close()
+    for t in ts:
+        t.join(30)
+    srv.close()
+    assert errors == [None, None], errors
+    d0, d1 = workers[0].directives, workers[1].directives
+    assert d0 == d1 and len(d0) >= 3
+    assert WK.D_STEP in d0                         # rank 0's clock forced interleaved steps; rank 1 followed
+    assert d0[-1] == WK.D_CANCEL                   # and the cancellation seen by rank 0 only
+    assert any(j == "b" and k == "error" and p["code"] == "cancelled" for j, k, p in ev)
+    assert not any(j == "b" and k == "tokens" for j, k, p in ev)
+    assert any(j == "a" and k == "done" for j, k, p in ev)
+
+
+def test_job_cancelled_while_queued_gets_a_terminal_event():
+    s = Scheduler(1, 4, 2)
+    ev = []
+    a, b = _job("a", [5] * 8, 4, ev), _job("b", [6] * 8, 4, ev)
+    s.submit(a)
+    s.submit(b)
+    assert s.admit() == [a]
+    b.cancelled.set()
+    s.release(a)
+    assert s.admit() == []
+    assert ("b", "error", {"code": "cancelled", "message": "cancelled while queued"}) in ev

@@ -88,17 +88,29 @@ class Scheduler:
                 job = None
                 while self.fg and job is None:
                     j = self.fg.popleft()
-                    job = None if j.cancelled.is_set() else j
+                    job = None if self._dropped(j) else j
                 if job is None and now >= self.hold_background_until:
                     while self.bg and job is None:
                         j = self.bg.popleft()
-                        job = None if j.cancelled.is_set() else j
+                        job = None if self._dropped(j) else j
                 if job is None:
                     break
                 job.region = r
                 self.active[r] = job
                 out.append(job)
         return out
+
+    @staticmethod
+    def _dropped(j: Job) -> bool:
+        """A job cancelled while it waited never reaches a region; its HTTP handler still gets a
+        terminal event, so it does not wait forever."""
+        if not j.cancelled.is_set():
+            return False
+        try:
+            j.emit("error", {"code": "cancelled", "message": "cancelled while queued"})
+        except Exception:  # noqa: BLE001  (a dead client must not stop admission)
+            pass
+        return True
 
     def release(self, job: Job) -> None:
         with self.lock:

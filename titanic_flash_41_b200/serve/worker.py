@@ -7,7 +7,11 @@ execute, :6115 run_http loop, :2559 agree_progress).
 
 Begin   restore the best cached image whose prefix the prompt starts with, prefill the rest in
         chunks (saving prompt checkpoints on the way; other conversations take a batched decode
-        step when a prefill slice runs long), sample the first token
+        step when a prefill slice runs long), sample the first token.  What happens after each
+        chunk -- continue, interleave a decode step, or stop because the request was cancelled --
+        is decided by rank 0 alone (its clock, its view of the job) and broadcast as a one-byte
+        directive; the other ranks never consult their own clock or job table (reference:
+        should_cancel -> PrefillDirective through the control channel, src/resident_worker.rs:4009)
 Step    one batched speculative verification round for every decoding conversation
 Finish  save the completed turn into the session cache and free the region
 Idle    one unit of background cache work (tier moves)
@@ -39,6 +43,10 @@ class Active:
     finished: Optional[str] = None
 
 
+# per-chunk prefill directives (rank 0 decides, every rank follows)
+D_CONTINUE, D_STEP, D_CANCEL = 0, 1, 2
+
+
 class Worker:
     def __init__(self, backend, scheduler: Optional[Scheduler], cache: Optional[SessionCache] = None,
                  eos_id: int = 1, log: Optional[EventLog] = None, control=None, rank: int = 0,
@@ -51,6 +59,8 @@ class Worker:
         self.jobs: Dict[str, Job] = {}
         self.running = True
         self.requests = 0
+        self.clock = time.monotonic          # rank 0's time source for prefill slices (tests skew it)
+        self.directives: List[int] = []      # per-chunk directives this rank followed (diagnostics)
 
     # ---------------------------------------------------------------- command codec
     @staticmethod
@@ -132,6 +142,27 @@ class Worker:
         elif op == "shutdown":
             self.running = False
 
+    def _chunk_directive(self, job: Optional[Job], last_slice: float) -> int:
+        """What to do after a prefill chunk.  Rank 0 decides from its own clock and job state and
+        broadcasts the decision; every other rank receives it, so all ranks leave the prefill, or
+        interleave a decode step, at the same chunk."""
+        if self.rank == 0:
+            if job is not None and job.cancelled.is_set():
+                d = D_CANCEL
+            elif self.active and self.clock() - last_slice > self.slice_s:
+                d = D_STEP
+            else:
+                d = D_CONTINUE
+            if self.control is not None and self.control.world > 1:
+                self.control.command(bytes([d]))
+        else:
+            raw = self.control.command(None)
+            if len(raw) != 1 or raw[0] not in (D_CONTINUE, D_STEP, D_CANCEL):
+                raise RuntimeError("malformed prefill directive")
+            d = raw[0]
+        self.directives.append(d)
+        return d
+
     def _emit(self, job: Optional[Job], kind: str, payload: Any) -> None:
         if job is not None and self.rank == 0:
             job.emit(kind, payload)
@@ -164,7 +195,7 @@ class Worker:
         if shared is not None:
             cks = sorted(set(cks + [shared]))
         logits, pos = None, start
-        last_slice = time.monotonic()
+        last_slice = self.clock()
         for stop in cks + [len(prompt)]:
             if stop <= pos:
                 continue
@@ -172,10 +203,11 @@ class Worker:
             def on_chunk(done, _base=pos):
                 nonlocal last_slice
                 # a long prefill lets the decoding conversations take one batched step per slice
-                if self.active and time.monotonic() - last_slice > self.slice_s:
+                d = self._chunk_directive(job, last_slice)
+                if d == D_STEP:
                     self._step()
-                    last_slice = time.monotonic()
-                return not (job is not None and job.cancelled.is_set())
+                    last_slice = self.clock()
+                return d != D_CANCEL
             if getattr(self.b, "wants_prev", False):
                 # n-gram memory layers hash across the seam between reused and new tokens
                 logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk, prev=prompt[max(0, pos - 8):pos])
