@@ -403,7 +403,7 @@ def test_draft_head_with_markov_correction_matches_oracle():
     cfg = small_config(draft=DraftConfig(layers=1, depth=3, markov_rank=256))
     plain = small_config(draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
-    assert W["mtp.markov_head.head.weight"].shape == (cfg.vocab, 256)
+    assert W["mtp.0.markov_head.head.weight"].shape == (cfg.vocab, 256)
     rt = {}
     ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
@@ -434,8 +434,8 @@ def test_draft_head_with_markov_correction_matches_oracle():
     err = _row_err(got, want)
     assert err.median() < 0.1, err
     # the correction is exactly the bigram term
-    bias = (W["mtp.markov_head.embed.weight"][toks].bfloat16().float()
-            @ W["mtp.markov_head.head.weight"].bfloat16().float().t())
+    bias = (W["mtp.0.markov_head.embed.weight"][toks].bfloat16().float()
+            @ W["mtp.0.markov_head.head.weight"].bfloat16().float().t())
     assert (got - got_plain - bias).abs().max() <= 2e-3 * bias.abs().max() + 1e-3
     assert bias.abs().max() > 0.5
 

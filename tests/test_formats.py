@@ -115,3 +115,76 @@ def test_export_and_reload_matches_oracle_weights(tmp_path):
         assert torch.equal(ck.read(k).view(torch.uint8), ck2.read(k).view(torch.uint8)), k
     W3 = loader.checkpoint_weights(ck2, cfg)        # FP4 group scales may renormalise; the values may not move
     assert torch.equal(W3["layers.1.ffn.experts.w1.weight"], W2["layers.1.ffn.experts.w1.weight"])
+
+
+def test_reference_tensor_names_validate_and_shard(tmp_path):
+    """A header-only checkpoint with the reference's names for the parts that have their own naming
+    rules (src/layout.rs:86, :275-292, :362): the Markov head of the LAST draft stage, the Engram
+    row store as MXFP8 weight + scale, the image-token selection bias.  It must validate, and the
+    rank plan must split vocabulary rows / Engram rows while the Markov latents stay whole."""
+    from titanic_flash_41_b200.config import DraftConfig, EngramConfig
+    cfg = tiny_config(n_layers=2, hidden=256, n_experts=4, moe_inter=128, shared_inter=256, vocab=512,
+                      dense_quant="fp8_ue8m0_32", expert_quant="mxfp4", router_bias=True, router_bias_vl=True,
+                      image_token=500, draft=DraftConfig(layers=3, depth=3, markov_rank=32),
+                      engram=EngramConfig(layers=(1,), tables=1, rows_per_table=40))
+    names = {n: (dt, sh) for n, dt, sh in layout.expected_tensors(cfg)}
+    for want in ("mtp.2.markov_head.embed.weight", "mtp.2.markov_head.head.weight", "layers.1.engram.embed.weight",
+                 "layers.1.engram.embed.scale", "layers.1.engram.wkv.weight", "layers.1.engram.wkv.scale",
+                 "layers.1.engram.q_weight", "layers.0.ffn.gate.bias_vl", "layers.1.ffn.gate.bias_vl"):
+        assert want in names, want
+    assert "mtp.markov_head.head.weight" not in names and "mtp.0.ffn.gate.bias_vl" not in names
+    assert names["layers.1.engram.embed.weight"][0] == "F8_E4M3" and names["layers.1.engram.embed.weight"][1][1] == 256
+    assert names["layers.1.engram.embed.scale"] == ("F8_E8M0", (names["layers.1.engram.embed.weight"][1][0], 8))
+    assert names["layers.0.attn.wkv.scale"][0] == "F8_E8M0"              # 32 x 32 UE8M0 dense scales
+    # header-only file: every tensor of the contract with its dtype and shape, zero-filled payload
+    header, off = {}, 0
+    esize = {"BF16": 2, "F32": 4, "F8_E4M3": 1, "F8_E8M0": 1, "I8": 1, "I64": 8}
+    for n, (dt, sh) in names.items():
+        nb = esize[dt]
+        for v in sh:
+            nb *= v
+        header[n] = {"dtype": dt, "shape": list(sh), "data_offsets": [off, off + nb]}
+        off += nb
+    hb = json.dumps(header).encode()
+    hb += b" " * ((8 - len(hb) % 8) % 8)
+    with open(os.path.join(str(tmp_path), "model-00001.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hb)) + hb)
+        f.truncate(8 + len(hb) + off)
+    ck = Checkpoint.scan(str(tmp_path))
+    layout.validate_checkpoint(ck, cfg)
+    plan = layout.RankPlan.build(ck, cfg, 1, 2, "ep").entries
+    head = plan["mtp.2.markov_head.head.weight"]
+    assert (head.kind, head.axis, head.start, head.length) == ("shard", 0, 256, 256)
+    assert plan["mtp.2.markov_head.embed.weight"].kind == "replicated"
+    rows = names["layers.1.engram.embed.weight"][1][0]
+    eg = plan["layers.1.engram.embed.weight"]
+    assert eg.kind == "shard" and eg.start == rows // 2 and eg.start + eg.length == rows
+    assert plan["layers.1.engram.embed.scale"].start == eg.start
+    assert plan["layers.1.engram.wkv.weight"].kind == "shard" and plan["layers.0.ffn.gate.bias_vl"].kind == "replicated"
+    # a checkpoint with the unqualified name is refused
+    header["mtp.markov_head.head.weight"] = header.pop("mtp.2.markov_head.head.weight")
+    os.remove(os.path.join(str(tmp_path), "model-00001.safetensors"))
+    hb = json.dumps(header).encode()
+    hb += b" " * ((8 - len(hb) % 8) % 8)
+    with open(os.path.join(str(tmp_path), "model-00001.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hb)) + hb)
+        f.truncate(8 + len(hb) + off)
+    with pytest.raises(CheckpointError):
+        layout.validate_checkpoint(Checkpoint.scan(str(tmp_path)), cfg)
+
+
+def test_image_rows_select_experts_with_the_vl_bias():
+    from titanic_flash_41_b200.models import oracle
+    cfg = tiny_config(router_bias=True, router_bias_vl=True, image_token=7, scoring="sqrtsoftplus")
+    logits = torch.randn(5, cfg.n_experts)
+    bias = torch.zeros(cfg.n_experts)
+    bias_vl = torch.zeros(cfg.n_experts)
+    bias_vl[3] = 100.0                                             # image rows must pick expert 3 first
+    img = torch.tensor([False, True, False, True, False])
+    ids, wts = oracle.route(logits, cfg, bias, bias_vl, img)
+    plain, wplain = oracle.route(logits, cfg, bias)
+    assert ids[1, 0] == 3 and ids[3, 0] == 3
+    assert torch.equal(ids[[0, 2, 4]], plain[[0, 2, 4]]) and torch.equal(wts[[0, 2, 4]], wplain[[0, 2, 4]])
+    # weights stay the UNBIASED scores of the winners
+    sp = torch.sqrt(torch.log1p(torch.exp(logits[1])))
+    assert torch.allclose(wts[1] / wts[1].sum(), sp[ids[1]] / sp[ids[1]].sum(), atol=1e-6)

@@ -143,7 +143,7 @@ def test_router_matches_oracle():
     logits = torch.zeros(T, Ex, device=DEV)
     ids = torch.zeros(T, k, device=DEV, dtype=torch.int32)
     wts = torch.zeros(T, k, device=DEV)
-    native.call("tf_router", h, gate, bias, logits, ids, wts, T, Ex, d, k, 1, 1, 1.5)
+    native.call("tf_router", h, gate, bias, None, None, -1, logits, ids, wts, T, Ex, d, k, 1, 1, 1.5)
     ref_logits = h.float() @ gate.float().t()
     assert _rel(logits, ref_logits) < 1e-4
     rid, rw = route(logits.cpu(), cfg, bias.cpu())
@@ -485,10 +485,10 @@ def test_router_topk_group_equals_the_two_launches(M):
         ids, wts = i32(M, k), torch.zeros(M, k, device=DEV)
         ge, gs, gc, ng, sp, nl = i32(El), i32(El), i32(El), i32(1), i32(M * k), i32(1)
         if fused:
-            native.call("tf_router_topk_group", logits, bias, ids, wts, M, E_, k, 1, 1, 1.5, e_lo, e_lo + El,
+            native.call("tf_router_topk_group", logits, bias, None, None, -1, ids, wts, M, E_, k, 1, 1, 1.5, e_lo, e_lo + El,
                         ge, gs, gc, ng, sp, nl)
         else:
-            native.call("tf_router_topk", logits, bias, ids, wts, M, E_, k, 1, 1, 1.5)
+            native.call("tf_router_topk", logits, bias, None, None, -1, ids, wts, M, E_, k, 1, 1, 1.5)
             native.call("tf_route_group", ids, M * k, e_lo, e_lo + El, ge, gs, gc, ng, sp, nl)
         torch.cuda.synchronize()
         n, g = int(nl), int(ng)

@@ -142,6 +142,8 @@ class ModelConfig(_JsonMixin):
     shared_inter: int = 512
     scoring: str = "softmax"           # "softmax" | "sqrtsoftplus"
     router_bias: bool = False
+    router_bias_vl: bool = False       # image-token rows select experts with gate.bias_vl instead of gate.bias
+    image_token: int = -1              # token id of image placeholder rows (reference: 129264)
     renorm: bool = True
     route_scale: float = 1.0
     swiglu_limit: float = 0.0          # 0 = no clamp

@@ -368,7 +368,14 @@ __global__ void router_logits_kernel(const __half* __restrict__ h, const __nv_bf
 
 // top-k per row (one warp per row) + weights.  scoring 0 = softmax, 1 = sqrtsoftplus.
 // Ties go to the lowest expert id; NaN keys count as +inf.
-__device__ __forceinline__ void router_topk_rows(const float* __restrict__ logits, const float* __restrict__ bias,
+// The selection bias is chosen per row: rows whose token is `image_token` use bias_vl (when given).
+struct RouterBias {
+  const float* bias;
+  const float* bias_vl;
+  const int* tokens;
+  int image_token;
+};
+__device__ __forceinline__ void router_topk_rows(const float* __restrict__ logits, const RouterBias rb,
                                                  int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
                                                  int scoring, int renorm, float scale, float* sc, int row0) {
   // sc: [warps][2][E] floats of shared memory; warp w serves row row0 + w
@@ -378,6 +385,7 @@ __device__ __forceinline__ void router_topk_rows(const float* __restrict__ logit
   float* score = sc + (long)warp * 2 * E;
   float* key = score + E;
   const float* lg = logits + (long)r * E;
+  const float* bias = (rb.bias_vl && rb.tokens && rb.tokens[r] == rb.image_token) ? rb.bias_vl : rb.bias;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
   mx = warp_max(mx);
@@ -438,7 +446,7 @@ __device__ __forceinline__ void router_topk_rows(const float* __restrict__ logit
   }
 }
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+__global__ void router_topk_kernel(const float* __restrict__ logits, const RouterBias bias,
                                    int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
                                    int scoring, int renorm, float scale) {
   extern __shared__ float sc[];                       // [warps][2][E]
@@ -515,7 +523,7 @@ __global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int
 // Decode rows: top-k of every row (one warp each, 16 rows per pass) and the grouping of the
 // resulting pairs in ONE single-CTA launch.
 __global__ void __launch_bounds__(512) router_topk_group_kernel(
-    const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ wts,
+    const float* __restrict__ logits, const RouterBias bias, int* __restrict__ ids, float* __restrict__ wts,
     int M, int E, int topk, int scoring, int renorm, float scale, int e_lo, int e_hi, int* group_expert,
     int* group_start, int* group_count, int* n_groups, int* sorted_pairs, int* n_local_pairs) {
   extern __shared__ float fsm[];                       // [16][2][E] floats, reused as ints by the grouping
@@ -592,35 +600,42 @@ TF_API int tf_attn_prep(const void* P, int p_kind, int ldp, int T, const int* po
   return (int)cudaGetLastError();
 }
 
-TF_API int tf_router(const void* h16, const void* gate, const float* bias, float* logits, int* ids,
-                     float* wts, int M, int E, int d, int topk, int scoring, int renorm, float scale,
-                     cudaStream_t st) {
+// bias_vl / tokens / image_token (all optional): rows whose token is the image token are selected
+// with bias_vl (reference: kernels/moe_frontend.cuh:140).
+TF_API int tf_router(const void* h16, const void* gate, const float* bias, const float* bias_vl, const int* tokens,
+                     int image_token, float* logits, int* ids, float* wts, int M, int E, int d, int topk, int scoring,
+                     int renorm, float scale, cudaStream_t st) {
   if (d % 256) return -1;
+  const RouterBias rb{bias, bias_vl, tokens, image_token};
   router_logits_kernel<<<(E + 7) / 8, 256, 0, st>>>((const __half*)h16, (const __nv_bfloat16*)gate,
                                                     logits, M, E, d);
   const int nw = 4;
   router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
-      logits, bias, ids, wts, M, E, topk, scoring, renorm, scale);
+      logits, rb, ids, wts, M, E, topk, scoring, renorm, scale);
   return (int)cudaGetLastError();
 }
 
 // top-k + weights only, for logits produced elsewhere (large row counts: tensor-core GEMM)
-TF_API int tf_router_topk(const float* logits, const float* bias, int* ids, float* wts, int M, int E, int topk,
-                          int scoring, int renorm, float scale, cudaStream_t st) {
+TF_API int tf_router_topk(const float* logits, const float* bias, const float* bias_vl, const int* tokens,
+                          int image_token, int* ids, float* wts, int M, int E, int topk, int scoring, int renorm,
+                          float scale, cudaStream_t st) {
   const int nw = 4;
+  const RouterBias rb{bias, bias_vl, tokens, image_token};
   router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
-      logits, bias, ids, wts, M, E, topk, scoring, renorm, scale);
+      logits, rb, ids, wts, M, E, topk, scoring, renorm, scale);
   return (int)cudaGetLastError();
 }
 
 // tf_router_topk followed by tf_route_group for up to 32 rows, one launch
-TF_API int tf_router_topk_group(const float* logits, const float* bias, int* ids, float* wts, int M, int E, int topk,
+TF_API int tf_router_topk_group(const float* logits, const float* bias, const float* bias_vl, const int* tokens,
+                                int image_token, int* ids, float* wts, int M, int E, int topk,
                                 int scoring, int renorm, float scale, int e_lo, int e_hi, int* group_expert,
                                 int* group_start, int* group_count, int* n_groups, int* sorted_pairs,
                                 int* n_local_pairs, cudaStream_t st) {
   const size_t smem = max((size_t)16 * 2 * E * sizeof(float), (size_t)(e_hi - e_lo + M * topk) * sizeof(int));
   if (M <= 0 || M > 32 || e_hi <= e_lo || smem > 48 * 1024) return -1;
-  router_topk_group_kernel<<<1, 512, smem, st>>>(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, e_lo, e_hi,
+  const RouterBias rb{bias, bias_vl, tokens, image_token};
+  router_topk_group_kernel<<<1, 512, smem, st>>>(logits, rb, ids, wts, M, E, topk, scoring, renorm, scale, e_lo, e_hi,
                                                  group_expert, group_start, group_count, n_groups, sorted_pairs,
                                                  n_local_pairs);
   return (int)cudaGetLastError();

@@ -38,7 +38,9 @@ _EXPERT = re.compile(r"\.ffn\.experts\.(\d+)\.")
 
 def classify(name: str, shape: Tuple[int, ...], cfg: ModelConfig, rank: int, world: int,
              moe_parallel: str = "ep") -> Placement:
-    if name in ("embed.weight", "head.weight", "mtp.markov_head.head.weight"):
+    if name in ("embed.weight", "head.weight") or re.fullmatch(r"mtp\.\d+\.markov_head\.head\.weight", name):
+        # vocabulary rows; the Markov head of the last draft stage is split like the head, its
+        # embedding (latents) stays whole on every rank (reference: src/layout.rs:86)
         return _split(shape[0], rank, world, 0)
     m = re.match(r"(?:layers|mtp)\.(\d+)\.", name)
     layer = int(m.group(1)) if m else None
@@ -70,6 +72,11 @@ def classify(name: str, shape: Tuple[int, ...], cfg: ModelConfig, rank: int, wor
     return Placement("replicated")
 
 
+def markov_prefix(cfg: ModelConfig) -> str:
+    """Tensor-name prefix of the Markov correction head: it belongs to the last draft stage."""
+    return f"mtp.{cfg.draft.layers - 1}.markov_head"
+
+
 def comp_width(cfg: ModelConfig) -> int:
     """Output width of the compressor projections: the pooled latent plus the pooled index key."""
     return cfg.head_dim + cfg.index_dim
@@ -96,9 +103,24 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
         # token ids of the drafter's 4-bit vocabulary-subset head (the rows themselves are cut from head.weight)
         out.append(("mtp.head_subset.ids", "I64", (cfg.draft.subset_rows,)))
     if n_draft and cfg.draft.markov_rank:
-        # Markov correction of the draft logits: embedding replicated, head rows split like the vocabulary head
-        out.append(("mtp.markov_head.embed.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
-        out.append(("mtp.markov_head.head.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
+        # Markov correction of the draft logits, owned by the LAST draft stage (reference:
+        # mtp.2.markov_head.{embed,head}.weight, src/layout.rs:362): embedding replicated, head rows
+        # split like the vocabulary head
+        mk = markov_prefix(cfg)
+        out.append((f"{mk}.embed.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
+        out.append((f"{mk}.head.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
+    if cfg.engram is not None and cfg.engram.layers:
+        # hashed n-gram memory (reference: src/layout.rs:277-292, src/engram_gpu.rs:174-183): the row
+        # store as MXFP8 (e4m3 values + one UE8M0 per 32), the projection, the gate weights
+        from ..models import engram as EG
+        rows = EG.table_rows(cfg)
+        ids = (cfg.engram.ngram - 1) * cfg.engram.heads
+        for l in cfg.engram.layers:
+            out.append((f"layers.{l}.engram.embed.weight", "F8_E4M3", (rows, cfg.engram.width)))
+            out.append((f"layers.{l}.engram.embed.scale", "F8_E8M0", (rows, cfg.engram.width // 32)))
+            dense(f"layers.{l}.engram.wkv", (cfg.hc_mult + 1) * d, ids * cfg.engram.width)
+            out.append((f"layers.{l}.engram.q_weight", "BF16", (cfg.hc_mult, d)))
+            out.append((f"layers.{l}.engram.k_weight", "BF16", (cfg.hc_mult, d)))
     for l in range(cfg.n_layers + n_draft):
         draft = l >= cfg.n_layers
         p = f"mtp.{l - cfg.n_layers}" if draft else f"layers.{l}"
@@ -147,6 +169,9 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
                 dense(f"{p}.ffn.shared_experts.{nm}", n, k)
         out.append((f"{p}.ffn.gate.weight", "BF16", (cfg.n_experts, d)))
         out.append((f"{p}.ffn.gate.bias", "F32", (cfg.n_experts,)))
+        if cfg.router_bias_vl and not draft:
+            # alternative selection bias used for image-token rows (reference: src/layout.rs:275)
+            out.append((f"{p}.ffn.gate.bias_vl", "F32", (cfg.n_experts,)))
     return out
 
 

@@ -59,6 +59,7 @@ class LayerWeights:
     sink: Optional[torch.Tensor] = None
     gate: torch.Tensor = None
     gate_bias: Optional[torch.Tensor] = None
+    gate_bias_vl: Optional[torch.Tensor] = None    # selection bias of image-token rows
     ew1: torch.Tensor = None
     ew3: torch.Tensor = None
     ew2: torch.Tensor = None
@@ -232,6 +233,8 @@ def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: i
         roundtrip[f"{p}.ffn.gate.weight"] = L.gate.float().cpu()
     if cfg.router_bias:
         L.gate_bias = dev(W[f"{p}.ffn.gate.bias"], torch.float32)
+        if cfg.router_bias_vl and f"{p}.ffn.gate.bias_vl" in W:
+            L.gate_bias_vl = dev(W[f"{p}.ffn.gate.bias_vl"], torch.float32)
     El = cfg.n_experts // world
     for nm in ("w1", "w3", "w2"):
         full = dev(W[f"{p}.ffn.experts.{nm}.weight"])
@@ -482,8 +485,9 @@ class Engine:
             if cfg.draft.markov_rank:
                 # low-rank bigram correction of the draft logits: embed replicated, head rows sharded
                 Vm = cfg.vocab // comm.world
-                extra["markov_embed"] = W["mtp.markov_head.embed.weight"].to(device, torch.bfloat16).contiguous()
-                extra["markov_head"] = W["mtp.markov_head.head.weight"][comm.rank * Vm:(comm.rank + 1) * Vm].to(
+                mk = f"mtp.{cfg.draft.layers - 1}.markov_head"
+                extra["markov_embed"] = W[f"{mk}.embed.weight"].to(device, torch.bfloat16).contiguous()
+                extra["markov_head"] = W[f"{mk}.head.weight"][comm.rank * Vm:(comm.rank + 1) * Vm].to(
                     device, torch.bfloat16).contiguous()
         if cfg.hc_mult > 1:
             extra = dict(extra, hc_head=tuple(W[k].to(device, torch.float32).contiguous()
@@ -936,19 +940,21 @@ class Engine:
             # router logits of a prefill chunk on the tensor cores (bf16 x bf16), then top-k
             native.call("tf_gemm_tc", 0, b["hb"], d, L.gate, d, b["logits_r"], cfg.n_experts, T, cfg.n_experts,
                         d, None, 0, None, 0, 0, None, None, 0, self.status.t)
-            native.call("tf_router_topk", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
-                        cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
+            native.call("tf_router_topk", b["logits_r"], L.gate_bias, L.gate_bias_vl, b["meta"][0], cfg.image_token,
+                        b["ids"], b["wts"], T, cfg.n_experts, cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
         elif T <= self.SMALL_M and cfg.n_experts % 32 == 0:
             # one warp per expert row over the bf16 gate matrix, then top-k
             native.call("tf_router_logits_small", b["hb"], d, L.gate, b["logits_r"], cfg.n_experts, T,
                         cfg.n_experts, d)
             e0 = self.rank * self.El
-            native.call("tf_router_topk_group", b["logits_r"], L.gate_bias, b["ids"], b["wts"], T, cfg.n_experts,
+            native.call("tf_router_topk_group", b["logits_r"], L.gate_bias, L.gate_bias_vl, b["meta"][0],
+                        cfg.image_token, b["ids"], b["wts"], T, cfg.n_experts,
                         cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale, e0, e0 + self.El,
                         b["g_expert"], b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
             grouped = True
         else:
-            native.call("tf_router", b["h16"], L.gate, L.gate_bias, b["logits_r"], b["ids"], b["wts"], T,
+            native.call("tf_router", b["h16"], L.gate, L.gate_bias, L.gate_bias_vl, b["meta"][0], cfg.image_token,
+                        b["logits_r"], b["ids"], b["wts"], T,
                         cfg.n_experts, d, cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale)
         e_lo = self.rank * self.El
         npairs = T * cfg.topk

@@ -3,9 +3,14 @@
 ``export_checkpoint`` writes a weight dict (the oracle's names: stacked experts, plain fp32
 matrices) as safetensors shards in the checkpoint contract (per-expert tensors, FP8 block scales,
 packed FP4 + UE8M0), and ``checkpoint_weights`` reads such a checkpoint back into a dict that
-``Engine.from_weights`` and ``OracleModel`` accept.  Re-quantising what was dequantised here is
-exact (the block grids line up), so the engine ends up with the checkpoint's own bytes
-(reference: src/weights.rs:369-540 view selection and expert packing; src/layout.rs:220-295).
+``Engine.from_weights`` and ``OracleModel`` accept.  For block-128 FP8 and MXFP4 checkpoints,
+re-quantising what was dequantised here is exact (the block grids line up), so the engine ends up
+with the checkpoint's own bytes.  Dense weights stored with 32x32 UE8M0 scales are re-expressed on
+the engine's 128x128 grid, which is NOT exact: values of sub-blocks whose scale is far below the
+largest scale of their 128x128 block lose low bits.  The Engram row store travels in its packed
+MXFP8 form (``layers.{l}.engram.embed.{weight,scale}``) and is exposed to the model as
+``engram.{e}.table`` (reference: src/weights.rs:369-540 view selection and expert packing;
+src/layout.rs:220-295).
 """
 from __future__ import annotations
 
@@ -51,6 +56,14 @@ def export_checkpoint(W: Dict[str, torch.Tensor], cfg: ModelConfig, out_dir: str
         if name.endswith(".scale"):
             continue                                        # written with its weight
         stem = name[:-len(".weight")] if name.endswith(".weight") else name
+        if name.endswith(".engram.embed.weight"):
+            # the row store in its packed form: e4m3 values + one UE8M0 scale per 32
+            from . import engram as EG
+            e = cfg.engram.layers.index(int(name.split(".")[1]))
+            packed = EG.pack_rows(W[f"engram.{e}.table"].float())
+            put(name, packed[:, :cfg.engram.width].contiguous().view(torch.float8_e4m3fn))
+            put(stem + ".scale", packed[:, cfg.engram.width:].contiguous(), "F8_E8M0")
+            continue
         if ".ffn.experts." in name:
             pre, rest = name.split(".ffn.experts.")
             e, nm, _ = rest.split(".")
@@ -88,6 +101,12 @@ def checkpoint_weights(ck: Checkpoint, cfg: ModelConfig, validate: bool = True) 
         if name.endswith(".scale"):
             continue
         stem = name[:-len(".weight")] if name.endswith(".weight") else name
+        if name.endswith(".engram.embed.weight"):
+            from . import engram as EG
+            e = cfg.engram.layers.index(int(name.split(".")[1]))
+            packed = torch.cat([ck.read(name).view(torch.uint8), ck.read(stem + ".scale").view(torch.uint8)], dim=1)
+            W[f"engram.{e}.table"] = EG.unpack_rows(packed)
+            continue
         if ".ffn.experts." in name:
             pre, rest = name.split(".ffn.experts.")
             e, nm, _ = rest.split(".")

@@ -84,7 +84,8 @@ def apply_rope(x: torch.Tensor, pos: torch.Tensor, freqs: torch.Tensor, inverse:
     return torch.cat([head, rot], -1)
 
 
-def route(logits: torch.Tensor, cfg: ModelConfig, bias: Optional[torch.Tensor]
+def route(logits: torch.Tensor, cfg: ModelConfig, bias: Optional[torch.Tensor],
+          bias_vl: Optional[torch.Tensor] = None, image_rows: Optional[torch.Tensor] = None
           ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Router: returns (expert ids [T,k] in selection order, weights [T,k] fp32).
 
@@ -98,6 +99,9 @@ def route(logits: torch.Tensor, cfg: ModelConfig, bias: Optional[torch.Tensor]
     else:
         score = torch.softmax(lf, -1)
     key = score + bias if (bias is not None and cfg.router_bias) else score
+    if bias_vl is not None and image_rows is not None and cfg.router_bias and bool(image_rows.any()):
+        # the selection bias is chosen per token: image rows use gate.bias_vl (kernels/moe_frontend.cuh:140)
+        key = torch.where(image_rows[:, None], score + bias_vl, key)
     key = torch.nan_to_num(key, nan=float("inf"))
     # stable descending sort => ties resolved by lowest expert id
     order = torch.sort(key, dim=-1, descending=True, stable=True).indices[:, : cfg.topk]
@@ -197,6 +201,8 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32) -> Dict[s
             mat(f"{p}.attn.indexer.weights_proj.weight", cfg.index_heads, d, std=1.0 / math.sqrt(d))
         mat(f"{p}.ffn.gate.weight", cfg.n_experts, d, std=1.0 / math.sqrt(d))
         W[f"{p}.ffn.gate.bias"] = torch.zeros(cfg.n_experts, dtype=dtype)
+        if cfg.router_bias_vl and not is_draft:
+            W[f"{p}.ffn.gate.bias_vl"] = (0.5 * torch.randn(cfg.n_experts, generator=g)).to(dtype)
         for nm, n, k in (("w1", cfg.moe_inter, d), ("w3", cfg.moe_inter, d), ("w2", d, cfg.moe_inter)):
             W[f"{p}.ffn.experts.{nm}.weight"] = (
                 torch.randn(cfg.n_experts, n, k, generator=g) * cfg.init_std).to(dtype)
@@ -216,9 +222,10 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32) -> Dict[s
                 W["mtp.head_subset.ids"] = torch.sort(
                     torch.randperm(cfg.vocab, generator=g)[: cfg.draft.subset_rows]).values.to(torch.int64)
             if cfg.draft.markov_rank:
-                # Markov correction head (reference names: mtp.2.markov_head.{embed,head}.weight)
-                mat("mtp.markov_head.embed.weight", cfg.vocab, cfg.draft.markov_rank, std=1.0)
-                mat("mtp.markov_head.head.weight", cfg.vocab, cfg.draft.markov_rank,
+                # Markov correction head of the last draft stage (reference: mtp.2.markov_head.{embed,head}.weight)
+                mk = f"mtp.{cfg.draft.layers - 1}.markov_head"
+                mat(f"{mk}.embed.weight", cfg.vocab, cfg.draft.markov_rank, std=1.0)
+                mat(f"{mk}.head.weight", cfg.vocab, cfg.draft.markov_rank,
                     std=1.0 / math.sqrt(cfg.draft.markov_rank))
     if cfg.engram is not None and cfg.engram.layers:
         # hashed n-gram memory: one table per Engram layer (values exactly representable in the packed
@@ -253,7 +260,7 @@ def shard_weights(W: Dict[str, torch.Tensor], cfg: ModelConfig, rank: int, world
         return t.narrow(axis, rank * (n // world), n // world).contiguous()
 
     for name, t in W.items():
-        if name in ("embed.weight", "head.weight", "mtp.markov_head.head.weight"):
+        if name in ("embed.weight", "head.weight") or name.endswith(".markov_head.head.weight"):
             out[name] = sl(t, 0)
         elif name.endswith((".attn.wq.weight", ".attn.wq_b.weight", ".attn.attn_sink")):
             out[name] = sl(t, 0)
@@ -488,10 +495,12 @@ class OracleModel:
             out = self._aq(o.reshape(T, Hl * Dh)) @ W[f"{p}.attn.wo.weight"].t()
         return self.comm.all_reduce(out)
 
-    def _ffn(self, p: str, h: torch.Tensor) -> torch.Tensor:
+    def _ffn(self, p: str, h: torch.Tensor, tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg, W = self.cfg, self.W
         T = h.shape[0]
-        ids, wts = route(h @ W[f"{p}.ffn.gate.weight"].t(), cfg, W.get(f"{p}.ffn.gate.bias"))
+        image_rows = (tokens.to(h.device) == cfg.image_token) if (tokens is not None and cfg.router_bias_vl) else None
+        ids, wts = route(h @ W[f"{p}.ffn.gate.weight"].t(), cfg, W.get(f"{p}.ffn.gate.bias"),
+                         W.get(f"{p}.ffn.gate.bias_vl"), image_rows)
         w1, w3, w2 = (W[f"{p}.ffn.experts.{n}.weight"] for n in ("w1", "w3", "w2"))
         y = torch.zeros(T, cfg.hidden, dtype=torch.float32, device=h.device)
         El = w1.shape[0]
@@ -529,7 +538,7 @@ class OracleModel:
                                  W[f"{p}.engram.k_weight"].to(torch.float32), cfg.rms_eps)
         return out if cfg.hc_mult > 1 else out[:, 0]
 
-    def _layer(self, p, layer, x, pos, s, draft=False, engram_ids=None):
+    def _layer(self, p, layer, x, pos, s, draft=False, engram_ids=None, tokens=None):
         cfg = self.cfg
         src = cfg.kv_source_of(layer) if not draft else -1
         src_prefix = f"layers.{src}" if src >= 0 else None
@@ -541,7 +550,7 @@ class OracleModel:
                             (not draft) and layer in cfg.index_source_layers, draft)
         x = self._residual(x, a, hc)
         h, hc = self._boundary(x, p, "ffn")
-        f = self._ffn(p, h.to(self.dtype))
+        f = self._ffn(p, h.to(self.dtype), None if draft else tokens)
         return self._residual(x, f, hc)
 
     def head(self, x: torch.Tensor, subset: bool = False) -> torch.Tensor:
@@ -598,7 +607,7 @@ class OracleModel:
             eg_ids = torch.from_numpy(EG.hash_positions(md, prev, tokens.tolist(), start).astype("int64")
                                       ).to(tokens.device)
         for l in range(cfg.n_layers):
-            x = self._layer(f"layers.{l}", l, x, pos, s, engram_ids=eg_ids)
+            x = self._layer(f"layers.{l}", l, x, pos, s, engram_ids=eg_ids, tokens=tokens)
         self.last_hidden = x
         if commit:
             s.length = start + T
@@ -624,8 +633,9 @@ class OracleModel:
         if cfg.draft.markov_rank:
             # Markov correction: a rank-r bigram term from the token each row was fed
             # (reference: src/dspark_markov.rs:886-971, kernels/core.cu:1110-1122)
-            lat = W["mtp.markov_head.embed.weight"][tokens.long()].to(self.dtype)
-            bias = (lat @ W["mtp.markov_head.head.weight"].t()).to(torch.float32)
+            mk = f"mtp.{cfg.draft.layers - 1}.markov_head"
+            lat = W[f"{mk}.embed.weight"][tokens.long()].to(self.dtype)
+            bias = (lat @ W[f"{mk}.head.weight"].t()).to(torch.float32)
             logits = logits + self.comm.all_gather(bias, dim=1)
         return logits, x
 
