@@ -81,6 +81,19 @@ def expand(tokens: Sequence[int], uris: Sequence[str], marker_id: int, image_tok
     return PromptMedia(out, preps, offs, ident)
 
 
+class VisionFrontend:
+    """What the HTTP front end needs to accept image parts: the tokenizer's image marker, the
+    placeholder token id of the language model, the per-image token cap and a content-keyed cache
+    of prepared images (CPU decode / resize / patchify happens once per distinct image)."""
+
+    def __init__(self, marker_id: int, image_token_id: int, max_tokens: int = 1024, cache_bytes: int = 256 << 20):
+        self.marker_id, self.image_token_id, self.max_tokens = marker_id, image_token_id, max_tokens
+        self.cache = VI.ImageCache(cache_bytes)
+
+    def expand(self, tokens: Sequence[int], uris: Sequence[str]) -> PromptMedia:
+        return expand(tokens, uris, self.marker_id, self.image_token_id, self.cache, self.max_tokens)
+
+
 class SpanEncoder:
     """Vision tower + feature cache: prepared images -> rows that replace image-token embeddings."""
 

@@ -41,14 +41,34 @@ class Frontend:
     """Protocol + tokenizer: request body -> token ids; token ids -> deltas."""
 
     def __init__(self, tokenizer, context: int, allow_sampling: bool = True, vision=None):
+        """``vision``: an ``api.media.VisionFrontend`` when the deployment has a vision tower; without
+        one a request that carries image parts is refused (it must never be answered as if the image
+        had been seen)."""
         self.tok, self.context, self.allow_sampling, self.vision = tokenizer, context, allow_sampling, vision
 
     def prepare(self, body: Dict[str, Any]):
+        """-> (request, prompt tokens, token limit, PromptMedia or None).  Image parts become runs of
+        image-placeholder tokens (one per language-model position of the image's plan) and a media
+        identity that keys prefix caches (reference: src/http_server.rs:883 chat_input)."""
+        from . import media as M
         req = P.normalize_chat_request(body, self.allow_sampling)
         text = P.render_chat(req)
         tokens = self.tok.encode(text)
+        uris = P.image_parts(req.messages)
+        pm = None
+        if uris:
+            if self.vision is None:
+                raise P.ProtocolError("this deployment has no vision tower: image parts are not supported",
+                                      400, "unsupported_media")
+            if any(not isinstance(u, str) for u in uris):
+                raise P.ProtocolError("image part without a URL", 400, "invalid_media")
+            try:
+                pm = self.vision.expand(tokens, uris)
+            except M.MediaError as e:
+                raise P.ProtocolError(str(e), 400, "invalid_media") from e
+            tokens = pm.tokens
         limit = P.resolve_max_tokens(req.max_new_tokens, len(tokens), self.context)
-        return req, tokens, limit
+        return req, tokens, limit, pm
 
 
 class Server:
@@ -174,7 +194,7 @@ class Server:
         if self.state != "ready":
             return _err(503, "not_ready", f"server is {self.state}")
         try:
-            req, tokens, limit = self.front.prepare(body)
+            req, tokens, limit, pm = self.front.prepare(body)
         except P.ProtocolError as e:
             return _err(e.status, e.code, str(e))
         rid = "req-" + uuid.uuid4().hex[:16]
@@ -186,6 +206,8 @@ class Server:
         background = request.headers.get("X-LocalAI-Mode", "").lower() == "background"
         job = Job(rid, tokens, limit, req.temperature, req.top_p, req.seed if req.seed is not None else
                   int.from_bytes(hashlib.sha256(rid.encode()).digest()[:4], "little"), background, emit=emit)
+        if pm is not None:
+            job.media, job.images = pm.identity, [pm]
         try:
             self.sched.submit(job)
         except QueueFull as e:

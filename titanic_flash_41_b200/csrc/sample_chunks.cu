@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   float* tbuf = reinterpret_cast<float*>(smem);
   float* dbuf = tbuf + p.chunk;
   unsigned long long* whist = reinterpret_cast<unsigned long long*>(dbuf + p.chunk);   // [32][256]
-  __shared__ unsigned long long gbins[256];
+  __shared__ unsigned long long gbins[256], gpart[4][256];
   __shared__ double wm[32], cm[(kMaxG + 1) * kMaxP], Rrow[kMaxG + 1], wrow[kMaxG + 1], ptq[2 * kMaxG];
   __shared__ float redf[32];
   __shared__ int redi[32];
@@ -181,7 +181,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
     if (has_d) *reinterpret_cast<float4*>(dbuf + k) = *reinterpret_cast<const float4*>(drow + k);
   }
   __syncthreads();
-  const float inv_t = 1.f / p.sess_temp[s];
+  // IEEE reciprocal (not the fast-math approximation): every kernel and the host agree on 1 / T bit for bit
+  const float inv_t = __frcp_rn(p.sess_temp[s]);
   const float top_p = p.sess_top_p[s];
 
   // ---- 1. row maximum
@@ -237,12 +238,25 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
     for (int k = threadIdx.x; k < 32 * 256; k += kThreads) whist[k] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix, mask = s_mask;
-    for (int k = threadIdx.x; k < n; k += kThreads) {
-      const float v = tbuf[k];
-      const uint32_t key = fkey(v);
-      if ((key & mask) == prefix)
-        atomicAdd(&whist[warp * 256 + ((key >> shift) & 255)],
-                  (unsigned long long)((double)expf((v - stat.m) * inv_t) * kFix));
+    {
+      // a thread's consecutive elements mostly fall into the same few bins (the top key bits are the
+      // sign and the exponent): add up a run privately and touch shared memory once per run
+      int cur = -1;
+      unsigned long long run = 0;
+      for (int k = threadIdx.x; k < n; k += kThreads) {
+        const float v = tbuf[k];
+        const uint32_t key = fkey(v);
+        if ((key & mask) != prefix) continue;
+        const int bin = (key >> shift) & 255;
+        const unsigned long long mass = (unsigned long long)((double)expf((v - stat.m) * inv_t) * kFix);
+        if (bin != cur) {
+          if (cur >= 0) atomicAdd(&whist[warp * 256 + cur], run);
+          cur = bin;
+          run = 0;
+        }
+        run += mass;
+      }
+      if (cur >= 0) atomicAdd(&whist[warp * 256 + cur], run);
     }
     __syncthreads();
     if (threadIdx.x < 256) {
@@ -250,14 +264,30 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
       for (int w = 0; w < 32; ++w) acc += whist[w * 256 + threadIdx.x];
       push2(p, A.hist + ((((long)(level & 1) * P + part) * p.max_rows + row) * 256 + threadIdx.x) * 2, (uint32_t)acc,
             (uint32_t)(acc >> 32), tag);
+    }
+    {
+      // every thread polls one bin of up to four source chunks, all loads in flight at once
+      const int bin = threadIdx.x & 255, qg = threadIdx.x >> 8;
+      const unsigned long long* src0 = mine + A.hist + ((((long)(level & 1) * P) * p.max_rows + row) * 256 + bin) * 2;
+      const long qstride = (long)p.max_rows * 256 * 2;
+      ulonglong2 v[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        if (qg + 4 * t < P) v[t] = ld_ll2(src0 + (qg + 4 * t) * qstride);
       unsigned long long tot = 0;
-      for (int q = 0; q < P; ++q)
-        tot += pair_u64(W.wait(mine + A.hist + ((((long)(level & 1) * P + q) * p.max_rows + row) * 256 + threadIdx.x) * 2,
-                               tag, 1 + level, row));
-      gbins[threadIdx.x] = tot;
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        if (qg + 4 * t < P) {
+          if (!ll_ready(v[t], tag)) v[t] = W.wait(src0 + (qg + 4 * t) * qstride, tag, 1 + level, row);
+          tot += pair_u64(v[t]);
+        }
+      gpart[qg][bin] = tot;
     }
     __syncthreads();
     if (s_fail) return;
+    if (threadIdx.x < 256)
+      gbins[threadIdx.x] = gpart[0][threadIdx.x] + gpart[1][threadIdx.x] + gpart[2][threadIdx.x] + gpart[3][threadIdx.x];
+    __syncthreads();
     if (threadIdx.x == 0) {
       if (level == 0) {
         unsigned long long tot = 0;

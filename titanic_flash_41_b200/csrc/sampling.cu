@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(256) rowhist_kernel(const float* __restrict__ 
                                                       int level, void* scratch) {
   __shared__ unsigned long long sh[4096];
   const int r = blockIdx.x;
-  if (sess_temp) inv_t = 1.f / sess_temp[r / rps];
+  if (sess_temp) inv_t = __frcp_rn(sess_temp[r / rps]);    // IEEE reciprocal, as the host computes 1 / T
   RowScratch* rs = row_scratch(scratch, r);
   const int shift = level == 0 ? 20 : (level == 1 ? 8 : 0);
   const int nb = level == 2 ? 256 : 4096;
@@ -312,11 +312,11 @@ __device__ double weight_chain(const VerifyParams& p, int s, int i) {
   for (int j = 1; j <= i; ++j) {
     const int x = p.proposals[s * p.g + j - 1];
     const float* tx = p.tlogits + ((long)s * (p.g + 1) + j - 1) * p.ldl;
-    const double pt = prob_of(tx, p.tstat[s * (p.g + 1) + j - 1], 1.f / (p.sess_temp ? p.sess_temp[s] : p.t_temp), x);
+    const double pt = prob_of(tx, p.tstat[s * (p.g + 1) + j - 1], __frcp_rn(p.sess_temp ? p.sess_temp[s] : p.t_temp), x);
     double q = 1.0;
     if (!p.point_mass) {
       const float* dx = p.dlogits + ((long)s * p.g + j - 1) * p.ldl;
-      q = prob_of(dx, p.dstat[s * p.g + j - 1], 1.f / (p.sess_temp ? p.sess_temp[s] : p.d_temp), x);
+      q = prob_of(dx, p.dstat[s * p.g + j - 1], __frcp_rn(p.sess_temp ? p.sess_temp[s] : p.d_temp), x);
     }
     const double ratio = q > 0.0 ? w * pt / q : (pt > 0.0 ? 1.0 : 0.0);
     w = ratio < 1.0 ? ratio : 1.0;
@@ -340,13 +340,13 @@ __device__ __forceinline__ RowCtx row_ctx(const VerifyParams& p, int s, int i, d
   c.tx = p.tlogits + ((long)s * (p.g + 1) + i) * p.ldl;
   c.tm = ts.m;
   c.tthr = ts.thr;
-  c.t_inv = 1.f / (p.sess_temp ? p.sess_temp[s] : p.t_temp);
+  c.t_inv = __frcp_rn(p.sess_temp ? p.sess_temp[s] : p.t_temp);
   c.wz = wi / ts.z;
   c.dx = nullptr;
   c.point_tok = -1;
   c.dm = 0.f;
   c.dthr = 0;
-  c.d_inv = 1.f / (p.sess_temp ? p.sess_temp[s] : p.d_temp);
+  c.d_inv = __frcp_rn(p.sess_temp ? p.sess_temp[s] : p.d_temp);
   c.qz = 0.0;
   if (i < p.g) {
     if (p.point_mass) c.point_tok = p.proposals[s * p.g + i];

@@ -582,7 +582,8 @@ class OracleModel:
 
     # -- public ----------------------------------------------------------
     def forward(self, tokens: torch.Tensor, s: OracleSession, start: Optional[int] = None,
-                need_logits: bool = True, commit: bool = True) -> Optional[torch.Tensor]:
+                need_logits: bool = True, commit: bool = True,
+                x_patch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
         """Run ``tokens`` at positions ``start..start+T`` (default: append after the committed
         length).  Returns logits [T, vocab] (fp32).  ``commit=False`` leaves ``s.length`` alone so
         that a verification round can accept a prefix with ``s.length = ...`` afterwards."""
@@ -592,6 +593,10 @@ class OracleModel:
         assert start + T <= s.max_tokens, "conversation exceeds its region"
         pos = torch.arange(start, start + T, device=tokens.device)
         x = self.embed(tokens)
+        if x_patch is not None:
+            # rows that stand for image tokens take the vision tower's features instead
+            x = x.clone()
+            x[x_patch[0].long()] = x_patch[1].to(x.dtype)
         if cfg.hc_mult > 1:
             x = x[:, None, :].expand(T, cfg.hc_mult, cfg.hidden).contiguous()      # core.cu:536
         eg_ids = None

@@ -36,14 +36,21 @@ class OracleBackend:
         self.hidden[region] = None
 
     def prefill(self, region: int, tokens: Sequence[int], start: int,
-                on_chunk: Optional[Callable[[int], bool]] = None) -> Optional[torch.Tensor]:
+                on_chunk: Optional[Callable[[int], bool]] = None, embeds=None) -> Optional[torch.Tensor]:
+        """``embeds`` = (offsets into ``tokens``, rows [m, hidden]): image spans that replace the
+        embeddings of their placeholder tokens."""
         s = self.sessions[region]
         s.length = start
         toks = torch.tensor(list(tokens), dtype=torch.long)
         done, logits = 0, None
         while done < len(toks):
             n = min(self.chunk, len(toks) - done)
-            logits = self.model.forward(toks[done:done + n], s)
+            xp = None
+            if embeds is not None:
+                m = (embeds[0] >= done) & (embeds[0] < done + n)
+                if bool(m.any()):
+                    xp = (embeds[0][m] - done, embeds[1][m])
+            logits = self.model.forward(toks[done:done + n], s, x_patch=xp)
             self.hidden[region] = self.model.last_hidden[-1:].clone()
             done += n
             if on_chunk is not None and not on_chunk(done):
@@ -162,10 +169,10 @@ class EngineBackend:
 
     wants_prev = True      # prefill(..., prev=tokens right before `start`)
 
-    def prefill(self, region, tokens, start, on_chunk=None, prev=()):
+    def prefill(self, region, tokens, start, on_chunk=None, prev=(), embeds=None):
         from .prefill import run_prefill
         lg = run_prefill(self.e, region, torch.tensor(list(tokens), dtype=torch.int32), self.chunk, start,
-                         True, on_chunk, prev=prev)
+                         True, on_chunk, prev=prev, embeds=embeds)
         if lg is None:
             return None
         self.last_hidden_rows[region] = self.e.last_hidden[-1:].clone() if self.e.last_hidden is not None else None

@@ -51,7 +51,9 @@ class Worker:
     def __init__(self, backend, scheduler: Optional[Scheduler], cache: Optional[SessionCache] = None,
                  eos_id: int = 1, log: Optional[EventLog] = None, control=None, rank: int = 0,
                  prefill_slice_s: float = 0.5, checkpoint_min: int = policy.SHORT_TOKENS,
-                 checkpoint_align: int = 8192):
+                 checkpoint_align: int = 8192, span_encoder=None):
+        """``span_encoder`` (rank 0): ``api.media.SpanEncoder`` over the vision tower; needed to serve
+        requests that carry images."""
         self.b, self.sched, self.cache = backend, scheduler, cache or SessionCache()
         self.eos, self.log, self.control, self.rank = eos_id, log or EventLog(), control, rank
         self.slice_s, self.ck_min, self.ck_align = prefill_slice_s, checkpoint_min, checkpoint_align
@@ -59,6 +61,7 @@ class Worker:
         self.jobs: Dict[str, Job] = {}
         self.running = True
         self.requests = 0
+        self.span_encoder = span_encoder
         self.clock = time.monotonic          # rank 0's time source for prefill slices (tests skew it)
         self.directives: List[int] = []      # per-chunk directives this rank followed (diagnostics)
 
@@ -70,6 +73,33 @@ class Worker:
     @staticmethod
     def decode(raw: bytes) -> Dict[str, Any]:
         return json.loads(raw)
+
+    def _send_command(self, cmd: Dict[str, Any]) -> None:
+        """Broadcast a command.  The prompt of a Begin does not travel as JSON text: the header frame
+        names its length and the token ids follow as little-endian int32 in bounded frames, so a
+        million-token prompt costs 4 MB on the wire and never exceeds the channel's frame limit."""
+        import numpy as np
+        toks = cmd.get("tokens")
+        if toks is None:
+            self.control.command(self.encode(cmd))
+            return
+        head = {k: v for k, v in cmd.items() if k != "tokens"}
+        head["n_tokens"] = len(toks)
+        self.control.command(self.encode(head))
+        blob = np.asarray(toks, dtype="<i4").tobytes()
+        for i in range(0, len(blob), self.FRAME):
+            self.control.command(blob[i:i + self.FRAME])
+
+    def _recv_command(self) -> Dict[str, Any]:
+        import numpy as np
+        cmd = self.decode(self.control.command(None))
+        n = cmd.pop("n_tokens", None)
+        if n is not None:
+            blob = bytearray()
+            while len(blob) < 4 * n:
+                blob += self.control.command(None)
+            cmd["tokens"] = np.frombuffer(bytes(blob[:4 * n]), dtype="<i4").tolist()
+        return cmd
 
     def _digest(self) -> bytes:
         h = hashlib.sha256()
@@ -103,7 +133,8 @@ class Worker:
     def _begin_cmd(self, j: Job) -> Dict[str, Any]:
         self.jobs[j.id] = j
         return {"op": "begin", "id": j.id, "region": j.region, "tokens": j.tokens, "limit": j.max_new_tokens,
-                "temperature": j.temperature, "top_p": j.top_p, "seed": j.seed, "media": j.media}
+                "temperature": j.temperature, "top_p": j.top_p, "seed": j.seed, "media": j.media,
+                "images": len(j.images)}
 
     def run_once(self, idle_wait: float = 0.05) -> str:
         """One command: chosen by rank 0, broadcast, executed everywhere, agreed."""
@@ -111,11 +142,10 @@ class Worker:
             cmd = self.next_command()
             if cmd["op"] == "idle" and self.sched is not None and not self.active:
                 self.sched.wait_for_work(idle_wait)
-            raw = self.encode(cmd)
             if self.control is not None:
-                self.control.command(raw)
+                self._send_command(cmd)
         else:
-            cmd = self.decode(self.control.command(None))
+            cmd = self._recv_command()
         self.execute(cmd)
         if self.control is not None and cmd["op"] in ("begin", "step", "finish"):
             self.control.agree(self._digest())
@@ -163,6 +193,47 @@ class Worker:
         self.directives.append(d)
         return d
 
+    # ---------------------------------------------------------------- image spans
+    FRAME = 512 << 10
+
+    def _image_spans(self, job: Optional[Job]):
+        """(prompt offsets [m], feature rows [m, hidden]) of the request's images on every rank.
+        Rank 0 runs the vision tower (feature cache in front of it) and broadcasts the rows through
+        the control channel in bounded frames; the other ranks receive them (reference: patches or
+        spans broadcast to all ranks, src/worker_media.rs:301-470).  None on failure."""
+        import numpy as np
+        import torch
+        multi = self.control is not None and self.control.world > 1
+        if self.rank == 0:
+            offs = rows = None
+            try:
+                if self.span_encoder is None or job is None or not job.images:
+                    raise ValueError("no vision tower on this deployment")
+                got = [self.span_encoder.spans(pm) for pm in job.images]
+                offs = torch.cat([g[0] for g in got]).to(torch.int64).cpu()
+                rows = torch.cat([g[1] for g in got]).to(torch.bfloat16).cpu().contiguous()
+            except Exception as e:  # noqa: BLE001  (a bad image fails its request, not the worker)
+                self.log.log("image_failed", incident=True, error=str(e))
+            head = {"m": 0, "d": 0} if rows is None else {"m": int(rows.shape[0]), "d": int(rows.shape[1])}
+            if multi:
+                self.control.command(self.encode(head))
+                if rows is not None:
+                    blob = offs.numpy().tobytes() + rows.view(torch.int16).numpy().tobytes()
+                    for i in range(0, len(blob), self.FRAME):
+                        self.control.command(blob[i:i + self.FRAME])
+            return None if rows is None else (offs, rows)
+        head = self.decode(self.control.command(None))
+        m, d = int(head["m"]), int(head["d"])
+        if m == 0:
+            return None
+        total = m * 8 + m * d * 2
+        blob = bytearray()
+        while len(blob) < total:
+            blob += self.control.command(None)
+        offs = torch.from_numpy(np.frombuffer(bytes(blob[:m * 8]), dtype=np.int64).copy())
+        rows = torch.from_numpy(np.frombuffer(bytes(blob[m * 8:total]), dtype=np.int16).copy()).view(torch.bfloat16).view(m, d)
+        return offs, rows
+
     def _emit(self, job: Optional[Job], kind: str, payload: Any) -> None:
         if job is not None and self.rank == 0:
             job.emit(kind, payload)
@@ -177,6 +248,15 @@ class Worker:
             if self.sched and job:
                 self.sched.release(job)
             return
+        embeds = None
+        if cmd.get("images"):
+            embeds = self._image_spans(job)
+            if embeds is None:
+                self._emit(job, "error", {"code": "unsupported_media", "message": "the images of this request "
+                                          "could not be encoded"})
+                if self.sched and job:
+                    self.sched.release(job)
+                return
         # ---- prefix reuse
         start, hit = 0, self.cache.best_match(prompt, cmd.get("media", ""))
         if hit is not None and self.cache.ensure_loaded(hit, self.b.device):
@@ -208,11 +288,13 @@ class Worker:
                     self._step()
                     last_slice = self.clock()
                 return d != D_CANCEL
+            kw = {}
+            if embeds is not None:
+                kw["embeds"] = (embeds[0] - pos, embeds[1])       # offsets relative to this part of the prompt
             if getattr(self.b, "wants_prev", False):
                 # n-gram memory layers hash across the seam between reused and new tokens
-                logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk, prev=prompt[max(0, pos - 8):pos])
-            else:
-                logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk)
+                kw["prev"] = prompt[max(0, pos - 8):pos]
+            logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk, **kw)
             if logits is None:
                 self._emit(job, "error", {"code": "cancelled", "message": "cancelled during prefill"})
                 if self.sched and job:
