@@ -59,22 +59,65 @@ def main():
     wb = w.bfloat16()
     rows = []
     ws = SymmWorkspace(N, 32, device=dev)
-    for M in (1, 4, 16):
+    # decode-sized op.  One call is ~10 us, far below what a barrier + event pair resolves, and in a
+    # decode step the calls come back to back inside a CUDA graph: time a CHAIN of calls over
+    # distinct weight matrices (more bytes than L2 holds, so every call streams its weights from HBM)
+    # replayed as one graph, and report time per call.  `nccl` is the same chain as cuBLAS GEMV +
+    # NCCL all-reduce + the separate boundary kernel.
+    chain = 48
+    ws8 = [E.quant_fp8_device(torch.randn(N, Kl, device=dev, generator=g) * 0.02) for _ in range(chain)]
+    wbs = [dq.bfloat16() for dq in (E.dequant_fp8(w_) for w_ in ws8)]
+    nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
+    for M in (1, 4, 16, 32):
         x = torch.randn(M, Kl, device=dev, generator=g)
         x16, xb = x.half(), x.bfloat16()
-        out = torch.zeros(M, N, device=dev)
-        fused = timed(lambda: ws.gemv_allreduce(w8, x16, M, None, out, st.t))
+        resid = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+        h16 = torch.zeros(M, N, device=dev, dtype=torch.float16)
+        hb = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+        x8 = torch.zeros(M, N, device=dev, dtype=torch.uint8)
+        x8s = torch.zeros(M, N // 32, device=dev, dtype=torch.uint8)
+        norm = dict(w=nw, h16=h16, hb=hb, x8=x8, x8s=x8s, eps=1e-6)
         ref = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        delta = torch.zeros(M, N, device=dev)
 
-        def base():
-            torch.matmul(xb, wb.t(), out=ref)
-            dist.all_reduce(ref)
-        nccl = timed(base)
+        def fused_chain():
+            for w_ in ws8:
+                ws.gemv_allreduce(w_, x16, M, resid, None, st.t, norm=norm)
+
+        def nccl_chain():
+            for wb_ in wbs:
+                torch.matmul(xb, wb_.t(), out=ref)
+                dist.all_reduce(ref)
+                delta.copy_(ref)
+                native.call("tf_add_norm_fused", resid, delta, None, None, None, None, 0, 0, 0, nw, h16, hb, x8, x8s,
+                            M, N, 1e-6)
+
+        def graphed(fn):
+            fn()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            return gr.replay
+        fused = timed(graphed(fused_chain)) / chain
+        try:
+            nccl = timed(graphed(nccl_chain)) / chain
+        except Exception:                                   # noqa: BLE001  (NCCL under capture is optional)
+            torch.cuda.synchronize()
+            nccl = timed(nccl_chain) / chain
+        out = torch.zeros(M, N, device=dev)
+        ws.gemv_allreduce(w8, x16, M, None, out, st.t)
         want = x16.float() @ E.dequant_fp8(w8).t()
         dist.all_reduce(want)
         err = float((out - want).abs().max() / want.abs().max())
-        rows.append(dict(op="gemv+allreduce", M=M, fused_us=round(fused * 1e3, 1), nccl_cublas_us=round(nccl * 1e3, 1),
-                         speedup=round(nccl / fused, 2), rel_err=round(err, 5)))
+        # roofline of the decode-sized op: weight bytes from HBM, one NVLink one-way flight (~1.5 us
+        # measured for a flag round trip / 2) and the bf16 partials of M rows to 7 peers
+        hbm_us = (N * Kl) / (pk["hbm_gbs"] * 1e3)
+        link_us = 1.5 + M * N * 4 * (world - 1) / (NVLINK_GBS * 1e3)
+        roof = hbm_us + link_us
+        rows.append(dict(op="gemv+allreduce+residual+norm (chain of 48 in one graph)", M=M, fused_us=round(fused * 1e3, 2),
+                         nccl_cublas_us=round(nccl * 1e3, 2), speedup=round(nccl / fused, 2), rel_err=round(err, 5),
+                         roofline_us=round(roof, 2), frac_of_roofline=round(roof / (fused * 1e3), 3)))
     for M in (512, 4096, 16384):
         if M % (world * 128):
             continue

@@ -73,8 +73,14 @@ class Frontend:
 
 class Server:
     def __init__(self, cfg: ServerConfig, frontend: Frontend, scheduler: Scheduler, log: Optional[EventLog] = None,
-                 identity: str = "tflash"):
+                 identity: str = "tflash", memory=None, health=None):
+        """``memory``: a ``utils.memory.Admission`` for the host pool; every request reserves the bytes
+        its input pins (body, token ids, image patches) against it and is refused with 503
+        ``insufficient_memory`` when they do not fit above the floor (reference:
+        src/http_server.rs:866, src/memory.rs:112, :209).  ``health``: a callable returning the cohort's
+        sticky health record (``utils.health.Watchdog.state``); a poisoned cohort turns /health to 503."""
         self.cfg, self.front, self.sched, self.log = cfg, frontend, scheduler, log or EventLog()
+        self.memory, self.health_source = memory, health
         self.state = "loading"
         self.identity = identity
         self.jobs: Dict[str, Job] = {}
@@ -119,8 +125,14 @@ class Server:
 
     # ---- simple routes ------------------------------------------------------------------------
     async def health(self, request):
-        return web.json_response({"status": self.state, "identity": self.identity},
-                                 status=200 if self.state == "ready" else 503)
+        body = {"status": self.state, "identity": self.identity}
+        ok = self.state == "ready"
+        if self.health_source is not None:
+            h = self.health_source()
+            body["cohort"] = h
+            if h.get("poisoned"):
+                body["status"], ok = "poisoned", False
+        return web.json_response(body, status=200 if ok else 503)
 
     async def models(self, request):
         bad = self._auth(request)
@@ -197,6 +209,17 @@ class Server:
             req, tokens, limit, pm = self.front.prepare(body)
         except P.ProtocolError as e:
             return _err(e.status, e.code, str(e))
+        # input memory admission: what this request pins on the host until it finishes
+        hold = None
+        if self.memory is not None:
+            from ..utils.memory import CapacityError
+            need = (request.content_length or 0) + 8 * len(tokens)
+            if pm is not None:
+                need += sum(int(p.patches.numel()) * 2 for p in pm.images)
+            try:
+                hold = self.memory.reserve(need, "request input")
+            except CapacityError as e:
+                return _err(503, "insufficient_memory", str(e), {"Retry-After": "1"})
         rid = "req-" + uuid.uuid4().hex[:16]
         loop = asyncio.get_running_loop()
         q: "asyncio.Queue" = asyncio.Queue()
@@ -211,6 +234,8 @@ class Server:
         try:
             self.sched.submit(job)
         except QueueFull as e:
+            if hold is not None:
+                hold.release()
             return _err(429, e.code, "the request queue is full", {"Retry-After": "1"})
         self.jobs[rid] = job
         headers = {"x-request-id": rid, "x-native-execution-timing": "v1", "cache-control": "no-store",
@@ -221,6 +246,8 @@ class Server:
             return await self._collect(req, job, q, headers, len(tokens))
         finally:
             self.jobs.pop(rid, None)
+            if hold is not None:
+                hold.release()
 
     def _chunk(self, rid, delta, finish=None, extra=None):
         c = {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": self.cfg.model_name,

@@ -3,7 +3,7 @@
 ``serve`` runs the OpenAI-compatible server on rank 0 and a worker loop on every rank;
 ``bench`` times prefill and speculative decode; ``stage-weights`` writes this rank's weight atlas;
 ``probe`` prints the device / peer-access / build facts the engine depends on (reference:
-src/bin/titanic-flash-server.rs:49-93 Cli and subcommands, :95 entry).
+src/main.rs Cli and its subcommands).
 """
 from __future__ import annotations
 
@@ -49,6 +49,10 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--disk-cache", help="directory for the disk tier of the session cache")
     s.add_argument("--event-log", help="JSONL event log path")
     s.add_argument("--no-self-check", action="store_true", help="skip the start-up reproducibility check")
+    s.add_argument("--vision", action="store_true", help="accept image parts (the model config must describe a vision "
+                   "tower; random tower weights when the checkpoint has none)")
+    s.add_argument("--memory-floor-gib", type=float, default=4.0, help="host memory that must stay available; "
+                   "requests are refused with 429 below it")
     b = sub.add_parser("bench", help="prefill + decode timing (bench.py of the source tree)")
     b.add_argument("rest", nargs=argparse.REMAINDER)
     w = sub.add_parser("stage-weights", help="write this rank's staged weight atlas")
@@ -128,13 +132,33 @@ def make_backend(args, cfg: ModelConfig, comm):
              else oracle.init_weights(cfg, seed=args.seed))
         return OracleBackend(cfg, W, regions=args.regions, max_context=args.max_context, comm=comm)
     from .models.engine import Engine
-    ecfg = EngineConfig(regions=args.regions, max_context=args.max_context)
+    world = getattr(comm, "world", 1)
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    ecfg = EngineConfig(tp=world, regions=args.regions, max_context=args.max_context)
     if args.checkpoint:
         from .models import loader
-        eng = loader.load_engine(args.checkpoint, cfg, ecfg, comm)
+        eng = loader.load_engine(args.checkpoint, cfg, ecfg, comm, device=dev)
     else:
-        eng = Engine.random_init(cfg, ecfg, comm, seed=args.seed)
+        eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=args.seed)
+    if world > 1:
+        # the product runs what the benchmark measures: decode rows go through the fused
+        # GEMV / combine + all-reduce kernels over peer memory, not NCCL all-reduces per sublayer
+        from .parallel.symm import SymmWorkspace
+        eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev)
     return EngineBackend(eng)
+
+
+def policy_digest(cfg: ModelConfig, args, world: int) -> str:
+    """Digest of everything the ranks must agree on before they load: the model geometry and the
+    serving policy values that decide regions, context, backend and sampling determinism."""
+    import hashlib
+    from .config import agree_digest
+    h = hashlib.sha256(agree_digest([cfg]).encode())
+    for k in ("backend", "regions", "max_context", "seed", "checkpoint", "vision"):
+        h.update(f"{k}={getattr(args, k, None)!r};".encode())
+    h.update(f"world={world}".encode())
+    return h.hexdigest()
 
 
 def serve_main(args) -> int:
@@ -151,16 +175,38 @@ def serve_main(args) -> int:
     rank = int(os.environ.get("RANK", 0))
     comm = init_distributed() if world > 1 else LocalComm()
     control = None
+    scfg = ServerConfig(host=args.host, port=args.port, api_key=args.api_key, queue_limit=args.queue_limit,
+                        max_admitted=args.regions)
     if world > 1:
         control = ControlChannel.connect(rank, world, "127.0.0.1", int(os.environ.get("TFLASH_CONTROL_PORT", 29512)),
                                          os.environ.get("TFLASH_CONTROL_TICKET", "").encode())
+        # every value that shapes the deterministic command stream must be the same on all ranks
+        # before anything is loaded (reference: src/resident_worker.rs:5935-5977)
+        control.agree(policy_digest(cfg, args, world).encode())
     backend = make_backend(args, cfg, comm)
     log = EventLog(args.event_log) if args.event_log else EventLog()
     tok = load_tokenizer(args.tokenizer, cfg.vocab)
-    scfg = ServerConfig(host=args.host, port=args.port, api_key=args.api_key, queue_limit=args.queue_limit,
-                        max_admitted=args.regions)
     sched = Scheduler(scfg.max_admitted, scfg.queue_limit, scfg.background_queue_limit) if rank == 0 else None
-    worker = Worker(backend, sched, SessionCache(), eos_id=getattr(tok, "eos_id", 1), log=log, control=control, rank=rank)
+    vision_front = span_encoder = None
+    if args.vision:
+        if cfg.vision is None:
+            raise SystemExit("--vision needs a model configuration with a vision tower")
+        from .api.media import SpanEncoder, VisionFrontend
+        vision_front = VisionFrontend(tok.image_id, cfg.vision.image_token_id, cfg.vision.max_image_tokens)
+        if rank == 0:
+            from .models import vision as V
+            VW = V.init_vision_weights(cfg.vision, cfg.hidden, args.seed)
+            tower = (V.VisionTower(cfg.vision, cfg.hidden, VW, device=backend.device) if args.backend == "engine"
+                     else V.VisionOracle(cfg.vision, cfg.hidden, VW))
+            span_encoder = SpanEncoder(tower)
+    from .utils.health import Health, Watchdog, control_probe, status_probe
+    health = Health()
+    worker = Worker(backend, sched, SessionCache(), eos_id=getattr(tok, "eos_id", 1), log=log, control=control, rank=rank,
+                    span_encoder=span_encoder, health=health)
+    probes = {"control": control_probe(control)}
+    if hasattr(backend, "status_snapshot"):
+        probes["device"] = status_probe(backend.status_snapshot)
+    Watchdog(health, probes, on_poison=lambda rec: log.log("poisoned", incident=True, **rec)).start()
     if not args.no_self_check and backend.regions >= 2:
         # every rank runs the same fixture (its collectives line up); raises before the server reports ready
         from .serve.warmup import self_check
@@ -168,7 +214,12 @@ def serve_main(args) -> int:
     if rank != 0:
         worker.run_forever()
         return 0
-    server = Server(scfg, Frontend(tok, args.max_context), sched, log)
+    from .utils.memory import host_admission
+    server = Server(scfg, Frontend(tok, args.max_context, vision=vision_front), sched, log,
+                    memory=host_admission(int(args.memory_floor_gib * 2 ** 30),
+                                          log=lambda rec: log.log(rec.get("event", "memory"), incident=True,
+                                                                  **{k: v for k, v in rec.items() if k != "event"})),
+                    health=health.state)
     t = threading.Thread(target=worker.run_forever, daemon=True)
     t.start()
     server.ready(f"{cfg.digest()[:12]}/{backend.name}/tp{world}")

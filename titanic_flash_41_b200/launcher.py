@@ -2,9 +2,12 @@
 
 ``launch`` starts ``world`` copies of a module with RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* and a
 shared control ticket in the environment, pins each to the cores nearest its GPU when the
-topology is known, forwards SIGTERM / SIGINT to the exact PIDs it started, and stops the rest as
-soon as one rank exits non-zero (reference: the MPI launcher contract in
-src/bin/titanic-flash-server.rs:203-375 and the per-rank environment of run-ds41-demo.sh).
+topology is known, forwards SIGTERM / SIGINT to the exact PIDs it started, and supervises the
+cohort: a rank that fails stops the others at once; a rank that leaves cleanly while the others
+keep running gives them ``grace_s`` to follow (a coordinated shutdown), after which they are
+stopped too and the launch reports an incomplete cohort -- a tensor-parallel job cannot serve
+with a rank missing (reference: cohort health loop and coordinated stop, deploy/fleet.py:255,
+:437-458; per-rank environment of run-ds41-demo.sh).
 """
 from __future__ import annotations
 
@@ -41,8 +44,11 @@ def cores_for(rank: int, world: int, n_cores: Optional[int] = None) -> List[int]
     return block or cores
 
 
+INCOMPLETE = 70          # exit code: a rank left and the rest had to be stopped
+
+
 def launch(argv: Sequence[str], world: int, master_port: int = 29511, pin: bool = True,
-           poll_s: float = 0.2) -> int:
+           poll_s: float = 0.2, grace_s: float = 15.0, term_s: float = 10.0) -> int:
     ticket = secrets.token_hex(16)
     procs: List[subprocess.Popen] = []
     for r in range(world):
@@ -64,16 +70,31 @@ def launch(argv: Sequence[str], world: int, master_port: int = 29511, pin: bool 
     code = 0
     try:
         live = set(range(world))
+        first_exit: Optional[float] = None
+        stopping: Optional[float] = None
         while live:
             for r in list(live):
                 rc = procs[r].poll()
                 if rc is None:
                     continue
                 live.discard(r)
+                if first_exit is None:
+                    first_exit = time.monotonic()
                 if rc != 0 and code == 0:
                     code = rc
+                    stopping = stopping or time.monotonic()
                     for q in live:                       # a rank failed: the job cannot continue
                         procs[q].terminate()
+            now = time.monotonic()
+            if live and stopping is None and first_exit is not None and now - first_exit > grace_s:
+                # a rank left cleanly and the others did not follow: stop them, report the cohort incomplete
+                code = code or INCOMPLETE
+                stopping = now
+                for q in live:
+                    procs[q].terminate()
+            if live and stopping is not None and now - stopping > term_s:
+                for q in live:                           # SIGTERM was not enough
+                    procs[q].kill()
             time.sleep(poll_s)
     finally:
         for s, h in old.items():

@@ -162,10 +162,19 @@ class EngineBackend:
         self._dec: Dict[int, object] = {}
         self.max_graph_variants = 8      # decoders (one per batch size) kept with their CUDA graphs
         self._SpecDecoder, self._native = SpecDecoder, native
+        self._status_host = (0, 0, 0, 0)
         self.last_hidden_rows: Dict[int, torch.Tensor] = {}
 
     def reset(self, region: int) -> None:
         pass     # state is position-addressed: a new conversation simply overwrites it
+
+    def status_snapshot(self):
+        """Last host copy of the kernels' status word (code, kernel, detail0, detail1), refreshed by
+        the owner thread after every decode step and prefill; read by the health watchdog."""
+        return self._status_host
+
+    def _refresh_status(self) -> None:
+        self._status_host = tuple(self.e.status.read())
 
     wants_prev = True      # prefill(..., prev=tokens right before `start`)
 
@@ -173,6 +182,7 @@ class EngineBackend:
         from .prefill import run_prefill
         lg = run_prefill(self.e, region, torch.tensor(list(tokens), dtype=torch.int32), self.chunk, start,
                          True, on_chunk, prev=prev, embeds=embeds)
+        self._refresh_status()
         if lg is None:
             return None
         self.last_hidden_rows[region] = self.e.last_hidden[-1:].clone() if self.e.last_hidden is not None else None
@@ -202,6 +212,7 @@ class EngineBackend:
         out = dec.step(slots)
         for i, s in enumerate(slots):
             self.last_hidden_rows[s.region] = dec.hidden[i].clone()
+        self._refresh_status()
         return out
 
     def _views(self, region: int, length: int):

@@ -51,7 +51,7 @@ class Worker:
     def __init__(self, backend, scheduler: Optional[Scheduler], cache: Optional[SessionCache] = None,
                  eos_id: int = 1, log: Optional[EventLog] = None, control=None, rank: int = 0,
                  prefill_slice_s: float = 0.5, checkpoint_min: int = policy.SHORT_TOKENS,
-                 checkpoint_align: int = 8192, span_encoder=None):
+                 checkpoint_align: int = 8192, span_encoder=None, health=None):
         """``span_encoder`` (rank 0): ``api.media.SpanEncoder`` over the vision tower; needed to serve
         requests that carry images."""
         self.b, self.sched, self.cache = backend, scheduler, cache or SessionCache()
@@ -62,6 +62,7 @@ class Worker:
         self.running = True
         self.requests = 0
         self.span_encoder = span_encoder
+        self.health = health                 # utils.health.Health: sticky record of what stopped this rank
         self.clock = time.monotonic          # rank 0's time source for prefill slices (tests skew it)
         self.directives: List[int] = []      # per-chunk directives this rank followed (diagnostics)
 
@@ -152,9 +153,42 @@ class Worker:
         return cmd["op"]
 
     def run_forever(self) -> None:
+        """Command loop.  Any error (a poisoned control channel, a failed collective, a kernel status
+        word raised by the backend) is fatal for the rank: it is recorded in the sticky health state,
+        every request in flight gets a terminal error event, and the loop ends; the launcher's
+        supervisor then stops the rest of the cohort."""
         self._pending = []
         while self.running:
-            self.run_once()
+            try:
+                self.run_once()
+                if self.health is not None:
+                    self.health.beat()
+                    if not self.health.ok:
+                        raise RuntimeError("rank poisoned: " + str(self.health.state().get("why")))
+            except Exception as e:  # noqa: BLE001
+                if self.health is not None:
+                    self.health.report("worker", repr(e))
+                self.log.log("worker_stopped", incident=True, error=repr(e))
+                self.fail_all({"code": "cohort_failed", "message": "the serving cohort stopped: " + str(e)})
+                self.running = False
+                if self.health is None:
+                    raise
+
+    def fail_all(self, payload: Dict[str, Any]) -> None:
+        """Terminal error event for every admitted or queued request (rank 0)."""
+        for a in list(self.active.values()):
+            self._emit(a.job, "error", payload)
+            if self.sched is not None:
+                self.sched.release(a.job)
+        self.active.clear()
+        if self.sched is not None and self.rank == 0:
+            self.sched.close()
+            for q in (self.sched.fg, self.sched.bg):
+                while q:
+                    try:
+                        q.popleft().emit("error", payload)
+                    except Exception:  # noqa: BLE001
+                        pass
 
     # ---------------------------------------------------------------- execution (every rank)
     def execute(self, cmd: Dict[str, Any]) -> None:

@@ -25,7 +25,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
 # exact transcendental and division semantics are wanted in the sampling / norm kernels
-NO_FAST_MATH = {"sampling.cu", "elementwise.cu", "indexer.cu", "fused_norm.cu"}
+NO_FAST_MATH = {"sampling.cu", "sample_chunks.cu", "elementwise.cu", "indexer.cu", "fused_norm.cu"}
 
 
 def _nvcc() -> str:
@@ -77,8 +77,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> None:
     cuda_objs = [objdir / (s.stem + ".o") for s in cus]
     lib = OUT / "libtflash_cuda.so"
     if cus and _stale(lib, cuda_objs):
-        _run([nvcc, "-shared", "-o", str(lib), *map(str, cuda_objs), "-lcudart", "-lcuda"
-              ] if False else [nvcc, "-shared", "-o", str(lib), *map(str, cuda_objs)])
+        _run([nvcc, "-shared", "-o", str(lib), *map(str, cuda_objs)])
     host_objs = [objdir / (s.stem + ".host.o") for s in ccs]
     hlib = OUT / "libtflash_host.so"
     if ccs and _stale(hlib, host_objs):

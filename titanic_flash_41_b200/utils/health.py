@@ -1,0 +1,101 @@
+"""Sticky health of one rank and the watchdog that keeps it current.
+
+Everything that can make a cohort unusable ends in ONE place: the device status word of the
+kernels (a bounded wait that ran out, a bad index, a non-finite probability), a poisoned control
+channel (peer closed, frame out of order, diverging agreement), a process-group error raised by a
+collective, an exception of the worker loop.  The first report wins and stays: a poisoned rank
+never reports healthy again, it retires and the cohort is restarted from outside (reference:
+src/roce.rs:442-461 health(), src/collective.rs:255 check_async; there is no elastic recovery in
+the reference either).  ``/health`` serves the record; the launcher's supervisor stops the other
+ranks when one leaves.
+
+Nothing here touches the GPU: probes read host-side state (the status word arrives through a
+pinned copy that the owner thread refreshes between steps).
+"""
+from __future__ import annotations
+
+import threading
+import time
+from typing import Callable, Dict, Optional
+
+STATUS_CODES = {1: "bad_arg", 2: "timeout", 3: "bad_index", 4: "nonfinite"}
+
+
+class Health:
+    def __init__(self):
+        self._lock = threading.Lock()
+        self.poisoned: Optional[dict] = None
+        self.beats = 0
+        self.last_beat = time.monotonic()
+
+    def report(self, source: str, why: str) -> bool:
+        """Record a fatal condition; returns True when this call poisoned the rank (first report)."""
+        with self._lock:
+            if self.poisoned is not None:
+                return False
+            self.poisoned = {"source": source, "why": str(why), "at": round(time.time(), 3)}
+            return True
+
+    def beat(self) -> None:
+        self.beats += 1
+        self.last_beat = time.monotonic()
+
+    @property
+    def ok(self) -> bool:
+        return self.poisoned is None
+
+    def state(self) -> dict:
+        with self._lock:
+            out = {"poisoned": self.poisoned is not None, "beats": self.beats,
+                   "idle_s": round(time.monotonic() - self.last_beat, 3)}
+            if self.poisoned is not None:
+                out.update(self.poisoned)
+            return out
+
+
+def control_probe(control) -> Callable[[], Optional[str]]:
+    """Poison of the control channel (None while it is healthy or absent)."""
+    return lambda: (getattr(control, "poisoned", None) if control is not None else None)
+
+
+def status_probe(snapshot: Callable[[], Optional[tuple]]) -> Callable[[], Optional[str]]:
+    """``snapshot`` returns the last host copy of the device status word (code, kernel, d0, d1)."""
+    def probe():
+        w = snapshot()
+        if not w or int(w[0]) == 0:
+            return None
+        return f"kernel {int(w[1])} reported {STATUS_CODES.get(int(w[0]), int(w[0]))} (detail {int(w[2])}, {int(w[3])})"
+    return probe
+
+
+class Watchdog(threading.Thread):
+    """Polls the probes every ``interval`` seconds and folds the first failure into ``health``."""
+
+    def __init__(self, health: Health, probes: Dict[str, Callable[[], Optional[str]]], interval: float = 0.5,
+                 on_poison: Optional[Callable[[dict], None]] = None):
+        super().__init__(daemon=True, name="tflash-watchdog")
+        self.health, self.probes, self.interval, self.on_poison = health, dict(probes), interval, on_poison
+        self._stop = threading.Event()
+
+    def poll_once(self) -> bool:
+        for name, probe in self.probes.items():
+            try:
+                why = probe()
+            except Exception as e:  # noqa: BLE001  (a probe that fails is itself a finding)
+                why = f"probe failed: {e!r}"
+            if why and self.health.report(name, why):
+                if self.on_poison is not None:
+                    try:
+                        self.on_poison(self.health.state())
+                    except Exception:  # noqa: BLE001
+                        pass
+        return self.health.ok
+
+    def run(self) -> None:
+        while not self._stop.is_set():
+            if not self.poll_once():
+                return
+            self._stop.wait(self.interval)
+
+    def stop(self) -> None:
+        self._stop.set()
