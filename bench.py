@@ -5,10 +5,14 @@ vocab 129280, 1-layer draft head depth 3; T = 0.6, top-p = 0.95).
 
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched with torchrun)
 
-Prints ONE JSON line on rank 0.  ``value`` is the device-timed decode throughput (graph replays
-only); ``e2e`` is the same metric through ``SpecDecoder.step`` including the pinned-memory upload
-of each step's metadata and the download of its result.  Strong scaling: the model and workload
-are fixed, N GPUs share them (tensor-parallel attention, expert-parallel MoE).
+Prints ONE JSON line on rank 0.  Both numbers come from the SAME loop of ``SpecDecoder.step`` calls:
+``e2e`` is tokens over the wall time of the loop on the device clock (pinned-memory upload of each
+step's metadata, the captured step, the download of its result, host bookkeeping); ``value`` is
+the same tokens over the summed device time of the steps alone (CUDA events around every graph
+replay).  The decode starts from the KV state that the timed prefill wrote: the prompt is extended
+to the decode start and the conversation is copied into the other regions.  Strong scaling: the
+model and workload are fixed, N GPUs share them (tensor-parallel attention and expert-parallel
+MoE for decode rows, sequence-parallel prefill).
 """
 from __future__ import annotations
 
@@ -109,8 +113,9 @@ def synth_state(eng, gen):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--index-heads", type=int, default=0, help="indexer heads (flagship: 8; the reference's geometry has 32)")
     ap.add_argument("--impl", default="own")
     ap.add_argument("--model", default="flash-b200")
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (result is then not a headline number)")
@@ -145,6 +150,8 @@ def main():
     over = {}
     if args.layers:
         over = dict(n_layers=args.layers, kv_source_layers=(0,), index_source_layers=(0,), late_start=-1)
+    if args.index_heads:
+        over["index_heads"] = args.index_heads
     cfg = NAMED_MODELS[args.model](**over)
     chunk = 16384
     ecfg = EngineConfig(tp=world, regions=SESSIONS, max_context=CONTEXT + 4096, prefill_widths=(chunk,),
@@ -154,8 +161,10 @@ def main():
     from titanic_flash_41_b200.ops import bigpath
     bigpath.attach(eng)
     if world > 1:
+        from titanic_flash_41_b200.parallel import sp
         from titanic_flash_41_b200.parallel.symm import SymmWorkspace
         eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev)
+        sp.attach(eng)
     gen = torch.Generator(device=dev).manual_seed(1234)
     synth_state(eng, gen)
     torch.cuda.synchronize()
@@ -175,7 +184,7 @@ def main():
             pt = prompt.to(dev)
             dist.broadcast(pt, 0)
             prompt = pt.cpu()
-        run_prefill(eng, 0, prompt[: 2 * 1024], chunk)             # warm-up of every kernel shape
+        run_prefill(eng, 0, prompt[: chunk + 2048], chunk)         # warm-up of every kernel shape and buffer
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -193,12 +202,36 @@ def main():
                 run_prefill(eng, 0, prompt, chunk)
             if rank == 0:
                 print(kc.report(), file=sys.stderr, flush=True)
-        synth_state(eng, gen)
 
     # ------------------------------------------------------------------ decode
     start_len = CONTEXT - DECODE_TOKENS
+    state_from = "synthetic KV state at 131072 tokens"
+    last_hidden = None
+    if prefill_s is not None and args.prefill_tokens <= start_len:
+        # decode from what the prefill wrote: extend the conversation to the decode start (untimed) and
+        # copy it into the other regions
+        ext = torch.randint(0, cfg.vocab, (start_len - args.prefill_tokens,), generator=cpu_gen, dtype=torch.int32)
+        if world > 1:
+            et = ext.to(dev)
+            dist.broadcast(et, 0)
+            ext = et.cpu()
+        if ext.numel():
+            run_prefill(eng, 0, ext, chunk, start=args.prefill_tokens)
+        torch.cuda.synchronize()
+        if eng.status.read()[0] == 0:
+            for r in range(1, SESSIONS):
+                for t in (eng.win, eng.comp, eng.keys, eng.carry):
+                    t[:, r].copy_(t[:, 0])
+            if eng.last_hidden is not None:
+                last_hidden = eng.last_hidden[-1:].clone()
+            state_from = "KV state written by the timed prefill (extended to the decode start, copied to 4 regions)"
+        else:
+            eng.status.t.zero_()
+            synth_state(eng, gen)
     slots = [DecodeSlot(region=r, length=start_len, anchor=100 + r, seed=r + 1) for r in range(SESSIONS)]
     dec = SpecDecoder(eng, SESSIONS, temperature=0.6, top_p=0.95, use_graph=not args.no_graph)
+    if last_hidden is not None:
+        dec.hidden.copy_(last_hidden.reshape(1, -1)[:, -cfg.hidden:].expand(SESSIONS, cfg.hidden))
     if args.knockout:
         # capture the graph without the named families: the difference to a plain run is what they
         # cost inside the graph, dependent-launch gaps included
@@ -216,36 +249,46 @@ def main():
     for _ in range(args.warmup):
         dec.step(slots)
     barrier()
+    if eng.status.read()[0] != 0 and state_from.startswith("KV"):
+        # the prefilled state of this random-init model produced non-finite logits: fall back to the
+        # synthetic state rather than time a step that reports errors
+        eng.status.t.zero_()
+        synth_state(eng, gen)
+        state_from = "synthetic KV state at 131072 tokens (the prefilled state gave non-finite logits)"
+        slots = [DecodeSlot(region=r, length=start_len, anchor=100 + r, seed=r + 1) for r in range(SESSIONS)]
+        for _ in range(args.warmup):
+            dec.step(slots)
+        barrier()
     sampler = ClockSampler(f"/tmp/clocks_{rank}.csv")
     if rank == 0:
         sampler.start()
     # e2e: the public API, upload + graph + download every step
     tok0 = sum(len(s.emitted) for s in slots)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # exactly `steps` steps, timed in three consecutive segments (their spread is reported)
+    nseg = 3 if args.steps >= 30 else 1
+    seg_steps = [args.steps // nseg + (1 if i < args.steps % nseg else 0) for i in range(nseg)]
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(nseg + 1)]
+    dec.device_events = []
     barrier()
-    a.record()
-    for _ in range(args.steps):
-        dec.step(slots)
-    b.record()
+    marks[0].record()
+    for i, k in enumerate(seg_steps):
+        for _ in range(k):
+            dec.step(slots)
+        marks[i + 1].record()
     barrier()
-    e2e_ms = a.elapsed_time(b)
+    seg_ms = [marks[i].elapsed_time(marks[i + 1]) for i in range(nseg)]
+    e2e_ms = marks[0].elapsed_time(marks[nseg])
     tokens = sum(len(s.emitted) for s in slots) - tok0
-    # device-only: replay the captured step (no host work between launches)
-    dev_ms = None
-    if dec.graph is not None:
-        barrier()
-        a.record()
-        for _ in range(args.steps):
-            dec.graph.replay()
-        b.record()
-        barrier()
-        dev_ms = a.elapsed_time(b)
+    # device time of the very same steps: CUDA events around every step's captured graph
+    dev_ms = sum(x.elapsed_time(y) for x, y in dec.device_events)
+    dec.device_events = None
     clocks = sampler.stop(local) if rank == 0 else {}
     eng.status.check()
-    t = torch.tensor([e2e_ms, dev_ms if dev_ms is not None else e2e_ms], device=dev)
+    t = torch.tensor([e2e_ms, dev_ms] + [m / k for m, k in zip(seg_ms, seg_steps)], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms, dev_ms = float(t[0]), float(t[1])
+    seg_per_step = [round(float(v), 4) for v in t[2:]]
     if rank == 0:
         tok_per_step = tokens / args.steps
         value = tokens / (dev_ms / 1e3)
@@ -258,17 +301,23 @@ def main():
             "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4),
             "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16",
-            "data": "synthetic token ids, random-init weights, synthetic KV state at 131072 tokens",
+            "data": "synthetic token ids, random-init weights; decode from: " + state_from,
             "config": {"model": cfg.name, "layers": cfg.n_layers, "global_batch": SESSIONS,
                        "seq_len": CONTEXT, "parallelism": par, "draft_depth": dec.g,
                        "temperature": 0.6, "top_p": 0.95,
                        "tokens_per_step": round(tok_per_step, 3),
+                       "index_heads": cfg.index_heads, "index_topk": cfg.index_topk, "late_start": cfg.late_start,
+                       "kv_source_layers": list(cfg.kv_source_layers),
+                       "index_source_layers": list(cfg.index_source_layers),
+                       "prefill": ("sequence-parallel rows" if getattr(eng, "sp", None) is not None else "single rank"),
+                       "sampling": ("rank-local chunks" if dec.ws is not None else "gathered rows"),
                        "l2": "inputs larger than L2 (>= 5 GB of weights touched per step)",
                        "weights": "FP8 block-128 dense, MXFP4 experts, bf16 head (FP8 draft head)"},
             "prefill_s": None if prefill_s is None else round(prefill_s, 3),
             "prefill_tokens": args.prefill_tokens if prefill_s is not None else None,
             "prefill_vs_baseline": None if prefill_s is None else round(BASELINE_PREFILL_S / prefill_s, 3),
             "e2e": {"value": round(e2e, 2), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 4),
+                    "ms_per_step_segments": seg_per_step,
                     "h2d_bytes_per_step": dec.h2d_bytes_per_step, "d2h_bytes_per_step": dec.d2h_bytes_per_step},
             "gpu_launches": launches * args.steps,
             "gpu_launches_per_step": launches,

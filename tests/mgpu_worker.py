@@ -108,6 +108,34 @@ def main():
     srt = sorted(errs)
     assert srt[len(srt) // 2] < 0.08, errs
     say("engine ok %s" % errs)
+    # ---- 3b. sequence-parallel prefill (rows of every chunk split over the ranks) == single GPU,
+    #          and the KV state it leaves on every rank serves the tensor-parallel decode rows
+    from titanic_flash_41_b200.ops import bigpath
+    from titanic_flash_41_b200.parallel import sp as SP
+    from titanic_flash_41_b200.serve.prefill import run_prefill
+    bigpath.attach(eng)
+    bigpath.attach(ref)
+    assert SP.attach(eng) is not None
+    long_prompt = torch.randint(0, cfg.vocab, (64 * world * 3 + 37,), generator=gen, dtype=torch.int32)
+    a = run_prefill(eng, 1, long_prompt, 128)
+    b = run_prefill(ref, 1, long_prompt, 128)
+    errs_sp = [float((a - b).abs().max() / b.abs().max())]
+    p1 = int(long_prompt.numel())
+    for step in range(3):
+        toks = torch.randint(0, cfg.vocab, (4,), generator=gen).tolist()
+        a = eng.forward(E.StepPlan.build([(1, p1, toks)]))
+        b = ref.forward(E.StepPlan.build([(1, p1, toks)]))
+        errs_sp.append(float((a - b).abs().max() / b.abs().max()))
+        p1 += 4
+    torch.cuda.synchronize()
+    eng.status.check()
+    assert sorted(errs_sp)[len(errs_sp) // 2] < 0.08 and errs_sp[0] < 0.15, errs_sp
+    # every rank holds the same KV state after the gathers
+    for t in (eng.win, eng.comp, eng.keys):
+        got = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(got, t)
+        assert all(torch.equal(got[0], g_) for g_ in got)
+    say("sequence-parallel prefill ok %s" % errs_sp)
     # ---- 4. speculative decode under a CUDA graph with the fused collectives
     from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
     dec = SpecDecoder(eng, 1, temperature=0.6, top_p=0.95, use_graph=True)

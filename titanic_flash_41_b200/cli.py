@@ -146,7 +146,11 @@ def make_backend(args, cfg: ModelConfig, comm):
         # GEMV / combine + all-reduce kernels over peer memory, not NCCL all-reduces per sublayer
         from .parallel.symm import SymmWorkspace
         eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev)
-    return EngineBackend(eng)
+    backend = EngineBackend(eng)          # attaches the tensor-core prefill path
+    if world > 1:
+        from .parallel import sp
+        sp.attach(eng)                    # prefill chunks split by rows over the ranks
+    return backend
 
 
 def policy_digest(cfg: ModelConfig, args, world: int) -> str:

@@ -320,6 +320,7 @@ class EngineConfig(_JsonMixin):
     use_cuda_graphs: bool = True
     key_sharded_index_min: int = 8192  # decode rows: split index scoring over the ranks from this many keys (0 = never)
     two_level_index_min: int = 65536   # decode rows: from this many index keys on, layers after the candidate source score only its published blocks (0 = never)
+    sp_prefill: bool = True            # more than one rank: prefill chunks are split by rows over the ranks (every rank keeps the unsharded dense matrices of the encoder layers)
     moe_block_scaled: bool = True     # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
     seed: int = 0
 

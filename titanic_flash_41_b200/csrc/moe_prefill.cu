@@ -20,6 +20,8 @@ __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<__half>(const __half* p) { return __half2float(*p); }
 template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
 // four consecutive elements in one load (the address is a multiple of four elements)
 template <typename T>
 __device__ __forceinline__ void ld4(const T* p, float v[4]);
@@ -200,10 +202,10 @@ mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restri
 }
 
 // out[t,:] = sum_j wts[t,j] * y[pair_dst[t*k+j],:] (fixed j order) + shared[t,:]
-template <typename T>
+template <typename T, typename O>
 __global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const int* __restrict__ pair_dst,
                                         const float* __restrict__ wts, const float* __restrict__ shared_y,
-                                        float* __restrict__ out, int d, int topk) {
+                                        O* __restrict__ out, int d, int topk) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float acc = 0.f;
@@ -212,8 +214,35 @@ __global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const
       if (dst >= 0) acc = fmaf(wts[t * topk + j], ldf<T>(y + (long)dst * ldy + i), acc);
     }
     if (shared_y) acc += shared_y[(long)t * d + i];
-    out[(long)t * d + i] = acc;
+    stf(out + (long)t * d + i, acc);
   }
+}
+
+// out[i] = sum over w (in order) of slices[w * stride + i] (bf16) + extra[i], for i < n: the owner of
+// a row slice sums the partial outputs every rank sent for it, in rank order, in fp32
+__global__ void sum_slices_kernel(const __nv_bfloat16* __restrict__ slices, int world, long stride,
+                                  const float* __restrict__ extra, float* __restrict__ out, long n) {
+  const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int w = 0; w < world; ++w) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(slices + (long)w * stride + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      acc[2 * j] += f.x;
+      acc[2 * j + 1] += f.y;
+    }
+  }
+  if (extra) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += extra[i + j];
+  }
+  *reinterpret_cast<float4*>(out + i) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  *reinterpret_cast<float4*>(out + i + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
 }  // namespace
@@ -265,10 +294,29 @@ TF_API int tf_mxfp4_to_fp8_block(const void* w, const void* sc, void* out, float
   return (int)cudaGetLastError();
 }
 
+// out_kind: 0 = fp32, 2 = bf16
 TF_API int tf_moe_combine_perm(const void* y, int y_kind, long ldy, const int* pair_dst, const float* wts,
-                               const float* shared_y, float* out, int T, int d, int topk, cudaStream_t st) {
-  if (y_kind == 0) moe_combine_perm_kernel<float><<<T, 256, 0, st>>>((const float*)y, ldy, pair_dst, wts, shared_y, out, d, topk);
-  else if (y_kind == 2) moe_combine_perm_kernel<__nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, out, d, topk);
+                               const float* shared_y, void* out, int out_kind, int T, int d, int topk,
+                               cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (!y || !pair_dst || !wts || !out) return -1;
+  if (y_kind == 0 && out_kind == 0) moe_combine_perm_kernel<float, float><<<T, 256, 0, st>>>((const float*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
+  else if (y_kind == 2 && out_kind == 0) moe_combine_perm_kernel<__nv_bfloat16, float><<<T, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
+  else if (y_kind == 2 && out_kind == 2) moe_combine_perm_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (__nv_bfloat16*)out, d, topk);
   else return -1;
+  return (int)cudaGetLastError();
+}
+
+// out[i] = sum_w slices[w][i] (bf16, fixed order w = 0..world-1, fp32 accumulation) + extra[i] (fp32, optional)
+// for i < n; `stride` = elements between consecutive slices.  n, stride multiples of 8; 16-byte aligned.
+TF_API int tf_sum_slices(const void* slices, int world, long stride, const float* extra, float* out, long n,
+                         cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (!slices || !out || world < 1 || n % 8 || stride % 8 || (reinterpret_cast<uintptr_t>(slices) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15) || (extra && (reinterpret_cast<uintptr_t>(extra) & 15)))
+    return -1;
+  const long threads = n / 8;
+  sum_slices_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)slices, world, stride, extra,
+                                                                        out, n);
   return (int)cudaGetLastError();
 }

@@ -78,6 +78,10 @@ class LayerWeights:
     wq_b: Optional[Fp8Weight] = None
     wo_a: Optional[List[Fp8Weight]] = None         # grouped output projection: one [rank, per] per local group
     hc: Optional[Dict[str, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]] = None   # "attn"/"ffn" -> (fn, base, scale)
+    # unsharded dense matrices of this layer (all heads, full shared expert) for the sequence-parallel
+    # prefill, where every rank runs whole rows through the dense sublayers (reference: the derived
+    # full matrices of SP layers, src/staged_full.rs)
+    full: Optional["LayerWeights"] = None
 
 
 def quant_fp8_device(w: torch.Tensor) -> Fp8Weight:
@@ -149,9 +153,11 @@ def _layer_prefix(cfg: ModelConfig, li: int) -> str:
 
 
 def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: int, world: int,
-                  device, roundtrip: Optional[Dict[str, torch.Tensor]] = None) -> LayerWeights:
+                  device, roundtrip: Optional[Dict[str, torch.Tensor]] = None, keep_full: bool = False
+                  ) -> LayerWeights:
     """Quantise one layer's shard from an fp32/bf16 weight dict (full, unsharded tensors) and, when
-    ``roundtrip`` is given, record the dequantised full tensors there for the oracle."""
+    ``roundtrip`` is given, record the dequantised full tensors there for the oracle.  ``keep_full``
+    also keeps the unsharded dense matrices (``L.full``) for the sequence-parallel prefill."""
     p = _layer_prefix(cfg, li)
     draft = li >= cfg.n_layers
     H, Dh, d = cfg.n_heads, cfg.head_dim, cfg.hidden
@@ -195,14 +201,26 @@ def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: i
         rt(f"{p}.attn.indexer.wq.weight", quant_fp8_device(segs[-1][1]))
         segs.append(("iw", dev(W[f"{p}.attn.indexer.weights_proj.weight"])))
         rt(f"{p}.attn.indexer.weights_proj.weight", quant_fp8_device(segs[-1][1]))
-    qs, ss, off = [], [], 0
-    for nm, t in segs:
-        fw = quant_fp8_device(t)
-        L.offs[nm] = off
-        off += fw.q.shape[0]
-        qs.append(fw.q)
-        ss.append(fw.s)
-    L.proj = Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d)
+    def fuse(segments):
+        qs, ss, off, offs = [], [], 0, {}
+        for nm, t in segments:
+            fw = quant_fp8_device(t)
+            offs[nm] = off
+            off += fw.q.shape[0]
+            qs.append(fw.q)
+            ss.append(fw.s)
+        return Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d), offs
+    L.proj, L.offs = fuse(segs)
+    full_ok = keep_full and world > 1 and not cfg.q_lora_rank and not cfg.o_groups and not draft
+    F = LayerWeights() if full_ok else None
+    if full_ok:
+        F.proj, F.offs = fuse([("q", dev(W[f"{p}.attn.wq.weight"]))] + segs[1:])
+        F.wo = quant_fp8_device(dev(W[f"{p}.attn.wo.weight"]))
+        if cfg.attn_sink:
+            F.sink = dev(W[f"{p}.attn.attn_sink"], torch.float32).contiguous()
+        if cfg.n_shared:
+            F.sw1, F.sw3, F.sw2 = (quant_fp8_device(dev(W[f"{p}.ffn.shared_experts.{nm}.weight"]))
+                                   for nm in ("w1", "w3", "w2"))
     if cfg.o_groups:
         # grouped low-rank output projection: this rank's groups of wo_a (block-diagonal), then the
         # matching K-slice of wo_b
@@ -252,14 +270,24 @@ def prepare_layer(cfg: ModelConfig, W: Dict[str, torch.Tensor], li: int, rank: i
             rt(f"{p}.ffn.shared_experts.{nm}.weight", quant_fp8_device(full))
             sl = full[:, rank * Il:(rank + 1) * Il] if nm == "w2" else full[rank * Il:(rank + 1) * Il]
             setattr(L, "s" + nm, quant_fp8_device(sl.contiguous()))
+    if full_ok:
+        for nm in ("attn_norm", "ffn_norm", "kv_norm", "comp_norm", "gate", "gate_bias", "gate_bias_vl", "ew1", "ew3",
+                   "ew2", "es1", "es3", "es2", "is_kv_source", "is_index_source", "kv_source", "index_source"):
+            setattr(F, nm, getattr(L, nm))
+        L.full = F
     return L
 
 
-def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed: int) -> LayerWeights:
+def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed: int,
+                 keep_full: bool = False) -> LayerWeights:
     """Random-init one layer's shard directly on the device in its quantised storage formats
     (the full-size model never exists in fp32): dense weights are N(0, init_std) quantised to
-    block-128 FP8; expert nibbles are uniform random e2m1 codes with a fixed 2^-7 group scale."""
-    g = torch.Generator(device=device).manual_seed(seed * 1000 + li * 16 + rank)
+    block-128 FP8; expert nibbles are uniform random e2m1 codes with a fixed 2^-7 group scale.
+    Dense and replicated tensors come from a generator that does not depend on the rank: every rank
+    draws the same full matrix and keeps its slice, so replicated tensors agree across ranks and a
+    rank's shard is a slice of the full matrix (``keep_full`` keeps that matrix as ``L.full``)."""
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + li * 16)
+    ge = torch.Generator(device=device).manual_seed(seed * 1000 + li * 16 + 1 + rank)     # this rank's experts
     H, Dh, d = cfg.n_heads, cfg.head_dim, cfg.hidden
     Hl, El = H // world, cfg.n_experts // world
     draft = li >= cfg.n_layers
@@ -277,25 +305,37 @@ def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed:
         L.wq_b = quant_fp8_device(rnd(Hl * Dh, cfg.q_lora_rank))
         L.q_norm = torch.ones(cfg.q_lora_rank, dtype=torch.bfloat16, device=device)
     else:
-        segs = [("q", rnd(Hl * Dh, d)), ("kv", rnd(Dh, d))]
+        wq_full = rnd(H * Dh, d)
+        segs = [("q", wq_full[rank * Hl * Dh:(rank + 1) * Hl * Dh]), ("kv", rnd(Dh, d))]
     if L.is_kv_source:
         segs += [("cv", rnd(Dh + cfg.index_dim, d)), ("cg", rnd(Dh + cfg.index_dim, d))]
     if L.is_index_source:
         segs += [("iq", rnd(cfg.index_heads * cfg.index_dim, d)), ("iw", rnd(cfg.index_heads, d, 1 / math.sqrt(d)))]
-    qs, ss, off = [], [], 0
-    for nm, t in segs:
-        fw = quant_fp8_device(t)
-        L.offs[nm] = off
-        off += fw.q.shape[0]
-        qs.append(fw.q)
-        ss.append(fw.s)
-    L.proj = Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d)
+
+    def fuse(segments):
+        qs, ss, off, offs = [], [], 0, {}
+        for nm, t in segments:
+            fw = quant_fp8_device(t)
+            offs[nm] = off
+            off += fw.q.shape[0]
+            qs.append(fw.q)
+            ss.append(fw.s)
+        return Fp8Weight(torch.cat(qs).contiguous(), torch.cat(ss).contiguous(), off, d), offs
+    L.proj, L.offs = fuse(segs)
+    full_ok = keep_full and world > 1 and not cfg.q_lora_rank and not cfg.o_groups and not draft
+    F = LayerWeights() if full_ok else None
+    if full_ok:
+        F.proj, F.offs = fuse([("q", wq_full)] + segs[1:])
     if cfg.o_groups:
         G, R = cfg.o_groups // world, cfg.o_lora_rank
         L.wo_a = [quant_fp8_device(rnd(R, Hl * Dh // G)) for _ in range(G)]
         L.wo = quant_fp8_device(rnd(d, G * R))
     else:
-        L.wo = quant_fp8_device(rnd(d, Hl * Dh))
+        wo_full = rnd(d, H * Dh)
+        L.wo = quant_fp8_device(wo_full[:, rank * Hl * Dh:(rank + 1) * Hl * Dh].contiguous())
+        if full_ok:
+            F.wo = quant_fp8_device(wo_full)
+        del wo_full
     if cfg.hc_mult > 1:
         m = cfg.hc_mult
         L.hc = {br: ((torch.randn(m * (2 + m), m * d, generator=g, device=device) * cfg.init_std).contiguous(),
@@ -305,20 +345,34 @@ def random_layer(cfg: ModelConfig, li: int, rank: int, world: int, device, seed:
     if L.is_kv_source:
         L.comp_norm = ones(Dh)
     if cfg.attn_sink:
-        L.sink = torch.randn(Hl, generator=g, device=device) * 0.5
+        sink_full = torch.randn(H, generator=g, device=device) * 0.5
+        L.sink = sink_full[rank * Hl:(rank + 1) * Hl].contiguous()
+        if full_ok:
+            F.sink = sink_full
     L.gate = rnd(cfg.n_experts, d, 1 / math.sqrt(d)).contiguous()
     if cfg.router_bias:
         L.gate_bias = torch.zeros(cfg.n_experts, device=device)
     I = cfg.moe_inter
     for nm, n, k in (("w1", I, d), ("w3", I, d), ("w2", d, I)):
-        pk = torch.randint(0, 256, (El, n, k // 2), generator=g, device=device, dtype=torch.uint8)
+        pk = torch.randint(0, 256, (El, n, k // 2), generator=ge, device=device, dtype=torch.uint8)
         sc = torch.full((El, n, k // 32), 120, dtype=torch.uint8, device=device)
         setattr(L, "e" + nm, pk)
         setattr(L, "es" + nm[1], sc)
     if cfg.n_shared:
-        Il = cfg.shared_inter * cfg.n_shared // world
-        L.sw1, L.sw3 = quant_fp8_device(rnd(Il, d)), quant_fp8_device(rnd(Il, d))
-        L.sw2 = quant_fp8_device(rnd(d, Il))
+        Is = cfg.shared_inter * cfg.n_shared
+        Il = Is // world
+        s1, s3, s2 = rnd(Is, d), rnd(Is, d), rnd(d, Is)
+        L.sw1 = quant_fp8_device(s1[rank * Il:(rank + 1) * Il])
+        L.sw3 = quant_fp8_device(s3[rank * Il:(rank + 1) * Il])
+        L.sw2 = quant_fp8_device(s2[:, rank * Il:(rank + 1) * Il].contiguous())
+        if full_ok:
+            F.sw1, F.sw3, F.sw2 = quant_fp8_device(s1), quant_fp8_device(s3), quant_fp8_device(s2)
+    if full_ok:
+        # everything that is replicated anyway is shared with the sharded view
+        for nm in ("attn_norm", "ffn_norm", "kv_norm", "comp_norm", "gate", "gate_bias", "gate_bias_vl", "ew1", "ew3",
+                   "ew2", "es1", "es3", "es2", "is_kv_source", "is_index_source", "kv_source", "index_source"):
+            setattr(F, nm, getattr(L, nm))
+        L.full = F
     return L
 
 
@@ -452,6 +506,8 @@ class Engine:
         self._side: Optional[torch.cuda.Stream] = None     # parallel branch for the shared expert (decode rows)
         # hashed n-gram memory, one entry per Engram layer: (table, wkv, q_weight, k_weight)
         self.engram: List[tuple] = self.draft_extra.get("engram", [])
+        self.sp = None              # parallel.sp.SpPrefill: sequence-parallel prefill over the ranks
+        self.after_prep = None      # hook run between the KV store and the indexer / attention of a layer
         self.big_gemm = None        # set by ops.bigpath when the tcgen05 path is attached
         self.symm = None            # SymmWorkspace: fused GEMV/combine + all-reduce over peer memory
         self.last_hidden: Optional[torch.Tensor] = None
@@ -462,8 +518,9 @@ class Engine:
                      comm: Optional[Comm] = None, device="cuda", roundtrip: Optional[dict] = None,
                      max_chunk: int = 0) -> "Engine":
         comm = comm or LocalComm()
-        layers = [prepare_layer(cfg, W, li, comm.rank, comm.world, device, roundtrip)
-                  for li in range(cfg.n_layers)]
+        late = cfg.late_start if 0 < cfg.late_start < cfg.n_layers else cfg.n_layers
+        layers = [prepare_layer(cfg, W, li, comm.rank, comm.world, device, roundtrip,
+                                keep_full=ecfg.sp_prefill and li < late) for li in range(cfg.n_layers)]
         drafts, extra = [], {}
         if cfg.draft is not None and "mtp.0.main_proj.weight" in W:
             drafts = [prepare_layer(cfg, W, cfg.n_layers + j, comm.rank, comm.world, device, roundtrip)
@@ -525,7 +582,9 @@ class Engine:
     def random_init(cls, cfg: ModelConfig, ecfg: EngineConfig, comm: Optional[Comm] = None,
                     device="cuda", seed: int = 0, max_chunk: int = 0) -> "Engine":
         comm = comm or LocalComm()
-        layers = [random_layer(cfg, li, comm.rank, comm.world, device, seed) for li in range(cfg.n_layers)]
+        late = cfg.late_start if 0 < cfg.late_start < cfg.n_layers else cfg.n_layers
+        layers = [random_layer(cfg, li, comm.rank, comm.world, device, seed, keep_full=ecfg.sp_prefill and li < late)
+                  for li in range(cfg.n_layers)]
         drafts, extra = [], {}
         g = torch.Generator(device=device).manual_seed(seed + 7)
         d = cfg.hidden
@@ -722,6 +781,8 @@ class Engine:
                     self.comp[slot] if L.is_kv_source else None,
                     self.keys[slot] if L.is_kv_source else None, self.maxC, b["iq"], b["iw"],
                     self.status.t)
+        if self.after_prep is not None:
+            self.after_prep(li, L, T, b)
         comp = None
         sel = selcnt = None
         if L.kv_source >= 0:

@@ -58,7 +58,9 @@ class BigPath:
         native.call("tf_swiglu_rows", y, 2, 2 * N, out, out.stride(0), None, None, M, N, eng.cfg.swiglu_limit, None)
 
     # ---- routed experts ---------------------------------------------------------------------
-    def moe(self, eng, L, T: int, b: dict) -> None:
+    def moe(self, eng, L, T: int, b: dict, with_shared: bool = True, out: Optional[torch.Tensor] = None) -> None:
+        """Routed experts of this rank (+ the shared expert) over the T rows in ``b`` -> ``b['delta']``
+        (fp32), or -> ``out`` (bf16 or fp32 [T, hidden]) when given."""
         cfg = eng.cfg
         d, I, El, k = cfg.hidden, cfg.moe_inter, eng.El, cfg.topk
         npairs = T * k
@@ -118,11 +120,13 @@ class BigPath:
         native.call("tf_gemm_tc", 2, aq, I, w2, I, y2, d, cap, d, I, aqs, I // 128, s2, I // 128, 2,
                     tile_e, ntile[0:1], El, st)
         shared = None
-        if cfg.n_shared:
+        if cfg.n_shared and with_shared:
             eng._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
             eng._linear(b["s_act"], L.sw2, b["s_y"], T)
             shared = b["s_y"]
-        native.call("tf_moe_combine_perm", y2, 2, d, pair_dst, b["wts"], shared, b["delta"], T, d, k)
+        dst = b["delta"] if out is None else out
+        native.call("tf_moe_combine_perm", y2, 2, d, pair_dst, b["wts"], shared, dst,
+                    2 if dst.dtype == torch.bfloat16 else 0, T, d, k)
 
 
 def attach(engine) -> BigPath:

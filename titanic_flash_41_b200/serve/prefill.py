@@ -94,6 +94,56 @@ def _encoder_layer_major(eng: Engine, region: int, toks: np.ndarray, sizes: List
     return True
 
 
+def _encoder_sequence_parallel(eng: Engine, region: int, toks: np.ndarray, chunk: int, start: int, late: int,
+                               tail: torch.Tensor, tail_n: int, embeds=None, on_chunk=None) -> bool:
+    """Encoder layers [0, late) with every chunk's rows split over the ranks (``parallel/sp.py``),
+    layer by layer over all chunks like the single-rank sweep above.  Every rank keeps the residual
+    rows of ITS slices between layers; the KV state ends up identical on all ranks."""
+    cfg, sp = eng.cfg, eng.sp
+    n = int(toks.shape[0])
+    sizes = sp.chunk_sizes(n, chunk)
+    offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    d = cfg.hidden
+    resid: List[Optional[torch.Tensor]] = [None] * len(sizes)
+    sel_store: dict = {}
+    for li in range(late):
+        Lw = sp.view.layers[li]
+        src = Lw.index_source if Lw.kv_source >= 0 else -1
+        for c, Tc in enumerate(sizes):
+            lo, hi, _ = sp.bounds(Tc)
+            sel_in = None
+            if src >= 0 and not Lw.is_index_source and hi > lo:
+                sel_in = (src, sel_store[src][c][0], sel_store[src][c][1])
+            xp = _patch_for(embeds, int(offs[c]) + lo, hi - lo, eng.dev) if (li == 0 and hi > lo) else None
+            b, lo, T = sp.run_layer(li, region, start + int(offs[c]), Tc, toks[offs[c]:offs[c + 1]],
+                                    None if li == 0 else resid[c], xp, sel_in)
+            if T > 0:
+                # x + pending sublayer output, rounded once to bf16
+                resid[c] = (sp.view.residual_rows(b, slice(0, T)) if b.get("pending") else b["x"][:T].clone())
+                if Lw.is_index_source:
+                    if li not in sel_store:
+                        sel_store.clear()             # followers only ever read the latest source
+                        sel_store[li] = {}
+                    sel_store[li][c] = (b["sel"][li][:T].clone(), b["selcnt"][li][:T].clone())
+            if on_chunk is not None and not on_chunk(int(offs[c + 1]) if li == late - 1 else 0):
+                return False
+    # the rows the late group replays (and a head that follows directly) come from the last chunk(s)
+    last = len(sizes) - 1
+    full_last = sp.gather_rows(resid[last], sizes[last], d, torch.bfloat16).clone()
+    if tail_n > 0:
+        if sizes[last] >= tail_n:
+            tail[:tail_n].copy_(full_last[sizes[last] - tail_n:])
+        else:
+            prev = sp.gather_rows(resid[last - 1], sizes[last - 1], d, torch.bfloat16)
+            tail[:tail_n].copy_(torch.cat([prev, full_last])[-tail_n:])
+    T = sizes[-1]
+    b = eng._bufs(T)
+    b["x"][:T].copy_(full_last)
+    b["pending"] = False
+    eng._sp_last_rows = T
+    return True
+
+
 def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, need_logits: bool = True,
                 on_chunk: Optional[Callable[[int], bool]] = None,
                 widths: Optional[Sequence[int]] = None, layer_major: Optional[bool] = None,
@@ -115,7 +165,15 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
         layer_major = len(sizes) > 1 and getattr(eng, "big_moe_full", None) is not None
     done = 0
     logits = None
-    if layer_major:
+    if getattr(eng, "sp", None) is not None and eng.sp.usable(start, n):
+        # more than one rank: the rows of every chunk are split over the ranks
+        if not _encoder_sequence_parallel(eng, region, toks, chunk, start, late, tail, tail_n, embeds, on_chunk):
+            return None
+        if late == L and need_logits:
+            Tl = eng._sp_last_rows
+            logits = eng._head(Tl, eng._bufs(Tl), torch.tensor([Tl - 1], device=eng.dev))
+        sizes = []
+    elif layer_major:
         if not _encoder_layer_major(eng, region, toks, sizes, start, late, tail, tail_n, embeds, on_chunk, prev):
             return None
         if late == L and need_logits:

@@ -137,6 +137,9 @@ class SpecDecoder:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.nmax_bucket = 0
         self.steps = 0
+        # when a list: (start, end) CUDA events around the device work of every step (uploads and the
+        # result download excluded), for callers that report device time of exactly the steps they ran
+        self.device_events: Optional[list] = None
 
     # ---------------------------------------------------------------------------------
     def _fill_host(self, slots: Sequence[DecodeSlot]) -> int:
@@ -251,9 +254,13 @@ class SpecDecoder:
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
                     self._device_step(bucket)
+            ev = self._mark()
             self.graph.replay()
         else:
+            ev = self._mark()
             self._device_step(bucket)
+        if ev is not None:
+            ev[1].record()
         self.h_out.copy_(self.d_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.steps += 1
@@ -269,6 +276,14 @@ class SpecDecoder:
             s.anchor = nxt[i]
             out.append(toks)
         return out
+
+    def _mark(self):
+        if self.device_events is None:
+            return None
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ev[0].record()
+        self.device_events.append(ev)
+        return ev
 
     @property
     def h2d_bytes_per_step(self) -> int:
