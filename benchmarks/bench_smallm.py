@@ -60,43 +60,7 @@ def main():
         native.call("tf_smallm_gemm", 0, fw.q, None, fw.s, None, 0, 0, d, fw.s.shape[1], h16, d, yd, d * 2, 0, d * 2, d, T,
                     None, None, None, None, None, 1, 0, T, 0.0)
 
-    # FP8-activation variants on the quad-packed layout (random nibbles: packing them is a no-op for timing)
-    xq = torch.zeros(T, d, dtype=torch.uint8, device=dev)
-    xs = torch.zeros(T, device=dev)
-    aq = torch.zeros(npairs, I, dtype=torch.uint8, device=dev)
-    as_ = torch.zeros(npairs, device=dev)
-
-    def fc1_w4a8():
-        native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
-        native.call("tf_smallm_gemm_w4a8", w1, w3, s1, s3, I * (d // 2), I * (d // 32), d // 2, d // 32, xq, d, xs, act, I,
-                    1, I, d, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0, 0)
-
-    def fc2_w4a8():
-        native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
-        native.call("tf_smallm_gemm_w4a8", w2, None, s2, None, d * (I // 2), d * (I // 32), I // 2, I // 32, aq, I, as_, y,
-                    d, 0, d, I, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, 0)
-
-    def fc1_sm():
-        native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
-        native.call("tf_smallm_gemm_w4a8", w1, w3, s1, s3, I * (d // 2), I * (d // 32), 64, 4, xq, d, xs, act, I,
-                    1, I, d, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0, 1)
-
-    def fc2_sm():
-        native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
-        native.call("tf_smallm_gemm_w4a8", w2, None, s2, None, d * (I // 2), d * (I // 32), 64, 4, aq, I, as_, y,
-                    d, 0, d, I, 0, g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, 1)
-
     stw = native.StatusWord(dev)
-
-    def fc1_tma():
-        native.call("tf_quant_rows_e4m3_perm", h16, d, xq, d, xs, T, d)
-        native.call("tf_moe_gemv_w4a8_tma", w1, w3, s1, s3, El, d // 2, d // 32, I * (d // 32), xq, d, xs, act, I, 1, I, d,
-                    g_expert, g_start, g_count, n_groups, sorted_pairs, k, slots, 10.0, stw.t)
-
-    def fc2_tma():
-        native.call("tf_quant_rows_e4m3_perm", act, I, aq, I, as_, npairs, I)
-        native.call("tf_moe_gemv_w4a8_tma", w2, None, s2, None, El, I // 2, I // 32, d * (I // 32), aq, I, as_, y, d, 0, d, I,
-                    g_expert, g_start, g_count, n_groups, sorted_pairs, 1, slots, 0.0, stw.t)
 
     # block-scaled tensor-core form: MXFP8 activations, the MMA consumes nibbles and scales
     x8 = torch.zeros(T, d, dtype=torch.uint8, device=dev)
@@ -116,12 +80,6 @@ def main():
     print(f"# peaks ({pk['source']}): HBM {pk['hbm_gbs']} GB/s; {used} of {El} experts hit by {npairs} pairs")
     for name, fn, nbytes in (("moe_fc1_mxfp4_dual", fc1, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_mxfp4", fc2, used * d * (I // 2 + I // 32)),
-                             ("moe_fc1_w4a8_dual (+quant)", fc1_w4a8, used * 2 * I * (d // 2 + d // 32)),
-                             ("moe_fc2_w4a8 (+quant)", fc2_w4a8, used * d * (I // 2 + I // 32)),
-                             ("moe_fc1_w4a8 step-major (+quant)", fc1_sm, used * 2 * I * (d // 2 + d // 32)),
-                             ("moe_fc2_w4a8 step-major (+quant)", fc2_sm, used * d * (I // 2 + I // 32)),
-                             ("moe_fc1_w4a8_tma_dual (+quant)", fc1_tma, used * 2 * I * (d // 2 + d // 32)),
-                             ("moe_fc2_w4a8_tma (+quant)", fc2_tma, used * d * (I // 2 + I // 32)),
                              ("moe_fc1_mx_tcgen05_dual (+quant)", fc1_mx, used * 2 * I * (d // 2 + d // 32)),
                              ("moe_fc2_mx_tcgen05 (input quantised by FC1)", fc2_mx, used * d * (I // 2 + I // 32)),
                              # same bytes read as [128 x 128] blocks of 8 KB (random nibbles: timing only)

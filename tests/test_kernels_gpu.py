@@ -341,56 +341,6 @@ def test_key_sharded_selection_equals_unsharded(world):
     assert torch.equal(ids, want)
 
 
-@pytest.mark.parametrize("tma", [False, True])
-@pytest.mark.parametrize("dual,rows_per", [(True, 3), (False, 11), (True, 16), (False, 40), (True, 40)])
-def test_w4a8_expert_gemv_matches_reference(dual, rows_per, tma):
-    """Quad-packed MXFP4 weights x FP8 activations (m16n8k32 tensor-core steps, one scale group each)
-    against fp32 math on the dequantised weights and the dequantised FP8 activations."""
-    from titanic_flash_41_b200.models import engine as E
-    torch.manual_seed(3)
-    El, N, K, T, k = 4, 256, 512, rows_per, 2
-    w1 = torch.randn(El, N, K, device=DEV) * 0.1
-    w3 = torch.randn(El, N, K, device=DEV) * 0.1
-    p1, s1 = E.quant_mxfp4_device(w1)
-    p3, s3 = E.quant_mxfp4_device(w3)
-    d1, d3 = E.dequant_mxfp4(p1, s1), E.dequant_mxfp4(p3, s3)
-    assert torch.equal(E.quad_unpack(E.quad_pack(p1)), p1)
-    ids = torch.stack([torch.randperm(El, device=DEV)[:k] for _ in range(T)]).int().contiguous()
-    npairs = T * k
-    i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=DEV)
-    ge, gs, gc, ng, sp, nl = i32(El), i32(El), i32(El), i32(1), i32(npairs), i32(1)
-    native.call("tf_route_group", ids, npairs, 0, El, ge, gs, gc, ng, sp, nl)
-    x = torch.randn(T, K, device=DEV).half()
-    xq = torch.zeros(T, K, dtype=torch.uint8, device=DEV)
-    xs = torch.zeros(T, device=DEV)
-    native.call("tf_quant_rows_e4m3_perm", x, K, xq, K, xs, T, K)
-    # undo the 8-run order for the reference: stored [x0 x2 x4 x6 x1 x3 x5 x7]
-    xd = xq.view(torch.float8_e4m3fn).float().view(T, K // 8, 2, 4).transpose(2, 3).reshape(T, K) * xs[:, None]
-    assert (xd - x.float()).abs().max() <= 0.07 * x.float().abs().max()
-    y = torch.zeros(npairs, N, device=DEV)
-    if tma:
-        st = native.StatusWord(DEV)
-        native.call("tf_moe_gemv_w4a8_tma", E.quad_pack(p1), E.quad_pack(p3) if dual else None, s1, s3 if dual else None,
-                    El, K // 2, K // 32, N * (K // 32), xq, K, xs, y, N, 0, N, K, ge, gs, gc, ng, sp, k,
-                    min(El, npairs), 10.0 if dual else 0.0, st.t)
-        torch.cuda.synchronize()
-        st.check()
-    else:
-        native.call("tf_smallm_gemm_w4a8", E.quad_pack(p1), E.quad_pack(p3) if dual else None, s1, s3 if dual else None,
-                    N * (K // 2), N * (K // 32), K // 2, K // 32, xq, K, xs, y, N, 0, N, K, 0, ge, gs, gc, ng, sp, k,
-                    min(El, npairs), 10.0 if dual else 0.0, 0)
-    torch.cuda.synchronize()
-    for t in range(T):
-        for j in range(k):
-            e = int(ids[t, j])
-            a = d1[e] @ xd[t]
-            if dual:
-                up = (d3[e] @ xd[t]).clamp(-10, 10)
-                a = torch.nn.functional.silu(a.clamp(max=10)) * up
-            got = y[t * k + j]
-            assert (got - a).abs().max() <= 2e-3 * a.abs().max() + 1e-4, (t, j)
-
-
 @pytest.mark.parametrize("T", [1, 5, 16, 19])
 def test_router_logits_small_matches_fp32(T):
     torch.manual_seed(T)

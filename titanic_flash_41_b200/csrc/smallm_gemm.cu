@@ -59,31 +59,7 @@ struct SmallMParams {
   int use_comm;              // 0 = off, 1 = bf16 transport, 2 = fp32 transport
   CommParams comm;
   RowEpilogue ep;
-  // kind 3: X is e4m3 bytes (ldx in bytes), every 8 consecutive k stored as x0 x2 x4 x6 x1 x3 x5 x7,
-  // with one fp32 scale per activation row
-  const float* x_scale;
-  // kind 3: byte distance between consecutive 128-k steps of one weight row / of its scale word
-  // (64 and 4 = plain row-major; N*64 and N*4 = the k-step-major layout, where the 16 rows of a
-  // tile are adjacent and every step of a tile is one contiguous kilobyte)
-  long kstep, s_kstep;
 };
-
-// m16n8k32 e4m3 x e4m3 -> f32 with a zero C operand (each k32 step is one MXFP4 scale group,
-// scaled into the running sum by the caller)
-__device__ __forceinline__ void mma_e4m3_16832(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-  const float z = 0.f;
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%10,%10,%10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
-}
-// four e2m1 nibbles, one per byte (low 4 bits) -> four e4m3 bytes holding value * 2^-6:
-// sign to bit 7, the 3 magnitude bits into exponent-low / mantissa-high (exact, subnormal included)
-__device__ __forceinline__ uint32_t e2m1x4_to_e4m3x4(uint32_t x) {
-  return ((x << 4) & 0x80808080u) | ((x << 2) & 0x1c1c1c1cu);
-}
 
 __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], const uint32_t b[2]) {
   asm volatile(
@@ -123,8 +99,7 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
   for (int m = 0; m < MT; ++m) {
     const int r = min(row_base + m * 8 + g, rows - 1);
     const int xr = pairs ? pairs[r] / p.x_div : r;
-    xrow[m] = (KIND == 3) ? reinterpret_cast<const __half*>(reinterpret_cast<const uint8_t*>(p.X) + (long)xr * p.ldx)
-                          : p.X + (long)xr * p.ldx;
+    xrow[m] = p.X + (long)xr * p.ldx;
   }
   // tile ti -> matrix (ti >> 1), 16-row half (ti & 1)
   const uint8_t* wrow0[NT];
@@ -249,64 +224,6 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
         }
       }
     }
-  } else if (KIND == 3) {
-    // ---------------- MXFP4 weights in the quad-packed layout x e4m3 activations.
-    // Within every 64-byte run of a weight row (128 k = 4 scale groups) the 4-byte words are
-    // stored transposed: lane t's 16-byte load holds, for each group j, that group's nibbles
-    // 8t..8t+7.  One m16n8k32 then covers exactly one scale group; its result is scaled by the
-    // row's UE8M0 factor and added to the running sum.  Conversion is two shifts and two masks
-    // per four weights.
-    const uint8_t* srow0[NT];
-    const uint8_t* srow8[NT];
-#pragma unroll
-    for (int ti = 0; ti < NT; ++ti) {
-      const uint8_t* sb = reinterpret_cast<const uint8_t*>((ti >> 1) ? S3g : Sg);
-      srow0[ti] = sb + (long)(n0 + 16 * (ti & 1) + g) * p.lds;
-      srow8[ti] = srow0[ti] + 8L * p.lds;
-    }
-    const uint8_t* xb[MT];
-#pragma unroll
-    for (int m = 0; m < MT; ++m) xb[m] = reinterpret_cast<const uint8_t*>(xrow[m]);
-    for (int kb = k0; kb < k1; kb += 128) {
-      uint4 w0[NT], w8[NT];
-      uint32_t c0[NT], c8[NT];
-#pragma unroll
-      for (int ti = 0; ti < NT; ++ti) {
-        w0[ti] = ld_stream(wrow0[ti] + (kb >> 7) * p.kstep + t * 16);
-        w8[ti] = ld_stream(wrow8[ti] + (kb >> 7) * p.kstep + t * 16);
-        c0[ti] = __ldg(reinterpret_cast<const uint32_t*>(srow0[ti] + (kb >> 7) * p.s_kstep));
-        c8[ti] = __ldg(reinterpret_cast<const uint32_t*>(srow8[ti] + (kb >> 7) * p.s_kstep));
-      }
-      uint2 xv[MT][4];
-#pragma unroll
-      for (int m = 0; m < MT; ++m)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) xv[m][j] = *reinterpret_cast<const uint2*>(xb[m] + kb + 32 * j + 8 * t);
-#pragma unroll
-      for (int ti = 0; ti < NT; ++ti) {
-        const uint32_t* a0w = reinterpret_cast<const uint32_t*>(&w0[ti]);
-        const uint32_t* a8w = reinterpret_cast<const uint32_t*>(&w8[ti]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t a0 = e2m1x4_to_e4m3x4(a0w[j] & 0x0f0f0f0fu);
-          const uint32_t a2 = e2m1x4_to_e4m3x4((a0w[j] >> 4) & 0x0f0f0f0fu);
-          const uint32_t a1 = e2m1x4_to_e4m3x4(a8w[j] & 0x0f0f0f0fu);
-          const uint32_t a3 = e2m1x4_to_e4m3x4((a8w[j] >> 4) & 0x0f0f0f0fu);
-          // 2^(code - 127): the scale byte dropped into the exponent field
-          const float s0 = __uint_as_float(((c0[ti] >> (8 * j)) & 0xffu) << 23);
-          const float s8 = __uint_as_float(((c8[ti] >> (8 * j)) & 0xffu) << 23);
-#pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            float dd[4];
-            mma_e4m3_16832(dd, a0, a1, a2, a3, xv[m][j].x, xv[m][j].y);
-            acc[ti][m][0] = fmaf(s0, dd[0], acc[ti][m][0]);
-            acc[ti][m][1] = fmaf(s0, dd[1], acc[ti][m][1]);
-            acc[ti][m][2] = fmaf(s8, dd[2], acc[ti][m][2]);
-            acc[ti][m][3] = fmaf(s8, dd[3], acc[ti][m][3]);
-          }
-        }
-      }
-    }
   } else {
     // ---------------- MXFP4: 32 nibbles per 16-byte load = one scale group of one row; 128 k per step
     const uint8_t* srow0[NT];
@@ -393,12 +310,6 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
     const int n = n0 + 16 * h + gg + ((i & 2) ? 8 : 0);
     const int r = row_base + m * 8 + 2 * tt + (i & 1);
     if (r < rows && n < p.N) {
-      if (KIND == 3) {
-        // activation row scale, and 2^6 for the e2m1 -> e4m3 exponent offset
-        const float xs = p.x_scale[pairs ? pairs[r] / p.x_div : r] * 64.f;
-        v *= xs;
-        v3 *= xs;
-      }
       float o = v;
       if (DUAL) {
         float gate = v, up = v3;
@@ -420,9 +331,9 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 }
 
 template <int KIND, bool DUAL>
-__global__ void __launch_bounds__((KIND == 3 ? kWarps : kMaxWarps) * 32, (KIND == 3 ? (DUAL ? 4 : 5) : 1))
+__global__ void __launch_bounds__(kMaxWarps * 32, 1)
 smallm_gemm_kernel(SmallMParams p) {
-  __shared__ float red[(KIND == 3 ? kWarps : kMaxWarps) * (DUAL ? 4 : 2) * 2][32][4];
+  __shared__ float red[kMaxWarps * (DUAL ? 4 : 2) * 2][32][4];
   __shared__ __align__(16) float ctile[(KIND == 0 && !DUAL) ? 32 * 32 : 4];
   float* tile_out = (KIND == 0 && !DUAL && p.use_comm) ? ctile : nullptr;
   int rows;
@@ -465,52 +376,6 @@ smallm_gemm_kernel(SmallMParams p) {
   }
 }
 
-// one CTA per row: amax -> scale = amax / 448 -> e4m3 bytes, every 8 consecutive values stored as
-// x0 x2 x4 x6 x1 x3 x5 x7 (the order the kind-3 MMA fragments want)
-__global__ void __launch_bounds__(256) quant_rows_e4m3_perm_kernel(const __half* __restrict__ x, long ldx,
-                                                                   uint8_t* __restrict__ q, long ldq,
-                                                                   float* __restrict__ scale, int K) {
-  __shared__ float red[8];
-  const long r = blockIdx.x;
-  const __half* xr = x + r * ldx;
-  float m = 0.f;
-  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
-    const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(h[j]);
-      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
-    }
-  }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-  __syncthreads();
-  m = red[0];
-#pragma unroll
-  for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
-  const float s = fmaxf(m, 1e-20f) / 448.f, inv = 1.f / s;
-  if (threadIdx.x == 0) scale[r] = s;
-  for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
-    const __half2* h = reinterpret_cast<const __half2*>(&raw);
-    float f[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 v = __half22float2(h[j]);
-      f[2 * j] = v.x * inv;
-      f[2 * j + 1] = v.y * inv;
-    }
-    uint2 out;
-    out.x = (uint32_t)float_to_e4m3(f[0]) | ((uint32_t)float_to_e4m3(f[2]) << 8) |
-            ((uint32_t)float_to_e4m3(f[4]) << 16) | ((uint32_t)float_to_e4m3(f[6]) << 24);
-    out.y = (uint32_t)float_to_e4m3(f[1]) | ((uint32_t)float_to_e4m3(f[3]) << 8) |
-            ((uint32_t)float_to_e4m3(f[5]) << 16) | ((uint32_t)float_to_e4m3(f[7]) << 24);
-    *reinterpret_cast<uint2*>(q + r * ldq + i) = out;
-  }
-}
-
 template <int KIND, bool DUAL>
 cudaError_t launch(const SmallMParams& p, int slots, cudaStream_t st, int warps = kWarps) {
   dim3 grid((p.N + kTileN - 1) / kTileN, slots > 0 ? slots : 1);
@@ -541,8 +406,6 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   p.swiglu_limit = swiglu_limit;
   p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
   p.use_comm = 0;
-  p.x_scale = nullptr;
-  p.kstep = 64; p.s_kstep = 4;
   const bool dual = W3 != nullptr;
   cudaError_t e;
   // dense FP8 with so few tiles that an SM gets two CTAs or fewer: eight K-splitting warps per CTA
@@ -556,43 +419,6 @@ TF_API int tf_smallm_gemm(int kind, const void* W, const void* W3, const void* S
   else if (kind == 2) e = launch<2, false>(p, slots, stream);
   else return -1;
   return (int)e;
-}
-
-// Routed-expert GEMV with FP8 activations: W / W3 are MXFP4 in the quad-packed layout (see the
-// kind-3 loop), X is the output of tf_quant_rows_e4m3_perm ([rows, K] bytes, ldx in bytes) with
-// its per-row scales.  Other arguments as tf_smallm_gemm (grouped form).  With `step_major` the caller
-// passes ldw = 64, lds = 4 and the k-step-major layout described at SmallMParams::kstep.
-TF_API int tf_smallm_gemm_w4a8(const void* W, const void* W3, const void* S, const void* S3, long w_group_stride,
-                               long s_group_stride, int ldw, int lds, const void* X, int ldx, const float* x_scale,
-                               void* Y, int ldy, int out_kind, int N, int K, int M, const int* group_expert,
-                               const int* group_start, const int* group_count, const int* n_groups,
-                               const int* sorted_pairs, int x_div, int slots, float swiglu_limit, int step_major,
-                               cudaStream_t stream) {
-  if (N % kTileN != 0 || K % 128 != 0 || (ldx % 8) != 0 || (ldw % 16) != 0 || (lds % 4) != 0 || !x_scale) return -1;
-  SmallMParams p;
-  p.W = (const uint8_t*)W; p.W3 = (const uint8_t*)W3; p.S = S; p.S3 = S3;
-  p.w_group_stride = w_group_stride; p.s_group_stride = s_group_stride;
-  p.ldw = ldw; p.lds = lds; p.X = (const __half*)X; p.ldx = ldx; p.Y = Y; p.ldy = ldy;
-  p.out_kind = out_kind; p.N = N; p.K = K; p.M = M;
-  p.group_expert = group_expert; p.group_start = group_start; p.group_count = group_count;
-  p.n_groups = n_groups; p.sorted_pairs = sorted_pairs; p.x_div = x_div > 0 ? x_div : 1;
-  p.swiglu_limit = swiglu_limit;
-  p.k_per_warp = ((K + kWarps - 1) / kWarps + 127) / 128 * 128;
-  p.use_comm = 0;
-  p.x_scale = x_scale;
-  // step_major: W is [experts][K/128][N][64 B] and S [experts][K/128][N][4 B]; ldw / lds are then 64 / 4
-  p.kstep = step_major ? (long)N * 64 : 64;
-  p.s_kstep = step_major ? (long)N * 4 : 4;
-  return (int)(W3 ? launch<3, true>(p, slots, stream) : launch<3, false>(p, slots, stream));
-}
-
-// x [rows, K] f16 -> q [rows, K] e4m3 in the 8-run order of the kind-3 fragments + scale [rows]
-TF_API int tf_quant_rows_e4m3_perm(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int K,
-                                   cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  if (K % 8 != 0 || ldx % 8 != 0 || ldq % 8 != 0) return -1;
-  quant_rows_e4m3_perm_kernel<<<rows, 256, 0, stream>>>((const __half*)x, ldx, (uint8_t*)q, ldq, scale, K);
-  return (int)cudaGetLastError();
 }
 
 // Dense FP8 GEMV (M <= 32) fused with the tensor-parallel all-reduce, the residual update and the
@@ -618,8 +444,6 @@ TF_API int tf_smallm_gemm_allreduce(const void* W, const void* S, int ldw, int l
   p.sorted_pairs = nullptr; p.x_div = 1; p.swiglu_limit = 0.f;
   p.k_per_warp = ((K + kMaxWarps - 1) / kMaxWarps + 127) / 128 * 128;
   p.use_comm = resid ? 1 : 2;
-  p.x_scale = nullptr;
-  p.kstep = 64; p.s_kstep = 4;
   p.comm.peers = (const unsigned long long*)peers; p.comm.world = world; p.comm.rank = rank;
   p.comm.tiles = N / kTileN; p.comm.max_rows = max_rows; p.comm.N = N; p.comm.epoch = (unsigned int*)epoch;
   p.comm.spin_limit = spin_limit; p.comm.st = (TfStatusWord*)status;
