@@ -124,6 +124,8 @@ def main():
                     "left out of the captured decode graph (the printed number is then NOT a benchmark value)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--pdl", type=int, default=-1, help="1 / 0: launch kernels with programmatic dependent launch "
+                    "(default: the engine configuration's setting)")
     ap.add_argument("--trace", action="store_true", help="print per-kernel time tables of one extra prefill pass and one eager decode step")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -136,6 +138,7 @@ def main():
     from titanic_flash_41_b200.parallel.comm import init_distributed
     from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
     from titanic_flash_41_b200.serve.prefill import run_prefill
+    from titanic_flash_41_b200.ops import native as native_mod
     import __graft_entry__
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -156,6 +159,8 @@ def main():
     chunk = 16384
     ecfg = EngineConfig(tp=world, regions=SESSIONS, max_context=CONTEXT + 4096, prefill_widths=(chunk,),
                         use_cuda_graphs=not args.no_graph)
+    if args.pdl >= 0:
+        ecfg.pdl = bool(args.pdl)
     t0 = time.time()
     eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=0, max_chunk=chunk)
     from titanic_flash_41_b200.ops import bigpath
@@ -311,6 +316,7 @@ def main():
                        "index_source_layers": list(cfg.index_source_layers),
                        "prefill": ("sequence-parallel rows" if getattr(eng, "sp", None) is not None else "single rank"),
                        "sampling": ("rank-local chunks" if dec.ws is not None else "gathered rows"),
+                       "programmatic_dependent_launch": native_mod.pdl_enabled(),
                        "l2": "inputs larger than L2 (>= 5 GB of weights touched per step)",
                        "weights": "FP8 block-128 dense, MXFP4 experts, bf16 head (FP8 draft head)"},
             "prefill_s": None if prefill_s is None else round(prefill_s, 3),

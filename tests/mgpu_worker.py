@@ -85,9 +85,9 @@ def main():
     cfg = small_config(n_heads=4 * world if world > 4 else 4, shared_inter=max(256, 128 * world),
                        moe_inter=512, draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
-    ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=1024, prefill_widths=(128,))
     # the TP engine also splits index scoring by key range from 8 keys on (decode rows)
-    ecfg_tp = EngineConfig(regions=2, max_context=1024, prefill_widths=(128,), key_sharded_index_min=8)
+    ecfg_tp = EngineConfig(reference_matmul=True, regions=2, max_context=1024, prefill_widths=(128,), key_sharded_index_min=8)
     eng = E.Engine.from_weights(cfg, ecfg_tp, W, comm=comm, device=dev)
     eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev, spin_limit=2_000_000)
     ref = E.Engine.from_weights(cfg, ecfg, W, comm=LocalComm(), device=dev)

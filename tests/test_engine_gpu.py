@@ -28,7 +28,7 @@ def test_engine_matches_oracle_prefill_and_decode():
     cfg = small_config()
     W = oracle.init_weights(cfg, 0)
     rt = {}
-    ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
     ref = oracle.OracleModel(cfg, rt)
     g = torch.Generator().manual_seed(1)
@@ -62,10 +62,10 @@ def test_block_scaled_expert_path_matches_register_path_and_oracle():
     cfg = small_config(moe_inter=512)
     W = oracle.init_weights(cfg, 0)
     rt = {}
-    ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
     assert eng._moe_mx_ok(4) and "x8" in eng._bufs(4)
-    old = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,),
+    old = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,),
                                                   moe_block_scaled=False), W)
     assert "x8" not in old._bufs(4)
     ref = oracle.OracleModel(cfg, rt)
@@ -103,7 +103,7 @@ def test_block_scaled_expert_path_matches_register_path_and_oracle():
 def test_two_regions_batched_decode_equals_separate():
     cfg = small_config()
     W = oracle.init_weights(cfg, 3)
-    ecfg = EngineConfig(regions=3, max_context=512, prefill_widths=(128,))
+    ecfg = EngineConfig(reference_matmul=True, regions=3, max_context=512, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W)
     g = torch.Generator().manual_seed(2)
     pa, pb = (torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (40, 61))
@@ -121,7 +121,7 @@ def test_two_regions_batched_decode_equals_separate():
 
 def test_determinism_run_to_run():
     cfg = small_config()
-    ecfg = EngineConfig(regions=1, max_context=256, prefill_widths=(64,))
+    ecfg = EngineConfig(reference_matmul=True, regions=1, max_context=256, prefill_widths=(64,))
     eng = E.Engine.from_weights(cfg, ecfg, oracle.init_weights(cfg, 5))
     p = list(range(3, 35))
     a = eng.forward(E.StepPlan.build([(0, 0, p)])).clone()
@@ -138,7 +138,7 @@ def test_tensor_core_prefill_path_matches_staging_per_call():
     from titanic_flash_41_b200.ops import bigpath
     cfg = small_config()
     W = oracle.init_weights(cfg, 0)
-    ecfg = EngineConfig(regions=2, max_context=1024, prefill_widths=(512,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=1024, prefill_widths=(512,))
     eng = E.Engine.from_weights(cfg, ecfg, W)
     bp = bigpath.BigPath(eng)
     errs = []
@@ -192,7 +192,7 @@ def test_chunked_prefill_with_late_group_and_spec_decode():
     cfg = small_config(n_layers=4, kv_source_layers=(0, 1), index_source_layers=(0, 1, 3), late_start=2,
                        draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
-    ecfg = EngineConfig(regions=2, max_context=2048, prefill_widths=(256,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=2048, prefill_widths=(256,))
     eng = E.Engine.from_weights(cfg, ecfg, W)
     bigpath.attach(eng)
     g = torch.Generator().manual_seed(3)
@@ -225,7 +225,7 @@ def test_layer_major_prefill_matches_chunk_major():
     from titanic_flash_41_b200.serve.prefill import run_prefill
     cfg = small_config(n_layers=4, kv_source_layers=(0, 1), index_source_layers=(0, 1, 3), late_start=2)
     W = oracle.init_weights(cfg, 0)
-    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=2048, prefill_widths=(256,)), W)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=2048, prefill_widths=(256,)), W)
     bigpath.attach(eng)
     g = torch.Generator().manual_seed(5)
     p = torch.randint(0, cfg.vocab, (900,), generator=g, dtype=torch.int32)
@@ -260,7 +260,7 @@ def test_reference_geometry_matches_oracle(geom):
             if k.endswith("_base") and "hc_" in k:
                 W[k] = torch.randn(W[k].shape, generator=g0) * 0.3
     rt = {}
-    ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
     ref = oracle.OracleModel(cfg, rt)
     g = torch.Generator().manual_seed(1)
@@ -292,7 +292,7 @@ def test_engram_layers_match_oracle(hc):
     cfg = small_config(engram=EngramConfig(layers=(0, 2), rows_per_table=1500), hc_mult=hc)
     W = oracle.init_weights(cfg, 0)
     rt = {}
-    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,)), W, roundtrip=rt)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,)), W, roundtrip=rt)
     ref = oracle.OracleModel(cfg, rt)
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(3, cfg.vocab, (50,), generator=g)
@@ -327,7 +327,7 @@ def test_engram_ids_hashed_on_the_device_equal_the_host_hashes():
     from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
     cfg = small_config(engram=EngramConfig(layers=(0, 2), rows_per_table=1500), draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
-    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,)), W)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,)), W)
     g = torch.Generator().manual_seed(4)
     a = torch.randint(3, cfg.vocab, (9,), generator=g).tolist()
     hist = torch.randint(3, cfg.vocab, (40,), generator=g).tolist()
@@ -363,7 +363,7 @@ def test_two_level_candidates_in_the_layer_loop():
     from titanic_flash_41_b200.ops import two_level as TL
     cfg = small_config(candidate_blocks=4, index_topk=8)
     W = oracle.init_weights(cfg, 0)
-    mk = lambda tl: E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(256,),
+    mk = lambda tl: E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(256,),
                                                             two_level_index_min=tl), W)
     eng, dense = mk(16), mk(0)
     assert eng.candidate_source == 0
@@ -405,7 +405,7 @@ def test_draft_head_with_markov_correction_matches_oracle():
     W = oracle.init_weights(cfg, 0)
     assert W["mtp.0.markov_head.head.weight"].shape == (cfg.vocab, 256)
     rt = {}
-    ecfg = EngineConfig(regions=2, max_context=512, prefill_widths=(128,))
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,))
     eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
     base = E.Engine.from_weights(plain, ecfg, {k: v for k, v in W.items() if "markov" not in k})
     ref = oracle.OracleModel(cfg, rt)
@@ -449,7 +449,7 @@ def test_draft_subset_head_in_four_bits_matches_oracle_and_proposes_subset_token
     ids = W["mtp.head_subset.ids"]
     assert ids.shape == (1024,) and bool((ids[1:] > ids[:-1]).all())
     rt = {}
-    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(128,)), W, roundtrip=rt)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,)), W, roundtrip=rt)
     assert "head_mx" in eng.draft_extra and torch.equal(rt["mtp.head_subset.ids"], ids)
     ref = oracle.OracleModel(cfg, rt)
     g = torch.Generator().manual_seed(2)
@@ -495,7 +495,7 @@ def test_reference_model_widths_run_on_the_engine():
     from titanic_flash_41_b200.config import DraftConfig, reference_1017_config
     cfg = reference_1017_config(n_layers=4, kv_source_layers=(2,), index_source_layers=(2,), late_start=3, n_experts=32,
                                 draft=DraftConfig(layers=1, depth=3), engram=None, dense_quant="fp8_block128", vocab=16384)
-    eng = E.Engine.random_init(cfg, EngineConfig(regions=2, max_context=4096, prefill_widths=(256,)), seed=0, max_chunk=256)
+    eng = E.Engine.random_init(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(256,)), seed=0, max_chunk=256)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(3, cfg.vocab, (200,), generator=g).tolist()
     lg = eng.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
@@ -516,6 +516,6 @@ def test_startup_self_check_and_bitwise_determinism_on_the_engine():
     from titanic_flash_41_b200.serve.warmup import self_check
     cfg = small_config(draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
-    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(64,)), W)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(64,)), W)
     rep = self_check(EngineBackend(eng, chunk=64), steps=4)
     assert rep["tokens"] >= 5

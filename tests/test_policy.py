@@ -98,3 +98,24 @@ def test_draw_trace_and_logit_export(tmp_path):
     rc.add(torch.tensor([[0, 1], [1, 7], [1, -1]]))
     s = rc.summary()
     assert s["total"] == 5 and s["top"][0] == 1 and s["unused"] == 5
+
+
+def test_chained_block_hashes_find_million_token_prefixes_quickly():
+    import time
+
+    import numpy as np
+
+    from titanic_flash_41_b200.serve import policy as P
+    rng = np.random.default_rng(0)
+    a = rng.integers(0, 129280, size=1_000_000, dtype=np.int64)
+    b = a.copy()
+    b[777_777] += 1
+    ca, cb = P.chain_hashes(a), P.chain_hashes(b)
+    assert len(ca) == 1_000_000 // P.BLOCK and ca[:189] == cb[:189] and ca[189] != cb[189]
+    t0 = time.perf_counter()
+    for _ in range(20):
+        assert P.common_prefix(a, b, ca, cb) == 777_777
+    assert (time.perf_counter() - t0) / 20 < 0.01            # digests first, one vectorised compare of a block's tail
+    assert P.common_prefix(a, a[:5000], ca, P.chain_hashes(a[:5000])) == 5000
+    assert P.common_prefix(list(a[:10]), tuple(a[:7])) == 7   # plain sequences still work
+    assert P.common_prefix([], [1]) == 0

@@ -93,7 +93,7 @@ def test_prefill_with_image_span_embeddings():
     from titanic_flash_41_b200.serve.prefill import run_prefill
     cfg = small_config()
     W = oracle.init_weights(cfg, 0)
-    eng = E.Engine.from_weights(cfg, EngineConfig(regions=2, max_context=512, prefill_widths=(64,)), W)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(64,)), W)
     p = torch.randint(0, cfg.vocab, (150,), generator=torch.Generator().manual_seed(1), dtype=torch.int32)
     base = run_prefill(eng, 0, p, 64)
     offs = torch.arange(70, 90)

@@ -320,6 +320,8 @@ class EngineConfig(_JsonMixin):
     use_cuda_graphs: bool = True
     key_sharded_index_min: int = 8192  # decode rows: split index scoring over the ranks from this many keys (0 = never)
     two_level_index_min: int = 65536   # decode rows: from this many index keys on, layers after the candidate source score only its published blocks (0 = never)
+    reference_matmul: bool = False     # validation only: rows beyond the small-M limit may run through dequantised weights and torch.matmul when the tensor-core path is not attached (never set in serving or benchmarks: the engine refuses instead)
+    pdl: bool = False                  # launch kernels with programmatic dependent launch (each kernel waits for its predecessor on the device; the next one is already resident)
     sp_prefill: bool = True            # more than one rank: prefill chunks are split by rows over the ranks (every rank keeps the unsharded dense matrices of the encoder layers)
     moe_block_scaled: bool = True     # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
     seed: int = 0

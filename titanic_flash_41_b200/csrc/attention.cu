@@ -48,6 +48,7 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 
 template <int DH>
 __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
+  tf_pdl_sync();
   constexpr int KS = DH + 8;          // row stride of Ks (halfs)
   constexpr int VS = kChunk + 8;      // row stride of Vt (halfs)
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -267,6 +268,7 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
 // ---------------------------------------------------------------------------------------------
 template <int DH>
 __global__ void __launch_bounds__(128) sparse_attn_wide_kernel(AttnParams p) {
+  tf_pdl_sync();
   constexpr int SL = DH / 4;          // dims owned by one warp
   constexpr int KS = DH + 8;
   constexpr int VS = kChunk + 8;
@@ -493,6 +495,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
                                   const float* __restrict__ sink, const int* __restrict__ pos,
                                   const float* __restrict__ freqs, int nsplit, int Hl, int Dh, int rope_dim,
                                   __half* __restrict__ out16, __nv_bfloat16* __restrict__ outb, int ldo) {
+  tf_pdl_sync();
   extern __shared__ float vals[];   // Dh
   const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const float* lse = part_lse + ((long)r * nsplit) * Hl + h;
@@ -559,17 +562,17 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
                            (kChunk * (256 + 8) + 256 * (kChunk + 8)) * 2 + 4 * 16 * (kChunk + 4) * 4);
       attr_set = true;
     }
-    if (Dh == 512) sparse_attn_wide_kernel<512><<<grid, warps * 32, smem, st>>>(p);
-    else sparse_attn_wide_kernel<256><<<grid, warps * 32, smem, st>>>(p);
+    if (Dh == 512) tf_launch(sparse_attn_wide_kernel<512>, dim3(grid), dim3(warps * 32), smem, st, p);
+    else tf_launch(sparse_attn_wide_kernel<256>, dim3(grid), dim3(warps * 32), smem, st, p);
   } else if (Dh == 128) {
     const int smem = (kChunk * (128 + 8) + 128 * (kChunk + 8)) * 2;
-    sparse_attn_kernel<128><<<grid, warps * 32, smem, st>>>(p);
+    tf_launch(sparse_attn_kernel<128>, dim3(grid), dim3(warps * 32), smem, st, p);
   } else {
     const int smem = (kChunk * (64 + 8) + 64 * (kChunk + 8)) * 2;
-    sparse_attn_kernel<64><<<grid, warps * 32, smem, st>>>(p);
+    tf_launch(sparse_attn_kernel<64>, dim3(grid), dim3(warps * 32), smem, st, p);
   }
   dim3 mg(T, Hl);
-  attn_merge_kernel<<<mg, Dh, Dh * sizeof(float), st>>>(part_o, part_lse, sink, pos, freqs, nsplit, Hl, Dh,
+  tf_launch(attn_merge_kernel, dim3(mg), dim3(Dh), Dh * sizeof(float), st, part_o, part_lse, sink, pos, freqs, nsplit, Hl, Dh,
                                                         rope_dim, (__half*)out16, (__nv_bfloat16*)outb, ldo);
   return (int)cudaGetLastError();
 }

@@ -10,6 +10,39 @@
 #define TF_API extern "C" __attribute__((visibility("default")))
 
 // ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A decode step is several hundred short kernels, each of which
+// waits for the launch latency of its successor after it has finished.  Every kernel here begins
+// with tf_pdl_sync(): it waits until the kernel before it in the stream has completed and its
+// writes are visible (so the usual ordering holds for every read AND write that follows), then
+// lets the kernel after it be launched.  With the launch attribute set (tf_set_pdl), the next
+// kernel's CTAs are therefore already resident and parked at their own tf_pdl_sync() while this
+// one runs, and start the moment it ends.  Without the attribute both instructions are no-ops.
+// (Reference: launch_pdl, src/cuda.rs:2209.)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tf_pdl_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+extern int g_tf_pdl;     // set through tf_set_pdl (launch.cu)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t tf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_tf_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------------------
 // Status words.  No kernel traps, asserts or spins without a limit: a kernel that meets a
 // bad argument or a wait that runs out records (code, detail) here and returns; the host
 // reads the word after the step (the reference records a poison word + (peer, slot, seq)

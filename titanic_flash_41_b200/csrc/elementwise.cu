@@ -14,6 +14,7 @@ namespace {
 // --------------------------------------------------------------------------- embedding
 __global__ void embed_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int d, int vocab, TfStatusWord* st) {
+  tf_pdl_sync();
   const int r = blockIdx.x;
   int tok = tokens[r];
   if (tok < 0 || tok >= vocab) {
@@ -33,6 +34,7 @@ __global__ void add_norm_kernel(__nv_bfloat16* __restrict__ x, const void* __res
                                 int delta_kind, int ldd, const __nv_bfloat16* __restrict__ w,
                                 __half* __restrict__ h16, __nv_bfloat16* __restrict__ hb,
                                 uint8_t* __restrict__ q8, float* __restrict__ qs, int d, float eps) {
+  tf_pdl_sync();
   extern __shared__ float row[];            // d floats
   __shared__ float scratch[32];
   const int r = blockIdx.x;
@@ -179,6 +181,7 @@ __device__ void store_index_key(const float* v, uint8_t* dst, int D) {
 }
 
 __global__ void attn_prep_kernel(PrepParams p) {
+  tf_pdl_sync();
   extern __shared__ float sm[];     // max(Dh, Dh+Di) floats + scratch
   __shared__ float scratch[32];
   const int r = blockIdx.x, tid = threadIdx.x;
@@ -310,6 +313,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
 // are read by a later launch).  Runs after attn_prep_kernel on the same stream, so no row of
 // this launch still reads the slots being written.
 __global__ void carry_save_kernel(PrepParams p) {
+  tf_pdl_sync();
   const int r = blockIdx.x;
   const int pos = p.pos[r], reg = p.region[r];
   const int group_end = (pos / p.ratio + 1) * p.ratio - 1;
@@ -327,6 +331,7 @@ __global__ void carry_save_kernel(PrepParams p) {
 // logits[r, e] = h[r,:] . gate[e,:]  (f16 activations, bf16 gate), one warp per (expert, row-block)
 __global__ void router_logits_kernel(const __half* __restrict__ h, const __nv_bfloat16* __restrict__ gate,
                                      float* __restrict__ logits, int M, int E, int d) {
+  tf_pdl_sync();
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (e >= E) return;
   const __nv_bfloat16* g = gate + (long)e * d;
@@ -449,6 +454,7 @@ __device__ __forceinline__ void router_topk_rows(const float* __restrict__ logit
 __global__ void router_topk_kernel(const float* __restrict__ logits, const RouterBias bias,
                                    int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
                                    int scoring, int renorm, float scale) {
+  tf_pdl_sync();
   extern __shared__ float sc[];                       // [warps][2][E]
   router_topk_rows(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, sc, blockIdx.x * (blockDim.x >> 5));
 }
@@ -515,6 +521,7 @@ __device__ __forceinline__ void route_group_body(const int* __restrict__ ids, in
 __global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
                                    int* group_expert, int* group_start, int* group_count, int* n_groups,
                                    int* sorted_pairs, int* n_local_pairs) {
+  tf_pdl_sync();
   extern __shared__ int cnt_smem[];
   route_group_body(ids, n_pairs, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
                    n_local_pairs, cnt_smem);
@@ -526,6 +533,7 @@ __global__ void __launch_bounds__(512) router_topk_group_kernel(
     const float* __restrict__ logits, const RouterBias bias, int* __restrict__ ids, float* __restrict__ wts,
     int M, int E, int topk, int scoring, int renorm, float scale, int e_lo, int e_hi, int* group_expert,
     int* group_start, int* group_count, int* n_groups, int* sorted_pairs, int* n_local_pairs) {
+  tf_pdl_sync();
   extern __shared__ float fsm[];                       // [16][2][E] floats, reused as ints by the grouping
   for (int row0 = 0; row0 < M; row0 += 16)
     router_topk_rows(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, fsm, row0);
@@ -538,6 +546,7 @@ __global__ void __launch_bounds__(512) router_topk_group_kernel(
 __global__ void moe_combine_kernel(const float* __restrict__ y_pair, const int* __restrict__ ids,
                                    const float* __restrict__ wts, const float* __restrict__ shared_y,
                                    float* __restrict__ out, int d, int topk, int e_lo, int e_hi) {
+  tf_pdl_sync();
   const int r = blockIdx.x;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
@@ -551,6 +560,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y_pair, const int* 
 }
 
 __global__ void cast_f32_to_f16_kernel(const float* in, __half* out, long n) {
+  tf_pdl_sync();
   long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __float2half(in[i]);
 }
@@ -560,7 +570,7 @@ __global__ void cast_f32_to_f16_kernel(const float* in, __half* out, long n) {
 TF_API int tf_embed(const int* tokens, const void* table, void* out, int T, int d, int vocab,
                     void* status, cudaStream_t st) {
   if (d % 8) return -1;
-  embed_kernel<<<T, 128, 0, st>>>(tokens, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, d, vocab,
+  tf_launch(embed_kernel, dim3(T), dim3(128), 0, st, tokens, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, d, vocab,
                                   (TfStatusWord*)status);
   return (int)cudaGetLastError();
 }
@@ -568,7 +578,7 @@ TF_API int tf_embed(const int* tokens, const void* table, void* out, int T, int 
 TF_API int tf_add_norm(void* x, const void* delta, int delta_kind, int ldd, const void* w, void* h16,
                        void* hb, void* q8, void* qs, int T, int d, float eps, cudaStream_t st) {
   if (d % 128) return -1;
-  add_norm_kernel<<<T, 256, d * sizeof(float), st>>>((__nv_bfloat16*)x, delta, delta_kind, ldd,
+  tf_launch(add_norm_kernel, dim3(T), dim3(256), d * sizeof(float), st, (__nv_bfloat16*)x, delta, delta_kind, ldd,
                                                      (const __nv_bfloat16*)w, (__half*)h16,
                                                      (__nv_bfloat16*)hb, (uint8_t*)q8, (float*)qs, d, eps);
   return (int)cudaGetLastError();
@@ -595,8 +605,8 @@ TF_API int tf_attn_prep(const void* P, int p_kind, int ldp, int T, const int* po
   p.st = (TfStatusWord*)status;
   const int smf = (off_cv >= 0 ? Dh + Di : Dh);
   // few rows (decode): eight more CTAs per row share the query heads
-  attn_prep_kernel<<<dim3(T, (T <= 64 && off_q >= 0) ? 9 : 1), 256, smf * sizeof(float), st>>>(p);
-  if (off_cv >= 0) carry_save_kernel<<<T, 128, 0, st>>>(p);
+  tf_launch(attn_prep_kernel, dim3(dim3(T, (T <= 64 && off_q >= 0) ? 9 : 1)), dim3(256), smf * sizeof(float), st, p);
+  if (off_cv >= 0) tf_launch(carry_save_kernel, dim3(T), dim3(128), 0, st, p);
   return (int)cudaGetLastError();
 }
 
@@ -607,11 +617,10 @@ TF_API int tf_router(const void* h16, const void* gate, const float* bias, const
                      int renorm, float scale, cudaStream_t st) {
   if (d % 256) return -1;
   const RouterBias rb{bias, bias_vl, tokens, image_token};
-  router_logits_kernel<<<(E + 7) / 8, 256, 0, st>>>((const __half*)h16, (const __nv_bfloat16*)gate,
+  tf_launch(router_logits_kernel, dim3((E + 7) / 8), dim3(256), 0, st, (const __half*)h16, (const __nv_bfloat16*)gate,
                                                     logits, M, E, d);
   const int nw = 4;
-  router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
-      logits, rb, ids, wts, M, E, topk, scoring, renorm, scale);
+  tf_launch(router_topk_kernel, dim3((M + nw - 1) / nw), dim3(nw * 32), nw * 2 * E * sizeof(float), st, logits, rb, ids, wts, M, E, topk, scoring, renorm, scale);
   return (int)cudaGetLastError();
 }
 
@@ -621,8 +630,7 @@ TF_API int tf_router_topk(const float* logits, const float* bias, const float* b
                           float scale, cudaStream_t st) {
   const int nw = 4;
   const RouterBias rb{bias, bias_vl, tokens, image_token};
-  router_topk_kernel<<<(M + nw - 1) / nw, nw * 32, nw * 2 * E * sizeof(float), st>>>(
-      logits, rb, ids, wts, M, E, topk, scoring, renorm, scale);
+  tf_launch(router_topk_kernel, dim3((M + nw - 1) / nw), dim3(nw * 32), nw * 2 * E * sizeof(float), st, logits, rb, ids, wts, M, E, topk, scoring, renorm, scale);
   return (int)cudaGetLastError();
 }
 
@@ -635,7 +643,7 @@ TF_API int tf_router_topk_group(const float* logits, const float* bias, const fl
   const size_t smem = max((size_t)16 * 2 * E * sizeof(float), (size_t)(e_hi - e_lo + M * topk) * sizeof(int));
   if (M <= 0 || M > 32 || e_hi <= e_lo || smem > 48 * 1024) return -1;
   const RouterBias rb{bias, bias_vl, tokens, image_token};
-  router_topk_group_kernel<<<1, 512, smem, st>>>(logits, rb, ids, wts, M, E, topk, scoring, renorm, scale, e_lo, e_hi,
+  tf_launch(router_topk_group_kernel, dim3(1), dim3(512), smem, st, logits, rb, ids, wts, M, E, topk, scoring, renorm, scale, e_lo, e_hi,
                                                  group_expert, group_start, group_count, n_groups, sorted_pairs,
                                                  n_local_pairs);
   return (int)cudaGetLastError();
@@ -645,19 +653,18 @@ TF_API int tf_route_group(const int* ids, int n_pairs, int e_lo, int e_hi, int* 
                           int* group_start, int* group_count, int* n_groups, int* sorted_pairs,
                           int* n_local_pairs, cudaStream_t st) {
   if (n_pairs <= 0 || e_hi <= e_lo || (size_t)(e_hi - e_lo + n_pairs) * sizeof(int) > 48 * 1024) return -1;
-  route_group_kernel<<<1, 256, (e_hi - e_lo + n_pairs) * sizeof(int), st>>>(
-      ids, n_pairs, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
+  tf_launch(route_group_kernel, dim3(1), dim3(256), (e_hi - e_lo + n_pairs) * sizeof(int), st, ids, n_pairs, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
       n_local_pairs);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_moe_combine(const float* y_pair, const int* ids, const float* wts, const float* shared_y,
                           float* out, int M, int d, int topk, int e_lo, int e_hi, cudaStream_t st) {
-  moe_combine_kernel<<<dim3(M, M <= 64 ? (d + 255) / 256 : 1), 256, 0, st>>>(y_pair, ids, wts, shared_y, out, d, topk, e_lo, e_hi);
+  tf_launch(moe_combine_kernel, dim3(dim3(M, M <= 64 ? (d + 255) / 256 : 1)), dim3(256), 0, st, y_pair, ids, wts, shared_y, out, d, topk, e_lo, e_hi);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_cast_f32_f16(const float* in, void* out, long n, cudaStream_t st) {
-  cast_f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, (__half*)out, n);
+  tf_launch(cast_f32_to_f16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, in, (__half*)out, n);
   return (int)cudaGetLastError();
 }

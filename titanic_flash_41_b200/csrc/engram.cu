@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256) engram_dequant_kernel(const uint8_t* __re
                                                              const long long* __restrict__ ids,
                                                              __nv_bfloat16* __restrict__ out, int count,
                                                              long long row_start, long long row_end) {
+  tf_pdl_sync();
   const int r = blockIdx.x;
   if (r >= count) return;
   const long long id = ids[r];
@@ -36,6 +37,7 @@ __global__ void __launch_bounds__(256) engram_gate_kernel(const __nv_bfloat16* _
                                                           const __nv_bfloat16* __restrict__ qw,
                                                           const __nv_bfloat16* __restrict__ kw,
                                                           __nv_bfloat16* __restrict__ out, int m, int d, float eps) {
+  tf_pdl_sync();
   __shared__ float red[3][8];
   const int r = blockIdx.x, h = blockIdx.y;
   const __nv_bfloat16* xr = x + ((long)r * m + h) * d;
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(256) engram_gate_kernel(const __nv_bfloat16* _
 TF_API int tf_engram_dequant(const void* table, const void* ids, void* out, int count, long row_start, long row_end,
                              cudaStream_t st) {
   if (count <= 0) return 0;
-  engram_dequant_kernel<<<count, 256, 0, st>>>((const uint8_t*)table, (const long long*)ids, (__nv_bfloat16*)out, count,
+  tf_launch(engram_dequant_kernel, dim3(count), dim3(256), 0, st, (const uint8_t*)table, (const long long*)ids, (__nv_bfloat16*)out, count,
                                                row_start, row_end);
   return (int)cudaGetLastError();
 }
@@ -86,7 +88,7 @@ TF_API int tf_engram_dequant(const void* table, const void* ids, void* out, int 
 TF_API int tf_engram_gate(const void* x, const void* kv, const void* qw, const void* kw, void* out, int rows, int m,
                           int d, float eps, cudaStream_t st) {
   if (rows <= 0) return 0;
-  engram_gate_kernel<<<dim3(rows, m), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)kv,
+  tf_launch(engram_gate_kernel, dim3(dim3(rows, m)), dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)kv,
                                                     (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw,
                                                     (__nv_bfloat16*)out, m, d, eps);
   return (int)cudaGetLastError();
@@ -110,6 +112,7 @@ __global__ void engram_hash_kernel(const int* __restrict__ tokens, const int* __
                                    const unsigned long long* __restrict__ offsets, long long* __restrict__ out,
                                    int T, long out_table_stride, int tables, int ngram, int heads, int pad_token,
                                    int image_token, TfStatusWord* st) {
+  tf_pdl_sync();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * tables) return;
   const int i = idx / tables, t = idx % tables;
@@ -150,8 +153,7 @@ TF_API int tf_engram_hash(const int* tokens, const int* pos, const int* first_ro
                           int image_token, void* status, cudaStream_t st) {
   if (T <= 0 || ngram < 2 || ngram > kMaxNgram || pad_token < 0 || pad_token >= vocab) return -1;
   const int n = T * tables;
-  engram_hash_kernel<<<(n + 127) / 128, 128, 0, st>>>(
-      tokens, pos, first_row, recent, (const long long*)token_map, vocab, (const unsigned long long*)mult,
+  tf_launch(engram_hash_kernel, dim3((n + 127) / 128), dim3(128), 0, st, tokens, pos, first_row, recent, (const long long*)token_map, vocab, (const unsigned long long*)mult,
       (const unsigned long long*)primes, (const unsigned long long*)offsets, (long long*)out, T, out_table_stride,
       tables, ngram, heads, pad_token, image_token, (TfStatusWord*)status);
   return (int)cudaGetLastError();

@@ -58,6 +58,7 @@ __device__ __forceinline__ bool wait_epoch(const unsigned int* f, unsigned int w
 // one CTA (256 threads) per local token
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpParams p, const __nv_bfloat16* __restrict__ x, long ldx,
                                                           const int* __restrict__ ids, int Tl) {
+  tf_pdl_sync();
   extern __shared__ uint8_t sm[];
   uint8_t* q = sm;                                         // [d]
   float* sc = reinterpret_cast<float*>(sm + p.d);          // [d / 128]
@@ -122,6 +123,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpParams p, const __nv
 
 // ids_out[src * cap + i] = expert id of entry i from source src, -1 beyond what arrived
 __global__ void __launch_bounds__(256) ep_recv_ids_kernel(EpParams p, int* __restrict__ ids_out) {
+  tf_pdl_sync();
   __shared__ int s_cnt[kMaxWorld];
   __shared__ int s_fail;
   unsigned int* mine = ctrl(p, p.rank);
@@ -151,6 +153,7 @@ __global__ void __launch_bounds__(256) ep_recv_ids_kernel(EpParams p, int* __res
 // kernel of this call has already waited for).
 __global__ void __launch_bounds__(256) ep_gather_kernel(EpParams p, const int* __restrict__ pair_dst,
                                                         uint8_t* __restrict__ xp, float* __restrict__ xps) {
+  tf_pdl_sync();
   const unsigned int* mine = ctrl(p, p.rank);
   const uint8_t* base = reinterpret_cast<const uint8_t*>(p.peers[p.rank]);
   for (int src = 0; src < p.world; ++src) {
@@ -171,6 +174,7 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(EpParams p, const int* _
 // expert outputs back to the rank that owns the token
 __global__ void __launch_bounds__(256) ep_return_kernel(EpParams p, const int* __restrict__ pair_dst,
                                                         const __nv_bfloat16* __restrict__ y, long ldy) {
+  tf_pdl_sync();
   unsigned int* mine = ctrl(p, p.rank);
   for (int src = 0; src < p.world; ++src) {
     const int cnt = (int)mine[W_DISP_CNT + src];
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(EpParams p, const int* 
                                                          const float* __restrict__ wts,
                                                          const float* __restrict__ shared_y,
                                                          __nv_bfloat16* __restrict__ out, long ldo) {
+  tf_pdl_sync();
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
@@ -263,7 +268,7 @@ TF_API int tf_ep_dispatch(const void* peers, int world, int rank, int cap, int d
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, epoch, 0, status);
   // a rank without tokens still has to publish its (zero) counts: one CTA with no pairs
   const int grid = Tl > 0 ? Tl : 1;
-  ep_dispatch_kernel<<<grid, 256, d + (d / 128) * 4, st>>>(p, (const __nv_bfloat16*)x, ldx, ids, Tl);
+  tf_launch(ep_dispatch_kernel, dim3(grid), dim3(256), d + (d / 128) * 4, st, p, (const __nv_bfloat16*)x, ldx, ids, Tl);
   return (int)cudaGetLastError();
 }
 
@@ -271,21 +276,21 @@ TF_API int tf_ep_recv_ids(const void* peers, int world, int rank, int cap, int d
                           int* ids_out, int spin_limit, void* status, cudaStream_t st) {
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, epoch, spin_limit, status);
   const long n = (long)world * cap;
-  ep_recv_ids_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, ids_out);
+  tf_launch(ep_recv_ids_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, p, ids_out);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_ep_gather(const void* peers, int world, int rank, int cap, int d, int k, int El, int Tl_max,
                         const int* pair_dst, void* xp, float* xps, cudaStream_t st) {
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, 0, 0, nullptr);
-  ep_gather_kernel<<<kWalkCtas, 256, 0, st>>>(p, pair_dst, (uint8_t*)xp, xps);
+  tf_launch(ep_gather_kernel, dim3(kWalkCtas), dim3(256), 0, st, p, pair_dst, (uint8_t*)xp, xps);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_ep_return(const void* peers, int world, int rank, int cap, int d, int k, int El, int Tl_max, int epoch,
                         const int* pair_dst, const void* y, long ldy, void* status, cudaStream_t st) {
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, epoch, 0, status);
-  ep_return_kernel<<<kWalkCtas, 256, 0, st>>>(p, pair_dst, (const __nv_bfloat16*)y, ldy);
+  tf_launch(ep_return_kernel, dim3(kWalkCtas), dim3(256), 0, st, p, pair_dst, (const __nv_bfloat16*)y, ldy);
   return (int)cudaGetLastError();
 }
 
@@ -294,6 +299,6 @@ TF_API int tf_ep_combine(const void* peers, int world, int rank, int cap, int d,
                          int spin_limit, void* status, cudaStream_t st) {
   if (Tl <= 0) return 0;
   EpParams p = make_params(peers, world, rank, cap, d, k, El, Tl_max, epoch, spin_limit, status);
-  ep_combine_kernel<<<Tl, 256, 0, st>>>(p, ids, wts, shared_y, (__nv_bfloat16*)out, ldo);
+  tf_launch(ep_combine_kernel, dim3(Tl), dim3(256), 0, st, p, ids, wts, shared_y, (__nv_bfloat16*)out, ldo);
   return (int)cudaGetLastError();
 }

@@ -29,6 +29,7 @@ struct CombineParams {
 };
 
 __global__ void __launch_bounds__(256) combine_allreduce_kernel(const CombineParams p) {
+  tf_pdl_sync();
   __shared__ __align__(16) float tile[32 * 32];
   extern __shared__ float rowbuf[];
   const int j = blockIdx.x, n0 = j * 32, rows = p.rows, d = p.d, topk = p.topk;
@@ -63,6 +64,7 @@ __global__ void __launch_bounds__(256) combine_allreduce_kernel(const CombinePar
 
 // Wait on a flag nobody sets: exercises the bounded-wait path in isolation.
 __global__ void wait_probe_kernel(const unsigned int* flag, unsigned int want, int spin_limit, TfStatusWord* st) {
+  tf_pdl_sync();
   int spins = 0;
   while ((int)(ld_acquire_sys(flag) - want) < 0) {
     if (++spins > spin_limit) {
@@ -118,7 +120,7 @@ TF_API int tf_moe_combine_allreduce(const float* y_pair, const int* ids, const f
   const size_t dyn = (size_t)d * sizeof(float);
   cudaError_t a = dyn_smem(dyn);
   if (a != cudaSuccess) return (int)a;
-  combine_allreduce_kernel<<<d / 32, 256, dyn, st>>>(p);
+  tf_launch(combine_allreduce_kernel, dim3(d / 32), dim3(256), dyn, st, p);
   return (int)cudaGetLastError();
 }
 
@@ -153,6 +155,6 @@ TF_API int tf_comm_allreduce_emulated(const float* partial, int rows, int rows_a
 
 TF_API int tf_wait_probe(const void* flag, int want, int spin_limit, void* status, cudaStream_t st) {
   if (!flag) return -1;
-  wait_probe_kernel<<<1, 1, 0, st>>>((const unsigned int*)flag, (unsigned int)want, spin_limit, (TfStatusWord*)status);
+  tf_launch(wait_probe_kernel, dim3(1), dim3(1), 0, st, (const unsigned int*)flag, (unsigned int)want, spin_limit, (TfStatusWord*)status);
   return (int)cudaGetLastError();
 }

@@ -33,6 +33,7 @@ struct FusedNormParams {
 };
 
 __global__ void __launch_bounds__(1024) fused_norm_kernel(const FusedNormParams p) {
+  tf_pdl_sync();
   extern __shared__ float row[];            // d floats
   __shared__ float scratch[32];
   const int r = blockIdx.x, d = p.d;
@@ -97,6 +98,6 @@ TF_API int tf_add_norm_fused(void* x, const void* delta, const void* y_pair, con
   p.wts = (const float*)wts; p.shared_y = (const float*)shared_y; p.topk = topk; p.e_lo = e_lo; p.e_hi = e_hi;
   p.w = (const __nv_bfloat16*)w; p.h16 = (__half*)h16; p.hb = (__nv_bfloat16*)hb; p.x8 = (uint8_t*)x8;
   p.x8s = (uint8_t*)x8s; p.d = d; p.eps = eps;
-  fused_norm_kernel<<<T, d >= 4096 ? 1024 : 256, d * sizeof(float), st>>>(p);
+  tf_launch(fused_norm_kernel, dim3(T), dim3(d >= 4096 ? 1024 : 256), d * sizeof(float), st, p);
   return (int)cudaGetLastError();
 }

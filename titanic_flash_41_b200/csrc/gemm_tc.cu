@@ -165,6 +165,7 @@ template <int KIND, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const GemmParams p) {
+  tf_pdl_sync();
   // BN = 128: six 32 KB stages, four TMEM buffers; BN = 256: four 48 KB stages, two TMEM buffers
   // (a third less operand traffic from L2 per FLOP)
   constexpr int kStages = (BN == 128) ? 6 : 4;
@@ -470,6 +471,7 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const unsigned long long
                                                         int rows, int N, long recv_off, long flag_off,
                                                         unsigned int want, __nv_bfloat16* out, int ldo,
                                                         int spin_limit, TfStatusWord* st) {
+  tf_pdl_sync();
   __shared__ int s_fail;
   const int nt = N / 128, tile = blockIdx.x, mt_i = tile / nt, nt_i = tile % nt;
   const unsigned int* cnt = reinterpret_cast<const unsigned int*>(peers[rank] + flag_off) + tile;
@@ -569,13 +571,13 @@ TF_API int tf_gemm_tc(int kind, const void* A, long lda, const void* B, long ldb
     attr_set = true;
   }
   if (BN == 128) {
-    if (kind == 0) gemm_tc_kernel<0, 128><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
-    else if (kind == 1) gemm_tc_kernel<1, 128><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
-    else gemm_tc_kernel<2, 128><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    if (kind == 0) tf_launch(gemm_tc_kernel<0, 128>, dim3(grid), dim3(kThreads), kSmemBytes, stream, ma, mb, p);
+    else if (kind == 1) tf_launch(gemm_tc_kernel<1, 128>, dim3(grid), dim3(kThreads), kSmemBytes, stream, ma, mb, p);
+    else tf_launch(gemm_tc_kernel<2, 128>, dim3(grid), dim3(kThreads), kSmemBytes, stream, ma, mb, p);
   } else {
-    if (kind == 0) gemm_tc_kernel<0, 256><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
-    else if (kind == 1) gemm_tc_kernel<1, 256><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
-    else gemm_tc_kernel<2, 256><<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    if (kind == 0) tf_launch(gemm_tc_kernel<0, 256>, dim3(grid), dim3(kThreads), kSmemBytes, stream, ma, mb, p);
+    else if (kind == 1) tf_launch(gemm_tc_kernel<1, 256>, dim3(grid), dim3(kThreads), kSmemBytes, stream, ma, mb, p);
+    else tf_launch(gemm_tc_kernel<2, 256>, dim3(grid), dim3(kThreads), kSmemBytes, stream, ma, mb, p);
   }
   return (int)cudaGetLastError();
 }
@@ -608,7 +610,7 @@ TF_API int tf_gemm_rs(int kind, const void* A, long lda, const void* B, long ldb
   if (rc != 0) return rc;
   const int rows = M / world;
   const int tiles = (rows / BM) * (N / 128);
-  rs_reduce_kernel<<<tiles, 256, 0, stream>>>((const unsigned long long*)peers, rank, world, rows, N, recv_off, 0,
+  tf_launch(rs_reduce_kernel, dim3(tiles), dim3(256), 0, stream, (const unsigned long long*)peers, rank, world, rows, N, recv_off, 0,
                                               (unsigned int)epoch * (unsigned int)world, (__nv_bfloat16*)out, ldo,
                                               spin_limit, (TfStatusWord*)status);
   return (int)cudaGetLastError();

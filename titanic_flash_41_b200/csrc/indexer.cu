@@ -31,6 +31,7 @@ struct ScoreParams {
 
 template <int DI>
 __global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
+  tf_pdl_sync();
   constexpr int KS = DI + 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half* Ks = reinterpret_cast<__half*>(smem_raw);   // [128][KS]
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
                                                            const int* __restrict__ nvalid, int k,
                                                            int* __restrict__ out, int* __restrict__ count,
                                                            float* __restrict__ out_scores, int base) {
+  tf_pdl_sync();
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_need, s_run, s_tie_run;
@@ -289,6 +291,7 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
 // ids ascending.  Reuses the selection kernel on the gathered scores, then maps positions to ids.
 __global__ void map_ids_kernel(const int* __restrict__ picked, const int* __restrict__ cand_ids, int ldc,
                                int k, int* __restrict__ out) {
+  tf_pdl_sync();
   const int r = blockIdx.x;
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
     const int p = picked[(long)r * k + i];
@@ -303,6 +306,7 @@ __global__ void map_ids_kernel(const int* __restrict__ picked, const int* __rest
 __global__ void __launch_bounds__(256) index_block_max_kernel(const float* __restrict__ scores, int lds,
                                                               const int* __restrict__ nvalid,
                                                               float* __restrict__ bmax, int ldb, int nblk) {
+  tf_pdl_sync();
   const int r = blockIdx.y, j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= nblk) return;
   const int nv = nvalid[r];
@@ -325,6 +329,7 @@ __global__ void __launch_bounds__(256) index_scores_sparse_kernel(const __nv_bfl
                                                                   const uint8_t* __restrict__ keys,
                                                                   long key_region_stride, int key_row, int Hi,
                                                                   int C, float* __restrict__ out, int ldo) {
+  tf_pdl_sync();
   constexpr int PER = DI / 32;                       // dims per lane
   const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * 8 + warp;
@@ -372,21 +377,21 @@ TF_API int tf_index_scores(const void* q, const float* w, const int* region, con
   p.key_lo = key_lo; p.key_hi = key_hi;
   dim3 grid((key_hi - key_lo + kKeysPerCta - 1) / kKeysPerCta, (T + rows_per_group - 1) / rows_per_group);
   const int smem = kKeysPerCta * (Di + 8) * 2;
-  if (Di == 128) index_score_kernel<128><<<grid, 128, smem, st>>>(p);
-  else if (Di == 64) index_score_kernel<64><<<grid, 128, smem, st>>>(p);
-  else index_score_kernel<32><<<grid, 128, smem, st>>>(p);
+  if (Di == 128) tf_launch(index_score_kernel<128>, dim3(grid), dim3(128), smem, st, p);
+  else if (Di == 64) tf_launch(index_score_kernel<64>, dim3(grid), dim3(128), smem, st, p);
+  else tf_launch(index_score_kernel<32>, dim3(grid), dim3(128), smem, st, p);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_topk_select(const float* scores, int lds, const int* nvalid, int k, int* out, int* count,
                           float* out_scores, int base, int T, cudaStream_t st) {
-  topk_select_kernel<<<T, 1024, 0, st>>>(scores, lds, nvalid, k, out, count, out_scores, base);
+  tf_launch(topk_select_kernel, dim3(T), dim3(1024), 0, st, scores, lds, nvalid, k, out, count, out_scores, base);
   return (int)cudaGetLastError();
 }
 
 TF_API int tf_map_ids(const int* picked, const int* cand_ids, int ldc, int k, int* out, int T,
                       cudaStream_t st) {
-  map_ids_kernel<<<T, 256, 0, st>>>(picked, cand_ids, ldc, k, out);
+  tf_launch(map_ids_kernel, dim3(T), dim3(256), 0, st, picked, cand_ids, ldc, k, out);
   return (int)cudaGetLastError();
 }
 
@@ -394,7 +399,7 @@ TF_API int tf_map_ids(const int* picked, const int* cand_ids, int ldc, int k, in
 TF_API int tf_index_block_max(const float* scores, int lds, const int* nvalid, float* bmax, int ldb, int nblk, int T,
                               cudaStream_t st) {
   if (T <= 0 || nblk <= 0) return 0;
-  index_block_max_kernel<<<dim3((nblk + 255) / 256, T), 256, 0, st>>>(scores, lds, nvalid, bmax, ldb, nblk);
+  tf_launch(index_block_max_kernel, dim3(dim3((nblk + 255) / 256, T)), dim3(256), 0, st, scores, lds, nvalid, bmax, ldb, nblk);
   return (int)cudaGetLastError();
 }
 
@@ -405,10 +410,10 @@ TF_API int tf_index_scores_sparse(const void* q, const float* w, const int* regi
   if (T <= 0 || C <= 0) return 0;
   dim3 grid((C + 7) / 8, T);
   if (Di == 128)
-    index_scores_sparse_kernel<128><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, w, region, cand, ldc,
+    tf_launch(index_scores_sparse_kernel<128>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)q, w, region, cand, ldc,
                                                           (const uint8_t*)keys, key_region_stride, key_row, Hi, C, out, ldo);
   else if (Di == 64)
-    index_scores_sparse_kernel<64><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, w, region, cand, ldc,
+    tf_launch(index_scores_sparse_kernel<64>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)q, w, region, cand, ldc,
                                                          (const uint8_t*)keys, key_region_stride, key_row, Hi, C, out, ldo);
   else return -1;
   return (int)cudaGetLastError();

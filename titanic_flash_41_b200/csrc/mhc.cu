@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(256) hc_prepare_kernel(const __nv_bfloat16* __
                                                          const __nv_bfloat16* __restrict__ norm_w,
                                                          __half* __restrict__ h16, __nv_bfloat16* __restrict__ hb,
                                                          int H, int d, int iters, float eps, float rms_eps) {
+  tf_pdl_sync();
   __shared__ float red[kMaxMix + 1][8];
   __shared__ float mix[kMaxMix + 1];
   __shared__ float s_pre[kMaxH];
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(256) hc_prepare_kernel(const __nv_bfloat16* __
 __global__ void __launch_bounds__(256) hc_post_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ a,
                                                       const HcCoef* __restrict__ coef,
                                                       __nv_bfloat16* __restrict__ y, int H, int d) {
+  tf_pdl_sync();
   const int r = blockIdx.x, c = blockIdx.y;
   const HcCoef k = coef[r];
   const __nv_bfloat16* xr = x + (long)r * H * d;
@@ -156,7 +158,7 @@ TF_API int tf_hc_prepare(const void* x, const float* fn, const float* base, cons
                          float rms_eps, cudaStream_t st) {
   if (H < 1 || H > kMaxH) return -1;
   if (rows <= 0) return 0;
-  hc_prepare_kernel<<<rows, 256, 0, st>>>((const __nv_bfloat16*)x, fn, base, scale, (HcCoef*)coef, (__nv_bfloat16*)v,
+  tf_launch(hc_prepare_kernel, dim3(rows), dim3(256), 0, st, (const __nv_bfloat16*)x, fn, base, scale, (HcCoef*)coef, (__nv_bfloat16*)v,
                                           (const __nv_bfloat16*)norm_w, (__half*)h16, (__nv_bfloat16*)hb, H, d, iters,
                                           eps, rms_eps);
   return (int)cudaGetLastError();
@@ -167,6 +169,6 @@ TF_API int tf_hc_post(const void* x, const float* a, const void* coef, void* y, 
                       cudaStream_t st) {
   if (H < 1 || H > kMaxH) return -1;
   if (rows <= 0) return 0;
-  hc_post_kernel<<<dim3(rows, H), 256, 0, st>>>((const __nv_bfloat16*)x, a, (const HcCoef*)coef, (__nv_bfloat16*)y, H, d);
+  tf_launch(hc_post_kernel, dim3(dim3(rows, H)), dim3(256), 0, st, (const __nv_bfloat16*)x, a, (const HcCoef*)coef, (__nv_bfloat16*)y, H, d);
   return (int)cudaGetLastError();
 }

@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__ CUtensorMap mapW3,
               const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapS1,
               const __grid_constant__ CUtensorMap mapS3, const __grid_constant__ CUtensorMap mapSX, const MxParams p) {
+  tf_pdl_sync();
   constexpr int kMats = DUAL ? 2 : 1;
   constexpr int kStages = DUAL ? 6 : 11;
   // scale bytes of one 512-input block: [128 rows][16] per matrix, then [16 rows][16] of the activations
@@ -368,6 +369,7 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
 // one thread per group of 32 inputs: e4m3 values and the UE8M0 scale 2^ceil(log2(amax / 448))
 __global__ void quant_rows_mx8_kernel(const __half* __restrict__ x, int ldx, uint8_t* __restrict__ q,
                                       uint8_t* __restrict__ s, int rows, int K) {
+  tf_pdl_sync();
   const int ks = K / 32;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * ks) return;
@@ -427,7 +429,7 @@ inline bool make_map_fp4(CUtensorMap* map, const void* base, uint64_t rows, uint
 TF_API int tf_quant_rows_mx8(const void* x, int ldx, void* q, void* s, int rows, int K, cudaStream_t st) {
   if (K % 32 || ldx % 8 || rows <= 0) return -1;
   const int n = rows * (K / 32);
-  quant_rows_mx8_kernel<<<(n + 127) / 128, 128, 0, st>>>(reinterpret_cast<const __half*>(x), ldx,
+  tf_launch(quant_rows_mx8_kernel, dim3((n + 127) / 128), dim3(128), 0, st, reinterpret_cast<const __half*>(x), ldx,
                                                         reinterpret_cast<uint8_t*>(q), reinterpret_cast<uint8_t*>(s),
                                                         rows, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -487,7 +489,7 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
   const int stages = dual ? 6 : 11, mats = dual ? 2 : 1;
   const int sfs = (mats * kTile * 16 + kRows * 16 + 127) / 128 * 128;
   const int smem = stages * (mats * kTile * 128 + kRows * 128) + kSfBufs * sfs + 1024 + 512;
-  if (dual) moe_mx_kernel<1><<<grid, kThreads, smem, st>>>(m1, m3, mx, ms1, ms3, msx, p);
-  else moe_mx_kernel<0><<<grid, kThreads, smem, st>>>(m1, m3, mx, ms1, ms3, msx, p);
+  if (dual) tf_launch(moe_mx_kernel<1>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
+  else tf_launch(moe_mx_kernel<0>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -46,6 +46,7 @@ template <typename T>
 __global__ void quant_rows_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ row_src,
                                   int src_div, const int* __restrict__ row_dst, uint8_t* __restrict__ q,
                                   float* __restrict__ s, int rows, int K) {
+  tf_pdl_sync();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_per_row = K / 128;
   const long item = (long)blockIdx.x * warps + warp;
@@ -73,6 +74,7 @@ template <typename T>
 __global__ void swiglu_rows_kernel(const T* __restrict__ y, long ldy, __half* __restrict__ out16, long ldo,
                                    uint8_t* __restrict__ q, float* __restrict__ s, int rows, int I, float limit,
                                    const int* __restrict__ n_rows_dev) {
+  tf_pdl_sync();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_per_row = I / 128;
   const long item = (long)blockIdx.x * warps + warp;
@@ -111,6 +113,7 @@ __global__ void swiglu_rows_kernel(const T* __restrict__ y, long ldy, __half* __
 
 // ---- routed-expert bookkeeping ------------------------------------------------------------
 __global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int El, int* counts) {
+  tf_pdl_sync();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
   const int e = ids[i] - e_lo;
@@ -119,6 +122,7 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int e
 // single CTA: padded offsets, tile table, cursors reset.  tile_expert has room for max_tiles ints.
 __global__ void moe_offsets_kernel(int* counts, int El, int* offsets, int* cursor, int* tile_expert,
                                    int max_tiles, int* num_tiles, int* padded_rows) {
+  tf_pdl_sync();
   if (threadIdx.x == 0) {
     int off = 0, t = 0;
     for (int e = 0; e < El; ++e) {
@@ -136,6 +140,7 @@ __global__ void moe_offsets_kernel(int* counts, int El, int* offsets, int* curso
 }
 __global__ void moe_place_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int El,
                                  const int* __restrict__ offsets, int* cursor, int* pair_dst) {
+  tf_pdl_sync();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
   const int e = ids[i] - e_lo;
@@ -156,6 +161,7 @@ __global__ void __launch_bounds__(128)
 mxfp4_to_fp8_block_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sc,
                           uint8_t* __restrict__ out, float* __restrict__ out_s, int N, int K,
                           long out_expert_stride, int out_row0, int out_N) {
+  tf_pdl_sync();
   __shared__ int smax;
   __shared__ uint2 lut[16];                // [shift]: bytes 0..7 = e4m3 of magnitude code 0..7 times 2^-shift
   const int kb = blockIdx.x, nb = blockIdx.y, e = blockIdx.z, t = threadIdx.x;
@@ -206,6 +212,7 @@ template <typename T, typename O>
 __global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const int* __restrict__ pair_dst,
                                         const float* __restrict__ wts, const float* __restrict__ shared_y,
                                         O* __restrict__ out, int d, int topk) {
+  tf_pdl_sync();
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float acc = 0.f;
@@ -222,6 +229,7 @@ __global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const
 // a row slice sums the partial outputs every rank sent for it, in rank order, in fp32
 __global__ void sum_slices_kernel(const __nv_bfloat16* __restrict__ slices, int world, long stride,
                                   const float* __restrict__ extra, float* __restrict__ out, long n) {
+  tf_pdl_sync();
   const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
   float acc[8];
@@ -255,9 +263,9 @@ TF_API int tf_quant_rows(const void* x, int x_kind, long ldx, const int* row_src
   const long items = (long)rows * (K / 128);
   const unsigned grid = (unsigned)((items + 7) / 8);
   if (src_div < 1) src_div = 1;
-  if (x_kind == 0) quant_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
-  else if (x_kind == 1) quant_rows_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
-  else quant_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
+  if (x_kind == 0) tf_launch(quant_rows_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
+  else if (x_kind == 1) tf_launch(quant_rows_kernel<__half>, dim3(grid), dim3(256), 0, st, (const __half*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
+  else tf_launch(quant_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, ldx, row_src, src_div, row_dst, (uint8_t*)q, s, rows, K);
   return (int)cudaGetLastError();
 }
 
@@ -267,8 +275,8 @@ TF_API int tf_swiglu_rows(const void* y, int y_kind, long ldy, void* out16, long
   if (ldy % 4 || (reinterpret_cast<uintptr_t>(y) & 15)) return -1;      // rows are read four elements at a time
   const long items = (long)rows * (I / 128);
   const unsigned grid = (unsigned)((items + 7) / 8);
-  if (y_kind == 0) swiglu_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
-  else if (y_kind == 2) swiglu_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
+  if (y_kind == 0) tf_launch(swiglu_rows_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
+  else if (y_kind == 2) tf_launch(swiglu_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, (__half*)out16, ldo, (uint8_t*)q, s, rows, I, limit, n_rows_dev);
   else return -1;
   return (int)cudaGetLastError();
 }
@@ -278,9 +286,9 @@ TF_API int tf_moe_plan(const int* ids, int n_pairs, int e_lo, int El, int* count
                        int* tile_expert, int max_tiles, int* num_tiles, int* padded_rows, int* pair_dst,
                        cudaStream_t st) {
   const unsigned grid = (unsigned)((n_pairs + 255) / 256);
-  moe_count_kernel<<<grid, 256, 0, st>>>(ids, n_pairs, e_lo, El, counts);
-  moe_offsets_kernel<<<1, 32, 0, st>>>(counts, El, offsets, cursor, tile_expert, max_tiles, num_tiles, padded_rows);
-  moe_place_kernel<<<grid, 256, 0, st>>>(ids, n_pairs, e_lo, El, offsets, cursor, pair_dst);
+  tf_launch(moe_count_kernel, dim3(grid), dim3(256), 0, st, ids, n_pairs, e_lo, El, counts);
+  tf_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, st, counts, El, offsets, cursor, tile_expert, max_tiles, num_tiles, padded_rows);
+  tf_launch(moe_place_kernel, dim3(grid), dim3(256), 0, st, ids, n_pairs, e_lo, El, offsets, cursor, pair_dst);
   return (int)cudaGetLastError();
 }
 
@@ -289,7 +297,7 @@ TF_API int tf_mxfp4_to_fp8_block(const void* w, const void* sc, void* out, float
                                  int out_row0, int out_N, cudaStream_t st) {
   if (N % 128 || K % 128 || out_row0 % 128 || out_N % 128) return -1;
   dim3 grid(K / 128, N / 128, E);
-  mxfp4_to_fp8_block_kernel<<<grid, 128, 0, st>>>((const uint8_t*)w, (const uint8_t*)sc, (uint8_t*)out, out_s,
+  tf_launch(mxfp4_to_fp8_block_kernel, dim3(grid), dim3(128), 0, st, (const uint8_t*)w, (const uint8_t*)sc, (uint8_t*)out, out_s,
                                                   N, K, (long)out_N * K, out_row0, out_N);
   return (int)cudaGetLastError();
 }
@@ -300,9 +308,9 @@ TF_API int tf_moe_combine_perm(const void* y, int y_kind, long ldy, const int* p
                                cudaStream_t st) {
   if (T <= 0) return 0;
   if (!y || !pair_dst || !wts || !out) return -1;
-  if (y_kind == 0 && out_kind == 0) moe_combine_perm_kernel<float, float><<<T, 256, 0, st>>>((const float*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
-  else if (y_kind == 2 && out_kind == 0) moe_combine_perm_kernel<__nv_bfloat16, float><<<T, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
-  else if (y_kind == 2 && out_kind == 2) moe_combine_perm_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, st>>>((const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (__nv_bfloat16*)out, d, topk);
+  if (y_kind == 0 && out_kind == 0) tf_launch(moe_combine_perm_kernel<float, float>, dim3(T), dim3(256), 0, st, (const float*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
+  else if (y_kind == 2 && out_kind == 0) tf_launch(moe_combine_perm_kernel<__nv_bfloat16, float>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
+  else if (y_kind == 2 && out_kind == 2) tf_launch(moe_combine_perm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (__nv_bfloat16*)out, d, topk);
   else return -1;
   return (int)cudaGetLastError();
 }
@@ -316,7 +324,7 @@ TF_API int tf_sum_slices(const void* slices, int world, long stride, const float
       (reinterpret_cast<uintptr_t>(out) & 15) || (extra && (reinterpret_cast<uintptr_t>(extra) & 15)))
     return -1;
   const long threads = n / 8;
-  sum_slices_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)slices, world, stride, extra,
+  tf_launch(sum_slices_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)slices, world, stride, extra,
                                                                         out, n);
   return (int)cudaGetLastError();
 }

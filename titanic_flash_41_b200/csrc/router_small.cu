@@ -20,6 +20,7 @@ constexpr int kRowsPerPass = 16;
 __global__ void __launch_bounds__(128)
 router_logits_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ gate,
                            float* __restrict__ out, int ldo, int T, int E, int d) {
+  tf_pdl_sync();
   __shared__ float red[4][kRowsPerPass];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = blockIdx.x;
@@ -72,7 +73,7 @@ router_logits_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const _
 TF_API int tf_router_logits_small(const void* x, int ldx, const void* gate, void* out, int ldo, int T, int E, int d,
                                   cudaStream_t st) {
   if (T <= 0 || d % 8 || ldx % 8) return -1;
-  router_logits_small_kernel<<<E, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+  tf_launch(router_logits_small_kernel, dim3(E), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(x), ldx,
                                                         reinterpret_cast<const __nv_bfloat16*>(gate),
                                                         reinterpret_cast<float*>(out), ldo, T, E, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

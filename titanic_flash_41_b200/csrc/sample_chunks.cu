@@ -140,6 +140,7 @@ __device__ __forceinline__ double prob_of(float l, const RowStat& s, float inv_t
 }
 
 __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkParams p) {
+  tf_pdl_sync();
   extern __shared__ __align__(16) unsigned char smem[];
   float* tbuf = reinterpret_cast<float*>(smem);
   float* dbuf = tbuf + p.chunk;
@@ -549,6 +550,6 @@ TF_API int tf_sample_chunks(const float* tlogits, const float* dlogits, const vo
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sample_chunks_kernel, kThreads, dyn);
     if ((long)per_sm * sms < (long)S * (g + 1) * csplit * ez) return -1;
   }
-  sample_chunks_kernel<<<grid, kThreads, dyn, st>>>(p);
+  tf_launch(sample_chunks_kernel, dim3(grid), dim3(kThreads), dyn, st, p);
   return (int)cudaGetLastError();
 }

@@ -41,6 +41,7 @@ __device__ double block_sum_d(double v, double* scratch) {
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int ldl, int V, int* __restrict__ out,
                               float* __restrict__ out_val) {
+  tf_pdl_sync();
   __shared__ float bv[32];
   __shared__ int bi[32];
   const int r = blockIdx.x;
@@ -141,6 +142,7 @@ __device__ __forceinline__ void slice_range(int V4, int& lo, int& hi) {
 
 __global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ logits, int ldl, int V,
                                                      void* scratch) {
+  tf_pdl_sync();
   const int r = blockIdx.x;
   const float4* x4 = reinterpret_cast<const float4*>(logits + (long)r * ldl);
   int lo, hi;
@@ -172,6 +174,7 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ l
 __global__ void __launch_bounds__(256) rowhist_kernel(const float* __restrict__ logits, int ldl, int V,
                                                       float inv_t, const float* __restrict__ sess_temp, int rps,
                                                       int level, void* scratch) {
+  tf_pdl_sync();
   __shared__ unsigned long long sh[4096];
   const int r = blockIdx.x;
   if (sess_temp) inv_t = __frcp_rn(sess_temp[r / rps]);    // IEEE reciprocal, as the host computes 1 / T
@@ -210,6 +213,7 @@ __global__ void __launch_bounds__(256) rowhist_kernel(const float* __restrict__ 
 __global__ void __launch_bounds__(1024) rowpick_kernel(int level, float top_p, const float* __restrict__ sess_top_p,
                                                        int rps, int last, RowStat* __restrict__ out, void* scratch,
                                                        TfStatusWord* st) {
+  tf_pdl_sync();
   __shared__ unsigned long long chunk[32];
   const int r = blockIdx.x;
   if (sess_top_p) top_p = sess_top_p[r / rps];
@@ -374,6 +378,7 @@ __device__ __forceinline__ double residual(const RowCtx& c, int v) {
 
 // grid (S * (g+1), ntiles), 256 threads: residual mass of one 1024-token tile of one row
 __global__ void __launch_bounds__(256) verify_tiles_kernel(VerifyParams p) {
+  tf_pdl_sync();
   __shared__ double s_w;
   __shared__ double wsum[8];
   const int row = blockIdx.x, s = row / (p.g + 1), i = row % (p.g + 1), tile = blockIdx.y;
@@ -398,6 +403,7 @@ __global__ void __launch_bounds__(256) verify_tiles_kernel(VerifyParams p) {
 
 // grid S, 1024 threads: acceptance length and the emitted token
 __global__ void __launch_bounds__(1024) verify_decide_kernel(VerifyParams p, int ntiles) {
+  tf_pdl_sync();
   __shared__ double scan[1024];
   __shared__ double Rrow[64], wrow[64];
   __shared__ int s_tau, s_tile, s_tok;
@@ -485,7 +491,7 @@ __global__ void __launch_bounds__(1024) verify_decide_kernel(VerifyParams p, int
 
 TF_API int tf_argmax(const float* logits, int ldl, int V, int rows, int* out, float* out_val,
                      cudaStream_t st) {
-  argmax_kernel<<<rows, 1024, 0, st>>>(logits, ldl, V, out, out_val);
+  tf_launch(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, ldl, V, out, out_val);
   return (int)cudaGetLastError();
 }
 
@@ -508,11 +514,11 @@ static int rowstats_launch(const float* logits, int ldl, int V, int rows, float 
   const float inv_t = 1.f / temp;
   const int rps = rows_per_sess > 0 ? rows_per_sess : 1;
   dim3 grid(rows, kSlices);
-  rowmax_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, scratch);
+  tf_launch(rowmax_kernel, dim3(grid), dim3(256), 0, st, logits, ldl, V, scratch);
   const int levels = (sess_top_p || top_p < 1.f) ? 3 : 1;
   for (int level = 0; level < levels; ++level) {
-    rowhist_kernel<<<grid, 256, 0, st>>>(logits, ldl, V, inv_t, sess_temp, rps, level, scratch);
-    rowpick_kernel<<<rows, 1024, 0, st>>>(level, top_p, sess_top_p, rps, level == levels - 1, (RowStat*)out, scratch,
+    tf_launch(rowhist_kernel, dim3(grid), dim3(256), 0, st, logits, ldl, V, inv_t, sess_temp, rps, level, scratch);
+    tf_launch(rowpick_kernel, dim3(rows), dim3(1024), 0, st, level, top_p, sess_top_p, rps, level == levels - 1, (RowStat*)out, scratch,
                                           (TfStatusWord*)status);
   }
   return (int)cudaGetLastError();
@@ -553,8 +559,8 @@ TF_API int tf_spec_verify(const float* tlogits, const float* dlogits, const void
   p.n_accept = n_accept; p.next_token = next_token; p.st = (TfStatusWord*)status;
   const int ntiles = (V + kTile - 1) / kTile;
   dim3 grid(S * (g + 1), ntiles);
-  verify_tiles_kernel<<<grid, 256, 0, st>>>(p);
-  verify_decide_kernel<<<S, 1024, 0, st>>>(p, ntiles);
+  tf_launch(verify_tiles_kernel, dim3(grid), dim3(256), 0, st, p);
+  tf_launch(verify_decide_kernel, dim3(S), dim3(1024), 0, st, p, ntiles);
   return (int)cudaGetLastError();
 }
 

@@ -333,6 +333,7 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 template <int KIND, bool DUAL>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 smallm_gemm_kernel(SmallMParams p) {
+  tf_pdl_sync();
   __shared__ float red[kMaxWarps * (DUAL ? 4 : 2) * 2][32][4];
   __shared__ __align__(16) float ctile[(KIND == 0 && !DUAL) ? 32 * 32 : 4];
   float* tile_out = (KIND == 0 && !DUAL && p.use_comm) ? ctile : nullptr;
@@ -379,7 +380,7 @@ smallm_gemm_kernel(SmallMParams p) {
 template <int KIND, bool DUAL>
 cudaError_t launch(const SmallMParams& p, int slots, cudaStream_t st, int warps = kWarps) {
   dim3 grid((p.N + kTileN - 1) / kTileN, slots > 0 ? slots : 1);
-  smallm_gemm_kernel<KIND, DUAL><<<grid, warps * 32, 0, st>>>(p);
+  tf_launch(smallm_gemm_kernel<KIND, DUAL>, dim3(grid), dim3(warps * 32), 0, st, p);
   return cudaGetLastError();
 }
 
@@ -457,6 +458,6 @@ TF_API int tf_smallm_gemm_allreduce(const void* W, const void* S, int ldw, int l
     if (a != cudaSuccess) return (int)a;
   }
   dim3 grid(N / kTileN, 1);
-  smallm_gemm_kernel<0, false><<<grid, kMaxWarps * 32, dyn, stream>>>(p);
+  tf_launch(smallm_gemm_kernel<0, false>, dim3(grid), dim3(kMaxWarps * 32), dyn, stream, p);
   return (int)cudaGetLastError();
 }

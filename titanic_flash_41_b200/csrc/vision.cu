@@ -18,11 +18,13 @@ namespace {
 typedef __nv_bfloat16 B;
 
 __global__ void vis_bias_kernel(const B* x, const B* bias, B* y, long count, int width) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < count) y[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(bias[i % width]));
 }
 
 __global__ void __launch_bounds__(256) vis_norm_kernel(B* x, const B* delta, const B* w, B* y, int width, float eps) {
+  tf_pdl_sync();
   __shared__ float red[8];
   const long row = blockIdx.x;
   float s = 0.f;
@@ -48,6 +50,7 @@ __global__ void __launch_bounds__(256) vis_norm_kernel(B* x, const B* delta, con
 
 // q, k, v: [heads][n_pad][64]
 __global__ void vis_rope_split_kernel(const B* qkv, B* q, B* k, B* v, int n, int n_pad, int grid_w, int heads) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const int width = heads * 64;
   if (i >= (long)n * width) return;
@@ -68,6 +71,7 @@ __global__ void vis_rope_split_kernel(const B* qkv, B* q, B* k, B* v, int n, int
 
 // scores [rows, ld] f32 -> probs [rows, ld] bf16 over the first n columns (the rest zero)
 __global__ void __launch_bounds__(256) vis_softmax_kernel(const float* s, B* p, int n, int ld, float scale) {
+  tf_pdl_sync();
   __shared__ float red[8];
   const long row = blockIdx.x;
   const float* sr = s + row * ld;
@@ -96,6 +100,7 @@ __global__ void __launch_bounds__(256) vis_softmax_kernel(const float* s, B* p, 
 }
 
 __global__ void vis_swiglu_kernel(const B* gu, B* y, long count, int inter) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const long row = i / inter;
@@ -106,6 +111,7 @@ __global__ void vis_swiglu_kernel(const B* gu, B* y, long count, int inter) {
 }
 
 __global__ void vis_unfold_kernel(const B* x, B* y, int h, int w, int width, long count) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const int cols = width * 9, out_w = (w + 2) / 3;
@@ -115,6 +121,7 @@ __global__ void vis_unfold_kernel(const B* x, B* y, int h, int w, int width, lon
 }
 
 __global__ void vis_gelu_kernel(const B* x, B* y, long count) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const float v = __bfloat162float(x[i]);
@@ -123,6 +130,7 @@ __global__ void vis_gelu_kernel(const B* x, B* y, long count) {
 
 __global__ void vis_span_kernel(const B* f, const B* start, const B* newline, const B* end, B* out, int width,
                                 int tokens, int d) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long)tokens * d) return;
   const int row = (int)(i / d), col = (int)(i % d);
@@ -136,6 +144,7 @@ __global__ void vis_span_kernel(const B* f, const B* start, const B* newline, co
 
 // v [n_pad, 64] -> vt [128, n_pad]: vt[c][r] = v[r][c] for c < 64 and r < n, zero elsewhere
 __global__ void vis_transpose_pad_kernel(const B* v, B* vt, int n, int n_pad) {
+  tf_pdl_sync();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= 128L * n_pad) return;
   const int c = (int)(i / n_pad), r = (int)(i % n_pad);
@@ -146,44 +155,44 @@ inline unsigned blocks(long n) { return (unsigned)((n + 255) / 256); }
 }  // namespace
 
 TF_API int tf_vis_bias(const void* x, const void* bias, void* y, long count, int width, cudaStream_t st) {
-  vis_bias_kernel<<<blocks(count), 256, 0, st>>>((const B*)x, (const B*)bias, (B*)y, count, width);
+  tf_launch(vis_bias_kernel, dim3(blocks(count)), dim3(256), 0, st, (const B*)x, (const B*)bias, (B*)y, count, width);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_norm(void* x, const void* delta, const void* w, void* y, int rows, int width, float eps,
                        cudaStream_t st) {
-  vis_norm_kernel<<<rows, 256, 0, st>>>((B*)x, (const B*)delta, (const B*)w, (B*)y, width, eps);
+  tf_launch(vis_norm_kernel, dim3(rows), dim3(256), 0, st, (B*)x, (const B*)delta, (const B*)w, (B*)y, width, eps);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_rope_split(const void* qkv, void* q, void* k, void* v, int n, int n_pad, int grid_w, int heads,
                              cudaStream_t st) {
-  vis_rope_split_kernel<<<blocks((long)n * heads * 64), 256, 0, st>>>((const B*)qkv, (B*)q, (B*)k, (B*)v, n, n_pad,
+  tf_launch(vis_rope_split_kernel, dim3(blocks((long)n * heads * 64)), dim3(256), 0, st, (const B*)qkv, (B*)q, (B*)k, (B*)v, n, n_pad,
                                                                       grid_w, heads);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_softmax(const float* s, void* p, int rows, int n, int ld, float scale, cudaStream_t st) {
-  vis_softmax_kernel<<<rows, 256, 0, st>>>(s, (B*)p, n, ld, scale);
+  tf_launch(vis_softmax_kernel, dim3(rows), dim3(256), 0, st, s, (B*)p, n, ld, scale);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_swiglu(const void* gu, void* y, long rows, int inter, cudaStream_t st) {
-  vis_swiglu_kernel<<<blocks(rows * inter), 256, 0, st>>>((const B*)gu, (B*)y, rows * inter, inter);
+  tf_launch(vis_swiglu_kernel, dim3(blocks(rows * inter)), dim3(256), 0, st, (const B*)gu, (B*)y, rows * inter, inter);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_unfold(const void* x, void* y, int h, int w, int width, cudaStream_t st) {
   const long count = (long)((h + 2) / 3) * ((w + 2) / 3) * width * 9;
-  vis_unfold_kernel<<<blocks(count), 256, 0, st>>>((const B*)x, (B*)y, h, w, width, count);
+  tf_launch(vis_unfold_kernel, dim3(blocks(count)), dim3(256), 0, st, (const B*)x, (B*)y, h, w, width, count);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_gelu(const void* x, void* y, long count, cudaStream_t st) {
-  vis_gelu_kernel<<<blocks(count), 256, 0, st>>>((const B*)x, (B*)y, count);
+  tf_launch(vis_gelu_kernel, dim3(blocks(count)), dim3(256), 0, st, (const B*)x, (B*)y, count);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_span(const void* f, const void* start, const void* newline, const void* end, void* out, int width,
                        int tokens, int d, cudaStream_t st) {
-  vis_span_kernel<<<blocks((long)tokens * d), 256, 0, st>>>((const B*)f, (const B*)start, (const B*)newline,
+  tf_launch(vis_span_kernel, dim3(blocks((long)tokens * d)), dim3(256), 0, st, (const B*)f, (const B*)start, (const B*)newline,
                                                             (const B*)end, (B*)out, width, tokens, d);
   return (int)cudaGetLastError();
 }
 TF_API int tf_vis_transpose_pad(const void* v, void* vt, int n, int n_pad, cudaStream_t st) {
-  vis_transpose_pad_kernel<<<blocks(128L * n_pad), 256, 0, st>>>((const B*)v, (B*)vt, n, n_pad);
+  tf_launch(vis_transpose_pad_kernel, dim3(blocks(128L * n_pad)), dim3(256), 0, st, (const B*)v, (B*)vt, n, n_pad);
   return (int)cudaGetLastError();
 }

@@ -476,6 +476,7 @@ class Engine:
         self.draft_extra = draft_extra or {}
         self.embed_w, self.head_w, self.final_norm = embed, head, final_norm
         native.lib()
+        native.set_pdl(bool(getattr(ecfg, "pdl", False)))
         self.status = native.StatusWord(self.dev)
         r = cfg.rope
         self.freqs = oracle.rope_frequencies(r.dim, r.theta, r.factor, r.beta_fast, r.beta_slow,
@@ -717,8 +718,10 @@ class Engine:
         if self.big_gemm is not None:
             self.big_gemm(self, x16, w, out, M, w3)
             return
-        # staging path for large row counts when the tensor-core GEMM is not loaded: dequantised
-        # weights through torch.matmul (numerically the same contract, used for validation only)
+        if not self.ecfg.reference_matmul:
+            raise native.NativeError("more than %d rows need the tensor-core path: attach it with ops.bigpath.attach(engine)"
+                                     % self.SMALL_M)
+        # validation only (EngineConfig.reference_matmul): dequantised weights through torch.matmul
         wd = self._dequant_cached(w)
         y = x16[:M].float() @ wd.t()
         if w3 is not None:
@@ -1101,6 +1104,9 @@ class Engine:
         if getattr(self, "big_moe", None) is not None:
             self.big_moe(self, L, T, b)
             return
+        if not self.ecfg.reference_matmul:
+            raise native.NativeError("routed experts of more than %d rows need the tensor-core path: attach it with "
+                                     "ops.bigpath.attach(engine)" % self.SMALL_M)
         cfg = self.cfg
         ids = b["ids"][:T].long()
         e_lo = self.rank * self.El

@@ -134,6 +134,18 @@ def call(name: str, *args, stream: Optional[int] = None) -> None:
         raise NativeError(f"{name} failed with code {rc}" + (" (bad argument)" if rc == -1 else " (CUDA error)"))
 
 
+def set_pdl(on: bool) -> bool:
+    """Launch every kernel of the library with the programmatic-dependent-launch attribute (the next
+    kernel of a stream is made resident while the current one runs; each kernel still waits for its
+    predecessor's completion before it touches memory).  Applies to launches made from now on,
+    including those captured into CUDA graphs.  Returns the previous setting."""
+    return bool(lib().tf_set_pdl(1 if on else 0))
+
+
+def pdl_enabled() -> bool:
+    return bool(lib().tf_get_pdl())
+
+
 STATUS_CODES = {0: "ok", 1: "bad_arg", 2: "timeout", 3: "bad_index", 4: "nonfinite"}
 
 

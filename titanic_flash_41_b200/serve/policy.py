@@ -16,15 +16,46 @@ SHORT_TOKENS = 8192              # checkpoints below this count as "short"
 STALE_AFTER = 32                 # saves after which an entry no longer protects itself by cost
 
 
-def common_prefix(a: Sequence[int], b: Sequence[int]) -> int:
-    """Length of the common prefix; whole 4096-token blocks are compared first."""
-    n = min(len(a), len(b))
+BLOCK = 4096
+
+
+def as_array(tokens) -> "np.ndarray":
+    import numpy as np
+    return tokens if isinstance(tokens, np.ndarray) else np.asarray(tokens, dtype=np.int64)
+
+
+def chain_hashes(tokens, block: int = BLOCK) -> List[bytes]:
+    """Chained digests of the whole ``block``-token blocks of a token sequence: entry k identifies
+    tokens [0, (k + 1) * block).  Two sequences share their first k blocks exactly when their first k
+    entries agree, so million-token prefixes are matched by comparing a few hundred digests."""
+    import hashlib
+    t = as_array(tokens)
+    h = hashlib.sha256()
+    out = []
+    for i in range(0, len(t) - len(t) % block, block):
+        h.update(t[i:i + block].tobytes())
+        out.append(h.digest())
+    return out
+
+
+def common_prefix(a, b, chain_a: Optional[List[bytes]] = None, chain_b: Optional[List[bytes]] = None) -> int:
+    """Length of the common prefix of two token sequences (lists, tuples or integer arrays).  With
+    the sequences' chained block digests the shared whole blocks are found without touching the
+    tokens; the remainder is one vectorised comparison."""
+    import numpy as np
+    ta, tb = as_array(a), as_array(b)
+    n = min(len(ta), len(tb))
     i = 0
-    while i + 4096 <= n and list(a[i:i + 4096]) == list(b[i:i + 4096]):
-        i += 4096
-    while i < n and a[i] == b[i]:
-        i += 1
-    return i
+    if chain_a is not None and chain_b is not None:
+        k = 0
+        m = min(len(chain_a), len(chain_b), n // BLOCK)
+        while k < m and chain_a[k] == chain_b[k]:
+            k += 1
+        i = k * BLOCK
+    if i >= n:
+        return n
+    diff = np.flatnonzero(ta[i:n] != tb[i:n])
+    return n if diff.size == 0 else i + int(diff[0])
 
 
 def cache_capacity(session_budget: int, shared_budget: int, suspended_bytes: int, suspended_count: int,

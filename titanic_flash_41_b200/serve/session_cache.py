@@ -41,17 +41,40 @@ class SessionCache:
     def best_match(self, prompt: Sequence[int], media: str = "") -> Optional[Entry]:
         """Entry with the longest prefix that ``prompt`` starts with (same media identity)."""
         best = None
+        p, pc = self._prompt_key(prompt)
         for e in self.entries:
-            t = e.image.tokens
-            if e.image.media != media or len(t) > len(prompt) or (best and len(t) <= best.image.length):
+            n = e.image.length
+            if e.image.media != media or n > len(p) or (best and n <= best.image.length):
                 continue
-            if policy.common_prefix(prompt, t) == len(t):
+            t, tc = self._entry_key(e)
+            if policy.common_prefix(p, t, pc, tc) == n:
                 best = e
         return best
 
     def longest_shared(self, prompt: Sequence[int]) -> int:
         """Longest prefix of the prompt that any cached conversation also begins with."""
-        return max((policy.common_prefix(prompt, e.image.tokens) for e in self.entries), default=0)
+        p, pc = self._prompt_key(prompt)
+        return max((policy.common_prefix(p, *self._entry_key(e)[:1], pc, self._entry_key(e)[1]) for e in self.entries),
+                   default=0)
+
+    def _prompt_key(self, prompt):
+        """(token array, chained block digests) of a prompt, computed once per request."""
+        last = getattr(self, "_last_prompt", None)
+        if last is not None and last[0] is prompt:
+            return last[1], last[2]
+        arr = policy.as_array(prompt)
+        chain = policy.chain_hashes(arr)
+        self._last_prompt = (prompt, arr, chain)
+        return arr, chain
+
+    @staticmethod
+    def _entry_key(e: "Entry"):
+        k = getattr(e, "_key", None)
+        if k is None:
+            arr = policy.as_array(e.image.tokens)
+            k = (arr, policy.chain_hashes(arr))
+            e._key = k
+        return k
 
     def touch(self, e: Entry, reused: int) -> None:
         self.entries.remove(e)
