@@ -64,3 +64,22 @@ def test_exact_hits_and_prefix_reuse_equal_whole_tokenisation():
     small.tokens(doc)
     small.tokens(doc + "x")
     assert len(small.items) == 1
+
+
+def test_frontend_tokenises_through_the_region_cache():
+    """The HTTP front end encodes the rendered chat marker by marker: the ids equal encoding the whole
+    text, and a long document repeated in the next turn is served from the cache."""
+    from titanic_flash_41_b200.api import protocol as P
+    from titanic_flash_41_b200.api.server import Frontend
+    from titanic_flash_41_b200.api.tokenizer import ByteTokenizer
+    tok = ByteTokenizer(1024)
+    f = Frontend(tok, 1 << 20)
+    doc = "line of the document 12345\n" * 900
+    body = {"messages": [{"role": "user", "content": doc + "first question"}], "max_tokens": 4}
+    req, tokens, limit, pm = f.prepare(body)
+    assert tokens == tok.encode(P.render_chat(req)) and pm is None
+    body2 = {"messages": body["messages"] + [{"role": "assistant", "content": "answer"},
+                                             {"role": "user", "content": "second question"}], "max_tokens": 4}
+    req2, tokens2, _, _ = f.prepare(body2)
+    assert tokens2 == tok.encode(P.render_chat(req2))
+    assert f.regions.stats["hits"] >= 1                      # the document region was not tokenised again

@@ -255,3 +255,51 @@ def test_job_cancelled_while_queued_gets_a_terminal_event():
     s.release(a)
     assert s.admit() == []
     assert ("b", "error", {"code": "cancelled", "message": "cancelled while queued"}) in ev
+
+
+def test_two_conversations_take_turns_in_one_region_token_exactly():
+    """More conversations than regions: the decoding conversation is parked as a request checkpoint
+    after its turn, the waiting one runs, and so on; every conversation commits exactly the tokens
+    it commits when it runs alone (sampling is addressed by position)."""
+    cfg = tiny_config()
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, cfg.vocab, (30 + 7 * i,), generator=g).tolist() for i in range(2)]
+
+    def solo(p, seed):
+        _, w, s = _mk(regions=1, turn_tokens=0)
+        ev = []
+        s.submit(_job("x", p, 30, ev, temperature=0.7, top_p=0.9, seed=seed))
+        _drain(w)
+        return [t for j, k, pl in ev if k == "tokens" for t in pl]
+    want = [solo(p, 11 + i) for i, p in enumerate(prompts)]
+    _, w, s = _mk(regions=1, turn_tokens=8)
+    ev = []
+    for i, p in enumerate(prompts):
+        s.submit(_job(f"c{i}", p, 30, ev, temperature=0.7, top_p=0.9, seed=11 + i))
+    _drain(w, max_cmds=2000)
+    for i in range(2):
+        got = [t for j, k, pl in ev if k == "tokens" and j == f"c{i}" for t in pl]
+        assert got == want[i], i
+    kinds = [e["kind"] for e in w.log.snapshot(4096)["events"]]
+    assert kinds.count("pause") >= 2 and kinds.count("resume") == kinds.count("pause")
+    assert sorted(j for j, k, pl in ev if k == "done") == ["c0", "c1"] and not w.parked
+
+
+def test_copy_proposals_from_history_lookup_are_verified_exactly():
+    """A prompt that repeats itself: the lookup proposes the continuation it saw, greedy decoding
+    commits exactly what it commits without the lookup, in fewer steps."""
+    cfg = tiny_config()
+    g = torch.Generator().manual_seed(5)
+    phrase = torch.randint(3, cfg.vocab, (40,), generator=g).tolist()
+    prompt = phrase + phrase + phrase[:20]
+
+    def run(lookup):
+        _, w, s = _mk(regions=1, history_lookup=lookup)
+        ev = []
+        s.submit(_job("h", prompt, 16, ev, temperature=0.0))
+        _drain(w)
+        done = [pl for j, k, pl in ev if k == "done"][0]
+        return [t for j, k, pl in ev if k == "tokens" for t in pl], done["steps"]
+    plain, _ = run(False)
+    with_lookup, _ = run(True)
+    assert with_lookup == plain

@@ -45,6 +45,32 @@ class Frontend:
         one a request that carries image parts is refused (it must never be answered as if the image
         had been seen)."""
         self.tok, self.context, self.allow_sampling, self.vision = tokenizer, context, allow_sampling, vision
+        # plain-text regions between template markers are tokenised through a bounded, exact cache:
+        # long documents repeat from turn to turn (reference: src/prompt_regions.rs)
+        from .prompt_regions import RegionCache
+        import re
+        specials = getattr(tokenizer, "special_ids", None)
+        self._special_ids = dict(specials) if specials else {}
+        self._split = (re.compile("(" + "|".join(re.escape(s) for s in sorted(self._special_ids, key=len, reverse=True)) + ")")
+                       if self._special_ids else None)
+        self.regions = RegionCache(tokenizer.encode, lambda t: tokenizer.decode([t]))
+
+    def encode(self, text: str):
+        """Token ids of a rendered prompt: template markers are single ids, the plain regions between
+        them go through the region cache (a marker is a hard token boundary, so this equals encoding
+        the whole text)."""
+        if self._split is None:
+            return self.tok.encode(text)
+        out = []
+        for piece in self._split.split(text):
+            if not piece:
+                continue
+            sid = self._special_ids.get(piece)
+            if sid is not None:
+                out.append(sid)
+            else:
+                out += self.regions.tokens(piece)
+        return out
 
     def prepare(self, body: Dict[str, Any]):
         """-> (request, prompt tokens, token limit, PromptMedia or None).  Image parts become runs of
@@ -53,7 +79,7 @@ class Frontend:
         from . import media as M
         req = P.normalize_chat_request(body, self.allow_sampling)
         text = P.render_chat(req)
-        tokens = self.tok.encode(text)
+        tokens = self.encode(text)
         uris = P.image_parts(req.messages)
         pm = None
         if uris:

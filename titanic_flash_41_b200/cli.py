@@ -137,8 +137,9 @@ def make_backend(args, cfg: ModelConfig, comm):
     torch.cuda.set_device(dev)
     ecfg = EngineConfig(tp=world, regions=args.regions, max_context=args.max_context)
     if args.checkpoint:
-        from .models import loader
-        eng = loader.load_engine(args.checkpoint, cfg, ecfg, comm, device=dev)
+        # streamed, digest-checked, in the stored formats: never more than one layer on the host
+        from .models import stream_loader
+        eng = stream_loader.load_engine(args.checkpoint, cfg, ecfg, comm, device=dev)
     else:
         eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=args.seed)
     if world > 1:

@@ -66,6 +66,9 @@ struct ChunkParams {
   const float* sess_top_p;  // [S]
   int S, g, V, ldl, chunk, P, csplit;
   int point_mass;
+  const int* sess_point;    // [S] or null: 1 = this conversation's proposals are point masses (copy proposals)
+  const int* forced;        // g = 0 only, [S] at forced[s * tok_stride] or null: conversations flagged in
+                            // sess_point emit this token instead of the draw (their proposal is known)
   RowStat* tstat;           // out: statistics of the target rows, row r at tstat[r * stat_stride]
   int stat_stride;
   int* n_accept;            // out [S] (may be null)
@@ -175,7 +178,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   // ---- stage this chunk of the target row (and of the draft row it is verified against)
   const int n = p.chunk;
   const float* trow = p.tlogits + ez * p.emu_tl + (long)row * p.ldl + (long)lc * n;
-  const bool has_d = (i < g) && p.dlogits != nullptr;
+  const bool point = p.point_mass || (p.sess_point && p.sess_point[s]);
+  const bool has_d = (i < g) && p.dlogits != nullptr && !point;
   const float* drow = has_d ? p.dlogits + ez * p.emu_dl + (long)(s * g + i) * p.ldl + (long)lc * n : nullptr;
   for (int k = threadIdx.x * 4; k < n; k += kThreads * 4) {
     *reinterpret_cast<float4*>(tbuf + k) = *reinterpret_cast<const float4*>(trow + k);
@@ -330,13 +334,13 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   RowStat ds;
   float d_inv = inv_t;
   ds.m = 0.f; ds.thr = 0; ds.z = 1.0;
-  if (i < g && !p.point_mass && p.dstat) ds = p.dstat[s * g + i];
+  if (i < g && !point && p.dstat) ds = p.dstat[s * g + i];
   if (g > 0) {
     if (i < g && threadIdx.x == 0) {
       const int x = p.proposals[s * g + i];
       if (x >= base && x < base + n) {
         const double pt = prob_of(tbuf[x - base], stat, inv_t);
-        const double q = (p.point_mass || !has_d) ? 1.0 : prob_of(dbuf[x - base], ds, d_inv);
+        const double q = (point || !has_d) ? 1.0 : prob_of(dbuf[x - base], ds, d_inv);
         const long w0 = A.prop + ((long)par * p.max_rows + row) * 4;
         push_double(p, w0, pt, tag0 + 5);
         push_double(p, w0 + 2, q, tag0 + 5);
@@ -365,8 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
 
   // ---- 4. residual mass of this chunk: max(w_i p_i(v) - q_i(v), 0); the bonus row has q = 0
   const double wz = wrow[i] / stat.z;
-  const double qz = (has_d && !p.point_mass) ? 1.0 / ds.z : 0.0;
-  const int point_tok = (i < g && p.point_mass) ? p.proposals[s * g + i] : -1;
+  const double qz = has_d ? 1.0 / ds.z : 0.0;
+  const int point_tok = (i < g && point) ? p.proposals[s * g + i] : -1;
   auto residual = [&](int k) -> double {
     const float l = tbuf[k];
     double val = fkey(l) >= stat.thr ? wz * (double)expf((l - stat.m) * inv_t) : 0.0;
@@ -486,7 +490,9 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   if (i == 0 && lc == 0 && threadIdx.x == 0) {
     const ulonglong2 v = W.wait(mine + A.tok + ((long)par * p.max_rows + s) * 2, tag0 + 7, 7, row);
     if (!s_fail) {
-      p.next_token[ez * p.emu_tok + (long)s * p.tok_stride] = (int)(uint32_t)v.x;
+      int tok = (int)(uint32_t)v.x;
+      if (g == 0 && p.forced && p.sess_point && p.sess_point[s]) tok = p.forced[(long)s * p.tok_stride];
+      p.next_token[ez * p.emu_tok + (long)s * p.tok_stride] = tok;
       if (p.n_accept) p.n_accept[ez * p.emu_acc + s] = (int)(uint32_t)v.y;
     }
   }
@@ -510,13 +516,16 @@ TF_API long tf_sample_chunks_workspace_bytes(int V, int max_rows) {
 }
 
 // One launch = row statistics + block verification (g > 0) or plain sampling (g = 0) of S
-// conversations; see the header of this file.  `ctr`: world_emulated * max_rows * (P / world) zeroed
+// conversations; see the header of this file.  sess_point [S] (optional) flags conversations whose
+// proposals are point masses (copy proposals found on the host); in a g = 0 launch such a
+// conversation emits forced[s * tok_stride] instead of its draw.  `ctr`: world_emulated * max_rows * (P / world) zeroed
 // ints of this rank.  ranks_emulated > 1 runs that many ranks in one cooperative launch on this GPU
 // (peers then names areas of this device; emu_* are the element strides between the ranks' logits and
 // output arrays; proposals and dstat are shared by the emulated ranks).
 TF_API int tf_sample_chunks(const float* tlogits, const float* dlogits, const void* dstat, const int* proposals,
                             const double* uniforms, int u_stride, const float* sess_temp, const float* sess_top_p,
-                            int S, int g, int V, int ldl, int point_mass, void* tstat, int stat_stride, int* n_accept,
+                            int S, int g, int V, int ldl, int point_mass, const int* sess_point, const int* forced,
+                            void* tstat, int stat_stride, int* n_accept,
                             int* next_token, int tok_stride, const void* peers, int world, int rank, int max_rows,
                             void* ctr, int spin_limit, void* status, int ranks_emulated, long emu_tl, long emu_dl,
                             long emu_stat, long emu_tok, long emu_acc, cudaStream_t st) {
@@ -533,6 +542,7 @@ TF_API int tf_sample_chunks(const float* tlogits, const float* dlogits, const vo
   p.tlogits = tlogits; p.dlogits = dlogits; p.dstat = (const RowStat*)dstat; p.proposals = proposals;
   p.uniforms = uniforms; p.u_stride = u_stride; p.sess_temp = sess_temp; p.sess_top_p = sess_top_p;
   p.S = S; p.g = g; p.V = V; p.ldl = ldl; p.chunk = chunk; p.P = P; p.csplit = csplit; p.point_mass = point_mass;
+  p.sess_point = sess_point; p.forced = forced;
   p.tstat = (RowStat*)tstat; p.stat_stride = stat_stride; p.n_accept = n_accept; p.next_token = next_token;
   p.tok_stride = tok_stride; p.peers = (const unsigned long long*)peers; p.world = world; p.rank = rank;
   p.max_rows = max_rows; p.ctr = (unsigned int*)ctr; p.spin_limit = spin_limit; p.st = (TfStatusWord*)status;

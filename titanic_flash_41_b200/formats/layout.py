@@ -99,6 +99,10 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
             out.append((name + ".scale", sdt, (-(-n // blk), -(-k // blk))))
 
     n_draft = cfg.draft.layers if cfg.draft is not None else 0
+    if cfg.hc_mult > 1:
+        # final collapse of the residual copies in front of the head (reference: src/model_io.rs)
+        m = cfg.hc_mult
+        out += [("hc_head_fn", "F32", (m, m * d)), ("hc_head_base", "F32", (m,)), ("hc_head_scale", "F32", (1,))]
     if n_draft and cfg.draft.subset_rows:
         # token ids of the drafter's 4-bit vocabulary-subset head (the rows themselves are cut from head.weight)
         out.append(("mtp.head_subset.ids", "I64", (cfg.draft.subset_rows,)))
@@ -125,9 +129,9 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
         draft = l >= cfg.n_layers
         p = f"mtp.{l - cfg.n_layers}" if draft else f"layers.{l}"
         if draft and l == cfg.n_layers:
-            dense(f"{p}.main_proj", d, 2 * d)
+            dense(f"{p}.main_proj", d, d * (1 + cfg.draft.condition_layers))
             out.append((f"{p}.enorm.weight", "BF16", (d,)))
-            out.append((f"{p}.hnorm.weight", "BF16", (d,)))
+            out.append((f"{p}.hnorm.weight", "BF16", (d * cfg.draft.condition_layers,)))
         for br in ("attn", "ffn"):
             out.append((f"{p}.{br}_norm.weight", "BF16", (d,)))
             if cfg.hc_mult > 1:

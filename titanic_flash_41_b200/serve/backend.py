@@ -72,12 +72,19 @@ class OracleBackend:
             draft_u, accept_u, final_u = rng.round_uniforms(sl.seed, sl.length, g)
             props, Q = [], []
             hid, tok = self.hidden[sl.region], sl.anchor
-            for j in range(g):
+            copied = None
+            if g > 0 and sl.lookup is not None:
+                prop = sl.lookup.propose(pending=[sl.anchor])
+                if prop is not None and len(prop.tokens) >= g:
+                    copied = prop.tokens[:g]           # point-mass proposals: no draft law to sample
+            for j in range(g if copied is None else 0):
                 lg, hid = self.model.draft_forward(torch.tensor([tok]), hid, s, sl.length + j)
                 q = verify.modified_law(lg, sl.temperature, sl.top_p)[0]
                 tok = verify.sample_from(q, draft_u[j]) if sl.temperature > 0 else int(q.argmax())
                 props.append(tok)
                 Q.append(q)
+            if copied is not None:
+                props, Q = list(copied), None
             rows = torch.tensor([sl.anchor] + props)
             lg = self.model.forward(rows, s, start=sl.length, commit=False)
             P = verify.modified_law(lg, sl.temperature, sl.top_p)
@@ -90,8 +97,10 @@ class OracleBackend:
                     tau += 1
                 nxt = int(P[tau].argmax())
             else:
-                tau, nxt = verify.block_verify(P, torch.stack(Q), props, accept_u, final_u)
+                tau, nxt = verify.block_verify(P, torch.stack(Q) if Q is not None else None, props, accept_u, final_u)
             toks = [sl.anchor] + props[:tau]
+            if sl.lookup is not None:
+                sl.lookup.commit(sl.length, toks)
             sl.length += len(toks)
             s.length = sl.length
             sl.emitted += toks

@@ -61,7 +61,8 @@ def resume(worker, ck: RequestCheckpoint, region: int, job) -> None:
     worker.b.restore(region, ck.image)
     slot = DecodeSlot(region=region, length=len(ck.committed), anchor=ck.anchor, seed=ck.seed,
                       temperature=ck.temperature, top_p=ck.top_p, recent=list(ck.committed[-8:]))
-    job.generated = list(ck.emitted)
+    if not job.generated:                 # a placeholder job (ranks other than 0) takes over the emitted tokens
+        job.generated = list(ck.emitted)
     job.region = region
     worker.active[region] = Active(job, slot, list(ck.prompt), ck.limit, time.monotonic(), time.monotonic())
     worker.jobs[job.id] = job

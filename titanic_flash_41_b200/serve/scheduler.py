@@ -112,6 +112,20 @@ class Scheduler:
             pass
         return True
 
+    def occupy(self, job: Job, region: int) -> None:
+        """A parked conversation returns to a region (the worker resumes it there)."""
+        with self.lock:
+            if region in self.active:
+                raise RuntimeError(f"region {region} is not free")
+            job.region = region
+            self.active[region] = job
+
+    def oldest_submitted(self) -> float:
+        """Submission time of the request at the head of the queue (inf when nothing waits)."""
+        with self.lock:
+            heads = [q[0].submitted for q in (self.fg, self.bg) if q]
+            return min(heads) if heads else float("inf")
+
     def release(self, job: Job) -> None:
         with self.lock:
             if self.active.get(job.region) is job:

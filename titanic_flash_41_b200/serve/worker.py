@@ -14,6 +14,11 @@ Begin   restore the best cached image whose prefix the prompt starts with, prefi
         should_cancel -> PrefillDirective through the control channel, src/resident_worker.rs:4009)
 Step    one batched speculative verification round for every decoding conversation
 Finish  save the completed turn into the session cache and free the region
+Pause   park a decoding conversation as a request checkpoint (state image + sampler position) so
+        that a waiting request can take its region: with more conversations than regions they
+        take turns of ``turn_tokens`` tokens (reference: 64-token turns through parked images,
+        src/batched_serving.rs:1-17, src/request_checkpoint.rs)
+Resume  attach a parked conversation to a free region; it continues token-exactly
 Idle    one unit of background cache work (tier moves)
 """
 from __future__ import annotations
@@ -41,6 +46,7 @@ class Active:
     first_token_at: float = 0.0
     steps: int = 0
     finished: Optional[str] = None
+    turn: int = 0                      # tokens delivered since the conversation was last attached to a region
 
 
 # per-chunk prefill directives (rank 0 decides, every rank follows)
@@ -51,7 +57,8 @@ class Worker:
     def __init__(self, backend, scheduler: Optional[Scheduler], cache: Optional[SessionCache] = None,
                  eos_id: int = 1, log: Optional[EventLog] = None, control=None, rank: int = 0,
                  prefill_slice_s: float = 0.5, checkpoint_min: int = policy.SHORT_TOKENS,
-                 checkpoint_align: int = 8192, span_encoder=None, health=None):
+                 checkpoint_align: int = 8192, span_encoder=None, health=None, turn_tokens: int = 64,
+                 history_lookup: bool = True):
         """``span_encoder`` (rank 0): ``api.media.SpanEncoder`` over the vision tower; needed to serve
         requests that carry images."""
         self.b, self.sched, self.cache = backend, scheduler, cache or SessionCache()
@@ -63,6 +70,10 @@ class Worker:
         self.requests = 0
         self.span_encoder = span_encoder
         self.health = health                 # utils.health.Health: sticky record of what stopped this rank
+        self.turn_tokens = turn_tokens       # 0: never park a decoding conversation for a waiting one
+        self.history_lookup = history_lookup
+        self.parked: List[Any] = []          # RequestCheckpoints waiting for a region, oldest first (every rank)
+        self.parked_jobs: Dict[str, Job] = {}
         self.clock = time.monotonic          # rank 0's time source for prefill slices (tests skew it)
         self.directives: List[int] = []      # per-chunk directives this rank followed (diagnostics)
 
@@ -115,6 +126,24 @@ class Worker:
         for a in list(self.active.values()):
             if a.finished or a.job.cancelled.is_set():
                 return {"op": "finish", "region": a.job.region, "reason": a.finished or "cancelled"}
+        if self.sched is not None:
+            free = self.sched.free_regions()
+            waiting = self.sched.waiting()
+            if self.parked and free and (not waiting or self.parked_jobs[self.parked[0].id].submitted
+                                         <= self.sched.oldest_submitted()):
+                # a parked conversation goes first when it has waited longer than the queue's head
+                ck = self.parked[0]
+                job = self.parked_jobs[ck.id]
+                if job.cancelled.is_set():
+                    return {"op": "drop_parked", "id": ck.id}
+                self.sched.occupy(job, free[0])
+                return {"op": "resume", "id": ck.id, "region": free[0]}
+            if waiting and not free and self.turn_tokens > 0:
+                # every region decodes and a request waits: the conversation that has had the longest turn yields
+                over = [a for a in self.active.values() if not a.finished and a.turn >= self.turn_tokens]
+                if over:
+                    a = max(over, key=lambda x: (x.turn, -x.job.region))
+                    return {"op": "pause", "region": a.job.region}
         new = self.sched.admit() if self.sched else []
         if new:
             j = new[0]
@@ -148,7 +177,7 @@ class Worker:
         else:
             cmd = self._recv_command()
         self.execute(cmd)
-        if self.control is not None and cmd["op"] in ("begin", "step", "finish"):
+        if self.control is not None and cmd["op"] in ("begin", "step", "finish", "pause", "resume"):
             self.control.agree(self._digest())
         return cmd["op"]
 
@@ -199,6 +228,15 @@ class Worker:
             self._step()
         elif op == "finish":
             self._finish(cmd["region"], cmd["reason"])
+        elif op == "pause":
+            self._pause(cmd["region"])
+        elif op == "resume":
+            self._resume(cmd["id"], cmd["region"])
+        elif op == "drop_parked":
+            self.parked = [c for c in self.parked if c.id != cmd["id"]]
+            job = self.parked_jobs.pop(cmd["id"], None)
+            self._emit(job, "done", {"finish_reason": "cancelled", "completion_tokens": len(job.generated) if job else 0,
+                                     "prompt_tokens": 0, "steps": 0, "decode_tok_s": 0.0})
         elif op == "idle":
             did = self.cache.idle_step()
             if did:
@@ -267,6 +305,35 @@ class Worker:
         offs = torch.from_numpy(np.frombuffer(bytes(blob[:m * 8]), dtype=np.int64).copy())
         rows = torch.from_numpy(np.frombuffer(bytes(blob[m * 8:total]), dtype=np.int16).copy()).view(torch.bfloat16).view(m, d)
         return offs, rows
+
+    def _pause(self, region: int) -> None:
+        from . import request_checkpoint as RC
+        a = self.active.get(region)
+        if a is None:
+            return
+        job = a.job
+        lookup = a.slot.lookup
+        ck = RC.pause(self, region)
+        ck.lookup, ck.steps, ck.started, ck.first_token_at = lookup, a.steps, a.started, a.first_token_at
+        self.parked.append(ck)
+        self.parked_jobs[ck.id] = job
+        if self.sched is not None:
+            self.sched.release(job)
+        self.log.log("pause", id=ck.id, region=region, committed=len(ck.committed), bytes=ck.charge)
+
+    def _resume(self, rid: str, region: int) -> None:
+        from . import request_checkpoint as RC
+        ck = next((c for c in self.parked if c.id == rid), None)
+        if ck is None:
+            raise RuntimeError(f"resume of an unknown parked request {rid}")
+        self.parked.remove(ck)
+        job = self.parked_jobs.pop(rid)
+        RC.resume(self, ck, region, job)
+        a = self.active[region]
+        a.slot.lookup = getattr(ck, "lookup", None)
+        a.steps, a.started, a.first_token_at = getattr(ck, "steps", 0), getattr(ck, "started", a.started), \
+            getattr(ck, "first_token_at", a.first_token_at)
+        self.log.log("resume", id=rid, region=region, committed=len(ck.committed))
 
     def _emit(self, job: Optional[Job], kind: str, payload: Any) -> None:
         if job is not None and self.rank == 0:
@@ -340,6 +407,9 @@ class Worker:
         first = self.b.sample(logits, cmd["temperature"], cmd["top_p"], cmd["seed"], len(prompt))
         slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=cmd["seed"],
                           temperature=cmd["temperature"], top_p=cmd["top_p"], recent=list(prompt[-8:]))
+        if self.history_lookup:
+            from ..spec.history_lookup import HistoryLookup
+            slot.lookup = HistoryLookup(prompt, depth=8)
         a = Active(job or Job(cmd["id"], prompt, cmd["limit"]), slot, prompt, cmd["limit"], t0, time.monotonic())
         a.job.region = region
         self.active[region] = a
@@ -360,6 +430,7 @@ class Worker:
                 a.finished = "stop"
                 break
             a.job.generated.append(t)
+            a.turn += 1
             out.append(t)
             if len(a.job.generated) >= a.limit:
                 a.finished = "length"

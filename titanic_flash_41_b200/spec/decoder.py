@@ -43,6 +43,10 @@ class DecodeSlot:
     # models with Engram layers: the committed tokens right before ``anchor`` (oldest first; the
     # last ngram-1 are used), from which the device hashes the n-gram ids of the step's rows
     recent: List[int] = field(default_factory=list)
+    # spec.history_lookup.HistoryLookup over the conversation's committed text (optional): when the
+    # text ends with a phrase seen before, the tokens that followed it then are proposed as point
+    # masses instead of the draft head's samples (reference: src/dspark_generation.rs:1908)
+    lookup: Optional[object] = None
 
 
 def step_meta(regions: Sequence[int], lengths: Sequence[int], anchors: Sequence[int], g: int, ratio: int):
@@ -99,7 +103,10 @@ class SpecDecoder:
         self.n_eg = S * self.R * self.n_rec          # per verify row: the tokens before its block
         if engine.engram:
             self.bv["eg_hash"] = True
-        self.h_int = torch.zeros(self.n_meta_v + g * self.n_meta_d + self.n_eg, dtype=torch.int32).pin_memory()
+        self.n_look = S * (1 + max(g, 1))            # copy proposals: [flag per conversation | tokens S x g]
+        self.h_int = torch.zeros(self.n_meta_v + g * self.n_meta_d + self.n_eg + self.n_look,
+                                 dtype=torch.int32).pin_memory()
+        self.lookup_hits = 0
         self.d_int = torch.zeros_like(self.h_int, device=dev)
         self.h_u = torch.zeros(S, g + 2, dtype=torch.float64).pin_memory()     # accept[g], final, spare
         self.d_u = torch.zeros_like(self.h_u, device=dev)
@@ -157,6 +164,17 @@ class SpecDecoder:
             hi[o: o + self.n_eg] = StepPlan.recent_rows(cfg, [(R, s.recent) for s in slots]).reshape(-1)
         hf = self.h_f.numpy()
         hu = self.h_u.numpy()
+        o = self.n_meta_v + g * self.n_meta_d + self.n_eg
+        look = hi[o: o + self.n_look]
+        look[:] = 0
+        gs = max(g, 1)
+        for i, s in enumerate(slots):
+            if g > 0 and s.lookup is not None and self.ws is not None:
+                prop = s.lookup.propose(pending=[s.anchor])
+                if prop is not None and len(prop.tokens) >= g:
+                    look[i] = 1
+                    look[S + i * gs: S + i * gs + g] = prop.tokens[:g]
+                    self.lookup_hits += 1
         for i, s in enumerate(slots):
             hf[0, i] = max(float(s.temperature), 1e-3)      # temperature 0 (greedy) = a very sharp law
             hf[1, i] = min(max(float(s.top_p), 1e-6), 1.0)
@@ -179,6 +197,9 @@ class SpecDecoder:
         local = ws is not None
         temp, topp = self.d_f[0], self.d_f[1]
         gs = max(g, 1)
+        o = self.n_meta_v + g * self.n_meta_d + self.n_eg
+        look = self.d_int[o: o + S]                              # 1: the conversation's proposals were found by lookup
+        lprops = self.d_int[o + S: o + self.n_look].view(S, gs)
         for j in range(g):
             o = self.n_meta_v + j * self.n_meta_d
             md = self.d_int[o: o + self.n_meta_d].view(StepPlan.META_ROWS, S)
@@ -194,7 +215,7 @@ class SpecDecoder:
                 # one launch: statistics of the row (kept for the verification) + the draw, on this
                 # rank's columns; writes props[:, j] and dstat[:, j] in place
                 ws.sample(lg, None, None, None, self.d_ud[:, j:], gs, temp, topp, S, 0, lg.stride(0),
-                          self.dstat[:, j], gs, None, self.props[:, j:], gs, st)
+                          self.dstat[:, j], gs, None, self.props[:, j:], gs, st, sess_point=look, forced=lprops[:, j:])
                 continue
             stat = self.dstat[:, j].contiguous()
             native.call("tf_rowstats_per_session", lg, V, V, S, temp, topp, 1, stat, self.rs_scratch, st)
@@ -216,7 +237,7 @@ class SpecDecoder:
         if local:
             ws.sample(logits, self.dlogits if g > 0 else None, self.dstat if g > 0 else None,
                       self.props if g > 0 else None, self.d_u, g + 2, temp, topp, S, g, logits.stride(0),
-                      self.tstat, 1, self.d_out[0], self.d_out[1], 1, st)
+                      self.tstat, 1, self.d_out[0], self.d_out[1], 1, st, sess_point=look if g > 0 else None)
         else:
             native.call("tf_rowstats_per_session", logits, V, V, S * R, temp, topp, R, self.tstat, self.rs_scratch, st)
             native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
@@ -269,6 +290,8 @@ class SpecDecoder:
         props = self.h_out[2:].t().tolist() if self.g > 0 else None
         for i, s in enumerate(slots):
             toks = [s.anchor] + (props[i][: acc[i]] if props else [])
+            if s.lookup is not None:
+                s.lookup.commit(s.length, toks)
             s.length += len(toks)
             s.emitted += toks
             if self.n_rec:

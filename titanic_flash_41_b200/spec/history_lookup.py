@@ -40,13 +40,16 @@ class HistoryLookup:
         self.slots, self.lengths, self.depth = slots, tuple(lengths), depth
         self.minimum = minimum_match or self.lengths[0]
         self.tables = [[EMPTY] * slots for _ in self.lengths]
-        if prefix:
+        if len(prefix):
             self.commit(0, prefix)
 
     def commit(self, at: int, tokens: Sequence[int]) -> None:
         """Append ``tokens`` at position ``at`` (must equal the current length: history is append-only)."""
         if at != len(self.tokens):
             raise ValueError("history commits must be contiguous")
+        if len(tokens) > 256:
+            self._commit_bulk(tokens)
+            return
         for t in tokens:
             self.tokens.append(int(t))
             end = len(self.tokens)
@@ -56,6 +59,32 @@ class HistoryLookup:
                     key = fingerprint(self.tokens[end - 1 - L:end - 1]) % self.slots
                     self.tables[li][key] = end - 1           # position of the token that followed
 
+    def _commit_bulk(self, tokens: Sequence[int]) -> None:
+        """Index a long run (a prompt) with vectorised fingerprints: the same table contents as
+        token-by-token commits (a slot keeps the LAST position that hashed to it)."""
+        import numpy as np
+        base = len(self.tokens)
+        self.tokens.extend(int(t) for t in tokens)
+        text = np.asarray(self.tokens, dtype=np.uint64) & np.uint64(0xFFFFFFFF)
+        n = len(self.tokens)
+        for li, L in enumerate(self.lengths):
+            # windows [i, i + L) predict token i + L; only windows whose predicted token is new
+            lo = max(0, base - L)
+            hi = n - L                      # predicted positions lo + L .. n - 1
+            if hi <= lo:
+                continue
+            v = np.full(hi - lo, 0xCBF29CE484222325, dtype=np.uint64)
+            with np.errstate(over="ignore"):
+                for k in range(L):
+                    v = (v ^ text[lo + k: hi + k]) * np.uint64(0x100000001B3)
+            v = v ^ (v >> np.uint64(32))
+            keys = (v % np.uint64(self.slots)).astype(np.int64)
+            pos = np.arange(lo + L, hi + L, dtype=np.int64)
+            keep = pos >= max(base, L)
+            tab = np.asarray(self.tables[li], dtype=np.int64)
+            np.maximum.at(tab, keys[keep], pos[keep])
+            self.tables[li] = tab.tolist()
+
     def truncate(self, length: int) -> None:
         """Drop text past ``length`` (a cancelled or rolled-back turn); stale slots are caught by confirmation."""
         del self.tokens[length:]
@@ -63,22 +92,27 @@ class HistoryLookup:
     def propose(self, pending: Sequence[int] = ()) -> Optional[Proposal]:
         """``pending``: tokens already emitted but not yet committed (the anchor); the match runs over
         committed text followed by them."""
-        text = self.tokens + [int(t) for t in pending]
-        n = len(text)
+        pend = [int(t) for t in pending]
+        nt = len(self.tokens)
+        n = nt + len(pend)
+        span = self.lengths[-1]
+        tail = self.tokens[max(0, nt - span):] + pend        # the last tokens of the text: no copy of the history
+        at = lambda i: self.tokens[i] if i < nt else pend[i - nt]
         for li in range(len(self.lengths) - 1, -1, -1):
             L = self.lengths[li]
-            if n < L or L < self.minimum:
+            if n < L or L < self.minimum or len(tail) < L:
                 continue
-            pos = self.tables[li][fingerprint(text[n - L:]) % self.slots]
-            if pos == EMPTY or pos >= len(self.tokens) or pos < L:
+            suffix = tail[len(tail) - L:]
+            pos = self.tables[li][fingerprint(suffix) % self.slots]
+            if pos == EMPTY or pos >= nt or pos < L:
                 continue
-            if self.tokens[pos - L:pos] != text[n - L:]:
+            if self.tokens[pos - L:pos] != suffix:
                 continue                                       # collision or stale slot
             out = self.tokens[pos:pos + self.depth]
             if not out:
                 continue
             m = L                                              # extend the confirmed match backwards
-            while m < min(pos, n) and self.tokens[pos - m - 1] == text[n - m - 1]:
+            while m < min(pos, n, 4096) and self.tokens[pos - m - 1] == at(n - m - 1):
                 m += 1
             return Proposal(out, m, pos)
         return None

@@ -76,7 +76,7 @@ def block_verify(P: torch.Tensor, Q: Optional[torch.Tensor], proposals: Sequence
             h = R / den if den > 0 else 0.0
         else:
             h = w[g]
-        if u_accept[i - 1] <= h:
+        if u_accept[i - 1] < h:
             tau = i
     return tau, sample_from(residual(tau), u_final)
 
