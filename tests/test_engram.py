@@ -104,3 +104,41 @@ def test_engram_layer_in_the_oracle_model():
     # without the memory the model is a different function
     plain = oracle.OracleModel(tiny_config(), {k: v for k, v in W.items() if "engram" not in k})
     assert not torch.allclose(plain.forward(toks, plain.new_session(64)), whole, atol=1e-3)
+
+
+def test_row_store_on_disk_with_set_associative_host_cache(tmp_path):
+    """Rows come back exactly as written; repeated ids hit the host cache; a full set evicts its
+    least recently used way; ids outside the store's interval read as zero rows."""
+    import os
+
+    import numpy as np
+    import torch
+
+    from titanic_flash_41_b200.models import engram as EG
+    from titanic_flash_41_b200.utils import build
+    build.build(verbose=False)                         # the batched reader lives in the host runtime library
+    rows = 5000
+    packed = EG.pack_rows(torch.randn(rows, 256, generator=torch.Generator().manual_seed(3)))
+    path = os.path.join(str(tmp_path), "table.bin")
+    EG.write_table(path, packed, row_start=1000)
+    store = EG.EngramRowStore(path, cache_rows=64, ways=4, threads=4)
+    assert (store.row_start, store.row_end) == (1000, 6000) and store.sets == 16
+    ids = np.array([1000, 1005, 5999, 999, 6000, 1005, 2500], dtype=np.int64)
+    got = store.lookup(ids)
+    want = packed.numpy()
+    assert (got[0] == want[0]).all() and (got[1] == want[5]).all() and (got[2] == want[4999]).all()
+    assert (got[3] == 0).all() and (got[4] == 0).all() and (got[5] == want[5]).all() and (got[6] == want[1500]).all()
+    assert store.stats["reads"] == 4 and store.stats["foreign"] == 2       # the repeated id was read once
+    again = store.lookup(ids)
+    assert (again == got).all() and store.stats["reads"] == 4 and store.stats["hits"] >= 5
+    # five rows of one set in a 4-way cache: the oldest one is evicted and read again
+    same_set = np.array([1000 + 16 * k for k in range(5)], dtype=np.int64)
+    store.lookup(same_set[:4])
+    store.lookup(same_set[4:])
+    before = store.stats["reads"]
+    store.lookup(same_set[1:2])
+    assert store.stats["reads"] == before              # still cached
+    store.lookup(same_set[0:1])
+    assert store.stats["reads"] == before + 1          # was the least recently used way
+    big = np.random.default_rng(0).integers(1000, 6000, size=3000)
+    assert (store.lookup(big) == want[big - 1000]).all()

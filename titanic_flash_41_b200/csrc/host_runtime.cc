@@ -193,6 +193,53 @@ TF_API long tf_host_read_direct(const char* path, void* out, long n, long offset
   return err ? -err : done;
 }
 
+// Batched positional reads of fixed-size rows (the row store of the hashed n-gram memory lives on
+// NVMe; a lookup needs a few hundred scattered 264-byte rows).  A pool of threads issues one pread
+// per row into the caller's buffer, in id order within each thread's share; rows whose id is
+// negative or beyond `rows_in_file` are zero-filled.  Returns the number of rows read from the
+// file, or -errno (reference: the batched reader of src/engram_io.rs:209-329).
+TF_API long tf_host_read_rows(const char* path, long header_bytes, long row_bytes, long rows_in_file, const long* ids,
+                              long n, void* out, int threads) {
+  if (!path || !ids || !out || row_bytes <= 0 || n < 0) return -EINVAL;
+  const int fd = open(path, O_RDONLY);
+  if (fd < 0) return -errno;
+  if (threads < 1) threads = 1;
+  if (threads > 32) threads = 32;
+  if (n < 64) threads = 1;
+  std::vector<long> got((size_t)threads, 0);
+  std::vector<int> errs((size_t)threads, 0);
+  auto work = [&](int t) {
+    const long lo = n * t / threads, hi = n * (t + 1) / threads;
+    for (long i = lo; i < hi; ++i) {
+      uint8_t* dst = (uint8_t*)out + i * row_bytes;
+      const long id = ids[i];
+      if (id < 0 || id >= rows_in_file) {
+        memset(dst, 0, (size_t)row_bytes);
+        continue;
+      }
+      long done = 0;
+      while (done < row_bytes) {
+        const ssize_t r = pread(fd, dst + done, (size_t)(row_bytes - done), header_bytes + id * row_bytes + done);
+        if (r < 0) { if (errno == EINTR) continue; errs[(size_t)t] = errno; return; }
+        if (r == 0) { errs[(size_t)t] = EIO; return; }
+        done += (long)r;
+      }
+      got[(size_t)t] += 1;
+    }
+  };
+  std::vector<std::thread> pool;
+  for (int t = 1; t < threads; ++t) pool.emplace_back(work, t);
+  work(0);
+  for (auto& th : pool) th.join();
+  close(fd);
+  long total = 0;
+  for (int t = 0; t < threads; ++t) {
+    if (errs[(size_t)t]) return -errs[(size_t)t];
+    total += got[(size_t)t];
+  }
+  return total;
+}
+
 // frame = magic u32 | kind u32 | seq u64 | len u32 | payload | crc32 u32   (little endian)
 TF_API long tf_host_frame_bytes(long payload) { return 24 + payload; }
 TF_API long tf_host_frame_encode(int kind, long seq, const void* payload, long n, void* out) {

@@ -206,6 +206,110 @@ class EngramTable:
         return out
 
 
+class EngramRowStore:
+    """The packed row store of one Engram table on disk with a set-associative cache in host memory.
+
+    The full-size tables (hundreds of millions of 264-byte rows per layer) do not belong in HBM: the
+    file written by ``write_table`` stays on NVMe, a lookup reads the rows it misses with one batched
+    call into the host runtime (a pool of positional reads), and recently used rows stay in a
+    ``ways``-way set-associative cache of pinned host memory, replaced least-recently-used within a
+    set (reference: set-associative RAM cache + SSD reads, src/engram.rs, src/engram_io.rs:209-329).
+    Rows outside [row_start, row_end) -- other ranks' intervals -- come back as zeros."""
+
+    def __init__(self, path: str, cache_rows: int = 1 << 20, ways: int = 4, threads: int = 8):
+        with open(path, "rb") as f:
+            head = f.read(len(MAGIC) + 20)
+        if head[:len(MAGIC)] != MAGIC:
+            raise ValueError("not an Engram table file")
+        rows, row_start, rb = struct.unpack("<QQI", head[len(MAGIC):])
+        if rb != ROW_BYTES:
+            raise ValueError("unexpected Engram row size")
+        self.path, self.header = path, HEADER_BYTES
+        self.rows, self.row_start, self.row_end = int(rows), int(row_start), int(row_start + rows)
+        self.ways, self.threads = ways, threads
+        self.sets = max(1, cache_rows // ways)
+        self.tags = np.full((self.sets, ways), -1, dtype=np.int64)
+        self.stamp = np.zeros((self.sets, ways), dtype=np.int64)
+        self.data = np.zeros((self.sets, ways, ROW_BYTES), dtype=np.uint8)
+        self.clock = 0
+        self.stats = {"hits": 0, "misses": 0, "reads": 0, "foreign": 0}
+
+    def _read(self, ids: np.ndarray) -> np.ndarray:
+        """Rows ``ids`` (local row numbers) from the file."""
+        from ..ops import native
+        out = np.empty((len(ids), ROW_BYTES), dtype=np.uint8)
+        if len(ids) == 0:
+            return out
+        h = native.host_lib()
+        ids = np.ascontiguousarray(ids, dtype=np.int64)
+        if h is not None:
+            r = h.tf_host_read_rows(self.path.encode(), self.header, ROW_BYTES, self.rows, ids.ctypes.data, len(ids),
+                                    out.ctypes.data, self.threads)
+            if r < 0:
+                raise OSError(-r, "Engram row read failed", self.path)
+        else:
+            with open(self.path, "rb") as f:
+                for i, r in enumerate(ids):
+                    f.seek(self.header + int(r) * ROW_BYTES)
+                    out[i] = np.frombuffer(f.read(ROW_BYTES), dtype=np.uint8)
+        self.stats["reads"] += len(ids)
+        return out
+
+    def lookup(self, ids) -> np.ndarray:
+        """Global row ids [n] -> packed rows [n, 264] (zeros for rows this store does not own)."""
+        ids = np.asarray(ids, dtype=np.int64).reshape(-1)
+        out = np.zeros((len(ids), ROW_BYTES), dtype=np.uint8)
+        own = (ids >= self.row_start) & (ids < self.row_end)
+        self.stats["foreign"] += int((~own).sum())
+        loc = ids - self.row_start
+        sets = loc % self.sets
+        self.clock += 1
+        miss_pos = []
+        for i in np.flatnonzero(own):
+            st = int(sets[i])
+            w = np.flatnonzero(self.tags[st] == loc[i])
+            if w.size:
+                out[i] = self.data[st, w[0]]
+                self.stamp[st, w[0]] = self.clock
+                self.stats["hits"] += 1
+            else:
+                miss_pos.append(i)
+        if miss_pos:
+            mp = np.asarray(miss_pos)
+            uniq, inv = np.unique(loc[mp], return_inverse=True)
+            rows = self._read(uniq)
+            self.stats["misses"] += len(mp)
+            out[mp] = rows[inv]
+            for k, r in enumerate(uniq):                # insert: evict the least recently used way of the set
+                st = int(r % self.sets)
+                w = int(np.argmin(self.stamp[st])) if (self.tags[st] >= 0).all() else int(np.flatnonzero(self.tags[st] < 0)[0])
+                self.tags[st, w], self.stamp[st, w] = r, self.clock
+                self.data[st, w] = rows[k]
+        return out
+
+
+class EngramHostTable:
+    """An Engram table whose rows live in an ``EngramRowStore`` (disk + host cache): same ``lookup``
+    as ``EngramTable``.  The ids must come to the host, so a step that uses it runs eagerly (the
+    reference splits its graphs around these reads: engram_graphs, src/target.rs)."""
+
+    def __init__(self, store: EngramRowStore, device):
+        self.store, self.device = store, device
+        self.row_start, self.row_end = store.row_start, store.row_end
+
+    def lookup(self, ids: torch.Tensor) -> torch.Tensor:
+        from ..ops import native
+        host_ids = ids.detach().to("cpu", torch.int64).numpy()
+        packed = torch.from_numpy(self.store.lookup(host_ids)).to(self.device)
+        n = packed.shape[0]
+        out = torch.empty(n, 256, dtype=torch.bfloat16, device=self.device)
+        # rows this store does not own are already zero rows: a zero scale byte decodes them to ~0
+        own = torch.from_numpy(((host_ids >= self.row_start) & (host_ids < self.row_end))).to(self.device)
+        seq = torch.arange(n, dtype=torch.int64, device=self.device)
+        native.call("tf_engram_dequant", packed.contiguous(), torch.where(own, seq, torch.full_like(seq, -1)), out, n, 0, n)
+        return out
+
+
 def gate(x: torch.Tensor, kv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, eps: float) -> torch.Tensor:
     from ..ops import native
     r, m, d = x.shape
