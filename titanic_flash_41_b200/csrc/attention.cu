@@ -4,8 +4,11 @@
 //
 // Layout of the work: a CTA owns one query row and walks 64-key chunks of that row's key list
 // (split s takes chunks s, s+nsplit, ...).  Keys are dequantised once per chunk into shared
-// memory (row-major for QK^T and transposed for PV), each warp owns 16 heads and runs both
-// contractions on m16n8k16 tensor-core tiles with an online base-2 softmax.  Partials
+// memory, row-major; QK^T reads them as they lie and PV reads the same rows through
+// ldmatrix.trans (heads up to 128 wide), so no transposed copy is written.  FP4 entries, 94 % of
+// the keys of a long-context row, are unpacked eight at a time with the byte-permute form of
+// common.cuh.  Each warp owns 16 heads and runs both contractions on m16n8k16 tensor-core tiles
+// with an online base-2 softmax.  Partials
 // (normalised output + log2-sum-exp) are merged with the sink as an extra zero-valued logit,
 // then the inverse RoPE rotation is applied to the output tail (the value shares the key's
 // rotated latent; reference src/layer_attention.rs:1416-1423).  Partial/merge arithmetic follows
@@ -49,11 +52,9 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 template <int DH>
 __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
   tf_pdl_sync();
-  constexpr int KS = DH + 8;          // row stride of Ks (halfs)
-  constexpr int VS = kChunk + 8;      // row stride of Vt (halfs)
+  constexpr int KS = DH + 8;          // row stride of Ks (halfs): 16-byte rows shifted by one bank group per key
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half* Ks = reinterpret_cast<__half*>(smem_raw);          // [64][KS]
-  __half* Vt = Ks + kChunk * KS;                             // [DH][VS]
   __shared__ int key_src[kChunk];                            // >=0: window slot; <0: ~compressed id
 
   const int r = blockIdx.x, split = blockIdx.y;
@@ -131,10 +132,10 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
     for (int it = threadIdx.x; it < kChunk * (DH / 16); it += blockDim.x) {
       const int key = it % kChunk, seg = it / kChunk;
       const int src = key_src[key];
-      float v[16];
+      uint32_t hv[8];                  // sixteen f16 values of this key segment
       if (src == 0x7fffffff) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        for (int j = 0; j < 8; ++j) hv[j] = 0u;
       } else if (src >= 0) {
         const uint8_t* row = win + (long)src * wrow;
         uint4 raw = *reinterpret_cast<const uint4*>(row + seg * 16);
@@ -144,22 +145,27 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
         for (int j = 0; j < 8; ++j) {
           uint32_t h2 = e4m3x2_to_h2(h[j]);
           float2 f = __half22float2(*reinterpret_cast<__half2*>(&h2));
-          v[2 * j] = f.x * sc;
-          v[2 * j + 1] = f.y * sc;
+          hv[j] = pack_h2(f.x * sc, f.y * sc);
         }
       } else {
         const uint8_t* row = comp + (long)(~src) * crow;
-        uint2 raw = *reinterpret_cast<const uint2*>(row + seg * 8);
-        const float sc = e4m3_to_float(row[DH / 2 + seg]);
-        const uint32_t w[2] = {raw.x, raw.y};
+        const uint2 raw = *reinterpret_cast<const uint2*>(row + seg * 8);
+        // the unpacked halves hold value * 2^-14: fold 2^14 into the group's scale (fp32: no overflow)
+        const float sc = e4m3_to_float(row[DH / 2 + seg]) * 16384.f;
+        uint32_t lo4[4], hi4[4];
+        e2m1x8_to_h2x4_scaled(raw.x, lo4);
+        e2m1x8_to_h2x4_scaled(raw.y, hi4);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = e2m1_to_float((w[j >> 3] >> (4 * (j & 7))) & 0xfu) * sc;
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo4[j]));
+          const float2 c = __half22float2(*reinterpret_cast<__half2*>(&hi4[j]));
+          hv[j] = pack_h2(a.x * sc, a.y * sc);
+          hv[4 + j] = pack_h2(c.x * sc, c.y * sc);
+        }
       }
-      __half* kd = Ks + key * KS + seg * 16;
-#pragma unroll
-      for (int j = 0; j < 16; j += 2) *reinterpret_cast<__half2*>(kd + j) = __floats2half2_rn(v[j], v[j + 1]);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) Vt[(seg * 16 + j) * VS + key] = __float2half(v[j]);
+      uint4* kd = reinterpret_cast<uint4*>(Ks + key * KS + seg * 16);
+      kd[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+      kd[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
     }
     __syncthreads();
     if (!warp_active) continue;
@@ -223,16 +229,24 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
       pf[nt >> 1][(nt & 1) * 2 + 0] = pack_h2(p0, p1);
       pf[nt >> 1][(nt & 1) * 2 + 1] = pack_h2(p2, p3);
     }
-    // ---- O += P V
+    // ---- O += P V: the B fragments (keys along k, dims along n) come out of the row-major key
+    // tile through ldmatrix.trans, four 8x8 blocks (two k16 steps) per instruction
+    {
+      const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks);
+      const int lm = lane >> 3, lr = lane & 7;
 #pragma unroll
-    for (int dt = 0; dt < DH / 8; ++dt) {
-      const __half* vr = Vt + (dt * 8 + g) * VS + 2 * t;
+      for (int dt = 0; dt < DH / 8; ++dt) {
 #pragma unroll
-      for (int ks = 0; ks < kChunk / 16; ++ks) {
-        uint32_t b[2];
-        b[0] = *reinterpret_cast<const uint32_t*>(vr + ks * 16);
-        b[1] = *reinterpret_cast<const uint32_t*>(vr + ks * 16 + 8);
-        mma_f16_16816(o[dt], pf[ks], b);
+        for (int kp = 0; kp < kChunk / 32; ++kp) {
+          const int key = (2 * kp + (lm >> 1)) * 16 + (lm & 1) * 8 + lr;
+          const uint32_t addr = ks_base + (uint32_t)(key * KS + dt * 8) * 2u;
+          uint32_t b0[2], b1[2];
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b0[0]), "=r"(b0[1]), "=r"(b1[0]), "=r"(b1[1])
+                       : "r"(addr));
+          mma_f16_16816(o[dt], pf[2 * kp], b0);
+          mma_f16_16816(o[dt], pf[2 * kp + 1], b1);
+        }
       }
     }
   }
@@ -565,10 +579,10 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
     if (Dh == 512) tf_launch(sparse_attn_wide_kernel<512>, dim3(grid), dim3(warps * 32), smem, st, p);
     else tf_launch(sparse_attn_wide_kernel<256>, dim3(grid), dim3(warps * 32), smem, st, p);
   } else if (Dh == 128) {
-    const int smem = (kChunk * (128 + 8) + 128 * (kChunk + 8)) * 2;
+    const int smem = kChunk * (128 + 8) * 2;
     tf_launch(sparse_attn_kernel<128>, dim3(grid), dim3(warps * 32), smem, st, p);
   } else {
-    const int smem = (kChunk * (64 + 8) + 64 * (kChunk + 8)) * 2;
+    const int smem = kChunk * (64 + 8) * 2;
     tf_launch(sparse_attn_kernel<64>, dim3(grid), dim3(warps * 32), smem, st, p);
   }
   dim3 mg(T, Hl);
