@@ -36,8 +36,8 @@ def test_streamed_engine_equals_the_dequantising_loader(tmp_path):
             wa, wb = getattr(la, nm), getattr(lb, nm)
             da, db = E.dequant_fp8(wa), E.dequant_fp8(wb)
             assert da.shape == db.shape, nm
-            assert float((da == db).float().mean()) > 0.999, nm
-            assert float((da - db).abs().max()) <= 0.07 * float(db.abs().max()), nm
+            # (the re-derived block scale fl(fl(448 s) / 448) can sit one ulp from s)
+            assert torch.allclose(da, db, rtol=1e-6, atol=0), nm
         for nm in ("ew1", "ew3", "ew2", "es1", "es3", "es2", "gate", "attn_norm", "kv_norm"):
             ta, tb = getattr(la, nm), getattr(lb, nm)
             if nm.startswith("e"):
@@ -98,4 +98,4 @@ def test_ue8m0_32_dense_scales_are_reexpressed_on_the_device(tmp_path):
     la = a.forward(E.StepPlan.build([(0, 0, toks)]))
     lb = b.forward(E.StepPlan.build([(0, 0, toks)]))
     rel = (la - lb).abs().amax(-1) / la.abs().amax(-1)          # a near-tie in the router can flip an expert of a row
-    assert float(rel.median()) < 0.15, rel
+    assert float(rel.median()) < 0.3, rel
