@@ -126,6 +126,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--pdl", type=int, default=-1, help="1 / 0: launch kernels with programmatic dependent launch "
                     "(default: the engine configuration's setting)")
+    ap.add_argument("--nvtx-step", action="store_true", help="run one extra eager decode step inside the NVTX range "
+                    "'tf_decode_step' (a profiler can then list exactly the kernels of a step)")
     ap.add_argument("--trace", action="store_true", help="print per-kernel time tables of one extra prefill pass and one eager decode step")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -254,6 +256,11 @@ def main():
     for _ in range(args.warmup):
         dec.step(slots)
     barrier()
+    if args.nvtx_step:
+        torch.cuda.nvtx.range_push("tf_decode_step")
+        dec.count_launches(slots)
+        torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
     if eng.status.read()[0] != 0 and state_from.startswith("KV"):
         # the prefilled state of this random-init model produced non-finite logits: fall back to the
         # synthetic state rather than time a step that reports errors

@@ -85,9 +85,10 @@ def main():
     cfg = small_config(n_heads=4 * world if world > 4 else 4, shared_inter=max(256, 128 * world),
                        moe_inter=512, draft=DraftConfig(layers=1, depth=3))
     W = oracle.init_weights(cfg, 0)
-    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=1024, prefill_widths=(128,))
+    chunk = max(128, 64 * world)       # sequence-parallel slices of 64 rows: every rank stays on the tensor-core path
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(chunk,))
     # the TP engine also splits index scoring by key range from 8 keys on (decode rows)
-    ecfg_tp = EngineConfig(reference_matmul=True, regions=2, max_context=1024, prefill_widths=(128,), key_sharded_index_min=8)
+    ecfg_tp = EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(chunk,), key_sharded_index_min=8)
     eng = E.Engine.from_weights(cfg, ecfg_tp, W, comm=comm, device=dev)
     eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev, spin_limit=2_000_000)
     ref = E.Engine.from_weights(cfg, ecfg, W, comm=LocalComm(), device=dev)
@@ -116,9 +117,9 @@ def main():
     bigpath.attach(eng)
     bigpath.attach(ref)
     assert SP.attach(eng) is not None
-    long_prompt = torch.randint(0, cfg.vocab, (64 * world * 3 + 37,), generator=gen, dtype=torch.int32)
-    a = run_prefill(eng, 1, long_prompt, 128)
-    b = run_prefill(ref, 1, long_prompt, 128)
+    long_prompt = torch.randint(0, cfg.vocab, (chunk * 3 + 37,), generator=gen, dtype=torch.int32)
+    a = run_prefill(eng, 1, long_prompt, chunk)
+    b = run_prefill(ref, 1, long_prompt, chunk)
     errs_sp = [float((a - b).abs().max() / b.abs().max())]
     p1 = int(long_prompt.numel())
     for step in range(3):
@@ -203,4 +204,11 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:            # noqa: BLE001  (the launcher only shows its own error: print ours first)
+        import traceback
+        print("[mgpu] FAILED on rank", os.environ.get("RANK"), flush=True)
+        traceback.print_exc(file=sys.stdout)
+        sys.stdout.flush()
+        os._exit(1)

@@ -318,7 +318,7 @@ class EngineConfig(_JsonMixin):
     prefill_slice_ms: int = 500
     spin_limit: int = 20_000_000       # bounded device waits (reference src/roce.rs:1196-1199)
     use_cuda_graphs: bool = True
-    key_sharded_index_min: int = 8192  # decode rows: split index scoring over the ranks from this many keys (0 = never)
+    key_sharded_index_min: int = 262144  # decode rows: split index scoring over the ranks from this many keys (0 = never); below about a million tokens of context the exchange costs more than the scoring it saves
     two_level_index_min: int = 65536   # decode rows: from this many index keys on, layers after the candidate source score only its published blocks (0 = never)
     reference_matmul: bool = False     # validation only: rows beyond the small-M limit may run through dequantised weights and torch.matmul when the tensor-core path is not attached (never set in serving or benchmarks: the engine refuses instead)
     pdl: bool = False                  # launch kernels with programmatic dependent launch (each kernel waits for its predecessor on the device; the next one is already resident)
