@@ -447,6 +447,65 @@ def test_router_topk_group_equals_the_two_launches(M):
         assert torch.equal(a, b_) if isinstance(a, torch.Tensor) else a == b_
 
 
+@pytest.mark.parametrize("T,n_max", [(4, 32768), (16, 20000), (3, 65536)])
+def test_topk_select_of_few_long_rows_matches_a_stable_sort(T, n_max):
+    """A few long rows take the cluster-per-row kernel: same contract (exact, ties to the lower
+    position, ids ascending, -1 padding, optional scores) as the CTA-per-row kernel."""
+    torch.manual_seed(T)
+    k, lds = 2048, n_max
+    scores = (torch.randn(T, lds, device=DEV) * 0.3 + 5).relu()        # crowded exponents, like index scores
+    scores[:, ::7] = scores[:, :1]                                      # many exact ties, some at the cut
+    scores[0, :] = 1.25                                                 # a row of one value
+    nvalid = torch.tensor([n_max, n_max - 13, 5000, 100][:T] + [n_max // 2 + i for i in range(max(0, T - 4))],
+                          dtype=torch.int32, device=DEV)[:T]
+    sel = torch.zeros(T, k, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(T, dtype=torch.int32, device=DEV)
+    osc = torch.zeros(T, k, device=DEV)
+    native.call("tf_topk_select", scores, lds, nvalid, k, sel, cnt, osc, 100, T)
+    torch.cuda.synchronize()
+    for r in range(T):
+        n = int(nvalid[r])
+        s = scores[r, :n].cpu()
+        got = sel[r].cpu().tolist()
+        if n <= k:
+            assert got == [100 + i for i in range(n)] + [-1] * (k - n) and int(cnt[r]) == n
+            continue
+        order = sorted(torch.sort(s, descending=True, stable=True).indices[:k].tolist())
+        assert got == [100 + i for i in order] and int(cnt[r]) == k
+        assert torch.equal(osc[r].cpu(), s[order])
+
+
+@pytest.mark.parametrize("T", [1, 4, 16, 27])
+def test_router_single_launch_equals_logits_then_topk_group(T):
+    torch.manual_seed(40 + T)
+    E_, d, k, e_lo, El = 256, 1024, 6, 64, 64
+    x = torch.randn(T, d, device=DEV).bfloat16()
+    gate = (torch.randn(E_, d, device=DEV) * 0.05).bfloat16()
+    bias, bias_vl = torch.randn(E_, device=DEV) * 0.1, torch.randn(E_, device=DEV) * 0.1
+    tokens = torch.randint(0, 3, (T,), dtype=torch.int32, device=DEV)
+    i32 = lambda *s_: torch.zeros(*s_, dtype=torch.int32, device=DEV)
+    ticket = i32(1)
+    out = []
+    for fused in (False, True, True):                                   # twice: the ticket must come back to zero
+        logits = torch.zeros(T, E_, device=DEV)
+        ids, wts = i32(T, k), torch.zeros(T, k, device=DEV)
+        ge, gs, gc, ng, sp, nl = i32(El), i32(El), i32(El), i32(1), i32(T * k), i32(1)
+        if fused:
+            native.call("tf_router_small_fused", x, d, gate, logits, T, E_, d, bias, bias_vl, tokens, 1, ids, wts, k, 1, 1,
+                        1.5, e_lo, e_lo + El, ge, gs, gc, ng, sp, nl, ticket)
+        else:
+            native.call("tf_router_logits_small", x, d, gate, logits, E_, T, E_, d)
+            native.call("tf_router_topk", logits, bias, bias_vl, tokens, 1, ids, wts, T, E_, k, 1, 1, 1.5)
+            native.call("tf_route_group", ids, T * k, e_lo, e_lo + El, ge, gs, gc, ng, sp, nl)
+        torch.cuda.synchronize()
+        assert int(ticket) == 0
+        n, g = int(nl), int(ng)
+        out.append((logits, ids, wts, ge[:g].clone(), gs[:g].clone(), gc[:g].clone(), sp[:n].clone(), n, g))
+    for other in out[1:]:
+        for a, b_ in zip(out[0], other):
+            assert torch.equal(a, b_) if isinstance(a, torch.Tensor) else a == b_
+
+
 def test_mxfp4_to_fp8_block_conversion_is_exact_where_representable():
     """e2m1 x 2^e re-expressed as e4m3 with one power-of-two scale per 128 x 128 block: exact while a
     group's scale is within 2^-6 of the block's largest (e4m3 holds the shifted magnitudes), rounded

@@ -8,6 +8,7 @@
 // kernels/core.cu:944-950 generalised from pairs to groups of `ratio`; router
 // kernels/moe_frontend.cuh:27-130; ordered route sum kernels/ffn_sum_shared.cuh:7-33.
 #include "common.cuh"
+#include "router.cuh"
 
 namespace {
 
@@ -371,151 +372,12 @@ __global__ void router_logits_kernel(const __half* __restrict__ h, const __nv_bf
   }
 }
 
-// top-k per row (one warp per row) + weights.  scoring 0 = softmax, 1 = sqrtsoftplus.
-// Ties go to the lowest expert id; NaN keys count as +inf.
-// The selection bias is chosen per row: rows whose token is `image_token` use bias_vl (when given).
-struct RouterBias {
-  const float* bias;
-  const float* bias_vl;
-  const int* tokens;
-  int image_token;
-};
-__device__ __forceinline__ void router_topk_rows(const float* __restrict__ logits, const RouterBias rb,
-                                                 int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
-                                                 int scoring, int renorm, float scale, float* sc, int row0) {
-  // sc: [warps][2][E] floats of shared memory; warp w serves row row0 + w
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = row0 + warp;
-  if (r >= M) return;
-  float* score = sc + (long)warp * 2 * E;
-  float* key = score + E;
-  const float* lg = logits + (long)r * E;
-  const float* bias = (rb.bias_vl && rb.tokens && rb.tokens[r] == rb.image_token) ? rb.bias_vl : rb.bias;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
-  mx = warp_max(mx);
-  float den = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    float x = lg[e], s;
-    if (scoring == 1) {
-      float sp = x > 20.f ? x : log1pf(expf(x));
-      s = sqrtf(sp);
-    } else {
-      s = expf(x - mx);
-      den += s;
-    }
-    score[e] = s;
-  }
-  den = warp_sum(den);
-  for (int e = lane; e < E; e += 32) {
-    if (scoring == 0) score[e] /= den;
-    float k = score[e] + (bias ? bias[e] : 0.f);
-    key[e] = isnan(k) ? INFINITY : k;
-  }
-  __syncwarp();
-  float wsum = 0.f;
-  for (int j = 0; j < topk; ++j) {
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      float k = key[e];
-      if (k > best || (k == best && e < bi)) {
-        best = k;
-        bi = e;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ob > best || (ob == best && oi < bi)) {
-        best = ob;
-        bi = oi;
-      }
-    }
-    if (bi == 0x7fffffff) bi = 0;
-    if (lane == 0) {
-      ids[(long)r * topk + j] = bi;
-      wts[(long)r * topk + j] = score[bi];
-      key[bi] = -INFINITY;
-    }
-    wsum += score[bi];
-    __syncwarp();
-  }
-  if (lane == 0) {
-    for (int j = 0; j < topk; ++j) {
-      float w = wts[(long)r * topk + j];
-      if (renorm) w = w / (wsum + 1e-20f);
-      wts[(long)r * topk + j] = w * scale;
-    }
-  }
-}
-
 __global__ void router_topk_kernel(const float* __restrict__ logits, const RouterBias bias,
                                    int* __restrict__ ids, float* __restrict__ wts, int M, int E, int topk,
                                    int scoring, int renorm, float scale) {
   tf_pdl_sync();
   extern __shared__ float sc[];                       // [warps][2][E]
   router_topk_rows(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, sc, blockIdx.x * (blockDim.x >> 5));
-}
-
-// Group (token, slot) pairs by expert for the experts this rank owns: counting sort in one CTA.
-// Outputs: group_expert/start/count for the compacted active experts, n_groups, sorted_pairs.
-__device__ __forceinline__ void route_group_body(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
-                                                 int* group_expert, int* group_start, int* group_count,
-                                                 int* n_groups, int* sorted_pairs, int* n_local_pairs, int* cnt) {
-  // cnt: [E_local] counts, then offsets; then the local expert of every pair (shared memory)
-  const int El = e_hi - e_lo;
-  int* loc = cnt + El;
-  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int e = ids[i] - e_lo;
-    loc[i] = (e >= 0 && e < El) ? e : -1;
-  }
-  __syncthreads();
-  // one thread per expert counts its pairs out of shared memory (no atomics: fixed order)
-  for (int e = threadIdx.x; e < El; e += blockDim.x) {
-    int c = 0;
-    for (int i = 0; i < n_pairs; ++i) c += (loc[i] == e);
-    cnt[e] = c;
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    // warp 0: exclusive scan of the counts and compaction of the active experts, 32 at a time
-    const int lane = threadIdx.x;
-    int off = 0, ng = 0;
-    for (int base = 0; base < El; base += 32) {
-      const int e = base + lane;
-      const int c = e < El ? cnt[e] : 0;
-      int inc = c;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += v;
-      }
-      const unsigned act = __ballot_sync(0xffffffffu, c > 0);
-      const int start = off + inc - c;
-      if (c > 0) {
-        const int gi = ng + __popc(act & ((1u << lane) - 1u));
-        group_expert[gi] = e;
-        group_start[gi] = start;
-        group_count[gi] = c;
-      }
-      if (e < El) cnt[e] = start;
-      off += __shfl_sync(0xffffffffu, inc, 31);
-      ng += __popc(act);
-    }
-    if (lane == 0) {
-      *n_groups = ng;
-      *n_local_pairs = off;
-    }
-  }
-  __syncthreads();
-  // stable placement in pair order (single thread per expert keeps the order deterministic)
-  for (int e = threadIdx.x; e < El; e += blockDim.x) {
-    int off = cnt[e];
-    for (int i = 0; i < n_pairs; ++i)
-      if (loc[i] == e) sorted_pairs[off++] = i;
-  }
 }
 
 __global__ void route_group_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int e_hi,
@@ -535,6 +397,17 @@ __global__ void __launch_bounds__(512) router_topk_group_kernel(
     int* group_start, int* group_count, int* n_groups, int* sorted_pairs, int* n_local_pairs) {
   tf_pdl_sync();
   extern __shared__ float fsm[];                       // [16][2][E] floats, reused as ints by the grouping
+  if (E <= 256 && topk <= 32) {
+    // rows in registers; the local expert of every pair goes straight to the grouping's table
+    int* cnt = reinterpret_cast<int*>(fsm);
+    for (int r = threadIdx.x >> 5; r < M; r += blockDim.x >> 5)
+      router_topk_rows_reg<8, 1>(logits, E, bias, r, M, ids, wts, E, topk, scoring, renorm, scale,
+                                 cnt + (e_hi - e_lo), e_lo, e_hi);
+    __syncthreads();
+    route_group_body(nullptr, M * topk, e_lo, e_hi, group_expert, group_start, group_count, n_groups, sorted_pairs,
+                     n_local_pairs, cnt);
+    return;
+  }
   for (int row0 = 0; row0 < M; row0 += 16)
     router_topk_rows(logits, bias, ids, wts, M, E, topk, scoring, renorm, scale, fsm, row0);
   __syncthreads();                                     // ids of every row are written (same CTA)

@@ -8,6 +8,8 @@
 // (padded) heads of one row as the MMA's M.  Row `r` scores keys [0, nvalid[r]); the rest of its
 // score row is -inf.  Selection is exact: ties at the cut go to the lower position and the
 // output ids are ascending (reference contract: kernels/index_bf16.cu:1-21, src/topk.rs).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace {
@@ -57,14 +59,20 @@ __global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
     if (key0 + key < maxvalid) {
       const uint8_t* row = kb + (long)(key0 + key) * p.key_row;
       const float sc = ue8m0_to_float(row[DI / 2 + blk]);
-      const uint32_t* wv = reinterpret_cast<const uint32_t*>(row + blk * 16);
+      // unpacked halves hold value * 2^-14: the block scale takes the 2^14 (in fp32: no overflow)
+      const uint32_t* wv = reinterpret_cast<const uint32_t*>(row + blk * 16);   // key rows are 4-byte aligned
+      const float s14 = sc * 16384.f;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint32_t w = wv[q];
+        uint32_t h4[4], o[4];
+        e2m1x8_to_h2x4_scaled(wv[q], h4);
 #pragma unroll
-        for (int j = 0; j < 8; j += 2)
-          *reinterpret_cast<__half2*>(dst + q * 8 + j) = __floats2half2_rn(
-              e2m1_to_float((w >> (4 * j)) & 0xfu) * sc, e2m1_to_float((w >> (4 * j + 4)) & 0xfu) * sc);
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h4[j]));
+          const __half2 h = __floats2half2_rn(f.x * s14, f.y * s14);
+          o[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     } else {
 #pragma unroll
@@ -287,6 +295,147 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
   if (tid == 0 && count) count[r] = k;
 }
 
+// The same selection for a few rows (decode): one CLUSTER of 8 CTAs per row.  Every thread keeps its
+// run of consecutive keys in registers, the byte histograms are built with warp-aggregated shared
+// atomics (scores crowd into a few exponent bytes, which serialises plain atomics) and read by all
+// eight CTAs over distributed shared memory; the compaction needs only the totals of the CTAs
+// before this one.  Output identical to topk_select_kernel.
+constexpr int kSelCluster = 8, kSelThreads = 512, kSelKeysPerThread = 16;
+
+__global__ void __cluster_dims__(kSelCluster, 1, 1) __launch_bounds__(kSelThreads)
+topk_select_cluster_kernel(const float* __restrict__ scores, int lds, const int* __restrict__ nvalid, int k,
+                           int* __restrict__ out, int* __restrict__ count, float* __restrict__ out_scores,
+                           int base) {
+  tf_pdl_sync();
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ int hist[4][256];                      // one histogram per radix pass: no reuse, no second barrier
+  __shared__ int wsum[kSelThreads / 32][2];
+  __shared__ int cta_tot[2];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  const int r = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = (int)cluster.block_rank();
+  const int n = min(nvalid[r], lds);
+  const float* s = scores + (long)r * lds;
+  int* o = out + (long)r * k;
+  if (n <= k) {                                     // uniform over the cluster: nobody waits for anybody
+    if (c == 0) {
+      for (int i = tid; i < k; i += kSelThreads) {
+        o[i] = i < n ? base + i : -1;
+        if (out_scores) out_scores[(long)r * k + i] = i < n ? s[i] : -INFINITY;
+      }
+      if (tid == 0 && count) count[r] = n;
+    }
+    return;
+  }
+  const int chunk = (n + kSelCluster - 1) / kSelCluster;
+  const int per = (chunk + kSelThreads - 1) / kSelThreads;       // <= kSelKeysPerThread (host check)
+  const int lo = min(n, c * chunk), hi = min(n, lo + chunk);
+  const int i0 = lo + tid * per;
+  uint32_t key[kSelKeysPerThread];
+#pragma unroll
+  for (int j = 0; j < kSelKeysPerThread; ++j) key[j] = (j < per && i0 + j < hi) ? float_key(s[i0 + j]) : 0u;
+  for (int i = tid; i < 4 * 256; i += kSelThreads) (&hist[0][0])[i] = 0;
+  __syncthreads();
+  uint32_t prefix = 0, mask = 0;
+  int need = k;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+#pragma unroll
+    for (int j = 0; j < kSelKeysPerThread; ++j) {
+      if (j < per) {                                 // uniform over the warp
+        const bool in = i0 + j < hi && (key[j] & mask) == prefix;
+        const int bin = in ? (int)((key[j] >> shift) & 0xffu) : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[pass][bin], __popc(peers));
+      }
+    }
+    cluster.sync();
+    // thread t < 256 owns bin 255 - t: an inclusive scan over t is the count of keys in bins >= its own
+    int h = 0;
+    if (tid < 256) {
+#pragma unroll
+      for (int q = 0; q < kSelCluster; ++q) h += cluster.map_shared_rank(&hist[pass][0], q)[255 - tid];
+    }
+    int inc = h;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += v;
+    }
+    if (lane == 31) wsum[warp][0] = inc;
+    __syncthreads();
+    if (tid < 256) {
+      for (int w2 = 0; w2 < warp; ++w2) inc += wsum[w2][0];
+      if (inc >= need && inc - h < need) {           // exactly one bin holds the k-th largest
+        s_prefix = prefix | ((uint32_t)(255 - tid) << shift);
+        s_need = need - (inc - h);
+      }
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    need = s_need;
+    mask |= 0xffu << shift;
+  }
+  const uint32_t thr = prefix;                       // key of the k-th largest
+  const int need_ties = need;                        // keys equal to it that are kept (lowest positions first)
+  int cgt = 0, ceq = 0;
+#pragma unroll
+  for (int j = 0; j < kSelKeysPerThread; ++j) {
+    if (j < per && i0 + j < hi) {
+      cgt += key[j] > thr;
+      ceq += key[j] == thr;
+    }
+  }
+  int sg = cgt, se = ceq;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, sg, d), b = __shfl_up_sync(0xffffffffu, se, d);
+    if (lane >= d) {
+      sg += a;
+      se += b;
+    }
+  }
+  if (lane == 31) {
+    wsum[warp][0] = sg;
+    wsum[warp][1] = se;
+  }
+  __syncthreads();
+  int og = sg - cgt, oe = se - ceq;                  // keys before this thread's run, inside the CTA
+  for (int w2 = 0; w2 < warp; ++w2) {
+    og += wsum[w2][0];
+    oe += wsum[w2][1];
+  }
+  if (tid == kSelThreads - 1) {
+    cta_tot[0] = og + cgt;
+    cta_tot[1] = oe + ceq;
+  }
+  cluster.sync();
+  for (int q = 0; q < c; ++q) {                      // ... and in the CTAs before this one
+    const int* t = cluster.map_shared_rank(&cta_tot[0], q);
+    og += t[0];
+    oe += t[1];
+  }
+#pragma unroll
+  for (int j = 0; j < kSelKeysPerThread; ++j) {
+    if (j < per && i0 + j < hi) {
+      const bool gt = key[j] > thr, eq = key[j] == thr;
+      if (gt || (eq && oe < need_ties)) {
+        const int dst = og + min(oe, need_ties);
+        if (dst < k) {
+          o[dst] = base + i0 + j;
+          if (out_scores) out_scores[(long)r * k + dst] = s[i0 + j];
+        }
+      }
+      og += gt;
+      oe += eq;
+    }
+  }
+  if (c == 0 && tid == 0 && count) count[r] = k;
+  cluster.sync();                                    // nobody leaves while its totals may still be read
+}
+
 // Merge per-rank candidate lists (key-sharded scoring): cand_scores/cand_ids [T, ranks*k] -> top-k
 // ids ascending.  Reuses the selection kernel on the gathered scores, then maps positions to ids.
 __global__ void map_ids_kernel(const int* __restrict__ picked, const int* __restrict__ cand_ids, int ldc,
@@ -385,7 +534,12 @@ TF_API int tf_index_scores(const void* q, const float* w, const int* region, con
 
 TF_API int tf_topk_select(const float* scores, int lds, const int* nvalid, int k, int* out, int* count,
                           float* out_scores, int base, int T, cudaStream_t st) {
-  tf_launch(topk_select_kernel, dim3(T), dim3(1024), 0, st, scores, lds, nvalid, k, out, count, out_scores, base);
+  // a few long rows (decode): one cluster of CTAs per row; many rows: one CTA per row fills the GPU
+  if (T <= 32 && lds > 4096 && lds <= kSelCluster * kSelThreads * kSelKeysPerThread)
+    tf_launch(topk_select_cluster_kernel, dim3(kSelCluster, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
+              count, out_scores, base);
+  else
+    tf_launch(topk_select_kernel, dim3(T), dim3(1024), 0, st, scores, lds, nvalid, k, out, count, out_scores, base);
   return (int)cudaGetLastError();
 }
 
