@@ -19,6 +19,8 @@
 // one runs, and start the moment it ends.  Without the attribute both instructions are no-ops.
 // (Reference: launch_pdl, src/cuda.rs:2209.)
 // ---------------------------------------------------------------------------------------
+// A kernel whose first loads are of data no kernel writes (weights) may issue those loads before
+// tf_pdl_sync(): they then overlap the tail of the kernel before it.
 __device__ __forceinline__ void tf_pdl_sync() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -93,7 +93,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__ CUtensorMap mapW3,
               const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapS1,
               const __grid_constant__ CUtensorMap mapS3, const __grid_constant__ CUtensorMap mapSX, const MxParams p) {
-  tf_pdl_sync();
   constexpr int kMats = DUAL ? 2 : 1;
   constexpr int kStages = DUAL ? 6 : 11;
   // scale bytes of one 512-input block: [128 rows][16] per matrix, then [16 rows][16] of the activations
@@ -119,7 +118,6 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = p.N / kTile;
-  const int items = *p.n_groups * tiles_n;
   const int kchunks = p.K / kBK, nsuper = p.K / kSuper;
 
   if (threadIdx.x == 0) {
@@ -145,6 +143,10 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers and tensor memory are set up; only now wait for the kernel before this one (its
+  // outputs, the group list first of all, are read from here on)
+  tf_pdl_sync();
+  const int items = *p.n_groups * tiles_n;
   // columns: accumulators [0,64) = buf*32 + mat*16; A scales [64,192) = 64 + slot*32 + mat*16;
   // B scales [192,256) = 192 + slot*16
   if (warp == 0) {

@@ -87,13 +87,23 @@ __device__ __forceinline__ uint4 ld_stream(const uint8_t* p) {
 template <int KIND, int MT, bool DUAL>
 __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* Wg, const uint8_t* W3g,
                                          const void* Sg, const void* S3g, int rows, const int* pairs,
-                                         int row_base, float (*red)[32][4], float* tile_out) {
+                                         int row_base, float (*red)[32][4], float* tile_out, bool& need_wait) {
+  // need_wait: the kernel has not yet waited for its predecessor in the stream.  The dense forms
+  // request their first weight block (immutable data) before they wait, so that the weight stream
+  // starts while the kernel before this one is still finishing; activations are read after.
+  auto wait_once = [&]() {
+    if (need_wait) {
+      tf_pdl_sync();
+      need_wait = false;
+    }
+  };
   constexpr int NM = DUAL ? 2 : 1;
   constexpr int NT = 2 * NM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * kTileN;
   const int k0 = warp * p.k_per_warp, k1 = min(p.K, k0 + p.k_per_warp);
 
+  if (pairs) wait_once();                  // (grouped forms have waited already: their lists are kernel outputs)
   const __half* xrow[MT];
 #pragma unroll
   for (int m = 0; m < MT; ++m) {
@@ -135,14 +145,19 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
         }
     };
     if (kPrefetch && k0 < k1) load_block(k0, w0, w8);
+    if (kPrefetch) wait_once();
     for (int kb = k0; kb < k1; kb += 128) {
       float blk[NT][MT][4];
 #pragma unroll
       for (int ti = 0; ti < NT; ++ti)
 #pragma unroll
         for (int m = 0; m < MT; ++m) blk[ti][m][0] = blk[ti][m][1] = blk[ti][m][2] = blk[ti][m][3] = 0.f;
-      if (!kPrefetch) load_block(kb, w0, w8);
-      else if (kb + 128 < k1) load_block(kb + 128, w0n, w8n);
+      if (!kPrefetch) {
+        load_block(kb, w0, w8);
+        wait_once();
+      } else if (kb + 128 < k1) {
+        load_block(kb + 128, w0n, w8n);
+      }
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         const int k = kb + s * 64 + t * 16;
@@ -202,6 +217,7 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
           w0[ti][s] = ld_stream(wrow0[ti] + 2 * (kb + s * 32 + t * 8));
           w8[ti][s] = ld_stream(wrow8[ti] + 2 * (kb + s * 32 + t * 8));
         }
+      wait_once();
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         uint4 xv[MT];
@@ -288,6 +304,7 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 
   // ---- fixed-order reduction over the K-splitting warps, then the epilogue
   // red is [kWarps * NT * MT][32][4]
+  wait_once();                             // (a warp whose K range is empty has not waited yet)
   __syncthreads();
 #pragma unroll
   for (int ti = 0; ti < NT; ++ti)
@@ -333,7 +350,9 @@ __device__ __forceinline__ void run_rows(const SmallMParams& p, const uint8_t* W
 template <int KIND, bool DUAL>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 smallm_gemm_kernel(SmallMParams p) {
-  tf_pdl_sync();
+  // grouped forms read kernel outputs (the group lists) first; dense forms wait inside run_rows
+  bool need_wait = p.group_expert == nullptr;
+  if (!need_wait) tf_pdl_sync();
   __shared__ float red[kMaxWarps * (DUAL ? 4 : 2) * 2][32][4];
   __shared__ __align__(16) float ctile[(KIND == 0 && !DUAL) ? 32 * 32 : 4];
   float* tile_out = (KIND == 0 && !DUAL && p.use_comm) ? ctile : nullptr;
@@ -361,13 +380,14 @@ smallm_gemm_kernel(SmallMParams p) {
   int row_base = 0;
   while (row_base < rows) {
     if (rows - row_base <= 8) {
-      run_rows<KIND, 1, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red, tile_out);
+      run_rows<KIND, 1, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red, tile_out, need_wait);
       row_base += 8;
     } else {
-      run_rows<KIND, 2, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red, tile_out);
+      run_rows<KIND, 2, DUAL>(p, Wg, W3g, Sg, S3g, rows, pairs, row_base, red, tile_out, need_wait);
       row_base += 16;
     }
   }
+  if (need_wait) tf_pdl_sync();            // (no rows: nothing has waited)
   if (KIND == 0 && !DUAL) {
     if (p.use_comm) {
       extern __shared__ float rowbuf[];      // N floats, comm form only

@@ -478,7 +478,6 @@ class Engine:
         native.lib()
         native.set_pdl(bool(getattr(ecfg, "pdl", False)))
         self.status = native.StatusWord(self.dev)
-        self.route_ticket = torch.zeros(1, dtype=torch.int32, device=self.dev)   # last-CTA counter of the fused router
         r = cfg.rope
         self.freqs = oracle.rope_frequencies(r.dim, r.theta, r.factor, r.beta_fast, r.beta_slow,
                                              r.original_max_position).to(self.dev)
@@ -1010,19 +1009,12 @@ class Engine:
         elif T <= self.SMALL_M and cfg.n_experts % 32 == 0:
             # one warp per expert row over the bf16 gate matrix, then top-k
             e0 = self.rank * self.El
-            if cfg.n_experts <= 256 and cfg.topk <= 32:
-                # logits, top-k and grouping in one launch (the last CTA to finish selects and groups)
-                native.call("tf_router_small_fused", b["hb"], d, L.gate, b["logits_r"], T, cfg.n_experts, d,
-                            L.gate_bias, L.gate_bias_vl, b["meta"][0], cfg.image_token, b["ids"], b["wts"], cfg.topk,
-                            scoring, 1 if cfg.renorm else 0, cfg.route_scale, e0, e0 + self.El, b["g_expert"],
-                            b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"], self.route_ticket)
-            else:
-                native.call("tf_router_logits_small", b["hb"], d, L.gate, b["logits_r"], cfg.n_experts, T,
-                            cfg.n_experts, d)
-                native.call("tf_router_topk_group", b["logits_r"], L.gate_bias, L.gate_bias_vl, b["meta"][0],
-                            cfg.image_token, b["ids"], b["wts"], T, cfg.n_experts,
-                            cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale, e0, e0 + self.El,
-                            b["g_expert"], b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
+            native.call("tf_router_logits_small", b["hb"], d, L.gate, b["logits_r"], cfg.n_experts, T,
+                        cfg.n_experts, d)
+            native.call("tf_router_topk_group", b["logits_r"], L.gate_bias, L.gate_bias_vl, b["meta"][0],
+                        cfg.image_token, b["ids"], b["wts"], T, cfg.n_experts,
+                        cfg.topk, scoring, 1 if cfg.renorm else 0, cfg.route_scale, e0, e0 + self.El,
+                        b["g_expert"], b["g_start"], b["g_count"], b["n_groups"], b["sorted_pairs"], b["n_local"])
             grouped = True
         else:
             native.call("tf_router", b["h16"], L.gate, L.gate_bias, L.gate_bias_vl, b["meta"][0], cfg.image_token,

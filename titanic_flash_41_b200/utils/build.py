@@ -25,7 +25,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
 # exact transcendental and division semantics are wanted in the sampling / norm kernels
-NO_FAST_MATH = {"sampling.cu", "sample_chunks.cu", "elementwise.cu", "indexer.cu", "fused_norm.cu", "router_small.cu"}
+NO_FAST_MATH = {"sampling.cu", "sample_chunks.cu", "elementwise.cu", "indexer.cu", "fused_norm.cu"}
 
 
 def _nvcc() -> str:
