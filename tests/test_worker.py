@@ -303,3 +303,46 @@ def test_copy_proposals_from_history_lookup_are_verified_exactly():
     plain, _ = run(False)
     with_lookup, _ = run(True)
     assert with_lookup == plain
+
+
+def test_interrupted_prefill_is_resumed_from_its_last_whole_chunk():
+    """A request cancelled during its prefill leaves a checkpoint of the chunks it finished; the same
+    prompt sent again starts there and generates what an uninterrupted request generates."""
+    cfg = tiny_config()
+    W = oracle.init_weights(cfg, 0)
+    sched = Scheduler(1, 4, 1)
+    b = OracleBackend(cfg, W, regions=1, max_context=512, chunk=32)
+    w = Worker(b, sched, SessionCache(slots=8, budget_bytes=1 << 30), eos_id=1, checkpoint_min=64, checkpoint_align=512)
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(3, cfg.vocab, (200,), generator=g).tolist()
+    ev = []
+    j = _job("x", prompt, 4, ev, temperature=0.0)
+    looks = {"n": 0}
+    decide = w._chunk_directive
+
+    def directive(job, last_slice):            # the client goes away while the fourth chunk runs
+        looks["n"] += 1
+        if looks["n"] == 4:
+            j.cancelled.set()
+        return decide(job, last_slice)
+    w._chunk_directive = directive
+    sched.submit(j)
+    _drain(w)
+    assert any(k == "error" and p["code"] == "cancelled" for _, k, p in ev)
+    saved = [e for e in w.log.snapshot(4096)["events"] if e.get("kind") == "prefill_interrupted"]
+    assert saved and saved[0]["saved"] >= 64 and saved[0]["saved"] % 32 == 0 and saved[0]["saved"] < 200
+    w._chunk_directive = decide
+    ev2 = []
+    sched.submit(_job("y", prompt, 4, ev2, temperature=0.0))
+    _drain(w)
+    ready = [p for _, k, p in ev2 if k == "ready"][0]
+    assert ready["cache_n"] == saved[0]["saved"] and ready["prompt_n"] == 200 - saved[0]["saved"]
+    # the resumed request generates what a fresh worker generates for the same prompt
+    sched3 = Scheduler(1, 4, 1)
+    w3 = Worker(OracleBackend(cfg, W, regions=1, max_context=512, chunk=32), sched3,
+                SessionCache(slots=8, budget_bytes=1 << 30), eos_id=1, checkpoint_min=64, checkpoint_align=512)
+    ev3 = []
+    sched3.submit(_job("z", prompt, 4, ev3, temperature=0.0))
+    _drain(w3)
+    toks = lambda e: [t for _, k, p in e if k == "tokens" for t in p]
+    assert toks(ev2) == toks(ev3) and len(toks(ev2)) == 4

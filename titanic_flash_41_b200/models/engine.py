@@ -40,11 +40,14 @@ def _pad128(n: int) -> int:
 # ---------------------------------------------------------------------------------------------
 @dataclass
 class Fp8Weight:
-    """[N, K] e4m3 + fp32 scale per 128x128 block; N padded to 128."""
+    """[N, K] e4m3 + fp32 scale per 128x128 block; N padded to 128.  The scales are powers of two
+    (what a UE8M0 checkpoint gives), so the same values also serve the block-scaled tensor-core GEMM:
+    ``sfu`` caches their UE8M0 form in that kernel's layout (False: not expressible)."""
     q: torch.Tensor
     s: torch.Tensor
     n: int
     k: int
+    sfu: object = None
 
 
 @dataclass
@@ -93,6 +96,7 @@ def quant_fp8_device(w: torch.Tensor) -> Fp8Weight:
     wf[:n] = w.float()
     t = wf.view(npad // 128, 128, k // 128, 128)
     s = t.abs().amax(dim=(1, 3)).clamp_min(1e-12) / codecs.E4M3_MAX
+    s = torch.exp2(torch.ceil(torch.log2(s)).clamp(-126, 126))     # UE8M0: the checkpoint's scale format
     q = (t / s[:, None, :, None]).clamp(-448, 448).to(F8).view(npad, k)
     return Fp8Weight(q.contiguous(), s.contiguous(), n, k)
 

@@ -1,7 +1,15 @@
 """Large-row-count (prefill) execution of the linear layers and routed experts on the tcgen05
-GEMM: activations are quantised to FP8 with one scale per (row, 128), dense weights are
-block-128 FP8, and MXFP4 expert weights are re-expressed per chunk as block-scaled FP8 so that
-one grouped launch covers every active expert of the rank.
+GEMMs.
+
+Block-scaled form (``EngineConfig.prefill_mx``, the default): activations are quantised to MXFP8
+(one UE8M0 scale per row and 32 inputs), dense FP8 weights keep their values with their
+power-of-two block scales re-expressed per 32 inputs, and MXFP4 expert weights are read as stored;
+the tensor core applies both scale vectors (``csrc/gemm_mx.cu``).
+
+fp32-scaled form (weights whose scales are not powers of two, or ``prefill_mx`` off): activations
+get one fp32 scale per (row, 128), dense weights are block-128 FP8, MXFP4 expert weights are
+re-expressed per chunk as block-scaled FP8, and partial sums are promoted per 128 inputs in software
+(``csrc/gemm_tc.cu``).
 """
 from __future__ import annotations
 
@@ -9,7 +17,7 @@ from typing import Optional
 
 import torch
 
-from . import native
+from . import mx, native
 
 
 class BigPath:
@@ -17,6 +25,8 @@ class BigPath:
         self.e = engine
         self.buf = {}
         self._converted = None      # layer whose experts currently sit in the FP8 staging copy
+        self._mx_layer = None       # layer whose expert scales currently sit in the block-scaled layout
+        self._mx_u = []
         self.resident = engine.world >= 4          # per-layer FP8 expert copies stay on the device
         self._resident = {}
 
@@ -31,7 +41,43 @@ class BigPath:
         return t[:n].view(*shape)
 
     # ---- dense ----------------------------------------------------------------------------
+    def _units(self, w):
+        """UE8M0 scales of a dense weight in the block-scaled kernel's layout (cached on the weight)."""
+        if w.sfu is None:
+            u = mx.units_from_block_scales(w.s, w.q.shape[0], w.q.shape[1])
+            w.sfu = u if u is not None else False
+        return w.sfu if w.sfu is not False else None
+
+    def _gemm_mx(self, eng, x16: torch.Tensor, w, out: torch.Tensor, M: int, w3=None) -> bool:
+        if not eng.ecfg.prefill_mx:
+            return False
+        sfb = self._units(w)
+        sfb3 = self._units(w3) if w3 is not None else None
+        if sfb is None or (w3 is not None and sfb3 is None):
+            return False
+        N, K = w.q.shape
+        xq = self._get("xq_mx", (M, K), torch.uint8)
+        sfa = self._get("sfa_mx", (K // 128, mx.sf_units(M, 128), 128), torch.uint8)
+        mx.quant_rows(x16, M, K, xq, sfa)
+        st = eng.status.t
+        if w3 is None:
+            if out.dtype in (torch.float32, torch.bfloat16):
+                mx.gemm(xq, sfa, w.q, sfb, out, M, N, K, st)
+            else:
+                tmp = self._get("gemm_tmp", (M, N), torch.bfloat16)
+                mx.gemm(xq, sfa, w.q, sfb, tmp, M, N, K, st)
+                out[:M, :N].copy_(tmp)
+            return True
+        y = self._get("dual_y", (M, 2 * N), torch.bfloat16)
+        mx.gemm(xq, sfa, w.q, sfb, y, M, N, K, st)
+        mx.gemm(xq, sfa, w3.q, sfb3, y[:, N:], M, N, K, st)
+        assert out.dtype == torch.float16
+        native.call("tf_swiglu_rows", y, 2, 2 * N, out, out.stride(0), None, None, M, N, eng.cfg.swiglu_limit, None)
+        return True
+
     def gemm(self, eng, x16: torch.Tensor, w, out: torch.Tensor, M: int, w3=None) -> None:
+        if self._gemm_mx(eng, x16, w, out, M, w3):
+            return
         N, K = w.q.shape
         xq = self._get("xq", (M, K), torch.uint8)
         xs = self._get("xs", (M, K // 128), torch.float32)
@@ -80,6 +126,36 @@ class BigPath:
         e_lo = eng.rank * El
         native.call("tf_moe_plan", b["ids"], npairs, e_lo, El, z, offsets, cursor, tile_e, max_tiles, ntile[0:1],
                     ntile[1:2], pair_dst)
+        st = eng.status.t
+        if eng.ecfg.prefill_mx and d % 128 == 0 and I % 256 == 0 and d % 256 == 0:
+            # block-scaled form: the packed e2m1 weights are read as stored; their UE8M0 scales are
+            # re-ordered into the kernel's layout once per layer visit (a few hundred MB of traffic
+            # against the GBs of the FP8 re-expression below)
+            if self._mx_layer is not L:
+                u = self._get("mx_units", (3, (d // 128) * mx.sf_units(El * I, 256) * 128), torch.uint8)
+                self._mx_u = []
+                for j, (sc, rows, kk) in enumerate(((L.es1, El * I, d), (L.es3, El * I, d), (L.es2, El * d, I))):
+                    uu = u[j][: (kk // 128) * mx.sf_units(rows, 256) * 128].view(kk // 128, mx.sf_units(rows, 256), 128)
+                    native.call("tf_mx_sf_to_units", sc, uu, rows, kk, uu.shape[1])
+                    self._mx_u.append(uu)
+                self._mx_layer = L
+            u1, u3, u2 = self._mx_u
+            xp = self._get("xp", (cap, d), torch.uint8)
+            sfx = self._get("sfx_mx", (d // 128, cap // 32, 128), torch.uint8)
+            mx.quant_rows(b["h16"], npairs, d, xp, sfx, x_div=k, pair_dst=pair_dst)
+            y1 = self._get("y1", (cap, 2 * I), torch.bfloat16)
+            mx.gemm(xp, sfx, L.ew1, u1, y1, cap, I, d, st, b_fp4=True, b_rows=El * I, tile_expert=tile_e,
+                    num_m_tiles=ntile[0:1])
+            mx.gemm(xp, sfx, L.ew3, u3, y1[:, I:], cap, I, d, st, b_fp4=True, b_rows=El * I, tile_expert=tile_e,
+                    num_m_tiles=ntile[0:1])
+            aq = self._get("aq", (cap, I), torch.uint8)
+            sfq = self._get("sfq_mx", (I // 128, cap // 32, 128), torch.uint8)
+            native.call("tf_swiglu_rows_mx_units", y1, 2 * I, aq, sfq, cap // 32, cap, I, cfg.swiglu_limit, ntile[1:2])
+            y2 = self._get("y2", (cap, d), torch.bfloat16)
+            mx.gemm(aq, sfq, L.ew2, u2, y2, cap, d, I, st, b_fp4=True, b_rows=El * d, tile_expert=tile_e,
+                    num_m_tiles=ntile[0:1])
+            self._moe_tail(eng, L, T, b, y2, pair_dst, with_shared, out)
+            return
         # expert weights of this layer as block-scaled FP8: [El, 2I, d] (w1 | w3) and [El, d, I]
         def convert(w13, s13, w2, s2):
             native.call("tf_mxfp4_to_fp8_block", L.ew1, L.es1, w13, s13, El, I, d, 0, 2 * I)
@@ -109,7 +185,6 @@ class BigPath:
         xp = self._get("xp", (cap, d), torch.uint8)
         xps = self._get("xps", (cap, d // 128), torch.float32)
         native.call("tf_quant_rows", b["h16"], 1, d, None, k, pair_dst, xp, xps, npairs, d)
-        st = eng.status.t
         y1 = self._get("y1", (cap, 2 * I), torch.bfloat16)
         native.call("tf_gemm_tc", 2, xp, d, w13, d, y1, 2 * I, cap, 2 * I, d, xps, d // 128, s13, d // 128, 2,
                     tile_e, ntile[0:1], El, st)
@@ -119,14 +194,19 @@ class BigPath:
         y2 = self._get("y2", (cap, d), torch.bfloat16)
         native.call("tf_gemm_tc", 2, aq, I, w2, I, y2, d, cap, d, I, aqs, I // 128, s2, I // 128, 2,
                     tile_e, ntile[0:1], El, st)
+        self._moe_tail(eng, L, T, b, y2, pair_dst, with_shared, out)
+
+    def _moe_tail(self, eng, L, T: int, b: dict, y2, pair_dst, with_shared: bool, out) -> None:
+        """Shared expert, then the weighted sum of every row's expert outputs (+ shared) -> delta / out."""
+        cfg = eng.cfg
         shared = None
         if cfg.n_shared and with_shared:
             eng._linear(b["h16"], L.sw1, b["s_act"], T, w3=L.sw3)
             eng._linear(b["s_act"], L.sw2, b["s_y"], T)
             shared = b["s_y"]
         dst = b["delta"] if out is None else out
-        native.call("tf_moe_combine_perm", y2, 2, d, pair_dst, b["wts"], shared, dst,
-                    2 if dst.dtype == torch.bfloat16 else 0, T, d, k)
+        native.call("tf_moe_combine_perm", y2, 2, cfg.hidden, pair_dst, b["wts"], shared, dst,
+                    2 if dst.dtype == torch.bfloat16 else 0, T, cfg.hidden, cfg.topk)
 
 
 def attach(engine) -> BigPath:

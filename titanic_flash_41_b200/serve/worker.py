@@ -375,14 +375,15 @@ class Worker:
                                                  cks[0] if cks else len(prompt), len(prompt), 128)
         if shared is not None:
             cks = sorted(set(cks + [shared]))
-        logits, pos = None, start
+        logits, pos, reached = None, start, start
         last_slice = self.clock()
         for stop in cks + [len(prompt)]:
             if stop <= pos:
                 continue
 
             def on_chunk(done, _base=pos):
-                nonlocal last_slice
+                nonlocal last_slice, reached
+                reached = _base + done                 # the state of the region covers prompt[:reached]
                 # a long prefill lets the decoding conversations take one batched step per slice
                 d = self._chunk_directive(job, last_slice)
                 if d == D_STEP:
@@ -397,6 +398,15 @@ class Worker:
                 kw["prev"] = prompt[max(0, pos - 8):pos]
             logits = self.b.prefill(region, prompt[pos:stop], pos, on_chunk, **kw)
             if logits is None:
+                # an interrupted prefill keeps what it has computed: the same prompt sent again resumes
+                # from the last whole chunk instead of position 0 (reference: src/resident_worker.rs
+                # encoder checkpoints of an unfinished Begin)
+                if reached - start >= self.ck_min and reached < len(prompt):
+                    try:
+                        self.cache.insert(self.b.snapshot(region, prompt[:reached], "checkpoint", cmd.get("media", "")))
+                        self.log.log("prefill_interrupted", id=cmd["id"], saved=reached, of=len(prompt))
+                    except Exception as e:  # noqa: BLE001  (a refused save never fails the cancellation)
+                        self.log.log("save_failed", incident=True, error=str(e))
                 self._emit(job, "error", {"code": "cancelled", "message": "cancelled during prefill"})
                 if self.sched and job:
                     self.sched.release(job)
