@@ -309,11 +309,17 @@ __global__ void __launch_bounds__(128) quant_rows_mx_units_kernel(const T* __res
   const int dst = pair_dst ? pair_dst[r] : r;
   if (dst < 0) return;
   const T* src = x + (long)(r / x_div) * ldx + b * 32;
+  // 32 inputs = 64 (or 128) contiguous bytes, 16-byte aligned (ldx is a multiple of 8 elements)
+  constexpr int kVec = 16 / sizeof(T);
+  T raw[32];
+#pragma unroll
+  for (int j = 0; j < 32 / kVec; ++j)
+    *reinterpret_cast<uint4*>(raw + j * kVec) = *reinterpret_cast<const uint4*>(src + j * kVec);
   float v[32];
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    v[j] = to_f<T>(src[j]);
+    v[j] = to_f<T>(raw[j]);
     amax = fmaxf(amax, fabsf(v[j]));
   }
   const int ex = mx_exponent(amax);
@@ -346,11 +352,17 @@ __global__ void __launch_bounds__(128) swiglu_rows_mx_units_kernel(const __nv_bf
   const int r = (int)(i / ks), b = (int)(i % ks);
   const __nv_bfloat16* g = y + (long)r * ldy + b * 32;
   const __nv_bfloat16* u = g + I;
+  __nv_bfloat16 gr[32], ur[32];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    *reinterpret_cast<uint4*>(gr + 8 * j) = *reinterpret_cast<const uint4*>(g + 8 * j);
+    *reinterpret_cast<uint4*>(ur + 8 * j) = *reinterpret_cast<const uint4*>(u + 8 * j);
+  }
   float v[32];
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    float gate = __bfloat162float(g[j]), up = __bfloat162float(u[j]);
+    float gate = __bfloat162float(gr[j]), up = __bfloat162float(ur[j]);
     if (limit > 0.f) {
       gate = fminf(gate, limit);
       up = fminf(fmaxf(up, -limit), limit);
@@ -476,7 +488,7 @@ TF_API int tf_gemm_mx(const void* A, long lda, const void* B, long ldb, long b_r
 // [dst rows, K] + unit-layout scales.  pair_dst (optional): destination row of every source pair.
 TF_API int tf_quant_rows_mx_units(const void* x, int xkind, int ldx, int x_div, const int* pair_dst, void* q, void* sf,
                                   int sf_units, int rows, int K, cudaStream_t st) {
-  if (rows <= 0 || K % 128 || x_div <= 0 || !x || !q || !sf) return -1;
+  if (rows <= 0 || K % 128 || x_div <= 0 || !x || !q || !sf || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
   const long n = (long)rows * (K / 32);
   const dim3 grid((unsigned)((n + 127) / 128));
   uint8_t* qq = reinterpret_cast<uint8_t*>(q);
@@ -497,7 +509,7 @@ TF_API int tf_quant_rows_mx_units(const void* x, int xkind, int ldx, int x_div, 
 
 TF_API int tf_swiglu_rows_mx_units(const void* y, int ldy, void* q, void* sf, int sf_units, int rows, int I,
                                    float limit, const int* num_rows, cudaStream_t st) {
-  if (rows <= 0 || I % 128 || !y || !q || !sf) return -1;
+  if (rows <= 0 || I % 128 || !y || !q || !sf || ldy % 8 || (reinterpret_cast<uintptr_t>(y) & 15)) return -1;
   const long n = (long)rows * (I / 32);
   tf_launch(swiglu_rows_mx_units_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st,
             reinterpret_cast<const __nv_bfloat16*>(y), ldy, reinterpret_cast<uint8_t*>(q),

@@ -87,6 +87,9 @@ class LayerWeights:
     full: Optional["LayerWeights"] = None
 
 
+POW2_SCALES = True      # block scales rounded up to powers of two (False: amax / 448 exactly; such weights stay off the block-scaled GEMM)
+
+
 def quant_fp8_device(w: torch.Tensor) -> Fp8Weight:
     """Block-128 FP8 quantisation on the tensor's device; rows padded to a multiple of 128."""
     n, k = w.shape
@@ -96,7 +99,8 @@ def quant_fp8_device(w: torch.Tensor) -> Fp8Weight:
     wf[:n] = w.float()
     t = wf.view(npad // 128, 128, k // 128, 128)
     s = t.abs().amax(dim=(1, 3)).clamp_min(1e-12) / codecs.E4M3_MAX
-    s = torch.exp2(torch.ceil(torch.log2(s)).clamp(-126, 126))     # UE8M0: the checkpoint's scale format
+    if POW2_SCALES:
+        s = torch.exp2(torch.ceil(torch.log2(s)).clamp(-126, 126))     # UE8M0: the checkpoint's scale format
     q = (t / s[:, None, :, None]).clamp(-448, 448).to(F8).view(npad, k)
     return Fp8Weight(q.contiguous(), s.contiguous(), n, k)
 
