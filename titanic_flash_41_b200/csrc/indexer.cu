@@ -220,9 +220,14 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
     for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix;
-    for (int i = tid; i < n; i += blockDim.x) {
-      uint32_t key = float_key(s[i]);
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+    // index scores crowd into a few exponent bytes: one shared atomic per warp and distinct bin
+    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+      const int i = i0 + tid;
+      const uint32_t key = i < n ? float_key(s[i]) : 0u;
+      const bool in = i < n && (key & mask) == prefix;
+      const int bin = in ? (int)((key >> shift) & 0xffu) : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, bin);
+      if (in && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
     }
     __syncthreads();
     if (tid == 0) {

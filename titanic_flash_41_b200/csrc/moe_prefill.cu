@@ -225,6 +225,52 @@ __global__ void moe_combine_perm_kernel(const T* __restrict__ y, long ldy, const
   }
 }
 
+// The same sum for bf16 expert outputs, eight columns per thread (16-byte loads; d and ldy multiples
+// of 8, 16-byte aligned rows): same order of additions per element.
+template <typename O>
+__global__ void __launch_bounds__(256) moe_combine_perm_vec_kernel(const __nv_bfloat16* __restrict__ y, long ldy,
+                                                                   const int* __restrict__ pair_dst,
+                                                                   const float* __restrict__ wts,
+                                                                   const float* __restrict__ shared_y,
+                                                                   O* __restrict__ out, int d, int topk) {
+  tf_pdl_sync();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      const int dst = pair_dst[t * topk + j];
+      if (dst < 0) continue;
+      const float w = wts[t * topk + j];
+      const uint4 raw = *reinterpret_cast<const uint4*>(y + (long)dst * ldy + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 f = __bfloat1622float2(h[c]);
+        acc[2 * c] = fmaf(w, f.x, acc[2 * c]);
+        acc[2 * c + 1] = fmaf(w, f.y, acc[2 * c + 1]);
+      }
+    }
+    if (shared_y) {
+      const float4 a = *reinterpret_cast<const float4*>(shared_y + (long)t * d + i);
+      const float4 b = *reinterpret_cast<const float4*>(shared_y + (long)t * d + i + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    if (sizeof(O) == 4) {
+      float4* o = reinterpret_cast<float4*>(out + (long)t * d + i);
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      __nv_bfloat162 hh[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) hh[c] = __floats2bfloat162_rn(acc[2 * c], acc[2 * c + 1]);
+      *reinterpret_cast<uint4*>(out + (long)t * d + i) = *reinterpret_cast<uint4*>(hh);
+    }
+  }
+}
+
 // out[i] = sum over w (in order) of slices[w * stride + i] (bf16) + extra[i], for i < n: the owner of
 // a row slice sums the partial outputs every rank sent for it, in rank order, in fp32
 __global__ void sum_slices_kernel(const __nv_bfloat16* __restrict__ slices, int world, long stride,
@@ -308,7 +354,11 @@ TF_API int tf_moe_combine_perm(const void* y, int y_kind, long ldy, const int* p
                                cudaStream_t st) {
   if (T <= 0) return 0;
   if (!y || !pair_dst || !wts || !out) return -1;
-  if (y_kind == 0 && out_kind == 0) tf_launch(moe_combine_perm_kernel<float, float>, dim3(T), dim3(256), 0, st, (const float*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
+  const bool vec = y_kind == 2 && d % 8 == 0 && ldy % 8 == 0 && !(reinterpret_cast<uintptr_t>(y) & 15) &&
+                   !(reinterpret_cast<uintptr_t>(out) & 15) && !(shared_y && (reinterpret_cast<uintptr_t>(shared_y) & 15));
+  if (vec && out_kind == 0) tf_launch(moe_combine_perm_vec_kernel<float>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
+  else if (vec && out_kind == 2) tf_launch(moe_combine_perm_vec_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (__nv_bfloat16*)out, d, topk);
+  else if (y_kind == 0 && out_kind == 0) tf_launch(moe_combine_perm_kernel<float, float>, dim3(T), dim3(256), 0, st, (const float*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
   else if (y_kind == 2 && out_kind == 0) tf_launch(moe_combine_perm_kernel<__nv_bfloat16, float>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (float*)out, d, topk);
   else if (y_kind == 2 && out_kind == 2) tf_launch(moe_combine_perm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)y, ldy, pair_dst, wts, shared_y, (__nv_bfloat16*)out, d, topk);
   else return -1;
