@@ -4,6 +4,8 @@ under a GB on the device).  Each target prints the CUDA-event time of its launch
     python benchmarks/profile_targets.py allreduce     # one-shot all-reduce + boundary, 2 emulated ranks, 16 x 4096
     python benchmarks/profile_targets.py sampler       # chunked sampler: verification of 4 x (3 + 1) rows, vocabulary 129,280
     python benchmarks/profile_targets.py attention     # sparse attention: 2,048 prefill rows, 64 heads x 128, 128 window + 2,048 selected keys
+    python benchmarks/profile_targets.py index         # index scores + exact top-2048 of 2,048 prefill rows over 32,768 keys, 8 heads x 128
+    python benchmarks/profile_targets.py prep          # attention prep of 2,048 prefill rows (RoPE, FP8 window rows, pooling, FP4 entries, index keys)
 """
 import math
 import os
@@ -103,5 +105,62 @@ def attention():
           f"{flops / us / 1e6:.1f} TFLOP/s")
 
 
+def index():
+    T, Hi, Di, C, k = 2048, 8, 128, 32768, 2048
+    krow = Di // 2 + Di // 32
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    keys = torch.randint(0, 256, (1, C, krow), dtype=torch.uint8, device=DEV, generator=gen)
+    keys[:, :, Di // 2:] = 120                                  # UE8M0 scales near 2^-7
+    q = torch.randn(T, Hi, Di, device=DEV, generator=gen).bfloat16()
+    w = torch.rand(T, Hi, device=DEV, generator=gen)
+    region = torch.zeros(T, dtype=torch.int32, device=DEV)
+    nvalid = ((torch.arange(T, device=DEV) + 131072 - T + 1) // 4).int()
+    scores = torch.zeros(T, C, device=DEV)
+    sel = torch.zeros(T, k, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(T, dtype=torch.int32, device=DEV)
+    us = timed(lambda: native.call("tf_index_scores", q, w, region, nvalid, keys, C * krow, krow, T, Hi, Di, 32, scores, C, 0,
+                                   C), n=3, warm=1)
+    print(f"index scores, {T} rows x {C} keys, {Hi} heads x {Di}: {us:.0f} us per launch, "
+          f"{2.0 * T * C * Hi * Di / us / 1e6:.1f} TFLOP/s")
+    us = timed(lambda: native.call("tf_topk_select", scores, C, nvalid, k, sel, cnt, None, 0, T), n=3, warm=1)
+    print(f"top-{k} select of {T} rows x {C} scores: {us:.0f} us per launch")
+
+
+def prep():
+    T, Hl, Dh, Di, Hi, ratio, rope = 2048, 64, 128, 128, 8, 4, 64
+    ring, maxC = 16384 + 256, 32768 + 8
+    win_row, comp_row = -(-(Dh + Dh // 32) // 16) * 16, -(-(Dh // 2 + Dh // 16) // 16) * 16
+    krow = Di // 2 + Di // 32
+    C = Dh + Di
+    offs, o = {}, 0
+    for nm, wd in (("q", Hl * Dh), ("kv", Dh), ("cv", C), ("cg", C), ("iq", Hi * Di), ("iw", Hi)):
+        offs[nm] = o
+        o += wd
+    W = -(-o // 8) * 8
+    gen = torch.Generator(device=DEV).manual_seed(4)
+    P = torch.randn(T, W, device=DEV, generator=gen).half()
+    pos = (torch.arange(T, dtype=torch.int32) + 131072 - T).to(DEV)
+    region = torch.zeros(T, dtype=torch.int32, device=DEV)
+    first = torch.zeros(T, dtype=torch.int32, device=DEV)
+    last = torch.full((T,), 131071, dtype=torch.int32, device=DEV)
+    freqs = torch.tensor([10000.0 ** (-2.0 * j / rope) for j in range(rope // 2)], device=DEV)
+    norm = torch.ones(Dh, device=DEV, dtype=torch.bfloat16)
+    qo = torch.zeros(T, Hl * Dh, device=DEV, dtype=torch.bfloat16)
+    win = torch.zeros(1, ring, win_row, dtype=torch.uint8, device=DEV)
+    comp = torch.zeros(1, maxC, comp_row, dtype=torch.uint8, device=DEV)
+    keys = torch.zeros(1, maxC, krow, dtype=torch.uint8, device=DEV)
+    carry = torch.zeros(1, ratio + 32, 2 * C, device=DEV)
+    iq = torch.zeros(T, Hi * Di, device=DEV, dtype=torch.bfloat16)
+    iw = torch.zeros(T, Hi, device=DEV)
+    st = native.StatusWord(DEV)
+    us = timed(lambda: native.call("tf_attn_prep", P, 1, W, T, pos, region, first, last, Hl, Dh, rope, freqs, freqs, norm, 1e-6,
+                                   qo, win, ring * win_row, win_row, comp_row, krow, ring, offs["q"], offs["kv"], offs["cv"],
+                                   offs["cg"], offs["iq"], offs["iw"], ratio, Di, Hi, norm, carry, comp, keys, maxC, iq, iw,
+                                   st.t), n=3, warm=1)
+    st.check()
+    print(f"attention prep, {T} rows ({W} projected columns): {us:.0f} us per launch, "
+          f"{(T * W * 2 + T * Hl * Dh * 2) / us / 1e3:.0f} GB/s of rows read + queries written")
+
+
 if __name__ == "__main__":
-    {"allreduce": allreduce, "sampler": sampler, "attention": attention}[sys.argv[1]]()
+    {"allreduce": allreduce, "sampler": sampler, "attention": attention, "index": index, "prep": prep}[sys.argv[1]]()

@@ -32,7 +32,7 @@ struct ScoreParams {
 };
 
 template <int DI>
-__global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
+__global__ void __launch_bounds__(128, 3) index_score_kernel(ScoreParams p) {
   tf_pdl_sync();
   constexpr int KS = DI + 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
   const int rpt = p.Hi >= 16 ? 1 : 16 / p.Hi;
   const int head_tiles = p.Hi >= 16 ? (p.Hi + 15) / 16 : 1;
   const int units = (nrows + rpt - 1) / rpt;
+  const uint32_t kfrag = (uint32_t)__cvta_generic_to_shared(Ks + (lane & 7) * KS + (lane >> 3) * 8);
   for (int u = warp; u < units; u += 4) {
     float tot0[kKeysPerCta / 8][2], tot8[kKeysPerCta / 8][2];
 #pragma unroll
@@ -126,13 +127,17 @@ __global__ void __launch_bounds__(128) index_score_kernel(ScoreParams p) {
 #pragma unroll
       for (int nt = 0; nt < kKeysPerCta / 8; ++nt) {
         float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-        const __half* kr = Ks + (nt * 8 + g) * KS + 2 * t;
+        // one ldmatrix.x4 brings the B fragments of two 16-deep k steps (lane l: row l % 8 of
+        // matrix l / 8; matrices = k 0-7, 8-15, 16-23, 24-31 of this 32-deep piece)
+        const uint32_t kaddr = kfrag + nt * (8 * KS * 2);
 #pragma unroll
-        for (int ks = 0; ks < DI / 16; ++ks) {
-          uint32_t b[2];
-          b[0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
-          b[1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
-          mma_f16_16816(sacc, qf[ks], b);
+        for (int k2 = 0; k2 < DI / 32; ++k2) {
+          uint32_t b4[4];
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b4[0]), "=r"(b4[1]), "=r"(b4[2]), "=r"(b4[3])
+                       : "r"(kaddr + k2 * 64));
+          mma_f16_16816(sacc, qf[2 * k2], b4);
+          mma_f16_16816(sacc, qf[2 * k2 + 1], b4 + 2);
         }
         tot0[nt][0] += fmaxf(sacc[0], 0.f) * w0;
         tot0[nt][1] += fmaxf(sacc[1], 0.f) * w0;
