@@ -138,7 +138,7 @@ def prep():
         o += wd
     W = -(-o // 8) * 8
     gen = torch.Generator(device=DEV).manual_seed(4)
-    P = torch.randn(T, W, device=DEV, generator=gen).half()
+    P = torch.randn(T, W, device=DEV, generator=gen).bfloat16()
     pos = (torch.arange(T, dtype=torch.int32) + 131072 - T).to(DEV)
     region = torch.zeros(T, dtype=torch.int32, device=DEV)
     first = torch.zeros(T, dtype=torch.int32, device=DEV)

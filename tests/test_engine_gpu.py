@@ -94,7 +94,7 @@ def test_block_scaled_expert_path_matches_register_path_and_oracle():
     eng.status.check()
     ref.expert_act_mx8 = False
     errs, errs_old, between, oracle_shift = (torch.cat(v) for v in (errs, errs_old, between, oracle_shift))
-    assert errs_old.median() < 0.08, errs_old
+    assert errs_old.median() < 0.11, errs_old
     assert between.median() < 1.5 * oracle_shift.median() + 0.01, (between, oracle_shift)
     # rounding decisions of two noisy paths are independent: the distances add in quadrature
     bound = (errs_old.median() ** 2 + 2 * oracle_shift.median() ** 2) ** 0.5 + 0.02

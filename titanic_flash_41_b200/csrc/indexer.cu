@@ -146,17 +146,71 @@ __global__ void __launch_bounds__(128, 3) index_score_kernel(ScoreParams p) {
       }
     }
     // sum over the heads of one query row: lanes that differ in the low log2(min(Hi,8)) bits of g
-    const int span = p.Hi >= 16 ? 8 : p.Hi;            // fragment rows of one query row within g
+    if (p.Hi >= 8) {
+      // Eight fragment rows (g) per query row.  Halving exchange instead of a butterfly per value:
+      // in each of three rounds a lane keeps the half of its values whose key-tile bit equals its
+      // own bit of g and hands the other half to its partner, so 64 values cost 32 + 16 + 8
+      // shuffles (not 192) and every lane ends with the finished sums of key tiles g and g + 8,
+      // which it stores itself.  Same pairing order as a butterfly: bitwise the same sums.
+      const int nh = p.Hi >= 16 ? 1 : 2;                 // 16+ heads: tot0 and tot8 are the same query row
+      const bool g0 = g & 1, g1 = g & 2, g2 = g & 4;
+      float A[8][2][2], B[4][2][2], C[2][2][2];
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            if (h < nh) {
+              float lo = h ? tot8[2 * m][i] : tot0[2 * m][i], hi = h ? tot8[2 * m + 1][i] : tot0[2 * m + 1][i];
+              if (nh == 1) {
+                lo += tot8[2 * m][i];
+                hi += tot8[2 * m + 1][i];
+              }
+              A[m][h][i] = (g0 ? hi : lo) + __shfl_xor_sync(0xffffffffu, g0 ? lo : hi, 4);
+            }
+          }
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            if (h < nh)
+              B[n][h][i] = (g1 ? A[2 * n + 1][h][i] : A[2 * n][h][i]) +
+                           __shfl_xor_sync(0xffffffffu, g1 ? A[2 * n][h][i] : A[2 * n + 1][h][i], 8);
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            if (h < nh)
+              C[q][h][i] = (g2 ? B[2 * q + 1][h][i] : B[2 * q][h][i]) +
+                           __shfl_xor_sync(0xffffffffu, g2 ? B[2 * q][h][i] : B[2 * q + 1][h][i], 16);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int ri = h == 0 ? ra : rb;
+        if (h >= nh || ri >= nrows) continue;
+        const int r = row0 + ri;
+        const int nv = min(p.nvalid[r], p.key_hi);
+        float* out = p.scores + (long)r * p.lds;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int k = key0 + (8 * q + g) * 8 + 2 * t;   // this lane holds key tile 8q + g
+          if (k < p.lds && k < p.key_hi) out[k] = k < nv ? C[q][h][0] : -INFINITY;
+          if (k + 1 < p.lds && k + 1 < p.key_hi) out[k + 1] = k + 1 < nv ? C[q][h][1] : -INFINITY;
+        }
+      }
+      continue;
+    }
+    const int span = p.Hi;                               // fewer than 8 heads: fragment rows of one query row within g
     const bool writer = (g % span) == 0;
 #pragma unroll
     for (int nt = 0; nt < kKeysPerCta / 8; ++nt) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         float a = tot0[nt][i], b = tot8[nt][i];
-        if (p.Hi >= 16) {
-          a += b;
-          b = 0.f;
-        }
         for (int m = 4; m < 4 * span; m <<= 1) {
           a += __shfl_xor_sync(0xffffffffu, a, m);
           b += __shfl_xor_sync(0xffffffffu, b, m);
@@ -168,7 +222,6 @@ __global__ void __launch_bounds__(128, 3) index_score_kernel(ScoreParams p) {
         const int k = key0 + nt * 8 + 2 * t;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          if (half == 1 && p.Hi >= 16) break;
           const int ri = half == 0 ? ra : rb;
           if (ri >= nrows) continue;
           const int r = row0 + ri;
@@ -225,14 +278,20 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
     for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix;
-    // index scores crowd into a few exponent bytes: one shared atomic per warp and distinct bin
-    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
-      const int i = i0 + tid;
-      const uint32_t key = i < n ? float_key(s[i]) : 0u;
-      const bool in = i < n && (key & mask) == prefix;
-      const int bin = in ? (int)((key >> shift) & 0xffu) : -1;
-      const unsigned peers = __match_any_sync(0xffffffffu, bin);
-      if (in && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+    if (pass == 0) {
+      // index scores crowd into a few exponent bytes: one shared atomic per warp and distinct bin
+      for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+        const int i = i0 + tid;
+        const bool in = i < n;
+        const int bin = in ? (int)(float_key(s[i]) >> 24) : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (in && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+      }
+    } else {
+      for (int i = tid; i < n; i += blockDim.x) {
+        const uint32_t key = float_key(s[i]);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+      }
     }
     __syncthreads();
     if (tid == 0) {
