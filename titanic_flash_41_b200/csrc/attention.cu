@@ -55,7 +55,6 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
   constexpr int KS = DH + 8;          // row stride of Ks (halfs): 16-byte rows shifted by one bank group per key
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half* Ks = reinterpret_cast<__half*>(smem_raw);          // [64][KS]
-  __shared__ int key_src[kChunk];                            // >=0: window slot; <0: ~compressed id
 
   const int r = blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -108,65 +107,90 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
   const int wrow = p.win_row, crow = p.comp_row;
   const uint8_t* win = p.win + (long)reg * p.win_region_stride;
   const uint8_t* comp = p.comp ? p.comp + (long)reg * p.comp_region_stride : nullptr;
+  const uint32_t kfrag = (uint32_t)__cvta_generic_to_shared(Ks + (lane & 7) * KS + (lane >> 3) * 8);
+
+  // Gather pipeline.  Thread tid serves key tid % 64 of every chunk and NI = DH / 32 of its 16-value
+  // segments (tid / 64 + 2j).  The raw bytes of the NEXT chunk's rows (and the key ids of the chunk
+  // after it) are requested before this chunk's MMAs and converted after them, so the two dependent
+  // global loads of a gathered row (id -> row) overlap the tensor work instead of preceding it.
+  constexpr int NI = DH / 32;
+  const int my_key = threadIdx.x & (kChunk - 1), seg0 = threadIdx.x >> 6;
+  auto load_src = [&](int c) -> int {
+    const int i = c * kChunk + my_key;
+    if (c >= nchunks || i >= nkeys) return 0x7fffffff;
+    if (i < nwin) return (pos - nwin + 1 + i) % p.ring;
+    int id = p.sel[(long)r * p.sel_stride + (i - nwin)];
+    if (id < 0 || id >= p.maxC) {
+      tf_report(p.st, TF_BAD_INDEX, 10, r, id);
+      id = 0;
+    }
+    return ~id;
+  };
+  uint4 raw[NI];
+  uint8_t rsc[NI];
+  auto load_raw = [&](int src) {
+    if (src == 0x7fffffff) return;
+    if (src >= 0) {
+      const uint8_t* row = win + (long)src * wrow;
+#pragma unroll
+      for (int j = 0; j < NI; ++j) {
+        raw[j] = *reinterpret_cast<const uint4*>(row + (seg0 + 2 * j) * 16);
+        rsc[j] = row[DH + j];                        // (seg0 + 2j) >> 1 == j
+      }
+    } else {
+      const uint8_t* row = comp + (long)(~src) * crow;
+#pragma unroll
+      for (int j = 0; j < NI; ++j) {
+        const uint2 v = *reinterpret_cast<const uint2*>(row + (seg0 + 2 * j) * 8);
+        raw[j] = make_uint4(v.x, v.y, 0u, 0u);
+        rsc[j] = row[DH / 2 + seg0 + 2 * j];
+      }
+    }
+  };
+  int src_cur = load_src(split), src_next = load_src(split + p.nsplit);
+  load_raw(src_cur);
 
   for (int c = split; c < nchunks; c += p.nsplit) {
     const int kbase = c * kChunk;
-    __syncthreads();
-    for (int kk = threadIdx.x; kk < kChunk; kk += blockDim.x) {
-      const int i = kbase + kk;
-      int src = 0x7fffffff;
-      if (i < nwin) {
-        src = (pos - nwin + 1 + i) % p.ring;
-      } else if (i < nkeys) {
-        int id = p.sel[(long)r * p.sel_stride + (i - nwin)];
-        if (id < 0 || id >= p.maxC) {
-          tf_report(p.st, TF_BAD_INDEX, 10, r, id);
-          id = 0;
-        }
-        src = ~id;
-      }
-      key_src[kk] = src;
-    }
-    __syncthreads();
-    // dequantise: 8 threads per key, 16 elements each
-    for (int it = threadIdx.x; it < kChunk * (DH / 16); it += blockDim.x) {
-      const int key = it % kChunk, seg = it / kChunk;
-      const int src = key_src[key];
-      uint32_t hv[8];                  // sixteen f16 values of this key segment
-      if (src == 0x7fffffff) {
+    __syncthreads();                                   // the previous chunk's MMAs have read Ks
+    // convert this chunk's rows: sixteen f16 values per segment
 #pragma unroll
-        for (int j = 0; j < 8; ++j) hv[j] = 0u;
-      } else if (src >= 0) {
-        const uint8_t* row = win + (long)src * wrow;
-        uint4 raw = *reinterpret_cast<const uint4*>(row + seg * 16);
-        const float sc = ue8m0_to_float(row[DH + (seg >> 1)]);
-        const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
+    for (int j = 0; j < NI; ++j) {
+      uint32_t hv[8];
+      if (src_cur == 0x7fffffff) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t h2 = e4m3x2_to_h2(h[j]);
+        for (int q = 0; q < 8; ++q) hv[q] = 0u;
+      } else if (src_cur >= 0) {
+        const float sc = ue8m0_to_float(rsc[j]);
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw[j]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t h2 = e4m3x2_to_h2(h[q]);
           float2 f = __half22float2(*reinterpret_cast<__half2*>(&h2));
-          hv[j] = pack_h2(f.x * sc, f.y * sc);
+          hv[q] = pack_h2(f.x * sc, f.y * sc);
         }
       } else {
-        const uint8_t* row = comp + (long)(~src) * crow;
-        const uint2 raw = *reinterpret_cast<const uint2*>(row + seg * 8);
         // the unpacked halves hold value * 2^-14: fold 2^14 into the group's scale (fp32: no overflow)
-        const float sc = e4m3_to_float(row[DH / 2 + seg]) * 16384.f;
+        const float sc = e4m3_to_float(rsc[j]) * 16384.f;
         uint32_t lo4[4], hi4[4];
-        e2m1x8_to_h2x4_scaled(raw.x, lo4);
-        e2m1x8_to_h2x4_scaled(raw.y, hi4);
+        e2m1x8_to_h2x4_scaled(raw[j].x, lo4);
+        e2m1x8_to_h2x4_scaled(raw[j].y, hi4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo4[j]));
-          const float2 c = __half22float2(*reinterpret_cast<__half2*>(&hi4[j]));
-          hv[j] = pack_h2(a.x * sc, a.y * sc);
-          hv[4 + j] = pack_h2(c.x * sc, c.y * sc);
+        for (int q = 0; q < 4; ++q) {
+          const float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo4[q]));
+          const float2 cc = __half22float2(*reinterpret_cast<__half2*>(&hi4[q]));
+          hv[q] = pack_h2(a.x * sc, a.y * sc);
+          hv[4 + q] = pack_h2(cc.x * sc, cc.y * sc);
         }
       }
-      uint4* kd = reinterpret_cast<uint4*>(Ks + key * KS + seg * 16);
+      uint4* kd = reinterpret_cast<uint4*>(Ks + my_key * KS + (seg0 + 2 * j) * 16);
       kd[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
       kd[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
     }
+    // request the next chunk's rows and the ids of the chunk after it
+    src_cur = src_next;
+    load_raw(src_cur);
+    src_next = load_src(c + 2 * p.nsplit);
     __syncthreads();
     if (!warp_active) continue;
 
@@ -175,13 +199,16 @@ __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
 #pragma unroll
     for (int nt = 0; nt < kChunk / 8; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const __half* kr = Ks + (nt * 8 + g) * KS + 2 * t;
+      // one ldmatrix.x4 = the B fragments of two 16-deep steps (lane l: row l % 8 of block l / 8)
+      const uint32_t kaddr = kfrag + nt * (8 * KS * 2);
 #pragma unroll
-      for (int ks = 0; ks < DH / 16; ++ks) {
-        uint32_t b[2];
-        b[0] = *reinterpret_cast<const uint32_t*>(kr + ks * 16);
-        b[1] = *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8);
-        mma_f16_16816(s[nt], qf[ks], b);
+      for (int k2 = 0; k2 < DH / 32; ++k2) {
+        uint32_t b4[4];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b4[0]), "=r"(b4[1]), "=r"(b4[2]), "=r"(b4[3])
+                     : "r"(kaddr + k2 * 64));
+        mma_f16_16816(s[nt], qf[2 * k2], b4);
+        mma_f16_16816(s[nt], qf[2 * k2 + 1], b4 + 2);
       }
     }
     // mask keys beyond the list
