@@ -159,8 +159,10 @@ def main():
         over["index_heads"] = args.index_heads
     cfg = NAMED_MODELS[args.model](**over)
     chunk = 16384
+    # several ranks: a sequence-parallel prefill chunk spans every rank's slice (up to 65,536 rows), so the
+    # slices keep the single-rank kernel shapes and the host launches a quarter as many kernels
     ecfg = EngineConfig(tp=world, regions=SESSIONS, max_context=CONTEXT + 4096, prefill_widths=(chunk,),
-                        use_cuda_graphs=not args.no_graph)
+                        use_cuda_graphs=not args.no_graph, sp_chunk_rows=min(chunk * world, 65536) if world > 1 else 0)
     if args.pdl >= 0:
         ecfg.pdl = bool(args.pdl)
     t0 = time.time()

@@ -88,7 +88,9 @@ def main():
     chunk = max(128, 64 * world)       # sequence-parallel slices of 64 rows: every rank stays on the tensor-core path
     ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(chunk,))
     # the TP engine also splits index scoring by key range from 8 keys on (decode rows)
-    ecfg_tp = EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(chunk,), key_sharded_index_min=8)
+    # (a sequence-parallel chunk spans two single-rank chunks: the window ring holds all of it)
+    ecfg_tp = EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(chunk,), key_sharded_index_min=8,
+                           sp_chunk_rows=2 * chunk)
     eng = E.Engine.from_weights(cfg, ecfg_tp, W, comm=comm, device=dev)
     eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev, spin_limit=2_000_000)
     ref = E.Engine.from_weights(cfg, ecfg, W, comm=LocalComm(), device=dev)

@@ -281,6 +281,8 @@ def test_two_conversations_take_turns_in_one_region_token_exactly():
         got = [t for j, k, pl in ev if k == "tokens" and j == f"c{i}" for t in pl]
         assert got == want[i], i
     kinds = [e["kind"] for e in w.log.snapshot(4096)["events"]]
+    # every Begin records what the host stalled on while the prompt was prefilled
+    assert all(isinstance(e["host_stall"], dict) for e in w.log.snapshot(4096)["events"] if e["kind"] == "begin")
     assert kinds.count("pause") >= 2 and kinds.count("resume") == kinds.count("pause")
     assert sorted(j for j, k, pl in ev if k == "done") == ["c0", "c1"] and not w.parked
 

@@ -136,6 +136,8 @@ def make_backend(args, cfg: ModelConfig, comm):
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     ecfg = EngineConfig(tp=world, regions=args.regions, max_context=args.max_context)
+    if world > 1:
+        ecfg.sp_chunk_rows = min(max(ecfg.prefill_widths) * world, 65536)      # sequence-parallel chunks span the ranks' slices
     if args.checkpoint:
         # streamed, digest-checked, in the stored formats: never more than one layer on the host
         from .models import stream_loader

@@ -323,6 +323,7 @@ class EngineConfig(_JsonMixin):
     reference_matmul: bool = False     # validation only: rows beyond the small-M limit may run through dequantised weights and torch.matmul when the tensor-core path is not attached (never set in serving or benchmarks: the engine refuses instead)
     pdl: bool = False                  # launch kernels with programmatic dependent launch (each kernel waits for its predecessor on the device; the next one is already resident)
     sp_prefill: bool = True            # more than one rank: prefill chunks are split by rows over the ranks (every rank keeps the unsharded dense matrices of the encoder layers)
+    sp_chunk_rows: int = 0                 # rows of one sequence-parallel prefill chunk over ALL ranks (0: the single-rank chunk); the window ring holds a whole chunk
     prefill_mx: bool = True                # prefill GEMMs on the block-scaled tensor-core form (MXFP8 activations)
     moe_block_scaled: bool = True     # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
     seed: int = 0

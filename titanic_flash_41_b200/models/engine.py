@@ -495,7 +495,9 @@ class Engine:
         self.El = cfg.n_experts // self.world
         self.regions = ecfg.regions
         self.max_chunk = max_chunk or max(ecfg.prefill_widths)
-        self.ring = self.max_chunk + 2 * cfg.window
+        # the window ring holds every row of a chunk plus the window before it (a sequence-parallel
+        # chunk spans all ranks' slices)
+        self.ring = max(self.max_chunk, ecfg.sp_chunk_rows if self.world > 1 else 0) + 2 * cfg.window
         self.maxC = ecfg.max_context // cfg.compress_ratio + 8
         self.win_row, self.comp_row = cfg.window_kv_bytes, cfg.compressed_kv_bytes
         self.key_row = cfg.index_key_bytes

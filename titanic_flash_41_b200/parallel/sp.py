@@ -74,6 +74,7 @@ class SpPrefill:
         v.after_prep = self._gather_state
         self.view = v
         self._stage = {}
+        self._plans: dict = {}                                      # (region, first position, rows) -> plan of a slice; cleared per prefill
         self._slice: Tuple[int, int, int, int] = (0, 0, 0, 0)      # region, first position, rows of the chunk, rows per rank
 
     # ------------------------------------------------------------------------------------------
@@ -177,10 +178,12 @@ class SpPrefill:
             ids_l[:T].copy_(b["ids"][:T])
             wts_l[:T].copy_(b["wts"][:T])
         Tp = self.W * tq
-        pb = eng._bufs(Tp)                                          # the parent's buffers for the padded chunk
-        dist.all_gather_into_tensor(pb["h16"].view(-1)[: Tp * d], h_l.view(-1))
-        dist.all_gather_into_tensor(pb["ids"].view(-1)[: Tp * k], ids_l.view(-1))
-        dist.all_gather_into_tensor(pb["wts"].view(-1)[: Tp * k], wts_l.view(-1))
+        # rows, ids and weights of the padded chunk (all the expert path reads of its row buffers)
+        pb = {"h16": self._buf("h_g", (Tp, d), torch.float16), "ids": self._buf("ids_g", (Tp, k), torch.int32),
+              "wts": self._buf("wts_g", (Tp, k), torch.float32)}
+        dist.all_gather_into_tensor(pb["h16"].view(-1), h_l.view(-1))
+        dist.all_gather_into_tensor(pb["ids"].view(-1), ids_l.view(-1))
+        dist.all_gather_into_tensor(pb["wts"].view(-1), wts_l.view(-1))
         # ---- this rank's experts over all rows (the shared expert is not part of the exchange), written
         # as bf16 slices that go back to the owners of the rows, who sum them in rank order in fp32
         send = self._buf("y_send", (self.W, tq, d), torch.bfloat16)
@@ -214,10 +217,14 @@ class SpPrefill:
             self._gather_state(li, L, 0, None)
             self._moe(L, 0, None)
             return None, lo, 0
-        plan = StepPlan.build([(region, p0 + lo, tokens[lo:hi].tolist())], logits="last")
+        key = (region, p0 + lo, T)
+        hit = self._plans.get(key)
+        if hit is None:                                             # one plan per slice, shared by all layers
+            plan = StepPlan.build([(region, p0 + lo, tokens[lo:hi].tolist())], logits="last")
+            hit = self._plans[key] = (plan,) + tuple(v.plan_shape(plan, v.cfg.compress_ratio))
+        plan, nmax, rpg = hit
         b = v._bufs(T)
         v.upload_plan(plan, b)
-        nmax, rpg = v.plan_shape(plan, v.cfg.compress_ratio)
         if sel_in is not None:
             src, ids, cnt = sel_in
             b["sel"][src][:T].copy_(ids)
@@ -237,10 +244,14 @@ class SpPrefill:
         """Near-equal chunks whose sizes are multiples of world x compression ratio (so that every
         rank's slice of every chunk but the last is full and ends on a group boundary)."""
         unit = self.W * self.eng.cfg.compress_ratio
-        k = max(1, -(-n // chunk))
+        # a chunk may span `sp_chunk_rows` rows over all ranks as long as every rank's slice fits the
+        # row buffers of a single-rank chunk and the whole chunk fits the window ring
+        eng = self.eng
+        cap = min(max(chunk, eng.ecfg.sp_chunk_rows), eng.max_chunk * self.W, eng.ring - 2 * eng.cfg.window)
+        k = max(1, -(-n // cap))
         while True:
             per = -(-(-(-n // k)) // unit) * unit
-            if per <= min(chunk, self.eng.max_chunk) or per <= unit:
+            if per <= cap or per <= unit:
                 break
             k += 1
         sizes = []

@@ -101,6 +101,7 @@ def _encoder_sequence_parallel(eng: Engine, region: int, toks: np.ndarray, chunk
     rows of ITS slices between layers; the KV state ends up identical on all ranks."""
     cfg, sp = eng.cfg, eng.sp
     n = int(toks.shape[0])
+    sp._plans.clear()
     sizes = sp.chunk_sizes(n, chunk)
     offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
     d = cfg.hidden
@@ -136,9 +137,9 @@ def _encoder_sequence_parallel(eng: Engine, region: int, toks: np.ndarray, chunk
         else:
             prev = sp.gather_rows(resid[last - 1], sizes[last - 1], d, torch.bfloat16)
             tail[:tail_n].copy_(torch.cat([prev, full_last])[-tail_n:])
-    T = sizes[-1]
+    T = min(sizes[-1], eng.max_chunk)              # (a head that follows needs the last row only)
     b = eng._bufs(T)
-    b["x"][:T].copy_(full_last)
+    b["x"][:T].copy_(full_last[sizes[-1] - T:])
     b["pending"] = False
     eng._sp_last_rows = T
     return True

@@ -341,6 +341,8 @@ class Worker:
 
     def _begin(self, cmd: Dict[str, Any]) -> None:
         t0 = time.monotonic()
+        from ..utils import memory as _mem
+        stall0 = _mem.pressure_snapshot()          # host stall counters around the prefill (memory / io / cpu pressure)
         region, prompt = cmd["region"], list(cmd["tokens"])
         job = self.jobs.get(cmd["id"])
         self.requests += 1
@@ -427,7 +429,9 @@ class Worker:
         new = len(prompt) - start
         self._emit(job, "ready", {"prompt_n": new, "cache_n": start, "prompt_ms": round(ms, 3),
                                   "prompt_per_second": round(new / max(ms / 1e3, 1e-9), 1), "scope": "request"})
-        self.log.log("begin", id=cmd["id"], region=region, prompt=len(prompt), reused=start, ms=round(ms, 2))
+        stall = {k: v for k, v in _mem.pressure_delta(stall0, _mem.pressure_snapshot()).items() if v}
+        self.log.log("begin", id=cmd["id"], region=region, prompt=len(prompt), reused=start, ms=round(ms, 2),
+                     host_stall=stall)
         self._deliver(a, [first], pending=True)
 
     def _deliver(self, a: Active, toks: Sequence[int], pending: bool = False) -> None:
