@@ -324,10 +324,13 @@ def main():
                        "kv_source_layers": list(cfg.kv_source_layers),
                        "index_source_layers": list(cfg.index_source_layers),
                        "prefill": ("sequence-parallel rows" if getattr(eng, "sp", None) is not None else "single rank"),
+                       "prefill_chunk_rows": (ecfg.sp_chunk_rows if getattr(eng, "sp", None) is not None else chunk),
+                       "prefill_gemm": ("block-scaled by the tensor core (MXFP8 activations x FP8 / MXFP4 weights)"
+                                        if ecfg.prefill_mx else "FP8 with fp32 scales per 128, promoted in software"),
                        "sampling": ("rank-local chunks" if dec.ws is not None else "gathered rows"),
                        "programmatic_dependent_launch": native_mod.pdl_enabled(),
                        "l2": "inputs larger than L2 (>= 5 GB of weights touched per step)",
-                       "weights": "FP8 block-128 dense, MXFP4 experts, bf16 head (FP8 draft head)"},
+                       "weights": "FP8 dense with power-of-two scales per 128 x 128 block, MXFP4 experts, bf16 head (FP8 draft head)"},
             "prefill_s": None if prefill_s is None else round(prefill_s, 3),
             "prefill_tokens": args.prefill_tokens if prefill_s is not None else None,
             "prefill_vs_baseline": None if prefill_s is None else round(BASELINE_PREFILL_S / prefill_s, 3),
