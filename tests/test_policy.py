@@ -119,3 +119,25 @@ def test_chained_block_hashes_find_million_token_prefixes_quickly():
     assert P.common_prefix(a, a[:5000], ca, P.chain_hashes(a[:5000])) == 5000
     assert P.common_prefix(list(a[:10]), tuple(a[:7])) == 7   # plain sequences still work
     assert P.common_prefix([], [1]) == 0
+
+
+def test_sequence_parallel_chunk_sizes_respect_slice_and_ring_limits():
+    """A sequence-parallel chunk spans every rank's slice: its size is a multiple of ranks x compression
+    ratio, every slice fits the row buffers of a single-rank chunk and the whole chunk fits the window
+    ring."""
+    from types import SimpleNamespace as NS
+
+    from titanic_flash_41_b200.parallel.sp import SpPrefill
+    def sizes(n, chunk, world, sp_rows, max_chunk=16384, window=128, ratio=4):
+        ring = max(max_chunk, sp_rows) + 2 * window
+        fake = NS(W=world, eng=NS(cfg=NS(compress_ratio=ratio, window=window), ecfg=NS(sp_chunk_rows=sp_rows),
+                                  max_chunk=max_chunk, ring=ring))
+        return SpPrefill.chunk_sizes(fake, n, chunk)
+    s = sizes(129553, 16384, 8, 65536)
+    assert sum(s) == 129553 and len(s) == 2 and all(x % 32 == 0 for x in s[:-1]) and max(s) // 8 <= 16384
+    s = sizes(129553, 16384, 2, 32768)
+    assert sum(s) == 129553 and len(s) == 4 and max(s) <= 32768
+    s = sizes(129553, 16384, 4, 0)                     # no larger chunks configured: the single-rank chunk
+    assert sum(s) == 129553 and max(s) <= 16384
+    s = sizes(40000, 16384, 8, 1 << 20, max_chunk=2048)    # slices bound the chunk: 8 x 2,048 rows
+    assert sum(s) == 40000 and max(s) <= 8 * 2048
