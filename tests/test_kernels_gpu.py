@@ -234,6 +234,68 @@ def test_sparse_attention_matches_reference(Dh, Hl):
         assert _rel(out[r].cpu().view(Hl, Dh), o) < 1e-2, r
 
 
+@pytest.mark.parametrize("Hl", [64, 20])
+def test_sparse_attention_of_prefill_rows_on_tcgen05_matches_reference(Hl):
+    """64 rows or more of one split (head dim 128) run on the tcgen05 kernel (heads as M, 128-key
+    chunks, S / O in tensor memory): same result as the fp32 reference and as the mma.sync kernel,
+    for short rows (window only), rows with several chunks and a partly filled last chunk."""
+    torch.manual_seed(8 + Hl)
+    T, Dh, window, ring, C, k = 200, 128, 128, 512, 700, 320
+    win_row, comp_row = -(-(Dh + Dh // 32) // 16) * 16, -(-(Dh // 2 + Dh // 16) // 16) * 16
+    kv = torch.randn(2, ring, Dh) * 1.5
+    win = torch.zeros(2, ring, win_row, dtype=torch.uint8)
+    win[:, :, :Dh + Dh // 32] = codecs.kv_v41_encode(kv)
+    kvd = codecs.kv_v41_decode(win, Dh)
+    ck = torch.randn(2, C, Dh)
+    comp = torch.zeros(2, C, comp_row, dtype=torch.uint8)
+    comp[:, :, :Dh // 2 + Dh // 16] = codecs.kv_v41fp4_encode(ck)
+    ckd = codecs.kv_v41fp4_decode(comp, Dh)
+    pos = torch.cat([torch.arange(0, 100), torch.arange(300, 400)]).int()            # short windows, then full ones
+    region = torch.cat([torch.zeros(100), torch.ones(100)]).int()
+    sel = torch.full((T, k), -1, dtype=torch.int32)
+    cnt = torch.zeros(T, dtype=torch.int32)
+    for r in range(T):
+        n = [0, 1, 37, 128, 129, 255, 320][r % 7]
+        sel[r, :n] = torch.sort(torch.randperm(C)[:n]).values.int()
+        cnt[r] = n
+    q = (torch.randn(T, Hl, Dh) * 0.5).bfloat16()
+    sink = torch.randn(Hl) * 0.5
+    freqs = torch.tensor([10000.0 ** (-2.0 * j / 64) for j in range(32)])
+    dev = lambda t: t.to(DEV).contiguous()
+    st = native.StatusWord(DEV)
+    outs = []
+    for tc_on, counts in ((1, None), (1, dev(cnt)), (0, None)):
+        native.lib().tf_sparse_attention_set_tc(tc_on)
+        part_o = torch.zeros(T, 1, Hl, Dh, device=DEV)
+        part_lse = torch.zeros(T, 1, Hl, device=DEV)
+        out = torch.zeros(T, Hl * Dh, device=DEV, dtype=torch.float16)
+        try:
+            native.call("tf_sparse_attention", dev(q), T, Hl, Dh, dev(pos), dev(region), None, dev(win), ring * win_row,
+                        win_row, ring, window, dev(comp), C * comp_row, comp_row, dev(sel), k, counts, C,
+                        1 / math.sqrt(Dh), 1, part_o, part_lse, dev(sink), dev(freqs), 64, out, None, Hl * Dh, st.t)
+            torch.cuda.synchronize()
+        finally:
+            native.lib().tf_sparse_attention_set_tc(1)
+        st.check()
+        outs.append(out.cpu().view(T, Hl, Dh).float())
+    from titanic_flash_41_b200.models.oracle import apply_rope
+    worst = 0.0
+    for r in range(T):
+        p, rg = int(pos[r]), int(region[r])
+        nw = min(p + 1, window)
+        ks = [kvd[rg, (p - nw + 1 + i) % ring] for i in range(nw)]
+        ks += [ckd[rg, int(c)] for c in sel[r] if c >= 0]
+        Kmat = torch.stack(ks)
+        lg = q[r].float() @ Kmat.t() / math.sqrt(Dh)
+        lg = torch.cat([lg, sink[:, None]], 1)
+        P = torch.softmax(lg, -1)[:, :-1]
+        o = apply_rope((P @ Kmat)[None], torch.tensor([p]), freqs, inverse=True)[0]
+        for got in outs:
+            worst = max(worst, _rel(got[r], o))
+    assert worst < 1.5e-2, worst
+    assert _rel(outs[0], outs[2]) < 1e-2 and torch.equal(outs[0], outs[1])
+
+
 def test_sampling_kernels():
     torch.manual_seed(7)
     V, rows = 5000, 4

@@ -49,6 +49,11 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+#include "attention_tc.cuh"     // sparse_attn_tc_kernel: prefill rows on tcgen05 (inside this namespace)
+
+int g_attn_tc = 1;               // tf_sparse_attention_set_tc
+int g_attn_sms = 0;
+
 template <int DH>
 __global__ void __launch_bounds__(128) sparse_attn_kernel(AttnParams p) {
   tf_pdl_sync();
@@ -574,6 +579,14 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 }  // namespace
 
+// 1 (default): prefill rows (one split, head dim 128, 64 rows or more) run on the tcgen05 kernel;
+// 0: always the mma.sync kernels.  Returns the previous setting.
+TF_API int tf_sparse_attention_set_tc(int on) {
+  const int old = g_attn_tc;
+  g_attn_tc = on ? 1 : 0;
+  return old;
+}
+
 TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* pos, const int* region,
                                const int* min_pos,
                                const void* win, long win_region_stride, int win_row, int ring, int window,
@@ -593,7 +606,16 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
   // four warps always: all of them dequantise the key chunk, those that own heads run the MMAs
   const int warps = 4;
   dim3 grid(T, nsplit);
-  if (Dh == 512 || Dh == 256) {
+  if (g_attn_tc && Dh == 128 && nsplit == 1 && T >= 64 && Hl <= 64 && !(reinterpret_cast<uintptr_t>(q) & 15)) {
+    // prefill rows: persistent CTAs on the tcgen05 tensor cores, one query row at a time
+    if (!g_attn_sms) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&g_attn_sms, cudaDevAttrMultiProcessorCount, dev);
+      cudaFuncSetAttribute(sparse_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
+    }
+    tf_launch(sparse_attn_tc_kernel, dim3(T < g_attn_sms ? T : g_attn_sms), dim3(kTcThreads), kTcSmem, st, p);
+  } else if (Dh == 512 || Dh == 256) {
     const int smem = (kChunk * (Dh + 8) + Dh * (kChunk + 8)) * 2 + 4 * 16 * (kChunk + 4) * 4;
     static bool attr_set = false;
     if (!attr_set) {

@@ -1,0 +1,456 @@
+// Sparse attention of prefill rows on the tcgen05 tensor cores (head dim 128, up to 64 heads, one
+// split).  Included by attention.cu inside its anonymous namespace (AttnParams, kNegBig).
+//
+// A persistent CTA takes one query row at a time.  All heads of the row read the same latent keys,
+// so the heads are the M of both contractions (64 real rows of a 128-row MMA; the other 64 rows of
+// the operands are zero) and a chunk of 128 gathered keys is N of the first and K of the second:
+//
+//   S[head, key]  = Q[head, :] . K[key, :]        A = Q  [128 x 128 dims]  B = Kt [128 keys x 128 dims]
+//   O[head, dim] += P[head, key] * K[key, dim]     A = P  [128 x 128 keys]  B = Vt [128 dims x 128 keys]
+//
+// Every operand is K-major bf16 in shared memory with the 128-byte swizzle (two 64-column sub-tiles
+// per operand), S (two buffers) and O live in tensor memory, and a softmax thread owns one head =
+// one TMEM lane: row maxima and sums need no exchange between threads.
+//
+//   warps 0-3   gather: thread t fetches key t of the chunk (FP8 window row or FP4 compressed
+//               row, the next chunk's bytes requested before this chunk is converted), converts it
+//               to bf16 and writes it twice: as a row of Kt and as a column of Vt
+//   warps 4-5   softmax (lanes 0-63 of tensor memory): base-2 online softmax over the chunk, P as
+//               bf16 into shared memory, O rescaled in tensor memory when a maximum moved, the
+//               normalised row written at the end
+//   warp 6      one thread issues the MMAs: QK of chunk c + 1 is issued before PV of chunk c, so the
+//               softmax of a chunk overlaps the next chunk's first contraction
+// Every wait is bounded; on a time-out the CTA raises its abort flag, reports TF_TIMEOUT, frees its
+// tensor memory and returns.
+//
+// Output: the same normalised partials (fp32) and base-2 log-sum-exp the mma.sync kernel writes with
+// one split; attn_merge_kernel adds the sink and the inverse rotation.
+#pragma once
+#include "tc.cuh"
+
+constexpr int kTcKeys = 128;
+constexpr int kTcThreads = 7 * 32;
+constexpr int kTcSub = 16384;                       // one [128 rows x 128 B] sub-tile
+constexpr int kTcQSub = 8192;                       // Q holds 64 rows (the heads): [64 rows x 128 B] sub-tiles, two buffers
+constexpr int kTcStage = 2 * kTcSub;                // the key tile: two 64-dim sub-tiles of [128 keys x 128 B]
+constexpr int kTcStages = 3;                        // key tiles in flight (the gather runs ahead of the MMAs)
+constexpr int kTcSmem = 4 * kTcQSub /*Q x2*/ + 4 * kTcSub /*P x2*/ + kTcStages * kTcStage + 1024 + 256;
+
+// byte offset of (row, byte column) inside a 128-byte-swizzled sub-tile
+__device__ __forceinline__ uint32_t sw128(int row, int colb) {
+  return (uint32_t)(row * 128 + ((((colb >> 4) ^ (row & 7)) << 4) | (colb & 15)));
+}
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t v[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+// MN-major operand (the contiguous direction is M / N, here the 128 dims of a key row) in the same
+// 128-byte-swizzled tile of 128-byte rows: 8 k-rows form a 1,024-byte group (stride offset), the
+// second 64 columns live one sub-tile further (leading offset)
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(kTcSub >> 4) << 16;              // leading byte offset: next 64 columns
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: next 8 k-rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void tmem_st_wait_tc() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ int attn_row_keys(const AttnParams& p, int r, int* nwin_out) {
+  const int pos = p.pos[r];
+  const int nwin = min(pos + 1 - (p.min_pos ? p.min_pos[r] : 0), p.window);
+  int nsel = 0;
+  if (p.comp) {
+    if (p.sel_count) nsel = p.sel_count[r];
+    else {
+      int lo = 0, hi = p.sel_stride;
+      const int* s = p.sel + (long)r * p.sel_stride;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (s[mid] >= 0) lo = mid + 1; else hi = mid;
+      }
+      nsel = lo;
+    }
+  }
+  *nwin_out = nwin;
+  return nwin + nsel;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParams p) {
+  tf_pdl_sync();
+  constexpr int DH = 128;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw0 = tc::smem_u32(smem_raw);
+  const uint32_t base = (raw0 + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - raw0);
+  // Q: two buffers of two 64-row sub-tiles.  The MMA reads 128 rows of A: rows 64..127 of a Q
+  // sub-tile alias the shared memory behind it (finite or not, they only reach accumulator lanes
+  // 64..127, which nobody reads).  P keeps 128 rows with rows 64..127 zero.
+  constexpr int kQBytes = 4 * kTcQSub, kOpBytes = kQBytes + 4 * kTcSub;
+  const uint32_t q_s = base, p_s = base + kQBytes, st_s = base + kOpBytes;
+  uint8_t* q_g = aligned;
+  uint8_t* p_g = aligned + kQBytes;
+  uint8_t* st_g = aligned + kOpBytes;
+  const uint32_t bar0 = base + kOpBytes + kTcStages * kTcStage;
+  auto full = [&](int s) { return bar0 + 8u * s; };              // gather -> MMA            (4 warps)
+  auto empty = [&](int s) { return bar0 + 8u * (4 + s); };       // PV done: stage free        (commit)
+  auto s_ready = [&](int b) { return bar0 + 8u * (8 + b); };     // QK done                    (commit)
+  auto s_free = [&](int b) { return bar0 + 8u * (10 + b); };     // softmax has read S         (2 warps)
+  const uint32_t p_ready = bar0 + 8u * 12;                       // P written, O rescaled      (2 warps)
+  const uint32_t o_ready = bar0 + 8u * 13;                       // PV done                    (commit)
+  const uint32_t row_done = bar0 + 8u * 14;                      // softmax has read O         (2 warps)
+  auto q_ready = [&](int b) { return bar0 + 8u * (15 + b); };    // Q buffer written           (4 warps)
+  auto q_free = [&](int b) { return bar0 + 8u * (17 + b); };     // the row's QK MMAs are done (commit)
+  auto p_free = [&](int b) { return bar0 + 8u * (19 + b); };     // the PV that read P[b] is done (commit)
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kOpBytes + kTcStages * kTcStage + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + kOpBytes + kTcStages * kTcStage + 200);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      tc::mbar_init(full(s), 4);
+      tc::mbar_init(empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      tc::mbar_init(s_ready(s), 1);
+      tc::mbar_init(s_free(s), 2);
+      tc::mbar_init(q_ready(s), 4);
+      tc::mbar_init(q_free(s), 1);
+      tc::mbar_init(p_free(s), 1);
+    }
+    tc::mbar_init(p_ready, 2);
+    tc::mbar_init(o_ready, 1);
+    tc::mbar_init(row_done, 2);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  // Q and P start as zeros: rows 64..127 of P (no heads there) stay zero for the whole launch
+  for (int i = threadIdx.x; i < kOpBytes / 16; i += kTcThreads)
+    reinterpret_cast<uint4*>(q_g)[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (warp == 6) tc::tmem_alloc(tc::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+  tc::fence_proxy_async();
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128u};
+  const uint32_t tO = tmem_base + 256u;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ gather + convert
+    const int tid = threadIdx.x;                    // key of the chunk served by this thread
+    uint4 rawv[8];
+    uint32_t rsc[2];
+    int it = 0, n_row = 0;
+    bool ok = true;
+    for (int r = blockIdx.x; r < p.T && ok; r += gridDim.x, ++n_row) {
+      int nwin;
+      const int nkeys = attn_row_keys(p, r, &nwin);
+      const int nchunks = (nkeys + kTcKeys - 1) / kTcKeys;
+      const int pos = p.pos[r], reg = p.region[r];
+      const uint8_t* win = p.win + (long)reg * p.win_region_stride;
+      const uint8_t* comp = p.comp ? p.comp + (long)reg * p.comp_region_stride : nullptr;
+      auto load_src = [&](int c) -> int {
+        const int i = c * kTcKeys + tid;
+        if (c >= nchunks || i >= nkeys) return 0x7fffffff;
+        if (i < nwin) return (pos - nwin + 1 + i) % p.ring;
+        int id = p.sel[(long)r * p.sel_stride + (i - nwin)];
+        if (id < 0 || id >= p.maxC) {
+          tf_report(p.st, TF_BAD_INDEX, 11, r, id);
+          id = 0;
+        }
+        return ~id;
+      };
+      auto load_raw = [&](int src) {
+        if (src == 0x7fffffff) return;
+        if (src >= 0) {
+          const uint8_t* row = win + (long)src * p.win_row;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + j * 16);
+          rsc[0] = *reinterpret_cast<const uint32_t*>(row + DH);
+        } else {
+          const uint8_t* row = comp + (long)(~src) * p.comp_row;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + j * 16);
+          const uint2 s2 = *reinterpret_cast<const uint2*>(row + DH / 2);
+          rsc[0] = s2.x;
+          rsc[1] = s2.y;
+        }
+      };
+      int src_cur = load_src(0), src_next = load_src(1);
+      load_raw(src_cur);
+      // Q of this row into buffer n_row & 1: free once the QK MMAs of the row before last are done
+      const int qb = n_row & 1;
+      if (!(ok = tc::mbar_wait(q_free(qb), ((n_row >> 1) & 1) ^ 1, abort_flag))) break;
+      {
+        // 64 heads x 128 dims bf16 = 1,024 16-byte pieces over 128 threads
+        const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + (long)r * p.Hl * DH);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int piece = tid + 128 * j;
+          const int h = piece >> 4, c16 = piece & 15;           // 16 pieces per head row
+          uint4 v = h < p.Hl ? qsrc[piece] : make_uint4(0u, 0u, 0u, 0u);
+          uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {                          // bf16 pair -> f16 pair (exact in range)
+            const float2 f2 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&vw[e]));
+            vw[e] = pack_h2(f2.x, f2.y);
+          }
+          *reinterpret_cast<uint4*>(q_g + (qb * 2 + (c16 >> 3)) * kTcQSub + sw128(h, (c16 & 7) * 16)) = v;
+        }
+        tc::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(q_ready(qb));
+      }
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const int s = it % kTcStages;
+        if (!(ok = tc::mbar_wait(empty(s), ((it / kTcStages) & 1) ^ 1, abort_flag))) break;
+        uint8_t* kt = st_g + s * kTcStage;
+        // The key row as f16 (what a latent value times its scale is exactly: at most five mantissa
+        // bits for FP4 rows, four for FP8 rows), sixteen values = one 32-byte piece at a time.  One
+        // branch per row kind, not per piece: the FP4 body (all but the window rows) stays small.
+        auto put = [&](int seg, const uint32_t (&hv)[8]) {
+          const int d0 = seg * 16;
+          uint8_t* ksub = kt + (d0 >> 6) * kTcSub;
+          *reinterpret_cast<uint4*>(ksub + sw128(tid, (d0 & 63) * 2)) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+          *reinterpret_cast<uint4*>(ksub + sw128(tid, (d0 & 63) * 2 + 16)) = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+        };
+        if (src_cur == 0x7fffffff) {
+          const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+          for (int seg = 0; seg < 8; ++seg) put(seg, z);
+        } else if (src_cur >= 0) {
+#pragma unroll
+          for (int seg = 0; seg < 8; ++seg) {
+            uint32_t hv[8];
+            const float sc = ue8m0_to_float((rsc[0] >> (8 * (seg >> 1))) & 0xffu);
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(&rawv[seg]);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              uint32_t h2 = e4m3x2_to_h2(h[q]);
+              const float2 v = __half22float2(*reinterpret_cast<__half2*>(&h2));
+              hv[q] = pack_h2(v.x * sc, v.y * sc);
+            }
+            put(seg, hv);
+          }
+        } else {
+          // the unpacked halves hold value * 2^-14; two packed f16 multiplies (by 2^14, exact, then by
+          // the group's e4m3 scale, exact) instead of a trip through fp32 and back
+          const __half2 k14 = __floats2half2_rn(16384.f, 16384.f);
+#pragma unroll
+          for (int seg = 0; seg < 8; ++seg) {
+            uint32_t hv[8];
+            const uint32_t sb = (rsc[seg >> 2] >> (8 * (seg & 3))) & 0xffu;
+            const uint32_t sh = e4m3x2_to_h2((uint16_t)(sb | (sb << 8)));
+            const __half2 sc2 = *reinterpret_cast<const __half2*>(&sh);
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&rawv[seg >> 1]) + 2 * (seg & 1);
+            e2m1x8_to_h2x4_scaled(w[0], hv);
+            e2m1x8_to_h2x4_scaled(w[1], hv + 4);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const __half2 x = __hmul2(__hmul2(*reinterpret_cast<__half2*>(&hv[q]), k14), sc2);
+              hv[q] = *reinterpret_cast<const uint32_t*>(&x);
+            }
+            put(seg, hv);
+          }
+        }
+        // request the next chunk's rows and the ids of the chunk after it, then hand the stage over
+        src_cur = src_next;
+        load_raw(src_cur);
+        src_next = load_src(c + 2);
+        tc::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(full(s));
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, 128);      // f16 x f16, M 128, N 128, both K-major
+      constexpr uint32_t idesc_pv = idesc | (1u << 16);               // B (the key tile as V) MN-major
+      int it = 0, n_row = 0;
+      bool ok = true;
+      auto qk = [&](int i, int qb) -> bool {                         // S[i & 1] = Q[qb] . Kt(stage i & 1)^T
+        const int s = i & 1, stg = i % kTcStages;
+        if (!tc::mbar_wait(full(stg), (i / kTcStages) & 1, abort_flag)) return false;
+        if (!tc::mbar_wait(s_free(s), ((i >> 1) & 1) ^ 1, abort_flag)) return false;
+        tc::tc_fence_after();
+        const uint32_t kt = st_s + stg * kTcStage;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc::mma_f16(tS[s], tc::smem_desc_sw128(q_s + (qb * 2 + j) * kTcQSub) + 2 * k,
+                        tc::smem_desc_sw128(kt + j * kTcSub) + 2 * k, idesc, (j | k) ? 1u : 0u);
+        tc::mma_commit(s_ready(s));
+        return true;
+      };
+      for (int r = blockIdx.x; r < p.T && ok; r += gridDim.x, ++n_row) {
+        int nwin;
+        const int nkeys = attn_row_keys(p, r, &nwin);
+        const int nchunks = (nkeys + kTcKeys - 1) / kTcKeys;
+        const int qb = n_row & 1;
+        if (!(ok = tc::mbar_wait(q_ready(qb), (n_row >> 1) & 1, abort_flag))) break;
+        if (!(ok = qk(it, qb))) break;
+        if (nchunks == 1) tc::mma_commit(q_free(qb));
+        for (int c = 0; c < nchunks; ++c, ++it) {
+          if (c + 1 < nchunks) {
+            if (!(ok = qk(it + 1, qb))) break;
+            if (c + 2 == nchunks) tc::mma_commit(q_free(qb));      // the row's last QK is issued
+          }
+          if (!(ok = tc::mbar_wait(p_ready, it & 1, abort_flag))) break;
+          // the first PV of a row overwrites O: the previous row's result must have been read
+          if (c == 0 && !(ok = tc::mbar_wait(row_done, (n_row & 1) ^ 1, abort_flag))) break;
+          tc::tc_fence_after();
+          // B = the same key tile read MN-major (dims contiguous): 16 keys per step = 2,048 bytes
+          const uint32_t kt = st_s + (it % kTcStages) * kTcStage;
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc::mma_f16(tO, tc::smem_desc_sw128(p_s + ((it & 1) * 2 + j) * kTcSub) + 2 * k, smem_desc_sw128_mn(kt) + 128u * (4 * j + k),
+                          idesc_pv, (c | j | k) ? 1u : 0u);
+          tc::mma_commit(empty(it % kTcStages));
+          tc::mma_commit(p_free(it & 1));
+          tc::mma_commit(o_ready);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax (thread = head)
+    const int h = (warp - 4) * 32 + lane;
+    const uint32_t lane_off = (uint32_t)((warp - 4) * 32) << 16;
+    int it = 0, n_row = 0;
+    bool ok = true;
+    for (int r = blockIdx.x; r < p.T && ok; r += gridDim.x, ++n_row) {
+      int nwin;
+      const int nkeys = attn_row_keys(p, r, &nwin);
+      const int nchunks = (nkeys + kTcKeys - 1) / kTcKeys;
+      float m = kNegBig, l = 0.f;
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const int sb = it & 1;
+        const int valid = nkeys - c * kTcKeys;                       // columns >= valid are padding
+        if (!(ok = tc::mbar_wait(s_ready(sb), (it >> 1) & 1, abort_flag))) break;
+        tc::tc_fence_after();
+        // The reference maximum m is the first chunk's; it moves only when some head of the warp finds
+        // a score more than 2^8 above it (then O is rescaled, which has to wait for the PV before, and
+        // the chunk is exponentiated again).  Until then exp2(s - m) <= 256 is harmless in f16 / fp32,
+        // the ratio O / l does not depend on m, and one short loop over four pieces of 32 scores
+        // does everything (small code: the instruction cache, not the arithmetic, was the limit).
+        if (c == 0) {
+          float cm = kNegBig;
+#pragma unroll 1
+          for (int q = 0; q < 4; ++q) {
+            uint32_t v[32];
+            tc::tmem_ld32(tS[sb] + lane_off + q * 32, v);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (q * 32 + i < valid) cm = fmaxf(cm, __uint_as_float(v[i]) * p.scale_log2);
+          }
+          m = cm;
+        }
+        // the PV that read this P buffer two chunks ago is done
+        if (!(ok = tc::mbar_wait(p_free(it & 1), ((it >> 1) & 1) ^ 1, abort_flag))) break;
+        for (;;) {
+          float cm = kNegBig, ls = 0.f;
+#pragma unroll 1
+          for (int q = 0; q < 4; ++q) {
+            uint32_t v[32];
+            tc::tmem_ld32(tS[sb] + lane_off + q * 32, v);
+            tc::tmem_ld_wait();
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float x0 = (q * 32 + 2 * i < valid) ? __uint_as_float(v[2 * i]) * p.scale_log2 : kNegBig;
+              const float x1 = (q * 32 + 2 * i + 1 < valid) ? __uint_as_float(v[2 * i + 1]) * p.scale_log2 : kNegBig;
+              cm = fmaxf(cm, fmaxf(x0, x1));
+              const float a = exp2f(x0 - m), b = exp2f(x1 - m);
+              ls += a + b;
+              pk[i] = pack_h2(a, b);
+            }
+            // 32 keys = 64 bytes = four 16-byte pieces of row h in sub-tile q / 2 of this P buffer
+            uint8_t* psub = p_g + ((it & 1) * 2 + (q >> 1)) * kTcSub;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(psub + sw128(h, (q & 1) * 64 + i * 16)) =
+                  make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+          }
+          if (!__any_sync(0xffffffffu, cm > m + 8.f)) {
+            l += ls;
+            break;
+          }
+          // rare: move the maximum, rescale O and l, exponentiate the chunk again
+          const float nm = fmaxf(m, cm);
+          const float f = exp2f(m - nm);
+          m = nm;
+          l *= f;
+          if (c > 0) {
+            if (!(ok = tc::mbar_wait(o_ready, (it & 1) ^ 1, abort_flag))) break;
+            tc::tc_fence_after();
+#pragma unroll 1
+            for (int q = 0; q < 4; ++q) {
+              uint32_t o[32];
+              tc::tmem_ld32(tO + lane_off + q * 32, o);
+              tc::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+              tmem_st32(tO + lane_off + q * 32, o);
+            }
+            tmem_st_wait_tc();
+          }
+        }
+        if (!ok) break;
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(s_free(sb));
+        tc::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(p_ready);
+      }
+      if (!ok) break;
+      // ---- the row's result: wait for the last PV, normalise, write the partial
+      if (!(ok = tc::mbar_wait(o_ready, (it & 1) ^ 1, abort_flag))) break;
+      tc::tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float* po = p.part_o + ((long)r * p.Hl + h) * DH;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t v[32];
+        tc::tmem_ld32(tO + lane_off + q * 32, v);
+        tc::tmem_ld_wait();
+        if (h < p.Hl) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(po + q * 32 + 4 * i) =
+                make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
+                            __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+        }
+      }
+      if (h < p.Hl) p.part_lse[(long)r * p.Hl + h] = l > 0.f ? m + log2f(l) : kNegBig;
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(row_done);
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) tf_report(p.st, TF_TIMEOUT, 150, blockIdx.x, 0);
+  if (warp == 6) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, 512);
+  }
+}
