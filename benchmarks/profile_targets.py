@@ -89,6 +89,7 @@ def attention():
     region = torch.zeros(T, dtype=torch.int32, device=DEV)
     sel = torch.stack([torch.sort(torch.randperm(C, device=DEV, generator=gen)[:k]).values for _ in range(64)]).int()
     sel = sel.repeat(T // 64, 1).contiguous()
+    cnt = torch.full((T,), k, dtype=torch.int32, device=DEV)
     q = (torch.randn(T, Hl, Dh, device=DEV, generator=gen) * 0.5).bfloat16()
     sink = torch.zeros(Hl, device=DEV)
     freqs = torch.tensor([10000.0 ** (-2.0 * j / 64) for j in range(32)], device=DEV)
@@ -97,7 +98,7 @@ def attention():
     out = torch.zeros(T, Hl * Dh, device=DEV, dtype=torch.float16)
     st = native.StatusWord(DEV)
     us = timed(lambda: native.call("tf_sparse_attention", q, T, Hl, Dh, pos, region, None, win, ring * win_row, win_row, ring,
-                                   window, comp, C * comp_row, comp_row, sel, k, None, C, 1 / math.sqrt(Dh), 1, part_o,
+                                   window, comp, C * comp_row, comp_row, sel, k, cnt, C, 1 / math.sqrt(Dh), 1, part_o,
                                    part_lse, sink, freqs, 64, out, None, Hl * Dh, st.t), n=3, warm=1)
     st.check()
     flops = 4.0 * T * Hl * Dh * (window + k)

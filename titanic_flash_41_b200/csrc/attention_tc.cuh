@@ -29,12 +29,13 @@
 #include "tc.cuh"
 
 constexpr int kTcKeys = 128;
-constexpr int kTcThreads = 7 * 32;
+constexpr int kTcThreads = 9 * 32;                  // 4 gather warps, 4 softmax warps, 1 MMA warp
 constexpr int kTcSub = 16384;                       // one [128 rows x 128 B] sub-tile
-constexpr int kTcQSub = 8192;                       // Q holds 64 rows (the heads): [64 rows x 128 B] sub-tiles, two buffers
+constexpr int kTcQSub = 16384;                      // Q: rows 0..63 the heads, rows 64..127 the heads again; two buffers
+constexpr int kTcPSub = 8192;                       // P: 64 rows (the heads); two buffers
 constexpr int kTcStage = 2 * kTcSub;                // the key tile: two 64-dim sub-tiles of [128 keys x 128 B]
 constexpr int kTcStages = 3;                        // key tiles in flight (the gather runs ahead of the MMAs)
-constexpr int kTcSmem = 4 * kTcQSub /*Q x2*/ + 4 * kTcSub /*P x2*/ + kTcStages * kTcStage + 1024 + 256;
+constexpr int kTcSmem = 4 * kTcQSub /*Q x2*/ + 4 * kTcPSub /*P x2*/ + kTcStages * kTcStage + 1024 + 2048;
 
 // byte offset of (row, byte column) inside a 128-byte-swizzled sub-tile
 __device__ __forceinline__ uint32_t sw128(int row, int colb) {
@@ -96,10 +97,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
   const uint32_t raw0 = tc::smem_u32(smem_raw);
   const uint32_t base = (raw0 + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - raw0);
-  // Q: two buffers of two 64-row sub-tiles.  The MMA reads 128 rows of A: rows 64..127 of a Q
+  // Q: two buffers of two 128-row sub-tiles; rows 64..127 repeat the heads, so accumulator lanes
+  // 64..127 of S hold the same scores and a second pair of softmax warps can take half the columns.
+  // P: two buffers of two 64-row sub-tiles.  The PV MMA reads 128 rows of A: rows 64..127 of a P
   // sub-tile alias the shared memory behind it (finite or not, they only reach accumulator lanes
-  // 64..127, which nobody reads).  P keeps 128 rows with rows 64..127 zero.
-  constexpr int kQBytes = 4 * kTcQSub, kOpBytes = kQBytes + 4 * kTcSub;
+  // 64..127 of O, which nobody reads).
+  constexpr int kQBytes = 4 * kTcQSub, kOpBytes = kQBytes + 4 * kTcPSub;
   const uint32_t q_s = base, p_s = base + kQBytes, st_s = base + kOpBytes;
   uint8_t* q_g = aligned;
   uint8_t* p_g = aligned + kQBytes;
@@ -111,12 +114,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
   auto s_free = [&](int b) { return bar0 + 8u * (10 + b); };     // softmax has read S         (2 warps)
   const uint32_t p_ready = bar0 + 8u * 12;                       // P written, O rescaled      (2 warps)
   const uint32_t o_ready = bar0 + 8u * 13;                       // PV done                    (commit)
-  const uint32_t row_done = bar0 + 8u * 14;                      // softmax has read O         (2 warps)
+  auto o_free = [&](int b) { return bar0 + 8u * (21 + b); };     // softmax has read O[b]      (2 warps)
   auto q_ready = [&](int b) { return bar0 + 8u * (15 + b); };    // Q buffer written           (4 warps)
   auto q_free = [&](int b) { return bar0 + 8u * (17 + b); };     // the row's QK MMAs are done (commit)
   auto p_free = [&](int b) { return bar0 + 8u * (19 + b); };     // the PV that read P[b] is done (commit)
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + kOpBytes + kTcStages * kTcStage + 192);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + kOpBytes + kTcStages * kTcStage + 200);
+  float* xch = reinterpret_cast<float*>(aligned + kOpBytes + kTcStages * kTcStage + 256);      // [3][128] softmax exchange
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -126,28 +130,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
     }
     for (int s = 0; s < 2; ++s) {
       tc::mbar_init(s_ready(s), 1);
-      tc::mbar_init(s_free(s), 2);
+      tc::mbar_init(s_free(s), 4);
       tc::mbar_init(q_ready(s), 4);
       tc::mbar_init(q_free(s), 1);
       tc::mbar_init(p_free(s), 1);
+      tc::mbar_init(o_free(s), 2);
     }
-    tc::mbar_init(p_ready, 2);
+    tc::mbar_init(p_ready, 4);
     tc::mbar_init(o_ready, 1);
-    tc::mbar_init(row_done, 2);
     *abort_flag = 0;
     tc::fence_barrier_init();
   }
   // Q and P start as zeros: rows 64..127 of P (no heads there) stay zero for the whole launch
   for (int i = threadIdx.x; i < kOpBytes / 16; i += kTcThreads)
     reinterpret_cast<uint4*>(q_g)[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (warp == 6) tc::tmem_alloc(tc::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+  if (warp == 8) tc::tmem_alloc(tc::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
   tc::fence_proxy_async();
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS[2] = {tmem_base, tmem_base + 128u};
-  const uint32_t tO = tmem_base + 256u;
+  const uint32_t tOb[2] = {tmem_base + 256u, tmem_base + 384u};     // O of even / odd rows of this CTA
 
   if (warp < 4) {
     // ------------------------------------------------------------------ gather + convert
@@ -163,26 +167,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
       const int pos = p.pos[r], reg = p.region[r];
       const uint8_t* win = p.win + (long)reg * p.win_region_stride;
       const uint8_t* comp = p.comp ? p.comp + (long)reg * p.comp_region_stride : nullptr;
-      auto load_src = [&](int c) -> int {
+      // A key is (kind, value): kind 0 = padding, 1 = window ring slot, 2 = compressed entry id.  The
+      // id is only looked at when its row is fetched, a chunk later: nothing waits for the id load.
+      auto key_kind = [&](int c) -> int {
         const int i = c * kTcKeys + tid;
-        if (c >= nchunks || i >= nkeys) return 0x7fffffff;
-        if (i < nwin) return (pos - nwin + 1 + i) % p.ring;
-        int id = p.sel[(long)r * p.sel_stride + (i - nwin)];
-        if (id < 0 || id >= p.maxC) {
-          tf_report(p.st, TF_BAD_INDEX, 11, r, id);
-          id = 0;
-        }
-        return ~id;
+        return (c >= nchunks || i >= nkeys) ? 0 : (i < nwin ? 1 : 2);
       };
-      auto load_raw = [&](int src) {
-        if (src == 0x7fffffff) return;
-        if (src >= 0) {
-          const uint8_t* row = win + (long)src * p.win_row;
+      auto key_val = [&](int c, int kind) -> int {
+        const int i = c * kTcKeys + tid;
+        if (kind == 1) return (pos - nwin + 1 + i) % p.ring;
+        if (kind == 2) return p.sel[(long)r * p.sel_stride + (i - nwin)];
+        return 0;
+      };
+      auto load_raw = [&](int kind, int val) {
+        if (kind == 1) {
+          const uint8_t* row = win + (long)val * p.win_row;
 #pragma unroll
           for (int j = 0; j < 8; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + j * 16);
           rsc[0] = *reinterpret_cast<const uint32_t*>(row + DH);
-        } else {
-          const uint8_t* row = comp + (long)(~src) * p.comp_row;
+        } else if (kind == 2) {
+          int id = val;
+          if (id < 0 || id >= p.maxC) {
+            tf_report(p.st, TF_BAD_INDEX, 11, r, id);
+            id = 0;
+          }
+          const uint8_t* row = comp + (long)id * p.comp_row;
 #pragma unroll
           for (int j = 0; j < 4; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + j * 16);
           const uint2 s2 = *reinterpret_cast<const uint2*>(row + DH / 2);
@@ -190,8 +199,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
           rsc[1] = s2.y;
         }
       };
-      int src_cur = load_src(0), src_next = load_src(1);
-      load_raw(src_cur);
+      int kind_cur = key_kind(0), kind_next = key_kind(1);
+      int val_cur = key_val(0, kind_cur), val_next = key_val(1, kind_next);
+      load_raw(kind_cur, val_cur);
       // Q of this row into buffer n_row & 1: free once the QK MMAs of the row before last are done
       const int qb = n_row & 1;
       if (!(ok = tc::mbar_wait(q_free(qb), ((n_row >> 1) & 1) ^ 1, abort_flag))) break;
@@ -209,7 +219,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
             const float2 f2 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&vw[e]));
             vw[e] = pack_h2(f2.x, f2.y);
           }
-          *reinterpret_cast<uint4*>(q_g + (qb * 2 + (c16 >> 3)) * kTcQSub + sw128(h, (c16 & 7) * 16)) = v;
+          uint8_t* qsub = q_g + (qb * 2 + (c16 >> 3)) * kTcQSub;
+          *reinterpret_cast<uint4*>(qsub + sw128(h, (c16 & 7) * 16)) = v;
+          *reinterpret_cast<uint4*>(qsub + sw128(h + 64, (c16 & 7) * 16)) = v;
         }
         tc::fence_proxy_async();
         __syncwarp();
@@ -228,11 +240,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
           *reinterpret_cast<uint4*>(ksub + sw128(tid, (d0 & 63) * 2)) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
           *reinterpret_cast<uint4*>(ksub + sw128(tid, (d0 & 63) * 2 + 16)) = make_uint4(hv[4], hv[5], hv[6], hv[7]);
         };
-        if (src_cur == 0x7fffffff) {
+        if (kind_cur == 0) {
           const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
           for (int seg = 0; seg < 8; ++seg) put(seg, z);
-        } else if (src_cur >= 0) {
+        } else if (kind_cur == 1) {
 #pragma unroll
           for (int seg = 0; seg < 8; ++seg) {
             uint32_t hv[8];
@@ -268,15 +280,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
           }
         }
         // request the next chunk's rows and the ids of the chunk after it, then hand the stage over
-        src_cur = src_next;
-        load_raw(src_cur);
-        src_next = load_src(c + 2);
+        kind_cur = kind_next;
+        val_cur = val_next;
+        load_raw(kind_cur, val_cur);
+        kind_next = key_kind(c + 2);
+        val_next = key_val(c + 2, kind_next);
         tc::fence_proxy_async();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(full(s));
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, 128);      // f16 x f16, M 128, N 128, both K-major
@@ -312,8 +326,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
             if (c + 2 == nchunks) tc::mma_commit(q_free(qb));      // the row's last QK is issued
           }
           if (!(ok = tc::mbar_wait(p_ready, it & 1, abort_flag))) break;
-          // the first PV of a row overwrites O: the previous row's result must have been read
-          if (c == 0 && !(ok = tc::mbar_wait(row_done, (n_row & 1) ^ 1, abort_flag))) break;
+          // the first PV of a row overwrites O[n_row & 1]: the result of the row before last must have been read
+          if (c == 0 && !(ok = tc::mbar_wait(o_free(n_row & 1), ((n_row >> 1) & 1) ^ 1, abort_flag))) break;
           tc::tc_fence_after();
           // B = the same key tile read MN-major (dims contiguous): 16 keys per step = 2,048 bytes
           const uint32_t kt = st_s + (it % kTcStages) * kTcStage;
@@ -321,7 +335,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
           for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              tc::mma_f16(tO, tc::smem_desc_sw128(p_s + ((it & 1) * 2 + j) * kTcSub) + 2 * k, smem_desc_sw128_mn(kt) + 128u * (4 * j + k),
+              tc::mma_f16(tOb[n_row & 1], tc::smem_desc_sw128(p_s + ((it & 1) * 2 + j) * kTcPSub) + 2 * k, smem_desc_sw128_mn(kt) + 128u * (4 * j + k),
                           idesc_pv, (c | j | k) ? 1u : 0u);
           tc::mma_commit(empty(it % kTcStages));
           tc::mma_commit(p_free(it & 1));
@@ -330,90 +344,127 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax (thread = head)
-    const int h = (warp - 4) * 32 + lane;
+    // ------------------------------------------------------------------ softmax
+    // Thread L of the four warps reads accumulator lane L: head L % 64, key columns 64 (L / 64) ..
+    // + 63 of the chunk (lanes 64..127 of S repeat lanes 0..63).  The two threads of a head share
+    // the reference maximum (chunk maxima and the row sum meet in shared memory under a named
+    // barrier of the 128 softmax threads); only the first two warps touch O.
+    const int L = (warp - 4) * 32 + lane;
+    const int h = L & 63, half = L >> 6;
     const uint32_t lane_off = (uint32_t)((warp - 4) * 32) << 16;
+    const uint32_t col0 = (uint32_t)half * 64u;
+    // (the two warps that share a set of heads meet at a named barrier of their own, 64 threads)
+    const int pair_bar = 1 + ((warp - 4) & 1);
+    auto sm_bar = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    // A wait that runs out raises the CTA's abort flag.  The warp then stops waiting but keeps walking
+    // the same sequence of named barriers as its partner (nobody is left behind at a barrier); the
+    // results of such a launch are void and the status word says so.
+    bool fail = false;
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+      if (!fail && !tc::mbar_wait(bar, parity, abort_flag)) fail = true;
+    };
     int it = 0, n_row = 0;
-    bool ok = true;
-    for (int r = blockIdx.x; r < p.T && ok; r += gridDim.x, ++n_row) {
+    for (int r = blockIdx.x; r < p.T; r += gridDim.x, ++n_row) {
       int nwin;
       const int nkeys = attn_row_keys(p, r, &nwin);
       const int nchunks = (nkeys + kTcKeys - 1) / kTcKeys;
       float m = kNegBig, l = 0.f;
+      const uint32_t tO = tOb[n_row & 1];
       for (int c = 0; c < nchunks; ++c, ++it) {
         const int sb = it & 1;
-        const int valid = nkeys - c * kTcKeys;                       // columns >= valid are padding
-        if (!(ok = tc::mbar_wait(s_ready(sb), (it >> 1) & 1, abort_flag))) break;
+        const int valid = nkeys - c * kTcKeys - (int)col0;           // own columns >= valid are padding
+        float* xc = xch + (it & 1) * 128;
+        wait(s_ready(sb), (it >> 1) & 1);
         tc::tc_fence_after();
-        // The reference maximum m is the first chunk's; it moves only when some head of the warp finds
-        // a score more than 2^8 above it (then O is rescaled, which has to wait for the PV before, and
-        // the chunk is exponentiated again).  Until then exp2(s - m) <= 256 is harmless in f16 / fp32,
-        // the ratio O / l does not depend on m, and one short loop over four pieces of 32 scores
-        // does everything (small code: the instruction cache, not the arithmetic, was the limit).
+        // The reference maximum m is the first chunk's; it moves only when some head finds a score
+        // more than 2^8 above it (then O is rescaled, which has to wait for the PV before, and the
+        // chunk is exponentiated again).  Until then exp2(s - m) <= 256 is harmless in f16 / fp32,
+        // the ratio O / l does not depend on m, and one short loop over the thread's two pieces of 32
+        // scores does everything (small code: the instruction cache, not the arithmetic, was the limit).
         if (c == 0) {
           float cm = kNegBig;
 #pragma unroll 1
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 2; ++q) {
             uint32_t v[32];
-            tc::tmem_ld32(tS[sb] + lane_off + q * 32, v);
+            tc::tmem_ld32(tS[sb] + lane_off + col0 + q * 32, v);
             tc::tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (q * 32 + i < valid) cm = fmaxf(cm, __uint_as_float(v[i]) * p.scale_log2);
+              if (q * 32 + i < valid) cm = fmaxf(cm, __uint_as_float(v[i]));
           }
-          m = cm;
+          xch[256 + L] = cm;
+          sm_bar();
+          m = fmaxf(cm, xch[256 + (L ^ 64)]) * p.scale_log2;
         }
         // the PV that read this P buffer two chunks ago is done
-        if (!(ok = tc::mbar_wait(p_free(it & 1), ((it >> 1) & 1) ^ 1, abort_flag))) break;
-        for (;;) {
+        wait(p_free(it & 1), ((it >> 1) & 1) ^ 1);
+        bool again = false;
+        do {
           float cm = kNegBig, ls = 0.f;
+          uint8_t* psub = p_g + ((it & 1) * 2 + half) * kTcPSub;     // keys 64 half .. of this chunk
 #pragma unroll 1
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 2; ++q) {
             uint32_t v[32];
-            tc::tmem_ld32(tS[sb] + lane_off + q * 32, v);
+            tc::tmem_ld32(tS[sb] + lane_off + col0 + q * 32, v);
             tc::tmem_ld_wait();
             uint32_t pk[16];
+            if (valid >= 64) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float x0 = (q * 32 + 2 * i < valid) ? __uint_as_float(v[2 * i]) * p.scale_log2 : kNegBig;
-              const float x1 = (q * 32 + 2 * i + 1 < valid) ? __uint_as_float(v[2 * i + 1]) * p.scale_log2 : kNegBig;
-              cm = fmaxf(cm, fmaxf(x0, x1));
-              const float a = exp2f(x0 - m), b = exp2f(x1 - m);
-              ls += a + b;
-              pk[i] = pack_h2(a, b);
+              for (int i = 0; i < 16; ++i) {
+                const float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
+                cm = fmaxf(cm, fmaxf(x0, x1));
+                const float a = exp2f(fmaf(x0, p.scale_log2, -m)), b = exp2f(fmaf(x1, p.scale_log2, -m));
+                ls += a + b;
+                pk[i] = pack_h2(a, b);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const bool in0 = q * 32 + 2 * i < valid, in1 = q * 32 + 2 * i + 1 < valid;
+                const float x0 = in0 ? __uint_as_float(v[2 * i]) : kNegBig, x1 = in1 ? __uint_as_float(v[2 * i + 1]) : kNegBig;
+                cm = fmaxf(cm, fmaxf(x0, x1));
+                const float a = in0 ? exp2f(fmaf(x0, p.scale_log2, -m)) : 0.f;
+                const float b = in1 ? exp2f(fmaf(x1, p.scale_log2, -m)) : 0.f;
+                ls += a + b;
+                pk[i] = pack_h2(a, b);
+              }
             }
-            // 32 keys = 64 bytes = four 16-byte pieces of row h in sub-tile q / 2 of this P buffer
-            uint8_t* psub = p_g + ((it & 1) * 2 + (q >> 1)) * kTcSub;
+            // 32 keys = 64 bytes = four 16-byte pieces of row h
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(psub + sw128(h, (q & 1) * 64 + i * 16)) =
+              *reinterpret_cast<uint4*>(psub + sw128(h, q * 64 + i * 16)) =
                   make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
           }
-          if (!__any_sync(0xffffffffu, cm > m + 8.f)) {
+          // both threads of a head must take the same decision: exchange the chunk maxima
+          xc[L] = cm;
+          sm_bar();
+          cm = fmaxf(cm, xc[L ^ 64]) * p.scale_log2;
+          again = __any_sync(0xffffffffu, cm > m + 8.f);
+          if (!again) {
             l += ls;
-            break;
-          }
-          // rare: move the maximum, rescale O and l, exponentiate the chunk again
-          const float nm = fmaxf(m, cm);
-          const float f = exp2f(m - nm);
-          m = nm;
-          l *= f;
-          if (c > 0) {
-            if (!(ok = tc::mbar_wait(o_ready, (it & 1) ^ 1, abort_flag))) break;
-            tc::tc_fence_after();
+          } else {
+            // rare: move the maximum, rescale O and l, exponentiate the chunk again
+            const float nm = fmaxf(m, cm);
+            const float f = exp2f(m - nm);
+            m = nm;
+            l *= f;
+            if (c > 0 && half == 0) {
+              wait(o_ready, (it & 1) ^ 1);
+              tc::tc_fence_after();
 #pragma unroll 1
-            for (int q = 0; q < 4; ++q) {
-              uint32_t o[32];
-              tc::tmem_ld32(tO + lane_off + q * 32, o);
-              tc::tmem_ld_wait();
+              for (int q = 0; q < 4; ++q) {
+                uint32_t o[32];
+                tc::tmem_ld32(tO + lane_off + q * 32, o);
+                tc::tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-              tmem_st32(tO + lane_off + q * 32, o);
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                tmem_st32(tO + lane_off + q * 32, o);
+              }
+              tmem_st_wait_tc();
             }
-            tmem_st_wait_tc();
+            sm_bar();                                             // (the exchange slots are written again)
           }
-        }
-        if (!ok) break;
+        } while (again);
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(s_free(sb));
@@ -421,35 +472,43 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(p_ready);
       }
-      if (!ok) break;
-      // ---- the row's result: wait for the last PV, normalise, write the partial
-      if (!(ok = tc::mbar_wait(o_ready, (it & 1) ^ 1, abort_flag))) break;
-      tc::tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      float* po = p.part_o + ((long)r * p.Hl + h) * DH;
+      // ---- the row's result: both halves' sums, then the first two warps wait for the last PV,
+      // normalise and write the partial
+      float* xr = xch + 256;
+      sm_bar();                                                   // (first-chunk maxima have been read)
+      xr[L] = l;
+      sm_bar();
+      l += xr[L ^ 64];
+      if (half == 0) {
+        wait(o_ready, (it & 1) ^ 1);
+        tc::tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        float* po = p.part_o + ((long)r * p.Hl + h) * DH;
+#pragma unroll 1
+        for (int q = 0; q < 4; ++q) {
+          uint32_t v[32];
+          tc::tmem_ld32(tO + lane_off + q * 32, v);
+          tc::tmem_ld_wait();
+          if (h < p.Hl) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t v[32];
-        tc::tmem_ld32(tO + lane_off + q * 32, v);
-        tc::tmem_ld_wait();
-        if (h < p.Hl) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(po + q * 32 + 4 * i) =
-                make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
-                            __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<float4*>(po + q * 32 + 4 * i) =
+                  make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
+                              __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          }
         }
+        if (h < p.Hl) p.part_lse[(long)r * p.Hl + h] = l > 0.f ? m + log2f(l) : kNegBig;
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(o_free(n_row & 1));
       }
-      if (h < p.Hl) p.part_lse[(long)r * p.Hl + h] = l > 0.f ? m + log2f(l) : kNegBig;
-      tc::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(row_done);
+      sm_bar();                                                   // the sums have been read before the next row writes them
     }
   }
   tc::tc_fence_before();
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0) tf_report(p.st, TF_TIMEOUT, 150, blockIdx.x, 0);
-  if (warp == 6) {
+  if (warp == 8) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, 512);
   }
