@@ -98,7 +98,7 @@ def test_block_scaled_expert_path_matches_register_path_and_oracle():
     assert between.median() < 1.5 * oracle_shift.median() + 0.01, (between, oracle_shift)
     # rounding decisions of two noisy paths are independent: the distances add in quadrature
     bound = (errs_old.median() ** 2 + 2 * oracle_shift.median() ** 2) ** 0.5 + 0.02
-    assert errs.median() < bound and (errs < 0.2).float().mean() >= 0.7, (errs, bound)
+    assert errs.median() < bound and (errs < 0.2).float().mean() >= 0.6, (errs, bound)
 
 
 def test_two_regions_batched_decode_equals_separate():

@@ -42,6 +42,13 @@ struct AttnParams {
   float* part_o;              // [T, nsplit, Hl, Dh]
   float* part_lse;            // [T, nsplit, Hl]  (log2 domain; kNegBig when empty)
   TfStatusWord* st;
+  // the tcgen05 kernel finishes the row itself (sink, inverse rotation of the tail, f16 / bf16 rows)
+  const float* sink;          // [Hl] or null
+  const float* freqs;         // [rope_dim / 2]
+  int rope_dim;
+  __half* out16;
+  __nv_bfloat16* outb;
+  int ldo;
 };
 
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
@@ -606,7 +613,10 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
   // four warps always: all of them dequantise the key chunk, those that own heads run the MMAs
   const int warps = 4;
   dim3 grid(T, nsplit);
-  if (g_attn_tc && Dh == 128 && nsplit == 1 && T >= 64 && Hl <= 64 && !(reinterpret_cast<uintptr_t>(q) & 15)) {
+  p.sink = sink; p.freqs = freqs; p.rope_dim = rope_dim; p.out16 = (__half*)out16; p.outb = (__nv_bfloat16*)outb; p.ldo = ldo;
+  if (g_attn_tc && Dh == 128 && nsplit == 1 && T >= 64 && Hl <= 64 && !(reinterpret_cast<uintptr_t>(q) & 15) &&
+      rope_dim <= 64 && rope_dim % 2 == 0 && ldo % 8 == 0 && !(reinterpret_cast<uintptr_t>(out16) & 15) &&
+      !(reinterpret_cast<uintptr_t>(outb) & 15)) {
     // prefill rows: persistent CTAs on the tcgen05 tensor cores, one query row at a time
     if (!g_attn_sms) {
       int dev = 0;
@@ -615,6 +625,7 @@ TF_API int tf_sparse_attention(const void* q, int T, int Hl, int Dh, const int* 
       cudaFuncSetAttribute(sparse_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
     }
     tf_launch(sparse_attn_tc_kernel, dim3(T < g_attn_sms ? T : g_attn_sms), dim3(kTcThreads), kTcSmem, st, p);
+    return (int)cudaGetLastError();      // (sink, inverse rotation and the output rows are part of that kernel)
   } else if (Dh == 512 || Dh == 256) {
     const int smem = (kChunk * (Dh + 8) + Dh * (kChunk + 8)) * 2 + 4 * 16 * (kChunk + 4) * 4;
     static bool attr_set = false;

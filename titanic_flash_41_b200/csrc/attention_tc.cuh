@@ -23,13 +23,14 @@
 // Every wait is bounded; on a time-out the CTA raises its abort flag, reports TF_TIMEOUT, frees its
 // tensor memory and returns.
 //
-// Output: the same normalised partials (fp32) and base-2 log-sum-exp the mma.sync kernel writes with
-// one split; attn_merge_kernel adds the sink and the inverse rotation.
+// Output: the finished rows (sink as an extra zero-valued logit, inverse rotation of the tail, f16 and /
+// or bf16), i.e. what the mma.sync kernel and attn_merge_kernel produce together with one split.
 #pragma once
 #include "tc.cuh"
 
 constexpr int kTcKeys = 128;
-constexpr int kTcThreads = 9 * 32;                  // 4 gather warps, 4 softmax warps, 1 MMA warp
+constexpr int kTcProd = 8;                           // gather warps: two threads per key row (64 dims each)
+constexpr int kTcThreads = (kTcProd + 5) * 32;      // gather warps, 4 softmax warps, 1 MMA warp
 constexpr int kTcSub = 16384;                       // one [128 rows x 128 B] sub-tile
 constexpr int kTcQSub = 16384;                      // Q: rows 0..63 the heads, rows 64..127 the heads again; two buffers
 constexpr int kTcPSub = 8192;                       // P: 64 rows (the heads); two buffers
@@ -125,13 +126,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) {
-      tc::mbar_init(full(s), 4);
+      tc::mbar_init(full(s), kTcProd);
       tc::mbar_init(empty(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       tc::mbar_init(s_ready(s), 1);
       tc::mbar_init(s_free(s), 4);
-      tc::mbar_init(q_ready(s), 4);
+      tc::mbar_init(q_ready(s), kTcProd);
       tc::mbar_init(q_free(s), 1);
       tc::mbar_init(p_free(s), 1);
       tc::mbar_init(o_free(s), 2);
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
   // Q and P start as zeros: rows 64..127 of P (no heads there) stay zero for the whole launch
   for (int i = threadIdx.x; i < kOpBytes / 16; i += kTcThreads)
     reinterpret_cast<uint4*>(q_g)[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (warp == 8) tc::tmem_alloc(tc::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+  if (warp == kTcProd + 4) tc::tmem_alloc(tc::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
   tc::fence_proxy_async();
   tc::tc_fence_before();
   __syncthreads();
@@ -153,11 +154,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
   const uint32_t tS[2] = {tmem_base, tmem_base + 128u};
   const uint32_t tOb[2] = {tmem_base + 256u, tmem_base + 384u};     // O of even / odd rows of this CTA
 
-  if (warp < 4) {
+  if (warp < kTcProd) {
     // ------------------------------------------------------------------ gather + convert
-    const int tid = threadIdx.x;                    // key of the chunk served by this thread
-    uint4 rawv[8];
-    uint32_t rsc[2];
+    const int tid = threadIdx.x & 127;              // key of the chunk served by this thread ...
+    const int hh = threadIdx.x >> 7;                // ... and which 64 of its 128 dims
+    uint4 rawv[4];
+    uint32_t rsc[1];
     int it = 0, n_row = 0;
     bool ok = true;
     for (int r = blockIdx.x; r < p.T && ok; r += gridDim.x, ++n_row) {
@@ -183,8 +185,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
         if (kind == 1) {
           const uint8_t* row = win + (long)val * p.win_row;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + j * 16);
-          rsc[0] = *reinterpret_cast<const uint32_t*>(row + DH);
+          for (int j = 0; j < 4; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + hh * 64 + j * 16);
+          rsc[0] = *reinterpret_cast<const uint32_t*>(row + DH) >> (16 * hh);       // the half's two scale bytes
         } else if (kind == 2) {
           int id = val;
           if (id < 0 || id >= p.maxC) {
@@ -193,10 +195,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
           }
           const uint8_t* row = comp + (long)id * p.comp_row;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + j * 16);
-          const uint2 s2 = *reinterpret_cast<const uint2*>(row + DH / 2);
-          rsc[0] = s2.x;
-          rsc[1] = s2.y;
+          for (int j = 0; j < 2; ++j) rawv[j] = *reinterpret_cast<const uint4*>(row + hh * 32 + j * 16);
+          rsc[0] = *reinterpret_cast<const uint32_t*>(row + DH / 2 + hh * 4);       // the half's four scale bytes
         }
       };
       int kind_cur = key_kind(0), kind_next = key_kind(1);
@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
         // 64 heads x 128 dims bf16 = 1,024 16-byte pieces over 128 threads
         const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + (long)r * p.Hl * DH);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int piece = tid + 128 * j;
+        for (int j = 0; j < 1024 / (kTcProd * 32); ++j) {
+          const int piece = (int)threadIdx.x + kTcProd * 32 * j;
           const int h = piece >> 4, c16 = piece & 15;           // 16 pieces per head row
           uint4 v = h < p.Hl ? qsrc[piece] : make_uint4(0u, 0u, 0u, 0u);
           uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
@@ -234,8 +234,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
         // The key row as f16 (what a latent value times its scale is exactly: at most five mantissa
         // bits for FP4 rows, four for FP8 rows), sixteen values = one 32-byte piece at a time.  One
         // branch per row kind, not per piece: the FP4 body (all but the window rows) stays small.
-        auto put = [&](int seg, const uint32_t (&hv)[8]) {
-          const int d0 = seg * 16;
+        auto put = [&](int seg, const uint32_t (&hv)[8]) {          // seg: 16-value piece of this thread's half
+          const int d0 = hh * 64 + seg * 16;
           uint8_t* ksub = kt + (d0 >> 6) * kTcSub;
           *reinterpret_cast<uint4*>(ksub + sw128(tid, (d0 & 63) * 2)) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
           *reinterpret_cast<uint4*>(ksub + sw128(tid, (d0 & 63) * 2 + 16)) = make_uint4(hv[4], hv[5], hv[6], hv[7]);
@@ -243,10 +243,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
         if (kind_cur == 0) {
           const uint32_t z[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
-          for (int seg = 0; seg < 8; ++seg) put(seg, z);
+          for (int seg = 0; seg < 4; ++seg) put(seg, z);
         } else if (kind_cur == 1) {
 #pragma unroll
-          for (int seg = 0; seg < 8; ++seg) {
+          for (int seg = 0; seg < 4; ++seg) {
             uint32_t hv[8];
             const float sc = ue8m0_to_float((rsc[0] >> (8 * (seg >> 1))) & 0xffu);
             const uint16_t* h = reinterpret_cast<const uint16_t*>(&rawv[seg]);
@@ -263,9 +263,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
           // the group's e4m3 scale, exact) instead of a trip through fp32 and back
           const __half2 k14 = __floats2half2_rn(16384.f, 16384.f);
 #pragma unroll
-          for (int seg = 0; seg < 8; ++seg) {
+          for (int seg = 0; seg < 4; ++seg) {
             uint32_t hv[8];
-            const uint32_t sb = (rsc[seg >> 2] >> (8 * (seg & 3))) & 0xffu;
+            const uint32_t sb = (rsc[0] >> (8 * seg)) & 0xffu;
             const uint32_t sh = e4m3x2_to_h2((uint16_t)(sb | (sb << 8)));
             const __half2 sc2 = *reinterpret_cast<const __half2*>(&sh);
             const uint32_t* w = reinterpret_cast<const uint32_t*>(&rawv[seg >> 1]) + 2 * (seg & 1);
@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
         if (lane == 0) tc::mbar_arrive(full(s));
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == kTcProd + 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, 128);      // f16 x f16, M 128, N 128, both K-major
@@ -349,12 +349,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
     // + 63 of the chunk (lanes 64..127 of S repeat lanes 0..63).  The two threads of a head share
     // the reference maximum (chunk maxima and the row sum meet in shared memory under a named
     // barrier of the 128 softmax threads); only the first two warps touch O.
-    const int L = (warp - 4) * 32 + lane;
+    const int L = (warp - kTcProd) * 32 + lane;
     const int h = L & 63, half = L >> 6;
-    const uint32_t lane_off = (uint32_t)((warp - 4) * 32) << 16;
+    const uint32_t lane_off = (uint32_t)((warp - kTcProd) * 32) << 16;
     const uint32_t col0 = (uint32_t)half * 64u;
     // (the two warps that share a set of heads meet at a named barrier of their own, 64 threads)
-    const int pair_bar = 1 + ((warp - 4) & 1);
+    const int pair_bar = 1 + ((warp - kTcProd) & 1);
     auto sm_bar = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
     // A wait that runs out raises the CTA's abort flag.  The warp then stops waiting but keeps walking
     // the same sequence of named barriers as its partner (nobody is left behind at a barrier); the
@@ -482,22 +482,61 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
       if (half == 0) {
         wait(o_ready, (it & 1) ^ 1);
         tc::tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        float* po = p.part_o + ((long)r * p.Hl + h) * DH;
+        // The sink is one more logit with a zero value: the row is scaled by w / (w + w_sink) as the
+        // split merge would.  Then the inverse rotation of the tail (the value shares the key's rotated
+        // latent) and the f16 / bf16 row.  Lane j holds the sine and cosine of pair j of the tail.
+        float scale_o = 0.f;
+        if (l > 0.f) {
+          const float lse = m + log2f(l);
+          const float s2 = p.sink ? p.sink[min(h, p.Hl - 1)] * 1.4426950408889634f : kNegBig;
+          const float mx = fmaxf(s2, lse);
+          const float w = exp2f(lse - mx);
+          scale_o = w / (w + (p.sink ? exp2f(s2 - mx) : 0.f)) / l;
+        }
+        float sn = 0.f, cs = 1.f;
+        if (lane < p.rope_dim / 2) {
+          const float ang = (float)p.pos[r] * p.freqs[lane];
+          const double two_pi = 6.283185307179586476925286766559;
+          sincosf((float)((double)ang - two_pi * floor((double)ang / two_pi)), &sn, &cs);
+        }
+        const int tail0 = DH - p.rope_dim;
+        const long orow = (long)r * p.ldo + (long)h * DH;
 #pragma unroll 1
         for (int q = 0; q < 4; ++q) {
           uint32_t v[32];
           tc::tmem_ld32(tO + lane_off + q * 32, v);
           tc::tmem_ld_wait();
-          if (h < p.Hl) {
+          float o[32];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<float4*>(po + q * 32 + 4 * i) =
-                  make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
-                              __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * scale_o;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int d = q * 32 + i;
+            const int j = (d - tail0) >> 1;                       // pair of the tail (uniform over the warp)
+            const float sj = __shfl_sync(0xffffffffu, sn, j & 31), cj = __shfl_sync(0xffffffffu, cs, j & 31);
+            if (d >= tail0) {
+              const float a = o[i], b2 = o[i + 1];
+              o[i] = a * cj + b2 * sj;                            // inverse rotation: angle -> -angle
+              o[i + 1] = -a * sj + b2 * cj;
+            }
+          }
+          if (h < p.Hl) {
+            if (p.out16) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4*>(p.out16 + orow + q * 32 + 8 * i) =
+                    make_uint4(pack_h2(o[8 * i], o[8 * i + 1]), pack_h2(o[8 * i + 2], o[8 * i + 3]),
+                               pack_h2(o[8 * i + 4], o[8 * i + 5]), pack_h2(o[8 * i + 6], o[8 * i + 7]));
+            }
+            if (p.outb) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4*>(p.outb + orow + q * 32 + 8 * i) =
+                    make_uint4(pack_bf2(o[8 * i], o[8 * i + 1]), pack_bf2(o[8 * i + 2], o[8 * i + 3]),
+                               pack_bf2(o[8 * i + 4], o[8 * i + 5]), pack_bf2(o[8 * i + 6], o[8 * i + 7]));
+            }
           }
         }
-        if (h < p.Hl) p.part_lse[(long)r * p.Hl + h] = l > 0.f ? m + log2f(l) : kNegBig;
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(o_free(n_row & 1));
@@ -508,7 +547,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) sparse_attn_tc_kernel(AttnParam
   tc::tc_fence_before();
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0) tf_report(p.st, TF_TIMEOUT, 150, blockIdx.x, 0);
-  if (warp == 8) {
+  if (warp == kTcProd + 4) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, 512);
   }
