@@ -117,7 +117,10 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(const_cast<uint32_t*>(tmem_slot) + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = p.N / kTile;
+  // DUAL: 0 = one weight tile per item; 1 = w1 and w3 tiles + SwiGLU; 2 = two adjacent tiles of ONE
+  // matrix per item (half as many items, each streaming twice the bytes: the second GEMV of the experts)
+  constexpr int kItemN = DUAL == 2 ? 2 * kTile : kTile;
+  const int tiles_n = p.N / kItemN;
   const int kchunks = p.K / kBK, nsuper = p.K / kSuper;
 
   if (threadIdx.x == 0) {
@@ -161,9 +164,9 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
       int it = 0, fsf = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-        const int g = item / tiles_n, n0 = (item % tiles_n) * kTile;
+        const int g = item / tiles_n, n0 = (item % tiles_n) * kItemN;
         const int wrow = p.g_expert[g] * p.N + n0;
-        const int xrow = DUAL ? 0 : p.g_start[g];
+        const int xrow = DUAL == 1 ? 0 : p.g_start[g];
         for (int kc = 0; kc < kchunks; ++kc, ++it) {
           if (kc % (kSuper / kBK) == 0) {
             // the scale bytes of the next 512 inputs travel with the data: the four loader warps
@@ -173,7 +176,8 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
             tc::mbar_expect_tx(sfs_full(sl), kMats * kTile * 16 + kRows * 16);
             const uint32_t d = sfs0 + sl * kSfsBytes;
             tc::tma_load_2d(d, &mapS1, sc * 16, wrow, sfs_full(sl));
-            if (DUAL) tc::tma_load_2d(d + kTile * 16, &mapS3, sc * 16, wrow, sfs_full(sl));
+            if (DUAL == 1) tc::tma_load_2d(d + kTile * 16, &mapS3, sc * 16, wrow, sfs_full(sl));
+            if (DUAL == 2) tc::tma_load_2d(d + kTile * 16, &mapS1, sc * 16, wrow + kTile, sfs_full(sl));
             tc::tma_load_2d(d + kMats * kTile * 16, &mapSX, sc * 16, xrow, sfs_full(sl));
             ++fsf;
           }
@@ -187,7 +191,9 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
           const int wx = p.blocked ? 0 : kc * kBK;
           const int wy = p.blocked ? ((wrow / kTile) * kchunks + kc) * kTile : wrow;
           tc::tma_load_2d(sa, &mapW1, wx, wy, full(s));
-          if (DUAL) tc::tma_load_2d(sa + kTile * 128, &mapW3, wx, wy, full(s));
+          if (DUAL == 1) tc::tma_load_2d(sa + kTile * 128, &mapW3, wx, wy, full(s));
+          if (DUAL == 2)
+            tc::tma_load_2d(sa + kTile * 128, &mapW1, wx, p.blocked ? wy + kchunks * kTile : wy + kTile, full(s));
           tc::tma_load_2d(sa + kMats * kTile * 128, &mapX, kc * kBK, xrow, full(s));
         }
       }
@@ -241,13 +247,13 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
     const int quad = warp & 3;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     auto epilogue = [&](int item, int n_item) -> bool {
-      const int g = item / tiles_n, n0 = (item % tiles_n) * kTile;
+      const int g = item / tiles_n, n0 = (item % tiles_n) * kItemN;
       const int gs = p.g_start[g], gc = p.g_count[g];
       const int ab = n_item & 1;
       // output row of accumulator column `lane` (-1: nobody routed there)
       int orow = -1;
       if (lane < kRows) {
-        if (DUAL) {
+        if (DUAL == 1) {
           for (int i = 0; i < gc; ++i)
             if (p.sorted_pairs[gs + i] / p.topk == lane) orow = gs + i;
         } else if (lane < gc) {
@@ -269,7 +275,7 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
         const int r = __shfl_sync(0xffffffffu, orow, c);
         if (r < 0) continue;
         float o = __uint_as_float(a1[c]);
-        if (DUAL) {
+        if (DUAL == 1) {
           float gate = o, up = __uint_as_float(a3[c]);
           if (p.limit > 0.f) {
             gate = fminf(gate, p.limit);
@@ -294,6 +300,7 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
           }
         } else {
           reinterpret_cast<float*>(p.out)[(long)r * p.ldo + n] = o;
+          if (DUAL == 2) reinterpret_cast<float*>(p.out)[(long)r * p.ldo + n + kTile] = __uint_as_float(a3[c]);
         }
       }
       return true;
@@ -463,6 +470,7 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
     cudaDeviceGetAttribute(&g_mx_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaFuncSetAttribute(moe_mx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(moe_mx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   }
   CUtensorMap m1, m3, mx, ms1, ms3, msx;
   if (!tc::make_map_2d_plain(&ms1, s1, (uint64_t)experts * N, K / 32, K / 32, 16, kTile)) return -4;
@@ -487,11 +495,13 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
   p.limit = limit;
   p.blocked = blocked;
   p.status = reinterpret_cast<TfStatusWord*>(status);
-  const int grid = min(g_mx_sms, max_groups * (N / kTile));
-  const int stages = dual ? 6 : 11, mats = dual ? 2 : 1;
+  const bool pair = !dual && N % (2 * kTile) == 0;         // plain form, two adjacent tiles per work item
+  const int grid = min(g_mx_sms, max_groups * (N / (pair ? 2 * kTile : kTile)));
+  const int stages = (dual || pair) ? 6 : 11, mats = (dual || pair) ? 2 : 1;
   const int sfs = (mats * kTile * 16 + kRows * 16 + 127) / 128 * 128;
   const int smem = stages * (mats * kTile * 128 + kRows * 128) + kSfBufs * sfs + 1024 + 512;
   if (dual) tf_launch(moe_mx_kernel<1>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
+  else if (pair) tf_launch(moe_mx_kernel<2>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
   else tf_launch(moe_mx_kernel<0>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
