@@ -2,29 +2,34 @@
 // split).  Included by attention.cu inside its anonymous namespace (AttnParams, kNegBig).
 //
 // A persistent CTA takes one query row at a time.  All heads of the row read the same latent keys,
-// so the heads are the M of both contractions (64 real rows of a 128-row MMA; the other 64 rows of
-// the operands are zero) and a chunk of 128 gathered keys is N of the first and K of the second:
+// so the heads are the M of both contractions and a chunk of 128 gathered keys is N of the first and
+// K of the second:
 //
-//   S[head, key]  = Q[head, :] . K[key, :]        A = Q  [128 x 128 dims]  B = Kt [128 keys x 128 dims]
-//   O[head, dim] += P[head, key] * K[key, dim]     A = P  [128 x 128 keys]  B = Vt [128 dims x 128 keys]
+//   S[head, key]  = Q[head, :] . K[key, :]        A = Q [128 x 128 dims]   B = key tile, K-major
+//   O[head, dim] += P[head, key] * K[key, dim]     A = P [ 64 x 128 keys]   B = the same tile, MN-major
 //
-// Every operand is K-major bf16 in shared memory with the 128-byte swizzle (two 64-column sub-tiles
-// per operand), S (two buffers) and O live in tensor memory, and a softmax thread owns one head =
-// one TMEM lane: row maxima and sums need no exchange between threads.
+// Operands are f16 in shared memory with the 128-byte swizzle (two 64-column sub-tiles each): a latent
+// value times its scale is exact in f16 (FP4 rows: five mantissa bits at most, FP8 rows: four), and
+// Q is bf16 converted once per row.  S (two buffers) and O (two buffers, alternating rows) live in
+// tensor memory.  Q's 64 head rows are stored twice, so accumulator lanes 64..127 of S repeat lanes
+// 0..63 and a softmax thread owns one lane and HALF of the chunk's key columns.
 //
-//   warps 0-3   gather: thread t fetches key t of the chunk (FP8 window row or FP4 compressed
-//               row, the next chunk's bytes requested before this chunk is converted), converts it
-//               to bf16 and writes it twice: as a row of Kt and as a column of Vt
-//   warps 4-5   softmax (lanes 0-63 of tensor memory): base-2 online softmax over the chunk, P as
-//               bf16 into shared memory, O rescaled in tensor memory when a maximum moved, the
-//               normalised row written at the end
-//   warp 6      one thread issues the MMAs: QK of chunk c + 1 is issued before PV of chunk c, so the
-//               softmax of a chunk overlaps the next chunk's first contraction
-// Every wait is bounded; on a time-out the CTA raises its abort flag, reports TF_TIMEOUT, frees its
-// tensor memory and returns.
+//   warps 0-7   gather: two threads per key of the chunk (64 dims each) fetch its FP8 window row or
+//               FP4 compressed row (the next chunk's bytes are requested before this chunk is
+//               converted; ids are decoded a chunk after they are loaded) and write it as a row of the
+//               key tile; three tiles in flight
+//   warps 8-11  softmax: base-2 online softmax with a stale reference maximum (O is rescaled, and
+//               the previous PV waited for, only when a score exceeds it by 2^8), P as f16 into
+//               shared memory (two buffers); the two threads of a head meet at a named barrier of
+//               their warp pair; warps 8-9 finish the row: sink as an extra zero-valued logit, inverse
+//               rotation of the tail, f16 / bf16 output
+//   warp 12     one thread issues the MMAs: QK of chunk c + 1 before PV of chunk c
+// Every mbarrier wait is bounded; on a time-out the CTA raises its abort flag, reports TF_TIMEOUT,
+// frees its tensor memory and returns (softmax warps stop waiting but keep walking their named
+// barriers, so no warp is left behind at one).
 //
-// Output: the finished rows (sink as an extra zero-valued logit, inverse rotation of the tail, f16 and /
-// or bf16), i.e. what the mma.sync kernel and attn_merge_kernel produce together with one split.
+// Output: the finished rows, i.e. what the mma.sync kernel and attn_merge_kernel produce together with
+// one split.
 #pragma once
 #include "tc.cuh"
 
