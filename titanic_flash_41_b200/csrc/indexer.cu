@@ -369,8 +369,12 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
 // atomics (scores crowd into a few exponent bytes, which serialises plain atomics) and read by all
 // eight CTAs over distributed shared memory; the compaction needs only the totals of the CTAs
 // before this one.  Output identical to topk_select_kernel.
-constexpr int kSelCluster = 8, kSelThreads = 512, kSelKeysPerThread = 16;
+// Two shapes: 8 CTAs x 16 keys per thread (a few long rows: decode), 2 or 4 CTAs x 32 keys per
+// thread (the many rows of a prefill chunk, up to 65,536 keys: the row is read once instead of
+// five times; past that the one-CTA kernel above takes over).
+constexpr int kSelThreads = 512;
 
+template <int kSelCluster, int kSelKeysPerThread>
 __global__ void __cluster_dims__(kSelCluster, 1, 1) __launch_bounds__(kSelThreads)
 topk_select_cluster_kernel(const float* __restrict__ scores, int lds, const int* __restrict__ nvalid, int k,
                            int* __restrict__ out, int* __restrict__ count, float* __restrict__ out_scores,
@@ -416,8 +420,12 @@ topk_select_cluster_kernel(const float* __restrict__ scores, int lds, const int*
       if (j < per) {                                 // uniform over the warp
         const bool in = i0 + j < hi && (key[j] & mask) == prefix;
         const int bin = in ? (int)((key[j] >> shift) & 0xffu) : -1;
-        const unsigned peers = __match_any_sync(0xffffffffu, bin);
-        if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[pass][bin], __popc(peers));
+        if (pass == 0) {                             // the first byte is crowded: one atomic per warp and bin
+          const unsigned peers = __match_any_sync(0xffffffffu, bin);
+          if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[pass][bin], __popc(peers));
+        } else if (in) {
+          atomicAdd(&hist[pass][bin], 1);
+        }
       }
     }
     cluster.sync();
@@ -604,8 +612,14 @@ TF_API int tf_index_scores(const void* q, const float* w, const int* region, con
 TF_API int tf_topk_select(const float* scores, int lds, const int* nvalid, int k, int* out, int* count,
                           float* out_scores, int base, int T, cudaStream_t st) {
   // a few long rows (decode): one cluster of CTAs per row; many rows: one CTA per row fills the GPU
-  if (T <= 32 && lds > 4096 && lds <= kSelCluster * kSelThreads * kSelKeysPerThread)
-    tf_launch(topk_select_cluster_kernel, dim3(kSelCluster, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
+  if (T <= 32 && lds > 4096 && lds <= 8 * kSelThreads * 16)
+    tf_launch(topk_select_cluster_kernel<8, 16>, dim3(8, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
+              count, out_scores, base);
+  else if (T > 32 && lds > 4096 && lds <= 2 * kSelThreads * 32)
+    tf_launch(topk_select_cluster_kernel<2, 32>, dim3(2, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
+              count, out_scores, base);
+  else if (T > 32 && lds > 4096 && lds <= 4 * kSelThreads * 32)
+    tf_launch(topk_select_cluster_kernel<4, 32>, dim3(4, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
               count, out_scores, base);
   else
     tf_launch(topk_select_kernel, dim3(T), dim3(1024), 0, st, scores, lds, nvalid, k, out, count, out_scores, base);
