@@ -511,9 +511,8 @@ def test_router_topk_group_equals_the_two_launches(M):
 
 @pytest.mark.parametrize("T,n_max", [(4, 32768), (16, 20000), (3, 65536), (40, 30000), (36, 60000), (34, 70000)])
 def test_topk_select_of_few_long_rows_matches_a_stable_sort(T, n_max):
-    """Long rows take the cluster-per-row kernel (8 CTAs per row for up to 32 rows, 2 or 4 CTAs per
-    row for the many rows of a prefill chunk up to 65,536 keys; beyond that one CTA per row): same
-    contract everywhere (exact, ties to the lower position, ids ascending, -1 padding, optional scores)."""
+    """A few long rows take the cluster-per-row kernel, more rows (or longer ones) the CTA-per-row
+    kernel: same contract (exact, ties to the lower position, ids ascending, -1 padding, optional scores)."""
     torch.manual_seed(T)
     k, lds = 2048, n_max
     scores = (torch.randn(T, lds, device=DEV) * 0.3 + 5).relu()        # crowded exponents, like index scores

@@ -369,9 +369,8 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float* __restri
 // atomics (scores crowd into a few exponent bytes, which serialises plain atomics) and read by all
 // eight CTAs over distributed shared memory; the compaction needs only the totals of the CTAs
 // before this one.  Output identical to topk_select_kernel.
-// Two shapes: 8 CTAs x 16 keys per thread (a few long rows: decode), 2 or 4 CTAs x 32 keys per
-// thread (the many rows of a prefill chunk, up to 65,536 keys: the row is read once instead of
-// five times; past that the one-CTA kernel above takes over).
+// (Measured for the many rows of a prefill chunk too, as 2 CTAs x 32 keys per thread: 1,058 us for
+// 2,048 rows x 32,768 scores against 816 us of the one-CTA kernel above, which therefore keeps them.)
 constexpr int kSelThreads = 512;
 
 template <int kSelCluster, int kSelKeysPerThread>
@@ -614,12 +613,6 @@ TF_API int tf_topk_select(const float* scores, int lds, const int* nvalid, int k
   // a few long rows (decode): one cluster of CTAs per row; many rows: one CTA per row fills the GPU
   if (T <= 32 && lds > 4096 && lds <= 8 * kSelThreads * 16)
     tf_launch(topk_select_cluster_kernel<8, 16>, dim3(8, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
-              count, out_scores, base);
-  else if (T > 32 && lds > 4096 && lds <= 2 * kSelThreads * 32)
-    tf_launch(topk_select_cluster_kernel<2, 32>, dim3(2, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
-              count, out_scores, base);
-  else if (T > 32 && lds > 4096 && lds <= 4 * kSelThreads * 32)
-    tf_launch(topk_select_cluster_kernel<4, 32>, dim3(4, T), dim3(kSelThreads), 0, st, scores, lds, nvalid, k, out,
               count, out_scores, base);
   else
     tf_launch(topk_select_kernel, dim3(T), dim3(1024), 0, st, scores, lds, nvalid, k, out, count, out_scores, base);
