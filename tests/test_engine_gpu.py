@@ -37,7 +37,7 @@ def test_engine_matches_oracle_prefill_and_decode():
     want = ref.forward(prompt, s)
     got = eng.forward(E.StepPlan.build([(1, 0, prompt.tolist())])).cpu()
     eng.status.check()
-    # a near-tie in the router can flip an expert for a row, so judge rows statistically (the median
+    # a near-tie in the router can flip an expert for a row, so rows are assessed statistically (the median
     # of this small random model moves between 0.04 and 0.10 with the weight seed alone)
     err = _row_err(got, want)
     assert err.median() < 0.11 and (err < 0.15).float().mean() >= 0.7, err
@@ -275,7 +275,7 @@ def test_reference_geometry_matches_oracle(geom):
     got = eng.forward(E.StepPlan.build([(1, 0, prompt.tolist())])).cpu()
     eng.status.check()
     err = _row_err(got, want)
-    # rows whose router decision flips on a near-tie differ a lot; judge the rows statistically
+    # rows whose router decision flips on a near-tie differ a lot; assess the rows statistically
     med, lim, frac = (0.15, 0.25, 0.55) if cfg.hc_mult > 1 else (0.1, 0.2, 0.7)   # bf16 residual copies feed the mix
     assert err.median() < med and (err < lim).float().mean() >= frac, err
     pos, errs = 61, []

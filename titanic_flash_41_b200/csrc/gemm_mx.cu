@@ -188,7 +188,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ scale movers
-    // When full(s) completes for round r, the MMAs that read scale columns s in round r - 1 are
+    // When full(s) completes for lap r of the ring, the MMAs that read scale columns s in lap r - 1 are
     // done (the producer refilled the stage only after their commit): the columns are free.
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     int it = 0;
