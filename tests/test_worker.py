@@ -348,3 +348,25 @@ def test_interrupted_prefill_is_resumed_from_its_last_whole_chunk():
     _drain(w3)
     toks = lambda e: [t for _, k, p in e if k == "tokens" for t in p]
     assert toks(ev2) == toks(ev3) and len(toks(ev2)) == 4
+
+
+def test_relocated_conversation_continues_with_the_same_tokens():
+    """A decoding conversation moved to another region between steps produces the tokens it would
+    have produced in place (sampling is addressed by position; the state image travels)."""
+    def run(move):
+        cfg, w, s = _mk(regions=2)
+        ev = []
+        g = torch.Generator().manual_seed(21)
+        s.submit(_job("m", torch.randint(3, cfg.vocab, (40,), generator=g).tolist(), 24, ev, temperature=0.7, top_p=0.9,
+                      seed=5))
+        for _ in range(4):
+            w.run_once(0.0)
+        if move:
+            assert 0 in w.active and 1 not in w.active
+            w.execute({"op": "relocate", "region": 0, "to": 1})
+            assert 1 in w.active and 0 not in w.active and w.active[1].job.region == 1
+            assert s.free_regions() == [0]
+        _drain(w)
+        return [t for _, k, p in ev if k == "tokens" for t in p], [p["finish_reason"] for _, k, p in ev if k == "done"]
+    a, b = run(False), run(True)
+    assert a == b and len(a[0]) == 24 and a[1] == ["length"]

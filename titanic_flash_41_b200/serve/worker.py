@@ -177,7 +177,7 @@ class Worker:
         else:
             cmd = self._recv_command()
         self.execute(cmd)
-        if self.control is not None and cmd["op"] in ("begin", "step", "finish", "pause", "resume"):
+        if self.control is not None and cmd["op"] in ("begin", "step", "finish", "pause", "resume", "relocate"):
             self.control.agree(self._digest())
         return cmd["op"]
 
@@ -232,6 +232,8 @@ class Worker:
             self._pause(cmd["region"])
         elif op == "resume":
             self._resume(cmd["id"], cmd["region"])
+        elif op == "relocate":
+            self._relocate(cmd["region"], cmd["to"])
         elif op == "drop_parked":
             self.parked = [c for c in self.parked if c.id != cmd["id"]]
             job = self.parked_jobs.pop(cmd["id"], None)
@@ -320,6 +322,23 @@ class Worker:
         if self.sched is not None:
             self.sched.release(job)
         self.log.log("pause", id=ck.id, region=region, committed=len(ck.committed), bytes=ck.charge)
+
+    def _relocate(self, region: int, to: int) -> None:
+        """Move a decoding conversation to another (free) region between steps: its state image is
+        captured and restored there, sampling continues at the same positions, so the tokens are the
+        ones it would have produced in place (reference: src/batched_serving.rs:243 detach_active /
+        :604 attach_peer; the reference relocates conversations out of the region its prefills use)."""
+        a = self.active.get(region)
+        if a is None or to == region:
+            return
+        if to in self.active or not (0 <= to < self.b.regions):
+            raise RuntimeError(f"relocation target {to} is not a free region")
+        rid = a.job.id
+        self._pause(region)
+        if self.sched is not None:
+            self.sched.occupy(self.parked_jobs[rid], to)
+        self._resume(rid, to)
+        self.log.log("relocate", id=rid, source=region, target=to)
 
     def _resume(self, rid: str, region: int) -> None:
         from . import request_checkpoint as RC
