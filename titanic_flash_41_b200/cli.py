@@ -138,12 +138,20 @@ def make_backend(args, cfg: ModelConfig, comm):
     ecfg = EngineConfig(tp=world, regions=args.regions, max_context=args.max_context)
     if world > 1:
         ecfg.sp_chunk_rows = min(max(ecfg.prefill_widths) * world, 65536)      # sequence-parallel chunks span the ranks' slices
+    import time as _time
+    t_load = _time.monotonic()
     if args.checkpoint:
         # streamed, digest-checked, in the stored formats: never more than one layer on the host
         from .models import stream_loader
         eng = stream_loader.load_engine(args.checkpoint, cfg, ecfg, comm, device=dev)
     else:
         eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=args.seed)
+    # one structured line per rank: what was loaded, how long it took, what it occupies
+    import json as _json
+    import sys as _sys
+    print(_json.dumps({"event": "engine_loaded", "rank": getattr(comm, "rank", 0), "world": world,
+                       "source": args.checkpoint or "random-init", "load_s": round(_time.monotonic() - t_load, 3),
+                       "bytes": eng.memory_report()}), file=_sys.stderr, flush=True)
     if world > 1:
         # the product runs what the benchmark measures: decode rows go through the fused
         # GEMV / combine + all-reduce kernels over peer memory, not NCCL all-reduces per sublayer

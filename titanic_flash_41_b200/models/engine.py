@@ -974,6 +974,42 @@ class Engine:
             from ..ops import two_level as TL
             b["cand"] = TL.publish(scores[:T, :nmax], nvalid, cfg.candidate_blocks, T)
 
+    def memory_report(self) -> Dict[str, int]:
+        """Bytes this engine holds on the device, by kind (reference: the allocation lines the
+        reference logs at load, src/memory.rs / src/weights.rs): dense and expert weights, embeddings
+        and heads, the KV state of all regions, and the per-row-count scratch allocated so far."""
+        def nbytes(obj, seen) -> int:
+            if isinstance(obj, torch.Tensor):
+                key = (obj.untyped_storage().data_ptr(), obj.untyped_storage().nbytes())
+                if key in seen:
+                    return 0
+                seen.add(key)
+                return obj.untyped_storage().nbytes() if obj.is_cuda else 0
+            if isinstance(obj, Fp8Weight):
+                return nbytes(obj.q, seen) + nbytes(obj.s, seen) + (nbytes(obj.sfu, seen) if isinstance(obj.sfu, torch.Tensor) else 0)
+            if isinstance(obj, (list, tuple)):
+                return sum(nbytes(o, seen) for o in obj)
+            if isinstance(obj, dict):
+                return sum(nbytes(o, seen) for o in obj.values())
+            if isinstance(obj, LayerWeights):
+                return sum(nbytes(getattr(obj, f), seen) for f in obj.__dataclass_fields__)
+            return 0
+        seen: set = set()
+        experts = dense = 0
+        for L in list(self.layers) + list(self.draft_layers):
+            for f in L.__dataclass_fields__:
+                b = nbytes(getattr(L, f), seen)
+                if f in ("ew1", "ew3", "ew2", "es1", "es3", "es2"):
+                    experts += b
+                else:
+                    dense += b
+        out = {"dense_weights": dense, "expert_weights": experts,
+               "embeddings_and_heads": nbytes([self.embed_w, getattr(self, "head_w", None), self.draft_extra], seen),
+               "kv_state": nbytes([self.win, self.comp, self.keys, self.carry], seen),
+               "row_scratch": nbytes([self._scratch, getattr(self, "_buf_cache", None)], seen)}
+        out["total"] = sum(out.values())
+        return out
+
     @property
     def candidate_source(self) -> int:
         """The index source layer that publishes candidate blocks: the last one before the late
