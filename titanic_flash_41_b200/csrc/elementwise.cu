@@ -197,7 +197,29 @@ __global__ void attn_prep_kernel(PrepParams p) {
   // with blockIdx.y > 0 share the query elements of the row, the CTA with blockIdx.y == 0 does the rest.
   const int qparts = gridDim.y > 1 ? gridDim.y - 1 : 1;
   const int qpart = gridDim.y > 1 ? (int)blockIdx.y - 1 : 0;
-  if (p.off_q >= 0 && qpart >= 0) {
+  const bool q_vec = p.p_kind != 0 && p.ldp % 8 == 0 && p.off_q % 8 == 0 && p.Dh % 8 == 0 && tail0 % 8 == 0 &&
+                     !(reinterpret_cast<uintptr_t>(p.P) & 15) && !(reinterpret_cast<uintptr_t>(p.q_out) & 15);
+  if (p.off_q >= 0 && qpart >= 0 && q_vec) {
+    // bf16 rows, eight elements (four rotation pairs) per 16-byte load and store: same arithmetic as
+    // the element-wise loop below
+    const __nv_bfloat16* prow = reinterpret_cast<const __nv_bfloat16*>(p.P) + (long)r * p.ldp + p.off_q;
+    __nv_bfloat16* qrow = p.q_out + (long)r * p.Hl * p.Dh;
+    for (int v = qpart * blockDim.x + tid; v < p.Hl * p.Dh / 8; v += qparts * blockDim.x) {
+      uint4 raw = *reinterpret_cast<const uint4*>(prow + v * 8);
+      const int dd = (v * 8) % p.Dh;
+      if (dd >= tail0) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int j = ((dd - tail0) >> 1) + k;
+          const float sn = s_sin[j], cs = s_cos[j];
+          const float2 f = __bfloat1622float2(h[k]);
+          h[k] = __halves2bfloat162(__float2bfloat16(f.x * cs - f.y * sn), __float2bfloat16(f.x * sn + f.y * cs));
+        }
+      }
+      *reinterpret_cast<uint4*>(qrow + v * 8) = raw;
+    }
+  } else if (p.off_q >= 0 && qpart >= 0) {
     for (int i = qpart * blockDim.x + tid; i < p.Hl * p.Dh; i += qparts * blockDim.x) {
       const int dd = i % p.Dh;
       float v = ldp(p, r, p.off_q + i);
