@@ -156,7 +156,7 @@ def prep():
     st = native.StatusWord(DEV)
     us = timed(lambda: native.call("tf_attn_prep", P, 1, W, T, pos, region, first, last, Hl, Dh, rope, freqs, freqs, norm, 1e-6,
                                    qo, win, ring * win_row, win_row, comp_row, krow, ring, offs["q"], offs["kv"], offs["cv"],
-                                   offs["cg"], offs["iq"], offs["iw"], ratio, Di, Hi, norm, carry, comp, keys, maxC, iq, iw,
+                                   offs["cg"], offs["iq"], offs["iw"], ratio, Di, Hi, norm, carry, carry.shape[1], comp, keys, maxC, iq, iw,
                                    st.t), n=3, warm=1)
     st.check()
     print(f"attention prep, {T} rows ({W} projected columns): {us:.0f} us per launch, "

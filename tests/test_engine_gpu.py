@@ -55,6 +55,52 @@ def test_engine_matches_oracle_prefill_and_decode():
     assert errs.median() < 0.11 and (errs < 0.15).float().mean() >= 0.7, errs
 
 
+def test_mixed_compression_ratios_match_oracle_and_travel_in_state_images():
+    """Two compressed streams with their own ratios (pairs pooled at the first source, every token kept
+    at the second: the reference's layers 2-19 / 20-39, src/config.rs:252-280): prefill and decode rows
+    against the oracle, then the state image of the conversation restored into another region
+    continues with identical logits."""
+    from titanic_flash_41_b200.serve.backend import EngineBackend
+    # index_topk above the entry count and every expert routed: nothing discrete can flip on a
+    # near-tie (selection and routing have their own tests), so EVERY row must agree closely
+    cfg = small_config(n_layers=4, compress_ratio=1, compress_ratios=(2, 1), kv_source_layers=(0, 2),
+                       index_source_layers=(0, 2, 3), index_topk=128, topk=8)
+    W = oracle.init_weights(cfg, 0)
+    rt = {}
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,))
+    eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
+    ref = oracle.OracleModel(cfg, rt)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (77,), generator=g)
+    s = ref.new_session(256)
+    want = ref.forward(prompt, s)
+    got = eng.forward(E.StepPlan.build([(1, 0, prompt.tolist())])).cpu()
+    eng.status.check()
+    err = _row_err(got, want)
+    assert err.max() < 0.15 and err.median() < 0.07, err
+    # 38 pairs in the coarse stream, 77 entries in the fine one; nothing written past them
+    assert bool(eng.comp[0, 1, :38].any(-1).all()) and not bool(eng.comp[0, 1, 38:].any())
+    assert bool(eng.comp[1, 1, :77].any(-1).all()) and not bool(eng.comp[1, 1, 77:].any())
+    pos, errs = 77, []
+    for step in range(4):
+        toks = torch.randint(0, cfg.vocab, (4,), generator=g)
+        want = ref.forward(toks, s)
+        got = eng.forward(E.StepPlan.build([(1, pos, toks.tolist())])).cpu()
+        pos += 4
+        errs.append(_row_err(got, want))
+    eng.status.check()
+    errs = torch.cat(errs)
+    assert errs.max() < 0.15 and errs.median() < 0.07, errs
+    be = EngineBackend(eng, chunk=128)
+    img = be.snapshot(1, list(range(pos)))
+    be.restore(0, img)
+    toks = torch.randint(0, cfg.vocab, (4,), generator=g).tolist()
+    a = eng.forward(E.StepPlan.build([(1, pos, toks)])).cpu()
+    b = eng.forward(E.StepPlan.build([(0, pos, toks)])).cpu()
+    eng.status.check()
+    assert torch.equal(a, b)
+
+
 def test_block_scaled_expert_path_matches_register_path_and_oracle():
     """Decode rows with the routed experts on block-scaled tcgen05 MMAs.  MXFP8 activations are a
     different arithmetic from f16 ones (the W4A8 form of the reference's expert kernels): the
@@ -500,7 +546,8 @@ def test_reference_model_widths_run_on_the_engine():
     output groups of rank 1024, four residual copies, 32 index heads, expert width 2304) with few layers and
     experts: prefill and a decode block produce finite logits and no kernel reports a problem."""
     from titanic_flash_41_b200.config import DraftConfig, reference_1017_config
-    cfg = reference_1017_config(n_layers=4, kv_source_layers=(2,), index_source_layers=(2,), late_start=3, n_experts=32,
+    cfg = reference_1017_config(n_layers=4, kv_source_layers=(1, 2), compress_ratios=(2, 1), index_source_layers=(1, 2, 3),
+                                late_start=3, n_experts=32,
                                 draft=DraftConfig(layers=1, depth=3), engram=None, dense_quant="fp8_block128", vocab=16384)
     eng = E.Engine.random_init(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=4096, prefill_widths=(256,)), seed=0, max_chunk=256)
     g = torch.Generator().manual_seed(0)

@@ -27,6 +27,35 @@ def test_chunked_prefill_equals_one_shot():
     assert torch.allclose(torch.cat(parts), full, atol=2e-5)
 
 
+def test_mixed_compression_ratios_per_source_layer():
+    """Two source layers with their own ratios (the reference pools pairs in layers 2-19 and keeps every
+    token from layer 20 on, src/config.rs:252-280): each stream gets position // ratio entries, chunked
+    prefill equals one shot, and the coarser stream changes the logits against a uniform fine one."""
+    kw = dict(n_layers=3, kv_source_layers=(0, 1), index_source_layers=(0, 1, 2), index_topk=8)
+    cfg = tiny_config(compress_ratio=1, compress_ratios=(2, 1), **kw)
+    assert [cfg.ratio_of(l) for l in range(3)] == [2, 1, 1] and cfg.max_ratio == 2
+    W = oracle.init_weights(cfg, 0)
+    m = oracle.OracleModel(cfg, W)
+    p = _prompts(cfg, 1, 51)[0]
+    s1 = m.new_session(64)
+    full = m.forward(p, s1)
+    assert s1.comp["layers.0"].shape[0] == 64 // 2 + 1 and s1.comp["layers.1"].shape[0] == 64 + 1
+    # 25 complete pairs in the coarse stream, 51 entries in the fine one
+    assert bool(s1.comp["layers.0"][:25].abs().sum(-1).gt(0).all()) and not bool(s1.comp["layers.0"][25:].any())
+    assert bool(s1.comp["layers.1"][:51].abs().sum(-1).gt(0).all()) and not bool(s1.comp["layers.1"][51:].any())
+    assert m.last_selection[2].shape == (51, 8) and int(m.last_selection[2].max()) <= 50
+    assert int(m.last_selection[0].max()) <= 24
+    s2 = m.new_session(64)
+    parts = [m.forward(p[a:b], s2) for a, b in ((0, 7), (7, 30), (30, 31), (31, 51))]
+    assert torch.allclose(torch.cat(parts), full, atol=2e-5)
+    uni = oracle.OracleModel(tiny_config(compress_ratio=1, **kw), W)
+    assert not torch.allclose(uni.forward(p, uni.new_session(64)), full, atol=1e-3)
+    with pytest.raises(ValueError):
+        tiny_config(compress_ratio=2, compress_ratios=(2, 3), **kw)
+    with pytest.raises(ValueError):
+        tiny_config(compress_ratio=1, compress_ratios=(2,), **kw)
+
+
 def test_rollback_of_speculative_rows():
     cfg = tiny_config()
     m = oracle.OracleModel(cfg, oracle.init_weights(cfg, 1))

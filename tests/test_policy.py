@@ -130,7 +130,7 @@ def test_sequence_parallel_chunk_sizes_respect_slice_and_ring_limits():
     from titanic_flash_41_b200.parallel.sp import SpPrefill
     def sizes(n, chunk, world, sp_rows, max_chunk=16384, window=128, ratio=4):
         ring = max(max_chunk, sp_rows) + 2 * window
-        fake = NS(W=world, eng=NS(cfg=NS(compress_ratio=ratio, window=window), ecfg=NS(sp_chunk_rows=sp_rows),
+        fake = NS(W=world, eng=NS(cfg=NS(compress_ratio=ratio, max_ratio=ratio, window=window), ecfg=NS(sp_chunk_rows=sp_rows),
                                   max_chunk=max_chunk, ring=ring))
         return SpPrefill.chunk_sizes(fake, n, chunk)
     s = sizes(129553, 16384, 8, 65536)

@@ -2,6 +2,7 @@
 resume from a cached image, cancellation."""
 import threading
 
+import pytest
 import torch
 
 from titanic_flash_41_b200.config import tiny_config
@@ -12,8 +13,8 @@ from titanic_flash_41_b200.serve.session_cache import SessionCache
 from titanic_flash_41_b200.serve.worker import Worker
 
 
-def _mk(regions=2, queue_limit=4, **kw):
-    cfg = tiny_config()
+def _mk(regions=2, queue_limit=4, cfg=None, **kw):
+    cfg = cfg or tiny_config()
     W = oracle.init_weights(cfg, 0)
     b = OracleBackend(cfg, W, regions=regions, max_context=512, chunk=32)
     s = Scheduler(regions, queue_limit, 2)
@@ -350,11 +351,15 @@ def test_interrupted_prefill_is_resumed_from_its_last_whole_chunk():
     assert toks(ev2) == toks(ev3) and len(toks(ev2)) == 4
 
 
-def test_relocated_conversation_continues_with_the_same_tokens():
+@pytest.mark.parametrize("mixed", [False, True])
+def test_relocated_conversation_continues_with_the_same_tokens(mixed):
     """A decoding conversation moved to another region between steps produces the tokens it would
-    have produced in place (sampling is addressed by position; the state image travels)."""
+    have produced in place (sampling is addressed by position; the state image travels).  ``mixed``:
+    two compressed streams with their own ratios, each saved with its own entry count."""
+    model = tiny_config(n_layers=3, compress_ratio=1, compress_ratios=(2, 1), kv_source_layers=(0, 1),
+                        index_source_layers=(0, 1, 2), index_topk=8) if mixed else None
     def run(move):
-        cfg, w, s = _mk(regions=2)
+        cfg, w, s = _mk(regions=2, cfg=model)
         ev = []
         g = torch.Generator().manual_seed(21)
         s.submit(_job("m", torch.randint(3, cfg.vocab, (40,), generator=g).tolist(), 24, ev, temperature=0.7, top_p=0.9,

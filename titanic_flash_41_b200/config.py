@@ -125,6 +125,8 @@ class ModelConfig(_JsonMixin):
     window: int = 32
     # sparse attention over compressed KV
     compress_ratio: int = 4            # tokens pooled per compressed entry at source layers
+    #   (with ``compress_ratios``: the finest stream's ratio, which the step metadata counts in)
+    compress_ratios: Tuple[int, ...] = ()         # one ratio per kv source layer; () = compress_ratio everywhere
     kv_source_layers: Tuple[int, ...] = (0,)      # layers owning a compressed KV stream
     index_source_layers: Tuple[int, ...] = (0,)   # layers running the indexer (others reuse)
     index_heads: int = 4
@@ -183,6 +185,11 @@ class ModelConfig(_JsonMixin):
              "every kv source layer must run an indexer")
         need(all(0 <= l < self.n_layers for l in self.index_source_layers), "index source layer range")
         need(self.compress_ratio >= 1, "compress ratio")
+        if self.compress_ratios:
+            need(len(self.compress_ratios) == len(self.kv_source_layers), "one compress ratio per kv source layer")
+            need(min(self.compress_ratios) == self.compress_ratio, "compress_ratio must be the smallest of compress_ratios")
+            need(all(r % self.compress_ratio == 0 for r in self.compress_ratios),
+                 "every compress ratio must be a multiple of the smallest")
         need(self.dense_quant in ("none", "fp8_block128", "fp8_ue8m0_32"), "dense_quant")
         need(self.expert_quant in ("none", "mxfp4"), "expert_quant")
         need(self.kv_quant in ("none", "v41"), "kv_quant")
@@ -197,6 +204,22 @@ class ModelConfig(_JsonMixin):
             if s <= layer:
                 best = max(best, s)
         return best
+
+    def ratio_of_source(self, source_layer: int) -> int:
+        """Tokens pooled per compressed entry in the stream of one kv source layer (reference:
+        ``compress_ratios`` per layer, src/config.rs:252-280: 2 for layers 2-19, 1 from layer 20)."""
+        if not self.compress_ratios:
+            return self.compress_ratio
+        return self.compress_ratios[self.kv_source_layers.index(source_layer)]
+
+    def ratio_of(self, layer: int) -> int:
+        """Ratio of the compressed stream a layer reads (the finest ratio for window-only layers)."""
+        src = self.kv_source_of(layer)
+        return self.ratio_of_source(src) if src >= 0 else self.compress_ratio
+
+    @property
+    def max_ratio(self) -> int:
+        return max(self.compress_ratios) if self.compress_ratios else self.compress_ratio
 
     def index_source_of(self, layer: int) -> int:
         best = -1
@@ -271,10 +294,10 @@ def flash_b200_config(**over) -> ModelConfig:
 
 def reference_1017_config(**over) -> ModelConfig:
     """The geometry the reference serves (tests/fixtures/1017-config.json; src/config.rs:193-296)."""
-    ratios = [0, 0] + [2] * 18 + [1] * 20
+    # per layer [0, 0] + [2] * 18 + [1] * 20: the three early sources pool pairs, layer 20 keeps every token
     kw = dict(name="DeepSeek-V4.1-Flash-1017", n_layers=40, hidden=5120, vocab=129280, n_heads=64,
               head_dim=512, q_lora_rank=1280, o_groups=8, o_lora_rank=1024, window=128,
-              compress_ratio=2, kv_source_layers=(2, 8, 14, 20),
+              compress_ratio=1, compress_ratios=(2, 2, 2, 1), kv_source_layers=(2, 8, 14, 20),
               index_source_layers=(2, 8, 14, 20, 24, 28, 32, 36), index_heads=32, index_dim=128,
               index_topk=512, candidate_blocks=2048, candidate_block=8, late_start=21,
               n_experts=384, topk=6, moe_inter=2304, n_shared=1, shared_inter=2304,
@@ -286,7 +309,6 @@ def reference_1017_config(**over) -> ModelConfig:
               draft=DraftConfig(layers=3, depth=5, condition_layers=3),
               vision=VisionConfig(), engram=EngramConfig(layers=(1, 14), rows_per_table=384_000_000))
     kw.update(over)
-    del ratios
     return ModelConfig(**kw)
 
 

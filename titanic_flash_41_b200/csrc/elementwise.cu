@@ -84,8 +84,9 @@ __global__ void add_norm_kernel(__nv_bfloat16* __restrict__ x, const void* __res
 
 // --------------------------------------------------------------------------- attention prep
 // The compressor inputs of an open group wait in a ring addressed by absolute position with
-// `ratio + kCarrySpan` slots per conversation: a speculative row up to kCarrySpan positions past
-// the committed length can then never overwrite a slot that a later, shorter re-run still needs.
+// at least `ratio + kCarrySpan` slots per conversation: a speculative row up to kCarrySpan positions
+// past the committed length can then never overwrite a slot that a later, shorter re-run still needs.
+// (Sources with different ratios may share one allocation sized for the largest: `carry_slots`.)
 constexpr int kCarrySpan = 32;
 
 struct PrepParams {
@@ -112,7 +113,8 @@ struct PrepParams {
   // compressor (source layers)
   int ratio, Di, Hi;
   const __nv_bfloat16* comp_norm_w;
-  float* carry;         // [regions][ratio][2*(Dh+Di)]
+  float* carry;         // [regions][carry_slots][2*(Dh+Di)]
+  int carry_slots;
   uint8_t* comp;        // [regions][maxC][Dh/2 + Dh/16]
   uint8_t* keys;        // [regions][maxC][Di/2 + Di/32]
   int maxC;
@@ -276,7 +278,7 @@ __global__ void attn_prep_kernel(PrepParams p) {
       return;
     }
     const int first = p.first_row[r];
-    const int CS = p.ratio + kCarrySpan;
+    const int CS = p.carry_slots;
     const float* car = p.carry + (long)reg * CS * 2 * C;
     for (int c = tid; c < C; c += blockDim.x) {
       float mx = -INFINITY;
@@ -342,7 +344,7 @@ __global__ void carry_save_kernel(PrepParams p) {
   const int group_end = (pos / p.ratio + 1) * p.ratio - 1;
   if (group_end <= p.last_pos[r]) return;
   const int C = p.Dh + p.Di;
-  const int CS = p.ratio + kCarrySpan;
+  const int CS = p.carry_slots;
   float* cs = p.carry + ((long)reg * CS + (pos % CS)) * 2 * C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     cs[c] = ldp(p, r, p.off_cv + c);
@@ -485,9 +487,11 @@ TF_API int tf_attn_prep(const void* P, int p_kind, int ldp, int T, const int* po
                         void* q_out, void* win, long win_region_stride, int win_row, int comp_row,
                         int key_row, int ring, int off_q, int off_kv,
                         int off_cv, int off_cg, int off_iq, int off_iw, int ratio, int Di, int Hi,
-                        const void* comp_norm_w, float* carry, void* comp, void* keys, int maxC,
-                        void* iq_out, float* iw_out, void* status, cudaStream_t st) {
+                        const void* comp_norm_w, float* carry, int carry_slots, void* comp, void* keys,
+                        int maxC, void* iq_out, float* iw_out, void* status, cudaStream_t st) {
   if (Dh % 32 || rope_dim > 256 || (off_cv >= 0 && Di % 32)) return -1;
+  if (carry_slots <= 0) carry_slots = ratio + kCarrySpan;
+  if (carry_slots < ratio + kCarrySpan) return -1;
   PrepParams p;
   p.P = P; p.p_kind = p_kind; p.ldp = ldp; p.T = T; p.pos = pos; p.region = region;
   p.first_row = first_row; p.last_pos = last_pos; p.Hl = Hl; p.Dh = Dh; p.rope_dim = rope_dim;
@@ -495,7 +499,7 @@ TF_API int tf_attn_prep(const void* P, int p_kind, int ldp, int T, const int* po
   p.q_out = (__nv_bfloat16*)q_out; p.win = (uint8_t*)win; p.win_region_stride = win_region_stride;
   p.ring = ring; p.win_row = win_row; p.comp_row = comp_row; p.key_row = key_row; p.off_q = off_q; p.off_kv = off_kv; p.off_cv = off_cv; p.off_cg = off_cg;
   p.off_iq = off_iq; p.off_iw = off_iw; p.ratio = ratio; p.Di = Di; p.Hi = Hi;
-  p.comp_norm_w = (const __nv_bfloat16*)comp_norm_w; p.carry = carry; p.comp = (uint8_t*)comp;
+  p.comp_norm_w = (const __nv_bfloat16*)comp_norm_w; p.carry = carry; p.carry_slots = carry_slots; p.comp = (uint8_t*)comp;
   p.keys = (uint8_t*)keys; p.maxC = maxC; p.iq_out = (__nv_bfloat16*)iq_out; p.iw_out = iw_out;
   p.st = (TfStatusWord*)status;
   const int smf = (off_cv >= 0 ? Dh + Di : Dh);

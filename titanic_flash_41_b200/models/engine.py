@@ -509,8 +509,8 @@ class Engine:
         C = cfg.head_dim + cfg.index_dim
         self.comp = torch.zeros(ns, self.regions, self.maxC, self.comp_row, **u8)
         self.keys = torch.zeros(ns, self.regions, self.maxC, self.key_row, **u8)
-        # position-addressed ring of open-group compressor inputs (ratio + 32 slots: csrc kCarrySpan)
-        self.carry = torch.zeros(ns, self.regions, cfg.compress_ratio + 32, 2 * C, dtype=torch.float32,
+        # position-addressed rings of open-group compressor inputs (largest ratio + 32 slots: csrc kCarrySpan)
+        self.carry = torch.zeros(ns, self.regions, cfg.max_ratio + 32, 2 * C, dtype=torch.float32,
                                  device=self.dev)
         self._scratch: Dict[int, dict] = {}
         self._dq_cache: Dict[int, torch.Tensor] = {}
@@ -638,6 +638,8 @@ class Engine:
         Il = cfg.shared_inter * cfg.n_shared // self.world
         b = dict(
             meta=torch.zeros(StepPlan.META_ROWS, T, **i32),
+            nvalid_m={r // cfg.compress_ratio: torch.zeros(T, **i32)
+                      for r in set(cfg.compress_ratios) if r != cfg.compress_ratio},
             x=torch.zeros(T, d, dtype=torch.bfloat16, device=dev),
             h16=torch.zeros(T, d, dtype=torch.float16, device=dev),
             hb=torch.zeros(T, d, dtype=torch.bfloat16, device=dev),
@@ -785,12 +787,16 @@ class Engine:
             q_off = self.q_col
             self._linear(b["qa16"], L.wq_b, P[:, q_off:q_off + Hl * Dh], T)
         slot = self.src_slot.get(li, 0)
+        # the stream this layer writes (a source) or reads; the step metadata and ``nmax`` count
+        # entries of the finest stream, a coarser one has 1 / mult as many
+        ratio = cfg.ratio_of(li) if li < cfg.n_layers else cfg.compress_ratio
+        mult = ratio // cfg.compress_ratio
         native.call("tf_attn_prep", P, 0 if P.dtype == torch.float32 else 1, P.stride(0), T, pos, region, first_row, last_pos, Hl, Dh,
                     cfg.rope.dim, self.freqs, self.cfreqs, L.kv_norm, cfg.rms_eps, b["q"], self.win[li],
                     self.win[li].stride(0), self.win_row, self.comp_row, self.key_row, self.ring,
                     q_off, o["kv"], o.get("cv", -1), o.get("cg", -1), o.get("iq", -1), o.get("iw", -1),
-                    cfg.compress_ratio, cfg.index_dim, cfg.index_heads, L.comp_norm,
-                    self.carry[slot] if L.is_kv_source else None,
+                    ratio, cfg.index_dim, cfg.index_heads, L.comp_norm,
+                    self.carry[slot] if L.is_kv_source else None, self.carry.shape[2],
                     self.comp[slot] if L.is_kv_source else None,
                     self.keys[slot] if L.is_kv_source else None, self.maxC, b["iq"], b["iw"],
                     self.status.t)
@@ -802,7 +808,7 @@ class Engine:
             sslot = self.src_slot[L.kv_source]
             comp = self.comp[sslot]
             if L.is_index_source:
-                self._index(L, T, b, nmax, rpg, sslot, li)
+                self._index(L, T, b, nmax // mult, rpg, sslot, li, b["meta"][5] if mult == 1 else b["nvalid_m"][mult])
             sel, selcnt = b["sel"][L.index_source], b["selcnt"][L.index_source]
         nsplit = b["part_o"].shape[1]
         native.call("tf_sparse_attention", b["q"], T, Hl, Dh, pos, region, b["meta"][6], self.win[li],
@@ -932,9 +938,11 @@ class Engine:
         b["pending"] = False
 
     def _index(self, L: LayerWeights, T: int, b: dict, nmax: int, rows_per_group: int, sslot: int,
-               li: int) -> None:
+               li: int, nvalid: torch.Tensor) -> None:
+        """``nmax`` / ``nvalid``: entries of THIS layer's compressed stream (largest over the rows /
+        per row)."""
         cfg = self.cfg
-        region, nvalid = b["meta"][2], b["meta"][5]
+        region = b["meta"][2]
         sel, selcnt = b["sel"][li], b["selcnt"][li]
         if nmax == 0:
             sel.fill_(-1)
@@ -1220,6 +1228,10 @@ class Engine:
         if self.engram and b.get("eg_hash"):
             self._engram_hash(T, b)
         b["cand"] = None               # candidate blocks are published and consumed within one launch
+        if cfg.max_ratio != cfg.compress_ratio:
+            # valid entries per row in the coarser streams (the metadata counts the finest one)
+            for m, t in b["nvalid_m"].items():
+                torch.div(b["meta"][5], m, rounding_mode="floor", out=t)
         if x_in is None:
             e = b["e"] if cfg.hc_mult > 1 else b["x"]
             native.call("tf_embed", b["meta"][0], self.embed_w, e, T, cfg.hidden, cfg.vocab, self.status.t)

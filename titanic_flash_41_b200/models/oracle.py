@@ -397,7 +397,7 @@ class OracleModel:
         win[p0:p1] = kv.to(win.dtype)
 
         # compressor at source layers --------------------------------------------------
-        r = cfg.compress_ratio
+        r = cfg.compress_ratio if draft else cfg.ratio_of(layer)     # of the stream this layer writes or reads
         if (not draft) and layer in cfg.kv_source_layers:
             C = Dh + cfg.index_dim
             cv = h @ W[f"{p}.attn.compressor.wkv.weight"].t()

@@ -79,14 +79,14 @@ class SpPrefill:
 
     # ------------------------------------------------------------------------------------------
     def rows_per_rank(self, T: int) -> int:
-        r = self.eng.cfg.compress_ratio
+        r = self.eng.cfg.max_ratio            # slices begin on a group boundary of every stream
         per = -(-T // self.W)
         return -(-per // r) * r
 
     def usable(self, start: int, n: int) -> bool:
         """Chunks must begin on a compressor-group boundary and leave every rank at least the small-M
         limit of rows (shorter prompts take the tensor-parallel path)."""
-        return start % self.eng.cfg.compress_ratio == 0 and n >= self.W * 2 * Engine.SMALL_M
+        return start % self.eng.cfg.max_ratio == 0 and n >= self.W * 2 * Engine.SMALL_M
 
     def bounds(self, T: int) -> Tuple[int, int, int]:
         """(first row, end row, rows per rank) of this rank's slice of a chunk of T rows."""
@@ -128,7 +128,7 @@ class SpPrefill:
         if not L.is_kv_source:
             return
         # compressed entries and index keys completed inside the chunk: entry e = position // ratio
-        r = cfg.compress_ratio
+        r = cfg.ratio_of_source(li)
         slot = eng.src_slot[li]
         eq = tq // r
         e0 = p0 // r
@@ -243,7 +243,7 @@ class SpPrefill:
     def chunk_sizes(self, n: int, chunk: int) -> list:
         """Near-equal chunks whose sizes are multiples of world x compression ratio (so that every
         rank's slice of every chunk but the last is full and ends on a group boundary)."""
-        unit = self.W * self.eng.cfg.compress_ratio
+        unit = self.W * self.eng.cfg.max_ratio
         # a chunk may span `sp_chunk_rows` rows over all ranks as long as every rank's slice fits the
         # row buffers of a single-rank chunk and the whole chunk fits the window ring
         eng = self.eng

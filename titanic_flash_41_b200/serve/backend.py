@@ -112,16 +112,16 @@ class OracleBackend:
     # ---- state images ------------------------------------------------------------------------
     def _views(self, region: int, length: int) -> List[Tuple[str, torch.Tensor]]:
         s = self.sessions[region]
-        r = self.cfg.compress_ratio
+        ratio = lambda k: self.cfg.ratio_of_source(int(k.rsplit(".", 1)[1]))      # key: "layers.<source layer>"
         out = []
         for k, t in s.window.items():
             out.append((f"swa.{k}", t[max(0, length - self.cfg.window - 8):length]))
         for k, t in s.comp.items():
-            out.append((f"compressed.{k}.kv", t[: length // r]))
+            out.append((f"compressed.{k}.kv", t[: length // ratio(k)]))
         for k, t in s.keys.items():
-            out.append((f"compressed.{k}.keys", t[: length // r]))
+            out.append((f"compressed.{k}.keys", t[: length // ratio(k)]))
         for k, t in s.carry.items():
-            out.append((f"compressed.{k}.carry", t[length // r * r:length]))
+            out.append((f"compressed.{k}.carry", t[length // ratio(k) * ratio(k):length]))
         if self.hidden[region] is not None:
             out.append(("hidden", self.hidden[region]))
         return out
@@ -133,7 +133,6 @@ class OracleBackend:
         self.reset(region)
         s = self.sessions[region]
         n = img.length
-        r = self.cfg.compress_ratio
         for name, flat in img.regions:
             t = flat.view(torch.float32)
             if name == "hidden":
@@ -146,6 +145,7 @@ class OracleBackend:
                 buf[lo:n] = t.reshape(n - lo, -1)
             else:
                 key, what = key.rsplit(".", 1)
+                r = self.cfg.ratio_of_source(int(key.rsplit(".", 1)[1]))
                 if what == "kv":
                     s.buf(s.comp, key, s.max_tokens // r + 1, self.cfg.head_dim)[: n // r] = t.reshape(n // r, -1)
                 elif what == "keys":
@@ -230,10 +230,11 @@ class EngineBackend:
         keep = min(length, cfg.window + 64)
         slots = torch.arange(length - keep, length, device=e.dev) % e.ring
         out.append(("swa", e.win[:, region][:, slots]))
-        nC = length // cfg.compress_ratio
-        out.append(("compressed.kv", e.comp[:, region, :nC]))
-        out.append(("compressed.keys", e.keys[:, region, :nC]))
-        out.append(("compressed.carry", e.carry[:, region]))
+        for slot, src in enumerate(cfg.kv_source_layers):
+            nC = length // cfg.ratio_of_source(src)
+            out.append((f"compressed.kv.{slot}", e.comp[slot, region, :nC]))
+            out.append((f"compressed.keys.{slot}", e.keys[slot, region, :nC]))
+            out.append((f"compressed.carry.{slot}", e.carry[slot, region]))
         h = self.last_hidden_rows.get(region)
         if h is not None:
             out.append(("hidden", h))
@@ -252,11 +253,14 @@ class EngineBackend:
                 keep = min(n, cfg.window + 64)
                 slots = torch.arange(n - keep, n, device=e.dev) % e.ring
                 e.win[:, region][:, slots] = flat.view(e.win.shape[0], keep, e.win_row)
-            elif name == "compressed.kv":
-                e.comp[:, region, : n // cfg.compress_ratio] = flat.view(e.comp.shape[0], -1, e.comp_row)
-            elif name == "compressed.keys":
-                e.keys[:, region, : n // cfg.compress_ratio] = flat.view(e.keys.shape[0], -1, e.key_row)
-            elif name == "compressed.carry":
-                e.carry[:, region] = flat.view(torch.float32).view(e.carry[:, region].shape)
+            elif name.startswith("compressed."):
+                what, slot = name.split(".")[1], int(name.split(".")[2])
+                nC = n // cfg.ratio_of_source(cfg.kv_source_layers[slot])
+                if what == "kv":
+                    e.comp[slot, region, :nC] = flat.view(nC, e.comp_row)
+                elif what == "keys":
+                    e.keys[slot, region, :nC] = flat.view(nC, e.key_row)
+                else:
+                    e.carry[slot, region] = flat.view(torch.float32).view(e.carry[slot, region].shape)
             elif name == "hidden":
                 self.last_hidden_rows[region] = flat.view(torch.bfloat16).clone()
