@@ -493,6 +493,68 @@ def test_draft_head_with_markov_correction_matches_oracle():
     assert bias.abs().max() > 0.5
 
 
+@pytest.mark.parametrize("hc", [1, 4])
+def test_confidence_head_and_causal_stopping_in_the_decode_graph(hc):
+    """The drafter's confidences against the oracle, the device's stopping rule against the host rule
+    on the same confidences, never more accepted than verified, and (sharp law) the same text
+    whatever the ladder."""
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    from titanic_flash_41_b200.spec.verify import causal_rows
+    # every expert routed: no discrete flips between the engine and the oracle
+    mk = lambda ladder: small_config(topk=8, hc_mult=hc, draft=DraftConfig(layers=1, depth=3, markov_rank=256,
+                                                                           confidence_head=True, confidence_ladder=ladder))
+    cfg = mk((0.15, 0.25, 0.20))
+    W = oracle.init_weights(cfg, 0)
+    rt = {}
+    ecfg = EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,))
+    eng = E.Engine.from_weights(cfg, ecfg, W, roundtrip=rt)
+    ref = oracle.OracleModel(cfg, rt)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab, (60,), generator=g)
+    s = ref.new_session(256)
+    ref.forward(prompt, s)
+    hid_ref = ref.last_hidden[-1:].clone()
+    eng.forward(E.StepPlan.build([(0, 0, prompt.tolist())], logits="last"))
+    hid = eng.last_hidden[-1:].clone()
+    toks = [11, 900, 5, 1300, 77, 1999]
+    conf = torch.zeros(1, 3, device="cuda")
+    cum, nver = torch.zeros(1, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda")
+    ladder = torch.tensor([0.15, 0.25, 0.20], device="cuda")
+    want, got = [], []
+    for t in toks:
+        _, x = ref.draft_forward(torch.tensor([t]), hid_ref, s, 60)
+        want.append(float(ref.draft_confidence(torch.tensor([t]), x)[0]))
+        b = eng._bufs(1)
+        eng.upload_plan(E.StepPlan.build([(0, 60, [t])]), b)
+        eng.draft_run(1, b, hid, torch.arange(1, device="cuda"))
+        eng.draft_confidence(1, b, 0, 3, ladder, conf, cum, nver)
+        got.append(float(conf[0, 0]))
+        assert int(nver[0]) == 1 and float(cum[0]) == got[-1]
+    eng.status.check()
+    want, got = torch.tensor(want), torch.tensor(got)
+    assert (want - got).abs().max() < 0.08, (want, got)
+    assert want.std() > 0.05                                     # the head is not a constant
+    # the decode loop: rule on the device == rule on the host, accepted <= verified
+    texts, stopped = [], 0
+    for lad in ((0.15, 0.25, 0.20), (0.0,), (2.0,)):
+        e = E.Engine.from_weights(mk(lad), ecfg, W)
+        lg = e.forward(E.StepPlan.build([(0, 0, prompt.tolist())], logits="last"))
+        sl = DecodeSlot(region=0, length=60, anchor=int(lg.argmax()), seed=3, temperature=0.0, top_p=1.0)
+        dec = SpecDecoder(e, 1, use_graph=True)
+        assert dec.causal
+        dec.hidden.copy_(e.last_hidden[-1:])
+        while len(sl.emitted) < 20:
+            n = len(dec.step([sl])[0])
+            assert len(sl.confidence) == 3 and sl.verified == causal_rows(sl.confidence, lad)
+            assert n - 1 <= sl.verified
+            stopped += sl.verified < 3
+        e.status.check()
+        texts.append(sl.emitted[:20])
+    assert texts[0] == texts[1] == texts[2]
+    assert stopped > 0
+
+
 def test_draft_subset_head_in_four_bits_matches_oracle_and_proposes_subset_tokens():
     """The drafter's vocabulary-subset head: MXFP4 rows x MXFP8 activations on the block-scaled GEMV."""
     from titanic_flash_41_b200.config import DraftConfig

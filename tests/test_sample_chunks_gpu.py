@@ -28,7 +28,7 @@ class Flow:
         self.sb = native.lib().tf_rowstat_bytes()
         self.st = native.StatusWord(DEV)
 
-    def run(self, tl, dl, u_draft, u_ver, temp, topp, point_props=None):
+    def run(self, tl, dl, u_draft, u_ver, temp, topp, point_props=None, sess_g=None):
         """tl [S, g+1, V], dl [S, g, V] full rows.  Returns (props, dstat, tstat, n_accept, token) of
         rank 0 after checking that every rank produced the same."""
         S, g, R, V, W, sb = self.S, self.g, self.R, self.V, self.world, self.sb
@@ -56,7 +56,7 @@ class Flow:
             props[:] = point_props[None]
         self.ws.sample(tls, dls, dstat[0] if (g > 0 and not point) else None, props[0] if g > 0 else None, u_ver, g + 2,
                        temp, topp, S, g, Vl, tstat, 1, nacc, tok, 1, self.st.t, point_mass=point,
-                       emu_strides=(S * R * Vl, S * g * Vl, S * R, S, S))
+                       emu_strides=(S * R * Vl, S * g * Vl, S * R, S, S), sess_g=sess_g)
         torch.cuda.synchronize()
         self.st.check()
         for r in range(W):
@@ -182,3 +182,28 @@ def test_point_mass_proposals_and_bad_arguments():
     assert native.lib().tf_sample_chunks_count(1000) == 0      # 1000 / 8 = 125 is not a multiple of 4
     with pytest.raises(ValueError):
         SampleWorkspace(1000, 4, DEV)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_per_conversation_block_lengths_equal_shorter_blocks(world):
+    """Causal stopping: a conversation that verifies only its first k proposals commits exactly what a
+    block of k proposals commits (row k is its bonus row, later rows are ignored), inside one launch
+    with conversations of other lengths."""
+    V, S, g = 4096, 4, 3
+    tl, dl, u_d, u_v = _inputs(S, g, V, seed=11)
+    temp = torch.full((S,), 0.8, device=DEV)
+    topp = torch.full((S,), 0.95, device=DEV)
+    lens = torch.tensor([1, 2, 3, 2], dtype=torch.int32, device=DEV)
+    props, _, _, nacc, tok = Flow(V, S, g, world).run(tl, dl, u_d, u_v, temp, topp, sess_g=lens)
+    full = Flow(V, S, g, world).run(tl, dl, u_d, u_v, temp, topp)
+    assert bool((nacc <= lens).all())
+    differs = False
+    for s in range(S):
+        k = int(lens[s])
+        uv = torch.cat([u_v[s:s + 1, :k], u_v[s:s + 1, g:g + 1], u_v[s:s + 1, g + 1:g + 2]], 1).contiguous()
+        p1, _, _, n1, t1 = Flow(V, 1, k, world).run(tl[s:s + 1, :k + 1].contiguous(), dl[s:s + 1, :k].contiguous(),
+                                                      u_d[s:s + 1].contiguous(), uv, temp[s:s + 1], topp[s:s + 1])
+        assert torch.equal(p1[0, :k], props[s, :k])
+        assert int(n1[0]) == int(nacc[s]) and int(t1[0]) == int(tok[s]), (s, k)
+        differs |= k < g and (int(full[3][s]) != int(nacc[s]) or int(full[4][s]) != int(tok[s]))
+    assert differs            # the shorter blocks are not what the full blocks would have committed

@@ -111,3 +111,63 @@ def test_recent_rows_and_prefill_seams_for_engram_models():
     # models without Engram layers: the plan is left alone
     plain = tiny_config()
     assert _recent(StepPlan.build([(0, 0, [1, 2])]), plain, [], toks, 0).engram_recent is None
+
+
+def test_causal_ladder_uses_only_the_confidences_before_each_admitted_proposal():
+    """Proposal 1 is always verified; proposal j only while the running products c1..ci (i <= j) clear
+    their thresholds; changing a confidence after the one that stopped changes nothing; NaN stops."""
+    from titanic_flash_41_b200.spec.verify import causal_rows
+    ladder = (0.15, 0.25, 0.20, 0.15)
+    assert causal_rows([], ladder) == 0
+    assert causal_rows([0.01, 0.99, 0.99], ladder) == 1            # c1 c2 = 0.0099 < 0.15
+    assert causal_rows([0.9, 0.9, 0.9, 0.9, 0.9], ladder) == 5     # 0.81, 0.729, 0.656, 0.59
+    assert causal_rows([0.9, 0.5, 0.5, 0.99, 0.99], ladder) == 2   # 0.45 >= 0.15; 0.225 < 0.25
+    assert causal_rows([0.9, 0.5, 0.6, 0.6, 0.99], ladder) == 3    # 0.45, 0.27 >= 0.25, 0.162 < 0.20
+    assert causal_rows([0.9, float("nan"), 0.9], ladder) == 1
+    base = [0.9, 0.5, 0.5, 0.3, 0.3]
+    n = causal_rows(base, ladder)
+    for later in range(n + 1, len(base)):
+        for v in (0.0, 1.0):
+            alt = list(base)
+            alt[later] = v
+            assert causal_rows(alt, ladder) == n
+    # a short ladder repeats its last threshold
+    assert causal_rows([0.9, 0.9, 0.9, 0.9], (0.5,)) == 4 and causal_rows([0.9, 0.9, 0.6, 0.9], (0.5,)) == 2
+
+
+def test_confidence_head_stops_blocks_early_and_greedy_text_is_unchanged():
+    """Oracle backend with a confidence head: rounds verify fewer proposals when the running product
+    drops under the ladder, every round records its confidences, and at temperature 0 the text is the
+    plain greedy text whatever the ladder."""
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.serve.backend import OracleBackend
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot
+
+    def run(ladder, temperature):
+        cfg = tiny_config(draft=DraftConfig(layers=1, depth=3, confidence_head=True, markov_rank=8,
+                                            confidence_ladder=ladder))
+        W = oracle.init_weights(cfg, 0)
+        assert W["mtp.0.confidence_head.proj.weight"].shape == (1, cfg.hidden + 8)
+        b = OracleBackend(cfg, W, regions=1, max_context=256, chunk=32)
+        prompt = torch.randint(3, cfg.vocab, (30,), generator=torch.Generator().manual_seed(2)).tolist()
+        lg = b.prefill(0, prompt, 0, None)
+        sl = DecodeSlot(region=0, length=30, anchor=b.sample(lg, temperature, 1.0, 7, 30), seed=7,
+                        temperature=temperature, top_p=1.0)
+        rounds = []
+        while len(sl.emitted) < 24:
+            toks = b.decode_step([sl])[0]
+            assert 1 <= len(sl.confidence) <= 3 and all(0.0 < c < 1.0 for c in sl.confidence)
+            rounds.append((len(toks), list(sl.confidence)))
+        return sl.emitted[:24], rounds
+    never, r_never = run((0.0,), 0.0)          # thresholds of zero: every proposal is verified
+    always, r_always = run((2.0,), 0.0)        # unreachable thresholds: one proposal per round
+    prod, r_prod = run((0.15, 0.25, 0.20), 0.0)
+    assert never == always == prod
+    assert all(len(c) == 3 for _, c in r_never) and all(len(c) == 2 and n <= 2 for n, c in r_always)
+    from titanic_flash_41_b200.spec.verify import causal_rows
+    for n, c in r_prod:
+        # the drafter stopped exactly where the rule says (the last confidence is the one that failed)
+        assert n <= len(c) + 1 and (len(c) == 3 or causal_rows(c, (0.15, 0.25, 0.20)) == len(c) - 1)
+    # sampling: still runs and still commits at least the anchor every round
+    sampled, r_s = run((0.15, 0.25, 0.20), 0.8)
+    assert len(sampled) == 24 and all(n >= 1 for n, _ in r_s)

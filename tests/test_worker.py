@@ -375,3 +375,16 @@ def test_relocated_conversation_continues_with_the_same_tokens(mixed):
         return [t for _, k, p in ev if k == "tokens" for t in p], [p["finish_reason"] for _, k, p in ev if k == "done"]
     a, b = run(False), run(True)
     assert a == b and len(a[0]) == 24 and a[1] == ["length"]
+
+
+def test_worker_logs_the_drafters_confidences_per_round_when_asked():
+    from titanic_flash_41_b200.config import DraftConfig
+    cfg = tiny_config(draft=DraftConfig(layers=1, depth=3, confidence_head=True))
+    _, w, s = _mk(regions=1, cfg=cfg, log_confidence=True)
+    ev = []
+    s.submit(_job("c", torch.randint(3, cfg.vocab, (20,), generator=torch.Generator().manual_seed(4)).tolist(), 10, ev))
+    _drain(w)
+    rounds = [e for e in w.log.snapshot(4096)["events"] if e["kind"] == "step_confidence"]
+    assert rounds and all(1 <= e["verified"] <= 3 and e["emitted"] <= e["verified"] + 1 and
+                          len(e["confidence"]) >= e["verified"] for e in rounds)
+    assert not any("token" in k for e in rounds for k in e)

@@ -49,6 +49,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--disk-cache", help="directory for the disk tier of the session cache")
     s.add_argument("--event-log", help="JSONL event log path")
     s.add_argument("--no-self-check", action="store_true", help="skip the start-up reproducibility check")
+    s.add_argument("--log-confidence", action="store_true", help="event per decode round with the drafter's confidences "
+                   "and the proposals verified (models with a confidence head)")
     s.add_argument("--vision", action="store_true", help="accept image parts (the model config must describe a vision "
                    "tower; random tower weights when the checkpoint has none)")
     s.add_argument("--memory-floor-gib", type=float, default=4.0, help="host memory that must stay available; "
@@ -217,7 +219,7 @@ def serve_main(args) -> int:
     from .utils.health import Health, Watchdog, control_probe, status_probe
     health = Health()
     worker = Worker(backend, sched, SessionCache(), eos_id=getattr(tok, "eos_id", 1), log=log, control=control, rank=rank,
-                    span_encoder=span_encoder, health=health)
+                    span_encoder=span_encoder, health=health, log_confidence=getattr(args, "log_confidence", False))
     probes = {"control": control_probe(control)}
     if hasattr(backend, "status_snapshot"):
         probes["device"] = status_probe(backend.status_snapshot)

@@ -80,7 +80,8 @@ class DraftConfig(_JsonMixin):
     depth: int = 3                     # proposals per verification round
     condition_layers: int = 1          # last N target layers whose output feeds the draft
     temperature: float = 0.7           # proposal temperature when sampling
-    confidence_ladder: Tuple[float, ...] = (0.15, 0.25, 0.20, 0.15)
+    confidence_head: bool = False      # the drafter scores each proposal before it is verified (causal stopping)
+    confidence_ladder: Tuple[float, ...] = (0.15, 0.25, 0.20, 0.15)    # thresholds of proposals 2, 3, ... on the running product
     markov_rank: int = 0               # rank of the Markov (bigram) correction of the draft logits; 0 = none (reference: 256)
     subset_rows: int = 0               # 4-bit vocabulary-subset head of the drafter: it proposes only these many tokens (multiple of 128; 0 = whole vocabulary; reference: 61 % of the vocabulary)
 
@@ -306,7 +307,7 @@ def reference_1017_config(**over) -> ModelConfig:
               rope=RopeConfig(theta=10000.0, compress_theta=160000.0, dim=64, factor=16.0,
                               beta_fast=32.0, beta_slow=1.0, original_max_position=65536),
               dense_quant="fp8_ue8m0_32", expert_quant="mxfp4", kv_quant="v41",
-              draft=DraftConfig(layers=3, depth=5, condition_layers=3),
+              draft=DraftConfig(layers=3, depth=5, condition_layers=3, markov_rank=256, confidence_head=True),
               vision=VisionConfig(), engram=EngramConfig(layers=(1, 14), rows_per_table=384_000_000))
     kw.update(over)
     return ModelConfig(**kw)

@@ -69,6 +69,8 @@ struct ChunkParams {
   const int* sess_point;    // [S] or null: 1 = this conversation's proposals are point masses (copy proposals)
   const int* forced;        // g = 0 only, [S] at forced[s * tok_stride] or null: conversations flagged in
                             // sess_point emit this token instead of the draw (their proposal is known)
+  const int* sess_g;        // [S] or null: conversation s verifies only its first sess_g[s] proposals (1..g); the
+                            // row after them is its bonus row and later rows are ignored (causal stopping)
   RowStat* tstat;           // out: statistics of the target rows, row r at tstat[r * stat_stride]
   int stat_stride;
   int* n_accept;            // out [S] (may be null)
@@ -179,7 +181,10 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   const int n = p.chunk;
   const float* trow = p.tlogits + ez * p.emu_tl + (long)row * p.ldl + (long)lc * n;
   const bool point = p.point_mass || (p.sess_point && p.sess_point[s]);
-  const bool has_d = (i < g) && p.dlogits != nullptr && !point;
+  // proposals this conversation verifies: rows past its bonus row still publish (every CTA of the
+  // block takes part in the exchanges) but nothing reads what they publish
+  const int gs = (g > 0 && p.sess_g) ? min(max(p.sess_g[s], 1), g) : g;
+  const bool has_d = (i < gs) && p.dlogits != nullptr && !point;
   const float* drow = has_d ? p.dlogits + ez * p.emu_dl + (long)(s * g + i) * p.ldl + (long)lc * n : nullptr;
   for (int k = threadIdx.x * 4; k < n; k += kThreads * 4) {
     *reinterpret_cast<float4*>(tbuf + k) = *reinterpret_cast<const float4*>(trow + k);
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   RowStat ds;
   float d_inv = inv_t;
   ds.m = 0.f; ds.thr = 0; ds.z = 1.0;
-  if (i < g && !point && p.dstat) ds = p.dstat[s * g + i];
+  if (has_d && p.dstat) ds = p.dstat[s * g + i];
   if (g > 0) {
     if (i < g && threadIdx.x == 0) {
       const int x = p.proposals[s * g + i];
@@ -370,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
   // ---- 4. residual mass of this chunk: max(w_i p_i(v) - q_i(v), 0); the bonus row has q = 0
   const double wz = wrow[i] / stat.z;
   const double qz = has_d ? 1.0 / ds.z : 0.0;
-  const int point_tok = (i < g && point) ? p.proposals[s * g + i] : -1;
+  const int point_tok = (i < gs && point) ? p.proposals[s * g + i] : -1;
   auto residual = [&](int k) -> double {
     const float l = tbuf[k];
     double val = fkey(l) >= stat.thr ? wz * (double)expf((l - stat.m) * inv_t) : 0.0;
@@ -409,10 +414,10 @@ __global__ void __launch_bounds__(kThreads, 1) sample_chunks_kernel(const ChunkP
     }
     const double* u = p.uniforms + (long)s * p.u_stride;
     int tau = 0;
-    for (int ii = 1; ii <= g; ++ii) {
+    for (int ii = 1; ii <= gs; ++ii) {
       const double Rr = Rrow[ii], w = wrow[ii];
       if (!(Rr >= 0.0) || isinf(Rr)) tf_report(p.st, TF_NONFINITE, 21, s, ii);
-      const double h = (ii < g) ? (Rr + 1.0 - w > 0.0 ? Rr / (Rr + 1.0 - w) : 0.0) : w;
+      const double h = (ii < gs) ? (Rr + 1.0 - w > 0.0 ? Rr / (Rr + 1.0 - w) : 0.0) : w;
       if (u[ii - 1] < h) tau = ii;
     }
     s_tau = tau;
@@ -518,14 +523,15 @@ TF_API long tf_sample_chunks_workspace_bytes(int V, int max_rows) {
 // One launch = row statistics + block verification (g > 0) or plain sampling (g = 0) of S
 // conversations; see the header of this file.  sess_point [S] (optional) flags conversations whose
 // proposals are point masses (copy proposals found on the host); in a g = 0 launch such a
-// conversation emits forced[s * tok_stride] instead of its draw.  `ctr`: world_emulated * max_rows * (P / world) zeroed
+// conversation emits forced[s * tok_stride] instead of its draw.  sess_g [S] (optional, g > 0): how many of its
+// proposals each conversation verifies (1..g).  `ctr`: world_emulated * max_rows * (P / world) zeroed
 // ints of this rank.  ranks_emulated > 1 runs that many ranks in one cooperative launch on this GPU
 // (peers then names areas of this device; emu_* are the element strides between the ranks' logits and
 // output arrays; proposals and dstat are shared by the emulated ranks).
 TF_API int tf_sample_chunks(const float* tlogits, const float* dlogits, const void* dstat, const int* proposals,
                             const double* uniforms, int u_stride, const float* sess_temp, const float* sess_top_p,
                             int S, int g, int V, int ldl, int point_mass, const int* sess_point, const int* forced,
-                            void* tstat, int stat_stride, int* n_accept,
+                            const int* sess_g, void* tstat, int stat_stride, int* n_accept,
                             int* next_token, int tok_stride, const void* peers, int world, int rank, int max_rows,
                             void* ctr, int spin_limit, void* status, int ranks_emulated, long emu_tl, long emu_dl,
                             long emu_stat, long emu_tok, long emu_acc, cudaStream_t st) {
@@ -542,7 +548,7 @@ TF_API int tf_sample_chunks(const float* tlogits, const float* dlogits, const vo
   p.tlogits = tlogits; p.dlogits = dlogits; p.dstat = (const RowStat*)dstat; p.proposals = proposals;
   p.uniforms = uniforms; p.u_stride = u_stride; p.sess_temp = sess_temp; p.sess_top_p = sess_top_p;
   p.S = S; p.g = g; p.V = V; p.ldl = ldl; p.chunk = chunk; p.P = P; p.csplit = csplit; p.point_mass = point_mass;
-  p.sess_point = sess_point; p.forced = forced;
+  p.sess_point = sess_point; p.forced = forced; p.sess_g = sess_g;
   p.tstat = (RowStat*)tstat; p.stat_stride = stat_stride; p.n_accept = n_accept; p.next_token = next_token;
   p.tok_stride = tok_stride; p.peers = (const unsigned long long*)peers; p.world = world; p.rank = rank;
   p.max_rows = max_rows; p.ctr = (unsigned int*)ctr; p.spin_limit = spin_limit; p.st = (TfStatusWord*)status;

@@ -72,6 +72,11 @@ def classify(name: str, shape: Tuple[int, ...], cfg: ModelConfig, rank: int, wor
     return Placement("replicated")
 
 
+def confidence_name(cfg: ModelConfig) -> str:
+    """Tensor of the drafter's confidence head, owned by the last draft stage."""
+    return f"mtp.{cfg.draft.layers - 1}.confidence_head.proj.weight"
+
+
 def markov_prefix(cfg: ModelConfig) -> str:
     """Tensor-name prefix of the Markov correction head: it belongs to the last draft stage."""
     return f"mtp.{cfg.draft.layers - 1}.markov_head"
@@ -113,6 +118,10 @@ def expected_tensors(cfg: ModelConfig) -> List[Tuple[str, str, Tuple[int, ...]]]
         mk = markov_prefix(cfg)
         out.append((f"{mk}.embed.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
         out.append((f"{mk}.head.weight", "BF16", (cfg.vocab, cfg.draft.markov_rank)))
+    if n_draft and cfg.draft.confidence_head:
+        # one row over [hidden state of the draft pass ; Markov embedding of the token it was fed]
+        # (reference: mtp.2.confidence_head.proj.weight [1, 5376], src/layout.rs:367)
+        out.append((confidence_name(cfg), "BF16", (1, d + cfg.draft.markov_rank)))
     if cfg.engram is not None and cfg.engram.layers:
         # hashed n-gram memory (reference: src/layout.rs:277-292, src/engram_gpu.rs:174-183): the row
         # store as MXFP8 (e4m3 values + one UE8M0 per 32), the projection, the gate weights

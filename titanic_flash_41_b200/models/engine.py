@@ -557,6 +557,10 @@ class Engine:
                 extra["markov_embed"] = W[f"{mk}.embed.weight"].to(device, torch.bfloat16).contiguous()
                 extra["markov_head"] = W[f"{mk}.head.weight"][comm.rank * Vm:(comm.rank + 1) * Vm].to(
                     device, torch.bfloat16).contiguous()
+            if cfg.draft.confidence_head:
+                # stored bf16, widened to fp32 once (the reference does the same at load)
+                extra["confidence"] = W[f"mtp.{cfg.draft.layers - 1}.confidence_head.proj.weight"].to(
+                    device, torch.bfloat16).to(torch.float32).reshape(-1).contiguous()
         if cfg.hc_mult > 1:
             extra = dict(extra, hc_head=tuple(W[k].to(device, torch.float32).contiguous()
                                               for k in ("hc_head_fn", "hc_head_base", "hc_head_scale")))
@@ -616,6 +620,9 @@ class Engine:
             m = cfg.hc_mult
             extra["hc_head"] = ((torch.randn(m, m * d, generator=g, device=device) * cfg.init_std).contiguous(),
                                 torch.zeros(m, device=device), torch.ones(1, device=device))
+        if cfg.draft is not None and cfg.draft.confidence_head:
+            extra["confidence"] = (torch.randn(d + cfg.draft.markov_rank, generator=g, device=device)
+                                   * (2.0 / math.sqrt(d))).contiguous()
         return cls(cfg, ecfg, layers, embed, head, torch.ones(d, dtype=torch.bfloat16, device=device),
                    comm, device, max_chunk, drafts, extra)
 
@@ -1381,6 +1388,18 @@ class Engine:
         if logits is not None and "markov_head" in ex:
             logits = logits + self._markov_bias(T, b, local_logits)[logit_rows]
         return logits
+
+    def draft_confidence(self, T: int, b: dict, j: int, g: int, ladder: torch.Tensor, conf: torch.Tensor,
+                         cum: torch.Tensor, verify: torch.Tensor) -> None:
+        """After ``draft_run`` of pass ``j``: the confidence of the proposal about to be sampled,
+        ``conf[:, j]``, and the causal stopping rule (``verify``: proposals each conversation will have
+        verified; ``csrc/confidence.cu``).  Features: the pass's residual stream before the final norm
+        (the collapsed copies with hc_mult > 1) and the Markov embedding of the token it was fed."""
+        cfg, ex = self.cfg, self.draft_extra
+        x = b["v"] if cfg.hc_mult > 1 else b["x"]
+        lat = b.get("mk_lat") if cfg.draft.markov_rank else None
+        native.call("tf_draft_confidence", x, 1, x.stride(0), lat, cfg.draft.markov_rank, ex["confidence"], ladder,
+                    ladder.numel(), j, g, conf, cum, verify, T, cfg.hidden)
 
     def _markov_bias(self, T: int, b: dict, local: bool = False) -> torch.Tensor:
         """Markov correction of the draft logits: bias[r, :] = head_m @ embed_m[token of row r], the

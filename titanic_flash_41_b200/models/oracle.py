@@ -227,6 +227,10 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32) -> Dict[s
                 mat(f"{mk}.embed.weight", cfg.vocab, cfg.draft.markov_rank, std=1.0)
                 mat(f"{mk}.head.weight", cfg.vocab, cfg.draft.markov_rank,
                     std=1.0 / math.sqrt(cfg.draft.markov_rank))
+            if cfg.draft.confidence_head:
+                # (reference: mtp.2.confidence_head.proj.weight [1, hidden + Markov rank])
+                mat(f"mtp.{cfg.draft.layers - 1}.confidence_head.proj.weight", 1, d + cfg.draft.markov_rank,
+                    std=2.0 / math.sqrt(d))
     if cfg.engram is not None and cfg.engram.layers:
         # hashed n-gram memory: one table per Engram layer (values exactly representable in the packed
         # MXFP8 row format), the projection of the looked-up rows to (copies + 1) x hidden, gate weights
@@ -643,6 +647,28 @@ class OracleModel:
             bias = (lat @ W[f"{mk}.head.weight"].t()).to(torch.float32)
             logits = logits + self.comm.all_gather(bias, dim=1)
         return logits, x
+
+
+def _draft_confidence(self, tokens: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """Confidence of the proposal each draft row is about to make, [T] in (0, 1): a sigmoid over
+    [residual stream of the draft pass before the final norm ; Markov embedding of the token the row
+    was fed] (reference: kernels/dspark_confidence_fused.cuh; weights widened to fp32)."""
+    cfg, W = self.cfg, self.W
+    if cfg.hc_mult > 1:
+        T = x.shape[0]
+        flat = x.reshape(T, -1).to(torch.float32)
+        inv = torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + cfg.rms_eps)
+        pre = torch.sigmoid((flat @ W["hc_head_fn"].t()) * inv * W["hc_head_scale"][0] + W["hc_head_base"]) + cfg.hc_eps
+        x = hc_collapse(x, pre)
+    feat = x.to(torch.bfloat16).to(torch.float32)
+    if cfg.draft.markov_rank:
+        lat = W[f"mtp.{cfg.draft.layers - 1}.markov_head.embed.weight"][tokens.long()]
+        feat = torch.cat([feat, lat.to(torch.bfloat16).to(torch.float32)], -1)
+    w = W[f"mtp.{cfg.draft.layers - 1}.confidence_head.proj.weight"].to(torch.bfloat16).to(torch.float32)
+    return torch.sigmoid(feat @ w.reshape(-1))
+
+
+OracleModel.draft_confidence = _draft_confidence
 
 
 def greedy_generate(model: OracleModel, prompts: Sequence[torch.Tensor], steps: int

@@ -26,7 +26,7 @@ import torch
 
 from ..config import EngineConfig, ModelConfig
 from ..formats import codecs
-from ..formats.layout import RankPlan, markov_prefix, validate_checkpoint
+from ..formats.layout import RankPlan, confidence_name, markov_prefix, validate_checkpoint
 from ..formats.safetensors import Checkpoint, CheckpointError
 from . import engine as E
 
@@ -242,6 +242,8 @@ def engine_from_stored(cfg: ModelConfig, ecfg: EngineConfig, src, comm=None, dev
             mk = markov_prefix(cfg)
             extra["markov_embed"] = g.raw(f"{mk}.embed.weight", torch.bfloat16).contiguous()
             extra["markov_head"] = g.raw(f"{mk}.head.weight", torch.bfloat16).contiguous()      # this rank's vocabulary rows
+        if cfg.draft.confidence_head:
+            extra["confidence"] = g.raw(confidence_name(cfg), torch.bfloat16).to(torch.float32).reshape(-1).contiguous()
     if cfg.hc_mult > 1:
         extra = dict(extra, hc_head=tuple(g.raw(k, torch.float32).contiguous()
                                           for k in ("hc_head_fn", "hc_head_base", "hc_head_scale")))

@@ -150,9 +150,11 @@ class SampleWorkspace:
 
     def sample(self, tlogits, dlogits, dstat, proposals, uniforms, u_stride: int, sess_temp, sess_top_p, S: int,
                g: int, ldl: int, tstat, stat_stride: int, n_accept, next_token, tok_stride: int, status,
-               point_mass: bool = False, emu_strides=(0, 0, 0, 0, 0), sess_point=None, forced=None) -> None:
+               point_mass: bool = False, emu_strides=(0, 0, 0, 0, 0), sess_point=None, forced=None,
+               sess_g=None) -> None:
+        """``sess_g`` [S] int32 (g > 0): proposals each conversation verifies (causal stopping)."""
         native.call("tf_sample_chunks", tlogits, dlogits, dstat, proposals, uniforms, u_stride, sess_temp, sess_top_p,
-                    S, g, self.V, ldl, 1 if point_mass else 0, sess_point, forced, tstat, stat_stride, n_accept,
+                    S, g, self.V, ldl, 1 if point_mass else 0, sess_point, forced, sess_g, tstat, stat_stride, n_accept,
                     next_token, tok_stride,
                     self.peers, self.world, self.rank, self.max_rows, self.ctr, self.spin_limit, status,
                     self.emulate, *emu_strides)

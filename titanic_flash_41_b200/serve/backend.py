@@ -77,14 +77,30 @@ class OracleBackend:
                 prop = sl.lookup.propose(pending=[sl.anchor])
                 if prop is not None and len(prop.tokens) >= g:
                     copied = prop.tokens[:g]           # point-mass proposals: no draft law to sample
+            conf, cum = [], 1.0
+            ladder = self.cfg.draft.confidence_ladder
             for j in range(g if copied is None else 0):
+                fed = tok
                 lg, hid = self.model.draft_forward(torch.tensor([tok]), hid, s, sl.length + j)
+                if self.cfg.draft.confidence_head:
+                    # causal stopping: the confidence of proposal j + 1 is known before it is sampled;
+                    # the first running product under its threshold ends the block (nothing later can
+                    # change that decision, so the accepted tokens keep the target's law)
+                    conf.append(float(self.model.draft_confidence(torch.tensor([fed]), hid)[0]))
+                    cum *= conf[-1]
+                    if j >= 1 and not (cum >= ladder[min(j - 1, len(ladder) - 1)]):
+                        break
                 q = verify.modified_law(lg, sl.temperature, sl.top_p)[0]
                 tok = verify.sample_from(q, draft_u[j]) if sl.temperature > 0 else int(q.argmax())
                 props.append(tok)
                 Q.append(q)
             if copied is not None:
                 props, Q = list(copied), None
+            sl.confidence, sl.verified = conf, len(props)
+            if len(props) < g:
+                # a shorter block: its last row is the bonus row; the final draw stays the round's own
+                g = len(props)
+                accept_u = accept_u[:g]
             rows = torch.tensor([sl.anchor] + props)
             lg = self.model.forward(rows, s, start=sl.length, commit=False)
             P = verify.modified_law(lg, sl.temperature, sl.top_p)

@@ -58,9 +58,12 @@ class Worker:
                  eos_id: int = 1, log: Optional[EventLog] = None, control=None, rank: int = 0,
                  prefill_slice_s: float = 0.5, checkpoint_min: int = policy.SHORT_TOKENS,
                  checkpoint_align: int = 8192, span_encoder=None, health=None, turn_tokens: int = 64,
-                 history_lookup: bool = True):
+                 history_lookup: bool = True, log_confidence: bool = False):
         """``span_encoder`` (rank 0): ``api.media.SpanEncoder`` over the vision tower; needed to serve
-        requests that carry images."""
+        requests that carry images.  ``log_confidence``: one ``step_confidence`` event per conversation
+        and round with the drafter's confidences, the proposals verified and the tokens emitted (no
+        token ids; reference: src/dspark_generation.rs log_step_confidence)."""
+        self.log_confidence = log_confidence
         self.b, self.sched, self.cache = backend, scheduler, cache or SessionCache()
         self.eos, self.log, self.control, self.rank = eos_id, log or EventLog(), control, rank
         self.slice_s, self.ck_min, self.ck_align = prefill_slice_s, checkpoint_min, checkpoint_align
@@ -487,6 +490,9 @@ class Worker:
             a.steps += 1
             # toks = [old anchor] + accepted proposals are now in the KV state; the anchor was already
             # delivered when it was sampled, so deliver the accepted proposals and the new anchor
+            if self.log_confidence and getattr(a.slot, "confidence", None):
+                self.log.log("step_confidence", id=a.job.id, confidence=[round(c, 4) for c in a.slot.confidence],
+                             verified=a.slot.verified or len(a.slot.confidence), emitted=len(toks))
             self._deliver(a, list(toks[1:]) + [a.slot.anchor])
 
     def _finish(self, region: int, reason: str) -> None:

@@ -47,6 +47,10 @@ class DecodeSlot:
     # text ends with a phrase seen before, the tokens that followed it then are proposed as point
     # masses instead of the draft head's samples (reference: src/dspark_generation.rs:1908)
     lookup: Optional[object] = None
+    # models with a confidence head: the drafter's confidences of the last round and how many of
+    # its proposals were verified (causal stopping)
+    confidence: List[float] = field(default_factory=list)
+    verified: int = 0
 
 
 def step_meta(regions: Sequence[int], lengths: Sequence[int], anchors: Sequence[int], g: int, ratio: int):
@@ -128,6 +132,15 @@ class SpecDecoder:
         self.dstat = torch.zeros(S, max(g, 1), sb, dtype=torch.uint8, device=dev)
         self.tstat = torch.zeros(S, self.R, sb, dtype=torch.uint8, device=dev)
         self.props = torch.zeros(S, max(g, 1), **i32)
+        # confidence head (causal stopping): confidences [S, g], running products, proposals to verify
+        self.causal = bool(g > 0 and engine.draft_extra.get("confidence") is not None and self.ws is not None)
+        if self.causal:
+            self.conf = torch.zeros(S, g, dtype=torch.float32, device=dev)
+            self.cum = torch.zeros(S, dtype=torch.float32, device=dev)
+            self.nver = torch.ones(S, **i32)
+            self.ladder = torch.tensor(list(cfg.draft.confidence_ladder) or [0.0], dtype=torch.float32, device=dev)
+            self.h_conf = torch.zeros(S, g + 1, dtype=torch.float32).pin_memory()     # confidences | verified count
+            self.d_conf = torch.zeros_like(self.h_conf, device=dev)
         self.ptok = torch.zeros(S, **i32)
         self.pacc = torch.zeros(S, **i32)
         self.u1 = torch.zeros(S, 2, **f64)
@@ -207,9 +220,16 @@ class SpecDecoder:
             if j > 0:
                 self.bd["meta"][0].copy_(self.props[:, j - 1])
             lg = e.draft_run(S, self.bd, hid, self.rows_d, local_logits=local)
+            if self.causal:
+                e.draft_confidence(S, self.bd, j, g, self.ladder, self.conf, self.cum, self.nver)
             self.dlogits[:, j].copy_(lg)
             hid = self.dhid
-            hid.copy_(self.bd["x"])
+            if cfg.hc_mult > 1:
+                # the next pass is conditioned on the mean of the residual copies (as the target's
+                # hidden state is: Engine._head)
+                hid.copy_(self.bd["x"].view(S, cfg.hc_mult, cfg.hidden).float().mean(1))
+            else:
+                hid.copy_(self.bd["x"])
             # sample proposal j from the modified draft law
             if local:
                 # one launch: statistics of the row (kept for the verification) + the draw, on this
@@ -237,7 +257,11 @@ class SpecDecoder:
         if local:
             ws.sample(logits, self.dlogits if g > 0 else None, self.dstat if g > 0 else None,
                       self.props if g > 0 else None, self.d_u, g + 2, temp, topp, S, g, logits.stride(0),
-                      self.tstat, 1, self.d_out[0], self.d_out[1], 1, st, sess_point=look if g > 0 else None)
+                      self.tstat, 1, self.d_out[0], self.d_out[1], 1, st, sess_point=look if g > 0 else None,
+                      sess_g=self.nver if self.causal else None)
+            if self.causal:
+                self.d_conf[:, :g].copy_(self.conf)
+                self.d_conf[:, g].copy_(self.nver)
         else:
             native.call("tf_rowstats_per_session", logits, V, V, S * R, temp, topp, R, self.tstat, self.rs_scratch, st)
             native.call("tf_spec_verify", logits, self.dlogits if g > 0 else None, self.tstat,
@@ -283,6 +307,8 @@ class SpecDecoder:
         if ev is not None:
             ev[1].record()
         self.h_out.copy_(self.d_out, non_blocking=True)
+        if self.causal:
+            self.h_conf.copy_(self.d_conf, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.steps += 1
         out = []
@@ -297,6 +323,9 @@ class SpecDecoder:
             if self.n_rec:
                 s.recent = (list(s.recent) + toks)[-self.n_rec:]
             s.anchor = nxt[i]
+            if self.causal:
+                s.confidence = self.h_conf[i, : self.g].tolist()
+                s.verified = int(self.h_conf[i, self.g])
             out.append(toks)
         return out
 
@@ -314,7 +343,7 @@ class SpecDecoder:
 
     @property
     def d2h_bytes_per_step(self) -> int:
-        return self.h_out.numel() * 4
+        return self.h_out.numel() * 4 + (self.h_conf.numel() * 4 if self.causal else 0)
 
     def count_launches(self, slots: Sequence[DecodeSlot]) -> int:
         """Kernels of this package launched by one step, counted on an eager run of the step."""

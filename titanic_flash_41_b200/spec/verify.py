@@ -82,14 +82,19 @@ def block_verify(P: torch.Tensor, Q: Optional[torch.Tensor], proposals: Sequence
 
 
 def causal_rows(confidences: Sequence[float], ladder: Sequence[float]) -> int:
-    """How many proposals to verify: proposal 1 always; proposal j>=2 only while every running
-    product of confidences stays above its threshold.  The decision never looks at later
-    confidences (reference: src/dspark_generation.rs:206-290)."""
-    n, prod = 1, 1.0
+    """How many proposals to verify.  Confidence j precedes proposal j (it is computed from what the
+    drafter saw before sampling it): proposal 1 is always verified, proposal j >= 2 only while every
+    running product c_1 ... c_i, i <= j, stays at or above its threshold ``ladder[i - 2]`` (the last
+    threshold repeats).  The first failed threshold stops and a NaN stops, so the length never
+    depends on later confidences or on excluded proposals (reference:
+    src/dspark_generation.rs causal_ladder_rows)."""
+    if not len(confidences):
+        return 0
+    n, prod = 1, float(confidences[0])
     for j in range(1, len(confidences)):
-        prod *= confidences[j - 1]
+        prod *= float(confidences[j])
         thr = ladder[min(j - 1, len(ladder) - 1)]
-        if prod < thr:
+        if not (prod >= thr):
             break
         n = j + 1
     return n
