@@ -71,11 +71,11 @@ def main():
     def fc1_mx(blocked=0):
         native.call("tf_quant_rows_mx8", h16, d, x8, x8s, T, d)
         native.call("tf_moe_gemv_mx", w1, w3, s1, s3, El, x8, x8s, T, None, I, a8, a8s, I, d, k, g_expert, g_start,
-                    g_count, n_groups, sorted_pairs, slots, 10.0, 0, blocked, stw.t)
+                    g_count, n_groups, sorted_pairs, slots, 10.0, 0, blocked, T, stw.t)
 
     def fc2_mx(blocked=0):
         native.call("tf_moe_gemv_mx", w2, None, s2, None, El, a8, a8s, npairs, y, d, None, None, d, I, 1, g_expert,
-                    g_start, g_count, n_groups, sorted_pairs, slots, 0.0, 0, blocked, stw.t)
+                    g_start, g_count, n_groups, sorted_pairs, slots, 0.0, 0, blocked, T, stw.t)
 
     print(f"# peaks ({pk['source']}): HBM {pk['hbm_gbs']} GB/s; {used} of {El} experts hit by {npairs} pairs")
     for name, fn, nbytes in (("moe_fc1_mxfp4_dual", fc1, used * 2 * I * (d // 2 + d // 32)),

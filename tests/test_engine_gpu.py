@@ -145,6 +145,22 @@ def test_block_scaled_expert_path_matches_register_path_and_oracle():
     # rounding decisions of two noisy paths are independent: the distances add in quadrature
     bound = (errs_old.median() ** 2 + 2 * oracle_shift.median() ** 2) ** 0.5 + 0.02
     assert errs.median() < bound and (errs < 0.2).float().mean() >= 0.6, (errs, bound)
+    # a block of 24 rows (deeper drafts, more conversations): the 32-column form of the tensor-core
+    # kernel against the register-fed form, with every expert routed so that nothing discrete flips
+    cfg24 = small_config(moe_inter=512, topk=8)
+    W24 = oracle.init_weights(cfg24, 0)
+    new24 = E.Engine.from_weights(cfg24, ecfg, W24)
+    old24 = E.Engine.from_weights(cfg24, EngineConfig(reference_matmul=True, regions=2, max_context=512,
+                                                      prefill_widths=(128,), moe_block_scaled=False), W24)
+    assert "x8" in new24._bufs(24) and "x8" not in old24._bufs(24)
+    toks = torch.randint(0, cfg.vocab, (24,), generator=g).tolist()
+    outs = []
+    for e in (new24, old24):
+        e.forward(E.StepPlan.build([(0, 0, prompt.tolist())], logits="last"))
+        outs.append(e.forward(E.StepPlan.build([(0, 77, toks)])).cpu())
+        e.status.check()
+    d24 = _row_err(outs[0], outs[1])
+    assert d24.max() < 0.12 and d24.median() < 0.06, d24
 
 
 def test_two_regions_batched_decode_equals_separate():

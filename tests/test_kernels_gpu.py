@@ -608,10 +608,11 @@ def test_mx8_row_quantiser_matches_codec():
     assert torch.equal(q.cpu().view(7, 16, 32)[ws != 0], wq.view(torch.uint8).view(7, 16, 32)[ws != 0])
 
 
-@pytest.mark.parametrize("dual,T", [(True, 16), (True, 5), (False, 16), (False, 3)])
+@pytest.mark.parametrize("dual,T", [(True, 16), (True, 5), (False, 16), (False, 3), (True, 24), (True, 32), (False, 24),
+                                    (False, 32), (True, 17)])
 def test_block_scaled_expert_gemv_matches_reference(dual, T):
     """MXFP4 weights x MXFP8 activations on tcgen05 block-scaled MMAs (scales applied by the tensor
-    core) against fp32 math on the dequantised operands."""
+    core) against fp32 math on the dequantised operands.  17..32 rows run the 32-column form."""
     from titanic_flash_41_b200.models import engine as E
     torch.manual_seed(7)
     El, N, K, k = 6, 256, 1024, 2
@@ -641,7 +642,7 @@ def test_block_scaled_expert_gemv_matches_reference(dual, T):
     y8s = torch.zeros(npairs, N // 32, dtype=torch.uint8, device=DEV)
     native.call("tf_moe_gemv_mx", p1, p3 if dual else None, s1, s3 if dual else None, El, xq, xs, rows, y, N,
                 y8 if dual else None, y8s if dual else None, N, K, k, ge, gs, gc, ng, sp, min(El, npairs),
-                10.0 if dual else 0.0, 0, 0, st.t)
+                10.0 if dual else 0.0, 0, 0, T, st.t)
     torch.cuda.synchronize()
     st.check()
     if dual:

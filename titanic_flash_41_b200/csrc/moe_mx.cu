@@ -6,10 +6,11 @@
 // scales itself: `tcgen05.mma kind::mxf8f6f4.block_scale` with
 //   A = 128 output features x 32 inputs of e2m1, brought by TMA in the padded form (sixteen
 //       4-bit values per 16 bytes of shared memory) the instruction expects, 128-byte swizzle;
-//   B = 16 activation rows x 32 inputs of e4m3 (MXFP8: UE8M0 scale per 32 inputs);
+//   B = 16 (or 32: verification blocks of 17..32 rows) activation rows x 32 inputs of e4m3 (MXFP8:
+//       UE8M0 scale per 32 inputs);
 //   scale factors in tensor memory: for A four 32-bit columns per 128 inputs (column j holds
 //       rows 32j..32j+31, byte b the b-th group of 32 inputs), for B one column per 128 inputs;
-//   D = f32 in tensor memory, 128 lanes x 16 columns.
+//   D = f32 in tensor memory, 128 lanes x 16 (32) columns.
 // The CUDA cores touch only the scales (16 bytes per row and 512 inputs: TMA stages them in shared
 // memory with the data, the four warps that later run the epilogue rearrange them and write them
 // to tensor memory with tcgen05.st) and the 16 x 128 results.
@@ -33,10 +34,9 @@ namespace {
 
 constexpr int kThreads = 192;
 constexpr int kTile = 128;          // output features per work item
-constexpr int kRows = 16;           // activation rows (MMA N)
+constexpr int kRows = 16;           // activation rows (MMA N) of the narrow form; the wide form takes 32
 constexpr int kBK = 128;            // inputs per stage
 constexpr int kSuper = 512;         // inputs per scale load (4 stages)
-constexpr int kTmemCols = 256;
 constexpr int kSfBufs = 4;          // scale-factor slots in tensor memory (loaders run ahead of the MMAs)
 
 struct MxParams {
@@ -83,19 +83,27 @@ __device__ __forceinline__ void mma_mx(uint32_t tmem_d, uint64_t da, uint64_t db
 }
 // block-scaled instruction descriptor: A = e2m1 (5), B = e4m3 (0), both K-major, UE8M0 scales,
 // `sf` = which byte of the 32-bit scale columns this 32-input step uses (same for A and B)
-__device__ __forceinline__ uint32_t idesc_mx(uint32_t sf) {
-  return (sf << 4) | (5u << 7) | (0u << 10) | ((uint32_t)(kRows >> 3) << 17) | (1u << 23) |
+__device__ __forceinline__ uint32_t idesc_mx(uint32_t sf, int rows) {
+  return (sf << 4) | (5u << 7) | (0u << 10) | ((uint32_t)(rows >> 3) << 17) | (1u << 23) |
          ((uint32_t)(kTile >> 4) << 24) | (sf << 29);
 }
 
-template <int DUAL>
+// stages of the weight ring: what fits beside the scale slots in 227 KB
+__host__ __device__ constexpr int mx_stages(int dual, int rows) { return dual ? (rows > 16 ? 5 : 6) : (rows > 16 ? 10 : 11); }
+
+template <int DUAL, int ROWS>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__ CUtensorMap mapW3,
               const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapS1,
               const __grid_constant__ CUtensorMap mapS3, const __grid_constant__ CUtensorMap mapSX, const MxParams p) {
   constexpr int kMats = DUAL ? 2 : 1;
-  constexpr int kStages = DUAL ? 6 : 11;
-  // scale bytes of one 512-input block: [128 rows][16] per matrix, then [16 rows][16] of the activations
+  constexpr int kRows = ROWS;
+  constexpr int kStages = mx_stages(DUAL, ROWS);
+  // tensor-memory columns: accumulators [0, kAccCols) = buf * 2 * kRows + mat * kRows; A scales
+  // [kAccCols, kAccCols + 128) = slot * 32 + mat * 16; B scales after them = slot * 16
+  constexpr int kAccCols = 4 * kRows, kSfaCol = kAccCols, kSfbCol = kAccCols + 128;
+  constexpr int kTmemCols = kRows > 16 ? 512 : 256;
+  // scale bytes of one 512-input block: [128 rows][16] per matrix, then [kRows][16] of the activations
   constexpr int kSfsBytes = (kMats * kTile * 16 + kRows * 16 + 127) / 128 * 128;
   constexpr int kStageBytes = kMats * kTile * 128 + kRows * 128;
   extern __shared__ uint8_t smem_raw[];
@@ -150,8 +158,6 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
   // outputs, the group list first of all, are read from here on)
   tf_pdl_sync();
   const int items = *p.n_groups * tiles_n;
-  // columns: accumulators [0,64) = buf*32 + mat*16; A scales [64,192) = 64 + slot*32 + mat*16;
-  // B scales [192,256) = 192 + slot*16
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -210,12 +216,12 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++n_item) {
         const int ab = n_item & 1;
         if (!(ok = tc::mbar_wait(acc_empty(ab), ((n_item >> 1) & 1) ^ 1, abort_flag))) break;
-        const uint32_t td = tmem_base + ab * 32;
+        const uint32_t td = tmem_base + ab * 2 * kRows;
         for (int sc = 0; sc < nsuper && ok; ++sc, ++sfit) {
           const int sb = sfit % kSfBufs;
           if (!(ok = tc::mbar_wait(sf_full(sb), (sfit / kSfBufs) & 1, abort_flag))) break;
           tc::tc_fence_after();
-          const uint32_t sfa = tmem_base + 64 + sb * 32, sfb = tmem_base + 192 + sb * 16;
+          const uint32_t sfa = tmem_base + kSfaCol + sb * 32, sfb = tmem_base + kSfbCol + sb * 16;
           for (int c = 0; c < kSuper / kBK; ++c, ++it) {
             const int s = it % kStages;
             if (!(ok = tc::mbar_wait(full(s), (it / kStages) & 1, abort_flag))) break;
@@ -226,9 +232,9 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               const uint32_t acc = (sc == 0 && c == 0 && k == 0) ? 0u : 1u;
-              const uint32_t id = idesc_mx(k);
+              const uint32_t id = idesc_mx(k, kRows);
               mma_mx(td, da1 + 2 * k, db + 2 * k, id, sfa + c * 4, sfb + c * 4, acc);
-              if (DUAL) mma_mx(td + 16, da3 + 2 * k, db + 2 * k, id, sfa + 16 + c * 4, sfb + c * 4, acc);
+              if (DUAL) mma_mx(td + kRows, da3 + 2 * k, db + 2 * k, id, sfa + 16 + c * 4, sfb + c * 4, acc);
             }
             tc::mma_commit(empty(s));
           }
@@ -262,9 +268,12 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
       }
       if (!tc::mbar_wait(acc_full(ab), (n_item >> 1) & 1, abort_flag)) return false;
       tc::tc_fence_after();
-      uint32_t a1[16], a3[16];
-      tmem_ld16(tmem_base + lane_base + ab * 32, a1);
-      if (DUAL) tmem_ld16(tmem_base + lane_base + ab * 32 + 16, a3);
+      uint32_t a1[kRows], a3[kRows];
+#pragma unroll
+      for (int h = 0; h < kRows / 16; ++h) {
+        tmem_ld16(tmem_base + lane_base + ab * 2 * kRows + h * 16, a1 + h * 16);
+        if (DUAL) tmem_ld16(tmem_base + lane_base + ab * 2 * kRows + kRows + h * 16, a3 + h * 16);
+      }
       tc::tmem_ld_wait();
       tc::tc_fence_before();
       __syncwarp();
@@ -324,7 +333,7 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           w[m][j] = *reinterpret_cast<const uint4*>(sl + m * kTile * 16 + (lane + 32 * j) * 16);
-      const uint4 xa = *reinterpret_cast<const uint4*>(sl + kMats * kTile * 16 + (lane & 15) * 16);
+      const uint4 xa = *reinterpret_cast<const uint4*>(sl + kMats * kTile * 16 + (lane & (kRows - 1)) * 16);
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(sfs_empty(sb));
       if (!(ok = tc::mbar_wait(sf_empty(sb), par ^ 1, abort_flag))) break;
@@ -339,14 +348,14 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
           v[8 + j] = w[m][j].z;
           v[12 + j] = w[m][j].w;
         }
-        tmem_st16(tmem_base + lane_base + 64 + sb * 32 + m * 16, v);
+        tmem_st16(tmem_base + lane_base + kSfaCol + sb * 32 + m * 16, v);
       }
       {
         uint32_t v[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0;
         v[0] = xa.x; v[4] = xa.y; v[8] = xa.z; v[12] = xa.w;
-        tmem_st16(tmem_base + lane_base + 192 + sb * 16, v);
+        tmem_st16(tmem_base + lane_base + kSfbCol + sb * 16, v);
       }
       tmem_st_wait();
       tc::tc_fence_before();
@@ -368,7 +377,7 @@ moe_mx_kernel(const __grid_constant__ CUtensorMap mapW1, const __grid_constant__
   }
   tc::tc_fence_before();
   __syncthreads();
-  if (*abort_flag && threadIdx.x == 0) tf_report(p.status, TF_TIMEOUT, 130 + DUAL, blockIdx.x, items);
+  if (*abort_flag && threadIdx.x == 0) tf_report(p.status, TF_TIMEOUT, 130 + DUAL + (ROWS > 16 ? 4 : 0), blockIdx.x, items);
   if (warp == 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, kTmemCols);
@@ -449,9 +458,11 @@ TF_API int tf_quant_rows_mx8(const void* x, int ldx, void* q, void* s, int rows,
 //   rows by pair index); weights [experts, N, K/2] packed e2m1, scales [experts, N, K/32] UE8M0.
 //   q_out / q_scale (fused form, optional): the same output rows as MXFP8 [rows, N] + [rows, N/32],
 //   ready to be the plain form's input; `out` may then be null.
-//   x8 / sx: MXFP8 activation rows.  Fused form: the T token rows (T <= 16), one accumulator
+//   x8 / sx: MXFP8 activation rows.  Fused form: the T token rows (T <= 32), one accumulator
 //   column per token.  Plain form: rows in sorted pair order, the group's rows are consecutive;
 //   x8 needs no padding rows (a box that runs past the last row reads zeros), sx is clamped.
+//   group_rows: the most rows one group can hold (the token rows of the step; 0 = 16): above 16
+//   the 32-column form of the kernel runs.
 //   a_tx_bytes: bytes a [128 x 128] e2m1 box adds to the mbarrier's transaction count (0: the
 //   packed size).  blocked: the weights are stored block by block ([128 rows x 128 inputs] = 8 KB
 //   contiguous, blocks of one row tile consecutive) instead of row-major.
@@ -460,28 +471,34 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
                           void* q_scale, int N, int K, int topk,
                           const int* g_expert, const int* g_start, const int* g_count, const int* n_groups,
                           const int* sorted_pairs, int max_groups, float limit, int a_tx_bytes, int blocked,
-                          void* status, cudaStream_t st) {
+                          int group_rows, void* status, cudaStream_t st) {
   if (N % kTile || K % kSuper || x_rows <= 0 || max_groups <= 0) return -1;
   const bool dual = w3 != nullptr;
-  if (dual && x_rows > kRows) return -1;
+  if (group_rows <= 0) group_rows = kRows;
+  if (dual && x_rows > group_rows) group_rows = x_rows;
+  if (group_rows > 32) return -1;
+  const int rows = group_rows > kRows ? 32 : kRows;
   if (!g_mx_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_mx_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(moe_mx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    cudaFuncSetAttribute(moe_mx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    cudaFuncSetAttribute(moe_mx_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<0, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<2, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<0, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<1, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(moe_mx_kernel<2, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   }
   CUtensorMap m1, m3, mx, ms1, ms3, msx;
   if (!tc::make_map_2d_plain(&ms1, s1, (uint64_t)experts * N, K / 32, K / 32, 16, kTile)) return -4;
   if (!tc::make_map_2d_plain(&ms3, dual ? s3 : s1, (uint64_t)experts * N, K / 32, K / 32, 16, kTile)) return -4;
-  if (!tc::make_map_2d_plain(&msx, sx, x_rows, K / 32, K / 32, 16, kRows)) return -4;
+  if (!tc::make_map_2d_plain(&msx, sx, x_rows, K / 32, K / 32, 16, rows)) return -4;
   // blocked: [experts * N/128 * K/128] blocks of [128 rows x 128 inputs], each 8 KB contiguous
   const uint64_t wrows = blocked ? (uint64_t)experts * N * (K / kBK) : (uint64_t)experts * N;
   const uint64_t wcols = blocked ? kBK : K;
   if (!make_map_fp4(&m1, w1, wrows, wcols)) return -4;
   if (!make_map_fp4(&m3, dual ? w3 : w1, wrows, wcols)) return -4;
-  if (!tc::make_map_2d(&mx, x8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x_rows, K, K, kRows)) return -4;
+  if (!tc::make_map_2d(&mx, x8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x_rows, K, K, rows)) return -4;
   MxParams p;
   p.g_expert = g_expert; p.g_start = g_start; p.g_count = g_count; p.n_groups = n_groups;
   p.sorted_pairs = sorted_pairs;
@@ -497,11 +514,19 @@ TF_API int tf_moe_gemv_mx(const void* w1, const void* w3, const void* s1, const 
   p.status = reinterpret_cast<TfStatusWord*>(status);
   const bool pair = !dual && N % (2 * kTile) == 0;         // plain form, two adjacent tiles per work item
   const int grid = min(g_mx_sms, max_groups * (N / (pair ? 2 * kTile : kTile)));
-  const int stages = (dual || pair) ? 6 : 11, mats = (dual || pair) ? 2 : 1;
-  const int sfs = (mats * kTile * 16 + kRows * 16 + 127) / 128 * 128;
-  const int smem = stages * (mats * kTile * 128 + kRows * 128) + kSfBufs * sfs + 1024 + 512;
-  if (dual) tf_launch(moe_mx_kernel<1>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
-  else if (pair) tf_launch(moe_mx_kernel<2>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
-  else tf_launch(moe_mx_kernel<0>, dim3(grid), dim3(kThreads), smem, st, m1, m3, mx, ms1, ms3, msx, p);
+  const int stages = mx_stages(dual || pair, rows), mats = (dual || pair) ? 2 : 1;
+  const int sfs = (mats * kTile * 16 + rows * 16 + 127) / 128 * 128;
+  const int smem = stages * (mats * kTile * 128 + rows * 128) + kSfBufs * sfs + 1024 + 512;
+  if (smem > 227 * 1024) return -3;
+  const dim3 g(grid), t(kThreads);
+  if (rows == kRows) {
+    if (dual) tf_launch(moe_mx_kernel<1, 16>, g, t, smem, st, m1, m3, mx, ms1, ms3, msx, p);
+    else if (pair) tf_launch(moe_mx_kernel<2, 16>, g, t, smem, st, m1, m3, mx, ms1, ms3, msx, p);
+    else tf_launch(moe_mx_kernel<0, 16>, g, t, smem, st, m1, m3, mx, ms1, ms3, msx, p);
+  } else {
+    if (dual) tf_launch(moe_mx_kernel<1, 32>, g, t, smem, st, m1, m3, mx, ms1, ms3, msx, p);
+    else if (pair) tf_launch(moe_mx_kernel<2, 32>, g, t, smem, st, m1, m3, mx, ms1, ms3, msx, p);
+    else tf_launch(moe_mx_kernel<0, 32>, g, t, smem, st, m1, m3, mx, ms1, ms3, msx, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -1095,10 +1095,10 @@ class Engine:
                     native.call("tf_quant_rows_mx8", b["h16"], d, b["x8"], b["x8s"], T, d)
                 native.call("tf_moe_gemv_mx", L.ew1, L.ew3, L.es1, L.es3, self.El, b["x8"], b["x8s"], T, None, I,
                             b["a8"], b["a8s"], I, d, cfg.topk, b["g_expert"], b["g_start"], b["g_count"],
-                            b["n_groups"], b["sorted_pairs"], slots, cfg.swiglu_limit, 0, 0, self.status.t)
+                            b["n_groups"], b["sorted_pairs"], slots, cfg.swiglu_limit, 0, 0, T, self.status.t)
                 native.call("tf_moe_gemv_mx", L.ew2, None, L.es2, None, self.El, b["a8"], b["a8s"], npairs,
                             b["y_pair"], d, None, None, d, I, 1, b["g_expert"], b["g_start"], b["g_count"],
-                            b["n_groups"], b["sorted_pairs"], slots, 0.0, 0, 0, self.status.t)
+                            b["n_groups"], b["sorted_pairs"], slots, 0.0, 0, 0, T, self.status.t)
             else:
                 self._moe_small_f16(L, T, b, slots)
         elif getattr(self, "big_moe_full", None) is not None:
@@ -1109,15 +1109,15 @@ class Engine:
         self._moe_finish(L, T, b, side, next_norm)
 
     def _moe_mx_ok(self, T: int) -> bool:
-        """Block-scaled tensor-core GEMV for the routed experts: up to 16 rows, MXFP4 experts,
-        widths in whole 512-input scale loads and 128-feature tiles."""
+        """Block-scaled tensor-core GEMV for the routed experts: up to 32 rows (16 or 32 accumulator
+        columns), MXFP4 experts, widths in whole 512-input scale loads and 128-feature tiles."""
         cfg = self.cfg
-        return (self.ecfg.moe_block_scaled and T <= 16 and cfg.expert_quant == "mxfp4"
+        return (self.ecfg.moe_block_scaled and T <= 32 and cfg.expert_quant == "mxfp4"
                 and cfg.hidden % 512 == 0 and cfg.moe_inter % 512 == 0)
 
     def _moe_small_f16(self, L: LayerWeights, T: int, b: dict, slots: int) -> None:
-        """Register-fed form (f16 activations, nibbles unpacked on the CUDA cores): rows 17..32 and
-        widths the tensor-core form does not tile."""
+        """Register-fed form (f16 activations, nibbles unpacked on the CUDA cores): widths the
+        tensor-core form does not tile."""
         cfg = self.cfg
         d, I = cfg.hidden, cfg.moe_inter
         native.call("tf_smallm_gemm", 1, L.ew1, L.ew3, L.es1, L.es3, I * (d // 2), I * (d // 32),
@@ -1331,7 +1331,7 @@ class Engine:
         reference: src/nvfp4_head.rs, a 4-bit head over 61 % of the vocabulary)."""
         pk, sc, ids = self.draft_extra["head_mx"]
         n, d, Vs = h16.shape[0], self.cfg.hidden, pk.shape[1]
-        assert n <= 16
+        assert n <= 32
         st = self._scratch.get(("head_mx", n))
         if st is None:
             i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.dev)
@@ -1342,7 +1342,7 @@ class Engine:
         native.call("tf_quant_rows_mx8", h16, d, st["x8"], st["x8s"], n, d)
         y = torch.empty(n, Vs, dtype=torch.float32, device=self.dev)
         native.call("tf_moe_gemv_mx", pk, None, sc, None, 1, st["x8"], st["x8s"], n, y, Vs, None, None, Vs, d, 1,
-                    st["ge"], st["gs"], st["gc"], st["ng"], st["sp"], 1, 0.0, 0, 0, self.status.t)
+                    st["ge"], st["gs"], st["gc"], st["ng"], st["sp"], 1, 0.0, 0, 0, n, self.status.t)
         logits = torch.full((n, self.cfg.vocab), float("-inf"), dtype=torch.float32, device=self.dev)
         logits.index_copy_(1, ids, y)
         return logits
