@@ -5,7 +5,14 @@ requests interleaved, then every conversation resumed with a small follow-up.
                                             [--short 17] [--follow 2048] [--backend engine|oracle]
 
 Runs the real serving stack (scheduler, worker, session cache with host and disk tiers, state
-images, engine) in one process.  Reports, as one JSON line: time to first token of the resumed
+images, engine): in one process, or as one rank per GPU under torchrun
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29541 \
+        benchmarks/bench_long_context.py --target 1000000 --grow 65536
+
+where rank 0 owns the scheduler and the clients and every rank runs a worker that follows rank 0's
+commands over the control channel (tensor-parallel decode through the fused all-reduce kernels,
+sequence-parallel prefill).  Reports, as one JSON line: time to first token of the resumed
 turns, the share of prompt tokens served from cached state, and where the restored images came
 from (device / host / disk).  The oracle backend with ``--preset tiny`` runs the same script on
 the CPU in seconds (used by the tests).
@@ -27,7 +34,19 @@ from titanic_flash_41_b200.serve.state_image import DiskTier  # noqa: E402
 from titanic_flash_41_b200.serve.worker import Worker  # noqa: E402
 
 
-def build_backend(a):
+def small_gpu_config(world: int = 1):
+    """A model the CUDA engine runs in seconds (the geometry of the GPU tests), for trials of this script."""
+    from titanic_flash_41_b200.config import DraftConfig, ModelConfig, RopeConfig
+    return ModelConfig(name="small", n_layers=3, hidden=512, vocab=2048, n_heads=4 * world if world > 4 else 4, head_dim=128,
+                       window=32, compress_ratio=4, kv_source_layers=(0,), index_source_layers=(0, 2), index_heads=4,
+                       index_dim=128, index_topk=16, n_experts=8, topk=2, moe_inter=512, n_shared=1,
+                       shared_inter=max(256, 128 * world), scoring="sqrtsoftplus", router_bias=True, route_scale=1.5,
+                       swiglu_limit=10.0, rope=RopeConfig(theta=10000.0, compress_theta=160000.0, dim=64),
+                       dense_quant="fp8_block128", expert_quant="mxfp4", kv_quant="v41", init_std=0.05,
+                       draft=DraftConfig(layers=1, depth=3))
+
+
+def build_backend(a, comm=None):
     if a.backend == "oracle":
         from titanic_flash_41_b200.models import oracle
         from titanic_flash_41_b200.serve.backend import OracleBackend
@@ -36,10 +55,22 @@ def build_backend(a):
                                   chunk=a.chunk)
     from titanic_flash_41_b200.models.engine import Engine
     from titanic_flash_41_b200.serve.backend import EngineBackend
-    cfg = flash_b200_config() if a.preset == "flash-b200" else tiny_config()
-    ecfg = EngineConfig(regions=a.regions, max_context=a.target + a.follow + 4096, prefill_widths=(a.chunk,))
-    eng = Engine.random_init(cfg, ecfg, seed=0, max_chunk=a.chunk)
-    return cfg, EngineBackend(eng, chunk=a.chunk)
+    world = comm.world if comm is not None else 1
+    cfg = {"flash-b200": flash_b200_config, "tiny": tiny_config, "small": lambda: small_gpu_config(world)}[a.preset]()
+    ecfg = EngineConfig(tp=world, regions=a.regions, max_context=a.target + a.follow + 4096, prefill_widths=(a.chunk,),
+                        sp_chunk_rows=min(a.chunk * world, 65536) if world > 1 else 0)
+    if a.preset == "small":
+        ecfg.reference_matmul = True          # the trial model's prompt tails are shorter than a tensor-core tile
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    eng = Engine.random_init(cfg, ecfg, comm, device=dev, seed=0, max_chunk=a.chunk)
+    if world > 1:
+        from titanic_flash_41_b200.parallel.symm import SymmWorkspace
+        eng.symm = SymmWorkspace(cfg.hidden, 32, device=dev)
+    backend = EngineBackend(eng, chunk=a.chunk)
+    if world > 1:
+        from titanic_flash_41_b200.parallel import sp
+        sp.attach(eng)
+    return cfg, backend
 
 
 def drain(w, limit=100000):
@@ -67,13 +98,31 @@ def main(argv=None):
     ap.add_argument("--device-cache-gb", type=float, default=2.0)
     ap.add_argument("--host-cache-gb", type=float, default=16.0)
     a = ap.parse_args(argv)
-    cfg, backend = build_backend(a)
+    world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
+    comm = control = None
+    if world > 1:
+        import torch.distributed as dist
+        from titanic_flash_41_b200.parallel.comm import DistComm
+        from titanic_flash_41_b200.parallel.control import ControlChannel
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+        comm = DistComm()
+        control = ControlChannel.connect(rank, world, "127.0.0.1", int(os.environ["MASTER_PORT"]) + 13, b"long-context", 600.0)
+    cfg, backend = build_backend(a, comm)
     tmp = tempfile.mkdtemp(prefix="tflash_tier_")
     disk = DiskTier(tmp)
     cache = SessionCache(slots=a.cache_slots, budget_bytes=int(a.device_cache_gb * 2 ** 30), disk=disk,
                          host_budget_bytes=int(a.host_cache_gb * 2 ** 30), park_after=2)
-    sched = Scheduler(a.regions, 64, 8)
-    w = Worker(backend, sched, cache, eos_id=-1, checkpoint_min=a.checkpoint, checkpoint_align=a.checkpoint)
+    sched = Scheduler(a.regions, 64, 8) if rank == 0 else None
+    w = Worker(backend, sched, cache, eos_id=-1, checkpoint_min=a.checkpoint, checkpoint_align=a.checkpoint,
+               control=control, rank=rank)
+    if rank != 0:
+        # follow rank 0's commands until it says stop; the numbers are rank 0's
+        w._pending = []
+        while w.running:
+            w.run_once(0.05)
+        _leave(world, disk, tmp)
+        return None
     g = torch.Generator().manual_seed(0)
     rand = lambda n: torch.randint(3, cfg.vocab, (n,), generator=g).tolist()
     events = {}
@@ -137,12 +186,28 @@ def main(argv=None):
            "resume_ttft_mean_s": round(sum(ttft) / len(ttft), 4),
            "resume_cached_tokens": [r["cache_n"] for r in resumed], "resume_prefilled_tokens": [r["prompt_n"] for r in resumed],
            "reused_token_share": round(reused_total / max(1, prompt_total), 4), "cache_stats": dict(cache.stats),
-           "image_tiers_before_resume": tiers_before,
+           "image_tiers_before_resume": tiers_before, "n_gpus": world, "model": a.preset,
+           "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1) if a.backend == "engine" else None,
            "data": "synthetic token ids, random-init weights"}
     print(json.dumps(out), flush=True)
+    if world > 1:
+        sched.close()
+        w._pending = []
+        while w.running:                      # the stop command reaches the other ranks through the worker
+            w.run_once(0.05)
+    _leave(world, disk, tmp)
+    return out
+
+
+def _leave(world, disk, tmp):
     disk.reset_dir()
     os.rmdir(tmp)
-    return out
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)          # no collective teardown while symmetric-memory mappings are alive
 
 
 if __name__ == "__main__":

@@ -48,7 +48,7 @@ def main():
     sched = Scheduler(2, 8, 2) if rank == 0 else None
     worker = Worker(backend, sched, SessionCache(slots=8, budget_bytes=1 << 30), eos_id=-1, control=control, rank=rank,
                     checkpoint_min=chunk, checkpoint_align=chunk)
-    events, failure = {}, []
+    events, failure, shared = {}, [], {}
 
     def submit(jid, toks, n, **kw):
         events[jid] = []
@@ -71,14 +71,17 @@ def main():
             g = torch.Generator().manual_seed(5)
             rand = lambda n: torch.randint(3, cfg.vocab, (n,), generator=g).tolist()
             long_prompt, short_prompt = rand(3 * chunk + 37), rand(50)
-            submit("long", long_prompt, 12, temperature=0.0, top_p=1.0, seed=1)
+            submit("long", long_prompt, 13, temperature=0.0, top_p=1.0, seed=1)
             submit("short", short_prompt, 10, temperature=0.7, top_p=0.9, seed=2)          # decodes beside the long prefill
             wait("long")
             wait("short")
-            submit("again", long_prompt, 12, temperature=0.0, top_p=1.0, seed=1)           # served from the cached image
+            submit("again", long_prompt, 13, temperature=0.0, top_p=1.0, seed=1)           # served from the cached image
             wait("again")
-            follow = long_prompt + toks_of("long") + rand(70)
-            submit("follow", follow, 6, temperature=0.6, top_p=0.95, seed=3)               # appended turn: prefix reuse
+            # appended turn: the cached prefix ends inside a compressor group (421 + 12 committed tokens), so the
+            # new part starts on the tensor-parallel path and continues split over the ranks
+            follow = long_prompt + toks_of("long") + rand(3 * chunk)
+            shared["follow"] = follow
+            submit("follow", follow, 6, temperature=0.6, top_p=0.95, seed=3)
             wait("follow")
         except BaseException as e:  # noqa: BLE001
             failure.append(e)
@@ -96,11 +99,11 @@ def main():
         assert not failure, failure
         for jid in ("long", "short", "again", "follow"):
             assert any(k == "done" for k, _ in events[jid]), (jid, events[jid][-2:])
-        assert len(toks_of("long")) == 12 and len(toks_of("short")) == 10 and len(toks_of("follow")) == 6
+        assert len(toks_of("long")) == 13 and len(toks_of("short")) == 10 and len(toks_of("follow")) == 6
         assert toks_of("again") == toks_of("long"), (toks_of("again"), toks_of("long"))
         assert ready_of("long")["cache_n"] == 0
         assert ready_of("again")["cache_n"] >= 3 * chunk and ready_of("again")["prompt_n"] <= chunk
-        assert ready_of("follow")["cache_n"] >= 3 * chunk
+        assert ready_of("follow")["cache_n"] == 3 * chunk + 37 + 12
     torch.cuda.synchronize()
     eng.status.check()
     # every rank took the same commands ...
@@ -108,7 +111,22 @@ def main():
     all_kinds = [None] * world
     dist.all_gather_object(all_kinds, kinds)
     assert all(k == all_kinds[0] for k in all_kinds) and len(kinds) >= 8, all_kinds
-    # ... and holds the same KV state
+    # the appended turn ran sequence-parallel after its unaligned head, and left the state that a
+    # prefill of the whole conversation from position 0 leaves
+    assert len(eng.sp._plans) > 0
+    box = [shared.get("follow"), next((e["region"] for e in worker.log.snapshot(4096)["events"]
+                                       if e["kind"] == "begin" and e.get("id") == "follow"), None)]
+    dist.broadcast_object_list(box, src=0)
+    follow, region = box
+    from titanic_flash_41_b200.serve.prefill import run_prefill
+    run_prefill(eng, 1 - region, torch.tensor(follow, dtype=torch.int32), chunk)
+    torch.cuda.synchronize()
+    eng.status.check()
+    nC = len(follow) // cfg.compress_ratio
+    for t in (eng.comp, eng.keys):
+        same = (t[:, region, :nC] == t[:, 1 - region, :nC]).float().mean()
+        assert same > 0.95, float(same)
+    # ... and every rank holds the same KV state
     for t in (eng.win, eng.comp, eng.keys):
         got = [torch.empty_like(t) for _ in range(world)]
         dist.all_gather(got, t)

@@ -163,6 +163,24 @@ def test_block_scaled_expert_path_matches_register_path_and_oracle():
     assert d24.max() < 0.12 and d24.median() < 0.06, d24
 
 
+def test_index_scoring_in_row_tiles_is_bitwise_the_same():
+    """Long contexts bound the fp32 score matrix by scoring and selecting a tile of rows at a time: the
+    selections and the logits do not change."""
+    cfg = small_config()
+    W = oracle.init_weights(cfg, 0)
+    mk = lambda nbytes: E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512,
+                                                               prefill_widths=(256,), index_score_bytes=nbytes), W)
+    whole, tiled = mk(2 << 30), mk(16 << 10)          # 16 KB: tiles of 64 rows at 60 entries a row
+    prompt = torch.randint(0, cfg.vocab, (239,), generator=torch.Generator().manual_seed(8)).tolist()
+    a = whole.forward(E.StepPlan.build([(0, 0, prompt)]))
+    b = tiled.forward(E.StepPlan.build([(0, 0, prompt)]))
+    tiled.status.check()
+    assert ("scores", 239) in whole._scratch and ("scores", 64) in tiled._scratch and ("scores", 239) not in tiled._scratch
+    for li in cfg.index_source_layers:
+        assert torch.equal(whole._bufs(239)["sel"][li], tiled._bufs(239)["sel"][li])
+    assert torch.equal(a, b)
+
+
 def test_two_regions_batched_decode_equals_separate():
     cfg = small_config()
     W = oracle.init_weights(cfg, 3)

@@ -347,6 +347,7 @@ class EngineConfig(_JsonMixin):
     pdl: bool = False                  # launch kernels with programmatic dependent launch (each kernel waits for its predecessor on the device; the next one is already resident)
     sp_prefill: bool = True            # more than one rank: prefill chunks are split by rows over the ranks (every rank keeps the unsharded dense matrices of the encoder layers)
     sp_chunk_rows: int = 0                 # rows of one sequence-parallel prefill chunk over ALL ranks (0: the single-rank chunk); the window ring holds a whole chunk
+    index_score_bytes: int = 2 << 30       # most bytes of one fp32 index-score matrix: prefill rows are scored and selected in row tiles beyond it (long contexts)
     prefill_mx: bool = True                # prefill GEMMs on the block-scaled tensor-core form (MXFP8 activations)
     moe_block_scaled: bool = True     # decode rows <= 16: routed experts on block-scaled tcgen05 MMAs (MXFP8 activations)
     seed: int = 0

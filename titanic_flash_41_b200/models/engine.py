@@ -968,7 +968,14 @@ class Engine:
             sel[:T].copy_(ids)
             selcnt[:T].copy_(cnt)
             return
-        scores = self.scores_buffer(T, nmax)
+        # rows scored per launch: all of them unless the fp32 score matrix would pass the limit
+        # (whole scoring groups of one conversation's consecutive rows)
+        rows_t = T
+        if T > self.SMALL_M and T * nmax * 4 > self.ecfg.index_score_bytes:
+            unit = max(rows_per_group, 32)
+            rows_t = max(unit, (self.ecfg.index_score_bytes // (4 * max(nmax, 1))) // unit * unit)
+            rows_t = min(rows_t, T)
+        scores = self.scores_buffer(rows_t, nmax)
         ks_min = self.ecfg.key_sharded_index_min
         if self.world > 1 and ks_min > 0 and T <= self.SMALL_M and nmax >= ks_min and not (two_level and li == pub):
             # every rank holds all index keys: split the scoring work by key range, gather the local
@@ -979,6 +986,18 @@ class Engine:
                                  cfg.index_topk, self.rank, self.world, lambda t: self.comm.all_gather(t, dim=1))
             sel[:T].copy_(ids)
             selcnt[:T].copy_(cnt)
+            return
+        if rows_t < T:
+            # long contexts: score and select a tile of rows at a time, so that the score matrix stays
+            # within `index_score_bytes` whatever the context (a 1M-token context has 262,144 entries a row)
+            Hi, Di = cfg.index_heads, cfg.index_dim
+            for r0 in range(0, T, rows_t):
+                n = min(rows_t, T - r0)
+                native.call("tf_index_scores", b["iq"][r0:], b["iw"][r0:], region[r0:], nvalid[r0:], self.keys[sslot],
+                            self.keys[sslot].stride(0), self.key_row, n, Hi, Di,
+                            rows_per_group, scores, scores.stride(0), 0, nmax)
+                native.call("tf_topk_select", scores, scores.stride(0), nvalid[r0:], cfg.index_topk, sel[r0:], selcnt[r0:],
+                            None, 0, n)
             return
         native.call("tf_index_scores", b["iq"], b["iw"], region, nvalid, self.keys[sslot],
                     self.keys[sslot].stride(0), self.key_row, T, cfg.index_heads, cfg.index_dim,

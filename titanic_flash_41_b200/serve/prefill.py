@@ -161,6 +161,21 @@ def run_prefill(eng: Engine, region: int, tokens, chunk: int, start: int = 0, ne
     late = cfg.late_start if 0 < cfg.late_start < L else L
     tail_n = min(n, cfg.window) if late < L else 0
     tail = torch.zeros(max(tail_n, 1), cfg.hidden * cfg.hc_mult, dtype=torch.bfloat16, device=eng.dev)
+    sp = getattr(eng, "sp", None)
+    if sp is not None and embeds is None and not sp.usable(start, n):
+        # a prefill that begins inside a compressor group (a conversation resumed right after its
+        # last committed token): the rows up to the next group boundary take the tensor-parallel
+        # path through the encoder layers, the rest is split over the ranks
+        k = (-start) % cfg.max_ratio
+        if 0 < k and n - k >= max(cfg.window, 1) and sp.usable(start + k, n - k):
+            plan = _recent(StepPlan.build([(region, start, toks[:k].tolist())], logits="last"), cfg, prev, toks, 0)
+            b = eng._bufs(k)
+            eng.upload_plan(plan, b)
+            nmax, rpg = eng.plan_shape(plan, cfg.compress_ratio)
+            eng.run(k, b, nmax, rpg, None, 0, late)
+            cb = None if on_chunk is None else (lambda done: on_chunk(done + k))
+            return run_prefill(eng, region, toks[k:], chunk, start + k, need_logits, cb, widths, layer_major, None,
+                               (list(prev) + toks[:k].tolist())[-8:] if len(prev) else ())
     sizes = plan_chunks(n, tuple(widths) if widths else (chunk,))
     if layer_major is None:
         layer_major = len(sizes) > 1 and getattr(eng, "big_moe_full", None) is not None
