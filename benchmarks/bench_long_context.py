@@ -97,6 +97,7 @@ def main(argv=None):
     ap.add_argument("--checkpoint", type=int, default=65536, help="prompt checkpoint spacing (tokens)")
     ap.add_argument("--device-cache-gb", type=float, default=2.0)
     ap.add_argument("--host-cache-gb", type=float, default=16.0)
+    ap.add_argument("--progress", action="store_true", help="one line per turn on stderr (elapsed time, context)")
     a = ap.parse_args(argv)
     world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
     comm = control = None
@@ -108,7 +109,10 @@ def main(argv=None):
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
         comm = DistComm()
         control = ControlChannel.connect(rank, world, "127.0.0.1", int(os.environ["MASTER_PORT"]) + 13, b"long-context", 600.0)
+    t_load = time.monotonic()
     cfg, backend = build_backend(a, comm)
+    if a.progress and rank == 0:
+        print(f"[long-context] model ready in {time.monotonic() - t_load:.1f} s", file=sys.stderr, flush=True)
     tmp = tempfile.mkdtemp(prefix="tflash_tier_")
     disk = DiskTier(tmp)
     cache = SessionCache(slots=a.cache_slots, budget_bytes=int(a.device_cache_gb * 2 ** 30), disk=disk,
@@ -156,6 +160,9 @@ def main(argv=None):
             submit(f"short{shorts_left}", rand(a.short_tokens), a.new_tokens)
             shorts_left -= 1
         drain(w)
+        if a.progress:
+            print(f"[long-context] turn {turn + 1}/{turns}: context {len(convs[0])}, {time.monotonic() - t_start:.1f} s",
+                  file=sys.stderr, flush=True)
         for s in range(a.sessions):
             jid = f"s{s}t{turn}"
             r = ready(jid)
@@ -163,9 +170,9 @@ def main(argv=None):
             reused_total += r["cache_n"]
             convs[s] = convs[s] + tokens_of(jid)
     grow_s = time.monotonic() - t_start
-    # let idle steps write images behind to the lower tiers
+    # let idle steps write images behind to the lower tiers (on every rank: idle commands travel too)
     for _ in range(64):
-        w.execute({"op": "idle"})
+        w.run_once(0.0)
     tiers_before = {t: sum(1 for e in cache.entries if e.image.tier == t) for t in ("device", "host", "disk")}
     # ---- resume every conversation with a short follow-up
     ttft, resumed = [], []

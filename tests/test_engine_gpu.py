@@ -484,6 +484,29 @@ def test_two_level_candidates_in_the_layer_loop():
     assert err.median() < 0.5, err
 
 
+def test_two_level_selection_inside_the_captured_decode_graph():
+    """Contexts long enough for two-level selection decode under a CUDA graph: the replayed graph commits
+    what the eager step commits (the candidate tensors are allocated inside the capture)."""
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    cfg = small_config(candidate_blocks=4, index_topk=8, draft=DraftConfig(layers=1, depth=3))
+    W = oracle.init_weights(cfg, 0)
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=1024, prefill_widths=(256,),
+                                                  two_level_index_min=16), W)
+    prompt = torch.randint(0, cfg.vocab, (230,), generator=torch.Generator().manual_seed(6)).tolist()
+    outs = []
+    for region, graph in ((0, True), (1, False)):
+        lg = eng.forward(E.StepPlan.build([(region, 0, prompt)], logits="last"))
+        sl = DecodeSlot(region=region, length=230, anchor=int(lg.argmax()), seed=4, temperature=0.0, top_p=1.0)
+        dec = SpecDecoder(eng, 1, use_graph=graph)
+        dec.hidden.copy_(eng.last_hidden[-1:])
+        for _ in range(6):
+            dec.step([sl])
+        eng.status.check()
+        outs.append(list(sl.emitted))
+    assert outs[0] == outs[1] and len(outs[0]) >= 6
+
+
 def test_draft_head_with_markov_correction_matches_oracle():
     """Draft logits = draft head + rank-r bigram term of the token each row was fed."""
     from titanic_flash_41_b200.config import DraftConfig

@@ -34,6 +34,8 @@ class Proposal:
 
 
 class HistoryLookup:
+    BULK_SPAN = 4           # a bulk commit indexes at most this many windows per table slot
+
     def __init__(self, prefix: Sequence[int] = (), slots: int = SLOTS, lengths: Sequence[int] = LENGTHS,
                  minimum_match: Optional[int] = None, depth: int = 5):
         self.tokens: List[int] = []
@@ -64,19 +66,24 @@ class HistoryLookup:
         token-by-token commits (a slot keeps the LAST position that hashed to it)."""
         import numpy as np
         base = len(self.tokens)
-        self.tokens.extend(int(t) for t in tokens)
-        text = np.asarray(self.tokens, dtype=np.uint64) & np.uint64(0xFFFFFFFF)
+        self.tokens.extend(np.asarray(tokens, dtype=np.int64).tolist())
         n = len(self.tokens)
+        # A slot keeps the last position that hashed to it, so of a very long run only the most recent
+        # windows survive: with 4 x slots windows indexed, an older one would have been overwritten
+        # with probability 1 - e^-4.  Bounding the run keeps a million-token prompt at the cost of a
+        # quarter-million-token one.
+        first = max(0, n - self.BULK_SPAN * self.slots - self.lengths[-1])
+        text = np.asarray(self.tokens[first:], dtype=np.uint64) & np.uint64(0xFFFFFFFF)
         for li, L in enumerate(self.lengths):
             # windows [i, i + L) predict token i + L; only windows whose predicted token is new
-            lo = max(0, base - L)
+            lo = max(0, base - L, first)
             hi = n - L                      # predicted positions lo + L .. n - 1
             if hi <= lo:
                 continue
             v = np.full(hi - lo, 0xCBF29CE484222325, dtype=np.uint64)
             with np.errstate(over="ignore"):
                 for k in range(L):
-                    v = (v ^ text[lo + k: hi + k]) * np.uint64(0x100000001B3)
+                    v = (v ^ text[lo - first + k: hi - first + k]) * np.uint64(0x100000001B3)
             v = v ^ (v >> np.uint64(32))
             keys = (v % np.uint64(self.slots)).astype(np.int64)
             pos = np.arange(lo + L, hi + L, dtype=np.int64)
