@@ -52,10 +52,15 @@ def common_prefix(a, b, chain_a: Optional[List[bytes]] = None, chain_b: Optional
         while k < m and chain_a[k] == chain_b[k]:
             k += 1
         i = k * BLOCK
-    if i >= n:
-        return n
-    diff = np.flatnonzero(ta[i:n] != tb[i:n])
-    return n if diff.size == 0 else i + int(diff[0])
+    # sequences that differ usually differ early: look at a short window before the whole remainder
+    step = 1024
+    while i < n:
+        j = min(n, i + step)
+        diff = np.flatnonzero(ta[i:j] != tb[i:j])
+        if diff.size:
+            return i + int(diff[0])
+        i, step = j, step * 16
+    return n
 
 
 def cache_capacity(session_budget: int, shared_budget: int, suspended_bytes: int, suspended_count: int,

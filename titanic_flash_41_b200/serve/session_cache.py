@@ -17,7 +17,7 @@ from . import policy
 from .state_image import DiskTier, Image
 
 
-@dataclass
+@dataclass(eq=False)          # identity: two images of the same prefix are still two images
 class Entry:
     image: Image
     uid: int
@@ -91,13 +91,18 @@ class SessionCache:
     def insert(self, image: Image, optional: bool = False, completed: bool = False) -> bool:
         """Store an image; returns False when the policy refuses (it would not fit or, for an
         optional image, something would have to go)."""
-        same = [e for e in self.entries if e.image.tokens == image.tokens and e.image.media == image.media]
+        # token arrays and chained block digests are computed once per image: comparing the incoming
+        # image with every entry must not convert million-token sequences again and again
+        ia = policy.as_array(image.tokens)
+        key = (ia, policy.chain_hashes(ia))
+        pairs = [(e, policy.common_prefix(ia, self._entry_key(e)[0], key[1], self._entry_key(e)[1])) for e in self.entries]
+        same = [e for e, c in pairs if c == image.length == e.image.length and e.image.media == image.media]
         for e in same:
             self._drop(e)
+        pairs = [(e, c) for e, c in pairs if not any(e is x for x in same)]      # in the order of self.entries
         desc = [(e.image.length, e.image.nbytes) for e in self.entries]
         incoming = (image.length, image.nbytes)
-        anc = [policy.common_prefix(image.tokens, e.image.tokens) == e.image.length and
-               e.image.length < image.length for e in self.entries]
+        anc = [c == e.image.length and e.image.length < image.length for e, c in pairs]
         opt = [e.optional for e in self.entries]
         if optional:
             ev = policy.prompt_cache_evictions(desc, incoming, self.budget, self.long_first, self.slots,
@@ -112,7 +117,9 @@ class SessionCache:
         for e in [self.entries[i] for i in ev]:
             self._drop(e)
             self.stats["evictions"] += 1
-        self.entries.append(Entry(image, next(self._uid), optional))
+        ent = Entry(image, next(self._uid), optional)
+        ent._key = key
+        self.entries.append(ent)
         return True
 
     def _drop(self, e: Entry) -> None:

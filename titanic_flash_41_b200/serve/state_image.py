@@ -28,9 +28,9 @@ class ImageError(RuntimeError):
     pass
 
 
-@dataclass
+@dataclass(eq=False)          # identity: two images of the same prefix are still two images
 class Image:
-    tokens: Tuple[int, ...]                    # the prefix this image restores
+    tokens: Tuple[int, ...]                    # the prefix this image restores (tuple of ints, or a read-only int64 array)
     regions: List[Tuple[str, torch.Tensor]]    # (name, flat uint8 tensor)
     kind: str = "complete"                     # complete | checkpoint | encoder | request | optional
     media: str = ""                            # identity of images inside the prefix
@@ -85,6 +85,20 @@ class Image:
         self.tier = "device"
 
 
+def _token_tuple(tokens):
+    """The prefix an image restores, immutable: a tuple of plain ints, or, when the caller hands an
+    integer array (the worker does: a million-token prefix must not become a million Python ints
+    for every image), a read-only int64 copy of it."""
+    import numpy as np
+    if isinstance(tokens, tuple):
+        return tokens
+    if isinstance(tokens, np.ndarray):
+        arr = np.array(tokens, dtype=np.int64)
+        arr.flags.writeable = False
+        return arr
+    return tuple(np.asarray(tokens, dtype=np.int64).tolist())
+
+
 def capture(tokens: Sequence[int], named: Sequence[Tuple[str, torch.Tensor]], kind: str = "complete",
             media: str = "", meta: Optional[Dict[str, int]] = None, pool=None) -> Image:
     """Copy the given tensor views (any dtype/shape) into a new image on their own device.
@@ -95,7 +109,7 @@ def capture(tokens: Sequence[int], named: Sequence[Tuple[str, torch.Tensor]], ki
     propagates: the caller treats it like any other refused optional allocation."""
     if pool is None:
         regs = [(n, t.contiguous().view(torch.uint8).reshape(-1).clone()) for n, t in named]
-        return Image(tuple(int(x) for x in tokens), regs, kind, media, dict(meta or {}))
+        return Image(_token_tuple(tokens), regs, kind, media, dict(meta or {}))
     flats = [(n, t.contiguous().view(torch.uint8).reshape(-1)) for n, t in named]
     offs, total = [], 0
     for _, f in flats:
@@ -108,7 +122,7 @@ def capture(tokens: Sequence[int], named: Sequence[Tuple[str, torch.Tensor]], ki
         dst = whole[o:o + f.numel()]
         dst.copy_(f)
         regs.append((n, dst))
-    img = Image(tuple(int(x) for x in tokens), regs, kind, media, dict(meta or {}))
+    img = Image(_token_tuple(tokens), regs, kind, media, dict(meta or {}))
     img._range = rng
     return img
 
@@ -153,7 +167,7 @@ class DiskTier:
         if img.tier == "disk":
             return img.nbytes
         path = os.path.join(self.dir, image_id + ".img")
-        header = {"tokens": list(img.tokens), "kind": img.kind, "media": img.media, "meta": img.meta,
+        header = {"tokens": [int(t) for t in img.tokens] if isinstance(img.tokens, tuple) else img.tokens.tolist(), "kind": img.kind, "media": img.media, "meta": img.meta,
                   "regions": [[n, int(t.numel())] for n, t in img.regions]}
         self.fault("write_open")
         hb = json.dumps(header).encode() + b"\n"

@@ -365,7 +365,11 @@ class Worker:
         t0 = time.monotonic()
         from ..utils import memory as _mem
         stall0 = _mem.pressure_snapshot()          # host stall counters around the prefill (memory / io / cpu pressure)
+        import numpy as np
         region, prompt = cmd["region"], list(cmd["tokens"])
+        # one integer array of the prompt for everything that compares, hashes or stores it (a
+        # million-token list is converted once, not once per cache entry)
+        parr = np.asarray(prompt, dtype=np.int64)
         job = self.jobs.get(cmd["id"])
         self.requests += 1
         if len(prompt) + 1 >= self.b.max_context:
@@ -383,7 +387,7 @@ class Worker:
                     self.sched.release(job)
                 return
         # ---- prefix reuse
-        start, hit = 0, self.cache.best_match(prompt, cmd.get("media", ""))
+        start, hit = 0, self.cache.best_match(parr, cmd.get("media", ""))
         if hit is not None and self.cache.ensure_loaded(hit, self.b.device):
             self.b.restore(region, hit.image)
             start = hit.image.length
@@ -395,7 +399,7 @@ class Worker:
             start -= 1                       # the last prompt token is re-run to produce its logits
         # ---- checkpoint plan for the part that is prefilled now
         cks = policy.checkpoint_positions(len(prompt), start, self.ck_min, self.ck_align)
-        shared = policy.shared_prefix_checkpoint(self.cache.longest_shared(prompt), start,
+        shared = policy.shared_prefix_checkpoint(self.cache.longest_shared(parr), start,
                                                  cks[0] if cks else len(prompt), len(prompt), 128)
         if shared is not None:
             cks = sorted(set(cks + [shared]))
@@ -427,7 +431,7 @@ class Worker:
                 # encoder checkpoints of an unfinished Begin)
                 if reached - start >= self.ck_min and reached < len(prompt):
                     try:
-                        self.cache.insert(self.b.snapshot(region, prompt[:reached], "checkpoint", cmd.get("media", "")))
+                        self.cache.insert(self.b.snapshot(region, parr[:reached], "checkpoint", cmd.get("media", "")))
                         self.log.log("prefill_interrupted", id=cmd["id"], saved=reached, of=len(prompt))
                     except Exception as e:  # noqa: BLE001  (a refused save never fails the cancellation)
                         self.log.log("save_failed", incident=True, error=str(e))
@@ -437,14 +441,15 @@ class Worker:
                 return
             pos = stop
             if stop != len(prompt):
-                self.cache.insert(self.b.snapshot(region, prompt[:stop], "checkpoint", cmd.get("media", "")))
+                self.cache.insert(self.b.snapshot(region, parr[:stop], "checkpoint", cmd.get("media", "")))
         first = self.b.sample(logits, cmd["temperature"], cmd["top_p"], cmd["seed"], len(prompt))
         slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=cmd["seed"],
                           temperature=cmd["temperature"], top_p=cmd["top_p"], recent=list(prompt[-8:]))
         if self.history_lookup:
             from ..spec.history_lookup import HistoryLookup
-            slot.lookup = HistoryLookup(prompt, depth=8)
+            slot.lookup = HistoryLookup(parr, depth=8)
         a = Active(job or Job(cmd["id"], prompt, cmd["limit"]), slot, prompt, cmd["limit"], t0, time.monotonic())
+        a.prompt_arr = parr
         a.job.region = region
         self.active[region] = a
         ms = (time.monotonic() - t0) * 1e3
@@ -499,7 +504,11 @@ class Worker:
         a = self.active.pop(region, None)
         if a is None:
             return
-        committed = a.prompt + a.slot.emitted
+        import numpy as np
+        parr = getattr(a, "prompt_arr", None)
+        if parr is None:
+            parr = np.asarray(a.prompt, dtype=np.int64)
+        committed = np.concatenate([parr, np.asarray(a.slot.emitted, dtype=np.int64)])
         try:
             self.cache.insert(self.b.snapshot(region, committed[: a.slot.length], "complete", a.job.media),
                               completed=True)

@@ -33,15 +33,67 @@ class Proposal:
     source_end: int         # index in the history right after the earlier occurrence
 
 
+class _Text:
+    """Append-only token text: an integer array for what arrived in bulk (a prompt of a million
+    tokens stays one array: no Python integer per token) followed by a list of the tokens committed
+    one by one.  Indexing and slicing return Python ints / lists."""
+
+    def __init__(self):
+        import numpy as np
+        self.base = np.zeros(0, dtype=np.int64)
+        self.tail: List[int] = []
+
+    def __len__(self) -> int:
+        return int(self.base.shape[0]) + len(self.tail)
+
+    def __getitem__(self, i):
+        nb = int(self.base.shape[0])
+        if isinstance(i, slice):
+            lo, hi, st = i.indices(len(self))
+            assert st == 1
+            out = self.base[lo:min(hi, nb)].tolist() if lo < nb else []
+            if hi > nb:
+                out += self.tail[max(0, lo - nb):hi - nb]
+            return out
+        if i < 0:
+            i += len(self)
+        return int(self.base[i]) if i < nb else self.tail[i - nb]
+
+    def append(self, t: int) -> None:
+        self.tail.append(t)
+
+    def extend_array(self, arr) -> None:
+        import numpy as np
+        if self.tail:
+            self.base = np.concatenate([self.base, np.asarray(self.tail, dtype=np.int64)])
+            self.tail = []
+        self.base = np.concatenate([self.base, arr]) if self.base.shape[0] else arr.copy()
+
+    def array(self, lo: int):
+        """Tokens [lo, end) as an int64 array."""
+        import numpy as np
+        nb = int(self.base.shape[0])
+        head = self.base[min(lo, nb):]
+        return np.concatenate([head, np.asarray(self.tail[max(0, lo - nb):], dtype=np.int64)]) if self.tail else head
+
+    def truncate(self, length: int) -> None:
+        nb = int(self.base.shape[0])
+        if length >= nb:
+            del self.tail[length - nb:]
+        else:
+            self.base, self.tail = self.base[:length].copy(), []
+
+
 class HistoryLookup:
     BULK_SPAN = 4           # a bulk commit indexes at most this many windows per table slot
 
     def __init__(self, prefix: Sequence[int] = (), slots: int = SLOTS, lengths: Sequence[int] = LENGTHS,
                  minimum_match: Optional[int] = None, depth: int = 5):
-        self.tokens: List[int] = []
+        import numpy as np
+        self.tokens = _Text()
         self.slots, self.lengths, self.depth = slots, tuple(lengths), depth
         self.minimum = minimum_match or self.lengths[0]
-        self.tables = [[EMPTY] * slots for _ in self.lengths]
+        self.tables = [np.full(slots, EMPTY, dtype=np.int64) for _ in self.lengths]
         if len(prefix):
             self.commit(0, prefix)
 
@@ -66,14 +118,15 @@ class HistoryLookup:
         token-by-token commits (a slot keeps the LAST position that hashed to it)."""
         import numpy as np
         base = len(self.tokens)
-        self.tokens.extend(np.asarray(tokens, dtype=np.int64).tolist())
+        new = np.asarray(tokens, dtype=np.int64)
+        self.tokens.extend_array(new)
         n = len(self.tokens)
         # A slot keeps the last position that hashed to it, so of a very long run only the most recent
         # windows survive: with 4 x slots windows indexed, an older one would have been overwritten
         # with probability 1 - e^-4.  Bounding the run keeps a million-token prompt at the cost of a
         # quarter-million-token one.
         first = max(0, n - self.BULK_SPAN * self.slots - self.lengths[-1])
-        text = np.asarray(self.tokens[first:], dtype=np.uint64) & np.uint64(0xFFFFFFFF)
+        text = self.tokens.array(first).astype(np.uint64) & np.uint64(0xFFFFFFFF)
         for li, L in enumerate(self.lengths):
             # windows [i, i + L) predict token i + L; only windows whose predicted token is new
             lo = max(0, base - L, first)
@@ -88,13 +141,11 @@ class HistoryLookup:
             keys = (v % np.uint64(self.slots)).astype(np.int64)
             pos = np.arange(lo + L, hi + L, dtype=np.int64)
             keep = pos >= max(base, L)
-            tab = np.asarray(self.tables[li], dtype=np.int64)
-            np.maximum.at(tab, keys[keep], pos[keep])
-            self.tables[li] = tab.tolist()
+            np.maximum.at(self.tables[li], keys[keep], pos[keep])
 
     def truncate(self, length: int) -> None:
         """Drop text past ``length`` (a cancelled or rolled-back turn); stale slots are caught by confirmation."""
-        del self.tokens[length:]
+        self.tokens.truncate(length)
 
     def propose(self, pending: Sequence[int] = ()) -> Optional[Proposal]:
         """``pending``: tokens already emitted but not yet committed (the anchor); the match runs over
@@ -110,7 +161,7 @@ class HistoryLookup:
             if n < L or L < self.minimum or len(tail) < L:
                 continue
             suffix = tail[len(tail) - L:]
-            pos = self.tables[li][fingerprint(suffix) % self.slots]
+            pos = int(self.tables[li][fingerprint(suffix) % self.slots])
             if pos == EMPTY or pos >= nt or pos < L:
                 continue
             if self.tokens[pos - L:pos] != suffix:
