@@ -170,12 +170,13 @@ def test_index_scoring_in_row_tiles_is_bitwise_the_same():
     W = oracle.init_weights(cfg, 0)
     mk = lambda nbytes: E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512,
                                                                prefill_widths=(256,), index_score_bytes=nbytes), W)
-    whole, tiled = mk(2 << 30), mk(16 << 10)          # 16 KB: tiles of 64 rows at 60 entries a row
+    whole, tiled = mk(2 << 30), mk(256 << 10)         # 256 KB: tiles of 64 rows of 1,024 scores
     prompt = torch.randint(0, cfg.vocab, (239,), generator=torch.Generator().manual_seed(8)).tolist()
     a = whole.forward(E.StepPlan.build([(0, 0, prompt)]))
     b = tiled.forward(E.StepPlan.build([(0, 0, prompt)]))
     tiled.status.check()
-    assert ("scores", 239) in whole._scratch and ("scores", 64) in tiled._scratch and ("scores", 239) not in tiled._scratch
+    assert ("scores", 239) in whole._scratch and "scores_flat" in tiled._scratch and ("scores", 239) not in tiled._scratch
+    assert tiled._scratch["scores_flat"].numel() == 64 * 1024
     for li in cfg.index_source_layers:
         assert torch.equal(whole._bufs(239)["sel"][li], tiled._bufs(239)["sel"][li])
     assert torch.equal(a, b)

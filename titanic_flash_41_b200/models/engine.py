@@ -712,12 +712,20 @@ class Engine:
         sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
         return max(1, min(64, -(-keys // 64), -(-2 * sms // T)))
 
-    def scores_buffer(self, T: int, n: int) -> torch.Tensor:
+    def scores_buffer(self, T: int, n: int, tiled: bool = False) -> torch.Tensor:
+        """fp32 [T, width >= n] index scores.  ``tiled``: a view of ONE flat buffer of at most
+        ``index_score_bytes`` shared by every tile shape (the tile height changes with the context
+        length; a buffer per shape would pile up)."""
+        width = -(-max(n, 1024) // 1024) * 1024
+        if tiled:
+            flat = self._scratch.get("scores_flat")
+            if flat is None or flat.numel() < T * width:
+                flat = torch.empty(max(T * width, self.ecfg.index_score_bytes // 4), dtype=torch.float32, device=self.dev)
+                self._scratch["scores_flat"] = flat
+            return flat[: T * width].view(T, width)
         key = ("scores", T)
         b = self._scratch.get(key)
         if b is None or b.shape[1] < n:
-            width = max(n, 1024)
-            width = -(-width // 1024) * 1024
             b = torch.empty(T, width, dtype=torch.float32, device=self.dev)
             self._scratch[key] = b
         return b
@@ -971,11 +979,14 @@ class Engine:
         # rows scored per launch: all of them unless the fp32 score matrix would pass the limit
         # (whole scoring groups of one conversation's consecutive rows)
         rows_t = T
-        if T > self.SMALL_M and T * nmax * 4 > self.ecfg.index_score_bytes:
+        width = -(-max(nmax, 1024) // 1024) * 1024
+        if T > self.SMALL_M and T * width * 4 > self.ecfg.index_score_bytes:
             unit = max(rows_per_group, 32)
-            rows_t = max(unit, (self.ecfg.index_score_bytes // (4 * max(nmax, 1))) // unit * unit)
+            rows_t = max(unit, (self.ecfg.index_score_bytes // (4 * width)) // unit * unit)
             rows_t = min(rows_t, T)
-        scores = self.scores_buffer(rows_t, nmax)
+        # prefill rows with a large score matrix share the flat buffer (never captured in a graph);
+        # decode rows keep a buffer per row count, whose address a captured graph may hold
+        scores = self.scores_buffer(rows_t, nmax, tiled=rows_t < T or (T > self.SMALL_M and T * width * 4 > (64 << 20)))
         ks_min = self.ecfg.key_sharded_index_min
         if self.world > 1 and ks_min > 0 and T <= self.SMALL_M and nmax >= ks_min and not (two_level and li == pub):
             # every rank holds all index keys: split the scoring work by key range, gather the local
