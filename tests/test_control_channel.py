@@ -84,3 +84,31 @@ def test_bad_ticket_is_refused():
     t.join(10)
     srv.close()
     assert "bad control hello" in out.get("err", "")
+
+
+def test_followers_that_start_before_the_leader_keep_trying():
+    """Ranks start in any order: a follower whose connect is refused because rank 0 is not listening
+    yet retries until the deadline (and reports a clear error when nobody ever listens)."""
+    import time
+    probe = socket.create_server(("127.0.0.1", 0))
+    port = probe.getsockname()[1]
+    probe.close()                                  # a free port nobody listens on yet
+    out, err = [None, None], [None, None]
+
+    def run(rank, delay):
+        try:
+            time.sleep(delay)
+            ch = ControlChannel.connect(rank, 2, "127.0.0.1", port, b"late", 10.0)
+            out[rank] = ch.command(b"hello" if rank == 0 else None)
+        except Exception as e:  # noqa: BLE001
+            err[rank] = e
+    ts = [threading.Thread(target=run, args=(1, 0.0)), threading.Thread(target=run, args=(0, 0.6))]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(20)
+    assert err == [None, None] and out == [b"hello", b"hello"]
+    t0 = time.monotonic()
+    with pytest.raises(ControlError, match="no control listener"):
+        ControlChannel.connect(1, 2, "127.0.0.1", port, b"late", 0.4)
+    assert time.monotonic() - t0 < 5

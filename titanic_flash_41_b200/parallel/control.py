@@ -19,6 +19,7 @@ from __future__ import annotations
 import hashlib
 import socket
 import struct
+import time
 import threading
 from typing import List, Optional
 
@@ -87,7 +88,16 @@ class ControlChannel:
                 if listener is None:
                     srv.close()
             return ControlChannel(0, world, [p for p in peers[1:]])
-        s = socket.create_connection((host, port), timeout=timeout)
+        # rank 0 may not be listening yet (the ranks start in any order): keep trying until the deadline
+        deadline = time.monotonic() + timeout
+        while True:
+            try:
+                s = socket.create_connection((host, port), timeout=timeout)
+                break
+            except (ConnectionRefusedError, ConnectionResetError, socket.timeout, TimeoutError) as e:
+                if time.monotonic() >= deadline:
+                    raise ControlError(f"rank {rank}: no control listener at {host}:{port} within {timeout:.0f} s") from e
+                time.sleep(0.05)
         s.settimeout(timeout)
         s.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
         _send(s, K_HELLO, 0, struct.pack("<I", rank) + tag)
