@@ -167,3 +167,63 @@ def test_supervisor_stops_the_cohort_when_a_rank_leaves_cleanly():
     # all ranks leaving together within the grace period is a normal shutdown
     ok = ["-c", "import os, time; time.sleep(0.1 * int(os.environ['RANK']))"]
     assert launcher.launch(ok, 3, master_port=_free_port(), pin=False, poll_s=0.02, grace_s=5.0) == 0
+
+
+def _heartbeat_rank(rank, world, port, scenario, q):
+    """One CPU rank of the heartbeat tests (gloo).  ``scenario``: "poison" = rank 1 reports a local
+    fatal condition after a few rounds; "leave" = rank 2 exits between rounds without a word."""
+    import torch.distributed as dist
+
+    from titanic_flash_41_b200.utils.health import CohortHeartbeat, Health
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    group = CohortHeartbeat.make_group(timeout=3.0)
+    health = Health()
+    hb = CohortHeartbeat(health, group, rank, world, interval=0.1)
+    hb.start()
+    t0 = time.monotonic()
+    while hb.rounds < 3 and time.monotonic() - t0 < 20:
+        time.sleep(0.02)
+    healthy_rounds = hb.rounds
+    if scenario == "poison" and rank == 1:
+        health.report("device", "kernel 7 reported timeout")
+    if scenario == "leave" and rank == 2:
+        os._exit(0)                                   # between rounds, nothing in flight on any device
+    t1 = time.monotonic()
+    while health.ok and time.monotonic() - t1 < 20:
+        time.sleep(0.02)
+    q.put((rank, healthy_rounds, health.state(), time.monotonic() - t1))
+    time.sleep(0.5)                                   # let the last round reach the others
+    os._exit(0)
+
+
+@pytest.mark.parametrize("scenario", ["poison", "leave"])
+def test_cohort_heartbeat_spreads_a_poisoned_rank_and_notices_a_rank_that_left(scenario):
+    """Host-side heartbeat on its own gloo group: a rank that reports a fatal condition poisons the
+    others within an interval; a rank that exits between rounds makes the others' next round fail
+    (or time out after 3 s) -- no device collective has to run into its own timeout first."""
+    import torch.multiprocessing as mp
+    world, port = 3, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_heartbeat_rank, args=(r, world, port, scenario, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    got = {}
+    for _ in range(world if scenario == "poison" else world - 1):
+        r, rounds, state, waited = q.get(timeout=90)
+        got[r] = (rounds, state, waited)
+    for p in ps:
+        p.join(30)
+    assert all(v[0] >= 3 for v in got.values())                       # the cohort was healthy first
+    if scenario == "poison":
+        assert got[1][1]["source"] == "device"
+        for r in (0, 2):
+            st = got[r][1]
+            assert st["poisoned"] and st["source"] == "cohort" and "[1]" in st["why"] and "poisoned" in st["why"], st
+            assert got[r][2] < 5.0
+    else:
+        for r in (0, 1):
+            st = got[r][1]
+            assert st["poisoned"] and st["source"] == "cohort", st
+            assert got[r][2] < 10.0

@@ -223,6 +223,13 @@ def serve_main(args) -> int:
     probes = {"control": control_probe(control)}
     if hasattr(backend, "status_snapshot"):
         probes["device"] = status_probe(backend.status_snapshot)
+    if world > 1:
+        # host-side heartbeat of the cohort on its own gloo group: a poisoned rank poisons the others
+        # within a second, a rank that died is noticed without waiting for a device collective to time out
+        from .utils.health import CohortHeartbeat
+        heartbeat = CohortHeartbeat(health, CohortHeartbeat.make_group(timeout=20.0), rank, world, interval=1.0)
+        heartbeat.start()
+        probes["cohort"] = heartbeat.probe()
     Watchdog(health, probes, on_poison=lambda rec: log.log("poisoned", incident=True, **rec)).start()
     if not args.no_self_check and backend.regions >= 2:
         # every rank runs the same fixture (its collectives line up); raises before the server reports ready

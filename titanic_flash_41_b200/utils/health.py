@@ -99,3 +99,69 @@ class Watchdog(threading.Thread):
 
     def stop(self) -> None:
         self._stop.set()
+
+
+class CohortHeartbeat(threading.Thread):
+    """Host-side heartbeat of the whole cohort on its OWN gloo process group.
+
+    Every ``interval`` seconds each rank's heartbeat thread joins one small all-reduce that carries
+    every rank's health flag.  Two things follow.  A rank that reported a fatal condition poisons
+    the others within one interval ("rank 3 is poisoned"), instead of at their next device
+    collective; and a rank whose process died or stopped on the host makes the all-reduce fail or
+    time out on the others after ``timeout`` seconds, long before a device collective would give up
+    (the default process-group timeout is minutes).  This is the job of the reference's async-error
+    poll on its communicator (src/collective.rs:255 check_async), done on the host: nothing here
+    touches the GPU or the device communicator, so it can run beside captured graphs.
+
+    The group must be created by every rank in the same order (``CohortHeartbeat.make_group``, a
+    collective call); the thread only ever issues collectives on that group.
+    """
+
+    def __init__(self, health: Health, group, rank: int, world: int, interval: float = 1.0):
+        super().__init__(daemon=True, name="tflash-heartbeat")
+        self.health, self.group, self.rank, self.world, self.interval = health, group, rank, world, interval
+        self.failed: Optional[str] = None
+        self.rounds = 0
+        self._stop = threading.Event()
+
+    @staticmethod
+    def make_group(timeout: float = 10.0):
+        import datetime
+
+        import torch.distributed as dist
+        return dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout))
+
+    def beat_once(self) -> Optional[str]:
+        """One round; returns what is wrong with the cohort (None: every rank is alive and healthy)."""
+        import torch
+        import torch.distributed as dist
+        flags = torch.zeros(self.world, dtype=torch.int32)
+        flags[self.rank] = 1 if self.health.ok else 2
+        try:
+            dist.all_reduce(flags, group=self.group)
+        except Exception as e:  # noqa: BLE001  (a peer that left, a timeout: both mean the cohort is gone)
+            return f"cohort heartbeat failed: {e!r}"
+        self.rounds += 1
+        bad = [r for r in range(self.world) if int(flags[r]) != 1]
+        if bad:
+            return "rank(s) %s %s" % (bad, "poisoned" if all(int(flags[r]) == 2 for r in bad) else "missed the heartbeat")
+        return None
+
+    def run(self) -> None:
+        while not self._stop.is_set():
+            why = self.beat_once()
+            if why is not None:
+                self.failed = why
+                self.health.report("cohort", why)
+                if not why.startswith("rank(s)"):
+                    return                      # the group itself is broken: no further rounds
+            if not self.health.ok and self.failed is not None and self.rounds > 0:
+                # one more round has told the others; a poisoned rank retires
+                return
+            self._stop.wait(self.interval)
+
+    def probe(self) -> Callable[[], Optional[str]]:
+        return lambda: self.failed
+
+    def stop(self) -> None:
+        self._stop.set()
