@@ -46,8 +46,13 @@ def main():
     backend = EngineBackend(eng, chunk=chunk)
     assert SP.attach(eng) is not None
     sched = Scheduler(2, 8, 2) if rank == 0 else None
+    # the host-side heartbeat of the cohort runs beside the serving loop, on its own gloo group
+    from titanic_flash_41_b200.utils.health import CohortHeartbeat, Health
+    health = Health()
+    heartbeat = CohortHeartbeat(health, CohortHeartbeat.make_group(timeout=30.0), rank, world, interval=0.2)
+    heartbeat.start()
     worker = Worker(backend, sched, SessionCache(slots=8, budget_bytes=1 << 30), eos_id=-1, control=control, rank=rank,
-                    checkpoint_min=chunk, checkpoint_align=chunk)
+                    checkpoint_min=chunk, checkpoint_align=chunk, health=health)
     events, failure, shared = {}, [], {}
 
     def submit(jid, toks, n, **kw):
@@ -106,6 +111,7 @@ def main():
         assert ready_of("follow")["cache_n"] == 3 * chunk + 37 + 12
     torch.cuda.synchronize()
     eng.status.check()
+    assert health.ok and heartbeat.rounds > 0 and heartbeat.failed is None, (health.state(), heartbeat.rounds)
     # every rank took the same commands ...
     kinds = [(e["kind"], e.get("id")) for e in worker.log.snapshot(4096)["events"] if e["kind"] in ("begin", "finish")]
     all_kinds = [None] * world
@@ -131,6 +137,7 @@ def main():
         got = [torch.empty_like(t) for _ in range(world)]
         dist.all_gather(got, t)
         assert all(torch.equal(got[0], g_) for g_ in got)
+    heartbeat.stop()
     dist.barrier()
     if rank == 0:
         print("MGPU_SERVE_OK", world, ready_of("again"), ready_of("follow"), flush=True)
