@@ -118,3 +118,24 @@ def test_protocol_and_checkpoint_utilities(tmp_path, capsys):
     assert cli.main(["scan", ck, "--model-config", cfgp]) == 0
     out = json.loads(capsys.readouterr().out)
     assert out["matches_config"] and "F8_E4M3" in out["dtypes"]
+
+
+def test_serve_policy_flags_reach_the_session_cache(tmp_path):
+    """--disk-cache / --cache-slots / --device-cache-gib / --host-cache-gib / --checkpoint-tokens shape the
+    cache and the worker the server builds (every rank its own disk directory)."""
+    from titanic_flash_41_b200 import cli
+    args = cli.build_parser().parse_args(["serve", "--preset", "tiny", "--disk-cache", str(tmp_path), "--cache-slots", "5",
+                                          "--device-cache-gib", "0.5", "--host-cache-gib", "2", "--checkpoint-tokens", "1024",
+                                          "--prefill-slice-ms", "250"])
+    ecfg = cli.engine_config(args, world=2)
+    assert (ecfg.session_slots, ecfg.session_budget_bytes, ecfg.host_tier_bytes) == (5, 1 << 29, 2 << 30)
+    assert ecfg.checkpoint_min_tokens == 1024 and ecfg.prefill_slice_ms == 250 and ecfg.tp == 2
+    cache = cli.make_session_cache(ecfg, rank=1)
+    assert cache.slots == 5 and cache.budget == 1 << 29 and cache.host_budget == 2 << 30
+    assert cache.disk is not None and cache.disk.dir.endswith("rank1") and (tmp_path / "rank1").is_dir()
+    none = cli.make_session_cache(cli.engine_config(cli.build_parser().parse_args(["serve", "--preset", "tiny"]), 1), 0)
+    assert none.disk is None and none.slots == 16
+    # ranks that were started with different cache policies must not form a cohort
+    other = cli.build_parser().parse_args(["serve", "--preset", "tiny", "--cache-slots", "6"])
+    cfg = cli.model_config(args)
+    assert cli.policy_digest(cfg, args, 2) != cli.policy_digest(cfg, other, 2)

@@ -46,7 +46,15 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--api-key", default=os.environ.get("TFLASH_API_KEY", ""))
     s.add_argument("--queue-limit", type=int, default=16)
     s.add_argument("--tokenizer", help="tokenizer.json (byte-level BPE); byte tokenizer when absent")
-    s.add_argument("--disk-cache", help="directory for the disk tier of the session cache")
+    s.add_argument("--disk-cache", help="directory for the disk tier of the session cache (every rank uses its own "
+                   "sub-directory)")
+    s.add_argument("--cache-slots", type=int, default=16, help="entries of the session cache")
+    s.add_argument("--device-cache-gib", type=float, default=8.0, help="device memory for cached state images")
+    s.add_argument("--host-cache-gib", type=float, default=32.0, help="pinned host memory for parked state images")
+    s.add_argument("--checkpoint-tokens", type=int, default=8192, help="spacing of prompt checkpoints; shorter prompts "
+                   "leave none")
+    s.add_argument("--prefill-slice-ms", type=int, default=500, help="a long prefill yields to a decode step of the "
+                   "other conversations this often")
     s.add_argument("--event-log", help="JSONL event log path")
     s.add_argument("--no-self-check", action="store_true", help="skip the start-up reproducibility check")
     s.add_argument("--log-confidence", action="store_true", help="event per decode round with the drafter's confidences "
@@ -124,6 +132,27 @@ def stage_weights(args) -> dict:
             "sha256": meta["sha256"]}
 
 
+def engine_config(args, world: int) -> EngineConfig:
+    """Runtime policy from the command line (what the serving stack reads: regions, context, cache
+    tiers, checkpoint spacing, prefill slices)."""
+    g = lambda name, default: getattr(args, name, default)
+    return EngineConfig(tp=world, regions=args.regions, max_context=args.max_context,
+                        session_slots=g("cache_slots", 16), session_budget_bytes=int(g("device_cache_gib", 8.0) * 2 ** 30),
+                        host_tier_bytes=int(g("host_cache_gib", 32.0) * 2 ** 30), disk_tier_dir=g("disk_cache", None) or "",
+                        checkpoint_min_tokens=g("checkpoint_tokens", 8192), prefill_slice_ms=g("prefill_slice_ms", 500))
+
+
+def make_session_cache(ecfg: EngineConfig, rank: int):
+    """The session cache with its three tiers as the policy describes them."""
+    from .serve.session_cache import SessionCache
+    disk = None
+    if ecfg.disk_tier_dir:
+        from .serve.state_image import DiskTier
+        disk = DiskTier(os.path.join(ecfg.disk_tier_dir, f"rank{rank}"))
+    return SessionCache(slots=ecfg.session_slots, budget_bytes=ecfg.session_budget_bytes, disk=disk,
+                        host_budget_bytes=ecfg.host_tier_bytes)
+
+
 def make_backend(args, cfg: ModelConfig, comm):
     import torch
     from .serve.backend import EngineBackend, OracleBackend
@@ -137,7 +166,7 @@ def make_backend(args, cfg: ModelConfig, comm):
     world = getattr(comm, "world", 1)
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    ecfg = EngineConfig(tp=world, regions=args.regions, max_context=args.max_context)
+    ecfg = engine_config(args, world)
     if world > 1:
         ecfg.sp_chunk_rows = min(max(ecfg.prefill_widths) * world, 65536)      # sequence-parallel chunks span the ranks' slices
     import time as _time
@@ -172,7 +201,8 @@ def policy_digest(cfg: ModelConfig, args, world: int) -> str:
     import hashlib
     from .config import agree_digest
     h = hashlib.sha256(agree_digest([cfg]).encode())
-    for k in ("backend", "regions", "max_context", "seed", "checkpoint", "vision"):
+    for k in ("backend", "regions", "max_context", "seed", "checkpoint", "vision", "cache_slots", "device_cache_gib",
+              "host_cache_gib", "checkpoint_tokens", "prefill_slice_ms"):
         h.update(f"{k}={getattr(args, k, None)!r};".encode())
     h.update(f"world={world}".encode())
     return h.hexdigest()
@@ -218,8 +248,12 @@ def serve_main(args) -> int:
             span_encoder = SpanEncoder(tower)
     from .utils.health import Health, Watchdog, control_probe, status_probe
     health = Health()
-    worker = Worker(backend, sched, SessionCache(), eos_id=getattr(tok, "eos_id", 1), log=log, control=control, rank=rank,
-                    span_encoder=span_encoder, health=health, log_confidence=getattr(args, "log_confidence", False))
+    policy_cfg = engine_config(args, world)
+    worker = Worker(backend, sched, make_session_cache(policy_cfg, rank), eos_id=getattr(tok, "eos_id", 1), log=log,
+                    control=control, rank=rank, span_encoder=span_encoder, health=health,
+                    log_confidence=getattr(args, "log_confidence", False),
+                    prefill_slice_s=policy_cfg.prefill_slice_ms / 1e3, checkpoint_min=policy_cfg.checkpoint_min_tokens,
+                    checkpoint_align=policy_cfg.checkpoint_min_tokens)
     probes = {"control": control_probe(control)}
     if hasattr(backend, "status_snapshot"):
         probes["device"] = status_probe(backend.status_snapshot)

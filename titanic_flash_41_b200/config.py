@@ -328,17 +328,13 @@ class EngineConfig(_JsonMixin):
     moe_parallel: str = "ep"           # "ep": whole experts per rank; "tp": column-sliced
     regions: int = 4                   # concurrently admitted conversations
     max_context: int = 131072
-    page_tokens: int = 64
     prefill_widths: Tuple[int, ...] = (256, 1024, 4096, 16384)
-    verify_rows: int = 4               # 1 anchor + draft depth
-    session_slots: int = 16
-    session_budget_bytes: int = 8 << 30
-    snapshot_chunk_bytes: int = 16 << 20
-    host_tier_bytes: int = 32 << 30
-    disk_tier_dir: str = ""
-    disk_chunk_bytes: int = 4 << 20
-    checkpoint_min_tokens: int = 8192
-    prefill_slice_ms: int = 500
+    session_slots: int = 16            # entries of the session cache (state images of prefixes and finished turns)
+    session_budget_bytes: int = 8 << 30   # device bytes the cache may hold; older images move to the host tier
+    host_tier_bytes: int = 32 << 30    # pinned host bytes of parked images; beyond it they go to the disk tier
+    disk_tier_dir: str = ""            # directory of the disk tier ("" = none: the oldest host images are dropped instead)
+    checkpoint_min_tokens: int = 8192  # prompts shorter than this leave no intermediate checkpoints; also the checkpoint spacing
+    prefill_slice_ms: int = 500        # a prefill yields to one batched decode step of the other conversations this often
     spin_limit: int = 20_000_000       # bounded device waits (reference src/roce.rs:1196-1199)
     use_cuda_graphs: bool = True
     key_sharded_index_min: int = 262144  # decode rows: split index scoring over the ranks from this many keys (0 = never); below about a million tokens of context the exchange costs more than the scoring it saves
