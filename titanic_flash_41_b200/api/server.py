@@ -40,11 +40,13 @@ def _err(status: int, code: str, message: str, headers: Optional[Dict[str, str]]
 class Frontend:
     """Protocol + tokenizer: request body -> token ids; token ids -> deltas."""
 
-    def __init__(self, tokenizer, context: int, allow_sampling: bool = True, vision=None):
+    def __init__(self, tokenizer, context: int, allow_sampling: bool = True, vision=None,
+                 default_max_tokens: int = P.DEFAULT_MAX_NEW_TOKENS):
         """``vision``: an ``api.media.VisionFrontend`` when the deployment has a vision tower; without
         one a request that carries image parts is refused (it must never be answered as if the image
         had been seen)."""
         self.tok, self.context, self.allow_sampling, self.vision = tokenizer, context, allow_sampling, vision
+        self.default_max_tokens = default_max_tokens      # new tokens of a request that names no limit
         # plain-text regions between template markers are tokenised through a bounded, exact cache:
         # long documents repeat from turn to turn (reference: src/prompt_regions.rs)
         from .prompt_regions import RegionCache
@@ -93,7 +95,7 @@ class Frontend:
             except M.MediaError as e:
                 raise P.ProtocolError(str(e), 400, "invalid_media") from e
             tokens = pm.tokens
-        limit = P.resolve_max_tokens(req.max_new_tokens, len(tokens), self.context)
+        limit = P.resolve_max_tokens(req.max_new_tokens, len(tokens), self.context, self.default_max_tokens)
         return req, tokens, limit, pm
 
 

@@ -273,7 +273,7 @@ def serve_main(args) -> int:
         worker.run_forever()
         return 0
     from .utils.memory import host_admission
-    server = Server(scfg, Frontend(tok, args.max_context, vision=vision_front), sched, log,
+    server = Server(scfg, Frontend(tok, args.max_context, vision=vision_front, default_max_tokens=scfg.default_max_tokens), sched, log,
                     memory=host_admission(int(args.memory_floor_gib * 2 ** 30),
                                           log=lambda rec: log.log(rec.get("event", "memory"), incident=True,
                                                                   **{k: v for k, v in rec.items() if k != "event"})),

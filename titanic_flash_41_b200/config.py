@@ -186,6 +186,7 @@ class ModelConfig(_JsonMixin):
              "every kv source layer must run an indexer")
         need(all(0 <= l < self.n_layers for l in self.index_source_layers), "index source layer range")
         need(self.compress_ratio >= 1, "compress ratio")
+        need(self.candidate_block == 8, "candidate blocks are 8 keys (the block-maximum kernel's unit)")
         if self.compress_ratios:
             need(len(self.compress_ratios) == len(self.kv_source_layers), "one compress ratio per kv source layer")
             need(min(self.compress_ratios) == self.compress_ratio, "compress_ratio must be the smallest of compress_ratios")

@@ -476,6 +476,8 @@ class Engine:
                  comm: Optional[Comm] = None, device="cuda", max_chunk: int = 0,
                  draft_layers: Optional[List[LayerWeights]] = None, draft_extra: Optional[dict] = None):
         self.cfg, self.ecfg = cfg, ecfg
+        if ecfg.max_context > cfg.max_positions:
+            raise ValueError(f"max_context {ecfg.max_context} exceeds the model's {cfg.max_positions} positions")
         self.comm = comm or LocalComm()
         self.world, self.rank = self.comm.world, self.comm.rank
         self.dev = torch.device(device)
