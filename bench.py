@@ -128,6 +128,8 @@ def main():
                     "(default: the engine configuration's setting)")
     ap.add_argument("--nvtx-step", action="store_true", help="run one extra eager decode step inside the NVTX range "
                     "'tf_decode_step' (a profiler can then list exactly the kernels of a step)")
+    ap.add_argument("--graph-clock", action="store_true", help="after the timed steps: capture the decode step once more with a "
+                    "device timestamp in front of every kernel call and print where the time goes inside the replayed graph")
     ap.add_argument("--trace", action="store_true", help="print per-kernel time tables of one extra prefill pass and one eager decode step")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -298,6 +300,19 @@ def main():
     dec.device_events = None
     clocks = sampler.stop(local) if rank == 0 else {}
     eng.status.check()
+    if args.graph_clock and not args.no_graph:
+        # a second decoder (the timed one stays as it was): its graph carries a timestamp kernel in front
+        # of every kernel call; the table is read after a replay
+        from titanic_flash_41_b200.utils.trace import GraphClock
+        dec2 = SpecDecoder(eng, SESSIONS, temperature=0.6, top_p=0.95, use_graph=True)
+        dec2.hidden.copy_(dec.hidden)
+        dec2.clock = GraphClock(device=dev)
+        probe = [DecodeSlot(region=s.region, length=s.length, anchor=s.anchor, seed=s.seed) for s in slots]
+        for _ in range(3):
+            dec2.step(probe)
+        if rank == 0:
+            print("decode step inside the replayed graph (device timestamps before and after every call; a call's time includes one ~2 us stamp)\n"
+                  + dec2.clock.report(top=30), file=sys.stderr, flush=True)
     t = torch.tensor([e2e_ms, dev_ms] + [m / k for m, k in zip(seg_ms, seg_steps)], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

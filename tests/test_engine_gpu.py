@@ -707,3 +707,33 @@ def test_memory_report_accounts_for_what_the_engine_holds():
     assert rep["expert_weights"] == sum(nb(getattr(L, f)) for L in eng.layers + eng.draft_layers
                                         for f in ("ew1", "ew3", "ew2", "es1", "es3", "es2") if getattr(L, f) is not None)
     assert rep["dense_weights"] > 0 and rep["row_scratch"] > 0 and rep["embeddings_and_heads"] >= nb(eng.embed_w)
+
+
+def test_graph_clock_times_the_kernels_inside_a_replayed_graph():
+    """Device timestamps captured with the decode graph: every replay refreshes them; the per-kernel
+    table covers the kernels of the step and adds up to about the span of the step."""
+    from titanic_flash_41_b200.config import DraftConfig
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot, SpecDecoder
+    from titanic_flash_41_b200.utils.trace import GraphClock
+    cfg = small_config(draft=DraftConfig(layers=1, depth=3))
+    eng = E.Engine.from_weights(cfg, EngineConfig(reference_matmul=True, regions=2, max_context=512, prefill_widths=(128,)),
+                                oracle.init_weights(cfg, 0))
+    prompt = torch.randint(0, cfg.vocab, (60,), generator=torch.Generator().manual_seed(2)).tolist()
+    lg = eng.forward(E.StepPlan.build([(0, 0, prompt)], logits="last"))
+    sl = DecodeSlot(region=0, length=60, anchor=int(lg.argmax()), seed=3)
+    dec = SpecDecoder(eng, 1, use_graph=True)
+    dec.clock = GraphClock()
+    dec.hidden.copy_(eng.last_hidden[-1:])
+    dec.step([sl])
+    first = dec.clock.ring[: 2 * len(dec.clock.marks)].clone()
+    dec.step([sl])
+    second = dec.clock.ring[: 2 * len(dec.clock.marks)].clone()
+    eng.status.check()
+    assert len(dec.clock.marks) > 50 and bool((second > first).all())          # the replay wrote new times
+    rows = dec.clock.table()
+    names = {r[0] for r in rows}
+    assert {"tf_sparse_attention", "tf_attn_prep", "tf_sample_chunks"} <= names
+    total, span = sum(r[2] for r in rows), dec.clock.span_us()
+    assert 0 < span < 1e5 and 0.3 * span <= total <= 1.3 * span, (total, span)   # gaps are not charged; side branches overlap
+    assert all(r[2] > 0 for r in rows)
+    assert "inside the graph" in dec.clock.report()

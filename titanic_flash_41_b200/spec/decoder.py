@@ -160,6 +160,9 @@ class SpecDecoder:
         # when a list: (start, end) CUDA events around the device work of every step (uploads and the
         # result download excluded), for callers that report device time of exactly the steps they ran
         self.device_events: Optional[list] = None
+        # utils.trace.GraphClock (set before the first step): device timestamps in front of every kernel
+        # call of the step, captured into the graph; ``clock.report()`` after a step shows the replay
+        self.clock = None
 
     # ---------------------------------------------------------------------------------
     def _fill_host(self, slots: Sequence[DecodeSlot]) -> int:
@@ -298,12 +301,20 @@ class SpecDecoder:
                 self.hidden.copy_(carried)
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
-                    self._device_step(bucket)
+                    if self.clock is not None:
+                        with self.clock:                # device timestamps captured with the kernels
+                            self._device_step(bucket)
+                    else:
+                        self._device_step(bucket)
             ev = self._mark()
             self.graph.replay()
         else:
             ev = self._mark()
-            self._device_step(bucket)
+            if self.clock is not None:
+                with self.clock:
+                    self._device_step(bucket)
+            else:
+                self._device_step(bucket)
         if ev is not None:
             ev[1].record()
         self.h_out.copy_(self.d_out, non_blocking=True)

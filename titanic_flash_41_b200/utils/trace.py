@@ -5,6 +5,10 @@
                   marks forward parts (attention, moe, head...), ``report()`` gives the table a
                   request's ``timings`` carries (reference: src/layer_clock.rs:45 arm, :135 part,
                   :148 mark, :99 parts_us; globaltimer marks become event pairs here).
+``GraphClock``    device timestamps (``tf_stamp``: the GPU's global timer, one tiny kernel) in front of
+                  every exported kernel call while a CUDA graph is captured; every replay refreshes
+                  them, so the table shows where the time goes INSIDE the graph, which CUDA events
+                  cannot do (reference: the globaltimer marks of src/layer_clock.rs).
 ``Knockout``      skips named kernels so that their cost can be bounded by difference; results are
                   wrong on purpose while it is active (reference: src/knockout.rs:37-63).
 ``RouteCensus``   per-expert routing counts from the router's id tensor
@@ -74,6 +78,73 @@ class KernelClock:
         for k, n, ms in rows[:top]:
             out.append(f"{k:34s} {n:7d} {ms:10.3f} {100 * ms / total:6.1f}%")
         out.append(f"{'total':34s} {sum(r[1] for r in rows):7d} {total:10.3f}")
+        return "\n".join(out)
+
+
+class GraphClock:
+    """Use: ``with clock:`` around the CAPTURE of a graph (or around eager launches), replay the
+    graph, synchronise, then ``table()``.  A stamp precedes and follows every exported kernel call on
+    the stream the call goes to, so a call's time is the difference of its own two stamps (it
+    includes one stamp, about 2 us); PyTorch's own kernels and the launch gaps between calls are what
+    is left of the span.  Calls on a side stream overlap the main stream: the rows need not add up
+    to the span."""
+
+    def __init__(self, capacity: int = 8192, device="cuda"):
+        self.capacity = capacity
+        self.ring = torch.zeros(capacity, dtype=torch.int64, device=device)
+        self.marks: List[str] = []          # kernel name per call; call i owns slots 2i (before) and 2i + 1 (after)
+        self._orig = None
+
+    def __enter__(self):
+        self.marks.clear()
+        self._orig = native.call
+        clock = self
+
+        def stamped(name, *args, **kw):
+            i = len(clock.marks)
+            if 2 * i + 1 >= clock.capacity:
+                return clock._orig(name, *args, **kw)
+            clock.marks.append(name)
+            clock._orig("tf_stamp", clock.ring, 2 * i, clock.capacity)
+            try:
+                return clock._orig(name, *args, **kw)
+            finally:
+                clock._orig("tf_stamp", clock.ring, 2 * i + 1, clock.capacity)
+        native.call = stamped
+        return self
+
+    def __exit__(self, *exc):
+        native.call = self._orig
+        self._orig = None
+        return False
+
+    def _times(self):
+        torch.cuda.synchronize()
+        return self.ring[: 2 * len(self.marks)].cpu().tolist()
+
+    def table(self) -> List[Tuple[str, int, float]]:
+        """(kernel, calls, microseconds) of the last run of the stamped launches, largest first."""
+        t = self._times()
+        acc: Dict[str, List[float]] = defaultdict(lambda: [0, 0.0])
+        for i, name in enumerate(self.marks):
+            acc[name][0] += 1
+            acc[name][1] += max(0, t[2 * i + 1] - t[2 * i]) / 1e3
+        return sorted(((k, int(v[0]), v[1]) for k, v in acc.items()), key=lambda r: -r[2])
+
+    def span_us(self) -> float:
+        """First stamp to last stamp of the last run."""
+        t = self._times()
+        return (max(t) - min(t)) / 1e3 if t else 0.0
+
+    def report(self, top: int = 24) -> str:
+        rows = self.table()
+        total = sum(r[2] for r in rows) or 1.0
+        span = self.span_us()
+        out = ["%-32s %6s %10s %6s" % ("kernel (inside the graph)", "calls", "us", "% span")]
+        for name, n, us in rows[:top]:
+            out.append("%-32s %6d %10.1f %5.1f%%" % (name, n, us, 100 * us / max(span, 1e-9)))
+        out.append("%-32s %6d %10.1f  (first to last stamp %.1f us; side-stream calls overlap the main stream)"
+                   % ("all calls", len(self.marks), total, span))
         return "\n".join(out)
 
 
