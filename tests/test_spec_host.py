@@ -171,3 +171,35 @@ def test_confidence_head_stops_blocks_early_and_greedy_text_is_unchanged():
     # sampling: still runs and still commits at least the anchor every round
     sampled, r_s = run((0.15, 0.25, 0.20), 0.8)
     assert len(sampled) == 24 and all(n >= 1 for n, _ in r_s)
+
+
+def test_history_text_of_bulk_and_single_commits_behaves_like_one_list():
+    """The copy-proposal history keeps a bulk-committed prompt as an array and later tokens in a list:
+    indexing, slicing across the seam, truncation on either side and proposals equal a plain list's."""
+    import random
+    rnd = random.Random(3)
+    prompt = [rnd.randrange(3, 40) for _ in range(700)]           # > 256 tokens: the bulk path
+    later = [rnd.randrange(3, 40) for _ in range(90)]
+    a = HistoryLookup(prompt, depth=6)
+    b = HistoryLookup(depth=6)
+    for i, t in enumerate(prompt):
+        b.commit(i, [t])
+    assert all((x == y).all() for x, y in zip(a.tables, b.tables))
+    for i, t in enumerate(later):
+        a.commit(700 + i, [t])
+        b.commit(700 + i, [t])
+    ref = prompt + later
+    assert len(a.tokens) == len(ref) and a.tokens[0] == ref[0] and a.tokens[-1] == ref[-1] and a.tokens[699] == ref[699]
+    assert a.tokens[690:710] == ref[690:710] and a.tokens[:5] == ref[:5] and a.tokens[780:] == ref[780:]
+    assert all((x == y).all() for x, y in zip(a.tables, b.tables))
+    pa, pb = a.propose(pending=[ref[-1]]), b.propose(pending=[ref[-1]])
+    assert (pa is None) == (pb is None) and (pa is None or (pa.tokens, pa.matched, pa.source_end) == (pb.tokens, pb.matched, pb.source_end))
+    a.truncate(750)                                                # inside the list part
+    assert len(a.tokens) == 750 and a.tokens[745:] == ref[745:750]
+    a.truncate(650)                                                # inside the array part
+    assert len(a.tokens) == 650 and a.tokens[640:] == ref[640:650]
+    a.commit(650, ref[650:660])
+    assert a.tokens[645:660] == ref[645:660]
+    # a second bulk commit after single tokens folds the list into the array
+    a.commit(660, ref[660:] + prompt)
+    assert len(a.tokens) == 790 + 700 and a.tokens[785:795] == (ref + prompt)[785:795]
