@@ -271,6 +271,8 @@ def serve_main(args) -> int:
         log.log("self_check", **self_check(backend))
     if rank != 0:
         worker.run_forever()
+        if world > 1:
+            heartbeat.stop()
         return 0
     from .utils.memory import host_admission
     server = Server(scfg, Frontend(tok, args.max_context, vision=vision_front, default_max_tokens=scfg.default_max_tokens), sched, log,
@@ -284,6 +286,8 @@ def serve_main(args) -> int:
     asyncio.run(serve(server))
     sched.close()
     t.join(timeout=30)
+    if world > 1:
+        heartbeat.stop()
     return 0
 
 

@@ -150,6 +150,8 @@ class CohortHeartbeat(threading.Thread):
     def run(self) -> None:
         while not self._stop.is_set():
             why = self.beat_once()
+            if self._stop.is_set():
+                return                          # stopping: a peer that already left is not a failure
             if why is not None:
                 self.failed = why
                 self.health.report("cohort", why)
