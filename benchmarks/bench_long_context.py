@@ -51,8 +51,9 @@ def build_backend(a, comm=None):
         from titanic_flash_41_b200.models import oracle
         from titanic_flash_41_b200.serve.backend import OracleBackend
         cfg = tiny_config()
+        kw = {"comm": comm} if comm is not None else {}
         return cfg, OracleBackend(cfg, oracle.init_weights(cfg, 0), regions=a.regions, max_context=a.target + a.follow + 512,
-                                  chunk=a.chunk)
+                                  chunk=a.chunk, **kw)
     from titanic_flash_41_b200.models.engine import Engine
     from titanic_flash_41_b200.serve.backend import EngineBackend
     world = comm.world if comm is not None else 1
@@ -105,8 +106,11 @@ def main(argv=None):
         import torch.distributed as dist
         from titanic_flash_41_b200.parallel.comm import DistComm
         from titanic_flash_41_b200.parallel.control import ControlChannel
-        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
-        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+        if a.backend == "oracle":
+            dist.init_process_group("gloo")          # the CPU plumbing run of the same driver
+        else:
+            torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
         comm = DistComm()
         control = ControlChannel.connect(rank, world, "127.0.0.1", int(os.environ["MASTER_PORT"]) + 13, b"long-context", 600.0)
     t_load = time.monotonic()
@@ -211,7 +215,8 @@ def _leave(world, disk, tmp):
     os.rmdir(tmp)
     if world > 1:
         import torch.distributed as dist
-        torch.cuda.synchronize()
+        if torch.cuda.is_available() and dist.get_backend() == "nccl":
+            torch.cuda.synchronize()
         dist.barrier()
         sys.stdout.flush()
         os._exit(0)          # no collective teardown while symmetric-memory mappings are alive

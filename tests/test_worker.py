@@ -388,3 +388,23 @@ def test_worker_logs_the_drafters_confidences_per_round_when_asked():
     assert rounds and all(1 <= e["verified"] <= 3 and e["emitted"] <= e["verified"] + 1 and
                           len(e["confidence"]) >= e["verified"] for e in rounds)
     assert not any("token" in k for e in rounds for k in e)
+
+
+def test_long_context_stress_script_as_two_cpu_ranks():
+    """The same script as one rank per process (gloo, oracle backend split over two ranks): rank 0 owns
+    the scheduler, rank 1 follows over the control channel; the run ends by itself on both."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29671", os.path.join(root, "benchmarks", "bench_long_context.py"), "--backend", "oracle",
+           "--sessions", "2", "--regions", "2", "--target", "128", "--grow", "64", "--short", "2", "--short-tokens", "16",
+           "--follow", "16", "--new-tokens", "3", "--chunk", "32", "--checkpoint", "32", "--cache-slots", "16"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert r.returncode == 0 and len(lines) == 1, r.stdout[-2000:] + r.stderr[-2000:]
+    out = json.loads(lines[0])
+    assert out["n_gpus"] == 2 and out["context"] >= 128 and len(out["resume_ttft_s"]) == 2
+    assert all(c >= 120 for c in out["resume_cached_tokens"]), out
