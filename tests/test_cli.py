@@ -139,3 +139,39 @@ def test_serve_policy_flags_reach_the_session_cache(tmp_path):
     other = cli.build_parser().parse_args(["serve", "--preset", "tiny", "--cache-slots", "6"])
     cfg = cli.model_config(args)
     assert cli.policy_digest(cfg, args, 2) != cli.policy_digest(cfg, other, 2)
+
+
+@pytest.mark.timeout(300)
+def test_launch_two_cpu_ranks_serve_end_to_end():
+    """``launch --gpus 2 -- serve`` on CPU (gloo, oracle backend split over two ranks): the ranks agree
+    on the policy, connect the control channel in whatever order they start, run the start-up check and
+    the cohort heartbeat, rank 0 answers over HTTP, and a shutdown request ends both ranks with code 0."""
+    port, mport = _free_port(), _free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    p = subprocess.Popen([sys.executable, "-m", "titanic_flash_41_b200", "launch", "--gpus", "2", "--master-port", str(mport),
+                          "--", "serve", "--preset", "tiny", "--backend", "oracle", "--port", str(port),
+                          "--max-context", "512", "--regions", "2", "--api-key", "k"],
+                         env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        base = f"http://127.0.0.1:{port}"
+        for _ in range(1200):
+            try:
+                if requests.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except requests.RequestException:
+                pass
+            assert p.poll() is None, p.stdout.read().decode()[-3000:]
+            time.sleep(0.1)
+        h = {"Authorization": "Bearer k"}
+        body = {"model": "x", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 5, "temperature": 0}
+        r = requests.post(base + "/v1/chat/completions", json=body, headers=h, timeout=120)
+        assert r.status_code == 200, r.text
+        again = requests.post(base + "/v1/chat/completions", json=body, headers=h, timeout=120).json()
+        assert again["choices"][0]["message"] == r.json()["choices"][0]["message"]
+        health = requests.get(base + "/health", timeout=5).json()
+        assert health.get("poisoned") in (False, None), health
+        assert requests.post(base + "/_native/shutdown", headers=h, timeout=5).status_code == 200
+        assert p.wait(timeout=90) == 0, p.stdout.read().decode()[-3000:]
+    finally:
+        if p.poll() is None:
+            p.kill()
