@@ -169,7 +169,7 @@ def test_launch_two_cpu_ranks_serve_end_to_end():
         again = requests.post(base + "/v1/chat/completions", json=body, headers=h, timeout=120).json()
         assert again["choices"][0]["message"] == r.json()["choices"][0]["message"]
         health = requests.get(base + "/health", timeout=5).json()
-        assert health.get("poisoned") in (False, None), health
+        assert health["status"] == "ready" and health["cohort"]["poisoned"] is False, health
         assert requests.post(base + "/_native/shutdown", headers=h, timeout=5).status_code == 200
         assert p.wait(timeout=90) == 0, p.stdout.read().decode()[-3000:]
     finally:
