@@ -175,3 +175,48 @@ def test_launch_two_cpu_ranks_serve_end_to_end():
     finally:
         if p.poll() is None:
             p.kill()
+
+
+def test_verify_staged_and_pack_engram_commands(tmp_path, capsys):
+    """Weight tools: a staged atlas is re-read and its digests checked (a flipped byte or another model is
+    refused); an n-gram table is packed into the row file the row store reads."""
+    import numpy as np
+    import torch
+
+    from titanic_flash_41_b200.formats.safetensors import CheckpointError
+    from titanic_flash_41_b200.models import engram as EG
+    from titanic_flash_41_b200.models import loader, oracle
+    cfg = tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4")
+    cfgp = os.path.join(str(tmp_path), "cfg.json")
+    open(cfgp, "w").write(cfg.to_json())
+    ck, st = os.path.join(str(tmp_path), "ck"), os.path.join(str(tmp_path), "st")
+    loader.export_checkpoint(oracle.init_weights(cfg, seed=1), cfg, ck)
+    assert cli.main(["stage-weights", "--model-config", cfgp, "--checkpoint", ck, "--out", st, "--rank", "0", "--world", "1"]) == 0
+    capsys.readouterr()
+    d = os.path.join(st, "rank0")
+    assert cli.main(["verify-staged", d, "--model-config", cfgp]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["ok"] and out["tensors"] > 10 and out["model_checked"] and len(out["digest"]) == 64
+    other = os.path.join(str(tmp_path), "other.json")
+    open(other, "w").write(tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4", n_layers=3).to_json())
+    with pytest.raises(CheckpointError):
+        cli.main(["verify-staged", d, "--model-config", other])
+    with open(os.path.join(d, "atlas.bin"), "r+b") as f:
+        f.seek(100)
+        b = f.read(1)
+        f.seek(100)
+        f.write(bytes([b[0] ^ 0x40]))
+    with pytest.raises(CheckpointError):
+        cli.main(["verify-staged", d])
+    # ---- n-gram table
+    vals = torch.randn(37, 256) * 3
+    np.save(os.path.join(str(tmp_path), "t.npy"), vals.numpy())
+    tab = os.path.join(str(tmp_path), "t.engram")
+    assert cli.main(["pack-engram", os.path.join(str(tmp_path), "t.npy"), "--out", tab, "--row-start", "100"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["rows"] == 37 and out["row_start"] == 100 and out["bytes"] == 37 * 264 and out["max_abs_error"] < 0.5
+    packed, start = EG.read_table(tab)
+    assert start == 100 and torch.equal(packed, EG.pack_rows(vals))
+    with pytest.raises(SystemExit):
+        np.save(os.path.join(str(tmp_path), "bad.npy"), np.zeros((4, 100), dtype=np.float32))
+        cli.main(["pack-engram", os.path.join(str(tmp_path), "bad.npy"), "--out", tab])

@@ -1,7 +1,8 @@
 """Command line: ``python -m titanic_flash_41_b200 {serve,bench,stage-weights,probe,launch}``.
 
 ``serve`` runs the OpenAI-compatible server on rank 0 and a worker loop on every rank;
-``bench`` times prefill and speculative decode; ``stage-weights`` writes this rank's weight atlas;
+``bench`` times prefill and speculative decode; ``stage-weights`` writes this rank's weight atlas,
+``verify-staged`` re-reads one and checks its digests, ``pack-engram`` packs an n-gram table;
 ``probe`` prints the device / peer-access / build facts the engine depends on (reference:
 src/main.rs Cli and its subcommands).
 """
@@ -91,6 +92,17 @@ def build_parser() -> argparse.ArgumentParser:
     sc.add_argument("checkpoint")
     sc.add_argument("--preset", choices=sorted(PRESETS))
     sc.add_argument("--model-config")
+    vs = sub.add_parser("verify-staged", help="re-read a staged weight atlas and check every tensor's digest "
+                        "(and, with a preset / model config, that it was staged for that model)")
+    vs.add_argument("dir")
+    vs.add_argument("--preset")
+    vs.add_argument("--model-config")
+    pe = sub.add_parser("pack-engram", help="pack an n-gram memory table ([rows, 256] values: .npy, or a tensor of a "
+                        "safetensors checkpoint) into the 264-byte MXFP8 row file the row store reads")
+    pe.add_argument("source", help=".npy file, or a checkpoint directory / .safetensors file with --tensor")
+    pe.add_argument("--tensor", help="tensor name inside the checkpoint")
+    pe.add_argument("--out", required=True)
+    pe.add_argument("--row-start", type=int, default=0, help="first row of this shard in the whole table")
     sm = sub.add_parser("smoke", help="live endpoint check: health, models, one completion, one stream")
     sm.add_argument("--url", default="http://127.0.0.1:8000")
     sm.add_argument("--api-key", default=os.environ.get("TFLASH_API_KEY", ""))
@@ -330,6 +342,30 @@ def utility(args) -> Optional[int]:
             out["matches_config"] = True
         print(json.dumps(out))
         return 0
+    if args.cmd == "verify-staged":
+        from .formats import atlas
+        cfg = model_config(args) if (args.preset or args.model_config) else None
+        tensors = atlas.load_staged(args.dir, cfg, verify=True)          # raises on a size, digest or model mismatch
+        print(json.dumps({"ok": True, "tensors": len(tensors), "bytes": sum(t.numel() * t.element_size() for t in tensors.values()),
+                          "digest": atlas.device_digest(tensors), "model_checked": cfg is not None}))
+        return 0
+    if args.cmd == "pack-engram":
+        import numpy as np
+        import torch
+        from .models import engram as EG
+        if args.tensor:
+            from .formats.safetensors import Checkpoint
+            vals = Checkpoint.scan(args.source).read(args.tensor).float()
+        else:
+            vals = torch.from_numpy(np.load(args.source)).float()
+        if vals.dim() != 2 or vals.shape[1] != 256:
+            raise SystemExit(f"pack-engram: expected [rows, 256] values, got {tuple(vals.shape)}")
+        packed = EG.pack_rows(vals)
+        EG.write_table(args.out, packed, args.row_start)
+        err = float((EG.unpack_rows(packed) - vals).abs().max())
+        print(json.dumps({"rows": int(vals.shape[0]), "row_start": args.row_start, "bytes": int(packed.numel()),
+                          "max_abs_error": err}))
+        return 0
     if args.cmd == "smoke":
         from .api.smoke import run as smoke_run
         return smoke_run(args.url, args.api_key)
@@ -338,7 +374,8 @@ def utility(args) -> Optional[int]:
 
 def main(argv: Optional[list] = None) -> int:
     args = build_parser().parse_args(argv)
-    if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke"):
+    if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke", "verify-staged",
+                    "pack-engram"):
         return utility(args)
     if args.cmd == "probe":
         print(json.dumps(probe()))
