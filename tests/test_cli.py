@@ -220,3 +220,37 @@ def test_verify_staged_and_pack_engram_commands(tmp_path, capsys):
     with pytest.raises(SystemExit):
         np.save(os.path.join(str(tmp_path), "bad.npy"), np.zeros((4, 100), dtype=np.float32))
         cli.main(["pack-engram", os.path.join(str(tmp_path), "bad.npy"), "--out", tab])
+
+
+def test_plan_and_run_file_commands(tmp_path, capsys):
+    """`plan`: bytes and tensor kinds per rank of a checkpoint; `run-file`: a JSONL of requests through the
+    serving stack without HTTP (a repeated prompt is served from the cache, greedy results repeat)."""
+    from titanic_flash_41_b200.models import loader, oracle
+    cfg = tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4")
+    cfgp = os.path.join(str(tmp_path), "cfg.json")
+    open(cfgp, "w").write(cfg.to_json())
+    ck = os.path.join(str(tmp_path), "ck")
+    loader.export_checkpoint(oracle.init_weights(cfg, seed=1), cfg, ck)
+    assert cli.main(["plan", ck, "--model-config", cfgp, "--world", "2"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["world"] == 2 and len(out["ranks"]) == 2
+    assert all(0 < r["bytes"] < out["checkpoint_bytes"] for r in out["ranks"])
+    assert sum(r["bytes"] for r in out["ranks"]) >= out["checkpoint_bytes"]          # replicated tensors count twice
+    assert "expert_local" in out["ranks"][0]["tensors_by_kind"] and "shard" in out["ranks"][0]["tensors_by_kind"]
+    # ---- file-driven run on the CPU oracle
+    reqs = os.path.join(str(tmp_path), "reqs.jsonl")
+    prompt = [5 + (i * 37) % 900 for i in range(200)]
+    with open(reqs, "w") as f:
+        f.write(json.dumps({"id": "a", "tokens": prompt, "max_tokens": 6}) + "\n")
+        f.write(json.dumps({"id": "b", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0.8,
+                            "seed": 3}) + "\n")
+        f.write(json.dumps({"id": "c", "tokens": prompt, "max_tokens": 6}) + "\n")
+    res = os.path.join(str(tmp_path), "res.jsonl")
+    assert cli.main(["run-file", "--preset", "tiny", "--backend", "oracle", "--regions", "1", "--max-context", "256",
+                     "--requests", reqs, "--out", res, "--checkpoint-tokens", "16"]) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summary == {"requests": 3, "completed": 3, "out": res}
+    rows = {r["id"]: r for r in map(json.loads, open(res).read().splitlines())}
+    assert rows["a"]["tokens"] == rows["c"]["tokens"] and len(rows["a"]["tokens"]) == 6
+    assert rows["a"]["cache_n"] == 0 and rows["c"]["cache_n"] >= 64              # the repeat came from the cache
+    assert rows["b"]["finish_reason"] in ("stop", "length") and isinstance(rows["b"]["text"], str)

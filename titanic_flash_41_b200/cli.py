@@ -14,7 +14,7 @@ import json
 import os
 import sys
 import threading
-from typing import Optional
+from typing import Dict, Optional
 
 from .config import EngineConfig, ModelConfig, ServerConfig, flash_b200_config, reference_1017_config, tiny_config
 
@@ -37,6 +37,18 @@ def _common(p: argparse.ArgumentParser) -> None:
     p.add_argument("--seed", type=int, default=0)
 
 
+def _cache_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--disk-cache", help="directory for the disk tier of the session cache (every rank uses its own "
+                   "sub-directory)")
+    p.add_argument("--cache-slots", type=int, default=16, help="entries of the session cache")
+    p.add_argument("--device-cache-gib", type=float, default=8.0, help="device memory for cached state images")
+    p.add_argument("--host-cache-gib", type=float, default=32.0, help="pinned host memory for parked state images")
+    p.add_argument("--checkpoint-tokens", type=int, default=8192, help="spacing of prompt checkpoints; shorter prompts "
+                   "leave none")
+    p.add_argument("--prefill-slice-ms", type=int, default=500, help="a long prefill yields to a decode step of the "
+                   "other conversations this often")
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="titanic_flash_41_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -47,15 +59,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--api-key", default=os.environ.get("TFLASH_API_KEY", ""))
     s.add_argument("--queue-limit", type=int, default=16)
     s.add_argument("--tokenizer", help="tokenizer.json (byte-level BPE); byte tokenizer when absent")
-    s.add_argument("--disk-cache", help="directory for the disk tier of the session cache (every rank uses its own "
-                   "sub-directory)")
-    s.add_argument("--cache-slots", type=int, default=16, help="entries of the session cache")
-    s.add_argument("--device-cache-gib", type=float, default=8.0, help="device memory for cached state images")
-    s.add_argument("--host-cache-gib", type=float, default=32.0, help="pinned host memory for parked state images")
-    s.add_argument("--checkpoint-tokens", type=int, default=8192, help="spacing of prompt checkpoints; shorter prompts "
-                   "leave none")
-    s.add_argument("--prefill-slice-ms", type=int, default=500, help="a long prefill yields to a decode step of the "
-                   "other conversations this often")
+    _cache_flags(s)
     s.add_argument("--event-log", help="JSONL event log path")
     s.add_argument("--no-self-check", action="store_true", help="skip the start-up reproducibility check")
     s.add_argument("--log-confidence", action="store_true", help="event per decode round with the drafter's confidences "
@@ -92,6 +96,21 @@ def build_parser() -> argparse.ArgumentParser:
     sc.add_argument("checkpoint")
     sc.add_argument("--preset", choices=sorted(PRESETS))
     sc.add_argument("--model-config")
+    pl = sub.add_parser("plan", help="per-rank placement of a checkpoint's tensors (replicated / sharded / local experts) "
+                        "and the bytes every rank would hold")
+    pl.add_argument("checkpoint")
+    pl.add_argument("--preset")
+    pl.add_argument("--model-config")
+    pl.add_argument("--world", type=int, default=8)
+    pl.add_argument("--moe-parallel", choices=["ep", "tp"], default="ep")
+    rf = sub.add_parser("run-file", help="file-driven finite run: requests from a JSONL file through the serving stack "
+                        "(scheduler, worker, cache), results to a JSONL file; no HTTP")
+    _common(rf)
+    rf.add_argument("--requests", required=True, help='JSONL: {"id", "tokens" | "messages", "max_tokens", "temperature", '
+                    '"top_p", "seed"} per line')
+    rf.add_argument("--out", required=True)
+    rf.add_argument("--tokenizer")
+    _cache_flags(rf)
     vs = sub.add_parser("verify-staged", help="re-read a staged weight atlas and check every tensor's digest "
                         "(and, with a preset / model config, that it was staged for that model)")
     vs.add_argument("dir")
@@ -303,6 +322,61 @@ def serve_main(args) -> int:
     return 0
 
 
+def run_file(args) -> int:
+    """Requests from a JSONL file through the serving stack of ONE process (the reference's
+    file-driven finite run, src/main.rs resident-token-peer): every request is admitted by the
+    scheduler, served by the worker (prefix reuse, batching, speculative decode) and written with its
+    tokens, finish reason and timings."""
+    from .api import protocol as P
+    from .api.tokenizer import load_tokenizer
+    from .parallel.comm import LocalComm
+    from .serve.scheduler import Job, Scheduler
+    from .serve.worker import Worker
+    cfg = model_config(args)
+    backend = make_backend(args, cfg, LocalComm())
+    tok = load_tokenizer(args.tokenizer, cfg.vocab)
+    sched = Scheduler(args.regions, 1 << 16, 1 << 16)
+    ecfg = engine_config(args, 1)
+    worker = Worker(backend, sched, make_session_cache(ecfg, 0), eos_id=getattr(tok, "eos_id", 1),
+                    checkpoint_min=ecfg.checkpoint_min_tokens, checkpoint_align=ecfg.checkpoint_min_tokens)
+    results: Dict[str, dict] = {}
+    order = []
+    for n, line in enumerate(l for l in open(args.requests).read().splitlines() if l.strip()):
+        req = json.loads(line)
+        jid = str(req.get("id", n))
+        if "tokens" in req:
+            toks = [int(t) for t in req["tokens"]]
+        else:
+            toks = tok.encode(P.render_chat(P.normalize_chat_request({"messages": req["messages"], "model": "x"})))
+        limit = P.resolve_max_tokens(req.get("max_tokens"), len(toks), args.max_context, 256)
+        results[jid] = {"id": jid, "prompt_tokens": len(toks), "tokens": []}
+        order.append(jid)
+
+        def emit(kind, payload, _r=results[jid]):
+            if kind == "tokens":
+                _r["tokens"] += list(payload)
+            elif kind == "ready":
+                _r["cache_n"], _r["prompt_ms"] = payload["cache_n"], payload["prompt_ms"]
+            elif kind == "done":
+                _r.update(finish_reason=payload["finish_reason"], decode_tok_s=payload.get("decode_tok_s"))
+            elif kind == "error":
+                _r.update(finish_reason="error", error=payload)
+        sched.submit(Job(jid, toks, limit, temperature=float(req.get("temperature", 0.0)), top_p=float(req.get("top_p", 1.0)),
+                         seed=int(req.get("seed", 0)), emit=emit))
+    sched.close()
+    worker._pending = []
+    while worker.running:
+        worker.run_once(0.0)
+    with open(args.out, "w") as f:
+        for jid in order:
+            r = results[jid]
+            r["text"] = tok.decode(r["tokens"])
+            f.write(json.dumps(r) + "\n")
+    done = sum(1 for r in results.values() if r.get("finish_reason") not in (None, "error"))
+    print(json.dumps({"requests": len(order), "completed": done, "out": args.out}))
+    return 0 if done == len(order) else 1
+
+
 def _read(arg: str) -> str:
     return sys.stdin.read() if arg == "-" else open(arg).read()
 
@@ -342,6 +416,26 @@ def utility(args) -> Optional[int]:
             out["matches_config"] = True
         print(json.dumps(out))
         return 0
+    if args.cmd == "plan":
+        from .formats import layout
+        from .formats.safetensors import Checkpoint
+        ck = Checkpoint.scan(args.checkpoint)
+        cfg = model_config(args) if (args.preset or args.model_config) else None
+        if cfg is None:
+            raise SystemExit("plan needs --preset or --model-config")
+        layout.validate_checkpoint(ck, cfg)
+        ranks = []
+        for r in range(args.world):
+            plan = layout.RankPlan.build(ck, cfg, r, args.world, args.moe_parallel)
+            kinds: dict = {}
+            for p_ in plan.entries.values():
+                kinds[p_.kind] = kinds.get(p_.kind, 0) + 1
+            ranks.append({"rank": r, "bytes": plan.local_bytes(ck), "tensors_by_kind": kinds})
+        print(json.dumps({"world": args.world, "moe_parallel": args.moe_parallel, "checkpoint_bytes":
+                          sum(t.nbytes for t in ck.tensors.values()), "ranks": ranks}))
+        return 0
+    if args.cmd == "run-file":
+        return run_file(args)
     if args.cmd == "verify-staged":
         from .formats import atlas
         cfg = model_config(args) if (args.preset or args.model_config) else None
@@ -375,7 +469,7 @@ def utility(args) -> Optional[int]:
 def main(argv: Optional[list] = None) -> int:
     args = build_parser().parse_args(argv)
     if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke", "verify-staged",
-                    "pack-engram"):
+                    "pack-engram", "plan", "run-file"):
         return utility(args)
     if args.cmd == "probe":
         print(json.dumps(probe()))
