@@ -103,6 +103,16 @@ def build_parser() -> argparse.ArgumentParser:
     pl.add_argument("--model-config")
     pl.add_argument("--world", type=int, default=8)
     pl.add_argument("--moe-parallel", choices=["ep", "tp"], default="ep")
+    pm = sub.add_parser("plan-memory", help="bytes one rank will hold on its GPU (weights, KV state of all regions, scratch, "
+                        "score buffer), from the configuration alone")
+    pm.add_argument("--preset", choices=sorted(PRESETS), default="flash-b200")
+    pm.add_argument("--model-config")
+    pm.add_argument("--gpus", type=int, default=1)
+    pm.add_argument("--regions", type=int, default=4)
+    pm.add_argument("--max-context", type=int, default=131072)
+    pm.add_argument("--chunk", type=int, default=16384, help="rows of a prefill chunk on one rank")
+    pm.add_argument("--device-cache-gib", type=float, default=8.0, help="device budget of the session cache")
+    pm.add_argument("--device-gib", type=float, default=180.0, help="memory of one GPU")
     rf = sub.add_parser("run-file", help="file-driven finite run: requests from a JSONL file through the serving stack "
                         "(scheduler, worker, cache), results to a JSONL file; no HTTP")
     _common(rf)
@@ -436,6 +446,23 @@ def utility(args) -> Optional[int]:
         return 0
     if args.cmd == "run-file":
         return run_file(args)
+    if args.cmd == "plan-memory":
+        from .utils.memory import plan_device_memory
+        cfg = model_config(args)
+        w = args.gpus
+        ecfg = EngineConfig(tp=w, regions=args.regions, max_context=args.max_context, prefill_widths=(args.chunk,),
+                            sp_chunk_rows=min(args.chunk * w, 65536) if w > 1 else 0)
+        plan = plan_device_memory(cfg, ecfg, w, chunk=args.chunk)
+        gib = {k: round(v / 2 ** 30, 2) for k, v in plan.items()}
+        gib["session_cache_budget"] = args.device_cache_gib
+        # measured on the runs recorded with the benchmarks: the row buffers of every other launch shape,
+        # the staging of the sequence-parallel exchanges and allocator slack add 7 GiB (one GPU) to 21 GiB (four)
+        gib["allowance_other_shapes_and_allocator"] = 7.0 if w == 1 else 21.0
+        need = gib["total"] + gib["session_cache_budget"] + gib["allowance_other_shapes_and_allocator"]
+        print(json.dumps({"model": cfg.name, "gpus": w, "regions": args.regions, "max_context": args.max_context,
+                          "gib_per_gpu": gib, "needed_gib": round(need, 1), "device_gib": args.device_gib,
+                          "fits": need <= args.device_gib}))
+        return 0
     if args.cmd == "verify-staged":
         from .formats import atlas
         cfg = model_config(args) if (args.preset or args.model_config) else None
@@ -469,7 +496,7 @@ def utility(args) -> Optional[int]:
 def main(argv: Optional[list] = None) -> int:
     args = build_parser().parse_args(argv)
     if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke", "verify-staged",
-                    "pack-engram", "plan", "run-file"):
+                    "pack-engram", "plan", "run-file", "plan-memory"):
         return utility(args)
     if args.cmd == "probe":
         print(json.dumps(probe()))
