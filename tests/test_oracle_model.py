@@ -120,3 +120,49 @@ def test_tp2_gloo_matches_single_rank(moe_parallel):
     assert toks1 == toks2
     for a, b in zip(logits1, logits2):
         assert torch.allclose(a, torch.from_numpy(b), atol=1e-4)
+
+
+def test_reference_feature_set_composes_at_toy_widths():
+    """Everything the reference model combines, at toy widths on the CPU oracle: per-source compression
+    ratios, four residual copies, low-rank query, grouped low-rank output, n-gram memory layers, a
+    two-layer drafter with Markov correction and confidence head.  Chunked prefill equals one shot, the
+    serving backend decodes with causal stopping, and a state image restores the conversation exactly."""
+    from titanic_flash_41_b200.config import DraftConfig, EngramConfig, RopeConfig, reference_1017_config
+    from titanic_flash_41_b200.serve.backend import OracleBackend
+    from titanic_flash_41_b200.spec.decoder import DecodeSlot
+    cfg = reference_1017_config(
+        n_layers=5, hidden=128, vocab=512, n_heads=4, head_dim=32, q_lora_rank=32, o_groups=2, o_lora_rank=16, window=16,
+        kv_source_layers=(1, 3), compress_ratios=(2, 1), index_source_layers=(1, 3, 4), index_heads=2, index_dim=32,
+        index_topk=8, candidate_blocks=0, late_start=4, n_experts=8, topk=2, moe_inter=64, shared_inter=64,
+        rope=RopeConfig(theta=10000.0, compress_theta=160000.0, dim=16), dense_quant="none", expert_quant="none",
+        kv_quant="none", draft=DraftConfig(layers=2, depth=4, condition_layers=1, markov_rank=16, confidence_head=True),
+        vision=None, engram=EngramConfig(layers=(1, 2), rows_per_table=64, width=256, heads=2, ngram=3, tables=2))
+    assert cfg.hc_mult == 4 and [cfg.ratio_of(l) for l in range(5)] == [1, 2, 2, 1, 1]
+    W = oracle.init_weights(cfg, 0)
+    m = oracle.OracleModel(cfg, W)
+    p = _prompts(cfg, 1, 45, 5)[0]
+    s1, s2 = m.new_session(64), m.new_session(64)
+    full = m.forward(p, s1)
+    parts = torch.cat([m.forward(p[a:b], s2) for a, b in ((0, 9), (9, 31), (31, 45))])
+    assert torch.isfinite(full).all() and torch.allclose(parts, full, atol=5e-5)
+
+    def decode(backend, slot, rounds):
+        for _ in range(rounds):
+            toks = backend.decode_step([slot])[0]
+            assert 1 <= len(toks) <= slot.verified + 1 <= 5 and len(slot.confidence) >= slot.verified
+        return list(slot.emitted)
+    b = OracleBackend(cfg, W, regions=2, max_context=128, chunk=16)
+    prompt = p.tolist()
+    lg = b.prefill(0, prompt, 0, None)
+    mk = lambda region, length, anchor, emitted=(): DecodeSlot(region=region, length=length, anchor=anchor, seed=1, temperature=0.7,
+                                                              top_p=0.9, recent=(prompt + list(emitted))[-8:])
+    sl = mk(0, 45, int(lg.argmax()))
+    first = decode(b, sl, 3)
+    img = b.snapshot(0, prompt + first[: sl.length - 45])
+    anchor = sl.anchor
+    rest = decode(b, sl, 3)[len(first):]
+    # the same conversation restored into the other region continues with the same tokens
+    b.restore(1, img)
+    sl2 = mk(1, img.length, anchor, first)
+    sl2.emitted = list(first)
+    assert decode(b, sl2, 3)[len(first):] == rest
