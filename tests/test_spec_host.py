@@ -203,3 +203,50 @@ def test_history_text_of_bulk_and_single_commits_behaves_like_one_list():
     # a second bulk commit after single tokens folds the list into the array
     a.commit(660, ref[660:] + prompt)
     assert len(a.tokens) == 790 + 700 and a.tokens[785:795] == (ref + prompt)[785:795]
+
+
+def test_rolling_hash_lookup_equals_a_brute_force_search():
+    """The rolled suffix hashes find what a search over the text finds: for random repetitive text, every
+    proposal is a true earlier occurrence of the longest indexed suffix that has one (hash collisions may only
+    lose a proposal, and with 65,536 slots over 600 tokens they do not)."""
+    import random
+    from titanic_flash_41_b200.spec.history_lookup import LENGTHS
+    rnd = random.Random(7)
+    phrase = [rnd.randrange(3, 30) for _ in range(70)]
+    text = []
+    while len(text) < 600:
+        text += phrase[: rnd.randrange(20, 70)] + [rnd.randrange(3, 30) for _ in range(rnd.randrange(1, 9))]
+    h = HistoryLookup(depth=5)
+    hits = 0
+    for i, t in enumerate(text):
+        h.commit(i, [t])
+        pending = [text[i + 1]] if i + 1 < len(text) and i % 3 == 0 else []
+        p = h.propose(pending=pending)
+        full = text[: i + 1] + pending
+        want = None
+        for L in sorted(LENGTHS, reverse=True):
+            if len(full) < L:
+                continue
+            suf = full[len(full) - L:]
+            # the LAST earlier occurrence whose following token is committed text (what a slot keeps)
+            cands = [e for e in range(L, i + 1) if text[e - L:e] == suf and e < len(text[: i + 1])]
+            cands = [e for e in cands if e <= i]
+            if cands:
+                want = (L, max(cands))
+                break
+        if want is None:
+            assert p is None
+        else:
+            assert p is not None and p.source_end == want[1] and p.matched >= want[0], (i, want, p)
+            assert p.tokens == text[want[1]: want[1] + 5][: len(p.tokens)] and len(p.tokens) >= 1
+            hits += 1
+    assert hits > 100
+    # a truncation re-seeds the rolling state (slots of the dropped text go stale and are caught by the
+    # confirmation): committing the same continuation again ends in the state of a fresh index
+    h.truncate(500)
+    for i in range(500, 600):
+        h.commit(i, [text[i]])
+    q = HistoryLookup(text[:600], depth=5)                # bulk path over the same text
+    assert h._raw == q._raw and len(h.tokens) == len(q.tokens) == 600
+    pa, pb = h.propose(), q.propose()
+    assert pa is None or pb is None or pa.tokens[:1] == text[pa.source_end: pa.source_end + 1]

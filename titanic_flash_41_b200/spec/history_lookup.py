@@ -19,11 +19,21 @@ EMPTY = -1
 MASK = (1 << 64) - 1
 
 
-def fingerprint(ids: Sequence[int]) -> int:
-    v = 0xCBF29CE484222325
-    for t in ids:
-        v = ((v ^ (t & 0xFFFFFFFF)) * 0x100000001B3) & MASK
+PRIME = 0x100000001B3            # odd multiplier of the polynomial hash (mod 2^64)
+
+
+def _mix(v: int) -> int:
     return v ^ (v >> 32)
+
+
+def fingerprint(ids: Sequence[int]) -> int:
+    """Polynomial hash of a window, sum (t_k + 1) * PRIME^(L-1-k) mod 2^64, folded once.  Unlike a
+    chained hash it can be ROLLED: appending a token and dropping the oldest is O(1), which is what a
+    decode step does for every suffix length."""
+    v = 0
+    for t in ids:
+        v = (v * PRIME + (t & 0xFFFFFFFF) + 1) & MASK
+    return _mix(v)
 
 
 @dataclass
@@ -94,6 +104,9 @@ class HistoryLookup:
         self.slots, self.lengths, self.depth = slots, tuple(lengths), depth
         self.minimum = minimum_match or self.lengths[0]
         self.tables = [np.full(slots, EMPTY, dtype=np.int64) for _ in self.lengths]
+        # raw (unfolded) hash of the last min(L, length) tokens per suffix length, rolled by every commit
+        self._raw = [0] * len(self.lengths)
+        self._top = [pow(PRIME, L - 1, 1 << 64) for L in self.lengths]       # weight of the oldest token of a full window
         if len(prefix):
             self.commit(0, prefix)
 
@@ -105,13 +118,16 @@ class HistoryLookup:
             self._commit_bulk(tokens)
             return
         for t in tokens:
-            self.tokens.append(int(t))
-            end = len(self.tokens)
-            # the suffix that ENDS BEFORE this token predicts it: index suffixes ending at end-1
+            t = int(t)
+            n = len(self.tokens)                            # position of this token
+            # the suffix that ENDS BEFORE this token predicts it: index it, then roll the window over the token
             for li, L in enumerate(self.lengths):
-                if end - 1 >= L:
-                    key = fingerprint(self.tokens[end - 1 - L:end - 1]) % self.slots
-                    self.tables[li][key] = end - 1           # position of the token that followed
+                raw = self._raw[li]
+                if n >= L:
+                    self.tables[li][_mix(raw) % self.slots] = n          # position of the token that followed
+                    raw = (raw - ((self.tokens[n - L] & 0xFFFFFFFF) + 1) * self._top[li]) & MASK
+                self._raw[li] = (raw * PRIME + (t & 0xFFFFFFFF) + 1) & MASK
+            self.tokens.append(t)
 
     def _commit_bulk(self, tokens: Sequence[int]) -> None:
         """Index a long run (a prompt) with vectorised fingerprints: the same table contents as
@@ -133,19 +149,30 @@ class HistoryLookup:
             hi = n - L                      # predicted positions lo + L .. n - 1
             if hi <= lo:
                 continue
-            v = np.full(hi - lo, 0xCBF29CE484222325, dtype=np.uint64)
+            v = np.zeros(hi - lo, dtype=np.uint64)
             with np.errstate(over="ignore"):
                 for k in range(L):
-                    v = (v ^ text[lo - first + k: hi - first + k]) * np.uint64(0x100000001B3)
+                    v = v * np.uint64(PRIME) + text[lo - first + k: hi - first + k] + np.uint64(1)
             v = v ^ (v >> np.uint64(32))
             keys = (v % np.uint64(self.slots)).astype(np.int64)
             pos = np.arange(lo + L, hi + L, dtype=np.int64)
             keep = pos >= max(base, L)
             np.maximum.at(self.tables[li], keys[keep], pos[keep])
+        self._reseed()
+
+    def _reseed(self) -> None:
+        """Rolling states from the text itself (after a bulk commit or a truncation)."""
+        n = len(self.tokens)
+        for li, L in enumerate(self.lengths):
+            raw = 0
+            for t in self.tokens[max(0, n - L):n]:
+                raw = (raw * PRIME + (t & 0xFFFFFFFF) + 1) & MASK
+            self._raw[li] = raw
 
     def truncate(self, length: int) -> None:
         """Drop text past ``length`` (a cancelled or rolled-back turn); stale slots are caught by confirmation."""
         self.tokens.truncate(length)
+        self._reseed()
 
     def propose(self, pending: Sequence[int] = ()) -> Optional[Proposal]:
         """``pending``: tokens already emitted but not yet committed (the anchor); the match runs over
@@ -154,16 +181,24 @@ class HistoryLookup:
         nt = len(self.tokens)
         n = nt + len(pend)
         span = self.lengths[-1]
-        tail = self.tokens[max(0, nt - span):] + pend        # the last tokens of the text: no copy of the history
         at = lambda i: self.tokens[i] if i < nt else pend[i - nt]
+        tail = None
         for li in range(len(self.lengths) - 1, -1, -1):
             L = self.lengths[li]
-            if n < L or L < self.minimum or len(tail) < L:
+            if n < L or L < self.minimum:
                 continue
-            suffix = tail[len(tail) - L:]
-            pos = int(self.tables[li][fingerprint(suffix) % self.slots])
+            # hash of the last L tokens of (committed + pending): the rolling state moved over the pending tokens
+            raw = self._raw[li]
+            for j, t in enumerate(pend):
+                if nt + j >= L:
+                    raw = (raw - ((at(nt + j - L) & 0xFFFFFFFF) + 1) * self._top[li]) & MASK
+                raw = (raw * PRIME + (t & 0xFFFFFFFF) + 1) & MASK
+            pos = int(self.tables[li][_mix(raw) % self.slots])
             if pos == EMPTY or pos >= nt or pos < L:
                 continue
+            if tail is None:
+                tail = self.tokens[max(0, nt - span):] + pend    # the last tokens of the text: no copy of the history
+            suffix = tail[len(tail) - L:]
             if self.tokens[pos - L:pos] != suffix:
                 continue                                       # collision or stale slot
             out = self.tokens[pos:pos + self.depth]
