@@ -105,6 +105,13 @@ class Worker:
         for i in range(0, len(blob), self.FRAME):
             self.control.command(blob[i:i + self.FRAME])
 
+    def _pool(self):
+        """One helper thread for host work that can run beside a prefill."""
+        if getattr(self, "_executor", None) is None:
+            from concurrent.futures import ThreadPoolExecutor
+            self._executor = ThreadPoolExecutor(max_workers=1, thread_name_prefix="tflash-host")
+        return self._executor
+
     def _recv_command(self) -> Dict[str, Any]:
         import numpy as np
         cmd = self.decode(self.control.command(None))
@@ -404,6 +411,12 @@ class Worker:
         if shared is not None:
             cks = sorted(set(cks + [shared]))
         logits, pos, reached = None, start, start
+        lookup_job = None
+        if self.history_lookup:
+            # indexing the prompt for copy proposals is host work that needs no result of the prefill:
+            # it runs beside it (array arithmetic releases the interpreter lock) and is collected below
+            from ..spec.history_lookup import HistoryLookup
+            lookup_job = self._pool().submit(HistoryLookup, parr, depth=8)
         last_slice = self.clock()
         for stop in cks + [len(prompt)]:
             if stop <= pos:
@@ -445,9 +458,8 @@ class Worker:
         first = self.b.sample(logits, cmd["temperature"], cmd["top_p"], cmd["seed"], len(prompt))
         slot = DecodeSlot(region=region, length=len(prompt), anchor=first, seed=cmd["seed"],
                           temperature=cmd["temperature"], top_p=cmd["top_p"], recent=list(prompt[-8:]))
-        if self.history_lookup:
-            from ..spec.history_lookup import HistoryLookup
-            slot.lookup = HistoryLookup(parr, depth=8)
+        if lookup_job is not None:
+            slot.lookup = lookup_job.result()
         a = Active(job or Job(cmd["id"], prompt, cmd["limit"]), slot, prompt, cmd["limit"], t0, time.monotonic())
         a.prompt_arr = parr
         a.job.region = region
