@@ -30,6 +30,33 @@ def test_probe_and_parser():
     assert a.cmd == "serve" and a.port == 1234 and cli.model_config(a).digest() == tiny_config().digest()
 
 
+def test_build_provenance_notices_changed_sources(tmp_path, monkeypatch):
+    """The build writes what it was built from; a source that changed afterwards is reported (a stale
+    library would otherwise be loaded without a word)."""
+    import shutil
+
+    from titanic_flash_41_b200.utils import build
+    src, out = tmp_path / "csrc", tmp_path / "lib"
+    src.mkdir()
+    out.mkdir()
+    (src / "a.cu").write_text("// a\n")
+    (src / "b.cuh").write_text("// b\n")
+    (out / "libx.so").write_bytes(b"\x7fELF fake")
+    monkeypatch.setattr(build, "CSRC", src)
+    monkeypatch.setattr(build, "OUT", out)
+    monkeypatch.setattr(build, "_run", lambda cmd: "nvcc: fake\nBuild fake_1.0")
+    assert build.provenance() == {"recorded": False, "stale_sources": [], "libraries_match": False}
+    build._write_provenance("nvcc")
+    ok = build.provenance()
+    assert ok["recorded"] and ok["stale_sources"] == [] and ok["libraries_match"] and ok["nvcc"] == "Build fake_1.0"
+    (src / "a.cu").write_text("// a changed\n")
+    (src / "c.cu").write_text("// new\n")
+    assert build.provenance()["stale_sources"] == ["a.cu", "c.cu"]
+    (out / "libx.so").write_bytes(b"other")
+    assert build.provenance()["libraries_match"] is False
+    shutil.rmtree(src)
+
+
 def test_stage_weights_command(tmp_path, capsys):
     from titanic_flash_41_b200.models import loader, oracle
     cfg = tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4")

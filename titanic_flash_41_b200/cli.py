@@ -148,6 +148,7 @@ def probe() -> dict:
     out = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available(),
            "library": str(build.OUT / "libtflash_cuda.so"), "devices": []}
     out["library_built"] = os.path.exists(out["library"])
+    out["build"] = build.provenance()          # sources changed since the libraries were built show up here
     if torch.cuda.is_available():
         n = torch.cuda.device_count()
         for i in range(n):

@@ -82,6 +82,46 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> None:
     hlib = OUT / "libtflash_host.so"
     if ccs and _stale(hlib, host_objs):
         _run(["g++", "-shared", "-pthread", "-o", str(hlib), *map(str, host_objs)])
+    _write_provenance(nvcc)
+
+
+def _sha256(path: Path) -> str:
+    import hashlib
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for block in iter(lambda: f.read(1 << 20), b""):
+            h.update(block)
+    return h.hexdigest()
+
+
+def _sources() -> List[Path]:
+    return sorted(p for pat in ("*.cu", "*.cuh", "*.h", "*.cc") for p in CSRC.glob(pat))
+
+
+def _write_provenance(nvcc: str) -> None:
+    """``lib/build.json``: what the libraries were built from (reference: the build-provenance record
+    of src/main.rs and tools/verify_runtime.py, which check bundles by SHA-256)."""
+    import json
+    ver = _run([nvcc, "--version"]).strip().splitlines()[-1]
+    rec = {"nvcc": ver, "flags": NVCC_FLAGS, "no_fast_math": sorted(NO_FAST_MATH),
+           "sources": {p.name: _sha256(p) for p in _sources()},
+           "libraries": {p.name: _sha256(p) for p in sorted(OUT.glob("*.so"))}}
+    (OUT / "build.json").write_text(json.dumps(rec, indent=1, sort_keys=True))
+
+
+def provenance() -> dict:
+    """Compare the tree with the record of the last build: sources changed, added or removed since then
+    (the loaded library would be stale) and libraries that are not the ones the build wrote."""
+    import json
+    path = OUT / "build.json"
+    if not path.exists():
+        return {"recorded": False, "stale_sources": [], "libraries_match": False}
+    rec = json.loads(path.read_text())
+    now = {p.name: _sha256(p) for p in _sources()}
+    stale = sorted(n for n in set(now) | set(rec["sources"]) if now.get(n) != rec["sources"].get(n))
+    libs = {p.name: _sha256(p) for p in sorted(OUT.glob("*.so"))}
+    return {"recorded": True, "nvcc": rec["nvcc"], "arch": "sm_100a", "stale_sources": stale,
+            "libraries_match": libs == rec["libraries"] and bool(libs), "libraries": sorted(libs)}
 
 
 if __name__ == "__main__":
