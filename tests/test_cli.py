@@ -111,6 +111,9 @@ def test_serve_end_to_end_oracle_backend():
         assert j["usage"]["completion_tokens"] >= 1 and j["choices"][0]["finish_reason"] in ("stop", "length")
         r2 = requests.post(base + "/v1/chat/completions", json=body, headers=h, timeout=120).json()
         assert r2["choices"][0]["message"] == j["choices"][0]["message"]          # greedy is deterministic
+        # the smoke client: health, models, a completion, a stream, two turns of the context transport
+        from titanic_flash_41_b200.api import smoke
+        assert smoke.run(base, "k") == 0
         assert requests.post(base + "/_native/shutdown", headers=h, timeout=5).status_code == 200
         assert p.wait(timeout=60) == 0
     finally:
