@@ -1,0 +1,112 @@
+"""Property tests (hypothesis) of host-side invariants: prefix matching by chained digests, the
+array-backed history text, the causal stopping rule, checkpoint positions, sequence-parallel chunking."""
+import numpy as np
+from hypothesis import given, settings
+from hypothesis import strategies as st
+
+from titanic_flash_41_b200.serve import policy
+from titanic_flash_41_b200.spec.history_lookup import HistoryLookup, _Text
+from titanic_flash_41_b200.spec.verify import causal_rows
+
+tokens = st.lists(st.integers(0, 50), min_size=0, max_size=120)
+
+
+@settings(max_examples=150, deadline=None)
+@given(tokens, tokens, st.integers(1, 16))
+def test_common_prefix_equals_the_naive_scan_with_and_without_digests(a, b, block):
+    share = min(len(a), len(b), 17)
+    b = a[:share] + b                                    # make long shared prefixes likely
+    naive = 0
+    while naive < min(len(a), len(b)) and a[naive] == b[naive]:
+        naive += 1
+    assert policy.common_prefix(a, b) == naive
+    ca, cb = policy.chain_hashes(a, block), policy.chain_hashes(b, block)
+    assert policy.common_prefix(np.asarray(a, dtype=np.int64), tuple(b), ca, cb) == naive
+    # digests of whole blocks agree exactly as far as the sequences do
+    same_blocks = sum(1 for x, y in zip(ca, cb) if x == y)
+    assert same_blocks == min(naive // block, len(ca), len(cb)) or ca[:same_blocks] == cb[:same_blocks]
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.lists(st.tuples(st.sampled_from(["append", "bulk", "truncate"]), tokens), min_size=1, max_size=12))
+def test_history_text_mirrors_a_plain_list(ops):
+    text, ref = _Text(), []
+    for op, toks in ops:
+        if op == "append":
+            for t in toks:
+                text.append(t)
+            ref += toks
+        elif op == "bulk":
+            text.extend_array(np.asarray(toks, dtype=np.int64))
+            ref += toks
+        else:
+            n = len(toks) % (len(ref) + 1)
+            text.truncate(n)
+            del ref[n:]
+        assert len(text) == len(ref)
+        if ref:
+            assert text[0] == ref[0] and text[-1] == ref[-1] and text[len(ref) // 2] == ref[len(ref) // 2]
+        lo, hi = len(ref) // 3, len(ref) - len(ref) // 4
+        assert text[lo:hi] == ref[lo:hi] and text[:] == ref and text.array(lo).tolist() == ref[lo:]
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.integers(3, 12), min_size=300, max_size=420), st.integers(0, 400))
+def test_bulk_and_single_commits_index_the_same_positions(text, split):
+    split = min(split, len(text))
+    a = HistoryLookup(text[:split], depth=4)             # a bulk part (when longer than 256) ...
+    for i in range(split, len(text)):
+        a.commit(i, [text[i]])                           # ... then token by token
+    b = HistoryLookup(depth=4)
+    for i, t in enumerate(text):
+        b.commit(i, [t])
+    assert all((x == y).all() for x, y in zip(a.tables, b.tables)) and a._raw == b._raw
+    pa, pb = a.propose(), b.propose()
+    assert (pa is None) == (pb is None) and (pa is None or (pa.tokens, pa.source_end) == (pb.tokens, pb.source_end))
+    if pa is not None:                                   # a proposal is what followed an earlier occurrence of the suffix
+        L = 8
+        assert text[pa.source_end - L: pa.source_end] == text[len(text) - L:] and pa.tokens == text[pa.source_end: pa.source_end + 4]
+
+
+conf = st.lists(st.floats(0.0, 1.0, allow_nan=False), min_size=0, max_size=6)
+
+
+@settings(max_examples=200, deadline=None)
+@given(conf, st.lists(st.floats(0.0, 1.0, allow_nan=False), min_size=1, max_size=4), st.data())
+def test_causal_rows_never_looks_past_the_stopping_confidence(c, ladder, data):
+    n = causal_rows(c, ladder)
+    assert (n == 0) == (len(c) == 0) and n <= len(c)
+    if n >= 1:
+        prod = c[0]
+        for j in range(1, n):                            # every admitted proposal cleared its threshold
+            prod *= c[j]
+            assert prod >= ladder[min(j - 1, len(ladder) - 1)]
+        for k in range(n + 1, len(c)):                   # confidences after the one that stopped do not matter
+            alt = list(c)
+            alt[k] = data.draw(st.floats(0.0, 1.0, allow_nan=False))
+            assert causal_rows(alt, ladder) == n
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(1, 300000), st.integers(0, 300000), st.sampled_from([128, 1024, 8192, 65536]))
+def test_checkpoint_positions_are_aligned_increasing_and_inside_the_new_part(prompt, start, align):
+    start = min(start, prompt - 1)
+    pos = policy.checkpoint_positions(prompt, start, align, align)
+    assert pos == sorted(set(pos)) and all(start < p < prompt and p >= align for p in pos)
+    assert all(p % align == 0 or p % 128 == 0 for p in pos)
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(1, 400000), st.sampled_from([2, 4, 8]), st.sampled_from([1, 2, 4]), st.sampled_from([0, 32768, 65536]))
+def test_sequence_parallel_chunks_cover_the_prompt_in_rank_aligned_pieces(n, world, ratio, sp_rows):
+    from types import SimpleNamespace as NS
+
+    from titanic_flash_41_b200.parallel.sp import SpPrefill
+    max_chunk, window = 16384, 128
+    ring = max(max_chunk, sp_rows) + 2 * window
+    fake = NS(W=world, eng=NS(cfg=NS(compress_ratio=ratio, max_ratio=ratio, window=window), ecfg=NS(sp_chunk_rows=sp_rows),
+                              max_chunk=max_chunk, ring=ring))
+    sizes = SpPrefill.chunk_sizes(fake, n, max_chunk)
+    assert sum(sizes) == n and all(s > 0 for s in sizes)
+    cap = min(max(max_chunk, sp_rows), max_chunk * world, ring - 2 * window)
+    assert all(s % (world * ratio) == 0 for s in sizes[:-1]) and all(s <= max(cap, world * ratio) for s in sizes)
