@@ -110,3 +110,60 @@ def test_sequence_parallel_chunks_cover_the_prompt_in_rank_aligned_pieces(n, wor
     assert sum(sizes) == n and all(s > 0 for s in sizes)
     cap = min(max(max_chunk, sp_rows), max_chunk * world, ring - 2 * window)
     assert all(s % (world * ratio) == 0 for s in sizes[:-1]) and all(s <= max(cap, world * ratio) for s in sizes)
+
+
+# ---- storage formats: decode(encode(x)) stays within the format's own error bound, and encoding what
+# was decoded is a fixed point (the formats are what the kernels read and write)
+import torch  # noqa: E402
+
+from titanic_flash_41_b200.formats import codecs  # noqa: E402
+
+rows = st.integers(1, 5)
+scale = st.floats(1e-3, 1e3)
+seed = st.integers(0, 10_000)
+
+
+def _rand(r, n, sc, sd):
+    g = torch.Generator().manual_seed(sd)
+    x = torch.randn(r, n, generator=g) * sc
+    x[0, : n // 8] = 0                                    # an all-zero group must survive
+    return x
+
+
+@settings(max_examples=60, deadline=None)
+@given(rows, scale, seed)
+def test_mxfp8_rows_round_trip_within_one_e4m3_step_and_requantise_exactly(r, sc, sd):
+    x = _rand(r, 128, sc, sd)
+    q, s = codecs.mxfp8_quant(x)
+    back = codecs.mxfp8_dequant(q, s)
+    amax = x.view(r, 4, 32).abs().amax(-1, keepdim=True).expand(r, 4, 32).reshape(r, 128)
+    assert bool(((back - x).abs() <= amax * 2 ** -3 + 1e-30).all())       # 3 mantissa bits, scale <= 2 x amax / 448
+    q2, s2 = codecs.mxfp8_quant(back)
+    assert torch.equal(codecs.mxfp8_dequant(q2, s2), back)
+
+
+@settings(max_examples=60, deadline=None)
+@given(rows, scale, seed)
+def test_mxfp4_weights_round_trip_and_requantise_exactly(r, sc, sd):
+    w = _rand(r, 64, sc, sd)
+    p, s = codecs.mxfp4_quant(w)
+    back = codecs.mxfp4_dequant(p, s)
+    amax = w.view(r, 2, 32).abs().amax(-1, keepdim=True).expand(r, 2, 32).reshape(r, 64)
+    assert bool(((back - w).abs() <= amax * 0.26 + 1e-30).all())          # e2m1: the largest gap (4 -> 6) is a third of the top code
+    p2, s2 = codecs.mxfp4_quant(back)
+    assert torch.equal(codecs.mxfp4_dequant(p2, s2), back)
+    assert torch.equal(codecs.unpack_nibbles(codecs.pack_nibbles(codecs.unpack_nibbles(p))), codecs.unpack_nibbles(p))
+
+
+@settings(max_examples=40, deadline=None)
+@given(rows, st.floats(1e-2, 1e2), seed)
+def test_kv_row_formats_round_trip_and_are_fixed_points(r, sc, sd):
+    k = _rand(r, 128, sc, sd)
+    for enc, dec, tol in ((codecs.kv_v41_encode, codecs.kv_v41_decode, 2 ** -3),
+                          (codecs.kv_v41fp4_encode, codecs.kv_v41fp4_decode, 0.3),
+                          (codecs.index_key_encode, codecs.index_key_decode, 0.3)):
+        row = enc(k)
+        back = dec(row, 128)
+        assert row.dtype == torch.uint8 and back.shape == k.shape
+        assert bool(((back - k).abs() <= k.abs().amax(-1, keepdim=True) * tol + 1e-30).all())
+        assert torch.equal(dec(enc(back), 128), back)
