@@ -167,3 +167,52 @@ def test_kv_row_formats_round_trip_and_are_fixed_points(r, sc, sd):
         assert row.dtype == torch.uint8 and back.shape == k.shape
         assert bool(((back - k).abs() <= k.abs().amax(-1, keepdim=True) * tol + 1e-30).all())
         assert torch.equal(dec(enc(back), 128), back)
+
+
+# ---- scheduler: random submissions, cancellations, admissions and releases
+from titanic_flash_41_b200.serve.scheduler import Job, QueueFull, Scheduler  # noqa: E402
+
+sched_ops = st.lists(st.tuples(st.sampled_from(["fg", "bg", "cancel", "admit", "release", "lease"]), st.integers(0, 7)),
+                     min_size=1, max_size=60)
+
+
+@settings(max_examples=150, deadline=None)
+@given(sched_ops, st.integers(1, 4))
+def test_scheduler_never_overfills_regions_and_serves_each_class_in_order(ops, regions):
+    s = Scheduler(regions, 5, 3)
+    events, jobs, admitted, n = [], [], [], 0
+    now = 0.0
+    for op, k in ops:
+        now += 1.0
+        if op in ("fg", "bg"):
+            j = Job(f"j{n}", [1], 1, background=(op == "bg"), emit=lambda kind, p, _n=n: events.append((_n, kind)))
+            n += 1
+            try:
+                s.submit(j)
+                jobs.append(j)
+            except QueueFull as e:
+                assert str(e) in ("queue_full", "background_queue_full")
+                assert len(s.bg if j.background else s.fg) >= (3 if j.background else 5)
+        elif op == "cancel" and jobs:
+            jobs[k % len(jobs)].cancelled.set()
+        elif op == "admit":
+            new = s.admit(now=now + 1e9)                       # far future: no lease holds the background back
+            admitted += new
+            assert not any(j.cancelled.is_set() for j in new)
+            assert len({j.region for j in s.active.values()}) == len(s.active) <= regions
+        elif op == "release" and s.active:
+            j = list(s.active.values())[k % len(s.active)]
+            s.release(j)
+            assert j.region not in s.active or s.active[j.region] is not j
+        elif op == "lease":
+            assert s.priority_lease(float(k)) >= 0.0
+        assert sorted(s.free_regions() + list(s.active)) == list(range(regions))
+    # every admitted job was submitted once, in submission order within its class, and none was cancelled at admission
+    order = {id(j): i for i, j in enumerate(jobs)}
+    for cls in (False, True):
+        seq = [order[id(j)] for j in admitted if j.background == cls]
+        assert seq == sorted(seq) and len(set(seq)) == len(seq)
+    # a job cancelled while it waited got a terminal event instead of a region
+    dropped = {i for i, kind in events if kind == "error"}
+    assert all(jobs_i.cancelled.is_set() for jobs_i in jobs if int(jobs_i.id[1:]) in dropped)
+    assert not any(int(j.id[1:]) in dropped for j in admitted)
