@@ -216,3 +216,35 @@ def test_scheduler_never_overfills_regions_and_serves_each_class_in_order(ops, r
     dropped = {i for i, kind in events if kind == "error"}
     assert all(jobs_i.cancelled.is_set() for jobs_i in jobs if int(jobs_i.id[1:]) in dropped)
     assert not any(int(j.id[1:]) in dropped for j in admitted)
+
+
+# ---- session cache: random insertions of images of related and unrelated prefixes
+from titanic_flash_41_b200.serve import state_image as SI  # noqa: E402
+from titanic_flash_41_b200.serve.session_cache import SessionCache  # noqa: E402
+
+cache_ops = st.lists(st.tuples(st.integers(0, 3), st.integers(1, 40), st.sampled_from(["complete", "checkpoint", "optional"]),
+                               st.integers(1, 6)), min_size=1, max_size=40)
+
+
+@settings(max_examples=120, deadline=None)
+@given(cache_ops, st.integers(2, 6), st.integers(8, 40))
+def test_session_cache_keeps_its_bounds_and_finds_the_longest_cached_prefix(ops, slots, budget_kb):
+    family = [[(7 * f + 3 * i) % 50 for i in range(64)] for f in range(4)]         # four conversations
+    cache = SessionCache(slots=slots, budget_bytes=budget_kb * 1024, host_budget_bytes=1 << 30, park_after=2)
+    for fam, length, kind, kb in ops:
+        toks = family[fam][:length]
+        img = SI.capture(np.asarray(toks, dtype=np.int64) if length % 2 else toks, [("x", torch.zeros(kb * 256))], kind)
+        stored = cache.insert(img, optional=(kind == "optional"), completed=(kind == "complete"))
+        assert len(cache.entries) <= slots
+        assert cache.device_bytes() <= budget_kb * 1024 or not stored
+        # no two entries hold the same prefix
+        keys = [(e.image.length, bytes(np.asarray(e.image.tokens, dtype=np.int64).tobytes()), e.image.media) for e in cache.entries]
+        assert len(set(keys)) == len(keys)
+        # lookups: the longest entry that is a prefix of the prompt (and of the same conversation family)
+        for f in range(4):
+            prompt = family[f][:50]
+            best = cache.best_match(np.asarray(prompt, dtype=np.int64))
+            want = max((e.image.length for e in cache.entries
+                        if e.image.length <= 50 and list(np.asarray(e.image.tokens)) == prompt[: e.image.length]), default=None)
+            assert (best.image.length if best else None) == want
+        assert cache.longest_shared(family[fam][:60]) >= (length if stored else 0) or not stored
