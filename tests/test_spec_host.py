@@ -250,3 +250,44 @@ def test_rolling_hash_lookup_equals_a_brute_force_search():
     assert h._raw == q._raw and len(h.tokens) == len(q.tokens) == 600
     pa, pb = h.propose(), q.propose()
     assert pa is None or pb is None or pa.tokens[:1] == text[pa.source_end: pa.source_end + 1]
+
+
+@pytest.mark.parametrize("g,stop", [(1, None), (3, None), (3, "causal"), (2, "point")])
+def test_block_verification_on_the_host_preserves_the_target_law(g, stop):
+    """Monte-Carlo over the host recurrence (the oracle of the sampling kernels): the first token a round
+    emits follows the (temperature / nucleus modified) target law, for full blocks, for blocks shortened by
+    a rule that only looks at what precedes each proposal, and for point-mass (copy) proposals."""
+    import random
+
+    from titanic_flash_41_b200.spec import verify
+    V, N = 7, 24000
+    gen = torch.Generator().manual_seed(4)
+    P = verify.modified_law(torch.randn(g + 1, V, generator=gen) * 1.5, 0.8, 0.9)
+    Q = verify.modified_law(torch.randn(g, V, generator=gen) * 1.5, 0.8, 0.9)
+    rnd = random.Random(9)
+    counts = torch.zeros(V, dtype=torch.float64)
+    lengths = [0] * (g + 1)
+    for _ in range(N):
+        if stop == "point":
+            props = [int(Q[i].argmax()) for i in range(g)]           # the copy source names its tokens with certainty
+            Qn = None
+        else:
+            props = [verify.sample_from(Q[i], rnd.random()) for i in range(g)]
+            Qn = Q
+        n = g
+        if stop == "causal":
+            # the length is decided from the tokens BEFORE each proposal only (here: a fake confidence of the previous token)
+            conf = [0.9] + [0.3 + 0.1 * (props[i - 1] % 5) for i in range(1, g)]
+            n = verify.causal_rows(conf, (0.3, 0.2))
+        lengths[n] += 1
+        Pn = P[: n + 1]
+        Qb = None if Qn is None else Qn[:n]
+        tau, nxt = verify.block_verify(Pn, Qb, props[:n], [rnd.random() for _ in range(n)], rnd.random())
+        first = props[0] if tau >= 1 else nxt
+        counts[first] += 1
+    emp = counts / N
+    # three standard errors of the largest cell, plus the nucleus cells that must stay empty
+    assert float((emp - P[0]).abs().max()) < 3.5 * (0.25 / N) ** 0.5 + 1e-9, (emp, P[0])
+    assert bool((emp[P[0] == 0] == 0).all())
+    if stop == "causal":
+        assert sum(1 for c in lengths if c > 0) >= 2              # blocks of different lengths really occurred
