@@ -397,9 +397,13 @@ def test_long_context_stress_script_as_two_cpu_ranks():
     import os
     import subprocess
     import sys
+    import socket
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as so:                      # a free port for the rendezvous (the control channel takes port + 13)
+        so.bind(("127.0.0.1", 0))
+        port = so.getsockname()[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29671", os.path.join(root, "benchmarks", "bench_long_context.py"), "--backend", "oracle",
+           "--master-port", str(port), os.path.join(root, "benchmarks", "bench_long_context.py"), "--backend", "oracle",
            "--sessions", "2", "--regions", "2", "--target", "128", "--grow", "64", "--short", "2", "--short-tokens", "16",
            "--follow", "16", "--new-tokens", "3", "--chunk", "32", "--checkpoint", "32", "--cache-slots", "16"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
