@@ -284,3 +284,38 @@ def test_plan_and_run_file_commands(tmp_path, capsys):
     assert rows["a"]["tokens"] == rows["c"]["tokens"] and len(rows["a"]["tokens"]) == 6
     assert rows["a"]["cache_n"] == 0 and rows["c"]["cache_n"] >= 64              # the repeat came from the cache
     assert rows["b"]["finish_reason"] in ("stop", "length") and isinstance(rows["b"]["text"], str)
+
+
+def test_preflight_reports_every_check(tmp_path, capsys, monkeypatch):
+    """`preflight`: the checks a launch depends on, each with its finding; on a box without GPUs the GPU
+    check fails and the command exits 1; with a fake probe of eight peered B200s everything passes; a busy
+    port, an oversized context and a checkpoint of another model are each reported."""
+    import socket
+
+    from titanic_flash_41_b200.models import loader, oracle
+    assert cli.main(["preflight", "--gpus", "2", "--port", str(_free_port()), "--master-port", str(_free_port())]) == 1
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["ok"] is False and out["checks"]["gpus"]["ok"] is False and out["checks"]["library"]["ok"] is True
+    devices = [{"index": i, "name": "B200", "sm": "10.0", "sms": 148, "memory_gib": 178.4,
+                "peers": [j for j in range(8) if j != i]} for i in range(8)]
+    monkeypatch.setattr(cli, "probe", lambda: {"devices": devices, "sm_100": True, "library_built": True})
+    p1, p2 = _free_port(), _free_port()
+    assert cli.main(["preflight", "--gpus", "8", "--max-context", "1000000", "--port", str(p1), "--master-port", str(p2)]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["ok"] and set(out["checks"]) >= {"gpus", "peer_access", "sm_100", "library", "memory", "context", "ports"}
+    # one GPU cannot hold the model plus a large session cache; a taken port; more context than the model has positions
+    with socket.socket() as so:
+        so.bind(("127.0.0.1", 0))
+        taken = so.getsockname()[1]
+        assert cli.main(["preflight", "--gpus", "1", "--device-cache-gib", "40", "--port", str(taken), "--master-port", str(p2),
+                         "--max-context", "2000000"]) == 1
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["checks"]
+    assert not out["memory"]["ok"] and not out["ports"]["ok"] and taken in out["ports"]["detail"]["busy"] and not out["context"]["ok"]
+    # a checkpoint that does not match the configuration
+    cfg = tiny_config(dense_quant="fp8_block128", expert_quant="mxfp4")
+    ck = os.path.join(str(tmp_path), "ck")
+    loader.export_checkpoint(oracle.init_weights(cfg, seed=1), cfg, ck)
+    assert cli.main(["preflight", "--gpus", "1", "--preset", "flash-b200", "--checkpoint", ck, "--port", str(p1),
+                     "--master-port", str(p2)]) == 1
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["checks"]
+    assert out["checkpoint"]["ok"] is False and out["gpus"]["ok"] is True

@@ -113,6 +113,17 @@ def build_parser() -> argparse.ArgumentParser:
     pm.add_argument("--chunk", type=int, default=16384, help="rows of a prefill chunk on one rank")
     pm.add_argument("--device-cache-gib", type=float, default=8.0, help="device budget of the session cache")
     pm.add_argument("--device-gib", type=float, default=180.0, help="memory of one GPU")
+    pf = sub.add_parser("preflight", help="checks before a cohort is launched: GPUs and peer access, the native library and "
+                        "its provenance, the memory plan, the ports, the checkpoint (reference: deploy/fleet.py preflight)")
+    pf.add_argument("--preset", choices=sorted(PRESETS), default="flash-b200")
+    pf.add_argument("--model-config")
+    pf.add_argument("--checkpoint")
+    pf.add_argument("--gpus", type=int, default=1)
+    pf.add_argument("--regions", type=int, default=4)
+    pf.add_argument("--max-context", type=int, default=131072)
+    pf.add_argument("--port", type=int, default=8000)
+    pf.add_argument("--master-port", type=int, default=29511)
+    pf.add_argument("--device-cache-gib", type=float, default=8.0)
     rf = sub.add_parser("run-file", help="file-driven finite run: requests from a JSONL file through the serving stack "
                         "(scheduler, worker, cache), results to a JSONL file; no HTTP")
     _common(rf)
@@ -333,6 +344,54 @@ def serve_main(args) -> int:
     return 0
 
 
+def preflight(args) -> dict:
+    """Everything that can be checked before ``launch``: each check is (ok, detail); ``ok`` is their AND."""
+    import socket
+
+    from .utils import build
+    from .utils.memory import plan_device_memory
+    checks: Dict[str, dict] = {}
+    info = probe()
+    n = len(info["devices"])
+    checks["gpus"] = {"ok": n >= args.gpus, "detail": f"{n} visible, {args.gpus} wanted"}
+    if n >= args.gpus and args.gpus > 1:
+        missing = [(d["index"], j) for d in info["devices"][: args.gpus] for j in range(args.gpus)
+                   if j != d["index"] and j not in d["peers"]]
+        checks["peer_access"] = {"ok": not missing, "detail": f"{len(missing)} device pairs without peer access"}
+    if n:
+        checks["sm_100"] = {"ok": bool(info.get("sm_100")), "detail": sorted({d["sm"] for d in info["devices"]})}
+    prov = build.provenance()
+    checks["library"] = {"ok": info["library_built"] and prov["recorded"] and not prov["stale_sources"] and prov["libraries_match"],
+                         "detail": {"built": info["library_built"], "stale_sources": prov["stale_sources"],
+                                    "libraries_match": prov["libraries_match"]}}
+    cfg = model_config(args)
+    w = args.gpus
+    ecfg = EngineConfig(tp=w, regions=args.regions, max_context=args.max_context,
+                        sp_chunk_rows=min(max(EngineConfig().prefill_widths) * w, 65536) if w > 1 else 0)
+    need = plan_device_memory(cfg, ecfg, w)["total"] / 2 ** 30 + args.device_cache_gib + (7.0 if w == 1 else 21.0)
+    have = min((d["memory_gib"] for d in info["devices"][: args.gpus]), default=180.0)
+    checks["memory"] = {"ok": need <= have, "detail": f"{need:.1f} GiB needed per GPU, {have:.1f} GiB there"}
+    checks["context"] = {"ok": args.max_context <= cfg.max_positions, "detail": f"{args.max_context} of {cfg.max_positions} positions"}
+    busy = []
+    for port in (args.port, args.master_port, args.master_port + 1):
+        with socket.socket() as so:
+            try:
+                so.bind(("127.0.0.1", port))
+            except OSError:
+                busy.append(port)
+    checks["ports"] = {"ok": not busy, "detail": {"busy": busy}}
+    if args.checkpoint:
+        try:
+            from .formats import layout
+            from .formats.safetensors import Checkpoint
+            ck = Checkpoint.scan(args.checkpoint)
+            layout.validate_checkpoint(ck, cfg)
+            checks["checkpoint"] = {"ok": True, "detail": f"{len(ck.tensors)} tensors match the configuration"}
+        except Exception as e:  # noqa: BLE001  (a preflight reports, it does not raise)
+            checks["checkpoint"] = {"ok": False, "detail": str(e)}
+    return {"ok": all(c["ok"] for c in checks.values()), "checks": checks}
+
+
 def run_file(args) -> int:
     """Requests from a JSONL file through the serving stack of ONE process (the reference's
     file-driven finite run, src/main.rs resident-token-peer): every request is admitted by the
@@ -447,6 +506,10 @@ def utility(args) -> Optional[int]:
         return 0
     if args.cmd == "run-file":
         return run_file(args)
+    if args.cmd == "preflight":
+        report = preflight(args)
+        print(json.dumps(report))
+        return 0 if report["ok"] else 1
     if args.cmd == "plan-memory":
         from .utils.memory import plan_device_memory
         cfg = model_config(args)
@@ -497,7 +560,7 @@ def utility(args) -> Optional[int]:
 def main(argv: Optional[list] = None) -> int:
     args = build_parser().parse_args(argv)
     if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke", "verify-staged",
-                    "pack-engram", "plan", "run-file", "plan-memory"):
+                    "pack-engram", "plan", "run-file", "plan-memory", "preflight"):
         return utility(args)
     if args.cmd == "probe":
         print(json.dumps(probe()))
