@@ -319,3 +319,10 @@ def test_preflight_reports_every_check(tmp_path, capsys, monkeypatch):
                      "--master-port", str(p2)]) == 1
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["checks"]
     assert out["checkpoint"]["ok"] is False and out["gpus"]["ok"] is True
+
+
+def test_bench_frontend_command(capsys):
+    assert cli.main(["bench-frontend", "--turns", "4", "--chars", "3000", "--vocab", "1024"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["cold"]["last_prompt_tokens"] == out["warm"]["last_prompt_tokens"] > 1000
+    assert out["warm"]["prompt_tokens_per_s"] > out["cold"]["prompt_tokens_per_s"] > 0      # the region cache pays

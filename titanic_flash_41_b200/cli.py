@@ -113,6 +113,12 @@ def build_parser() -> argparse.ArgumentParser:
     pm.add_argument("--chunk", type=int, default=16384, help="rows of a prefill chunk on one rank")
     pm.add_argument("--device-cache-gib", type=float, default=8.0, help="device budget of the session cache")
     pm.add_argument("--device-gib", type=float, default=180.0, help="memory of one GPU")
+    bf = sub.add_parser("bench-frontend", help="protocol front end alone: normalise + render + tokenise a growing conversation, "
+                        "cold and with the region cache warm (requests / s, prompt tokens / s)")
+    bf.add_argument("--tokenizer")
+    bf.add_argument("--vocab", type=int, default=129280)
+    bf.add_argument("--turns", type=int, default=16)
+    bf.add_argument("--chars", type=int, default=20000, help="characters of document text added per turn")
     pf = sub.add_parser("preflight", help="checks before a cohort is launched: GPUs and peer access, the native library and "
                         "its provenance, the memory plan, the ports, the checkpoint (reference: deploy/fleet.py preflight)")
     pf.add_argument("--preset", choices=sorted(PRESETS), default="flash-b200")
@@ -506,6 +512,35 @@ def utility(args) -> Optional[int]:
         return 0
     if args.cmd == "run-file":
         return run_file(args)
+    if args.cmd == "bench-frontend":
+        import random
+        import time as _t
+
+        from .api.server import Frontend
+        from .api.tokenizer import load_tokenizer
+        tok = load_tokenizer(args.tokenizer, args.vocab)
+        rnd = random.Random(0)
+        words = ["".join(rnd.choice("abcdefghijklmnopqrstuvwxyz") for _ in range(rnd.randrange(2, 10))) for _ in range(4000)]
+        doc = lambda: " ".join(rnd.choice(words) for _ in range(args.chars // 6))
+        msgs = [{"role": "system", "content": "You are terse."}]
+        out = {}
+        for name in ("cold", "warm"):
+            front = Frontend(tok, 1 << 22)
+            rnd.seed(1)
+            conv = list(msgs)
+            t0, ntok, nreq = _t.perf_counter(), 0, 0
+            for turn in range(args.turns):
+                conv = conv + [{"role": "user", "content": doc()}]
+                if name == "cold":
+                    front = Frontend(tok, 1 << 22)           # nothing remembered between requests
+                _, tokens, _, _ = front.prepare({"model": "x", "messages": conv, "max_tokens": 8})
+                ntok += len(tokens)
+                nreq += 1
+                conv = conv + [{"role": "assistant", "content": "ok"}]
+            dt = _t.perf_counter() - t0
+            out[name] = {"requests_per_s": round(nreq / dt, 2), "prompt_tokens_per_s": round(ntok / dt), "last_prompt_tokens": len(tokens)}
+        print(json.dumps(out))
+        return 0
     if args.cmd == "preflight":
         report = preflight(args)
         print(json.dumps(report))
@@ -560,7 +595,7 @@ def utility(args) -> Optional[int]:
 def main(argv: Optional[list] = None) -> int:
     args = build_parser().parse_args(argv)
     if args.cmd in ("encode-chat", "decode-tokens", "parse-completion", "config-validate", "scan", "smoke", "verify-staged",
-                    "pack-engram", "plan", "run-file", "plan-memory", "preflight"):
+                    "pack-engram", "plan", "run-file", "plan-memory", "preflight", "bench-frontend"):
         return utility(args)
     if args.cmd == "probe":
         print(json.dumps(probe()))
