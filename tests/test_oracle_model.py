@@ -85,13 +85,20 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _tp_worker(rank, world, port, q, moe_parallel):
+def _tp_config(variant):
+    if variant == "mixed":                       # two compressed streams with their own ratios
+        return tiny_config(n_layers=3, compress_ratio=1, compress_ratios=(2, 1), kv_source_layers=(0, 1),
+                           index_source_layers=(0, 1, 2), index_topk=8)
+    return tiny_config()
+
+
+def _tp_worker(rank, world, port, q, moe_parallel, variant="plain"):
     import torch.distributed as dist
     from titanic_flash_41_b200.parallel.comm import DistComm
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(2)
-    cfg = tiny_config()
+    cfg = _tp_config(variant)
     W = oracle.shard_weights(oracle.init_weights(cfg, 0), cfg, rank, world, moe_parallel)
     m = oracle.OracleModel(cfg, W, DistComm(), moe_parallel)
     toks, logits = oracle.greedy_generate(m, _prompts(cfg), 16)
@@ -101,17 +108,18 @@ def _tp_worker(rank, world, port, q, moe_parallel):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("moe_parallel", ["ep", "tp"])
-def test_tp2_gloo_matches_single_rank(moe_parallel):
+@pytest.mark.parametrize("moe_parallel,variant", [("ep", "plain"), ("tp", "plain"), ("ep", "mixed")])
+def test_tp2_gloo_matches_single_rank(moe_parallel, variant):
     """Tiny 2-layer MoE decoder, batch 2, 64 prompt ids then 16 greedy steps: logits of the
-    TP=2 gloo run within 1e-4 of the single-rank run."""
-    cfg = tiny_config()
+    TP=2 gloo run within 1e-4 of the single-rank run ("mixed": three layers, two compressed streams
+    with their own ratios)."""
+    cfg = _tp_config(variant)
     ref = oracle.OracleModel(cfg, oracle.init_weights(cfg, 0))
     toks1, logits1 = oracle.greedy_generate(ref, _prompts(cfg), 16)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q, moe_parallel)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q, moe_parallel, variant)) for r in range(2)]
     for p in procs:
         p.start()
     toks2, logits2 = q.get(timeout=300)
