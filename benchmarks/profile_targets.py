@@ -164,4 +164,7 @@ def prep():
 
 
 if __name__ == "__main__":
-    {"allreduce": allreduce, "sampler": sampler, "attention": attention, "index": index, "prep": prep}[sys.argv[1]]()
+    targets = {"allreduce": allreduce, "sampler": sampler, "attention": attention, "index": index, "prep": prep}
+    if len(sys.argv) != 2 or sys.argv[1] not in targets:
+        sys.exit("usage: python benchmarks/profile_targets.py {" + " | ".join(sorted(targets)) + "}")
+    targets[sys.argv[1]]()
