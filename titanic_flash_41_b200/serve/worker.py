@@ -98,10 +98,11 @@ class Worker:
         if toks is None:
             self.control.command(self.encode(cmd))
             return
-        head = {k: v for k, v in cmd.items() if k != "tokens"}
+        head = {k: v for k, v in cmd.items() if k not in ("tokens", "tokens_arr")}
         head["n_tokens"] = len(toks)
         self.control.command(self.encode(head))
-        blob = np.asarray(toks, dtype="<i4").tobytes()
+        arr = cmd.get("tokens_arr")
+        blob = (arr if arr is not None else np.asarray(toks)).astype("<i4").tobytes()
         for i in range(0, len(blob), self.FRAME):
             self.control.command(blob[i:i + self.FRAME])
 
@@ -120,7 +121,8 @@ class Worker:
             blob = bytearray()
             while len(blob) < 4 * n:
                 blob += self.control.command(None)
-            cmd["tokens"] = np.frombuffer(bytes(blob[:4 * n]), dtype="<i4").tolist()
+            arr = np.frombuffer(bytes(blob[:4 * n]), dtype="<i4").astype(np.int64)
+            cmd["tokens"], cmd["tokens_arr"] = arr.tolist(), arr        # the array is what Begin compares and hashes
         return cmd
 
     def _digest(self) -> bytes:
@@ -171,8 +173,11 @@ class Worker:
     _pending: List[Job] = []
 
     def _begin_cmd(self, j: Job) -> Dict[str, Any]:
+        import numpy as np
         self.jobs[j.id] = j
-        return {"op": "begin", "id": j.id, "region": j.region, "tokens": j.tokens, "limit": j.max_new_tokens,
+        # one conversion of the prompt for the wire, the cache digests, the images and the history index
+        return {"op": "begin", "id": j.id, "region": j.region, "tokens": j.tokens,
+                "tokens_arr": np.asarray(j.tokens, dtype=np.int64), "limit": j.max_new_tokens,
                 "temperature": j.temperature, "top_p": j.top_p, "seed": j.seed, "media": j.media,
                 "images": len(j.images)}
 
@@ -373,10 +378,13 @@ class Worker:
         from ..utils import memory as _mem
         stall0 = _mem.pressure_snapshot()          # host stall counters around the prefill (memory / io / cpu pressure)
         import numpy as np
-        region, prompt = cmd["region"], list(cmd["tokens"])
+        region = cmd["region"]
+        prompt = cmd["tokens"] if isinstance(cmd["tokens"], list) else list(cmd["tokens"])
         # one integer array of the prompt for everything that compares, hashes or stores it (a
         # million-token list is converted once, not once per cache entry)
-        parr = np.asarray(prompt, dtype=np.int64)
+        parr = cmd.get("tokens_arr")
+        if parr is None:
+            parr = np.asarray(prompt, dtype=np.int64)
         job = self.jobs.get(cmd["id"])
         self.requests += 1
         if len(prompt) + 1 >= self.b.max_context:
